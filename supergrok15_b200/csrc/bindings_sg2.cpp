@@ -1,0 +1,116 @@
+// Bindings of the SuperGrok v2 step pipeline (sort, scan, element step).
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include "bindings_decl.h"
+#include "mt_host.h"
+
+namespace sg {
+void sg2_upload_weights(const float* packed_dev, cudaStream_t s);
+void sg2_sqnorm(int dtype, const MTArgs& a, float* partials, cudaStream_t s);
+void sg2_prep(int dtype, const MTArgs& a, const float* tclip, float* g_packed, float* s_packed, uint32_t* keys, uint32_t* vals, cudaStream_t s);
+void sg2_gather(const uint32_t* vals_sorted, const float* g_packed, const float* s_packed, float* gs_sorted, int64_t total, cudaStream_t s);
+void sg2_scan(const void* items_dev, int n_items, int dir1_start, const void* tds_dev, int n_td, bool any_multi, const float* gs_sorted,
+              const uint32_t* vals_sorted, float* agg, float* carry, float* ctx, cudaStream_t s);
+void sg2_elem(int dtype, const MTArgs& a, float beta2, float lr, float wd_eff, float eps, float rescale, float lamb_eff, const float* g_packed,
+              const float* s_packed, const float* ctx, int* expert_counts, cudaStream_t s);
+size_t sg2_item_bytes();
+size_t sg2_td_bytes();
+}
+
+namespace sgb {
+namespace {
+using at::Tensor;
+using TL = std::vector<Tensor>;
+
+uint32_t* u32(const Tensor& t) { return reinterpret_cast<uint32_t*>(t.data_ptr()); }
+
+// ws: dict of workspace tensors allocated by the caller (see ops/sg2.py for the sizes)
+int64_t sg2_prepare(const TL& grads, const TL& sharps, const std::vector<int64_t>& offsets, int64_t total, Tensor seg_off, double clip,
+                    py::dict ws) {
+    TORCH_CHECK(!grads.empty(), "no gradients");
+    c10::cuda::CUDAGuard guard(grads[0].device());
+    cudaStream_t st = at::cuda::getCurrentCUDAStream();
+    const int dt = dtype_code(grads[0]);
+    auto W = [&](const char* k) { return ws[k].cast<Tensor>(); };
+    Tensor partials = W("partials"), tnorm = W("tnorm"), tclip = W("tclip"), g = W("g"), s = W("s");
+    Tensor k0 = W("keys0"), k1 = W("keys1"), v0 = W("vals0"), v1 = W("vals1"), hist = W("hist"), tot = W("tot"), gs = W("gs");
+    const int n = (int)grads.size();
+    for_each_launch({{}, grads}, {}, nullptr, [&](sg::MTArgs& a) {
+        sg::sg2_sqnorm(dt, a, partials.data_ptr<float>(), st);
+        sg::mt_finalize_per_tensor(a, partials.data_ptr<float>(), tnorm.data_ptr<float>(), st);
+    });
+    sg::scalar_finalize(sg::SC_SG2_CLIP, tnorm.data_ptr<float>(), n, tclip.data_ptr<float>(), (float)clip, 0.f, 0.f, st);
+    for_each_launch({{}, grads, sharps}, {}, &offsets, [&](sg::MTArgs& a) {
+        sg::sg2_prep(dt, a, tclip.data_ptr<float>(), g.data_ptr<float>(), s.data_ptr<float>(), u32(k0), u32(v0), st);
+    });
+    int cur = 0;
+    sg::sg2_segmented_sort(u32(k0), u32(k1), u32(v0), u32(v1), u32(hist), u32(tot), seg_off.data_ptr<int64_t>(), n, total, &cur, st);
+    const uint32_t* vs = cur ? u32(v1) : u32(v0);
+    sg::sg2_gather(vs, g.data_ptr<float>(), s.data_ptr<float>(), gs.data_ptr<float>(), total, st);
+    return cur;
+}
+
+void sg2_scan(Tensor items, int64_t n_items, int64_t dir1_start, Tensor tds, int64_t n_td, bool any_multi, int64_t sorted_buf, py::dict ws) {
+    c10::cuda::CUDAGuard guard(items.device());
+    cudaStream_t st = at::cuda::getCurrentCUDAStream();
+    auto W = [&](const char* k) { return ws[k].cast<Tensor>(); };
+    const uint32_t* vs = sorted_buf ? u32(W("vals1")) : u32(W("vals0"));
+    sg::sg2_scan(items.data_ptr(), (int)n_items, (int)dir1_start, tds.data_ptr(), (int)n_td, any_multi, W("gs").data_ptr<float>(), vs,
+                 W("agg").data_ptr<float>(), W("carry").data_ptr<float>(), W("ctx").data_ptr<float>(), st);
+}
+
+void sg2_elem(const TL& params, const TL& ms, const TL& vs, const TL& mus, const TL& grus, const std::vector<std::vector<double>>& ts,
+              const std::vector<int64_t>& offsets, double beta2, double lr, double wd_eff, double eps, double rescale, double lamb_eff,
+              c10::optional<Tensor> expert_counts, py::dict ws) {
+    c10::cuda::CUDAGuard guard(params[0].device());
+    cudaStream_t st = at::cuda::getCurrentCUDAStream();
+    const int dt = dtype_code(params[0]);
+    auto W = [&](const char* k) { return ws[k].cast<Tensor>(); };
+    Tensor g = W("g"), s = W("s"), ctx = W("ctx");
+    int* ec = expert_counts.has_value() ? expert_counts->data_ptr<int>() : nullptr;
+    for_each_launch({params, ms, vs, mus, grus}, ts, &offsets, [&](sg::MTArgs& a) {
+        sg::sg2_elem(dt, a, (float)beta2, (float)lr, (float)wd_eff, (float)eps, (float)rescale, (float)lamb_eff, g.data_ptr<float>(),
+                     s.data_ptr<float>(), ctx.data_ptr<float>(), ec, st);
+    });
+}
+
+void sg2_upload_weights(Tensor packed) {
+    TORCH_CHECK(packed.is_cuda() && packed.scalar_type() == at::kFloat && packed.numel() == sg::SG2Pack::TOTAL && packed.is_contiguous(),
+                "packed weights must be a contiguous fp32 CUDA vector of ", sg::SG2Pack::TOTAL, " floats");
+    c10::cuda::CUDAGuard guard(packed.device());
+    sg::sg2_upload_weights(packed.data_ptr<float>(), at::cuda::getCurrentCUDAStream());
+}
+
+// stand-alone stable segmented argsort of |x| (testing / bilevel): returns the index of the buffer holding the result
+int64_t sg2_sort(Tensor keys0, Tensor keys1, Tensor vals0, Tensor vals1, Tensor hist, Tensor tot, Tensor seg_off, int64_t n_seg, int64_t total) {
+    c10::cuda::CUDAGuard guard(keys0.device());
+    int cur = 0;
+    sg::sg2_segmented_sort(u32(keys0), u32(keys1), u32(vals0), u32(vals1), u32(hist), u32(tot), seg_off.data_ptr<int64_t>(), (int)n_seg, total,
+                           &cur, at::cuda::getCurrentCUDAStream());
+    return cur;
+}
+
+py::dict sg2_layout() {
+    py::dict d;
+    using P = sg::SG2Pack;
+#define L(X) d[#X] = (int)P::X;
+    L(IN_W) L(IN_B) L(DIR0) L(DIR1) L(D_INPROJ) L(D_DTW) L(D_DTB) L(D_BW) L(D_CW) L(D_ALOG) L(D_D) L(D_ROPE) L(D_OUT) L(DIR_SIZE)
+    L(GRU_WZ) L(GRU_WR) L(GRU_WH) L(GRU_BZ) L(GRU_BR) L(GRU_BH) L(PQ) L(KA) L(KB) L(EW1) L(EB1) L(EW2) L(EB2) L(TOTAL)
+#undef L
+    d["item_bytes"] = (int)sg::sg2_item_bytes();
+    d["td_bytes"] = (int)sg::sg2_td_bytes();
+    d["sort_tile"] = 4096;
+    return d;
+}
+}  // namespace
+
+void register_sg2(pybind11::module_& m) {
+    m.def("sg2_prepare", &sg2_prepare);
+    m.def("sg2_scan", &sg2_scan);
+    m.def("sg2_elem", &sg2_elem);
+    m.def("sg2_upload_weights", &sg2_upload_weights);
+    m.def("sg2_sort", &sg2_sort);
+    m.def("sg2_layout", &sg2_layout);
+    m.def("sg2_sort_blocks", [](int64_t total) { return (int64_t)sg::sg2_sort_blocks(total); });
+}
+}  // namespace sgb

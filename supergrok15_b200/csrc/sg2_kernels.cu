@@ -1,0 +1,540 @@
+// SuperGrok v2 optimizer step on sm_100a: prep, gather, bidirectional Mamba-3 scan, element step.
+//
+// What the reference does with ~450 launches and ~110 host syncs per step
+// (csrc/supergrok2_mamba_peer_kernels.cu:1754-2117, grokking_optimizers/supergrok2.py:310-345)
+// is one fixed sequence of launches here, independent of the number of tensors:
+//
+//   prep      per-tensor clip + NaN scrub, packed fp32 gradient / sharpness, sort keys
+//   sort      sg2_sort.cu
+//   gather    sorted (g, s) pairs
+//   scan 1    per-chunk aggregate 2x2 affine maps        (only tensors split into several chunks)
+//   scan 2    carry-in state of every chunk              (tiny)
+//   scan 3    re-run every chunk from its carry-in, apply SiLU gate / D skip / out_proj and write the
+//             8-float context straight to the element's ORIGINAL index (no un-sort gathers)
+//   elem      GRU + 4-head product-key routing + expert MLPs (shared memory) + mu EMA + Adam
+//
+// Scan decomposition: the sequence of a tensor is cut into chunks of `chunk_len` timesteps; an item is
+// (tensor, direction, chunk).  Sixteen lanes (one per d_inner column) own an item; each lane keeps the
+// 16 state values of its column (8 RoPE pairs) in registers, so y is accumulated in registers and
+// nothing is read-modify-written in global memory.  Per 16-timestep tile the lanes first act as
+// "one lane per timestep" to compute x, z, dt, B, C with warp-uniform weights from constant memory,
+// park them in shared memory, then act as "one lane per column" for the recurrence.
+// The meta-net weights (11,580 floats) live in __constant__ memory; the 144 experts are staged in
+// shared memory by the element kernel because their index is data dependent.
+#include "sg_native.h"
+#include "optim_math.cuh"
+
+namespace sg {
+
+__constant__ float c_w[SG2Pack::TOTAL];
+
+namespace {
+
+using P = SG2Pack;
+constexpr int TILE_T = 16;                 // timesteps per tile
+constexpr int ROW = 84;                    // floats per timestep row in shared memory (80 used; 84 keeps 128-bit stores conflict free)
+constexpr int SCAN_THREADS = 128;          // 8 items per CTA
+constexpr int ITEMS_PER_CTA = SCAN_THREADS / 16;
+
+__device__ __forceinline__ float softplus20(float x) { return x > 20.f ? x : log1pf(__expf(x)); }
+__device__ __forceinline__ float silu(float x) { return x / (1.f + __expf(-x)); }
+__device__ __forceinline__ float sigmoidf(float x) { return 1.f / (1.f + __expf(-x)); }
+
+// ---------------------------------------------------------------------------------------------------- prep
+// roles: 1 = grad (launch dtype), 2 = sharpness (fp32), 6 = packed offset (integer smuggled in the pointer slot)
+template <typename T>
+__global__ void __launch_bounds__(MT_THREADS) sg2_prep_kernel(const __grid_constant__ MTArgs a, const float* __restrict__ tclip,
+                                                              float* __restrict__ g_packed, float* __restrict__ s_packed,
+                                                              uint32_t* __restrict__ keys, uint32_t* __restrict__ vals) {
+    int lo = 0, hi = a.n;
+    const int b = blockIdx.x;
+    while (hi - lo > 1) { const int mid = (lo + hi) >> 1; if (a.blk_start[mid] <= b) lo = mid; else hi = mid; }
+    const int t = lo;
+    const int64_t begin = (int64_t)(b - a.blk_start[t]) * MT_CHUNK;
+    const int64_t n = a.numel[t];
+    const int64_t end = (begin + MT_CHUNK < n) ? begin + MT_CHUNK : n;
+    const int64_t off = (int64_t)reinterpret_cast<intptr_t>(a.ptr[6][t]);
+    const T* g = reinterpret_cast<const T*>(a.ptr[1][t]);
+    const float* sh = reinterpret_cast<const float*>(a.ptr[2][t]);
+    const float clip = tclip[a.t_off + t];
+    for (int64_t i = begin + threadIdx.x; i < end; i += MT_THREADS) {
+        float gv = Cvt<T>::to(g[i]);
+        float sv = sh[i];
+        gv = isfinite(gv) ? gv * clip : 0.f;
+        if (!isfinite(gv)) gv = 0.f;
+        if (!isfinite(sv)) sv = 0.f;
+        g_packed[off + i] = gv;
+        s_packed[off + i] = sv;
+        keys[off + i] = __float_as_uint(fabsf(gv));
+        vals[off + i] = (uint32_t)(off + i);
+    }
+}
+
+// finite-only sum of squares per CTA (per-tensor clip uses the norm of the scrubbed gradient)
+template <typename T>
+__global__ void __launch_bounds__(MT_THREADS) sg2_sqnorm_kernel(const __grid_constant__ MTArgs a, float* __restrict__ partials) {
+    __shared__ float red[32];
+    int lo = 0, hi = a.n;
+    const int b = blockIdx.x;
+    while (hi - lo > 1) { const int mid = (lo + hi) >> 1; if (a.blk_start[mid] <= b) lo = mid; else hi = mid; }
+    const int t = lo;
+    const int64_t begin = (int64_t)(b - a.blk_start[t]) * MT_CHUNK;
+    const int64_t n = a.numel[t];
+    const int64_t end = (begin + MT_CHUNK < n) ? begin + MT_CHUNK : n;
+    const T* g = reinterpret_cast<const T*>(a.ptr[1][t]);
+    float acc = 0.f;
+    for (int64_t i = begin + threadIdx.x; i < end; i += MT_THREADS) {
+        const float gv = Cvt<T>::to(g[i]);
+        if (isfinite(gv)) acc = fmaf(gv, gv, acc);
+    }
+    const float r = block_sum(acc, red);
+    if (threadIdx.x == 0) { float* o = partials + 3 * (int64_t)(a.blk_off + b); o[0] = r; o[1] = 0.f; o[2] = 0.f; }
+}
+
+__global__ void __launch_bounds__(256) sg2_gather_kernel(const uint32_t* __restrict__ vals_sorted, const float* __restrict__ g_packed,
+                                                         const float* __restrict__ s_packed, float2* __restrict__ gs_sorted,
+                                                         int64_t total) {
+    const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
+    if (i < total) {
+        const uint32_t v = vals_sorted[i];
+        gs_sorted[i] = make_float2(g_packed[v], s_packed[v]);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------- scan
+struct Item {          // 32 bytes
+    int64_t off;       // packed offset of the tensor
+    int32_t n;         // tensor length
+    int32_t ub, ue;    // scan-order range [ub, ue)
+    int32_t tensor;    // -1 = padding
+    int32_t td;        // index of the (tensor, direction) record
+    int32_t last;      // 1 = last chunk of its (tensor, direction)
+};
+struct TensorDir {     // 32 bytes
+    float* h;          // persistent [16,16] state of this tensor / direction
+    int32_t item0;     // first item index
+    int32_t nc;        // number of chunks
+    int32_t pad[4];
+};
+
+// Stage A: lane l = timestep (u0 + l).  Computes x,z,dt,B,C for its timestep and writes its shared-memory row.
+template <int DIR>
+__device__ __forceinline__ void stage_a(float* __restrict__ tile, const float2* __restrict__ gs, int64_t off, int n, int u, bool valid,
+                                        int l) {
+    constexpr int W = (DIR == 0) ? P::DIR0 : P::DIR1;
+    float4* row = reinterpret_cast<float4*>(tile + l * ROW);
+    if (!valid) return;
+    const int pos = (DIR == 0) ? u : (n - 1 - u);
+    const float2 v = gs[off + pos];
+    float inp[8];
+#pragma unroll
+    for (int d = 0; d < 8; ++d) inp[d] = fmaf(c_w[P::IN_W + 2 * d], v.x, fmaf(c_w[P::IN_W + 2 * d + 1], v.y, c_w[P::IN_B + d]));
+    float x[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        float acc = 0.f;
+#pragma unroll
+        for (int d = 0; d < 8; ++d) acc = fmaf(c_w[W + P::D_INPROJ + j * 8 + d], inp[d], acc);
+        x[j] = acc;
+    }
+#pragma unroll
+    for (int q = 0; q < 4; ++q) row[q] = make_float4(x[4 * q], x[4 * q + 1], x[4 * q + 2], x[4 * q + 3]);
+    {
+        float z[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            float acc = 0.f;
+#pragma unroll
+            for (int d = 0; d < 8; ++d) acc = fmaf(c_w[W + P::D_INPROJ + (16 + j) * 8 + d], inp[d], acc);
+            z[j] = acc;
+        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) row[4 + q] = make_float4(z[4 * q], z[4 * q + 1], z[4 * q + 2], z[4 * q + 3]);
+    }
+    {
+        float dt[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            float acc = c_w[W + P::D_DTB + j];
+#pragma unroll
+            for (int k = 0; k < 16; ++k) acc = fmaf(c_w[W + P::D_DTW + j * 16 + k], x[k], acc);
+            dt[j] = softplus20(acc);
+        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) row[8 + q] = make_float4(dt[4 * q], dt[4 * q + 1], dt[4 * q + 2], dt[4 * q + 3]);
+    }
+    {
+        float bb[16];
+#pragma unroll
+        for (int s = 0; s < 16; ++s) {
+            float acc = 0.f;
+#pragma unroll
+            for (int k = 0; k < 16; ++k) acc = fmaf(c_w[W + P::D_BW + s * 16 + k], x[k], acc);
+            bb[s] = acc;
+        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) row[12 + q] = make_float4(bb[4 * q], bb[4 * q + 1], bb[4 * q + 2], bb[4 * q + 3]);
+    }
+    {
+        float cc[16];
+#pragma unroll
+        for (int s = 0; s < 16; ++s) {
+            float acc = 0.f;
+#pragma unroll
+            for (int k = 0; k < 16; ++k) acc = fmaf(c_w[W + P::D_CW + s * 16 + k], x[k], acc);
+            cc[s] = acc;
+        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) row[16 + q] = make_float4(cc[4 * q], cc[4 * q + 1], cc[4 * q + 2], cc[4 * q + 3]);
+    }
+}
+
+// per (column, pair) transition: Abar_e, Abar_o, cos, sin from dt
+__device__ __forceinline__ void pair_coeffs(float dt, float ah_e, float ah_o, float f, float& abe, float& abo, float& cs, float& sn) {
+    const float ae = dt * ah_e, ao = dt * ah_o;          // dt*A/2
+    const float de = 1.f - ae + 1e-8f, dd = 1.f - ao + 1e-8f;
+    const float r = __fdividef(1.f, de * dd);
+    abe = (1.f + ae) * dd * r;
+    abo = (1.f + ao) * de * r;
+    __sincosf(dt * f, &sn, &cs);
+}
+
+// PHASE 1: aggregate map of a chunk.  PHASE 3: run the chunk from its carry-in and emit contexts.
+template <int DIR, int PHASE>
+__device__ void scan_body(const Item& it, const TensorDir* __restrict__ tds, const float2* __restrict__ gs,
+                          const uint32_t* __restrict__ vals_sorted, float* __restrict__ agg, const float* __restrict__ carry,
+                          float* __restrict__ ctx, float* __restrict__ tile, int item_idx, int j, unsigned hmask) {
+    constexpr int W = (DIR == 0) ? P::DIR0 : P::DIR1;
+    // column constants of lane j
+    float ah[16], f[8];
+#pragma unroll
+    for (int s = 0; s < 16; ++s) ah[s] = -0.5f * __expf(c_w[W + P::D_ALOG + j * 16 + s]);
+#pragma unroll
+    for (int p = 0; p < 8; ++p) f[p] = c_w[W + P::D_ROPE + j * 8 + p];
+    const float Dj = c_w[W + P::D_D + j];
+    float h[16];          // PHASE 3: state.  PHASE 1: bias part of the aggregate
+    float m[32];          // PHASE 1: 2x2 matrices of the aggregate (a,b,c,d per pair)
+    if (PHASE == 3) {
+        const float* cin = carry + ((int64_t)item_idx * 16 + j) * 16;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) { const float4 t = reinterpret_cast<const float4*>(cin)[q]; h[4 * q] = t.x; h[4 * q + 1] = t.y; h[4 * q + 2] = t.z; h[4 * q + 3] = t.w; }
+    } else {
+#pragma unroll
+        for (int s = 0; s < 16; ++s) h[s] = 0.f;
+#pragma unroll
+        for (int p = 0; p < 8; ++p) { m[4 * p] = 1.f; m[4 * p + 1] = 0.f; m[4 * p + 2] = 0.f; m[4 * p + 3] = 1.f; }
+    }
+    for (int u0 = it.ub; u0 < it.ue; u0 += TILE_T) {
+        const int cnt = (it.ue - u0 < TILE_T) ? (it.ue - u0) : TILE_T;
+        stage_a<DIR>(tile, gs, it.off, it.n, u0 + j, j < cnt, j);
+        __syncwarp(hmask);
+        // Stage B: lane j = column
+        for (int l = 0; l < cnt; ++l) {
+            const float* row = tile + l * ROW;
+            const float x = row[j], dt = row[32 + j];
+            float B[16], C[16];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const float4 t = reinterpret_cast<const float4*>(row + 48)[q];
+                B[4 * q] = t.x; B[4 * q + 1] = t.y; B[4 * q + 2] = t.z; B[4 * q + 3] = t.w;
+            }
+            if (PHASE == 3) {
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const float4 t = reinterpret_cast<const float4*>(row + 64)[q];
+                    C[4 * q] = t.x; C[4 * q + 1] = t.y; C[4 * q + 2] = t.z; C[4 * q + 3] = t.w;
+                }
+            }
+            const float dtx = dt * x;
+            float y = 0.f;
+#pragma unroll
+            for (int p = 0; p < 8; ++p) {
+                float abe, abo, cs, sn;
+                pair_coeffs(dt, ah[2 * p], ah[2 * p + 1], f[p], abe, abo, cs, sn);
+                const float he = h[2 * p], ho = h[2 * p + 1];
+                const float ne = fmaf(abe, he * cs - ho * sn, dtx * B[2 * p]);
+                const float no = fmaf(abo, ho * cs + he * sn, dtx * B[2 * p + 1]);
+                h[2 * p] = ne; h[2 * p + 1] = no;
+                if (PHASE == 3) {
+                    y = fmaf(ne, C[2 * p], fmaf(no, C[2 * p + 1], y));
+                } else {
+                    // M <- M_t * M with M_t = [[abe*cs, -abe*sn], [abo*sn, abo*cs]]
+                    const float a0 = m[4 * p], b0 = m[4 * p + 1], c0 = m[4 * p + 2], d0 = m[4 * p + 3];
+                    m[4 * p]     = abe * (cs * a0 - sn * c0);
+                    m[4 * p + 1] = abe * (cs * b0 - sn * d0);
+                    m[4 * p + 2] = abo * (sn * a0 + cs * c0);
+                    m[4 * p + 3] = abo * (sn * b0 + cs * d0);
+                }
+            }
+            if (PHASE == 3) {
+                const float z = row[16 + j];
+                const float o = fmaf(y, silu(z), Dj * x);
+                const_cast<float*>(row)[j] = o;        // park out_j in the x slot (only lane j reads x_j)
+            }
+        }
+        if (PHASE == 3) {
+            __syncwarp(hmask);
+            // Stage C: lane l = timestep again: ctx = out_proj . out, written at the element's original index
+            if (j < cnt) {
+                const float* row = tile + j * ROW;
+                float o[16];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) { const float4 t = reinterpret_cast<const float4*>(row)[q]; o[4 * q] = t.x; o[4 * q + 1] = t.y; o[4 * q + 2] = t.z; o[4 * q + 3] = t.w; }
+                float c8[8];
+#pragma unroll
+                for (int d = 0; d < 8; ++d) {
+                    float acc = 0.f;
+#pragma unroll
+                    for (int k = 0; k < 16; ++k) acc = fmaf(c_w[W + P::D_OUT + d * 16 + k], o[k], acc);
+                    c8[d] = acc;
+                }
+                const int u = u0 + j;
+                const int pos = (DIR == 0) ? u : (it.n - 1 - u);
+                const uint32_t orig = vals_sorted[it.off + pos];
+                float4* dst = reinterpret_cast<float4*>(ctx + (int64_t)orig * 16 + DIR * 8);
+                dst[0] = make_float4(c8[0], c8[1], c8[2], c8[3]);
+                dst[1] = make_float4(c8[4], c8[5], c8[6], c8[7]);
+            }
+        }
+        __syncwarp(hmask);
+    }
+    if (PHASE == 3) {
+        if (it.last) {
+            float* dst = tds[it.td].h + j * 16;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) reinterpret_cast<float4*>(dst)[q] = make_float4(h[4 * q], h[4 * q + 1], h[4 * q + 2], h[4 * q + 3]);
+        }
+    } else {
+        float* dst = agg + ((int64_t)item_idx * 16 + j) * 48;      // [pair][a b c d e o]
+#pragma unroll
+        for (int p = 0; p < 8; ++p) {
+            dst[6 * p] = m[4 * p]; dst[6 * p + 1] = m[4 * p + 1]; dst[6 * p + 2] = m[4 * p + 2]; dst[6 * p + 3] = m[4 * p + 3];
+            dst[6 * p + 4] = h[2 * p]; dst[6 * p + 5] = h[2 * p + 1];
+        }
+    }
+}
+
+// items [0, n_items0) are direction 0, [n_items0_padded, ...) direction 1; n_items0_padded is a multiple of 8,
+// so one CTA (8 items) never mixes directions.
+template <int PHASE>
+__global__ void __launch_bounds__(SCAN_THREADS, 3) sg2_scan_kernel(const Item* __restrict__ items, int n_items, int dir1_start,
+                                                                   const TensorDir* __restrict__ tds, const float2* __restrict__ gs,
+                                                                   const uint32_t* __restrict__ vals_sorted, float* __restrict__ agg,
+                                                                   const float* __restrict__ carry, float* __restrict__ ctx) {
+    __shared__ __align__(16) float tiles[ITEMS_PER_CTA][TILE_T * ROW];
+    const int slot = threadIdx.x >> 4, j = threadIdx.x & 15;
+    const int item_idx = blockIdx.x * ITEMS_PER_CTA + slot;
+    const unsigned hmask = 0xffffu << (16 * ((threadIdx.x >> 4) & 1));
+    if (item_idx >= n_items) return;
+    const Item it = items[item_idx];
+    if (it.tensor < 0) return;
+    if (PHASE == 1 && it.last) return;            // nobody consumes the aggregate of a last chunk
+    if (item_idx < dir1_start)
+        scan_body<0, PHASE>(it, tds, gs, vals_sorted, agg, carry, ctx, tiles[slot], item_idx, j, hmask);
+    else
+        scan_body<1, PHASE>(it, tds, gs, vals_sorted, agg, carry, ctx, tiles[slot], item_idx, j, hmask);
+}
+
+// Phase 2: carry-in of every chunk.  One CTA of 128 threads (column j, pair p) per (tensor, direction).
+__global__ void __launch_bounds__(128) sg2_carry_kernel(const TensorDir* __restrict__ tds, const float* __restrict__ agg,
+                                                        float* __restrict__ carry) {
+    const TensorDir td = tds[blockIdx.x];
+    const int j = threadIdx.x >> 3, p = threadIdx.x & 7;
+    float he = td.h[j * 16 + 2 * p], ho = td.h[j * 16 + 2 * p + 1];
+    for (int c = 0; c < td.nc; ++c) {
+        const int64_t idx = (int64_t)(td.item0 + c);
+        float* co = carry + (idx * 16 + j) * 16 + 2 * p;
+        co[0] = he; co[1] = ho;
+        if (c + 1 < td.nc) {
+            const float* a = agg + (idx * 16 + j) * 48 + 6 * p;
+            const float ne = fmaf(a[0], he, fmaf(a[1], ho, a[4]));
+            const float no = fmaf(a[2], he, fmaf(a[3], ho, a[5]));
+            he = ne; ho = no;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------- element step
+struct ElemParams {
+    float beta2, lr, wd_eff, eps, rescale;
+    const float* g_packed; const float* s_packed; const float* ctx;
+    int* expert_counts;                // [144] or nullptr
+    // optional replication of the updated parameter (bf16) into peer buffers: filled by the distributed step
+    int n_peers; void* peer_param[8]; int64_t peer_elem_off;
+};
+
+// roles: 0 = param (launch dtype), 1 = m, 2 = v, 3 = mu, 4 = gru [n,4], 6 = packed offset.  ts = alpha, beta1, bc1, bc2; lamb_eff in ts? no:
+// ts[0]=alpha ts[1]=beta1 ts[2]=bc1 ts[3]=bc2, lamb_eff is global.
+template <typename T>
+__global__ void __launch_bounds__(MT_THREADS) sg2_elem_kernel(const __grid_constant__ MTArgs a, const __grid_constant__ ElemParams prm,
+                                                              float lamb_eff) {
+    __shared__ float sW1[SG2_NE * SG2_EH], sB1[SG2_NE * SG2_EH], sW2[SG2_NE * SG2_EH], sB2[SG2_NE];
+    __shared__ int scount[SG2_NE];
+    for (int i = threadIdx.x; i < SG2_NE * SG2_EH; i += MT_THREADS) { sW1[i] = c_w[P::EW1 + i]; sB1[i] = c_w[P::EB1 + i]; sW2[i] = c_w[P::EW2 + i]; }
+    for (int i = threadIdx.x; i < SG2_NE; i += MT_THREADS) { sB2[i] = c_w[P::EB2 + i]; scount[i] = 0; }
+    __syncthreads();
+    int lo = 0, hi = a.n;
+    const int b = blockIdx.x;
+    while (hi - lo > 1) { const int mid = (lo + hi) >> 1; if (a.blk_start[mid] <= b) lo = mid; else hi = mid; }
+    const int t = lo;
+    const int64_t begin = (int64_t)(b - a.blk_start[t]) * MT_CHUNK;
+    const int64_t n = a.numel[t];
+    const int64_t end = (begin + MT_CHUNK < n) ? begin + MT_CHUNK : n;
+    const int64_t off = (int64_t)reinterpret_cast<intptr_t>(a.ptr[6][t]);
+    T* param = reinterpret_cast<T*>(a.ptr[0][t]);
+    float* M = reinterpret_cast<float*>(a.ptr[1][t]);
+    float* V = reinterpret_cast<float*>(a.ptr[2][t]);
+    float* MU = reinterpret_cast<float*>(a.ptr[3][t]);
+    float4* GRU = reinterpret_cast<float4*>(a.ptr[4][t]);
+    const float alpha = a.ts[t][0], beta1 = a.ts[t][1], bc1 = a.ts[t][2], bc2 = a.ts[t][3];
+
+    for (int64_t i = begin + threadIdx.x; i < end; i += MT_THREADS) {
+        const float g = prm.g_packed[off + i], s = prm.s_packed[off + i];
+        float cx[16];                                  // fwd ctx (8) then bwd ctx (8)
+        {
+            const float4* src = reinterpret_cast<const float4*>(prm.ctx + (off + i) * 16);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) { const float4 v = src[q]; cx[4 * q] = v.x; cx[4 * q + 1] = v.y; cx[4 * q + 2] = v.z; cx[4 * q + 3] = v.w; }
+        }
+        const float4 hv = GRU[i];
+        const float hold[4] = {hv.x, hv.y, hv.z, hv.w};
+        // GRU: input order [g, s, fwd(8), bwd(8), h(4)]
+        float zg[4], rg[4], hn[4];
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            float vz = c_w[P::GRU_BZ + r], vr = c_w[P::GRU_BR + r];
+            const int wz = P::GRU_WZ + r * 22, wr = P::GRU_WR + r * 22;
+            vz = fmaf(c_w[wz], g, fmaf(c_w[wz + 1], s, vz));
+            vr = fmaf(c_w[wr], g, fmaf(c_w[wr + 1], s, vr));
+#pragma unroll
+            for (int k = 0; k < 16; ++k) { vz = fmaf(c_w[wz + 2 + k], cx[k], vz); vr = fmaf(c_w[wr + 2 + k], cx[k], vr); }
+#pragma unroll
+            for (int k = 0; k < 4; ++k) { vz = fmaf(c_w[wz + 18 + k], hold[k], vz); vr = fmaf(c_w[wr + 18 + k], hold[k], vr); }
+            zg[r] = sigmoidf(vz); rg[r] = sigmoidf(vr);
+        }
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            const int wh = P::GRU_WH + r * 22;
+            float vh = fmaf(c_w[wh], g, fmaf(c_w[wh + 1], s, c_w[P::GRU_BH + r]));
+#pragma unroll
+            for (int k = 0; k < 16; ++k) vh = fmaf(c_w[wh + 2 + k], cx[k], vh);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) vh = fmaf(c_w[wh + 18 + k], rg[k] * hold[k], vh);
+            hn[r] = (1.f - zg[r]) * hold[r] + zg[r] * tanhf(vh);
+        }
+        GRU[i] = make_float4(hn[0], hn[1], hn[2], hn[3]);
+        // PEER: input order [h_new(4), fwd(8), bwd(8), g, s]
+        float total = 0.f;
+#pragma unroll
+        for (int hd = 0; hd < SG2_HEADS; ++hd) {
+            float q[8];
+#pragma unroll
+            for (int d = 0; d < 8; ++d) {
+                const int w = P::PQ + (hd * 8 + d) * 22;
+                float acc = 0.f;
+#pragma unroll
+                for (int k = 0; k < 4; ++k) acc = fmaf(c_w[w + k], hn[k], acc);
+#pragma unroll
+                for (int k = 0; k < 16; ++k) acc = fmaf(c_w[w + 4 + k], cx[k], acc);
+                acc = fmaf(c_w[w + 20], g, fmaf(c_w[w + 21], s, acc));
+                q[d] = acc;
+            }
+            int ba = 0, bb = 0;
+            float sa = -1e30f, sb = -1e30f;
+#pragma unroll
+            for (int k = 0; k < SG2_PK; ++k) {
+                const int wa = P::KA + (hd * SG2_PK + k) * 4, wb = P::KB + (hd * SG2_PK + k) * 4;
+                const float da = fmaf(q[0], c_w[wa], fmaf(q[1], c_w[wa + 1], fmaf(q[2], c_w[wa + 2], q[3] * c_w[wa + 3])));
+                const float db = fmaf(q[4], c_w[wb], fmaf(q[5], c_w[wb + 1], fmaf(q[6], c_w[wb + 2], q[7] * c_w[wb + 3])));
+                if (da > sa) { sa = da; ba = k; }
+                if (db > sb) { sb = db; bb = k; }
+            }
+            const int e = ba * SG2_PK + bb;
+            if (prm.expert_counts) atomicAdd(&scount[e], 1);
+            float ho = sB2[e];
+#pragma unroll
+            for (int k = 0; k < SG2_EH; ++k) ho = fmaf(sW2[e * SG2_EH + k], fmaxf(fmaf(sW1[e * SG2_EH + k], g, sB1[e * SG2_EH + k]), 0.f), ho);
+            total += ho;
+        }
+        const float smart = g + prm.rescale * total * (1.f / SG2_HEADS);
+        float mu = MU[i];
+        mu = alpha * mu + (1.f - alpha) * g;
+        MU[i] = mu;
+        const float fg = smart + lamb_eff * mu;
+        float mm = M[i], vv = V[i];
+        const float pnew = adam_update(Cvt<T>::to(param[i]), fg, mm, vv, prm.lr, beta1, prm.beta2, prm.eps, prm.wd_eff, bc1, bc2);
+        M[i] = mm; V[i] = vv;
+        param[i] = Cvt<T>::from(pnew);
+    }
+    if (prm.expert_counts) {
+        __syncthreads();
+        for (int i = threadIdx.x; i < SG2_NE; i += MT_THREADS)
+            if (scount[i]) atomicAdd(&prm.expert_counts[i], scount[i]);      // integer atomics: order independent
+    }
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------------------------------------------- host API
+void sg2_upload_weights(const float* packed_dev, cudaStream_t s) {
+    cudaMemcpyToSymbolAsync(c_w, packed_dev, sizeof(float) * SG2Pack::TOTAL, 0, cudaMemcpyDeviceToDevice, s);
+}
+
+void sg2_sqnorm(int dtype, const MTArgs& a, float* partials, cudaStream_t s) {
+    const int blocks = a.blk_start[a.n];
+    if (blocks <= 0) return;
+    switch (dtype) {
+        case F32:  sg2_sqnorm_kernel<float><<<blocks, MT_THREADS, 0, s>>>(a, partials); break;
+        case BF16: sg2_sqnorm_kernel<__nv_bfloat16><<<blocks, MT_THREADS, 0, s>>>(a, partials); break;
+        default:   sg2_sqnorm_kernel<__half><<<blocks, MT_THREADS, 0, s>>>(a, partials); break;
+    }
+}
+
+void sg2_prep(int dtype, const MTArgs& a, const float* tclip, float* g_packed, float* s_packed, uint32_t* keys, uint32_t* vals,
+              cudaStream_t s) {
+    const int blocks = a.blk_start[a.n];
+    if (blocks <= 0) return;
+    switch (dtype) {
+        case F32:  sg2_prep_kernel<float><<<blocks, MT_THREADS, 0, s>>>(a, tclip, g_packed, s_packed, keys, vals); break;
+        case BF16: sg2_prep_kernel<__nv_bfloat16><<<blocks, MT_THREADS, 0, s>>>(a, tclip, g_packed, s_packed, keys, vals); break;
+        default:   sg2_prep_kernel<__half><<<blocks, MT_THREADS, 0, s>>>(a, tclip, g_packed, s_packed, keys, vals); break;
+    }
+}
+
+void sg2_gather(const uint32_t* vals_sorted, const float* g_packed, const float* s_packed, float* gs_sorted, int64_t total,
+                cudaStream_t s) {
+    if (total <= 0) return;
+    sg2_gather_kernel<<<(unsigned)((total + 255) / 256), 256, 0, s>>>(vals_sorted, g_packed, s_packed,
+                                                                       reinterpret_cast<float2*>(gs_sorted), total);
+}
+
+void sg2_scan(const void* items_dev, int n_items, int dir1_start, const void* tds_dev, int n_td, bool any_multi,
+              const float* gs_sorted, const uint32_t* vals_sorted, float* agg, float* carry, float* ctx, cudaStream_t s) {
+    if (n_items <= 0) return;
+    const int blocks = (n_items + ITEMS_PER_CTA - 1) / ITEMS_PER_CTA;
+    const Item* items = reinterpret_cast<const Item*>(items_dev);
+    const TensorDir* tds = reinterpret_cast<const TensorDir*>(tds_dev);
+    const float2* gs = reinterpret_cast<const float2*>(gs_sorted);
+    if (any_multi) sg2_scan_kernel<1><<<blocks, SCAN_THREADS, 0, s>>>(items, n_items, dir1_start, tds, gs, vals_sorted, agg, carry, ctx);
+    sg2_carry_kernel<<<n_td, 128, 0, s>>>(tds, agg, carry);
+    sg2_scan_kernel<3><<<blocks, SCAN_THREADS, 0, s>>>(items, n_items, dir1_start, tds, gs, vals_sorted, agg, carry, ctx);
+}
+
+void sg2_elem(int dtype, const MTArgs& a, float beta2, float lr, float wd_eff, float eps, float rescale, float lamb_eff,
+              const float* g_packed, const float* s_packed, const float* ctx, int* expert_counts, cudaStream_t s) {
+    const int blocks = a.blk_start[a.n];
+    if (blocks <= 0) return;
+    ElemParams p{};
+    p.beta2 = beta2; p.lr = lr; p.wd_eff = wd_eff; p.eps = eps; p.rescale = rescale;
+    p.g_packed = g_packed; p.s_packed = s_packed; p.ctx = ctx; p.expert_counts = expert_counts; p.n_peers = 0;
+    switch (dtype) {
+        case F32:  sg2_elem_kernel<float><<<blocks, MT_THREADS, 0, s>>>(a, p, lamb_eff); break;
+        case BF16: sg2_elem_kernel<__nv_bfloat16><<<blocks, MT_THREADS, 0, s>>>(a, p, lamb_eff); break;
+        default:   sg2_elem_kernel<__half><<<blocks, MT_THREADS, 0, s>>>(a, p, lamb_eff); break;
+    }
+}
+
+size_t sg2_item_bytes() { return sizeof(Item); }
+size_t sg2_td_bytes() { return sizeof(TensorDir); }
+
+}  // namespace sg

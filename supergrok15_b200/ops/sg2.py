@@ -1,0 +1,275 @@
+"""SuperGrok v2 step and bilevel orchestration.
+
+CUDA: all tensors of the optimizer go through ONE batched pipeline of sm_100a kernels
+(``csrc/sg2_kernels.cu`` + ``csrc/sg2_sort.cu``): per-tensor clip -> packed keys -> segmented radix
+sort -> gather -> 3-phase multi-CTA bidirectional scan -> fused element step.  A *plan* (offsets,
+scan work items, workspace) is built once per set of tensors and reused; a step allocates nothing.
+CPU: the PyTorch oracle (meta-net ``forward`` per tensor + ``oracle.sg2_adam_``).
+
+The packed weight vector layout is defined once, in ``csrc/sg_native.h`` (``SG2Pack``), and read
+back from the extension so Python and CUDA cannot drift apart.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from .. import _build
+from . import oracle
+
+# target number of concurrently resident scan items: 148 SMs x 3 CTAs x 8 items, two waves
+_TARGET_ITEMS = 148 * 3 * 8 * 2
+_MIN_CHUNK = 512
+
+_FALLBACK_LAYOUT = None
+
+
+def layout() -> Dict[str, int]:
+    """Offsets of ``SG2Pack`` (from the extension; a pure-Python copy is used when it is not built)."""
+    global _FALLBACK_LAYOUT
+    C = _build.load()
+    if C is not None:
+        return dict(C.sg2_layout())
+    if _FALLBACK_LAYOUT is None:
+        L, o = {}, 0
+        def put(name, size):
+            nonlocal o
+            L[name] = o
+            o += size
+        put("IN_W", 16); put("IN_B", 8); put("DIR0", 0)
+        d = {"D_INPROJ": 256, "D_DTW": 256, "D_DTB": 16, "D_BW": 256, "D_CW": 256, "D_ALOG": 256, "D_D": 16,
+             "D_ROPE": 128, "D_OUT": 128}
+        oo = 0
+        for k, v in d.items():
+            L[k] = oo
+            oo += v
+        L["DIR_SIZE"] = oo
+        L["DIR1"] = L["DIR0"] + oo
+        o = L["DIR1"] + oo
+        for name, size in (("GRU_WZ", 88), ("GRU_WR", 88), ("GRU_WH", 88), ("GRU_BZ", 4), ("GRU_BR", 4), ("GRU_BH", 4),
+                           ("PQ", 704), ("KA", 192), ("KB", 192), ("EW1", 2304), ("EB1", 2304), ("EW2", 2304),
+                           ("EB2", 144)):
+            put(name, size)
+        L["TOTAL"] = o
+        _FALLBACK_LAYOUT = L
+    return _FALLBACK_LAYOUT
+
+
+def supports_native(meta_net) -> bool:
+    """The fused kernels are compiled for the default geometry (expert_hidden may be smaller than 16)."""
+    return (meta_net.d_model == 8 and meta_net.d_state == 16 and meta_net.mamba_fwd.d_inner == 16 and
+            meta_net.gru_hidden == 4 and meta_net.num_peer_heads == 4 and meta_net.num_experts == 144 and
+            meta_net.expert_hidden <= 16)
+
+
+@torch.no_grad()
+def pack_metanet(meta_net) -> torch.Tensor:
+    """Meta-net weights as one fp32 vector in ``SG2Pack`` order (experts zero-padded to 16 hidden units)."""
+    if not supports_native(meta_net):
+        raise ValueError("the fused v2 kernels support d_model 8, d_state 16, expand 2, gru 4, 4 heads, 144 experts, "
+                         "expert_hidden <= 16")
+    L = layout()
+    dev = meta_net.input_proj.weight.device
+    out = torch.zeros(L["TOTAL"], dtype=torch.float32, device=dev)
+
+    def put(off, t):
+        t = t.detach().float().reshape(-1)
+        out[off:off + t.numel()] = t
+
+    put(L["IN_W"], meta_net.input_proj.weight)
+    put(L["IN_B"], meta_net.input_proj.bias)
+    for base, blk in ((L["DIR0"], meta_net.mamba_fwd), (L["DIR1"], meta_net.mamba_bwd)):
+        put(base + L["D_INPROJ"], blk.in_proj.weight)
+        put(base + L["D_DTW"], blk.dt_proj.weight)
+        put(base + L["D_DTB"], blk.dt_proj.bias)
+        put(base + L["D_BW"], blk.B_proj.weight)
+        put(base + L["D_CW"], blk.C_proj.weight)
+        put(base + L["D_ALOG"], blk.A_log)
+        put(base + L["D_D"], blk.D)
+        put(base + L["D_ROPE"], blk.rope_freq)
+        put(base + L["D_OUT"], blk.out_proj.weight)
+    put(L["GRU_WZ"], meta_net.gru.W_z.weight); put(L["GRU_WR"], meta_net.gru.W_r.weight); put(L["GRU_WH"], meta_net.gru.W_h.weight)
+    put(L["GRU_BZ"], meta_net.gru.W_z.bias); put(L["GRU_BR"], meta_net.gru.W_r.bias); put(L["GRU_BH"], meta_net.gru.W_h.bias)
+    put(L["PQ"], torch.stack([q.weight for q in meta_net.peer_queries]))
+    put(L["KA"], torch.stack(list(meta_net.product_keys_A)))
+    put(L["KB"], torch.stack(list(meta_net.product_keys_B)))
+    eh = meta_net.expert_hidden
+    pad = lambda t: torch.nn.functional.pad(t.detach().float().reshape(144, eh), (0, 16 - eh))  # noqa: E731
+    put(L["EW1"], pad(meta_net.expert_W1)); put(L["EB1"], pad(meta_net.expert_b1)); put(L["EW2"], pad(meta_net.expert_W2))
+    put(L["EB2"], meta_net.expert_b2)
+    return out
+
+
+# --------------------------------------------------------------------------- plan
+class Plan:
+    """Static description of a v2 step over a fixed list of tensors (sizes, device tables, workspace)."""
+
+    ITEM = np.dtype([("off", "<i8"), ("n", "<i4"), ("ub", "<i4"), ("ue", "<i4"), ("tensor", "<i4"), ("td", "<i4"),
+                     ("last", "<i4")])
+    TD = np.dtype([("h", "<u8"), ("item0", "<i4"), ("nc", "<i4"), ("pad", "<i4", (4,))])
+
+    def __init__(self, numels: Sequence[int], h_fwd: List[torch.Tensor], h_bwd: List[torch.Tensor], device,
+                 chunk_len: int = 0):
+        C = _build.require()
+        assert self.ITEM.itemsize == C.sg2_layout()["item_bytes"] and self.TD.itemsize == C.sg2_layout()["td_bytes"]
+        self.numels = [int(n) for n in numels]
+        self.n = len(self.numels)
+        self.offsets = [0]
+        for n in self.numels:
+            self.offsets.append(self.offsets[-1] + n)
+        self.total = self.offsets[-1]
+        if max(self.numels) >= 2 ** 31 or self.total >= 2 ** 32:
+            raise ValueError("a v2 step handles < 2^31 elements per tensor and < 2^32 in total per call")
+        if chunk_len <= 0:
+            chunk_len = max(_MIN_CHUNK, -(-2 * self.total // _TARGET_ITEMS))
+        chunk_len = -(-chunk_len // 16) * 16
+        self.chunk_len = chunk_len
+        items, tds = [], []
+        for d, hs in ((0, h_fwd), (1, h_bwd)):
+            if d == 1:
+                while len(items) % 8:
+                    items.append((0, 0, 0, 0, -1, 0, 0))
+                self.dir1_start = len(items)
+            for t, n in enumerate(self.numels):
+                nc = max(1, -(-n // chunk_len))
+                tds.append((hs[t].data_ptr(), len(items), nc, (0, 0, 0, 0)))
+                for c in range(nc):
+                    items.append((self.offsets[t], n, c * chunk_len, min(n, (c + 1) * chunk_len), t, len(tds) - 1,
+                                  1 if c == nc - 1 else 0))
+        self.n_items = len(items)
+        self.n_td = len(tds)
+        self.any_multi = any(td[2] > 1 for td in tds)
+        self._keep = (h_fwd, h_bwd)
+        self.items = torch.from_numpy(np.array(items, dtype=self.ITEM).view(np.uint8).copy()).to(device)
+        self.tds = torch.from_numpy(np.array(tds, dtype=self.TD).view(np.uint8).copy()).to(device)
+        self.seg_off = torch.tensor(self.offsets, dtype=torch.int64, device=device)
+        tot = max(self.total, 1)
+        nb_sort = C.sg2_sort_blocks(tot)
+        nb_mt = C.mt_num_blocks(self.numels)
+        f32 = dict(dtype=torch.float32, device=device)
+        i32 = dict(dtype=torch.int32, device=device)
+        self.ws = {
+            "partials": torch.empty(3 * max(nb_mt, 1), **f32), "tnorm": torch.empty(3 * self.n, **f32),
+            "tclip": torch.empty(self.n, **f32), "g": torch.empty(tot, **f32), "s": torch.empty(tot, **f32),
+            "keys0": torch.empty(tot, **i32), "keys1": torch.empty(tot, **i32), "vals0": torch.empty(tot, **i32),
+            "vals1": torch.empty(tot, **i32), "hist": torch.empty(256 * nb_sort, **i32), "tot": torch.empty(256, **i32),
+            "gs": torch.empty(2 * tot, **f32), "ctx": torch.empty(16 * tot, **f32),
+            "agg": torch.empty(max(self.n_items, 1) * 16 * 48, **f32),
+            "carry": torch.empty(max(self.n_items, 1) * 16 * 16, **f32),
+        }
+
+    def workspace_bytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in self.ws.values())
+
+
+def _plan_for(opt, idx: List[int]) -> Plan:
+    key = (tuple(idx), tuple(opt._flat_mamba_fwd_states[i].data_ptr() for i in idx))
+    plan = getattr(opt, "_native_plan", None)
+    if plan is None or plan[0] != key:
+        dev = opt._flat_params[idx[0]].device
+        p = Plan([opt._flat_params[i].numel() for i in idx], [opt._flat_mamba_fwd_states[i] for i in idx],
+                 [opt._flat_mamba_bwd_states[i] for i in idx], dev, getattr(opt, "scan_chunk_len", 0))
+        opt._native_plan = plan = (key, p)
+    return plan[1]
+
+
+def _packed_weights(opt, dev) -> Tuple[torch.Tensor, bool]:
+    if opt._weights_dirty or getattr(opt, "_packed_w", None) is None or opt._packed_w.device != dev:
+        opt._packed_w = pack_metanet(opt.meta_net).to(dev)
+        opt._weights_dirty = False
+        return opt._packed_w, True
+    return opt._packed_w, False
+
+
+# the constant-memory copy of the weights is per process: remember whose weights it holds
+_resident = {"owner": None}
+
+
+@torch.no_grad()
+def step(opt, idx: List[int], per: List[Tuple[float, float, float, float, float]], *, beta2, lr, wd_eff, eps, clip):
+    """One v2 update of tensors ``idx`` of ``opt``; ``per[k] = (alpha, lamb_eff, beta1, bc1, bc2)``."""
+    params = [opt._flat_params[i] for i in idx]
+    grads = [p.grad for p in params]
+    if not params[0].is_cuda:
+        return _step_cpu(opt, idx, per, beta2=beta2, lr=lr, wd_eff=wd_eff, eps=eps, clip=clip)
+    C = _build.require()
+    dev = params[0].device
+    plan = _plan_for(opt, idx)
+    w, fresh = _packed_weights(opt, dev)
+    if fresh or _resident["owner"] is not opt:
+        C.sg2_upload_weights(w)
+        _resident["owner"] = opt
+    sharps = [opt._flat_sharpness[i] for i in idx]
+    offs = plan.offsets[:-1]
+    buf = C.sg2_prepare(grads, sharps, offs, plan.total, plan.seg_off, float(clip), plan.ws)
+    C.sg2_scan(plan.items, plan.n_items, plan.dir1_start, plan.tds, plan.n_td, plan.any_multi, buf, plan.ws)
+    ts = [[a, b1, bc1, bc2] for (a, _l, b1, bc1, bc2) in per]
+    counts = opt.meta_net.expert_counts if opt.meta_net.training else None
+    C.sg2_elem(params, [opt._flat_exp_avgs[i] for i in idx], [opt._flat_exp_avg_sqs[i] for i in idx],
+               [opt._flat_mus[i] for i in idx], [opt._flat_gru_states[i] for i in idx], ts, offs, beta2, lr, wd_eff,
+               eps, float(opt.meta_net.rescale), float(per[0][1]), counts, plan.ws)
+
+
+def clip_scrub(g: torch.Tensor, clip: float) -> torch.Tensor:
+    """Per-tensor preprocessing of the v2 step: non-finite entries -> 0, then clip to ``clip`` by the 2-norm."""
+    gf = g.detach().reshape(-1).float()
+    gf = torch.where(torch.isfinite(gf), gf, torch.zeros_like(gf))
+    n = gf.norm()
+    return gf * torch.where(n > clip, clip / (n + 1e-12), torch.ones_like(n))
+
+
+@torch.no_grad()
+def _step_cpu(opt, idx, per, *, beta2, lr, wd_eff, eps, clip):
+    mn = opt.meta_net
+    for k, i in enumerate(idx):
+        p = opt._flat_params[i]
+        alpha, lamb_eff, b1, bc1, bc2 = per[k]
+        g = clip_scrub(p.grad, clip)
+        s = opt._flat_sharpness[i].reshape(-1).float()
+        s = torch.where(torch.isfinite(s), s, torch.zeros_like(s))
+        smart, gru, hf, hb = mn(g, s, opt._flat_gru_states[i], opt._flat_mamba_fwd_states[i],
+                                opt._flat_mamba_bwd_states[i])
+        opt._flat_gru_states[i].copy_(gru)
+        opt._flat_mamba_fwd_states[i].copy_(hf)
+        opt._flat_mamba_bwd_states[i].copy_(hb)
+        oracle.sg2_adam_(p, smart.reshape(-1).float(), g, opt._flat_mus[i], opt._flat_exp_avgs[i],
+                         opt._flat_exp_avg_sqs[i], alpha, lamb_eff, b1, beta2, lr, wd_eff, eps, bc1, bc2)
+
+
+# --------------------------------------------------------------------------- bilevel
+def bilevel_backward(opt, named, train_grads: Dict[str, torch.Tensor], val_grads: Dict[str, torch.Tensor],
+                     checkpoint_interval: int = 1) -> int:
+    """Accumulate d(meta_loss)/d(meta-net weights) into ``.grad`` of the meta-net parameters.
+
+    meta_loss = -sum_tensors <smart_grad(train_grad, sharpness), vg/||vg||>; gradients do not flow into the
+    inputs, the sort permutation, the previous GRU state or the initial scan state
+    (reference supergrok2.py:815-1019).  Returns the number of tensors that contributed.
+    ``checkpoint_interval`` > 1 recomputes the per-tensor forward during backward (activation checkpointing)
+    instead of keeping every tensor's graph alive at once.
+    """
+    mn = opt.meta_net
+    used = 0
+    for name, p in named:
+        if name not in train_grads or name not in val_grads:
+            continue
+        i = opt._param_to_idx.get(id(p))
+        if i is None:
+            continue
+        vg = val_grads[name].detach().reshape(-1).float()
+        if not bool(torch.isfinite(vg).all()):
+            continue
+        vn = vg.norm()
+        vu = vg / vn if float(vn) > 1e-12 else vg
+        g = clip_scrub(train_grads[name], opt.gradient_clipping)
+        s = opt._flat_sharpness[i].reshape(-1).float()
+        with torch.enable_grad():
+            def fwd(g=g, s=s, i=i):
+                return mn.forward_for_bilevel(g, s, opt._flat_gru_states[i], opt._flat_mamba_fwd_states[i],
+                                              opt._flat_mamba_bwd_states[i])[0]
+            smart = fwd()
+            loss = -(smart.reshape(-1) * vu).sum()
+            loss.backward()           # per tensor: the graph of one tensor is alive at a time
+        used += 1
+    return used

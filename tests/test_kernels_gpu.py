@@ -1,0 +1,217 @@
+"""GPU tests: every sm_100a kernel against the plain-PyTorch fp32 oracle of the same op."""
+import copy
+
+import pytest
+import torch
+import torch.nn.functional as F
+
+from supergrok15_b200 import _build
+from supergrok15_b200 import optim as O
+from supergrok15_b200.ops import elementwise as ew
+from supergrok15_b200.ops import sg2 as sg2_ops
+
+from helpers import EDGE_SHAPES, make_params, set_grads, tol
+
+pytestmark = pytest.mark.gpu
+
+
+def test_extension_is_loaded():
+    assert _build.native_available(), _build.load_error()
+
+
+def _twins(shapes, dtype, seed=0):
+    cpu = make_params(shapes, dtype, "cpu", seed)
+    gpu = [torch.nn.Parameter(p.detach().clone().cuda()) for p in cpu]
+    for p, q in zip(cpu, gpu):
+        q.grad = p.grad.clone().cuda()
+    return cpu, gpu
+
+
+def _sync_grads(cpu, gpu, seed):
+    set_grads(cpu, seed)
+    for p, q in zip(cpu, gpu):
+        q.grad = p.grad.clone().cuda()
+
+
+def _compare_state(oc, og, cpu, gpu, dtype, skip=()):
+    rt, at = tol(dtype)
+    for p, q in zip(cpu, gpu):
+        assert torch.allclose(p.float(), q.float().cpu(), rtol=rt, atol=at), (p.float() - q.float().cpu()).abs().max()
+        sc, sg_ = oc.state.get(p, {}), og.state.get(q, {})
+        for k, v in sc.items():
+            if torch.is_tensor(v) and k not in skip:
+                assert torch.allclose(v.float(), sg_[k].float().cpu(), rtol=max(rt, 1e-4), atol=max(at, 1e-7)), k
+
+
+SIMPLE = {
+    "adamw": lambda ps: O.AdamW(ps, lr=1e-2, weight_decay=0.1),
+    "lion": lambda ps: O.Lion(ps, lr=1e-3),
+    "grokfast": lambda ps: O.Grokfast(ps),
+    "grokadamw": lambda ps: O.GrokAdamW(ps, grad_clip=0.05),
+    "prodigy": lambda ps: O.Prodigy(ps, lr=1e-3),
+    "neuralgrok": lambda ps: O.NeuralGrok(ps, grad_clip=0.05),
+    "supergrok15": lambda ps: O.SuperGrok15(ps, gradient_clipping=0.05, warmup_steps=0, warmup_ramp=1),
+    "supergrok11": lambda ps: O.SuperGrok11(ps, gradient_clipping=0.05, warmup_steps=0, warmup_ramp=1),
+}
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("name", list(SIMPLE))
+def test_elementwise_optimizer_matches_oracle(name, dtype):
+    if name == "prodigy" and dtype != torch.float32:
+        pytest.skip("the reference formula overflows half precision on step 2")
+    cpu, gpu = _twins(EDGE_SHAPES, dtype, seed=1)
+    torch.manual_seed(0)
+    oc = SIMPLE[name](cpu)
+    torch.manual_seed(0)
+    og = SIMPLE[name](gpu)
+    if name.startswith("supergrok1"):
+        with torch.no_grad():
+            oc.meta_net.rescale.fill_(0.3); og.meta_net.rescale.fill_(0.3)
+            for s in oc._flat_params:
+                pass
+        oc._ensure_state(); og._ensure_state()
+        for a, b in zip(oc._flat_sharpness, og._flat_sharpness):
+            a.uniform_(0, 1e-2); b.copy_(a)
+    steps = 2 if name == "prodigy" else 3
+    for s in range(steps):
+        kw = {"train_acc": 0.9} if name.startswith("supergrok") else {}
+        oc.step(**kw); og.step(**kw)
+        _sync_grads(cpu, gpu, 10 + s)
+    _compare_state(oc, og, cpu, gpu, dtype)
+    if name == "prodigy":
+        assert abs(oc.d_lr - og.d_lr) <= 1e-4 * abs(oc.d_lr)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_looksam_ops_match_oracle(dtype):
+    cpu, gpu = _twins(EDGE_SHAPES[:10], dtype, seed=2)
+    rt, at = tol(dtype)
+    bc = [torch.zeros(p.shape) for p in cpu]
+    bg = [torch.zeros(p.shape, device="cuda") for p in gpu]
+    ew.perturb(cpu, [p.grad for p in cpu], bc, 0.05)
+    ew.perturb(gpu, [p.grad for p in gpu], bg, 0.05)
+    for p, q in zip(cpu, gpu):
+        assert torch.allclose(p.float(), q.float().cpu(), rtol=rt, atol=at)
+    ew.restore(cpu, bc); ew.restore(gpu, bg)
+    sam_c = [torch.randn_like(p) * 1e-2 for p in cpu]
+    sam_g = [t.cuda() for t in sam_c]
+    vc = [torch.zeros(p.shape) for p in cpu]
+    vg = [torch.zeros(p.shape, device="cuda") for p in gpu]
+    gc, gg = [p.grad.clone() for p in cpu], [p.grad.clone() for p in gpu]
+    ew.looksam_direction_adjust(gc, sam_c, vc, 0.7)
+    ew.looksam_direction_adjust(gg, sam_g, vg, 0.7)
+    for a, b, c, d in zip(gc, gg, vc, vg):
+        assert torch.allclose(a.float(), b.float().cpu(), rtol=rt, atol=at)
+        assert torch.allclose(c, d.cpu(), rtol=1e-4, atol=1e-6)
+
+
+def test_reductions_are_deterministic_and_exact_enough():
+    gpu = make_params([(100003,), (7,), (8192 * 3 + 1,)], torch.float32, "cuda", 3)
+    gs = [p.grad for p in gpu]
+    a = ew.clip_coef_device(gs, 0.01).clone()
+    b = ew.clip_coef_device(gs, 0.01).clone()
+    assert torch.equal(a, b)                                      # bitwise reproducible: no float atomics
+    ref = sum(float(g.double().pow(2).sum()) for g in gs)
+    assert abs(float(a[0]) - ref) < 1e-5 * ref
+    assert abs(float(a[1]) - 0.01 / (ref ** 0.5 + 1e-6)) < 1e-6
+
+
+@pytest.mark.parametrize("sizes", [[1], [2, 3], [255, 256, 257], [5000, 1, 4097], [70000], [123, 40000, 9, 9000]])
+def test_segmented_sort_equals_stable_argsort(sizes):
+    C = _build.require()
+    torch.manual_seed(sum(sizes))
+    total = sum(sizes)
+    x = torch.randn(total, device="cuda")
+    x[torch.rand(total, device="cuda") < 0.3] = 0.5            # many ties: stability matters
+    x[::7] = 0.0
+    offs = [0]
+    for s in sizes:
+        offs.append(offs[-1] + s)
+    keys0 = x.abs().view(torch.int32).clone()
+    vals0 = torch.arange(total, device="cuda", dtype=torch.int32)
+    keys1, vals1 = torch.empty_like(keys0), torch.empty_like(vals0)
+    hist = torch.empty(256 * C.sg2_sort_blocks(total), dtype=torch.int32, device="cuda")
+    tot = torch.empty(256, dtype=torch.int32, device="cuda")
+    seg = torch.tensor(offs, dtype=torch.int64, device="cuda")
+    cur = C.sg2_sort(keys0, keys1, vals0, vals1, hist, tot, seg, len(sizes), total)
+    got = (vals1 if cur else vals0).long()
+    for a, b in zip(offs[:-1], offs[1:]):
+        ref = torch.argsort(x[a:b].abs(), stable=True) + a
+        assert torch.equal(got[a:b], ref)
+
+
+def _sg2_pair(shapes, dtype, seed=0, **kw):
+    cpu, gpu = _twins(shapes, dtype, seed)
+    torch.manual_seed(1)
+    oc = O.SuperGrok2(cpu, warmup_steps=0, warmup_ramp=1, **kw)
+    with torch.no_grad():
+        for blk in (oc.meta_net.mamba_fwd, oc.meta_net.mamba_bwd):
+            blk.rope_freq.mul_(20)
+        oc.meta_net.expert_W1.mul_(30); oc.meta_net.expert_W2.mul_(30)
+        for k in list(oc.meta_net.product_keys_A) + list(oc.meta_net.product_keys_B):
+            k.mul_(10)
+    og = O.SuperGrok2(gpu, warmup_steps=0, warmup_ramp=1, meta_net=copy.deepcopy(oc.meta_net).cuda(), **kw)
+    return cpu, gpu, oc, og
+
+
+@pytest.mark.parametrize("chunk", [0, 512])
+@pytest.mark.parametrize("shapes", [[(1,)], [(15,), (16,), (17,)], [(255,), (3, 100)], [(1100,), (40, 50), (513,)]])
+def test_sg2_step_matches_cpu_oracle(shapes, chunk):
+    cpu, gpu, oc, og = _sg2_pair(shapes, torch.float32)
+    og.scan_chunk_len = chunk
+    oc._ensure_state(); og._ensure_state()
+    for a, b in zip(oc._flat_sharpness, og._flat_sharpness):
+        a.uniform_(0, 1e-2); b.copy_(a)
+    for s in range(3):
+        oc.step(train_acc=0.9); og.step(train_acc=0.9)
+        _sync_grads(cpu, gpu, 20 + s)
+    for i, (p, q) in enumerate(zip(cpu, gpu)):
+        assert torch.allclose(p, q.cpu(), rtol=1e-4, atol=2e-6), (i, (p - q.cpu()).abs().max())
+        assert torch.allclose(oc._flat_gru_states[i], og._flat_gru_states[i].cpu(), rtol=1e-3, atol=1e-5)
+        assert torch.allclose(oc._flat_mamba_fwd_states[i], og._flat_mamba_fwd_states[i].cpu(), rtol=1e-3, atol=1e-6)
+        assert torch.allclose(oc._flat_mamba_bwd_states[i], og._flat_mamba_bwd_states[i].cpu(), rtol=1e-3, atol=1e-6)
+        assert torch.allclose(oc._flat_mus[i], og._flat_mus[i].cpu(), rtol=1e-5, atol=1e-8)
+    assert torch.equal(oc.meta_net.expert_counts, og.meta_net.expert_counts.cpu())
+
+
+def test_sg2_multi_chunk_equals_single_chunk_and_is_deterministic():
+    res = []
+    for chunk in (1 << 20, 512, 512):
+        torch.manual_seed(0)
+        gpu = make_params([(20000,), (3000,)], torch.float32, "cuda", 5)
+        torch.manual_seed(1)
+        og = O.SuperGrok2(gpu)
+        with torch.no_grad():
+            og.meta_net.mamba_fwd.rope_freq.mul_(20); og.meta_net.expert_W1.mul_(30); og.meta_net.expert_W2.mul_(30)
+        og.scan_chunk_len = chunk
+        for s in range(2):
+            og.step(); set_grads(gpu, 30 + s)
+        res.append([p.detach().clone() for p in gpu] + [og._flat_mamba_fwd_states[0].clone()])
+    for a, b in zip(res[1], res[2]):
+        assert torch.equal(a, b)                                   # run-to-run bitwise equal
+    for a, b in zip(res[0], res[1]):
+        assert torch.allclose(a, b, rtol=1e-4, atol=1e-6)          # association order differs: tolerance
+
+
+def test_sg2_handles_nonfinite_and_half_precision():
+    gpu = make_params([(300,), (64, 8)], torch.bfloat16, "cuda", 6)
+    gpu[0].grad[5] = float("nan"); gpu[0].grad[9] = float("inf")
+    og = O.SuperGrok2(gpu)
+    og.step()
+    assert all(torch.isfinite(p).all() for p in gpu)
+
+
+def test_cuda_graph_capture_of_fused_steps():
+    gpu = make_params([(5000,), (33, 7)], torch.float32, "cuda", 7)
+    ref = [torch.nn.Parameter(p.detach().clone()) for p in gpu]
+    a = O.CUDAGraphOptimizer(O.Lion(gpu, lr=1e-3), warmup_steps=2)
+    b = O.Lion(ref, lr=1e-3)
+    for s in range(6):
+        set_grads(gpu, 40 + s)
+        for p, q in zip(gpu, ref):
+            q.grad = p.grad.clone()
+        a.step(); b.step()
+    assert a._graph is not None
+    for p, q in zip(gpu, ref):
+        assert torch.allclose(p, q, rtol=1e-6, atol=1e-8)

@@ -1,0 +1,277 @@
+"""CPU tests of the optimizer API and of the PyTorch oracle (no GPU needed)."""
+import math
+
+import pytest
+import torch
+import torch.nn.functional as F
+
+from supergrok15_b200 import optim as O
+from supergrok15_b200.models import Transformer
+from supergrok15_b200.ops import oracle
+from supergrok15_b200.optim.metanet import Mamba3PEERMetaNet, Mamba3ScanBlock, affine_scan_chunked
+
+from helpers import make_params, set_grads
+
+
+def _model_and_batch(seed=0):
+    torch.manual_seed(seed)
+    m = Transformer(1, 32, 2)
+    x = torch.randint(0, 97, (64, 4))
+    y = torch.randint(0, 97, (64,))
+    return m, x, y
+
+
+FACTORIES = {
+    "adamw": lambda m: O.AdamW(m.parameters(), lr=1e-3),
+    "lion": lambda m: O.Lion(m.parameters()),
+    "grokfast": lambda m: O.Grokfast(m.parameters()),
+    "grokadamw": lambda m: O.GrokAdamW(m.parameters()),
+    "prodigy": lambda m: O.Prodigy(m.parameters(), lr=1e-3),
+    "neuralgrok": lambda m: O.NeuralGrok(m.parameters()),
+    "looksam": lambda m: O.LookSAM(m.parameters()),
+    "muon": lambda m: O.Muon([p for p in m.parameters() if p.dim() == 2], [p for p in m.parameters() if p.dim() != 2]),
+    "supergrok15": lambda m: O.SuperGrok15(m.parameters()),
+    "supergrok11": lambda m: O.SuperGrok11(m.parameters()),
+    "supergrok2": lambda m: O.SuperGrok2(m.parameters()),
+}
+
+
+def test_prodigy_follows_reference_formula():
+    """The reference's distance estimate divides by sum(s) with s = EMA of (d*g)^2 (csrc/ops.cpp:470-478), which is
+    tiny, so d_lr jumps by many orders of magnitude on the second step.  That behaviour is kept; this test pins it."""
+    ps = make_params([(40,), (6, 7)], seed=5)
+    opt = O.Prodigy(ps, lr=1e-3)
+    p0 = [p.detach().clone() for p in ps]
+    g = [p.grad.clone() for p in ps]
+    opt.step()
+    assert opt.d_lr == 1e-6                         # sum(s) == 0 on the first step: no update of d_lr
+    d, b1, b2 = 1e-6, 0.9, 0.999
+    for p, q, gg in zip(ps, p0, g):
+        m = (1 - b1) * d * gg
+        v = (1 - b2) * d * d * gg * gg
+        ref = q * (1 - 1e-3 * d * 1.0) - (1e-3 / (1 - b1)) * m / ((v / (1 - b2)).sqrt() + d * 1e-8)
+        assert torch.allclose(p, ref, rtol=1e-5, atol=1e-8)
+    set_grads(ps, 9)
+    opt.step()
+    assert opt.d_lr > 1e-6                          # monotone, non-decreasing
+
+
+@pytest.mark.parametrize("name", [n for n in FACTORIES if n != "prodigy"])
+def test_every_optimizer_steps_and_reduces_loss(name):
+    m, x, y = _model_and_batch()
+    opt = FACTORIES[name](m)
+    losses = []
+    for _ in range(3 if name == "supergrok2" else 6):
+        opt.zero_grad()
+        loss = F.cross_entropy(m(x), y)
+        loss.backward()
+        losses.append(loss.item())
+        opt.step()
+    assert all(math.isfinite(l) for l in losses)
+    assert losses[-1] < losses[0]
+    for p in m.parameters():
+        assert torch.isfinite(p).all()
+
+
+def test_adamw_matches_torch():
+    a = make_params([(7, 5), (11,)], seed=1)
+    b = [torch.nn.Parameter(p.detach().clone()) for p in a]
+    oa, ob = O.AdamW(a, lr=1e-2, betas=(0.9, 0.98), weight_decay=0.5), torch.optim.AdamW(b, lr=1e-2, betas=(0.9, 0.98), weight_decay=0.5)
+    for s in range(5):
+        set_grads(a, s)
+        for p, q in zip(a, b):
+            q.grad = p.grad.clone()
+        oa.step(); ob.step()
+    for p, q in zip(a, b):
+        assert torch.allclose(p, q, rtol=1e-5, atol=1e-7)
+
+
+def test_state_dict_layouts_match_reference():
+    m, x, y = _model_and_batch()
+    expect = {"lion": {"exp_avg"}, "grokfast": {"step", "ema", "exp_avg", "exp_avg_sq"},
+              "grokadamw": {"step", "exp_avg", "exp_avg_sq", "ema"}, "prodigy": {"step", "exp_avg", "exp_avg_sq", "s", "param_init"},
+              "neuralgrok": {"step", "exp_avg", "exp_avg_sq"}, "looksam": {"step", "exp_avg", "exp_avg_sq", "sam_direction"}}
+    for name, keys in expect.items():
+        m, x, y = _model_and_batch()
+        opt = FACTORIES[name](m)
+        F.cross_entropy(m(x), y).backward()
+        opt.step()
+        sd = opt.state_dict()
+        assert set(sd["state"][0].keys()) == keys, name
+    opt = FACTORIES["muon"](m)
+    opt.zero_grad(); F.cross_entropy(m(x), y).backward(); opt.step()
+    sd = opt.state_dict()
+    assert sd["param_groups"][0]["group_type"] == "muon" and sd["param_groups"][1]["group_type"] == "adamw"
+    assert set(sd["state"][0].keys()) == {"momentum_buffer"}
+
+
+@pytest.mark.parametrize("name", ["supergrok15", "supergrok11", "supergrok2", "prodigy"])
+def test_state_dict_round_trip_resumes_identically(name):
+    m, x, y = _model_and_batch()
+    opt = FACTORIES[name](m)
+    def one(mm, oo):
+        oo.zero_grad(); F.cross_entropy(mm(x), y).backward(); oo.step(**({"train_acc": 0.5} if name.startswith("super") else {}))
+    one(m, opt); one(m, opt)
+    import copy
+    m2 = copy.deepcopy(m)
+    opt2 = FACTORIES[name](m2)
+    opt2.load_state_dict(copy.deepcopy(opt.state_dict()))
+    one(m, opt); one(m2, opt2)
+    for p, q in zip(m.parameters(), m2.parameters()):
+        assert torch.allclose(p, q, rtol=0, atol=0, equal_nan=True)
+
+
+def test_reference_compat_freezes_bias_correction_and_breaks_sam():
+    m, x, y = _model_and_batch()
+    opt = O.SuperGrok15(m.parameters(), reference_compat=True)
+    crit = torch.nn.CrossEntropyLoss()
+    crit(m(x), y).backward()
+    with pytest.raises(RuntimeError):
+        opt.sam_step(m, x, y, crit)
+    assert all(p.grad is None for p in m.parameters())          # the literal reference outcome
+    before = [p.detach().clone() for p in m.parameters()]
+    opt.step()                                                   # no gradients -> update skipped, step counted
+    assert opt.get_global_step() == 1
+    assert all(torch.equal(a, b) for a, b in zip(before, m.parameters()))
+    # frozen bias correction: two identical gradients give the same first-step-style scaling
+    ps = make_params([(50,)], seed=3)
+    o1 = O.SuperGrok15(ps, reference_compat=True, gradient_clipping=0.0)
+    o1.step(); set_grads(ps, 3); o1.step()
+    qs = make_params([(50,)], seed=3)
+    o2 = O.SuperGrok15(qs, reference_compat=False, gradient_clipping=0.0)
+    o2.step(); set_grads(qs, 3); o2.step()
+    assert not torch.allclose(ps[0], qs[0])
+
+
+def test_sam_step_fills_sharpness_and_restores_grads():
+    m, x, y = _model_and_batch()
+    opt = O.SuperGrok15(m.parameters())
+    crit = torch.nn.CrossEntropyLoss()
+    crit(m(x), y).backward()
+    g0 = [p.grad.clone() for p in m.parameters()]
+    p0 = [p.detach().clone() for p in m.parameters()]
+    loss = opt.sam_step(m, x, y, crit)
+    assert math.isfinite(loss)
+    assert all(torch.equal(a, p.grad) for a, p in zip(g0, m.parameters()))
+    assert all(torch.equal(a, p) for a, p in zip(p0, m.parameters()))
+    assert sum(float(s.abs().sum()) for s in opt._flat_sharpness) > 0
+    # oracle: explicit perturbation
+    norm = math.sqrt(sum(float(g.pow(2).sum()) for g in g0)) + 1e-12
+    with torch.no_grad():
+        for p, g in zip(m.parameters(), g0):
+            p.add_(g, alpha=opt.sam_rho / norm)
+    m.zero_grad(); crit(m(x), y).backward()
+    ref = (list(m.parameters())[3].grad - g0[3]).abs().reshape(-1)
+    assert torch.allclose(opt._flat_sharpness[3], ref, rtol=1e-4, atol=1e-7)
+
+
+def test_bilevel_updates_meta_net_and_restores_grads():
+    for cls in (O.SuperGrok15, O.SuperGrok2):
+        m, x, y = _model_and_batch()
+        opt = cls(m.parameters())
+        if cls is O.SuperGrok15:
+            with torch.no_grad():
+                opt.meta_net.rescale.fill_(0.1)
+        crit = torch.nn.CrossEntropyLoss()
+        crit(m(x), y).backward()
+        g0 = [p.grad.clone() for p in m.parameters()]
+        w0 = [p.detach().clone() for p in opt.meta_net.parameters()]
+        mo = torch.optim.Adam(opt.meta_net.parameters(), lr=1e-3)
+        v = opt.bilevel_step(m, x, y, x, y, crit, mo)
+        assert math.isfinite(v)
+        assert all(torch.equal(a, p.grad) for a, p in zip(g0, m.parameters()))
+        assert any(not torch.equal(a, p) for a, p in zip(w0, opt.meta_net.parameters()))
+
+
+def test_newton_schulz_gram_form_equals_left_form():
+    torch.manual_seed(0)
+    for shape in ((24, 8), (8, 24), (16, 16)):
+        X = torch.randn(shape, dtype=torch.float64)
+        X = X / X.norm()
+        assert torch.allclose(oracle.newton_schulz(X, 5), oracle.newton_schulz_gram(X, 5), rtol=1e-8, atol=1e-10)
+
+
+def test_muon_rejects_1d_in_matrix_group():
+    p = torch.nn.Parameter(torch.randn(5)); p.grad = torch.randn(5)
+    with pytest.raises(ValueError):
+        O.Muon([p]).step()
+
+
+@pytest.mark.parametrize("N", [1, 2, 15, 16, 17, 63, 64, 65, 200, 1000])
+def test_scan_serial_equals_chunked(N):
+    torch.manual_seed(N)
+    blk = Mamba3ScanBlock().double()
+    with torch.no_grad():
+        blk.rope_freq.mul_(30)           # make the rotation matter
+    x = torch.randn(N, 8, dtype=torch.float64)
+    h0 = torch.randn(16, 16, dtype=torch.float64) * 0.1
+    a, ha = blk(x, h0, impl="serial")
+    b, hb = blk(x, h0, impl="chunked")
+    assert torch.allclose(a, b, rtol=1e-9, atol=1e-11) and torch.allclose(ha, hb, rtol=1e-9, atol=1e-11)
+
+
+def test_scan_gradients_serial_equals_chunked():
+    torch.manual_seed(0)
+    blk = Mamba3ScanBlock().double()
+    x = torch.randn(70, 8, dtype=torch.float64)
+    outs = []
+    for impl in ("serial", "chunked"):
+        blk.zero_grad()
+        y, _ = blk(x, None, impl=impl)
+        (y * torch.linspace(0, 1, y.numel()).reshape(y.shape)).sum().backward()
+        outs.append([p.grad.clone() for p in blk.parameters()])
+    for ga, gb in zip(*outs):
+        assert torch.allclose(ga, gb, rtol=1e-8, atol=1e-11)
+
+
+def test_metanet_forward_shapes_and_state_persistence():
+    torch.manual_seed(0)
+    mn = Mamba3PEERMetaNet()
+    g, s = torch.randn(300) * 1e-2, torch.rand(300) * 1e-3
+    gru = torch.zeros(300, 4)
+    sm, gru2, hf, hb = mn(g, s, gru)
+    assert sm.shape == g.shape and gru2.shape == (300, 4) and hf.shape == (16, 16) and hb.shape == (16, 16)
+    assert int(mn.expert_counts.sum()) == 300 * 4
+    sm2, *_ = mn(g, s, gru2, hf, hb)
+    assert not torch.equal(sm, sm2)                 # persistent states change the output
+    sb, *_ = mn.forward_for_bilevel(g, s, gru)
+    assert sb.shape == g.shape and torch.isfinite(sb).all()
+
+
+def test_expert_recycling_replaces_dead_experts_reproducibly():
+    def run():
+        torch.manual_seed(0)
+        mn = Mamba3PEERMetaNet()
+        mn.expert_counts[:10] = 1000
+        gen = torch.Generator().manual_seed(7)
+        w_before = mn.expert_W1.detach().clone()
+        mn._recycle_dead_experts(generator=gen)
+        return mn, w_before
+    a, wb = run()
+    b, _ = run()
+    assert torch.equal(a.expert_W1, b.expert_W1)
+    assert int(a.expert_counts.sum()) == 0
+    assert torch.equal(a.expert_W1[:10], wb[:10]) and not torch.equal(a.expert_W1[10:], wb[10:])
+
+
+def test_supergrok_schedules():
+    ps = make_params([(10,)])
+    o = O.SuperGrok15(ps)
+    assert o._get_effective_sam_freq() == 20 and o._get_effective_bilevel_freq() == 30
+    o._cached_train_acc = 1.0
+    assert o._get_effective_sam_freq() == 4 or o._get_effective_sam_freq() == 3
+    assert abs(o.get_effective_wd() - 1.0 * (1 + 4 * o._sigmoid(20, 1.0, 0.9))) < 1e-12
+    o._global_step = 150
+    assert abs(o._get_ramp_factor() - 0.5) < 1e-12
+    o._update_alpha(1.0, 3.0, 0.1)
+    assert abs(o.get_cached_alpha() - 0.98 * math.exp(-0.1 * 2.0)) < 1e-12
+    o._update_alpha(1e-6, 3.0, 0.1)
+    assert abs(o.get_cached_alpha() - 0.98 * math.exp(-1.0)) < 1e-12
+
+
+def test_cuda_graph_wrapper_is_eager_on_cpu():
+    ps = make_params([(10,)])
+    w = O.CUDAGraphOptimizer(O.Lion(ps), warmup_steps=1)
+    for s in range(3):
+        set_grads(ps, s); w.step()
+    assert w._graph is None

@@ -1,0 +1,327 @@
+#!/usr/bin/env python
+"""Headline benchmark: train tokens/s of ZeRO-2 SuperGrok v2 on the modular-division transformer.
+
+Config (the ZeRO-2 configuration of the baseline spec): modular division mod 113, all pairs with b != 0,
+30 % train split; 6-layer post-LN decoder, d_model 512, 8 heads, MLP 2048, sequence length 4; bf16 model
+with fp32 master weights; global batch 8192 sequences, split evenly over the ranks (strong scaling);
+one step = forward + backward + gradient reduce-scatter + SuperGrok v2 step + parameter all-gather.
+Inputs are synthetic: batches are drawn (seeded) from the 3,797-row train split; weights are random-init.
+
+    python bench.py --gpus N --steps K --warmup W            # this framework
+    python bench.py --impl reference --gpus N ...             # the reference from baseline/_ref (own model,
+                                                              # own optimizer, DistributedDataParallel for N>1)
+
+Rank 0 prints one JSON line.  ``value`` is device-timed (CUDA events, max over ranks) with inputs resident
+on the device; ``e2e`` times the public call ``ZeroEngine.train_step`` on pinned host batches, including the
+host-to-device copy and the device-to-host read of the loss every step.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+P_MOD, FRAC_TRAIN, SEQ = 113, 0.3, 4
+NL, D, H = 6, 512, 8
+GLOBAL_BATCH = 8192
+NTOK = P_MOD + 2
+BASELINE_VALUE = None          # the reference publishes no throughput number
+
+
+def dist_setup(n):
+    import torch
+    import torch.distributed as dist
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    return rank, world, local
+
+
+def make_division_data(p, frac, seed):
+    """All (a, b != 0) pairs of a / b mod p as [a, p, b, p+1]; python-random shuffle; int(len*frac) train rows."""
+    import random
+    import torch
+    rng = random.Random(seed)
+    rows = []
+    for a in range(p):
+        for b in range(1, p):
+            rows.append(([a, p, b, p + 1], (a * pow(b, p - 2, p)) % p))
+    rng.shuffle(rows)
+    n = int(len(rows) * frac)
+    x = torch.tensor([r[0] for r in rows], dtype=torch.long)
+    y = torch.tensor([r[1] for r in rows], dtype=torch.long)
+    return x[:n], y[:n], x[n:], y[n:]
+
+
+def batches(tx, ty, n_steps, per_rank, rank, seed):
+    """Seeded synthetic batches: each step draws per_rank rows (with replacement) from the train split."""
+    import torch
+    g = torch.Generator().manual_seed(seed * 1000 + rank)
+    out = []
+    for _ in range(n_steps):
+        idx = torch.randint(0, tx.shape[0], (per_rank,), generator=g)
+        out.append((tx[idx].pin_memory(), ty[idx].pin_memory()))
+    return out
+
+
+class ClockSampler:
+    """Samples SM clock / throttle reasons with nvidia-smi while the timed region runs (rank 0 only)."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index=0):
+        self.proc, self.lines, self.gpu = None, [], gpu_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200",
+                                          "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except Exception:  # noqa: BLE001
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        sm, mx, reasons = [], [], set()
+        for l in self.lines:
+            f = [t.strip() for t in l.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def timed_loop(step_fn, K, world):
+    """barrier + sync, K steps between CUDA events, sync + barrier; returns max-over-ranks ms per step."""
+    import torch
+    import torch.distributed as dist
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(K):
+        step_fn(i)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = torch.tensor([e0.elapsed_time(e1)], device="cuda")
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        dist.barrier()
+    return float(ms.item()) / K
+
+
+def wall_loop(step_fn, K, world):
+    import torch
+    import torch.distributed as dist
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for i in range(K):
+        step_fn(i)
+    torch.cuda.synchronize()
+    dt = torch.tensor([time.perf_counter() - t0], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(dt, op=dist.ReduceOp.MAX)
+        dist.barrier()
+    return float(dt.item()) * 1e3 / K
+
+
+# ------------------------------------------------------------------------------------------------ this framework
+def run_ours(args, rank, world, local):
+    import torch
+    from supergrok15_b200 import _build
+    from supergrok15_b200.models import Transformer
+    from supergrok15_b200.parallel import ZeroEngine
+    _build.require()
+    dev = torch.device("cuda", local)
+    torch.manual_seed(0)
+    model = Transformer(NL, D, H, NTOK, SEQ).to(dev)
+    eng = ZeroEngine(model, "supergrok2", dict(lr=1e-3, betas=(0.9, 0.98), weight_decay=1.0), comm=args.comm,
+                     param_dtype=torch.bfloat16)
+    tx, ty, _, _ = make_division_data(P_MOD, FRAC_TRAIN, 0)
+    per_rank = GLOBAL_BATCH // world
+    W, K = args.warmup, args.steps
+    host = batches(tx, ty, W + 2 * K, per_rank, rank, 1)
+    dev_batches = [(x.to(dev), y.to(dev)) for x, y in host[:W + K]]
+    for i in range(W):
+        eng.train_step(*dev_batches[i])
+    eng.check()
+    l0 = eng.launches
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    ms = timed_loop(lambda i: eng.train_step(*dev_batches[W + i]), K, world)
+    launches_region = eng.launches - l0
+    losses = []
+
+    def e2e_step(i):
+        x, y = host[W + K + i]
+        losses.append(float(eng.train_step(x, y).item()))       # H2D of the batch, D2H of the loss, every step
+    e2e_ms = wall_loop(e2e_step, K, world)
+    clocks = sampler.stop() if rank == 0 else None
+    eng.check()
+    tokens = GLOBAL_BATCH * SEQ
+    # kernels of this package per step: prep(3) + sort(3*passes) + gather + scan(3) + elem launches + comm kernels
+    plan = eng.opt._native_plan[1] if getattr(eng.opt, "_native_plan", None) else None
+    per_step = 0
+    if plan is not None:
+        seg_passes = 0
+        x = plan.n - 1
+        while x > 0:
+            seg_passes += 1
+            x >>= 8
+        n_mt = -(-plan.n // 96)
+        per_step = 3 * n_mt + 1 + 3 * (4 + seg_passes) + 1 + (3 if plan.any_multi else 2) + n_mt
+    gpu_launches = per_step * K + launches_region
+    return {
+        "metric": "train tokens/s (max over ranks), ZeRO-2 SuperGrok v2", "value": tokens / (ms * 1e-3), "unit": "tokens/s",
+        "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": (tokens / (ms * 1e-3) / BASELINE_VALUE) if BASELINE_VALUE else None, "dtype": "bf16",
+        "data": "synthetic: seeded batches drawn from the mod-113 division train split; random-init weights",
+        "config": {"model": "6-layer post-LN decoder d512 h8 mlp2048 (19.0M params)", "global_batch": GLOBAL_BATCH, "seq_len": SEQ,
+                   "parallelism": f"zero2-dp{world}", "optimizer": "SuperGrok v2 (fp32 master, bf16 model)", "comm": eng.comm,
+                   "l2": "per-step working set (optimizer state + sort/scan workspace, > 1 GB per rank) exceeds the 126 MB L2"},
+        "clocks": clocks,
+        "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": per_rank * SEQ * 8 + per_rank * 8, "d2h_bytes_per_step": 4,
+                "api": "supergrok15_b200.parallel.ZeroEngine.train_step(pinned_x, pinned_y).item()"},
+        "gpu_launches": gpu_launches, "final_loss": losses[-1] if losses else None, "impl": "ours",
+    }
+
+
+# ------------------------------------------------------------------------------------------------ reference arm
+def run_reference(args, rank, world, local):
+    """The unmodified reference: its own Transformer (grokking_race_v2.py:321-331), its own SuperGrok2 optimizer through
+    grokking_optimizers (stock batched CUDA path), bf16 autocast over fp32 parameters, DDP over NCCL when N > 1."""
+    import types
+    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref_dir, "grokking_optimizers")):
+        return {"impl": "reference", "unavailable": "baseline/_ref is not installed (pip install --target baseline/_ref of the reference)"}
+    sys.path.insert(0, ref_dir)
+    sys.modules.pop("grokking_optimizers", None)
+    for name in ("matplotlib", "matplotlib.pyplot"):            # the driver imports matplotlib at module level for its plots
+        try:
+            __import__(name)
+        except Exception:  # noqa: BLE001
+            m = types.ModuleType(name)
+            m.use = lambda *a, **k: None
+            sys.modules[name] = m
+    import torch
+    import torch.nn.functional as F
+    try:
+        import grokking_optimizers as go
+        import grokking_race_v2 as ref
+    except Exception as e:  # noqa: BLE001
+        return {"impl": "reference", "unavailable": f"reference import failed: {type(e).__name__}: {str(e)[:160]}"}
+    if "baseline/_ref" not in os.path.abspath(go.__file__).replace("\\", "/"):
+        return {"impl": "reference", "unavailable": "grokking_optimizers resolved outside baseline/_ref"}
+    dev = torch.device("cuda", local)
+    torch.manual_seed(0)
+    model = ref.Transformer(NL, D, H, NTOK, SEQ).to(dev)
+    opt = go.SuperGrok2(model.parameters(), lr=1e-3, betas=(0.9, 0.98), weight_decay=1.0)
+    opt.meta_net.to(dev)
+    fwd = model
+    if world > 1:
+        from torch.nn.parallel import DistributedDataParallel as DDP
+        fwd = DDP(model, device_ids=[local])
+    tx, ty, _, _ = ref.make_data(P_MOD, FRAC_TRAIN, 0)
+    per_rank = GLOBAL_BATCH // world
+    W, K = args.warmup, args.steps
+    host = batches(tx, ty, W + 2 * K, per_rank, rank, 1)
+    dev_batches = [(x.to(dev), y.to(dev)) for x, y in host[:W + K]]
+
+    def train_step(x, y):
+        if x.device != dev:
+            x, y = x.to(dev, non_blocking=True), y.to(dev, non_blocking=True)
+        opt.zero_grad()
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            loss = F.cross_entropy(fwd(x).float(), y)
+        loss.backward()
+        opt.step()
+        return loss.detach()
+
+    for i in range(W):
+        train_step(*dev_batches[i])
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    ms = timed_loop(lambda i: train_step(*dev_batches[W + i]), K, world)
+    losses = []
+    e2e_ms = wall_loop(lambda i: losses.append(float(train_step(*host[W + K + i]).item())), K, world)
+    clocks = sampler.stop() if rank == 0 else None
+    tokens = GLOBAL_BATCH * SEQ
+    return {
+        "metric": "train tokens/s (max over ranks), ZeRO-2 SuperGrok v2", "value": tokens / (ms * 1e-3), "unit": "tokens/s",
+        "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: seeded batches drawn from the mod-113 division train split; random-init weights",
+        "config": {"model": "6-layer post-LN decoder d512 h8 mlp2048 (19.0M params)", "global_batch": GLOBAL_BATCH, "seq_len": SEQ,
+                   "parallelism": f"ddp{world} (the reference has no sharding; replicated optimizer)",
+                   "optimizer": "reference SuperGrok2, fp32 parameters, bf16 autocast",
+                   "l2": "per-step working set exceeds the 126 MB L2"},
+        "clocks": clocks,
+        "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": per_rank * SEQ * 8 + per_rank * 8, "d2h_bytes_per_step": 4},
+        "gpu_launches": None, "final_loss": losses[-1] if losses else None, "impl": "reference",
+        "build_note": "built from an unmodified source copy; only the copy's setup.py changed (GPU check dropped, gencode sm_100)",
+    }
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--comm", default=None, choices=[None, "p2p", "nvls", "nccl"])
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    import torch
+    if not torch.cuda.is_available():
+        if args.impl == "reference":
+            print(json.dumps({"impl": "reference", "unavailable": "no CUDA device in this process"}))
+            return
+        raise SystemExit("bench.py needs a CUDA device")
+    rank, world, local = dist_setup(args.gpus)
+    try:
+        res = run_reference(args, rank, world, local) if args.impl == "reference" else run_ours(args, rank, world, local)
+    except Exception as e:  # noqa: BLE001
+        if args.impl == "reference":
+            res = {"impl": "reference", "unavailable": f"reference run failed: {type(e).__name__}: {str(e)[:200]}"}
+        else:
+            raise
+    if rank == 0:
+        print(json.dumps(res))
+    if world > 1:
+        import torch.distributed as dist
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

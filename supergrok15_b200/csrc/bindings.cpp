@@ -136,7 +136,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     SG_OP(OP_RESTORE) SG_OP(OP_SHARP_RESTORE) SG_OP(OP_LOOKSAM_DIR) SG_OP(OP_LOOKSAM_ADJ) SG_OP(OP_MUON_MOMENTUM)
     SG_OP(OP_MUON_UPDATE) SG_OP(OP_SCALE) SG_OP(OP_SQNORM) SG_OP(OP_PRODIGY_REDUCE) SG_OP(OP_DIFF_SQNORM)
     SG_OP(SC_CLIP) SG_OP(SC_PRODIGY) SG_OP(SC_SG11_GATES) SG_OP(SC_SAM_SCALE) SG_OP(SC_LOOKSAM_NORMS)
-    SG_OP(SC_MUON_NORMS) SG_OP(SC_SG2_CLIP)
+    SG_OP(SC_MUON_NORMS) SG_OP(SC_SG2_CLIP) SG_OP(SC_SUM3)
 #undef SG_OP
     m.attr("ops") = ops;
     sgb::register_sg2(m);

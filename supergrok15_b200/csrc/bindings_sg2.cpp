@@ -12,7 +12,8 @@ void sg2_gather(const uint32_t* vals_sorted, const float* g_packed, const float*
 void sg2_scan(const void* items_dev, int n_items, int dir1_start, const void* tds_dev, int n_td, bool any_multi, const float* gs_sorted,
               const uint32_t* vals_sorted, float* agg, float* carry, float* ctx, cudaStream_t s);
 void sg2_elem(int dtype, const MTArgs& a, float beta2, float lr, float wd_eff, float eps, float rescale, float lamb_eff, const float* g_packed,
-              const float* s_packed, const float* ctx, int* expert_counts, cudaStream_t s);
+              const float* s_packed, const float* ctx, int* expert_counts, int n_peers, void* local_base, void* const* peer_base,
+              cudaStream_t s);
 size_t sg2_item_bytes();
 size_t sg2_td_bytes();
 }
@@ -59,18 +60,25 @@ void sg2_scan(Tensor items, int64_t n_items, int64_t dir1_start, Tensor tds, int
                  W("agg").data_ptr<float>(), W("carry").data_ptr<float>(), W("ctx").data_ptr<float>(), st);
 }
 
-void sg2_elem(const TL& params, const TL& ms, const TL& vs, const TL& mus, const TL& grus, const std::vector<std::vector<double>>& ts,
-              const std::vector<int64_t>& offsets, double beta2, double lr, double wd_eff, double eps, double rescale, double lamb_eff,
-              c10::optional<Tensor> expert_counts, py::dict ws) {
+// masters: empty, or one fp32 tensor per parameter.  peer_ptrs: base addresses of the peers' parameter buffers (same layout as
+// the local buffer starting at local_base); the updated parameters are also stored there (all-gather fused into the step).
+void sg2_elem(const TL& params, const TL& ms, const TL& vs, const TL& mus, const TL& grus, const TL& masters,
+              const std::vector<std::vector<double>>& ts, const std::vector<int64_t>& offsets, double beta2, double lr, double wd_eff,
+              double eps, double rescale, double lamb_eff, c10::optional<Tensor> expert_counts, py::dict ws, int64_t local_base,
+              const std::vector<int64_t>& peer_ptrs) {
     c10::cuda::CUDAGuard guard(params[0].device());
     cudaStream_t st = at::cuda::getCurrentCUDAStream();
     const int dt = dtype_code(params[0]);
     auto W = [&](const char* k) { return ws[k].cast<Tensor>(); };
     Tensor g = W("g"), s = W("s"), ctx = W("ctx");
     int* ec = expert_counts.has_value() ? expert_counts->data_ptr<int>() : nullptr;
-    for_each_launch({params, ms, vs, mus, grus}, ts, &offsets, [&](sg::MTArgs& a) {
+    TORCH_CHECK(peer_ptrs.size() <= 8, "at most 8 peers");
+    void* peers[8] = {nullptr};
+    for (size_t r = 0; r < peer_ptrs.size(); ++r) peers[r] = reinterpret_cast<void*>(static_cast<intptr_t>(peer_ptrs[r]));
+    for_each_launch({params, ms, vs, mus, grus, masters}, ts, &offsets, [&](sg::MTArgs& a) {
         sg::sg2_elem(dt, a, (float)beta2, (float)lr, (float)wd_eff, (float)eps, (float)rescale, (float)lamb_eff, g.data_ptr<float>(),
-                     s.data_ptr<float>(), ctx.data_ptr<float>(), ec, st);
+                     s.data_ptr<float>(), ctx.data_ptr<float>(), ec, (int)peer_ptrs.size(),
+                     reinterpret_cast<void*>(static_cast<intptr_t>(local_base)), peers, st);
     });
 }
 
@@ -107,7 +115,10 @@ py::dict sg2_layout() {
 void register_sg2(pybind11::module_& m) {
     m.def("sg2_prepare", &sg2_prepare);
     m.def("sg2_scan", &sg2_scan);
-    m.def("sg2_elem", &sg2_elem);
+    m.def("sg2_elem", &sg2_elem, py::arg("params"), py::arg("ms"), py::arg("vs"), py::arg("mus"), py::arg("grus"), py::arg("masters"),
+          py::arg("ts"), py::arg("offsets"), py::arg("beta2"), py::arg("lr"), py::arg("wd_eff"), py::arg("eps"), py::arg("rescale"),
+          py::arg("lamb_eff"), py::arg("expert_counts"), py::arg("ws"), py::arg("local_base") = 0,
+          py::arg("peer_ptrs") = std::vector<int64_t>());
     m.def("sg2_upload_weights", &sg2_upload_weights);
     m.def("sg2_sort", &sg2_sort);
     m.def("sg2_layout", &sg2_layout);

@@ -1,0 +1,296 @@
+// In-kernel collectives for the ZeRO-sharded optimizer step (sm_100a, NVLink 5 / NVSwitch).
+//
+// Every rank owns a shard of the optimizer state.  Gradients live in a buffer that every peer has mapped
+// (symmetric memory); so do the low-precision parameters.  The kernels here read the peers' gradient shards
+// with plain 16-byte peer loads (or one NVLS multimem.ld_reduce on the multicast address), reduce in fp32
+// registers, run the optimizer arithmetic on the owner's fp32 master / moments, and store the updated
+// low-precision parameters into every peer's parameter buffer (or one multimem.st): reduce-scatter, step and
+// all-gather are one pass over the shard and nothing round-trips through HBM in between.
+// A path that calls NCCL reduce_scatter / all_gather around a local kernel exists only as the baseline
+// (parallel/engine.py, comm="nccl").
+//
+// Cross-GPU ordering uses epoch flags in a signal pad with st.release.sys / ld.acquire.sys; waits are bounded.
+#include "sg_native.h"
+#include "comm.cuh"
+#include "optim_math.cuh"
+
+namespace sg {
+namespace {
+
+// ---- barrier: rank r publishes `epoch` in slot r of every pad, then waits for all slots of its own pad ----
+__global__ void barrier_kernel(PeerPtrs pads, int rank, int world, uint32_t epoch, int* status, unsigned long long timeout_ns, int site) {
+    const int r = threadIdx.x;
+    if (r < world) {
+        __threadfence_system();
+        st_release_sys(reinterpret_cast<uint32_t*>(pads.p[r]) + rank, epoch);
+        if (!wait_flag_ge(reinterpret_cast<uint32_t*>(pads.p[rank]) + r, epoch, timeout_ns))
+            atomicCAS(status, STATUS_OK, STATUS_TIMEOUT | (r << 8) | (site << 16));
+        __threadfence_system();
+    }
+}
+
+template <typename T> struct Vec8;      // 16-byte vector of a gradient dtype
+template <> struct Vec8<float> { static constexpr int N = 4; };
+template <> struct Vec8<__nv_bfloat16> { static constexpr int N = 8; };
+template <> struct Vec8<__half> { static constexpr int N = 8; };
+
+template <typename T, int N>
+__device__ __forceinline__ void acc_vec(const uint4& v, float (&acc)[N]) {
+    const T* h = reinterpret_cast<const T*>(&v);
+#pragma unroll
+    for (int k = 0; k < N; ++k) acc[k] += Cvt<T>::to(h[k]);
+}
+
+// ---- reduce-scatter pull: out[i] = scale * sum_r grad_r[off + i], i in [0, n) ----
+// grads.p[r] is rank r's gradient buffer (same layout everywhere).  n and off are multiples of 16 bytes / sizeof(T).
+template <typename T, bool NVLS>
+__global__ void __launch_bounds__(256) pull_reduce_kernel(PeerPtrs grads, const void* mc_grad, int world, int rank, int64_t off, int64_t n,
+                                                          float scale, float* __restrict__ out) {
+    constexpr int N = Vec8<T>::N;
+    const int64_t nv = n / N;
+    for (int64_t v = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v < nv; v += (int64_t)gridDim.x * blockDim.x) {
+        float acc[N];
+#pragma unroll
+        for (int k = 0; k < N; ++k) acc[k] = 0.f;
+        if (NVLS) {
+            const char* a = reinterpret_cast<const char*>(mc_grad) + (off + v * N) * sizeof(T);
+            if constexpr (sizeof(T) == 4) {
+                const float4 t = multimem_ld_reduce_f32x4(a);
+                acc[0] = t.x; acc[1] = t.y; acc[2] = t.z; acc[3] = t.w;
+            } else {
+                const uint4 t = multimem_ld_reduce_bf16x8(a);
+                acc_vec<T, N>(t, acc);
+            }
+        } else {
+            // start with a different peer on every rank so the 8 ranks do not all hit the same GPU at once
+            for (int k = 0; k < world; ++k) {
+                const int r = (rank + k) % world;
+                const uint4 t = *reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(grads.p[r]) + off + v * N);
+                acc_vec<T, N>(t, acc);
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < N; ++k) out[v * N + k] = acc[k] * scale;
+    }
+    // tail (n not a multiple of the vector width): scalar
+    for (int64_t i = nv * N + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        float a = 0.f;
+        for (int r = 0; r < world; ++r) a += Cvt<T>::to(reinterpret_cast<const T*>(grads.p[r])[off + i]);
+        out[i] = a * scale;
+    }
+}
+
+// ---- all-gather push: copy [off, off+n) of the local parameter buffer into every peer's buffer ----
+template <bool NVLS>
+__global__ void __launch_bounds__(256) push_kernel(PeerPtrs params, void* mc_param, int world, int rank, int64_t off_bytes, int64_t n_bytes) {
+    const int64_t nv = n_bytes / 16;
+    const char* src = reinterpret_cast<const char*>(params.p[rank]) + off_bytes;
+    for (int64_t v = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v < nv; v += (int64_t)gridDim.x * blockDim.x) {
+        const uint4 t = reinterpret_cast<const uint4*>(src)[v];
+        if (NVLS) {
+            multimem_st_u32x4(reinterpret_cast<char*>(mc_param) + off_bytes + v * 16, t);
+        } else {
+            for (int k = 1; k < world; ++k) {
+                const int r = (rank + k) % world;
+                reinterpret_cast<uint4*>(reinterpret_cast<char*>(params.p[r]) + off_bytes)[v] = t;
+            }
+        }
+    }
+    for (int64_t i = nv * 16 + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_bytes; i += (int64_t)gridDim.x * blockDim.x)
+        for (int k = 1; k < world; ++k) {
+            const int r = (rank + k) % world;
+            (reinterpret_cast<char*>(params.p[r]) + off_bytes)[i] = src[i];
+        }
+}
+
+// ---- fused reduce-scatter + optimizer step + all-gather on a flat shard (single pass) ----
+// OP 0: AdamW, OP 1: Lion.  Gradient dtype G (buffer of every rank), parameter dtype T (buffer of every rank),
+// fp32 master / moments local to the owner.  off/n in elements, multiples of 8.
+struct FlatStep {
+    float lr, beta1, beta2, eps, wd, bc1, bc2, gscale;
+    float* master; float* m; float* v;      // local shard arrays (index 0 = element `off`)
+};
+
+template <int OP, typename G, typename T>
+__global__ void __launch_bounds__(256) fused_rs_step_ag_kernel(PeerPtrs grads, PeerPtrs params, int world, int rank, int64_t off, int64_t n,
+                                                               FlatStep st) {
+    constexpr int N = 8;
+    const int64_t nv = n / N;
+    for (int64_t v = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v < nv; v += (int64_t)gridDim.x * blockDim.x) {
+        float g[N];
+#pragma unroll
+        for (int k = 0; k < N; ++k) g[k] = 0.f;
+        for (int kk = 0; kk < world; ++kk) {
+            const int r = (rank + kk) % world;
+            const G* src = reinterpret_cast<const G*>(grads.p[r]) + off + v * N;
+            if constexpr (sizeof(G) == 2) {
+                const uint4 t = *reinterpret_cast<const uint4*>(src);
+                const G* h = reinterpret_cast<const G*>(&t);
+#pragma unroll
+                for (int k = 0; k < N; ++k) g[k] += Cvt<G>::to(h[k]);
+            } else {
+#pragma unroll
+                for (int q = 0; q < 2; ++q) {
+                    const float4 t = reinterpret_cast<const float4*>(src)[q];
+                    g[4 * q] += t.x; g[4 * q + 1] += t.y; g[4 * q + 2] += t.z; g[4 * q + 3] += t.w;
+                }
+            }
+        }
+        float p[N], mm[N], vv[N];
+        const int64_t i0 = v * N;
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+            const float4 a = reinterpret_cast<const float4*>(st.master + i0)[q];
+            p[4 * q] = a.x; p[4 * q + 1] = a.y; p[4 * q + 2] = a.z; p[4 * q + 3] = a.w;
+            const float4 b = reinterpret_cast<const float4*>(st.m + i0)[q];
+            mm[4 * q] = b.x; mm[4 * q + 1] = b.y; mm[4 * q + 2] = b.z; mm[4 * q + 3] = b.w;
+            if (OP == 0) {
+                const float4 c = reinterpret_cast<const float4*>(st.v + i0)[q];
+                vv[4 * q] = c.x; vv[4 * q + 1] = c.y; vv[4 * q + 2] = c.z; vv[4 * q + 3] = c.w;
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < N; ++k) {
+            const float gg = g[k] * st.gscale;
+            if (OP == 0) p[k] = adam_update(p[k], gg, mm[k], vv[k], st.lr, st.beta1, st.beta2, st.eps, st.wd, st.bc1, st.bc2);
+            else         p[k] = lion_update(p[k], gg, mm[k], st.lr, st.beta1, st.beta2, st.wd);
+        }
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+            reinterpret_cast<float4*>(st.master + i0)[q] = make_float4(p[4 * q], p[4 * q + 1], p[4 * q + 2], p[4 * q + 3]);
+            reinterpret_cast<float4*>(st.m + i0)[q] = make_float4(mm[4 * q], mm[4 * q + 1], mm[4 * q + 2], mm[4 * q + 3]);
+            if (OP == 0) reinterpret_cast<float4*>(st.v + i0)[q] = make_float4(vv[4 * q], vv[4 * q + 1], vv[4 * q + 2], vv[4 * q + 3]);
+        }
+        // all-gather: the updated low-precision parameters go straight to every rank's buffer
+        if constexpr (sizeof(T) == 2) {
+            uint4 o;
+            T* h = reinterpret_cast<T*>(&o);
+#pragma unroll
+            for (int k = 0; k < N; ++k) h[k] = Cvt<T>::from(p[k]);
+            for (int kk = 0; kk < world; ++kk) {
+                const int r = (rank + kk) % world;
+                *reinterpret_cast<uint4*>(reinterpret_cast<T*>(params.p[r]) + off + i0) = o;
+            }
+        } else {
+            for (int kk = 0; kk < world; ++kk) {
+                const int r = (rank + kk) % world;
+                float4* d = reinterpret_cast<float4*>(reinterpret_cast<float*>(params.p[r]) + off + i0);
+                d[0] = make_float4(p[0], p[1], p[2], p[3]);
+                d[1] = make_float4(p[4], p[5], p[6], p[7]);
+            }
+        }
+    }
+}
+
+// ---- all-gather fused with the fp32 -> low-precision cast: master[0..n) -> every rank's parameter buffer at element `off` ----
+template <typename T>
+__global__ void __launch_bounds__(256) cast_push_kernel(PeerPtrs params, int world, int rank, int64_t off, int64_t n,
+                                                        const float* __restrict__ master) {
+    const int64_t nv = n / 8;
+    for (int64_t v = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v < nv; v += (int64_t)gridDim.x * blockDim.x) {
+        const float4 a = reinterpret_cast<const float4*>(master)[2 * v], b = reinterpret_cast<const float4*>(master)[2 * v + 1];
+        const float p[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+        if constexpr (sizeof(T) == 2) {
+            uint4 o;
+            T* h = reinterpret_cast<T*>(&o);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) h[k] = Cvt<T>::from(p[k]);
+            for (int kk = 0; kk < world; ++kk) {
+                const int r = (rank + kk) % world;
+                *reinterpret_cast<uint4*>(reinterpret_cast<T*>(params.p[r]) + off + v * 8) = o;
+            }
+        } else {
+            for (int kk = 0; kk < world; ++kk) {
+                const int r = (rank + kk) % world;
+                float4* d = reinterpret_cast<float4*>(reinterpret_cast<float*>(params.p[r]) + off + v * 8);
+                d[0] = a; d[1] = b;
+            }
+        }
+    }
+    for (int64_t i = nv * 8 + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+        for (int r = 0; r < world; ++r) reinterpret_cast<T*>(params.p[r])[off + i] = Cvt<T>::from(master[i]);
+}
+
+// ---- small deterministic all-reduce (sum) through per-rank slots: every rank ends with bitwise identical results ----
+// slots.p[r] is rank r's scratch [world][n]; rank `rank` writes its vector into slot `rank` of every peer, a barrier
+// follows (separate launch), then reduce_slots sums the slots in rank order.
+__global__ void __launch_bounds__(256) scatter_slots_kernel(PeerPtrs slots, int world, int rank, const float* __restrict__ vec, int n) {
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+        const float x = vec[i];
+        for (int r = 0; r < world; ++r) reinterpret_cast<float*>(slots.p[r])[(int64_t)rank * n + i] = x;
+    }
+}
+__global__ void __launch_bounds__(256) reduce_slots_kernel(const float* __restrict__ my_slots, int world, float* __restrict__ out, int n, float scale) {
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+        float a = 0.f;
+        for (int r = 0; r < world; ++r) a += my_slots[(int64_t)r * n + i];
+        out[i] = a * scale;
+    }
+}
+
+int grid_for(int64_t work_items) {
+    const int64_t b = (work_items + 255) / 256;
+    const int64_t cap = 148 * 8;
+    return (int)(b < 1 ? 1 : (b > cap ? cap : b));
+}
+
+}  // namespace
+
+void dist_barrier(const PeerPtrs& pads, int rank, int world, uint32_t epoch, int* status, unsigned long long timeout_ns, int site, cudaStream_t s) {
+    barrier_kernel<<<1, 32, 0, s>>>(pads, rank, world, epoch, status, timeout_ns, site);
+}
+
+void dist_pull_reduce(int dtype, bool nvls, const PeerPtrs& grads, const void* mc, int world, int rank, int64_t off, int64_t n, float scale,
+                      float* out, cudaStream_t s) {
+    if (n <= 0) return;
+    const int g = grid_for(n / 4);
+#define LAUNCH(T) \
+    if (nvls) pull_reduce_kernel<T, true><<<g, 256, 0, s>>>(grads, mc, world, rank, off, n, scale, out); \
+    else pull_reduce_kernel<T, false><<<g, 256, 0, s>>>(grads, mc, world, rank, off, n, scale, out);
+    switch (dtype) { case F32: LAUNCH(float) break; case BF16: LAUNCH(__nv_bfloat16) break; default: LAUNCH(__half) break; }
+#undef LAUNCH
+}
+
+void dist_push(bool nvls, const PeerPtrs& params, void* mc, int world, int rank, int64_t off_bytes, int64_t n_bytes, cudaStream_t s) {
+    if (n_bytes <= 0 || world <= 1) return;
+    const int g = grid_for(n_bytes / 16);
+    if (nvls) push_kernel<true><<<g, 256, 0, s>>>(params, mc, world, rank, off_bytes, n_bytes);
+    else push_kernel<false><<<g, 256, 0, s>>>(params, mc, world, rank, off_bytes, n_bytes);
+}
+
+void dist_fused_flat_step(int op, int gdtype, int pdtype, const PeerPtrs& grads, const PeerPtrs& params, int world, int rank, int64_t off,
+                          int64_t n, float lr, float beta1, float beta2, float eps, float wd, float bc1, float bc2, float gscale,
+                          float* master, float* m, float* v, cudaStream_t s) {
+    if (n <= 0) return;
+    FlatStep st{lr, beta1, beta2, eps, wd, bc1, bc2, gscale, master, m, v};
+    const int g = grid_for(n / 8);
+#define L2(OPV, G, T) fused_rs_step_ag_kernel<OPV, G, T><<<g, 256, 0, s>>>(grads, params, world, rank, off, n, st)
+#define L1(OPV) \
+    if (gdtype == BF16 && pdtype == BF16) L2(OPV, __nv_bfloat16, __nv_bfloat16); \
+    else if (gdtype == F32 && pdtype == BF16) L2(OPV, float, __nv_bfloat16); \
+    else if (gdtype == F32 && pdtype == F32) L2(OPV, float, float); \
+    else if (gdtype == F16 && pdtype == F16) L2(OPV, __half, __half); \
+    else L2(OPV, __nv_bfloat16, float);
+    if (op == 0) { L1(0) } else { L1(1) }
+#undef L1
+#undef L2
+}
+
+void dist_cast_push(int pdtype, const PeerPtrs& params, int world, int rank, int64_t off, int64_t n, const float* master, cudaStream_t s) {
+    if (n <= 0) return;
+    const int g = grid_for(n / 8);
+    switch (pdtype) {
+        case F32:  cast_push_kernel<float><<<g, 256, 0, s>>>(params, world, rank, off, n, master); break;
+        case BF16: cast_push_kernel<__nv_bfloat16><<<g, 256, 0, s>>>(params, world, rank, off, n, master); break;
+        default:   cast_push_kernel<__half><<<g, 256, 0, s>>>(params, world, rank, off, n, master); break;
+    }
+}
+
+void dist_scatter_slots(const PeerPtrs& slots, int world, int rank, const float* vec, int n, cudaStream_t s) {
+    if (n > 0) scatter_slots_kernel<<<grid_for(n), 256, 0, s>>>(slots, world, rank, vec, n);
+}
+void dist_reduce_slots(const float* my_slots, int world, float* out, int n, float scale, cudaStream_t s) {
+    if (n > 0) reduce_slots_kernel<<<grid_for(n), 256, 0, s>>>(my_slots, world, out, n, scale);
+}
+
+}  // namespace sg

@@ -261,11 +261,12 @@ __global__ void scalar_finalize_kernel(int op, const float* __restrict__ pt, int
                                        float a1, float a2) {
     // one warp; per-tensor entries are summed lane-strided then tree-reduced (fixed order)
     const int lane = threadIdx.x;
-    if (op == SC_CLIP || op == SC_SAM_SCALE || op == SC_PRODIGY) {
-        float s0 = 0.f, s1 = 0.f;
-        for (int t = lane; t < n; t += 32) { s0 += pt[3 * t]; s1 += pt[3 * t + 1]; }
-        s0 = warp_sum(s0); s1 = warp_sum(s1);
-        if (lane == 0) {
+    if (op == SC_CLIP || op == SC_SAM_SCALE || op == SC_PRODIGY || op == SC_SUM3) {
+        float s0 = 0.f, s1 = 0.f, s2 = 0.f;
+        for (int t = lane; t < n; t += 32) { s0 += pt[3 * t]; s1 += pt[3 * t + 1]; s2 += pt[3 * t + 2]; }
+        s0 = warp_sum(s0); s1 = warp_sum(s1); s2 = warp_sum(s2);
+        if (lane == 0 && op == SC_SUM3) { out[0] = s0; out[1] = s1; out[2] = s2; }
+        if (lane == 0 && op != SC_SUM3) {
             if (op == SC_CLIP) {
                 const float norm = sqrtf(s0);
                 out[0] = s0; out[1] = (norm > a0) ? a0 / (norm + 1e-6f) : 1.f; out[2] = norm;

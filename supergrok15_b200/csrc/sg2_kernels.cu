@@ -36,7 +36,7 @@ constexpr int ROW = 84;                    // floats per timestep row in shared 
 constexpr int SCAN_THREADS = 128;          // 8 items per CTA
 constexpr int ITEMS_PER_CTA = SCAN_THREADS / 16;
 
-__device__ __forceinline__ float softplus20(float x) { return x > 20.f ? x : log1pf(__expf(x)); }
+__device__ __forceinline__ float softplus20(float x) { return x > 20.f ? x : __logf(1.f + __expf(x)); }
 __device__ __forceinline__ float silu(float x) { return x / (1.f + __expf(-x)); }
 __device__ __forceinline__ float sigmoidf(float x) { return 1.f / (1.f + __expf(-x)); }
 
@@ -192,58 +192,46 @@ __device__ __forceinline__ void stage_a(float* __restrict__ tile, const float2* 
 // per (column, pair) transition: Abar_e, Abar_o, cos, sin from dt
 __device__ __forceinline__ void pair_coeffs(float dt, float ah_e, float ah_o, float f, float& abe, float& abo, float& cs, float& sn) {
     const float ae = dt * ah_e, ao = dt * ah_o;          // dt*A/2
-    const float de = 1.f - ae + 1e-8f, dd = 1.f - ao + 1e-8f;
+    // the reference denominator is 1 - dt*A/2 + 1e-8; dt*A/2 <= 0, so the sum is >= 1 and adding 1e-8 (less than
+    // half an ulp of 1) does not change the fp32 value: it is dropped
+    const float de = 1.f - ae, dd = 1.f - ao;
     const float r = __fdividef(1.f, de * dd);
     abe = (1.f + ae) * dd * r;
     abo = (1.f + ao) * de * r;
     __sincosf(dt * f, &sn, &cs);
 }
 
-// PHASE 1: aggregate map of a chunk.  PHASE 3: run the chunk from its carry-in and emit contexts.
-template <int DIR, int PHASE>
-__device__ void scan_body(const Item& it, const TensorDir* __restrict__ tds, const float2* __restrict__ gs,
-                          const uint32_t* __restrict__ vals_sorted, float* __restrict__ agg, const float* __restrict__ carry,
-                          float* __restrict__ ctx, float* __restrict__ tile, int item_idx, int j, unsigned hmask) {
+// PHASE 3: run a chunk forward from its carry-in; apply SiLU gate, D skip and out_proj; write the contexts.
+template <int DIR>
+__device__ void scan_phase3(const Item& it, const TensorDir* __restrict__ tds, const float2* __restrict__ gs,
+                            const uint32_t* __restrict__ vals_sorted, const float* __restrict__ carry, float* __restrict__ ctx,
+                            float* __restrict__ tile, int item_idx, int j, unsigned hmask) {
     constexpr int W = (DIR == 0) ? P::DIR0 : P::DIR1;
-    // column constants of lane j
-    float ah[16], f[8];
+    float ah[16], f[8], h[16];
 #pragma unroll
     for (int s = 0; s < 16; ++s) ah[s] = -0.5f * __expf(c_w[W + P::D_ALOG + j * 16 + s]);
 #pragma unroll
     for (int p = 0; p < 8; ++p) f[p] = c_w[W + P::D_ROPE + j * 8 + p];
     const float Dj = c_w[W + P::D_D + j];
-    float h[16];          // PHASE 3: state.  PHASE 1: bias part of the aggregate
-    float m[32];          // PHASE 1: 2x2 matrices of the aggregate (a,b,c,d per pair)
-    if (PHASE == 3) {
+    {
         const float* cin = carry + ((int64_t)item_idx * 16 + j) * 16;
 #pragma unroll
         for (int q = 0; q < 4; ++q) { const float4 t = reinterpret_cast<const float4*>(cin)[q]; h[4 * q] = t.x; h[4 * q + 1] = t.y; h[4 * q + 2] = t.z; h[4 * q + 3] = t.w; }
-    } else {
-#pragma unroll
-        for (int s = 0; s < 16; ++s) h[s] = 0.f;
-#pragma unroll
-        for (int p = 0; p < 8; ++p) { m[4 * p] = 1.f; m[4 * p + 1] = 0.f; m[4 * p + 2] = 0.f; m[4 * p + 3] = 1.f; }
     }
     for (int u0 = it.ub; u0 < it.ue; u0 += TILE_T) {
         const int cnt = (it.ue - u0 < TILE_T) ? (it.ue - u0) : TILE_T;
         stage_a<DIR>(tile, gs, it.off, it.n, u0 + j, j < cnt, j);
         __syncwarp(hmask);
-        // Stage B: lane j = column
-        for (int l = 0; l < cnt; ++l) {
-            const float* row = tile + l * ROW;
+        for (int l = 0; l < cnt; ++l) {                 // lane j = column
+            float* row = tile + l * ROW;
             const float x = row[j], dt = row[32 + j];
             float B[16], C[16];
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
                 const float4 t = reinterpret_cast<const float4*>(row + 48)[q];
                 B[4 * q] = t.x; B[4 * q + 1] = t.y; B[4 * q + 2] = t.z; B[4 * q + 3] = t.w;
-            }
-            if (PHASE == 3) {
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    const float4 t = reinterpret_cast<const float4*>(row + 64)[q];
-                    C[4 * q] = t.x; C[4 * q + 1] = t.y; C[4 * q + 2] = t.z; C[4 * q + 3] = t.w;
-                }
+                const float4 c = reinterpret_cast<const float4*>(row + 64)[q];
+                C[4 * q] = c.x; C[4 * q + 1] = c.y; C[4 * q + 2] = c.z; C[4 * q + 3] = c.w;
             }
             const float dtx = dt * x;
             float y = 0.f;
@@ -255,62 +243,97 @@ __device__ void scan_body(const Item& it, const TensorDir* __restrict__ tds, con
                 const float ne = fmaf(abe, he * cs - ho * sn, dtx * B[2 * p]);
                 const float no = fmaf(abo, ho * cs + he * sn, dtx * B[2 * p + 1]);
                 h[2 * p] = ne; h[2 * p + 1] = no;
-                if (PHASE == 3) {
-                    y = fmaf(ne, C[2 * p], fmaf(no, C[2 * p + 1], y));
-                } else {
-                    // M <- M_t * M with M_t = [[abe*cs, -abe*sn], [abo*sn, abo*cs]]
-                    const float a0 = m[4 * p], b0 = m[4 * p + 1], c0 = m[4 * p + 2], d0 = m[4 * p + 3];
-                    m[4 * p]     = abe * (cs * a0 - sn * c0);
-                    m[4 * p + 1] = abe * (cs * b0 - sn * d0);
-                    m[4 * p + 2] = abo * (sn * a0 + cs * c0);
-                    m[4 * p + 3] = abo * (sn * b0 + cs * d0);
-                }
+                y = fmaf(ne, C[2 * p], fmaf(no, C[2 * p + 1], y));
             }
-            if (PHASE == 3) {
-                const float z = row[16 + j];
-                const float o = fmaf(y, silu(z), Dj * x);
-                const_cast<float*>(row)[j] = o;        // park out_j in the x slot (only lane j reads x_j)
-            }
+            row[j] = fmaf(y, silu(row[16 + j]), Dj * x);   // park out_j in the x slot (only lane j reads x_j)
         }
-        if (PHASE == 3) {
-            __syncwarp(hmask);
-            // Stage C: lane l = timestep again: ctx = out_proj . out, written at the element's original index
-            if (j < cnt) {
-                const float* row = tile + j * ROW;
-                float o[16];
+        __syncwarp(hmask);
+        if (j < cnt) {                                    // lane = timestep again: ctx = out_proj . out at the ORIGINAL index
+            const float* row = tile + j * ROW;
+            float o[16];
 #pragma unroll
-                for (int q = 0; q < 4; ++q) { const float4 t = reinterpret_cast<const float4*>(row)[q]; o[4 * q] = t.x; o[4 * q + 1] = t.y; o[4 * q + 2] = t.z; o[4 * q + 3] = t.w; }
-                float c8[8];
+            for (int q = 0; q < 4; ++q) { const float4 t = reinterpret_cast<const float4*>(row)[q]; o[4 * q] = t.x; o[4 * q + 1] = t.y; o[4 * q + 2] = t.z; o[4 * q + 3] = t.w; }
+            float c8[8];
 #pragma unroll
-                for (int d = 0; d < 8; ++d) {
-                    float acc = 0.f;
+            for (int d = 0; d < 8; ++d) {
+                float acc = 0.f;
 #pragma unroll
-                    for (int k = 0; k < 16; ++k) acc = fmaf(c_w[W + P::D_OUT + d * 16 + k], o[k], acc);
-                    c8[d] = acc;
-                }
-                const int u = u0 + j;
-                const int pos = (DIR == 0) ? u : (it.n - 1 - u);
-                const uint32_t orig = vals_sorted[it.off + pos];
-                float4* dst = reinterpret_cast<float4*>(ctx + (int64_t)orig * 16 + DIR * 8);
-                dst[0] = make_float4(c8[0], c8[1], c8[2], c8[3]);
-                dst[1] = make_float4(c8[4], c8[5], c8[6], c8[7]);
+                for (int k = 0; k < 16; ++k) acc = fmaf(c_w[W + P::D_OUT + d * 16 + k], o[k], acc);
+                c8[d] = acc;
             }
+            const int u = u0 + j;
+            const int pos = (DIR == 0) ? u : (it.n - 1 - u);
+            const uint32_t orig = vals_sorted[it.off + pos];
+            float4* dst = reinterpret_cast<float4*>(ctx + (int64_t)orig * 16 + DIR * 8);
+            dst[0] = make_float4(c8[0], c8[1], c8[2], c8[3]);
+            dst[1] = make_float4(c8[4], c8[5], c8[6], c8[7]);
         }
         __syncwarp(hmask);
     }
-    if (PHASE == 3) {
-        if (it.last) {
-            float* dst = tds[it.td].h + j * 16;
+    if (it.last) {
+        float* dst = tds[it.td].h + j * 16;
 #pragma unroll
-            for (int q = 0; q < 4; ++q) reinterpret_cast<float4*>(dst)[q] = make_float4(h[4 * q], h[4 * q + 1], h[4 * q + 2], h[4 * q + 3]);
-        }
-    } else {
-        float* dst = agg + ((int64_t)item_idx * 16 + j) * 48;      // [pair][a b c d e o]
+        for (int q = 0; q < 4; ++q) reinterpret_cast<float4*>(dst)[q] = make_float4(h[4 * q], h[4 * q + 1], h[4 * q + 2], h[4 * q + 3]);
+    }
+}
+
+// PHASE 1: aggregate affine map (M, b) of a chunk:  h_end = M h_in + b.
+// The chunk is walked BACKWARDS in time with the suffix product S = M_last ... M_{t+1}:  b += S b_t ; S <- S M_t.
+// With contracting dynamics S underflows to exactly zero after a few hundred steps; from then on every earlier
+// timestep contributes exactly nothing, so the walk stops early (all 16 columns of the item agree by ballot).
+// The result is the same floating-point sum evaluated in a different order, not an approximation.
+template <int DIR>
+__device__ void scan_phase1(const Item& it, const float2* __restrict__ gs, float* __restrict__ agg, float* __restrict__ tile,
+                            int item_idx, int j, unsigned hmask) {
+    constexpr int W = (DIR == 0) ? P::DIR0 : P::DIR1;
+    float ah[16], f[8], b[16], m[32];
 #pragma unroll
-        for (int p = 0; p < 8; ++p) {
-            dst[6 * p] = m[4 * p]; dst[6 * p + 1] = m[4 * p + 1]; dst[6 * p + 2] = m[4 * p + 2]; dst[6 * p + 3] = m[4 * p + 3];
-            dst[6 * p + 4] = h[2 * p]; dst[6 * p + 5] = h[2 * p + 1];
+    for (int s = 0; s < 16; ++s) { ah[s] = -0.5f * __expf(c_w[W + P::D_ALOG + j * 16 + s]); b[s] = 0.f; }
+#pragma unroll
+    for (int p = 0; p < 8; ++p) { f[p] = c_w[W + P::D_ROPE + j * 8 + p]; m[4 * p] = 1.f; m[4 * p + 1] = 0.f; m[4 * p + 2] = 0.f; m[4 * p + 3] = 1.f; }
+    const int len = it.ue - it.ub;
+    const int ntile = (len + TILE_T - 1) / TILE_T;
+    for (int tI = ntile - 1; tI >= 0; --tI) {
+        const int u0 = it.ub + tI * TILE_T;
+        const int cnt = (it.ue - u0 < TILE_T) ? (it.ue - u0) : TILE_T;
+        stage_a<DIR>(tile, gs, it.off, it.n, u0 + j, j < cnt, j);
+        __syncwarp(hmask);
+        for (int l = cnt - 1; l >= 0; --l) {
+            const float* row = tile + l * ROW;
+            const float x = row[j], dt = row[32 + j];
+            float B[16];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const float4 t = reinterpret_cast<const float4*>(row + 48)[q];
+                B[4 * q] = t.x; B[4 * q + 1] = t.y; B[4 * q + 2] = t.z; B[4 * q + 3] = t.w;
+            }
+            const float dtx = dt * x;
+#pragma unroll
+            for (int p = 0; p < 8; ++p) {
+                float abe, abo, cs, sn;
+                pair_coeffs(dt, ah[2 * p], ah[2 * p + 1], f[p], abe, abo, cs, sn);
+                const float a0 = m[4 * p], b0 = m[4 * p + 1], c0 = m[4 * p + 2], d0 = m[4 * p + 3];
+                const float be = dtx * B[2 * p], bo = dtx * B[2 * p + 1];
+                b[2 * p]     = fmaf(a0, be, fmaf(b0, bo, b[2 * p]));
+                b[2 * p + 1] = fmaf(c0, be, fmaf(d0, bo, b[2 * p + 1]));
+                const float p1 = abe * cs, p2 = abe * sn, p3 = abo * sn, p4 = abo * cs;   // M_t = [[p1,-p2],[p3,p4]]
+                m[4 * p]     = fmaf(a0, p1, b0 * p3);
+                m[4 * p + 1] = fmaf(b0, p4, -a0 * p2);
+                m[4 * p + 2] = fmaf(c0, p1, d0 * p3);
+                m[4 * p + 3] = fmaf(d0, p4, -c0 * p2);
+            }
         }
+        bool zero = true;
+#pragma unroll
+        for (int k = 0; k < 32; ++k) zero = zero && (m[k] == 0.f);
+        __syncwarp(hmask);
+        if (__all_sync(hmask, zero)) break;
+    }
+    float* dst = agg + ((int64_t)item_idx * 16 + j) * 48;      // [pair][a b c d e o]
+#pragma unroll
+    for (int p = 0; p < 8; ++p) {
+        dst[6 * p] = m[4 * p]; dst[6 * p + 1] = m[4 * p + 1]; dst[6 * p + 2] = m[4 * p + 2]; dst[6 * p + 3] = m[4 * p + 3];
+        dst[6 * p + 4] = b[2 * p]; dst[6 * p + 5] = b[2 * p + 1];
     }
 }
 
@@ -329,10 +352,13 @@ __global__ void __launch_bounds__(SCAN_THREADS, 3) sg2_scan_kernel(const Item* _
     const Item it = items[item_idx];
     if (it.tensor < 0) return;
     if (PHASE == 1 && it.last) return;            // nobody consumes the aggregate of a last chunk
-    if (item_idx < dir1_start)
-        scan_body<0, PHASE>(it, tds, gs, vals_sorted, agg, carry, ctx, tiles[slot], item_idx, j, hmask);
-    else
-        scan_body<1, PHASE>(it, tds, gs, vals_sorted, agg, carry, ctx, tiles[slot], item_idx, j, hmask);
+    if (PHASE == 1) {
+        if (item_idx < dir1_start) scan_phase1<0>(it, gs, agg, tiles[slot], item_idx, j, hmask);
+        else                       scan_phase1<1>(it, gs, agg, tiles[slot], item_idx, j, hmask);
+    } else {
+        if (item_idx < dir1_start) scan_phase3<0>(it, tds, gs, vals_sorted, carry, ctx, tiles[slot], item_idx, j, hmask);
+        else                       scan_phase3<1>(it, tds, gs, vals_sorted, carry, ctx, tiles[slot], item_idx, j, hmask);
+    }
 }
 
 // Phase 2: carry-in of every chunk.  One CTA of 128 threads (column j, pair p) per (tensor, direction).
@@ -359,8 +385,9 @@ struct ElemParams {
     float beta2, lr, wd_eff, eps, rescale;
     const float* g_packed; const float* s_packed; const float* ctx;
     int* expert_counts;                // [144] or nullptr
-    // optional replication of the updated parameter (bf16) into peer buffers: filled by the distributed step
-    int n_peers; void* peer_param[8]; int64_t peer_elem_off;
+    // optional replication of the updated parameter into the same offset of peer buffers (fused all-gather):
+    // a parameter at local address local_base + d is also stored to peer_base[r] + d for r < n_peers
+    int n_peers; char* local_base; char* peer_base[8];
 };
 
 // roles: 0 = param (launch dtype), 1 = m, 2 = v, 3 = mu, 4 = gru [n,4], 6 = packed offset.  ts = alpha, beta1, bc1, bc2; lamb_eff in ts? no:
@@ -386,6 +413,8 @@ __global__ void __launch_bounds__(MT_THREADS) sg2_elem_kernel(const __grid_const
     float* V = reinterpret_cast<float*>(a.ptr[2][t]);
     float* MU = reinterpret_cast<float*>(a.ptr[3][t]);
     float4* GRU = reinterpret_cast<float4*>(a.ptr[4][t]);
+    float* MASTER = reinterpret_cast<float*>(a.ptr[5][t]);       // fp32 master copy of a low-precision parameter (may be null)
+    const ptrdiff_t pdelta = reinterpret_cast<char*>(param) - prm.local_base;
     const float alpha = a.ts[t][0], beta1 = a.ts[t][1], bc1 = a.ts[t][2], bc2 = a.ts[t][3];
 
     for (int64_t i = begin + threadIdx.x; i < end; i += MT_THREADS) {
@@ -462,9 +491,13 @@ __global__ void __launch_bounds__(MT_THREADS) sg2_elem_kernel(const __grid_const
         MU[i] = mu;
         const float fg = smart + lamb_eff * mu;
         float mm = M[i], vv = V[i];
-        const float pnew = adam_update(Cvt<T>::to(param[i]), fg, mm, vv, prm.lr, beta1, prm.beta2, prm.eps, prm.wd_eff, bc1, bc2);
+        const float pold = MASTER ? MASTER[i] : Cvt<T>::to(param[i]);
+        const float pnew = adam_update(pold, fg, mm, vv, prm.lr, beta1, prm.beta2, prm.eps, prm.wd_eff, bc1, bc2);
         M[i] = mm; V[i] = vv;
-        param[i] = Cvt<T>::from(pnew);
+        if (MASTER) MASTER[i] = pnew;
+        const T pt = Cvt<T>::from(pnew);
+        param[i] = pt;
+        for (int r = 0; r < prm.n_peers; ++r) reinterpret_cast<T*>(prm.peer_base[r] + pdelta)[i] = pt;
     }
     if (prm.expert_counts) {
         __syncthreads();
@@ -521,12 +554,15 @@ void sg2_scan(const void* items_dev, int n_items, int dir1_start, const void* td
 }
 
 void sg2_elem(int dtype, const MTArgs& a, float beta2, float lr, float wd_eff, float eps, float rescale, float lamb_eff,
-              const float* g_packed, const float* s_packed, const float* ctx, int* expert_counts, cudaStream_t s) {
+              const float* g_packed, const float* s_packed, const float* ctx, int* expert_counts, int n_peers, void* local_base,
+              void* const* peer_base, cudaStream_t s) {
     const int blocks = a.blk_start[a.n];
     if (blocks <= 0) return;
     ElemParams p{};
     p.beta2 = beta2; p.lr = lr; p.wd_eff = wd_eff; p.eps = eps; p.rescale = rescale;
-    p.g_packed = g_packed; p.s_packed = s_packed; p.ctx = ctx; p.expert_counts = expert_counts; p.n_peers = 0;
+    p.g_packed = g_packed; p.s_packed = s_packed; p.ctx = ctx; p.expert_counts = expert_counts;
+    p.n_peers = n_peers; p.local_base = reinterpret_cast<char*>(local_base);
+    for (int r = 0; r < n_peers && r < 8; ++r) p.peer_base[r] = reinterpret_cast<char*>(peer_base[r]);
     switch (dtype) {
         case F32:  sg2_elem_kernel<float><<<blocks, MT_THREADS, 0, s>>>(a, p, lamb_eff); break;
         case BF16: sg2_elem_kernel<__nv_bfloat16><<<blocks, MT_THREADS, 0, s>>>(a, p, lamb_eff); break;

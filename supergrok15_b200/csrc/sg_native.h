@@ -84,7 +84,8 @@ enum ScalarOp : int {
     SC_SAM_SCALE,       // in: per-tensor {sq}; out[0] = rho/(sqrt(sum)+1e-12)
     SC_LOOKSAM_NORMS,   // in: per-tensor {dsq, gsq}; out[2t] = dnorm<1e-12 ? 0 : 1/dnorm ; out[2t+1] = sqrt(gsq)
     SC_MUON_NORMS,      // in: per-tensor {sq}; out[t] = 1/(sqrt(sq)+1e-7)
-    SC_SG2_CLIP         // in: per-tensor {sq}; out[t] = norm>max ? max/(norm+1e-12) : 1
+    SC_SG2_CLIP,        // in: per-tensor {sq}; out[t] = norm>max ? max/(norm+1e-12) : 1
+    SC_SUM3             // in: per-tensor {a,b,c}; out[0..2] = column sums (fixed order)
 };
 void scalar_finalize(int op, const float* per_tensor, int n_tensors, float* out, float a0, float a1, float a2,
                      cudaStream_t s);
@@ -159,4 +160,14 @@ void sg2_segmented_sort(uint32_t* keys0, uint32_t* keys1, uint32_t* vals0, uint3
                         uint32_t* tot256, const int64_t* seg_offsets_dev, int n_seg, int64_t total, int* out_buf_index,
                         cudaStream_t s);
 
+}  // namespace sg
+
+// ----------------------------------------------------------------------------------------
+// In-kernel collectives (dist_kernels.cu)
+// ----------------------------------------------------------------------------------------
+namespace sg {
+constexpr int MAX_RANKS = 8;
+constexpr int STATUS_OK = 0;
+constexpr int STATUS_TIMEOUT = 1;     // status word = STATUS_TIMEOUT | (peer << 8) | (site << 16)
+struct PeerPtrs { void* p[MAX_RANKS]; };
 }  // namespace sg

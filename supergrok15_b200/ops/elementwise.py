@@ -72,8 +72,30 @@ def clip_coef_device(grads: Tensors, max_norm: float) -> torch.Tensor:
     dev = grads[0].device
     pt = sqnorm_per_tensor(grads)
     out = workspace(dev, "clip", 4)
-    _build.require().scalar_finalize(_op("SC_CLIP"), pt, len(grads), out, float(max_norm), 0.0, 0.0)
+    tot = _global_totals(pt, len(grads), dev)
+    _build.require().scalar_finalize(_op("SC_CLIP"), tot, 1, out, float(max_norm), 0.0, 0.0)
     return out
+
+
+_reducer = None
+
+
+def set_cross_rank_reducer(fn) -> None:
+    """Install ``fn(vec) -> vec`` (in-place sum over data-parallel ranks of a small fp32 device vector).
+    The sharded engine sets it around an optimizer step so global scalars (clip norm, Prodigy numerator and
+    denominator, SAM norm) cover the tensors owned by every rank; ``None`` removes it."""
+    global _reducer
+    _reducer = fn
+    oracle.reducer = fn
+
+
+def _global_totals(pt: torch.Tensor, n: int, dev) -> torch.Tensor:
+    """Column sums of the per-tensor [n,3] partials as a device [3] tensor, combined across ranks if sharded."""
+    tot = workspace(dev, "tot3", 4)
+    _build.require().scalar_finalize(_op("SC_SUM3"), pt, n, tot, 0.0, 0.0, 0.0)
+    if _reducer is not None:
+        _reducer(tot[:3])
+    return tot
 
 
 # --------------------------------------------------------------------------- steps
@@ -121,7 +143,8 @@ def prodigy_dlr(params, grads, ss, p0s, d_lr_dev: Optional[torch.Tensor], d_lr: 
         return oracle.prodigy_dlr(params, grads, ss, p0s, d_lr)
     C = _build.require()
     pt = _reduce("OP_PRODIGY_REDUCE", [params, grads, p0s, ss], len(params), params[0].device, "prodigy")
-    C.scalar_finalize(_op("SC_PRODIGY"), pt, len(params), d_lr_dev, 0.0, 0.0, 0.0)
+    tot = _global_totals(pt, len(params), params[0].device)
+    C.scalar_finalize(_op("SC_PRODIGY"), tot, 1, d_lr_dev, 0.0, 0.0, 0.0)
     return d_lr_dev
 
 
@@ -200,7 +223,8 @@ def sam_scale_device(grads: Tensors, rho: float) -> torch.Tensor:
     dev = grads[0].device
     pt = sqnorm_per_tensor(grads, "sam")
     out = workspace(dev, "sam_scale", 4)
-    _build.require().scalar_finalize(_op("SC_SAM_SCALE"), pt, len(grads), out, float(rho), 0.0, 0.0)
+    tot = _global_totals(pt, len(grads), dev)
+    _build.require().scalar_finalize(_op("SC_SAM_SCALE"), tot, 1, out, float(rho), 0.0, 0.0)
     return out
 
 

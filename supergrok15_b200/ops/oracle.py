@@ -21,6 +21,7 @@ from typing import List, Optional, Sequence
 import torch
 
 Tensors = List[torch.Tensor]
+reducer = None          # optional fn(vec)->vec summing a small vector over data-parallel ranks (set by the ZeRO engine)
 
 
 def _f(t: torch.Tensor) -> torch.Tensor:
@@ -41,7 +42,9 @@ def global_sqnorm(grads: Sequence[Optional[torch.Tensor]]) -> torch.Tensor:
         s = _f(g).pow(2).sum()
         tot = s if tot is None else tot + s
     if tot is None:
-        return torch.zeros(())
+        tot = torch.zeros(())
+    if reducer is not None:                       # sharded data parallelism: sum over the ranks' tensors
+        tot = reducer(tot.reshape(1).clone())[0]
     return tot
 
 
@@ -133,6 +136,9 @@ def prodigy_dlr(params: Tensors, grads: Tensors, s_bufs: Tensors, param_inits: T
             continue
         num = num + float((_f(g) * (_f(p) - p0.view(-1))).sum())
         den = den + float(s.view(-1).sum())
+    if reducer is not None:
+        nd = reducer(torch.tensor([num, den], dtype=torch.float32))
+        num, den = float(nd[0]), float(nd[1])
     if den > 1e-30:
         d_lr = max(d_lr, abs(num) / (den + 1e-12))
     return d_lr

@@ -191,7 +191,8 @@ _resident = {"owner": None}
 def step(opt, idx: List[int], per: List[Tuple[float, float, float, float, float]], *, beta2, lr, wd_eff, eps, clip):
     """One v2 update of tensors ``idx`` of ``opt``; ``per[k] = (alpha, lamb_eff, beta1, bc1, bc2)``."""
     params = [opt._flat_params[i] for i in idx]
-    grads = [p.grad for p in params]
+    gsrc = getattr(opt, "_grad_override", None)     # reduced fp32 gradients supplied by the ZeRO engine
+    grads = [gsrc[i] for i in idx] if gsrc else [p.grad for p in params]
     if not params[0].is_cuda:
         return _step_cpu(opt, idx, per, beta2=beta2, lr=lr, wd_eff=wd_eff, eps=eps, clip=clip)
     C = _build.require()
@@ -207,9 +208,13 @@ def step(opt, idx: List[int], per: List[Tuple[float, float, float, float, float]
     C.sg2_scan(plan.items, plan.n_items, plan.dir1_start, plan.tds, plan.n_td, plan.any_multi, buf, plan.ws)
     ts = [[a, b1, bc1, bc2] for (a, _l, b1, bc1, bc2) in per]
     counts = opt.meta_net.expert_counts if opt.meta_net.training else None
+    masters = getattr(opt, "_flat_masters", None)
+    push = getattr(opt, "_peer_push", None)         # (local_base, [peer bases]) set by the ZeRO engine
     C.sg2_elem(params, [opt._flat_exp_avgs[i] for i in idx], [opt._flat_exp_avg_sqs[i] for i in idx],
-               [opt._flat_mus[i] for i in idx], [opt._flat_gru_states[i] for i in idx], ts, offs, beta2, lr, wd_eff,
-               eps, float(opt.meta_net.rescale), float(per[0][1]), counts, plan.ws)
+               [opt._flat_mus[i] for i in idx], [opt._flat_gru_states[i] for i in idx],
+               [masters[i] for i in idx] if masters else [], ts, offs, beta2, lr, wd_eff,
+               eps, float(opt.meta_net.rescale), float(per[0][1]), counts, plan.ws,
+               push[0] if push else 0, push[1] if push else [])
 
 
 def clip_scrub(g: torch.Tensor, clip: float) -> torch.Tensor:
@@ -262,7 +267,8 @@ def bilevel_backward(opt, named, train_grads: Dict[str, torch.Tensor], val_grads
             continue
         vn = vg.norm()
         vu = vg / vn if float(vn) > 1e-12 else vg
-        g = clip_scrub(train_grads[name], opt.gradient_clipping)
+        g = train_grads[name].detach().reshape(-1).float()      # raw (unclipped) training gradient, as in the reference
+        g = torch.where(torch.isfinite(g), g, torch.zeros_like(g))
         s = opt._flat_sharpness[i].reshape(-1).float()
         with torch.enable_grad():
             def fwd(g=g, s=s, i=i):

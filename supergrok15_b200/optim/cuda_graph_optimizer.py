@@ -56,6 +56,7 @@ class CUDAGraphOptimizer:
             self._record_graph()
             if self._graph is None:
                 return self.optimizer.step()
+            self._graph.replay()          # capturing records the work without running it
             return None
         self._swap_grads()
         self._graph.replay()

@@ -1,0 +1,296 @@
+"""ZeRO-2 data-parallel training engine with in-kernel collectives.
+
+One process per GPU.  The model is replicated in low precision (bf16); gradients are written by autograd
+into one flat peer-mapped buffer; the fp32 master weights and every optimizer state are sharded: each
+rank keeps them only for the tensors (or flat range) it owns.  A step is
+
+    barrier (all gradients written)
+    owner pulls the peers' gradient shards over NVLink and reduces them in fp32 registers
+    sharded optimizer step on the fp32 master
+    updated low-precision parameters are stored into every peer's parameter buffer
+    barrier (all parameters written)
+
+For SuperGrok v2 the pull feeds the batched sort/scan pipeline and the element-step kernel itself stores
+the new bf16 parameters to the peers (all-gather fused into the step).  For AdamW and Lion the whole step
+is ONE kernel over the flat shard (reduce-scatter + step + all-gather).  The other optimizers use the
+pull kernel, their multi-tensor kernels on the fp32 master, and a cast-and-push kernel; their global
+scalars (clip norm, Prodigy numerator / denominator, SAM norm) are combined across ranks by a small
+deterministic slot all-reduce.  ``comm="nccl"`` runs the same sharded step around NCCL all-reduce /
+broadcast and is the baseline the fused path is measured against.
+
+Waits on peers are bounded on the device (``timeout_s``); ``check()`` raises ``CommTimeout`` when a wait
+ran out, leaving the CUDA context usable.
+"""
+from __future__ import annotations
+
+import os
+from typing import Dict, List, Optional
+
+import torch
+import torch.nn.functional as F
+
+from .. import _build
+from .. import optim as O
+from ..ops import elementwise as ew
+from . import ownership, symm
+
+FLAT_OPTIMIZERS = {"adamw": 0, "lion": 1}
+OPTIMIZERS = {"supergrok2": O.SuperGrok2, "supergrok15": O.SuperGrok15, "supergrok11": O.SuperGrok11,
+              "grokadamw": O.GrokAdamW, "neuralgrok": O.NeuralGrok, "prodigy": O.Prodigy, "grokfast": O.Grokfast,
+              "lion": O.Lion, "looksam": O.LookSAM, "muon": O.Muon, "adamw": O.AdamW}
+_DT = {torch.float32: "f32", torch.bfloat16: "bf16", torch.float16: "f16"}
+
+
+class CommTimeout(RuntimeError):
+    """A bounded device-side wait on a peer ran out (the peer id and the wait site are in the message)."""
+
+
+class ZeroEngine:
+    def __init__(self, model: torch.nn.Module, optimizer: str = "supergrok2", opt_kwargs: Optional[dict] = None,
+                 comm: Optional[str] = None, param_dtype: torch.dtype = torch.bfloat16, group=None,
+                 timeout_s: float = 20.0, criterion=None):
+        self.comm = comm or os.environ.get("GROK_COMM", "p2p")
+        assert self.comm in ("p2p", "nvls", "nccl")
+        self.rank, self.world = symm.world_info(group)
+        self.group = group
+        self.name = optimizer
+        self.opt_kwargs = dict(opt_kwargs or {})
+        self.timeout_s = timeout_s
+        self.criterion = criterion or F.cross_entropy
+        self.model = model.to(param_dtype)
+        self.params = [p for p in self.model.parameters() if p.requires_grad]
+        self.device = self.params[0].device
+        self.cuda = self.device.type == "cuda"
+        self.pdtype = param_dtype
+        numels = [p.numel() for p in self.params]
+        self.flat_mode = optimizer in FLAT_OPTIMIZERS
+        # ---- layout of the flat parameter / gradient buffers
+        if self.flat_mode:
+            self.owner = [0] * len(numels)
+            offs, pos = [], 0
+            for n in numels:
+                offs.append(pos)
+                pos += -(-n // 8) * 8
+            total = -(-pos // (8 * self.world)) * 8 * self.world
+            self.offsets, self.total = offs, total
+            self.regions = ownership.flat_ranges(total, self.world)
+        else:
+            self.owner = ownership.assign_tensors(numels, self.world)
+            self.offsets, self.regions, self.total = ownership.grouped_layout(numels, self.owner, self.world)
+        self.my_begin, self.my_end = self.regions[self.rank]
+        self.pbuf = symm.alloc(self.total, param_dtype, self.device, group)
+        self.gbuf = symm.alloc(self.total, param_dtype, self.device, group)
+        with torch.no_grad():
+            for p, off in zip(self.params, self.offsets):
+                view = self.pbuf.tensor[off:off + p.numel()].view(p.shape)
+                view.copy_(p.data)
+                p.data = view
+                p.grad = self.gbuf.tensor[off:off + p.numel()].view(p.shape)
+        # ---- signalling and small all-reduce scratch
+        self.pads = symm.alloc(64, torch.int32, self.device, group)
+        self.slots_n = 16384
+        self.slots = symm.alloc(self.slots_n * max(self.world, 1), torch.float32, self.device, group)
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.epoch = 0
+        # ---- owner state
+        n_own = self.my_end - self.my_begin
+        self.master = self.pbuf.tensor[self.my_begin:self.my_end].float().clone()          # fp32 master shard
+        self.gred = torch.zeros(max(n_own, 1), dtype=torch.float32, device=self.device)    # reduced fp32 gradient shard
+        self._build_optimizer()
+        self.steps = 0
+        self.launches = 0
+
+    # ------------------------------------------------------------------ construction
+    def _owned(self):
+        return [i for i, o in enumerate(self.owner) if o == self.rank]
+
+    def _build_optimizer(self):
+        kw = self.opt_kwargs
+        if self.flat_mode:
+            n = self.my_end - self.my_begin
+            self.m = torch.zeros(max(n, 8), dtype=torch.float32, device=self.device)
+            self.v = torch.zeros(max(n, 8), dtype=torch.float32, device=self.device) if self.name == "adamw" else None
+            self.hp = dict(lr=kw.get("lr", 1e-3 if self.name == "adamw" else 3e-4),
+                           betas=kw.get("betas", (0.9, 0.999) if self.name == "adamw" else (0.9, 0.99)),
+                           eps=kw.get("eps", 1e-8), weight_decay=kw.get("weight_decay", 1e-2 if self.name == "adamw" else 3.0))
+            self.opt = None
+            return
+        own = self._owned()
+        self.own_idx = own
+        b = self.my_begin
+        # the optimizer sees fp32 master views as its parameters; gradients are views of the reduced shard
+        self.master_views = [torch.nn.Parameter(self.master[self.offsets[i] - b:self.offsets[i] - b + self.params[i].numel()]
+                                                .view(self.params[i].shape), requires_grad=False) for i in own]
+        self.grad_views = [self.gred[self.offsets[i] - b:self.offsets[i] - b + self.params[i].numel()].view(self.params[i].shape)
+                           for i in own]
+        cls = OPTIMIZERS[self.name]
+        if self.name == "supergrok2":
+            # v2 updates the low-precision parameter views directly and keeps the fp32 master beside them
+            views = [torch.nn.Parameter(self.params[i].data, requires_grad=False) for i in own] or \
+                    [torch.nn.Parameter(torch.zeros(0, device=self.device))]
+            self.opt = cls(views, **kw)
+            if own:
+                self.opt._ensure_state()
+                self.opt._flat_masters = [mv.data.reshape(-1) for mv in self.master_views]
+                self.opt._grad_override = [g.reshape(-1) for g in self.grad_views]
+                if self.cuda and self.world > 1 and self.comm != "nccl":
+                    peers = [p for r, p in enumerate(self.pbuf.peer_ptrs) if r != self.rank]
+                    self.opt._peer_push = (self.pbuf.peer_ptrs[self.rank], peers)
+            self._fix_layer_schedules(own)
+        elif self.name == "muon":
+            p2 = [mv for mv in self.master_views if mv.dim() == 2]
+            p1 = [mv for mv in self.master_views if mv.dim() != 2]
+            self.opt = cls(p2 or [torch.nn.Parameter(torch.zeros(1, 1, device=self.device))], p1, **kw)
+        else:
+            self.opt = cls(self.master_views or [torch.nn.Parameter(torch.zeros(0, device=self.device))], **kw)
+            if hasattr(self.opt, "_flat_layer_beta1s"):
+                self._fix_layer_schedules(own)
+
+    def _fix_layer_schedules(self, own):
+        """Layer-wise beta1 / alpha factors are functions of the parameter's index in the FULL model."""
+        o = self.opt
+        n_all = len(self.params)
+        beta1 = o.param_groups[0]["betas"][0]
+        for k, i in enumerate(own):
+            o._flat_layer_beta1s[k] = beta1 * ((1.0 - o.gamma) ** i)
+            o._flat_layer_alphas[k] = 1.0 if o.gamma_alpha == 0.0 else (1.0 - o.gamma_alpha) ** (max(n_all - 1, 1) - i)
+
+    # ------------------------------------------------------------------ collectives
+    def _barrier(self, site: int):
+        if self.world == 1:
+            return
+        if self.cuda and self.comm != "nccl":
+            self.epoch += 1
+            _build.require().dist_barrier(self.pads.peer_ptrs, self.rank, self.epoch, self.status, self.timeout_s, site)
+            self.launches += 1
+        else:
+            import torch.distributed as dist
+            dist.barrier(self.group)
+
+    def all_reduce_small(self, vec: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
+        """In-place deterministic sum of a small fp32 vector over the ranks (bitwise identical everywhere)."""
+        if self.world == 1:
+            return vec.mul_(scale) if scale != 1.0 else vec
+        if self.cuda and self.comm != "nccl":
+            C = _build.require()
+            n = vec.numel()
+            assert n <= self.slots_n
+            C.dist_scatter_slots(self.slots.peer_ptrs, self.rank, vec.contiguous())
+            self._barrier(3)
+            C.dist_reduce_slots(self.slots.tensor, self.world, vec, scale)
+            self._barrier(4)            # slots may be overwritten only after everybody has read them
+            self.launches += 2
+            return vec
+        import torch.distributed as dist
+        dist.all_reduce(vec, group=self.group)
+        return vec.mul_(scale) if scale != 1.0 else vec
+
+    def check(self):
+        """Raise if a device-side wait timed out since the last check (reads one int from the device)."""
+        s = int(self.status.item())
+        if s & 0xff:
+            self.status.zero_()
+            raise CommTimeout(f"rank {self.rank}: wait on peer {(s >> 8) & 0xff} timed out at site {(s >> 16) & 0xff}")
+
+    # ------------------------------------------------------------------ step
+    def zero_grad(self):
+        self.gbuf.tensor.zero_()
+
+    @torch.no_grad()
+    def step(self, **metrics):
+        W, r = self.world, self.rank
+        C = _build.require() if self.cuda else None
+        n_own = self.my_end - self.my_begin
+        fused = self.cuda and self.comm != "nccl"
+        self._barrier(1)                                              # every rank's backward has written its gradients
+        if self.flat_mode and fused:
+            self.steps += 1
+            b1, b2 = self.hp["betas"]
+            f = [self.hp["lr"], b1, b2, self.hp["eps"], self.hp["weight_decay"], 1 - b1 ** self.steps, 1 - b2 ** self.steps,
+                 1.0 / W]
+            if n_own:
+                C.dist_fused_flat_step(FLAT_OPTIMIZERS[self.name], _DT[self.pdtype], _DT[self.pdtype], self.gbuf.peer_ptrs,
+                                       self.pbuf.peer_ptrs, r, self.my_begin, n_own, f, self.master, self.m, self.v)
+                self.launches += 1
+            self._barrier(2)
+            return
+        # ---- reduce-scatter
+        if fused:
+            if n_own:
+                C.dist_pull_reduce(_DT[self.pdtype], self.comm == "nvls" and self.gbuf.multicast_ptr != 0, self.gbuf.peer_ptrs,
+                                   self.gbuf.multicast_ptr, r, self.my_begin, n_own, 1.0 / W, self.gred)
+                self.launches += 1
+        else:
+            if W > 1:
+                import torch.distributed as dist
+                dist.all_reduce(self.gbuf.tensor, group=self.group)
+            if n_own:
+                self.gred[:n_own].copy_(self.gbuf.tensor[self.my_begin:self.my_end])
+                if W > 1:
+                    self.gred.mul_(1.0 / W)
+        # ---- sharded optimizer step
+        if self.flat_mode:                                            # CPU / NCCL path of AdamW / Lion on the flat shard
+            self.steps += 1
+            b1, b2 = self.hp["betas"]
+            mp = [self.master[:n_own]]
+            if self.name == "adamw":
+                ew.adamw(mp, [self.gred[:n_own]], [self.m[:n_own]], [self.v[:n_own]], [self.steps], self.hp["lr"], b1, b2,
+                         self.hp["eps"], self.hp["weight_decay"])
+            else:
+                ew.lion(mp, [self.gred[:n_own]], [self.m[:n_own]], self.hp["lr"], b1, b2, self.hp["weight_decay"])
+            self.pbuf.tensor[self.my_begin:self.my_end].copy_(self.master[:n_own])
+        elif self.name == "supergrok2":
+            if self.own_idx:
+                self.opt.step(**metrics)
+            else:
+                self.opt._global_step += 1
+            if not (fused and W > 1):
+                pass                                                  # parameters were written in place by the element kernel
+        else:
+            for mv, g in zip(self.master_views, self.grad_views):
+                mv.grad = g
+            ew.set_cross_rank_reducer(self.all_reduce_small if W > 1 else None)
+            try:
+                self.opt.step(**metrics) if metrics else self.opt.step()
+            finally:
+                ew.set_cross_rank_reducer(None)
+            if n_own:
+                if fused:
+                    C.dist_cast_push(_DT[self.pdtype], self.pbuf.peer_ptrs, r, self.my_begin, n_own, self.master)
+                    self.launches += 1
+                else:
+                    self.pbuf.tensor[self.my_begin:self.my_end].copy_(self.master[:n_own])
+        # ---- all-gather (baseline path only: the fused paths pushed already)
+        if W > 1 and not fused:
+            import torch.distributed as dist
+            for rr, (b, e) in enumerate(self.regions):
+                if e > b:
+                    dist.broadcast(self.pbuf.tensor[b:e], src=rr, group=self.group)
+        self._barrier(2)                                              # every rank's parameters are complete
+
+    # ------------------------------------------------------------------ the call a user makes
+    def train_step(self, x: torch.Tensor, y: torch.Tensor, **metrics) -> torch.Tensor:
+        """Host (pinned) or device batch in, loss tensor out: H2D copy, forward, backward, sharded fused step."""
+        if x.device != self.device:
+            x = x.to(self.device, non_blocking=True)
+            y = y.to(self.device, non_blocking=True)
+        self.zero_grad()
+        logits = self.model(x)
+        loss = self.criterion(logits.float(), y)
+        loss.backward()
+        self.step(**metrics)
+        return loss.detach()
+
+    # ------------------------------------------------------------------ introspection
+    def state_bytes(self) -> int:
+        n = self.master.numel() * 4 + self.gred.numel() * 4
+        if self.opt is not None:
+            for st in self.opt.state.values():
+                n += sum(t.numel() * t.element_size() for t in st.values() if torch.is_tensor(t))
+        return n
+
+    def nvlink_bytes_per_step(self) -> Dict[str, int]:
+        """Bytes this rank moves over NVLink per step on the fused path: pull ingress, push egress."""
+        es = torch.tensor([], dtype=self.pdtype).element_size()
+        n_own = self.my_end - self.my_begin
+        return {"rs_ingress": (self.world - 1) * n_own * es, "ag_egress": (self.world - 1) * n_own * es}

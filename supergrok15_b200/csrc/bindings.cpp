@@ -129,6 +129,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           py::arg("b2") = c10::nullopt, py::arg("hidden") = 0, py::arg("write_grad") = false,
           py::arg("partials") = c10::nullopt, py::arg("per_tensor_out") = c10::nullopt);
     m.def("scalar_finalize", &scalar_finalize);
+    m.def("launch_count", []() { return sg::launch_count(); });
     py::dict ops;
 #define SG_OP(X) ops[#X] = (int)sg::X;
     SG_OP(OP_ADAMW) SG_OP(OP_LION) SG_OP(OP_GROKFAST_EMA) SG_OP(OP_GROKFAST_ADAMW) SG_OP(OP_GROKADAMW)

@@ -237,12 +237,14 @@ int grid_for(int64_t work_items) {
 }  // namespace
 
 void dist_barrier(const PeerPtrs& pads, int rank, int world, uint32_t epoch, int* status, unsigned long long timeout_ns, int site, cudaStream_t s) {
+    count_launch();
     barrier_kernel<<<1, 32, 0, s>>>(pads, rank, world, epoch, status, timeout_ns, site);
 }
 
 void dist_pull_reduce(int dtype, bool nvls, const PeerPtrs& grads, const void* mc, int world, int rank, int64_t off, int64_t n, float scale,
                       float* out, cudaStream_t s) {
     if (n <= 0) return;
+    count_launch();
     const int g = grid_for(n / 4);
 #define LAUNCH(T) \
     if (nvls) pull_reduce_kernel<T, true><<<g, 256, 0, s>>>(grads, mc, world, rank, off, n, scale, out); \
@@ -253,6 +255,7 @@ void dist_pull_reduce(int dtype, bool nvls, const PeerPtrs& grads, const void* m
 
 void dist_push(bool nvls, const PeerPtrs& params, void* mc, int world, int rank, int64_t off_bytes, int64_t n_bytes, cudaStream_t s) {
     if (n_bytes <= 0 || world <= 1) return;
+    count_launch();
     const int g = grid_for(n_bytes / 16);
     if (nvls) push_kernel<true><<<g, 256, 0, s>>>(params, mc, world, rank, off_bytes, n_bytes);
     else push_kernel<false><<<g, 256, 0, s>>>(params, mc, world, rank, off_bytes, n_bytes);
@@ -262,6 +265,7 @@ void dist_fused_flat_step(int op, int gdtype, int pdtype, const PeerPtrs& grads,
                           int64_t n, float lr, float beta1, float beta2, float eps, float wd, float bc1, float bc2, float gscale,
                           float* master, float* m, float* v, cudaStream_t s) {
     if (n <= 0) return;
+    count_launch();
     FlatStep st{lr, beta1, beta2, eps, wd, bc1, bc2, gscale, master, m, v};
     const int g = grid_for(n / 8);
 #define L2(OPV, G, T) fused_rs_step_ag_kernel<OPV, G, T><<<g, 256, 0, s>>>(grads, params, world, rank, off, n, st)
@@ -278,6 +282,7 @@ void dist_fused_flat_step(int op, int gdtype, int pdtype, const PeerPtrs& grads,
 
 void dist_cast_push(int pdtype, const PeerPtrs& params, int world, int rank, int64_t off, int64_t n, const float* master, cudaStream_t s) {
     if (n <= 0) return;
+    count_launch();
     const int g = grid_for(n / 8);
     switch (pdtype) {
         case F32:  cast_push_kernel<float><<<g, 256, 0, s>>>(params, world, rank, off, n, master); break;
@@ -287,9 +292,11 @@ void dist_cast_push(int pdtype, const PeerPtrs& params, int world, int rank, int
 }
 
 void dist_scatter_slots(const PeerPtrs& slots, int world, int rank, const float* vec, int n, cudaStream_t s) {
+    if (n > 0) count_launch();
     if (n > 0) scatter_slots_kernel<<<grid_for(n), 256, 0, s>>>(slots, world, rank, vec, n);
 }
 void dist_reduce_slots(const float* my_slots, int world, float* out, int n, float scale, cudaStream_t s) {
+    if (n > 0) count_launch();
     if (n > 0) reduce_slots_kernel<<<grid_for(n), 256, 0, s>>>(my_slots, world, out, n, scale);
 }
 

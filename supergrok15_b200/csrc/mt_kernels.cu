@@ -9,6 +9,7 @@
 // atomics): results are bitwise reproducible run to run.
 #include "sg_native.h"
 #include "optim_math.cuh"
+#include <atomic>
 
 namespace sg {
 
@@ -301,7 +302,12 @@ __global__ void scalar_finalize_kernel(int op, const float* __restrict__ pt, int
 
 }  // namespace
 
+static std::atomic<long long> g_launches{0};
+void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+long long launch_count() { return g_launches.load(std::memory_order_relaxed); }
+
 void mt_launch(int op, int dtype, const MTArgs& a, const MTParams& p, cudaStream_t s) {
+    if (a.blk_start[a.n] > 0) count_launch();
     switch (op) {
 #define SG_CASE(X) case X: launch_typed<X>(dtype, a, p, s); break;
         SG_CASE(OP_ADAMW) SG_CASE(OP_LION) SG_CASE(OP_GROKFAST_EMA) SG_CASE(OP_GROKFAST_ADAMW) SG_CASE(OP_GROKADAMW)
@@ -316,11 +322,13 @@ void mt_launch(int op, int dtype, const MTArgs& a, const MTParams& p, cudaStream
 
 void mt_finalize_per_tensor(const MTArgs& a, const float* partials, float* out, cudaStream_t s) {
     if (a.n <= 0) return;
+    count_launch();
     finalize_per_tensor_kernel<<<a.n, 32, 0, s>>>(a, partials, out);
 }
 
 void scalar_finalize(int op, const float* per_tensor, int n_tensors, float* out, float a0, float a1, float a2,
                      cudaStream_t s) {
+    count_launch();
     scalar_finalize_kernel<<<1, 32, 0, s>>>(op, per_tensor, n_tensors, out, a0, a1, a2);
 }
 

@@ -516,6 +516,7 @@ void sg2_upload_weights(const float* packed_dev, cudaStream_t s) {
 void sg2_sqnorm(int dtype, const MTArgs& a, float* partials, cudaStream_t s) {
     const int blocks = a.blk_start[a.n];
     if (blocks <= 0) return;
+    count_launch();
     switch (dtype) {
         case F32:  sg2_sqnorm_kernel<float><<<blocks, MT_THREADS, 0, s>>>(a, partials); break;
         case BF16: sg2_sqnorm_kernel<__nv_bfloat16><<<blocks, MT_THREADS, 0, s>>>(a, partials); break;
@@ -527,6 +528,7 @@ void sg2_prep(int dtype, const MTArgs& a, const float* tclip, float* g_packed, f
               cudaStream_t s) {
     const int blocks = a.blk_start[a.n];
     if (blocks <= 0) return;
+    count_launch();
     switch (dtype) {
         case F32:  sg2_prep_kernel<float><<<blocks, MT_THREADS, 0, s>>>(a, tclip, g_packed, s_packed, keys, vals); break;
         case BF16: sg2_prep_kernel<__nv_bfloat16><<<blocks, MT_THREADS, 0, s>>>(a, tclip, g_packed, s_packed, keys, vals); break;
@@ -537,6 +539,7 @@ void sg2_prep(int dtype, const MTArgs& a, const float* tclip, float* g_packed, f
 void sg2_gather(const uint32_t* vals_sorted, const float* g_packed, const float* s_packed, float* gs_sorted, int64_t total,
                 cudaStream_t s) {
     if (total <= 0) return;
+    count_launch();
     sg2_gather_kernel<<<(unsigned)((total + 255) / 256), 256, 0, s>>>(vals_sorted, g_packed, s_packed,
                                                                        reinterpret_cast<float2*>(gs_sorted), total);
 }
@@ -548,6 +551,7 @@ void sg2_scan(const void* items_dev, int n_items, int dir1_start, const void* td
     const Item* items = reinterpret_cast<const Item*>(items_dev);
     const TensorDir* tds = reinterpret_cast<const TensorDir*>(tds_dev);
     const float2* gs = reinterpret_cast<const float2*>(gs_sorted);
+    count_launch(any_multi ? 3 : 2);
     if (any_multi) sg2_scan_kernel<1><<<blocks, SCAN_THREADS, 0, s>>>(items, n_items, dir1_start, tds, gs, vals_sorted, agg, carry, ctx);
     sg2_carry_kernel<<<n_td, 128, 0, s>>>(tds, agg, carry);
     sg2_scan_kernel<3><<<blocks, SCAN_THREADS, 0, s>>>(items, n_items, dir1_start, tds, gs, vals_sorted, agg, carry, ctx);
@@ -558,6 +562,7 @@ void sg2_elem(int dtype, const MTArgs& a, float beta2, float lr, float wd_eff, f
               void* const* peer_base, cudaStream_t s) {
     const int blocks = a.blk_start[a.n];
     if (blocks <= 0) return;
+    count_launch();
     ElemParams p{};
     p.beta2 = beta2; p.lr = lr; p.wd_eff = wd_eff; p.eps = eps; p.rescale = rescale;
     p.g_packed = g_packed; p.s_packed = s_packed; p.ctx = ctx; p.expert_counts = expert_counts;

@@ -161,6 +161,7 @@ void sg2_segmented_sort(uint32_t* keys0, uint32_t* keys1, uint32_t* vals0, uint3
         int seg_passes = 0;
         for (int x = n_seg - 1; x > 0; x >>= 8) ++seg_passes;     // bytes needed for the largest segment id
         for (int pass = 0; pass < 4 + seg_passes; ++pass) {
+            count_launch(3);
             sort_hist_kernel<<<nb, SORT_THREADS, 0, s>>>(k[cur], v[cur], hist, seg_offsets_dev, n_seg, total, pass, nb);
             sort_scan_rows_kernel<<<256, 256, 0, s>>>(hist, tot, nb);
             sort_scatter_kernel<<<nb, SORT_THREADS, 0, s>>>(k[cur], v[cur], k[cur ^ 1], v[cur ^ 1], hist, tot, seg_offsets_dev,

@@ -32,6 +32,10 @@ struct MTArgs {
 
 enum DType : int { F32 = 0, BF16 = 1, F16 = 2 };
 
+// Number of kernels of this library enqueued so far by this process (every launcher counts its launches).
+void count_launch(int n = 1);
+long long launch_count();
+
 // Element-wise optimizer ids (pointer roles listed per op; p/g use the launch dtype, the rest fp32).
 enum MTOp : int {
     OP_ADAMW = 0,        // p g m v                ts: bc1 bc2

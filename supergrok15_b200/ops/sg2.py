@@ -231,7 +231,8 @@ def _step_cpu(opt, idx, per, *, beta2, lr, wd_eff, eps, clip):
     for k, i in enumerate(idx):
         p = opt._flat_params[i]
         alpha, lamb_eff, b1, bc1, bc2 = per[k]
-        g = clip_scrub(p.grad, clip)
+        gsrc = getattr(opt, "_grad_override", None)
+        g = clip_scrub(gsrc[i] if gsrc else p.grad, clip)
         s = opt._flat_sharpness[i].reshape(-1).float()
         s = torch.where(torch.isfinite(s), s, torch.zeros_like(s))
         smart, gru, hf, hb = mn(g, s, opt._flat_gru_states[i], opt._flat_mamba_fwd_states[i],
@@ -239,8 +240,12 @@ def _step_cpu(opt, idx, per, *, beta2, lr, wd_eff, eps, clip):
         opt._flat_gru_states[i].copy_(gru)
         opt._flat_mamba_fwd_states[i].copy_(hf)
         opt._flat_mamba_bwd_states[i].copy_(hb)
-        oracle.sg2_adam_(p, smart.reshape(-1).float(), g, opt._flat_mus[i], opt._flat_exp_avgs[i],
+        masters = getattr(opt, "_flat_masters", None)
+        tgt = masters[i] if masters else p                 # fp32 master copy under ZeRO, else the parameter itself
+        oracle.sg2_adam_(tgt, smart.reshape(-1).float(), g, opt._flat_mus[i], opt._flat_exp_avgs[i],
                          opt._flat_exp_avg_sqs[i], alpha, lamb_eff, b1, beta2, lr, wd_eff, eps, bc1, bc2)
+        if masters:
+            p.detach().copy_(tgt.reshape(p.shape).to(p.dtype))
 
 
 # --------------------------------------------------------------------------- bilevel

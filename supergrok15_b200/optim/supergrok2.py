@@ -88,7 +88,9 @@ class SuperGrok2(SuperGrok15):
         lr, beta2, eps = group["lr"], group["betas"][1], group["eps"]
         wd_eff = self._get_effective_wd(group["weight_decay"])
         lamb_eff = self.lamb * ramp * gate
-        idx = [i for i, p in enumerate(self._flat_params) if p.grad is not None and p.numel() > 0]
+        gsrc = getattr(self, "_grad_override", None)       # reduced gradients handed in by the ZeRO engine
+        idx = [i for i, p in enumerate(self._flat_params)
+               if p.numel() > 0 and (gsrc is not None or p.grad is not None)]
         if not idx:
             return loss
         per = []

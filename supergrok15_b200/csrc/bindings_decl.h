@@ -5,4 +5,5 @@ namespace sgb {
 void register_sg2(pybind11::module_& m);
 void register_dist(pybind11::module_& m);
 void register_gemm(pybind11::module_& m);
+void register_nn(pybind11::module_& m);
 }

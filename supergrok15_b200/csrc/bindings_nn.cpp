@@ -1,0 +1,84 @@
+// Bindings of the model-side kernels (short-sequence attention, LayerNorm with residual).
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include "bindings_decl.h"
+#include "mt_host.h"
+
+namespace sg {
+bool attn_small_supported(int S, int HD);
+void attn_small(int dtype, bool bwd, const void* qkv, const void* dout, void* out, int B, int S, int H, int HD, bool causal, cudaStream_t st);
+void ln_fwd(int dtype, const void* x, const void* r, const void* gamma, const void* beta, void* z, void* y, float* stats, int64_t rows, int D,
+            float eps, cudaStream_t st);
+int ln_bwd_parts(int64_t rows);
+void ln_bwd(int dtype, const void* z, const void* dy, const void* gamma, const float* stats, void* dz, float* part, void* dgamma, void* dbeta,
+            int64_t rows, int D, cudaStream_t st);
+}
+
+namespace sgb {
+namespace {
+using at::Tensor;
+
+Tensor attn_small_fwd(const Tensor& qkv, int64_t H, bool causal) {
+    TORCH_CHECK(qkv.is_cuda() && qkv.is_contiguous() && qkv.dim() == 3, "qkv must be a contiguous CUDA tensor [B, S, 3*D]");
+    const int B = (int)qkv.size(0), S = (int)qkv.size(1);
+    const int64_t D = qkv.size(2) / 3;
+    const int HD = (int)(D / H);
+    TORCH_CHECK(sg::attn_small_supported(S, HD), "attn_small supports S in {4,8} and head_dim in {32,64}");
+    TORCH_CHECK(qkv.scalar_type() == at::kBFloat16 || qkv.scalar_type() == at::kFloat, "attn_small: bf16 or fp32");
+    c10::cuda::CUDAGuard guard(qkv.device());
+    Tensor out = at::empty({B, S, D}, qkv.options());
+    sg::attn_small(dtype_code(qkv), false, qkv.data_ptr(), nullptr, out.data_ptr(), B, S, (int)H, HD, causal, at::cuda::getCurrentCUDAStream());
+    return out;
+}
+
+Tensor attn_small_bwd(const Tensor& qkv, const Tensor& dout, int64_t H, bool causal) {
+    const int B = (int)qkv.size(0), S = (int)qkv.size(1);
+    const int64_t D = qkv.size(2) / 3;
+    c10::cuda::CUDAGuard guard(qkv.device());
+    Tensor d = dout.contiguous();
+    Tensor dqkv = at::empty_like(qkv);
+    sg::attn_small(dtype_code(qkv), true, qkv.data_ptr(), d.data_ptr(), dqkv.data_ptr(), B, S, (int)H, (int)(D / H), causal, at::cuda::getCurrentCUDAStream());
+    return dqkv;
+}
+
+// returns (y, z, stats); z is x + r (the LayerNorm input, kept for backward); with no residual z aliases x
+std::vector<Tensor> ln_fwd(const Tensor& x, const c10::optional<Tensor>& r, const Tensor& gamma, const c10::optional<Tensor>& beta, double eps) {
+    TORCH_CHECK(x.is_cuda() && x.is_contiguous(), "x must be contiguous CUDA");
+    const int D = (int)x.size(-1);
+    TORCH_CHECK(D % 4 == 0, "LayerNorm width must be a multiple of 4");
+    const int64_t rows = x.numel() / D;
+    c10::cuda::CUDAGuard guard(x.device());
+    Tensor y = at::empty_like(x);
+    Tensor z = r.has_value() ? at::empty_like(x) : x;
+    Tensor stats = at::empty({rows, 2}, x.options().dtype(at::kFloat));
+    sg::ln_fwd(dtype_code(x), x.data_ptr(), r.has_value() ? r->contiguous().data_ptr() : nullptr, gamma.data_ptr(),
+               beta.has_value() ? beta->data_ptr() : nullptr, z.data_ptr(), y.data_ptr(), stats.data_ptr<float>(), rows, D, (float)eps,
+               at::cuda::getCurrentCUDAStream());
+    return {y, z, stats};
+}
+
+// returns (dz, dgamma, dbeta)
+std::vector<Tensor> ln_bwd(const Tensor& z, const Tensor& dy, const Tensor& gamma, const Tensor& stats, bool has_beta) {
+    const int D = (int)z.size(-1);
+    const int64_t rows = z.numel() / D;
+    TORCH_CHECK((size_t)8 * 2 * D * sizeof(float) <= 200 * 1024, "LayerNorm width too large for the fused backward");
+    c10::cuda::CUDAGuard guard(z.device());
+    Tensor d = dy.contiguous();
+    Tensor dz = at::empty_like(z);
+    Tensor part = at::empty({(int64_t)sg::ln_bwd_parts(rows), 2, D}, z.options().dtype(at::kFloat));
+    Tensor dgamma = at::empty_like(gamma);
+    Tensor dbeta = has_beta ? at::empty_like(gamma) : Tensor();
+    sg::ln_bwd(dtype_code(z), z.data_ptr(), d.data_ptr(), gamma.data_ptr(), stats.data_ptr<float>(), dz.data_ptr(), part.data_ptr<float>(),
+               dgamma.data_ptr(), has_beta ? dbeta.data_ptr() : nullptr, rows, D, at::cuda::getCurrentCUDAStream());
+    return {dz, dgamma, dbeta};
+}
+}  // namespace
+
+void register_nn(pybind11::module_& m) {
+    m.def("attn_small_fwd", &attn_small_fwd);
+    m.def("attn_small_bwd", &attn_small_bwd);
+    m.def("attn_small_supported", [](int64_t S, int64_t HD) { return sg::attn_small_supported((int)S, (int)HD); });
+    m.def("ln_fwd", &ln_fwd);
+    m.def("ln_bwd", &ln_bwd);
+}
+}  // namespace sgb

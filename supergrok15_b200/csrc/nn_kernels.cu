@@ -1,0 +1,304 @@
+// Model-side kernels for the small-sequence transformers of the grokking tasks (sm_100a):
+//   * causal multi-head attention for very short sequences (S <= 8) - one warp per (batch, head), the whole
+//     S x S score matrix lives in registers; forward and backward (scores recomputed, nothing saved but q,k,v);
+//   * LayerNorm with fused residual add, forward and backward (deterministic two-stage column reduction for
+//     the weight / bias gradients, no atomics).
+// They replace nn.MultiheadAttention / nn.LayerNorm of the reference model (grokking_race_v2.py:310-331); library
+// flash-attention kernels are tuned for long sequences and take ~2.5 ms per layer on a [8192, 8, 4, 64] problem
+// whose memory traffic is worth ~20 us.
+#include "sg_native.h"
+#include "optim_math.cuh"
+
+namespace sg {
+namespace {
+
+template <typename T, int EPL> struct LaneVec;       // EPL consecutive head-dim elements owned by one lane
+template <> struct LaneVec<__nv_bfloat16, 2> {
+    static __device__ __forceinline__ void ld(const __nv_bfloat16* p, float (&v)[2]) {
+        const __nv_bfloat162 t = *reinterpret_cast<const __nv_bfloat162*>(p);
+        v[0] = __bfloat162float(t.x); v[1] = __bfloat162float(t.y);
+    }
+    static __device__ __forceinline__ void st(__nv_bfloat16* p, const float (&v)[2]) {
+        *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(v[0], v[1]);
+    }
+};
+template <> struct LaneVec<__nv_bfloat16, 1> {
+    static __device__ __forceinline__ void ld(const __nv_bfloat16* p, float (&v)[1]) { v[0] = __bfloat162float(*p); }
+    static __device__ __forceinline__ void st(__nv_bfloat16* p, const float (&v)[1]) { *p = __float2bfloat16_rn(v[0]); }
+};
+template <> struct LaneVec<float, 2> {
+    static __device__ __forceinline__ void ld(const float* p, float (&v)[2]) { const float2 t = *reinterpret_cast<const float2*>(p); v[0] = t.x; v[1] = t.y; }
+    static __device__ __forceinline__ void st(float* p, const float (&v)[2]) { *reinterpret_cast<float2*>(p) = make_float2(v[0], v[1]); }
+};
+template <> struct LaneVec<float, 1> {
+    static __device__ __forceinline__ void ld(const float* p, float (&v)[1]) { v[0] = *p; }
+    static __device__ __forceinline__ void st(float* p, const float (&v)[1]) { *p = v[0]; }
+};
+
+// qkv [B, S, 3, H, HD] (HD = 32*EPL), out [B, S, H, HD]; one warp per (b, h); causal; scale = 1/sqrt(HD)
+template <typename T, int S, int EPL, bool CAUSAL>
+__global__ void __launch_bounds__(256) attn_small_fwd_kernel(const T* __restrict__ qkv, T* __restrict__ out, int B, int H, float scale) {
+    const int lane = threadIdx.x & 31;
+    const int64_t w = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (w >= (int64_t)B * H) return;
+    const int b = (int)(w / H), h = (int)(w % H);
+    constexpr int HD = 32 * EPL;
+    const int64_t D = (int64_t)H * HD;
+    float q[S][EPL], k[S][EPL], v[S][EPL];
+#pragma unroll
+    for (int s = 0; s < S; ++s) {
+        const T* base = qkv + ((int64_t)(b * S + s) * 3) * D + (int64_t)h * HD + lane * EPL;
+        LaneVec<T, EPL>::ld(base, q[s]); LaneVec<T, EPL>::ld(base + D, k[s]); LaneVec<T, EPL>::ld(base + 2 * D, v[s]);
+    }
+    float sc[S][S];
+#pragma unroll
+    for (int i = 0; i < S; ++i)
+#pragma unroll
+        for (int j = 0; j < S; ++j) {
+            if (CAUSAL && j > i) { sc[i][j] = 0.f; continue; }
+            float d = 0.f;
+#pragma unroll
+            for (int e = 0; e < EPL; ++e) d = fmaf(q[i][e], k[j][e], d);
+            sc[i][j] = warp_sum(d) * scale;
+        }
+#pragma unroll
+    for (int i = 0; i < S; ++i) {
+        const int jm = CAUSAL ? i : S - 1;
+        float mx = sc[i][0];
+#pragma unroll
+        for (int j = 1; j < S; ++j) if (j <= jm) mx = fmaxf(mx, sc[i][j]);
+        float den = 0.f;
+#pragma unroll
+        for (int j = 0; j < S; ++j) if (j <= jm) { sc[i][j] = __expf(sc[i][j] - mx); den += sc[i][j]; }
+        const float inv = 1.f / den;
+        float o[EPL];
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) o[e] = 0.f;
+#pragma unroll
+        for (int j = 0; j < S; ++j) if (j <= jm) {
+#pragma unroll
+            for (int e = 0; e < EPL; ++e) o[e] = fmaf(sc[i][j] * inv, v[j][e], o[e]);
+        }
+        LaneVec<T, EPL>::st(out + (int64_t)(b * S + i) * D + (int64_t)h * HD + lane * EPL, o);
+    }
+}
+
+template <typename T, int S, int EPL, bool CAUSAL>
+__global__ void __launch_bounds__(256) attn_small_bwd_kernel(const T* __restrict__ qkv, const T* __restrict__ dout, T* __restrict__ dqkv,
+                                                             int B, int H, float scale) {
+    const int lane = threadIdx.x & 31;
+    const int64_t w = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (w >= (int64_t)B * H) return;
+    const int b = (int)(w / H), h = (int)(w % H);
+    constexpr int HD = 32 * EPL;
+    const int64_t D = (int64_t)H * HD;
+    float q[S][EPL], k[S][EPL], v[S][EPL], dO[S][EPL];
+#pragma unroll
+    for (int s = 0; s < S; ++s) {
+        const T* base = qkv + ((int64_t)(b * S + s) * 3) * D + (int64_t)h * HD + lane * EPL;
+        LaneVec<T, EPL>::ld(base, q[s]); LaneVec<T, EPL>::ld(base + D, k[s]); LaneVec<T, EPL>::ld(base + 2 * D, v[s]);
+        LaneVec<T, EPL>::ld(dout + (int64_t)(b * S + s) * D + (int64_t)h * HD + lane * EPL, dO[s]);
+    }
+    float p[S][S], dp[S][S];
+#pragma unroll
+    for (int i = 0; i < S; ++i)
+#pragma unroll
+        for (int j = 0; j < S; ++j) {
+            if (CAUSAL && j > i) { p[i][j] = 0.f; dp[i][j] = 0.f; continue; }
+            float d = 0.f, e2 = 0.f;
+#pragma unroll
+            for (int e = 0; e < EPL; ++e) { d = fmaf(q[i][e], k[j][e], d); e2 = fmaf(dO[i][e], v[j][e], e2); }
+            p[i][j] = warp_sum(d) * scale;
+            dp[i][j] = warp_sum(e2);
+        }
+    float dq[S][EPL], dk[S][EPL], dv[S][EPL];
+#pragma unroll
+    for (int s = 0; s < S; ++s)
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) { dq[s][e] = 0.f; dk[s][e] = 0.f; dv[s][e] = 0.f; }
+#pragma unroll
+    for (int i = 0; i < S; ++i) {
+        const int jm = CAUSAL ? i : S - 1;
+        float mx = p[i][0];
+#pragma unroll
+        for (int j = 1; j < S; ++j) if (j <= jm) mx = fmaxf(mx, p[i][j]);
+        float den = 0.f;
+#pragma unroll
+        for (int j = 0; j < S; ++j) if (j <= jm) { p[i][j] = __expf(p[i][j] - mx); den += p[i][j]; }
+        const float inv = 1.f / den;
+        float dot = 0.f;
+#pragma unroll
+        for (int j = 0; j < S; ++j) if (j <= jm) { p[i][j] *= inv; dot = fmaf(p[i][j], dp[i][j], dot); }
+#pragma unroll
+        for (int j = 0; j < S; ++j) if (j <= jm) {
+            const float ds = p[i][j] * (dp[i][j] - dot) * scale;
+#pragma unroll
+            for (int e = 0; e < EPL; ++e) {
+                dv[j][e] = fmaf(p[i][j], dO[i][e], dv[j][e]);
+                dq[i][e] = fmaf(ds, k[j][e], dq[i][e]);
+                dk[j][e] = fmaf(ds, q[i][e], dk[j][e]);
+            }
+        }
+    }
+#pragma unroll
+    for (int s = 0; s < S; ++s) {
+        T* base = dqkv + ((int64_t)(b * S + s) * 3) * D + (int64_t)h * HD + lane * EPL;
+        LaneVec<T, EPL>::st(base, dq[s]); LaneVec<T, EPL>::st(base + D, dk[s]); LaneVec<T, EPL>::st(base + 2 * D, dv[s]);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------- LayerNorm
+// z = x (+ r); y = (z - mean) * rstd * gamma (+ beta).  One warp per row; rows of D <= 8192 elements.
+template <typename T>
+__global__ void __launch_bounds__(256) ln_fwd_kernel(const T* __restrict__ x, const T* __restrict__ r, const T* __restrict__ gamma,
+                                                     const T* __restrict__ beta, T* __restrict__ z, T* __restrict__ y,
+                                                     float* __restrict__ stats, int64_t rows, int D, float eps) {
+    const int lane = threadIdx.x & 31;
+    const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const T* xr = x + row * D;
+    const T* rr = r ? r + row * D : nullptr;
+    float s = 0.f, ss = 0.f;
+    for (int c = lane * 4; c < D; c += 128) {
+        float a[4], bres[4];
+        ld4<T>(xr, c, (D - c >= 4) ? 4 : D - c, true, a);
+        if (rr) { ld4<T>(rr, c, (D - c >= 4) ? 4 : D - c, true, bres);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) a[k] = Cvt<T>::to(Cvt<T>::from(a[k] + bres[k])); }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) { s += a[k]; ss = fmaf(a[k], a[k], ss); }
+    }
+    s = warp_sum(s); ss = warp_sum(ss);
+    const float mean = s / D;
+    const float var = fmaxf(ss / D - mean * mean, 0.f);
+    const float rstd = rsqrtf(var + eps);
+    if (lane == 0) { stats[2 * row] = mean; stats[2 * row + 1] = rstd; }
+    for (int c = lane * 4; c < D; c += 128) {
+        const int cnt = (D - c >= 4) ? 4 : D - c;
+        float a[4], bres[4], g[4], bb[4], o[4];
+        ld4<T>(xr, c, cnt, true, a);
+        if (rr) { ld4<T>(rr, c, cnt, true, bres);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) a[k] = Cvt<T>::to(Cvt<T>::from(a[k] + bres[k]));
+            st4<T>(z + row * D, c, cnt, true, a); }
+        ld4<T>(gamma, c, cnt, true, g);
+        if (beta) ld4<T>(beta, c, cnt, true, bb);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) o[k] = (a[k] - mean) * rstd * g[k] + (beta ? bb[k] : 0.f);
+        st4<T>(y + row * D, c, cnt, true, o);
+    }
+}
+
+// dz = rstd * (dy*g - mean_c(dy*g) - xhat * mean_c(dy*g*xhat)); per-CTA partial sums of dgamma / dbeta over its rows.
+constexpr int LN_ROWS_PER_CTA = 64;
+template <typename T>
+__global__ void __launch_bounds__(256) ln_bwd_kernel(const T* __restrict__ z, const T* __restrict__ dy, const T* __restrict__ gamma,
+                                                     const float* __restrict__ stats, T* __restrict__ dz, float* __restrict__ part,
+                                                     int64_t rows, int D) {
+    extern __shared__ float sm[];                       // [8 warps][2][D]  per-warp column partials
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    float* pg = sm + (size_t)w * 2 * D;
+    float* pb = pg + D;
+    for (int c = lane; c < D; c += 32) { pg[c] = 0.f; pb[c] = 0.f; }
+    const int64_t row0 = (int64_t)blockIdx.x * LN_ROWS_PER_CTA;
+    for (int rr = w; rr < LN_ROWS_PER_CTA; rr += 8) {
+        const int64_t row = row0 + rr;
+        if (row >= rows) break;
+        const float mean = stats[2 * row], rstd = stats[2 * row + 1];
+        float s1 = 0.f, s2 = 0.f;
+        for (int c = lane * 4; c < D; c += 128) {
+            const int cnt = (D - c >= 4) ? 4 : D - c;
+            float a[4], d[4], g[4];
+            ld4<T>(z + row * D, c, cnt, true, a); ld4<T>(dy + row * D, c, cnt, true, d); ld4<T>(gamma, c, cnt, true, g);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) if (k < cnt) {
+                const float xh = (a[k] - mean) * rstd, dg = d[k] * g[k];
+                s1 += dg; s2 = fmaf(dg, xh, s2);
+                pg[c + k] = fmaf(d[k], xh, pg[c + k]); pb[c + k] += d[k];
+            }
+        }
+        s1 = warp_sum(s1) / D; s2 = warp_sum(s2) / D;
+        for (int c = lane * 4; c < D; c += 128) {
+            const int cnt = (D - c >= 4) ? 4 : D - c;
+            float a[4], d[4], g[4], o[4];
+            ld4<T>(z + row * D, c, cnt, true, a); ld4<T>(dy + row * D, c, cnt, true, d); ld4<T>(gamma, c, cnt, true, g);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) { const float xh = (a[k] - mean) * rstd; o[k] = rstd * (d[k] * g[k] - s1 - xh * s2); }
+            st4<T>(dz + row * D, c, cnt, true, o);
+        }
+    }
+    __syncthreads();
+    for (int c = threadIdx.x; c < D; c += 256) {
+        float a = 0.f, b = 0.f;
+#pragma unroll
+        for (int ww = 0; ww < 8; ++ww) { a += sm[(size_t)ww * 2 * D + c]; b += sm[(size_t)ww * 2 * D + D + c]; }
+        part[((int64_t)blockIdx.x * 2) * D + c] = a;
+        part[((int64_t)blockIdx.x * 2 + 1) * D + c] = b;
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) ln_bwd_reduce_kernel(const float* __restrict__ part, int n_part, int D, T* __restrict__ dgamma,
+                                                            T* __restrict__ dbeta) {
+    const int c = blockIdx.x * 256 + threadIdx.x;
+    if (c >= D) return;
+    float a = 0.f, b = 0.f;
+    for (int p = 0; p < n_part; ++p) { a += part[((int64_t)p * 2) * D + c]; b += part[((int64_t)p * 2 + 1) * D + c]; }
+    dgamma[c] = Cvt<T>::from(a);
+    if (dbeta) dbeta[c] = Cvt<T>::from(b);
+}
+
+}  // namespace
+
+bool attn_small_supported(int S, int HD) { return (S == 4 || S == 8) && (HD == 32 || HD == 64); }
+
+template <typename T>
+static void attn_dispatch(bool bwd, const T* qkv, const T* dout, T* out, int B, int S, int H, int HD, bool causal, cudaStream_t st) {
+    const float scale = 1.f / sqrtf((float)HD);
+    const unsigned blocks = (unsigned)(((int64_t)B * H + 7) / 8);
+    count_launch();
+#define GO(SV, EV, CV) \
+    if (bwd) attn_small_bwd_kernel<T, SV, EV, CV><<<blocks, 256, 0, st>>>(qkv, dout, out, B, H, scale); \
+    else attn_small_fwd_kernel<T, SV, EV, CV><<<blocks, 256, 0, st>>>(qkv, out, B, H, scale);
+#define GO2(SV, EV) if (causal) { GO(SV, EV, true) } else { GO(SV, EV, false) }
+    if (S == 4 && HD == 64) { GO2(4, 2) } else if (S == 4 && HD == 32) { GO2(4, 1) }
+    else if (S == 8 && HD == 64) { GO2(8, 2) } else { GO2(8, 1) }
+#undef GO2
+#undef GO
+}
+
+void attn_small(int dtype, bool bwd, const void* qkv, const void* dout, void* out, int B, int S, int H, int HD, bool causal, cudaStream_t st) {
+    if (dtype == BF16) attn_dispatch<__nv_bfloat16>(bwd, (const __nv_bfloat16*)qkv, (const __nv_bfloat16*)dout, (__nv_bfloat16*)out, B, S, H, HD, causal, st);
+    else attn_dispatch<float>(bwd, (const float*)qkv, (const float*)dout, (float*)out, B, S, H, HD, causal, st);
+}
+
+void ln_fwd(int dtype, const void* x, const void* r, const void* gamma, const void* beta, void* z, void* y, float* stats, int64_t rows, int D,
+            float eps, cudaStream_t st) {
+    const unsigned blocks = (unsigned)((rows + 7) / 8);
+    count_launch();
+    if (dtype == BF16) ln_fwd_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)r, (const __nv_bfloat16*)gamma,
+                                                                           (const __nv_bfloat16*)beta, (__nv_bfloat16*)z, (__nv_bfloat16*)y, stats, rows, D, eps);
+    else ln_fwd_kernel<float><<<blocks, 256, 0, st>>>((const float*)x, (const float*)r, (const float*)gamma, (const float*)beta, (float*)z, (float*)y,
+                                                      stats, rows, D, eps);
+}
+
+int ln_bwd_parts(int64_t rows) { return (int)((rows + LN_ROWS_PER_CTA - 1) / LN_ROWS_PER_CTA); }
+
+void ln_bwd(int dtype, const void* z, const void* dy, const void* gamma, const float* stats, void* dz, float* part, void* dgamma, void* dbeta,
+            int64_t rows, int D, cudaStream_t st) {
+    const int parts = ln_bwd_parts(rows);
+    const size_t smem = (size_t)8 * 2 * D * sizeof(float);
+    count_launch(2);
+    if (dtype == BF16) {
+        cudaFuncSetAttribute(ln_bwd_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        ln_bwd_kernel<__nv_bfloat16><<<parts, 256, smem, st>>>((const __nv_bfloat16*)z, (const __nv_bfloat16*)dy, (const __nv_bfloat16*)gamma, stats,
+                                                                (__nv_bfloat16*)dz, part, rows, D);
+        ln_bwd_reduce_kernel<__nv_bfloat16><<<(D + 255) / 256, 256, 0, st>>>(part, parts, D, (__nv_bfloat16*)dgamma, (__nv_bfloat16*)dbeta);
+    } else {
+        cudaFuncSetAttribute(ln_bwd_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        ln_bwd_kernel<float><<<parts, 256, smem, st>>>((const float*)z, (const float*)dy, (const float*)gamma, stats, (float*)dz, part, rows, D);
+        ln_bwd_reduce_kernel<float><<<(D + 255) / 256, 256, 0, st>>>(part, parts, D, (float*)dgamma, (float*)dbeta);
+    }
+}
+
+}  // namespace sg

@@ -19,6 +19,8 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
+from ..ops import nn_ops
+
 
 class _Attn(nn.Module):
     """Causal multi-head self-attention with MultiheadAttention's parameter layout."""
@@ -27,6 +29,7 @@ class _Attn(nn.Module):
         super().__init__()
         assert d % h == 0
         self.d, self.h = d, h
+        self.fused = True            # use the short-sequence attention kernel when the input qualifies (CUDA, S in {4,8})
         self.in_proj_weight = nn.Parameter(torch.empty(3 * d, d))
         self.in_proj_bias = nn.Parameter(torch.zeros(3 * d)) if bias else None
         self.out_proj = nn.Linear(d, d, bias=bias)
@@ -36,7 +39,10 @@ class _Attn(nn.Module):
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         B, S, D = x.shape
-        qkv = F.linear(x, self.in_proj_weight, self.in_proj_bias).view(B, S, 3, self.h, D // self.h)
+        qkv = F.linear(x, self.in_proj_weight, self.in_proj_bias)
+        if self.fused and nn_ops.attention_small_supported(qkv, self.h):
+            return self.out_proj(nn_ops.attention_small(qkv, self.h, True))
+        qkv = qkv.view(B, S, 3, self.h, D // self.h)
         q, k, v = (qkv[:, :, i].transpose(1, 2) for i in range(3))
         o = F.scaled_dot_product_attention(q, k, v, is_causal=True)
         return self.out_proj(o.transpose(1, 2).reshape(B, S, D))
@@ -50,6 +56,9 @@ class DecoderBlock(nn.Module):
         self.ff = nn.Sequential(nn.Linear(d, 4 * d), nn.GELU(), nn.Linear(4 * d, d))
 
     def forward(self, x):
+        if x.is_cuda:                    # LayerNorm(x + sublayer) with the add fused into the normalisation kernel
+            x = nn_ops.layer_norm(x, self.attn(x), self.n1.weight, self.n1.bias, self.n1.eps)
+            return nn_ops.layer_norm(x, self.ff(x), self.n2.weight, self.n2.bias, self.n2.eps)
         x = self.n1(x + self.attn(x))
         return self.n2(x + self.ff(x))
 

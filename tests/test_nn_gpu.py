@@ -1,0 +1,55 @@
+"""GPU tests of the model-side kernels against plain PyTorch fp32."""
+import pytest
+import torch
+import torch.nn.functional as F
+
+from supergrok15_b200.ops import nn_ops
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("S,H,hd", [(4, 8, 64), (4, 4, 32), (8, 2, 64), (8, 4, 32)])
+def test_attention_small_forward_backward(S, H, hd, dtype):
+    torch.manual_seed(0)
+    B, D = 37, H * hd
+    qkv = torch.randn(B, S, 3 * D, device="cuda", dtype=dtype, requires_grad=True)
+    ref_in = qkv.detach().float().requires_grad_(True)
+    out = nn_ops.attention_small(qkv, H)
+    ref = nn_ops.attention_small_reference(ref_in, H)
+    w = torch.randn_like(ref)
+    (out.float() * w).sum().backward()
+    (ref * w).sum().backward()
+    tol = dict(rtol=1e-4, atol=1e-5) if dtype == torch.float32 else dict(rtol=3e-2, atol=3e-2)
+    assert torch.allclose(out.float(), ref, **tol)
+    assert torch.allclose(qkv.grad.float(), ref_in.grad, **tol)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("rows,D,res,bias", [(1, 128, True, True), (70, 512, True, True), (257, 256, False, True), (64, 512, True, False)])
+def test_layer_norm_residual_forward_backward(rows, D, res, bias, dtype):
+    torch.manual_seed(1)
+    x = torch.randn(rows, D, device="cuda", dtype=dtype, requires_grad=True)
+    r = torch.randn(rows, D, device="cuda", dtype=dtype, requires_grad=True) if res else None
+    w = torch.randn(D, device="cuda", dtype=dtype, requires_grad=True)
+    b = torch.randn(D, device="cuda", dtype=dtype, requires_grad=True) if bias else None
+    y = nn_ops.layer_norm(x, r, w, b)
+    xf, wf = x.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True)
+    rf = r.detach().float().requires_grad_(True) if res else None
+    bf = b.detach().float().requires_grad_(True) if bias else None
+    z = xf + rf if res else xf
+    if dtype == torch.bfloat16 and res:
+        z = z + (z.detach().to(dtype).float() - z.detach())          # the kernel rounds the sum to bf16, as x + r in bf16 does
+    yr = F.layer_norm(z, (D,), wf, bf)
+    g = torch.randn_like(yr)
+    (y.float() * g).sum().backward()
+    (yr * g).sum().backward()
+    tol = dict(rtol=1e-4, atol=1e-4) if dtype == torch.float32 else dict(rtol=4e-2, atol=4e-2)
+    assert torch.allclose(y.float(), yr, **tol)
+    assert torch.allclose(x.grad.float(), xf.grad, **tol)
+    if res:
+        assert torch.allclose(r.grad.float(), rf.grad, **tol)
+    wt = dict(rtol=1e-3, atol=1e-3) if dtype == torch.float32 else dict(rtol=5e-2, atol=0.3)
+    assert torch.allclose(w.grad.float(), wf.grad, **wt)
+    if bias:
+        assert torch.allclose(b.grad.float(), bf.grad, **wt)

@@ -1,2 +1,49 @@
+// Bindings of the tcgen05 GEMM.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
 #include "bindings_decl.h"
-namespace sgb { void register_gemm(pybind11::module_& m) {} }
+#include "mt_host.h"
+
+namespace sg {
+int gemm_bf16_tn(const void* A, int lda, const void* B, int ldb, int M, int N, int K, float alpha, float beta, const void* D, int ldd,
+                 bool d_bf16, const void* bias, bool bias_bf16, float diag, int act, void* C, int ldc, bool c_bf16, void* C2, int ldc2,
+                 int* err, cudaStream_t s);
+}
+
+namespace sgb {
+namespace {
+using at::Tensor;
+
+// out = act(alpha * a @ b.T + beta * d + bias + diag * I);  a [M,K], b [N,K] bf16 row-major (last stride 1, row stride multiple of 8).
+// out: bf16 or fp32 [M,N]; out_t (optional): [N,M] receives the transposed result.
+void gemm_tn(const Tensor& a, const Tensor& b, Tensor out, double alpha, double beta, const c10::optional<Tensor>& d,
+             const c10::optional<Tensor>& bias, double diag, int64_t act, const c10::optional<Tensor>& out_t, Tensor err) {
+    TORCH_CHECK(a.is_cuda() && b.is_cuda() && out.is_cuda(), "gemm_tn needs CUDA tensors");
+    TORCH_CHECK(a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16, "gemm_tn operands must be bf16");
+    TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && a.size(1) == b.size(1), "shape mismatch: a [M,K], b [N,K]");
+    TORCH_CHECK(a.stride(1) == 1 && b.stride(1) == 1 && out.stride(1) == 1, "innermost stride must be 1");
+    TORCH_CHECK(a.stride(0) % 8 == 0 && b.stride(0) % 8 == 0, "row strides must be multiples of 8 elements (16 bytes)");
+    TORCH_CHECK((reinterpret_cast<uintptr_t>(a.data_ptr()) & 15) == 0 && (reinterpret_cast<uintptr_t>(b.data_ptr()) & 15) == 0, "operands must be 16-byte aligned");
+    const int M = (int)a.size(0), N = (int)b.size(0), K = (int)a.size(1);
+    TORCH_CHECK(out.size(0) == M && out.size(1) == N, "out must be [M,N]");
+    const bool c_bf16 = out.scalar_type() == at::kBFloat16;
+    TORCH_CHECK(c_bf16 || out.scalar_type() == at::kFloat, "out must be bf16 or fp32");
+    if (d.has_value()) TORCH_CHECK(d->size(0) == M && d->size(1) == N && d->stride(1) == 1, "d must be [M,N]");
+    if (out_t.has_value()) TORCH_CHECK(out_t->size(0) == N && out_t->size(1) == M && out_t->stride(1) == 1 && out_t->scalar_type() == out.scalar_type(), "out_t must be [N,M] of out's dtype");
+    c10::cuda::CUDAGuard guard(a.device());
+    const int rc = sg::gemm_bf16_tn(a.data_ptr(), (int)a.stride(0), b.data_ptr(), (int)b.stride(0), M, N, K, (float)alpha, (float)beta,
+                                    d.has_value() ? d->data_ptr() : nullptr, d.has_value() ? (int)d->stride(0) : 0,
+                                    d.has_value() && d->scalar_type() == at::kBFloat16, bias.has_value() ? bias->data_ptr() : nullptr,
+                                    bias.has_value() && bias->scalar_type() == at::kBFloat16, (float)diag, (int)act, out.data_ptr(), (int)out.stride(0),
+                                    c_bf16, out_t.has_value() ? out_t->data_ptr() : nullptr, out_t.has_value() ? (int)out_t->stride(0) : 0,
+                                    err.data_ptr<int>(), at::cuda::getCurrentCUDAStream());
+    TORCH_CHECK(rc == 0, "gemm_tn launch failed (code ", rc, ")");
+}
+}  // namespace
+
+void register_gemm(pybind11::module_& m) {
+    m.def("gemm_tn", &gemm_tn, py::arg("a"), py::arg("b"), py::arg("out"), py::arg("alpha") = 1.0, py::arg("beta") = 0.0,
+          py::arg("d") = c10::nullopt, py::arg("bias") = c10::nullopt, py::arg("diag") = 0.0, py::arg("act") = 0,
+          py::arg("out_t") = c10::nullopt, py::arg("err"));
+}
+}  // namespace sgb

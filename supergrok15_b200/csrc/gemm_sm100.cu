@@ -1,0 +1,265 @@
+// bf16 x bf16 -> fp32 GEMM on the 5th-generation tensor cores (tcgen05 / TMEM / TMA), sm_100a only.
+//
+//   C[M,N] = epilogue( A[M,K] . B[N,K]^T )        A and B row-major with K contiguous ("TN": x . W^T of nn.Linear)
+//
+// One CTA computes a 128 x BN output tile.  Warp-specialised:
+//   warp 0   producer   one lane issues TMA 2-D tile loads (128-byte swizzle, no multicast) into a STAGES-deep ring
+//   warp 1   MMA        allocates TMEM, one lane issues tcgen05.mma (M=128, N=BN, K=16) four times per 64-wide K block,
+//                       tcgen05.commit releases the ring slot / signals the epilogue
+//   warps 2-5 epilogue  tcgen05.ld 32 lanes x 32 columns at a time -> alpha*acc + beta*D + bias + diag, activation -> global
+// Synchronisation is by mbarriers (full / empty per stage, one accumulator-ready barrier).  Every wait is bounded: when a
+// wait runs out the waiter raises an error word in global memory, the CTA drains, frees its TMEM and returns.
+//
+// This kernel family replaces cuBLAS (torch::mm) on the named paths of the reference: the Newton-Schulz chain of Muon
+// (csrc/ops.cpp:713-727) and the model's Linear layers.
+#include "sg_native.h"
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <cstdint>
+
+namespace sg {
+namespace {
+
+constexpr int BM = 128, BK = 64;                 // BK bf16 = 128 bytes = one swizzle row
+constexpr int GEMM_THREADS = 192;
+constexpr uint32_t SPIN_LIMIT = 4u * 1000u * 1000u;   // bounded mbarrier waits (try_wait suspends briefly between polls)
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// returns false if the phase did not complete within the spin limit
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    const uint32_t addr = smem_u32(bar);
+    for (uint32_t it = 0; it < SPIN_LIMIT; ++it) {
+        uint32_t done;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_mma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+                   "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+                   "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+                   "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// K-major operand tile in shared memory, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t make_desc_sw128(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3ffff) >> 4);            // start address, bits [0,14)
+    d |= (uint64_t)1 << 16;                                   // leading byte offset (unused for swizzled K-major), bits [16,30)
+    d |= (uint64_t)(1024 >> 4) << 32;                         // stride byte offset = 1024 bytes, bits [32,46)
+    d |= (uint64_t)1 << 46;                                   // descriptor version (Blackwell)
+    d |= (uint64_t)2 << 61;                                   // layout type: SWIZZLE_128B
+    return d;
+}
+
+struct Epilogue {
+    float alpha, beta, diag;       // C = act(alpha*acc + beta*D[m,n] + bias[n] + (m==n ? diag : 0))
+    const void* D; int ldd; int d_is_bf16;
+    const void* bias; int bias_is_bf16;
+    int act;                       // 0 none, 1 gelu (erf), 2 silu
+    void* C; int ldc; int c_is_bf16;
+    void* C2; int ldc2;            // optional second output: C2[n, m] = C[m, n] (transposed copy, same dtype)
+};
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a,
+                                                                  const __grid_constant__ CUtensorMap map_b, int M, int N, int K,
+                                                                  Epilogue ep, int* __restrict__ err) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+    uint64_t* empty = full + STAGES;
+    uint64_t* acc_ready = empty + STAGES;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_ready + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    const int KB = (K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        mbar_init(acc_ready, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)BN) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int kb = 0; kb < KB; ++kb) {
+                const int s = kb % STAGES;
+                if (kb >= STAGES && !mbar_wait(&empty[s], ((kb / STAGES) & 1) ^ 1)) { atomicExch(err, 1); break; }
+                uint8_t* a_dst = smem + s * STAGE_BYTES;
+                mbar_expect_tx(&full[s], STAGE_BYTES);
+                tma_load_2d(a_dst, &map_a, kb * BK, m0, &full[s]);
+                tma_load_2d(a_dst + A_BYTES, &map_b, kb * BK, n0, &full[s]);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // instruction descriptor: D fp32, A/B bf16, both K-major, N>>3 at bit 17, M>>4 at bit 24
+            constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+            bool ok = true;
+            for (int kb = 0; kb < KB && ok; ++kb) {
+                const int s = kb % STAGES;
+                if (!mbar_wait(&full[s], (kb / STAGES) & 1)) { atomicExch(err, 2); ok = false; break; }
+                tc_fence_after();
+                const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES);
+                const uint64_t da = make_desc_sw128(a_addr), db = make_desc_sw128(a_addr + A_BYTES);
+#pragma unroll
+                for (int k4 = 0; k4 < BK / 16; ++k4)              // 16 bf16 = 32 bytes per MMA: advance the start address by 2 (16-byte units)
+                    tc_mma_bf16(tmem_base, da + 2 * k4, db + 2 * k4, idesc, (kb > 0 || k4 > 0) ? 1u : 0u);
+                tc_commit(&empty[s]);                             // slot reusable once these MMAs have read it
+            }
+            tc_commit(acc_ready);                                 // accumulator complete (also arrives if the loop bailed out)
+        }
+    } else {
+        const int q = warp & 3;                                   // TMEM lane quarter this warp may access
+        const bool ok = mbar_wait(acc_ready, 0);
+        if (!ok && lane == 0) atomicExch(err, 3);
+        tc_fence_after();
+        const int row = m0 + q * 32 + lane;
+        if (ok) {
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 32) {
+                uint32_t r[32];
+                tc_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c, r);
+                tc_wait_ld();
+                if (row < M) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const int col = n0 + c + j;
+                        if (col >= N) break;
+                        float v = ep.alpha * __uint_as_float(r[j]);
+                        if (ep.D) v += ep.beta * (ep.d_is_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(ep.D)[(int64_t)row * ep.ldd + col])
+                                                               : reinterpret_cast<const float*>(ep.D)[(int64_t)row * ep.ldd + col]);
+                        if (ep.bias) v += ep.bias_is_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(ep.bias)[col])
+                                                          : reinterpret_cast<const float*>(ep.bias)[col];
+                        if (row == col) v += ep.diag;
+                        if (ep.act == 1) v = 0.5f * v * (1.f + erff(v * 0.70710678f));
+                        else if (ep.act == 2) v = v / (1.f + __expf(-v));
+                        r[j] = __float_as_uint(v);
+                    }
+                    const int ncol = (N - (n0 + c) < 32) ? (N - (n0 + c)) : 32;
+                    if (ncol > 0) {
+                        if (ep.c_is_bf16) {
+                            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(ep.C) + (int64_t)row * ep.ldc + n0 + c;
+                            if (ncol == 32 && (((uintptr_t)dst) & 15) == 0) {
+#pragma unroll
+                                for (int j = 0; j < 32; j += 8) {
+                                    uint4 o;
+                                    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+                                    for (int t = 0; t < 4; ++t) h[t] = __floats2bfloat162_rn(__uint_as_float(r[j + 2 * t]), __uint_as_float(r[j + 2 * t + 1]));
+                                    *reinterpret_cast<uint4*>(dst + j) = o;
+                                }
+                            } else {
+                                for (int j = 0; j < ncol; ++j) dst[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
+                            }
+                            if (ep.C2) {
+                                __nv_bfloat16* d2 = reinterpret_cast<__nv_bfloat16*>(ep.C2);
+                                for (int j = 0; j < ncol; ++j) d2[(int64_t)(n0 + c + j) * ep.ldc2 + row] = __float2bfloat16_rn(__uint_as_float(r[j]));
+                            }
+                        } else {
+                            float* dst = reinterpret_cast<float*>(ep.C) + (int64_t)row * ep.ldc + n0 + c;
+                            if (ncol == 32 && (((uintptr_t)dst) & 15) == 0) {
+#pragma unroll
+                                for (int j = 0; j < 32; j += 4)
+                                    *reinterpret_cast<float4*>(dst + j) = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+                            } else {
+                                for (int j = 0; j < ncol; ++j) dst[j] = __uint_as_float(r[j]);
+                            }
+                            if (ep.C2) {
+                                float* d2 = reinterpret_cast<float*>(ep.C2);
+                                for (int j = 0; j < ncol; ++j) d2[(int64_t)(n0 + c + j) * ep.ldc2 + row] = __uint_as_float(r[j]);
+                            }
+                        }
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)BN) : "memory");
+    }
+}
+
+// ---- host side -------------------------------------------------------------------------------------------------
+bool make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int64_t ld_elems, int box_rows) {
+    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)ld_elems * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = cuTensorMapEncodeTiled(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
+template <int BN, int STAGES>
+int launch(const void* A, int lda, const void* B, int ldb, int M, int N, int K, const Epilogue& ep, int* err, cudaStream_t s) {
+    CUtensorMap ma, mb;
+    if (!make_map(&ma, A, M, K, lda, BM) || !make_map(&mb, B, N, K, ldb, BN)) return 1;
+    constexpr size_t smem = (size_t)STAGES * (BM * BK * 2 + BN * BK * 2) + 1024 + 256;
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(gemm_tn_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return 2;
+        configured = true;
+    }
+    dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
+    count_launch();
+    gemm_tn_kernel<BN, STAGES><<<grid, GEMM_THREADS, smem, s>>>(ma, mb, M, N, K, ep, err);
+    return cudaGetLastError() == cudaSuccess ? 0 : 3;
+}
+
+}  // namespace
+
+// C = act(alpha * A[M,K] . B[N,K]^T + beta * D + bias + diag*I); A, B bf16 with leading dimensions lda / ldb (elements, multiples of 8).
+// Returns 0 on success.  `err` (device int, zeroed by the caller) becomes non-zero if a pipeline wait timed out.
+int gemm_bf16_tn(const void* A, int lda, const void* B, int ldb, int M, int N, int K, float alpha, float beta, const void* D, int ldd,
+                 bool d_bf16, const void* bias, bool bias_bf16, float diag, int act, void* C, int ldc, bool c_bf16, void* C2, int ldc2,
+                 int* err, cudaStream_t s) {
+    if (M <= 0 || N <= 0 || K <= 0) return 0;
+    Epilogue ep{alpha, beta, diag, D, ldd, d_bf16 ? 1 : 0, bias, bias_bf16 ? 1 : 0, act, C, ldc, c_bf16 ? 1 : 0, C2, ldc2};
+    if (N > 128) return launch<256, 4>(A, lda, B, ldb, M, N, K, ep, err, s);
+    return launch<128, 6>(A, lda, B, ldb, M, N, K, ep, err, s);
+}
+
+}  // namespace sg

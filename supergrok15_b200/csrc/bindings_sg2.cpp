@@ -103,7 +103,7 @@ py::dict sg2_layout() {
     using P = sg::SG2Pack;
 #define L(X) d[#X] = (int)P::X;
     L(IN_W) L(IN_B) L(DIR0) L(DIR1) L(D_INPROJ) L(D_DTW) L(D_DTB) L(D_BW) L(D_CW) L(D_ALOG) L(D_D) L(D_ROPE) L(D_OUT) L(DIR_SIZE)
-    L(GRU_WZ) L(GRU_WR) L(GRU_WH) L(GRU_BZ) L(GRU_BR) L(GRU_BH) L(PQ) L(KA) L(KB) L(EW1) L(EB1) L(EW2) L(EB2) L(TOTAL)
+    L(GRU_WZ) L(GRU_WR) L(GRU_WH) L(GRU_BZ) L(GRU_BR) L(GRU_BH) L(PQ) L(KA) L(KB) L(EW1) L(EB1) L(EW2) L(EB2) L(TOTAL) L(NET) L(A_X) L(A_Z) L(A_DT) L(A_B) L(A_C) L(AFF_SIZE) L(AFF0) L(AFF1)
 #undef L
     d["item_bytes"] = (int)sg::sg2_item_bytes();
     d["td_bytes"] = (int)sg::sg2_td_bytes();

@@ -32,7 +32,7 @@ namespace {
 
 using P = SG2Pack;
 constexpr int TILE_T = 16;                 // timesteps per tile
-constexpr int ROW = 84;                    // floats per timestep row in shared memory (80 used; 84 keeps 128-bit stores conflict free)
+constexpr int ROW = 52;                    // floats per timestep row in shared memory: B[16] C[16] (g,s,-,-) out[16]; 13 float4 (odd) keeps 128-bit stores conflict free
 constexpr int SCAN_THREADS = 128;          // 8 items per CTA
 constexpr int ITEMS_PER_CTA = SCAN_THREADS / 16;
 
@@ -117,89 +117,64 @@ struct TensorDir {     // 32 bytes
     int32_t pad[4];
 };
 
-// Stage A: lane l = timestep (u0 + l).  Computes x,z,dt,B,C for its timestep and writes its shared-memory row.
+// The scan's per-timestep inputs x, z, dt (pre-activation), B, C are all AFFINE functions of the two scalars (g, s) of the
+// timestep: input_proj is 2 -> 8 and in_proj / dt_proj / B_proj / C_proj are linear maps applied on top of it.  The host folds
+// the chain into five [16][3] tables per direction (SG2Pack::AFF*: coefficient of g, coefficient of s, constant), computed in
+// fp64.  Per timestep the precompute is then 160 FMAs instead of 1040, and x / z / dt are evaluated by the column's own lane.
+//
+// Stage A: lane l = timestep (u0 + l): B[16], C[16] and (g, s) of that timestep go to its shared-memory row.
 template <int DIR>
 __device__ __forceinline__ void stage_a(float* __restrict__ tile, const float2* __restrict__ gs, int64_t off, int n, int u, bool valid,
                                         int l) {
-    constexpr int W = (DIR == 0) ? P::DIR0 : P::DIR1;
-    float4* row = reinterpret_cast<float4*>(tile + l * ROW);
+    constexpr int AF = (DIR == 0) ? P::AFF0 : P::AFF1;
     if (!valid) return;
+    float4* row = reinterpret_cast<float4*>(tile + l * ROW);
     const int pos = (DIR == 0) ? u : (n - 1 - u);
     const float2 v = gs[off + pos];
-    float inp[8];
+    float bc[32];
 #pragma unroll
-    for (int d = 0; d < 8; ++d) inp[d] = fmaf(c_w[P::IN_W + 2 * d], v.x, fmaf(c_w[P::IN_W + 2 * d + 1], v.y, c_w[P::IN_B + d]));
-    float x[16];
-#pragma unroll
-    for (int j = 0; j < 16; ++j) {
-        float acc = 0.f;
-#pragma unroll
-        for (int d = 0; d < 8; ++d) acc = fmaf(c_w[W + P::D_INPROJ + j * 8 + d], inp[d], acc);
-        x[j] = acc;
+    for (int k = 0; k < 32; ++k) {                       // k < 16: B_k, k >= 16: C_(k-16)
+        const int w = AF + P::A_B + 3 * k;               // A_B and A_C tables are contiguous
+        bc[k] = fmaf(c_w[w], v.x, fmaf(c_w[w + 1], v.y, c_w[w + 2]));
     }
 #pragma unroll
-    for (int q = 0; q < 4; ++q) row[q] = make_float4(x[4 * q], x[4 * q + 1], x[4 * q + 2], x[4 * q + 3]);
-    {
-        float z[16];
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-            float acc = 0.f;
-#pragma unroll
-            for (int d = 0; d < 8; ++d) acc = fmaf(c_w[W + P::D_INPROJ + (16 + j) * 8 + d], inp[d], acc);
-            z[j] = acc;
-        }
-#pragma unroll
-        for (int q = 0; q < 4; ++q) row[4 + q] = make_float4(z[4 * q], z[4 * q + 1], z[4 * q + 2], z[4 * q + 3]);
-    }
-    {
-        float dt[16];
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-            float acc = c_w[W + P::D_DTB + j];
-#pragma unroll
-            for (int k = 0; k < 16; ++k) acc = fmaf(c_w[W + P::D_DTW + j * 16 + k], x[k], acc);
-            dt[j] = softplus20(acc);
-        }
-#pragma unroll
-        for (int q = 0; q < 4; ++q) row[8 + q] = make_float4(dt[4 * q], dt[4 * q + 1], dt[4 * q + 2], dt[4 * q + 3]);
-    }
-    {
-        float bb[16];
-#pragma unroll
-        for (int s = 0; s < 16; ++s) {
-            float acc = 0.f;
-#pragma unroll
-            for (int k = 0; k < 16; ++k) acc = fmaf(c_w[W + P::D_BW + s * 16 + k], x[k], acc);
-            bb[s] = acc;
-        }
-#pragma unroll
-        for (int q = 0; q < 4; ++q) row[12 + q] = make_float4(bb[4 * q], bb[4 * q + 1], bb[4 * q + 2], bb[4 * q + 3]);
-    }
-    {
-        float cc[16];
-#pragma unroll
-        for (int s = 0; s < 16; ++s) {
-            float acc = 0.f;
-#pragma unroll
-            for (int k = 0; k < 16; ++k) acc = fmaf(c_w[W + P::D_CW + s * 16 + k], x[k], acc);
-            cc[s] = acc;
-        }
-#pragma unroll
-        for (int q = 0; q < 4; ++q) row[16 + q] = make_float4(cc[4 * q], cc[4 * q + 1], cc[4 * q + 2], cc[4 * q + 3]);
-    }
+    for (int q = 0; q < 8; ++q) row[q] = make_float4(bc[4 * q], bc[4 * q + 1], bc[4 * q + 2], bc[4 * q + 3]);
+    row[8] = make_float4(v.x, v.y, 0.f, 0.f);
 }
 
-// per (column, pair) transition: Abar_e, Abar_o, cos, sin from dt
+__device__ __forceinline__ float rcp_approx(float x) {
+    float r;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+    return r;
+}
+
+// per (column, pair) transition: Abar_e, Abar_o, cos, sin from dt.   Abar = (1+a)/(1-a) = 2/(1-a) - 1 with a = dt*A/2 <= 0.
 __device__ __forceinline__ void pair_coeffs(float dt, float ah_e, float ah_o, float f, float& abe, float& abo, float& cs, float& sn) {
-    const float ae = dt * ah_e, ao = dt * ah_o;          // dt*A/2
     // the reference denominator is 1 - dt*A/2 + 1e-8; dt*A/2 <= 0, so the sum is >= 1 and adding 1e-8 (less than
     // half an ulp of 1) does not change the fp32 value: it is dropped
-    const float de = 1.f - ae, dd = 1.f - ao;
-    const float r = __fdividef(1.f, de * dd);
-    abe = (1.f + ae) * dd * r;
-    abo = (1.f + ao) * de * r;
+    abe = fmaf(2.f, rcp_approx(fmaf(-dt, ah_e, 1.f)), -1.f);
+    abo = fmaf(2.f, rcp_approx(fmaf(-dt, ah_o, 1.f)), -1.f);
     __sincosf(dt * f, &sn, &cs);
 }
+
+// column constants of lane j: A/2, rope frequencies, and the affine tables of x_j, z_j, dt_j
+template <int DIR>
+struct ColConst {
+    float ah[16], f[8], ux[3], uz[3], ud[3], Dj;
+    __device__ __forceinline__ void load(int j) {
+        constexpr int W = (DIR == 0) ? P::DIR0 : P::DIR1;
+        constexpr int AF = (DIR == 0) ? P::AFF0 : P::AFF1;
+#pragma unroll
+        for (int s = 0; s < 16; ++s) ah[s] = -0.5f * __expf(c_w[W + P::D_ALOG + j * 16 + s]);
+#pragma unroll
+        for (int p = 0; p < 8; ++p) f[p] = c_w[W + P::D_ROPE + j * 8 + p];
+#pragma unroll
+        for (int k = 0; k < 3; ++k) {
+            ux[k] = c_w[AF + P::A_X + 3 * j + k]; uz[k] = c_w[AF + P::A_Z + 3 * j + k]; ud[k] = c_w[AF + P::A_DT + 3 * j + k];
+        }
+        Dj = c_w[W + P::D_D + j];
+    }
+};
 
 // PHASE 3: run a chunk forward from its carry-in; apply SiLU gate, D skip and out_proj; write the contexts.
 template <int DIR>
@@ -207,12 +182,9 @@ __device__ void scan_phase3(const Item& it, const TensorDir* __restrict__ tds, c
                             const uint32_t* __restrict__ vals_sorted, const float* __restrict__ carry, float* __restrict__ ctx,
                             float* __restrict__ tile, int item_idx, int j, unsigned hmask) {
     constexpr int W = (DIR == 0) ? P::DIR0 : P::DIR1;
-    float ah[16], f[8], h[16];
-#pragma unroll
-    for (int s = 0; s < 16; ++s) ah[s] = -0.5f * __expf(c_w[W + P::D_ALOG + j * 16 + s]);
-#pragma unroll
-    for (int p = 0; p < 8; ++p) f[p] = c_w[W + P::D_ROPE + j * 8 + p];
-    const float Dj = c_w[W + P::D_D + j];
+    ColConst<DIR> cc;
+    cc.load(j);
+    float h[16];
     {
         const float* cin = carry + ((int64_t)item_idx * 16 + j) * 16;
 #pragma unroll
@@ -224,13 +196,16 @@ __device__ void scan_phase3(const Item& it, const TensorDir* __restrict__ tds, c
         __syncwarp(hmask);
         for (int l = 0; l < cnt; ++l) {                 // lane j = column
             float* row = tile + l * ROW;
-            const float x = row[j], dt = row[32 + j];
+            const float2 v = *reinterpret_cast<const float2*>(row + 32);
+            const float x = fmaf(cc.ux[0], v.x, fmaf(cc.ux[1], v.y, cc.ux[2]));
+            const float z = fmaf(cc.uz[0], v.x, fmaf(cc.uz[1], v.y, cc.uz[2]));
+            const float dt = softplus20(fmaf(cc.ud[0], v.x, fmaf(cc.ud[1], v.y, cc.ud[2])));
             float B[16], C[16];
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
-                const float4 t = reinterpret_cast<const float4*>(row + 48)[q];
+                const float4 t = reinterpret_cast<const float4*>(row)[q];
                 B[4 * q] = t.x; B[4 * q + 1] = t.y; B[4 * q + 2] = t.z; B[4 * q + 3] = t.w;
-                const float4 c = reinterpret_cast<const float4*>(row + 64)[q];
+                const float4 c = reinterpret_cast<const float4*>(row + 16)[q];
                 C[4 * q] = c.x; C[4 * q + 1] = c.y; C[4 * q + 2] = c.z; C[4 * q + 3] = c.w;
             }
             const float dtx = dt * x;
@@ -238,21 +213,21 @@ __device__ void scan_phase3(const Item& it, const TensorDir* __restrict__ tds, c
 #pragma unroll
             for (int p = 0; p < 8; ++p) {
                 float abe, abo, cs, sn;
-                pair_coeffs(dt, ah[2 * p], ah[2 * p + 1], f[p], abe, abo, cs, sn);
+                pair_coeffs(dt, cc.ah[2 * p], cc.ah[2 * p + 1], cc.f[p], abe, abo, cs, sn);
                 const float he = h[2 * p], ho = h[2 * p + 1];
                 const float ne = fmaf(abe, he * cs - ho * sn, dtx * B[2 * p]);
                 const float no = fmaf(abo, ho * cs + he * sn, dtx * B[2 * p + 1]);
                 h[2 * p] = ne; h[2 * p + 1] = no;
                 y = fmaf(ne, C[2 * p], fmaf(no, C[2 * p + 1], y));
             }
-            row[j] = fmaf(y, silu(row[16 + j]), Dj * x);   // park out_j in the x slot (only lane j reads x_j)
+            row[36 + j] = fmaf(y, silu(z), cc.Dj * x);    // out_j of this timestep
         }
         __syncwarp(hmask);
         if (j < cnt) {                                    // lane = timestep again: ctx = out_proj . out at the ORIGINAL index
             const float* row = tile + j * ROW;
             float o[16];
 #pragma unroll
-            for (int q = 0; q < 4; ++q) { const float4 t = reinterpret_cast<const float4*>(row)[q]; o[4 * q] = t.x; o[4 * q + 1] = t.y; o[4 * q + 2] = t.z; o[4 * q + 3] = t.w; }
+            for (int q = 0; q < 4; ++q) { const float4 t = reinterpret_cast<const float4*>(row + 36)[q]; o[4 * q] = t.x; o[4 * q + 1] = t.y; o[4 * q + 2] = t.z; o[4 * q + 3] = t.w; }
             float c8[8];
 #pragma unroll
             for (int d = 0; d < 8; ++d) {
@@ -286,12 +261,13 @@ __device__ void scan_phase3(const Item& it, const TensorDir* __restrict__ tds, c
 template <int DIR>
 __device__ void scan_phase1(const Item& it, const float2* __restrict__ gs, float* __restrict__ agg, float* __restrict__ tile,
                             int item_idx, int j, unsigned hmask) {
-    constexpr int W = (DIR == 0) ? P::DIR0 : P::DIR1;
-    float ah[16], f[8], b[16], m[32];
+    ColConst<DIR> cc;
+    cc.load(j);
+    float b[16], m[32];
 #pragma unroll
-    for (int s = 0; s < 16; ++s) { ah[s] = -0.5f * __expf(c_w[W + P::D_ALOG + j * 16 + s]); b[s] = 0.f; }
+    for (int s = 0; s < 16; ++s) b[s] = 0.f;
 #pragma unroll
-    for (int p = 0; p < 8; ++p) { f[p] = c_w[W + P::D_ROPE + j * 8 + p]; m[4 * p] = 1.f; m[4 * p + 1] = 0.f; m[4 * p + 2] = 0.f; m[4 * p + 3] = 1.f; }
+    for (int p = 0; p < 8; ++p) { m[4 * p] = 1.f; m[4 * p + 1] = 0.f; m[4 * p + 2] = 0.f; m[4 * p + 3] = 1.f; }
     const int len = it.ue - it.ub;
     const int ntile = (len + TILE_T - 1) / TILE_T;
     for (int tI = ntile - 1; tI >= 0; --tI) {
@@ -301,18 +277,20 @@ __device__ void scan_phase1(const Item& it, const float2* __restrict__ gs, float
         __syncwarp(hmask);
         for (int l = cnt - 1; l >= 0; --l) {
             const float* row = tile + l * ROW;
-            const float x = row[j], dt = row[32 + j];
+            const float2 v = *reinterpret_cast<const float2*>(row + 32);
+            const float x = fmaf(cc.ux[0], v.x, fmaf(cc.ux[1], v.y, cc.ux[2]));
+            const float dt = softplus20(fmaf(cc.ud[0], v.x, fmaf(cc.ud[1], v.y, cc.ud[2])));
             float B[16];
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
-                const float4 t = reinterpret_cast<const float4*>(row + 48)[q];
+                const float4 t = reinterpret_cast<const float4*>(row)[q];
                 B[4 * q] = t.x; B[4 * q + 1] = t.y; B[4 * q + 2] = t.z; B[4 * q + 3] = t.w;
             }
             const float dtx = dt * x;
 #pragma unroll
             for (int p = 0; p < 8; ++p) {
                 float abe, abo, cs, sn;
-                pair_coeffs(dt, ah[2 * p], ah[2 * p + 1], f[p], abe, abo, cs, sn);
+                pair_coeffs(dt, cc.ah[2 * p], cc.ah[2 * p + 1], cc.f[p], abe, abo, cs, sn);
                 const float a0 = m[4 * p], b0 = m[4 * p + 1], c0 = m[4 * p + 2], d0 = m[4 * p + 3];
                 const float be = dtx * B[2 * p], bo = dtx * B[2 * p + 1];
                 b[2 * p]     = fmaf(a0, be, fmaf(b0, bo, b[2 * p]));
@@ -341,7 +319,7 @@ __device__ void scan_phase1(const Item& it, const float2* __restrict__ gs, float
 // items [0, n_items0) are direction 0, [n_items0_padded, ...) direction 1; n_items0_padded is a multiple of 8,
 // so one CTA (8 items) never mixes directions.
 template <int PHASE>
-__global__ void __launch_bounds__(SCAN_THREADS, 3) sg2_scan_kernel(const Item* __restrict__ items, int n_items, int dir1_start,
+__global__ void __launch_bounds__(SCAN_THREADS, 4) sg2_scan_kernel(const Item* __restrict__ items, int n_items, int dir1_start,
                                                                    const TensorDir* __restrict__ tds, const float2* __restrict__ gs,
                                                                    const uint32_t* __restrict__ vals_sorted, float* __restrict__ agg,
                                                                    const float* __restrict__ carry, float* __restrict__ ctx) {

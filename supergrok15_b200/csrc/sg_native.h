@@ -130,7 +130,17 @@ struct SG2Pack {
     static constexpr int EB1 = EW1 + 2304;
     static constexpr int EW2 = EB1 + 2304;
     static constexpr int EB2 = EW2 + 2304;               // [144]
-    static constexpr int TOTAL = EB2 + 144;              // 11,580
+    static constexpr int NET = EB2 + 144;                // 11,580 floats of meta-net weights
+    // folded affine tables of the scan inputs, per direction: value = t[0]*g + t[1]*s + t[2]
+    static constexpr int A_X = 0;                        // [16][3] x_j
+    static constexpr int A_Z = A_X + 48;                 // [16][3] z_j
+    static constexpr int A_DT = A_Z + 48;                // [16][3] dt_j before softplus
+    static constexpr int A_B = A_DT + 48;                // [16][3] B_s
+    static constexpr int A_C = A_B + 48;                 // [16][3] C_s   (must follow A_B)
+    static constexpr int AFF_SIZE = A_C + 48;            // 240
+    static constexpr int AFF0 = NET;
+    static constexpr int AFF1 = AFF0 + AFF_SIZE;
+    static constexpr int TOTAL = AFF1 + AFF_SIZE;        // 12,060
 };
 
 struct SG2Tensor {          // one entry per parameter tensor handled by a v2 step

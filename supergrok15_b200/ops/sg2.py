@@ -52,7 +52,12 @@ def layout() -> Dict[str, int]:
                            ("PQ", 704), ("KA", 192), ("KB", 192), ("EW1", 2304), ("EB1", 2304), ("EW2", 2304),
                            ("EB2", 144)):
             put(name, size)
-        L["TOTAL"] = o
+        L["NET"] = o
+        for k, name in enumerate(("A_X", "A_Z", "A_DT", "A_B", "A_C")):
+            L[name] = 48 * k
+        L["AFF_SIZE"] = 240
+        L["AFF0"], L["AFF1"] = o, o + 240
+        L["TOTAL"] = o + 480
         _FALLBACK_LAYOUT = L
     return _FALLBACK_LAYOUT
 
@@ -99,6 +104,21 @@ def pack_metanet(meta_net) -> torch.Tensor:
     pad = lambda t: torch.nn.functional.pad(t.detach().float().reshape(144, eh), (0, 16 - eh))  # noqa: E731
     put(L["EW1"], pad(meta_net.expert_W1)); put(L["EB1"], pad(meta_net.expert_b1)); put(L["EW2"], pad(meta_net.expert_W2))
     put(L["EB2"], meta_net.expert_b2)
+    # Every per-timestep input of the scan is an affine function of (g, s): fold input_proj with in_proj and the
+    # dt / B / C projections into [16][3] tables (coefficient of g, coefficient of s, constant), in fp64.
+    Wi = meta_net.input_proj.weight.detach().double()          # [8,2]
+    bi = meta_net.input_proj.bias.detach().double()            # [8]
+    inp = torch.cat([Wi, bi.unsqueeze(1)], 1)                  # [8,3]: inp_d = inp[d,0] g + inp[d,1] s + inp[d,2]
+    for base, blk in ((L["AFF0"], meta_net.mamba_fwd), (L["AFF1"], meta_net.mamba_bwd)):
+        Win = blk.in_proj.weight.detach().double()             # [32,8]
+        xz = Win @ inp                                         # [32,3]
+        x_t, z_t = xz[:16], xz[16:]
+        dt_t = blk.dt_proj.weight.detach().double() @ x_t
+        dt_t[:, 2] += blk.dt_proj.bias.detach().double()
+        b_t = blk.B_proj.weight.detach().double() @ x_t
+        c_t = blk.C_proj.weight.detach().double() @ x_t
+        for name, tab in (("A_X", x_t), ("A_Z", z_t), ("A_DT", dt_t), ("A_B", b_t), ("A_C", c_t)):
+            put(base + L[name], tab)
     return out
 
 

@@ -84,33 +84,48 @@ struct Epilogue {
     const void* D; int ldd; int d_is_bf16;
     const void* bias; int bias_is_bf16;
     int act;                       // 0 none, 1 gelu (erf), 2 silu
-    void* C; int ldc; int c_is_bf16;
+    int c_is_bf16;
     void* C2; int ldc2;            // optional second output: C2[n, m] = C[m, n] (transposed copy, same dtype)
 };
 
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* src, int c0, int c1) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(map), "r"(smem_u32(src)), "r"(c0), "r"(c1) : "memory");
+}
+
+// Persistent kernel: CTA b computes tiles b, b + gridDim.x, ...  The accumulator is double-buffered in TMEM (2 x BN columns) so
+// the epilogue of tile i overlaps the MMAs of tile i+1.  The epilogue converts 32 rows x 128 bytes at a time, parks them in
+// shared memory in the 128-byte-swizzled layout and lets TMA store them (coalesced, clipped at the matrix edge).
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a,
-                                                                  const __grid_constant__ CUtensorMap map_b, int M, int N, int K,
+                                                                  const __grid_constant__ CUtensorMap map_b,
+                                                                  const __grid_constant__ CUtensorMap map_c, int M, int N, int K,
                                                                   Epilogue ep, int* __restrict__ err) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
-    uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+    constexpr uint32_t STG_BYTES = 32 * 128;                       // one staging buffer: 32 rows x 128 bytes
+    uint8_t* staging = smem + STAGES * STAGE_BYTES;                 // [4 warps][2][STG_BYTES]
+    uint64_t* full = reinterpret_cast<uint64_t*>(staging + 4 * 2 * STG_BYTES);
     uint64_t* empty = full + STAGES;
-    uint64_t* acc_ready = empty + STAGES;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_ready + 1);
+    uint64_t* acc_full = empty + STAGES;                            // [2]
+    uint64_t* acc_empty = acc_full + 2;                             // [2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
     const int KB = (K + BK - 1) / BK;
+    const int n_tiles_n = (N + BN - 1) / BN, n_tiles = n_tiles_n * ((M + BM - 1) / BM);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-        mbar_init(acc_ready, 1);
+        for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)BN) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)(2 * BN)) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     tc_fence_before();
@@ -120,132 +135,174 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tn_kernel(const __grid_c
 
     if (warp == 0) {
         if (lane == 0) {
-            for (int kb = 0; kb < KB; ++kb) {
-                const int s = kb % STAGES;
-                if (kb >= STAGES && !mbar_wait(&empty[s], ((kb / STAGES) & 1) ^ 1)) { atomicExch(err, 1); break; }
-                uint8_t* a_dst = smem + s * STAGE_BYTES;
-                mbar_expect_tx(&full[s], STAGE_BYTES);
-                tma_load_2d(a_dst, &map_a, kb * BK, m0, &full[s]);
-                tma_load_2d(a_dst + A_BYTES, &map_b, kb * BK, n0, &full[s]);
+            uint32_t it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+                const int m0 = (tile / n_tiles_n) * BM, n0 = (tile % n_tiles_n) * BN;
+                for (int kb = 0; kb < KB; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    if (it >= (uint32_t)STAGES && !mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1)) { atomicExch(err, 1); ok = false; break; }
+                    uint8_t* a_dst = smem + s * STAGE_BYTES;
+                    mbar_expect_tx(&full[s], STAGE_BYTES);
+                    tma_load_2d(a_dst, &map_a, kb * BK, m0, &full[s]);
+                    tma_load_2d(a_dst + A_BYTES, &map_b, kb * BK, n0, &full[s]);
+                }
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
             // instruction descriptor: D fp32, A/B bf16, both K-major, N>>3 at bit 17, M>>4 at bit 24
             constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+            uint32_t it = 0, t = 0;
             bool ok = true;
-            for (int kb = 0; kb < KB && ok; ++kb) {
-                const int s = kb % STAGES;
-                if (!mbar_wait(&full[s], (kb / STAGES) & 1)) { atomicExch(err, 2); ok = false; break; }
+            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++t) {
+                const uint32_t buf = t & 1;
+                if (t >= 2 && !mbar_wait(&acc_empty[buf], ((t >> 1) & 1) ^ 1)) { atomicExch(err, 4); ok = false; }
                 tc_fence_after();
-                const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES);
-                const uint64_t da = make_desc_sw128(a_addr), db = make_desc_sw128(a_addr + A_BYTES);
+                const uint32_t tmem_d = tmem_base + buf * BN;
+                for (int kb = 0; kb < KB && ok; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    if (!mbar_wait(&full[s], (it / STAGES) & 1)) { atomicExch(err, 2); ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES);
+                    const uint64_t da = make_desc_sw128(a_addr), db = make_desc_sw128(a_addr + A_BYTES);
 #pragma unroll
-                for (int k4 = 0; k4 < BK / 16; ++k4)              // 16 bf16 = 32 bytes per MMA: advance the start address by 2 (16-byte units)
-                    tc_mma_bf16(tmem_base, da + 2 * k4, db + 2 * k4, idesc, (kb > 0 || k4 > 0) ? 1u : 0u);
-                tc_commit(&empty[s]);                             // slot reusable once these MMAs have read it
+                    for (int k4 = 0; k4 < BK / 16; ++k4)          // 16 bf16 = 32 bytes per MMA: advance the start address by 2 (16-byte units)
+                        tc_mma_bf16(tmem_d, da + 2 * k4, db + 2 * k4, idesc, (kb > 0 || k4 > 0) ? 1u : 0u);
+                    tc_commit(&empty[s]);                         // slot reusable once these MMAs have read it
+                }
+                tc_commit(&acc_full[buf]);                        // accumulator of this tile complete (also arrives when bailing out)
             }
-            tc_commit(acc_ready);                                 // accumulator complete (also arrives if the loop bailed out)
         }
     } else {
         const int q = warp & 3;                                   // TMEM lane quarter this warp may access
-        const bool ok = mbar_wait(acc_ready, 0);
-        if (!ok && lane == 0) atomicExch(err, 3);
-        tc_fence_after();
-        const int row = m0 + q * 32 + lane;
-        if (ok) {
+        uint8_t* stg = staging + (warp - 2) * 2 * STG_BYTES;
+        uint32_t t = 0, sbuf = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++t) {
+            const int m0 = (tile / n_tiles_n) * BM, n0 = (tile % n_tiles_n) * BN;
+            const uint32_t buf = t & 1;
+            if (!mbar_wait(&acc_full[buf], (t >> 1) & 1)) { if (lane == 0) atomicExch(err, 3); ok = false; break; }
+            tc_fence_after();
+            const int row = m0 + q * 32 + lane;
+            constexpr int CPC = 32;                               // accumulator columns per tcgen05.ld
+            const int cols_per_box = ep.c_is_bf16 ? 64 : 32;      // 128 bytes of output per row
 #pragma unroll 1
-            for (int c = 0; c < BN; c += 32) {
-                uint32_t r[32];
-                tc_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c, r);
-                tc_wait_ld();
-                if (row < M) {
+            for (int c = 0; c < BN; c += cols_per_box) {
+                if (n0 + c >= N) break;
+                // wait until the TMA store that last used this staging buffer has read it
+                if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+                __syncwarp();
+                uint8_t* sb = stg + sbuf * STG_BYTES;
+                for (int h = 0; h < cols_per_box; h += CPC) {
+                    uint32_t r[32];
+                    tc_ld32(tmem_base + buf * BN + ((uint32_t)(q * 32) << 16) + (uint32_t)(c + h), r);
+                    tc_wait_ld();
+                    const bool plain = (ep.D == nullptr) && (ep.bias == nullptr) && ep.diag == 0.f && ep.act == 0 && ep.alpha == 1.f;
+                    if (!plain) {
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const int col = n0 + c + j;
-                        if (col >= N) break;
-                        float v = ep.alpha * __uint_as_float(r[j]);
-                        if (ep.D) v += ep.beta * (ep.d_is_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(ep.D)[(int64_t)row * ep.ldd + col])
-                                                               : reinterpret_cast<const float*>(ep.D)[(int64_t)row * ep.ldd + col]);
-                        if (ep.bias) v += ep.bias_is_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(ep.bias)[col])
-                                                          : reinterpret_cast<const float*>(ep.bias)[col];
-                        if (row == col) v += ep.diag;
-                        if (ep.act == 1) v = 0.5f * v * (1.f + erff(v * 0.70710678f));
-                        else if (ep.act == 2) v = v / (1.f + __expf(-v));
-                        r[j] = __float_as_uint(v);
-                    }
-                    const int ncol = (N - (n0 + c) < 32) ? (N - (n0 + c)) : 32;
-                    if (ncol > 0) {
-                        if (ep.c_is_bf16) {
-                            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(ep.C) + (int64_t)row * ep.ldc + n0 + c;
-                            if (ncol == 32 && (((uintptr_t)dst) & 15) == 0) {
-#pragma unroll
-                                for (int j = 0; j < 32; j += 8) {
-                                    uint4 o;
-                                    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&o);
-#pragma unroll
-                                    for (int t = 0; t < 4; ++t) h[t] = __floats2bfloat162_rn(__uint_as_float(r[j + 2 * t]), __uint_as_float(r[j + 2 * t + 1]));
-                                    *reinterpret_cast<uint4*>(dst + j) = o;
-                                }
-                            } else {
-                                for (int j = 0; j < ncol; ++j) dst[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
+                        for (int j = 0; j < 32; ++j) {
+                            const int col = n0 + c + h + j;
+                            float v = ep.alpha * __uint_as_float(r[j]);
+                            if (row < M && col < N) {
+                                if (ep.D) v += ep.beta * (ep.d_is_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(ep.D)[(int64_t)row * ep.ldd + col])
+                                                                       : reinterpret_cast<const float*>(ep.D)[(int64_t)row * ep.ldd + col]);
+                                if (ep.bias) v += ep.bias_is_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(ep.bias)[col])
+                                                                  : reinterpret_cast<const float*>(ep.bias)[col];
                             }
-                            if (ep.C2) {
-                                __nv_bfloat16* d2 = reinterpret_cast<__nv_bfloat16*>(ep.C2);
-                                for (int j = 0; j < ncol; ++j) d2[(int64_t)(n0 + c + j) * ep.ldc2 + row] = __float2bfloat16_rn(__uint_as_float(r[j]));
-                            }
-                        } else {
-                            float* dst = reinterpret_cast<float*>(ep.C) + (int64_t)row * ep.ldc + n0 + c;
-                            if (ncol == 32 && (((uintptr_t)dst) & 15) == 0) {
-#pragma unroll
-                                for (int j = 0; j < 32; j += 4)
-                                    *reinterpret_cast<float4*>(dst + j) = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-                            } else {
-                                for (int j = 0; j < ncol; ++j) dst[j] = __uint_as_float(r[j]);
-                            }
-                            if (ep.C2) {
-                                float* d2 = reinterpret_cast<float*>(ep.C2);
-                                for (int j = 0; j < ncol; ++j) d2[(int64_t)(n0 + c + j) * ep.ldc2 + row] = __uint_as_float(r[j]);
-                            }
+                            if (row == col) v += ep.diag;
+                            if (ep.act == 1) v = 0.5f * v * (1.f + erff(v * 0.70710678f));
+                            else if (ep.act == 2) v = v / (1.f + __expf(-v));
+                            r[j] = __float_as_uint(v);
                         }
                     }
+                    if (ep.C2 && row < M) {
+                        if (ep.c_is_bf16) { __nv_bfloat16* d2 = reinterpret_cast<__nv_bfloat16*>(ep.C2);
+#pragma unroll 4
+                            for (int j = 0; j < 32; ++j) if (n0 + c + h + j < N) d2[(int64_t)(n0 + c + h + j) * ep.ldc2 + row] = __float2bfloat16_rn(__uint_as_float(r[j]));
+                        } else { float* d2 = reinterpret_cast<float*>(ep.C2);
+#pragma unroll 4
+                            for (int j = 0; j < 32; ++j) if (n0 + c + h + j < N) d2[(int64_t)(n0 + c + h + j) * ep.ldc2 + row] = __uint_as_float(r[j]);
+                        }
+                    }
+                    // park this lane's row segment in the swizzled staging tile: 16-byte chunk k of row `lane` lives at chunk k ^ (lane & 7)
+                    uint8_t* rowp = sb + lane * 128;
+                    if (ep.c_is_bf16) {
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {             // 32 columns -> 64 bytes -> 4 chunks
+                            uint4 o;
+                            __nv_bfloat162* hh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+                            for (int u = 0; u < 4; ++u) hh[u] = __floats2bfloat162_rn(__uint_as_float(r[8 * k + 2 * u]), __uint_as_float(r[8 * k + 2 * u + 1]));
+                            const int chunk = (h / 8) + k;        // h is 0 or 32 -> chunks 0..3 or 4..7
+                            *reinterpret_cast<uint4*>(rowp + ((chunk ^ (lane & 7)) << 4)) = o;
+                        }
+                    } else {
+#pragma unroll
+                        for (int k = 0; k < 8; ++k)
+                            *reinterpret_cast<uint4*>(rowp + ((k ^ (lane & 7)) << 4)) = make_uint4(r[4 * k], r[4 * k + 1], r[4 * k + 2], r[4 * k + 3]);
+                    }
                 }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) {
+                    tma_store_2d(&map_c, sb, n0 + c, m0 + q * 32);
+                    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                }
+                sbuf ^= 1;
             }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[buf]);          // this warp no longer reads the TMEM buffer
         }
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     }
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)BN) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)(2 * BN)) : "memory");
     }
 }
 
 // ---- host side -------------------------------------------------------------------------------------------------
-bool make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int64_t ld_elems, int box_rows) {
+bool make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int64_t ld_elems, int box_rows, int box_cols, bool bf16) {
     const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-    const cuuint64_t strides[1] = {(cuuint64_t)ld_elems * 2};
-    const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)ld_elems * (bf16 ? 2 : 4)};
+    const cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
     const cuuint32_t estr[2] = {1, 1};
-    const CUresult r = cuTensorMapEncodeTiled(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-                                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    const CUresult r = cuTensorMapEncodeTiled(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2,
+                                              const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS;
 }
 
+int num_sms() {
+    static int n = 0;
+    if (n == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+        if (n <= 0) n = 148;
+    }
+    return n;
+}
+
 template <int BN, int STAGES>
-int launch(const void* A, int lda, const void* B, int ldb, int M, int N, int K, const Epilogue& ep, int* err, cudaStream_t s) {
-    CUtensorMap ma, mb;
-    if (!make_map(&ma, A, M, K, lda, BM) || !make_map(&mb, B, N, K, ldb, BN)) return 1;
-    constexpr size_t smem = (size_t)STAGES * (BM * BK * 2 + BN * BK * 2) + 1024 + 256;
+int launch(const void* A, int lda, const void* B, int ldb, int M, int N, int K, const Epilogue& ep, void* C, int ldc, int* err, cudaStream_t s) {
+    CUtensorMap ma, mb, mc;
+    if (!make_map(&ma, A, M, K, lda, BM, BK, true) || !make_map(&mb, B, N, K, ldb, BN, BK, true)) return 1;
+    if (!make_map(&mc, C, M, N, ldc, 32, ep.c_is_bf16 ? 64 : 32, ep.c_is_bf16 != 0)) return 4;
+    constexpr size_t smem = (size_t)STAGES * (BM * BK * 2 + BN * BK * 2) + 4 * 2 * 4096 + 1024 + 256;
     static bool configured = false;
     if (!configured) {
         if (cudaFuncSetAttribute(gemm_tn_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return 2;
         configured = true;
     }
-    dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
+    const int tiles = ((N + BN - 1) / BN) * ((M + BM - 1) / BM);
+    const int grid = tiles < num_sms() ? tiles : num_sms();
     count_launch();
-    gemm_tn_kernel<BN, STAGES><<<grid, GEMM_THREADS, smem, s>>>(ma, mb, M, N, K, ep, err);
+    gemm_tn_kernel<BN, STAGES><<<grid, GEMM_THREADS, smem, s>>>(ma, mb, mc, M, N, K, ep, err);
     return cudaGetLastError() == cudaSuccess ? 0 : 3;
 }
 
@@ -257,9 +314,11 @@ int gemm_bf16_tn(const void* A, int lda, const void* B, int ldb, int M, int N, i
                  bool d_bf16, const void* bias, bool bias_bf16, float diag, int act, void* C, int ldc, bool c_bf16, void* C2, int ldc2,
                  int* err, cudaStream_t s) {
     if (M <= 0 || N <= 0 || K <= 0) return 0;
-    Epilogue ep{alpha, beta, diag, D, ldd, d_bf16 ? 1 : 0, bias, bias_bf16 ? 1 : 0, act, C, ldc, c_bf16 ? 1 : 0, C2, ldc2};
-    if (N > 128) return launch<256, 4>(A, lda, B, ldb, M, N, K, ep, err, s);
-    return launch<128, 6>(A, lda, B, ldb, M, N, K, ep, err, s);
+    Epilogue ep{alpha, beta, diag, D, ldd, d_bf16 ? 1 : 0, bias, bias_bf16 ? 1 : 0, act, c_bf16 ? 1 : 0, C2, ldc2};
+    // the output goes through TMA: its base must be 16-byte aligned and its row pitch a multiple of 16 bytes
+    if ((reinterpret_cast<uintptr_t>(C) & 15) != 0 || (ldc * (c_bf16 ? 2 : 4)) % 16 != 0) return 5;
+    if (N > 128) return launch<256, 4>(A, lda, B, ldb, M, N, K, ep, C, ldc, err, s);
+    return launch<128, 6>(A, lda, B, ldb, M, N, K, ep, C, ldc, err, s);
 }
 
 }  // namespace sg

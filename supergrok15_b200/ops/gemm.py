@@ -39,7 +39,10 @@ def gemm_tn(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None
             out_dtype=torch.bfloat16, out_t: Optional[torch.Tensor] = None) -> torch.Tensor:
     C = _build.require()
     if out is None:
-        out = torch.empty(a.shape[0], b.shape[0], dtype=out_dtype, device=a.device)
+        n = b.shape[0]
+        q = 8 if out_dtype == torch.bfloat16 else 4          # the output is written by TMA: 16-byte row pitch
+        npad = -(-n // q) * q
+        out = torch.empty(a.shape[0], npad, dtype=out_dtype, device=a.device)[:, :n]
     C.gemm_tn(a, b, out, alpha, beta, d, bias, diag, ACT[act], out_t, _err_flag(a.device))
     return out
 
@@ -65,15 +68,15 @@ class _Linear(torch.autograd.Function):
         ctx.save_for_backward(x2, weight)
         ctx.has_bias, ctx.xshape = bias is not None, x.shape
         y = gemm_tn(_pad8(x2), _pad8(weight), bias=bias, act=act, out_dtype=x.dtype if x.dtype != torch.float32 else torch.float32)
-        return y.view(*x.shape[:-1], weight.shape[0])
+        return y.contiguous().view(*x.shape[:-1], weight.shape[0])
 
     @staticmethod
     def backward(ctx, dy):
         x2, weight = ctx.saved_tensors
         dy2 = dy.reshape(-1, dy.shape[-1])
         dyb = _pad8(dy2)
-        dx = gemm_tn(dyb, _pad8(weight.t().contiguous()), out_dtype=x2.dtype).view(ctx.xshape)       # dy [M,N] @ W [N,K]
-        dw = gemm_tn(_pad8(dy2.t().contiguous()), _pad8(x2.t().contiguous()), out_dtype=weight.dtype)  # dy^T [N,M] @ x [M,K]
+        dx = gemm_tn(dyb, _pad8(weight.t().contiguous()), out_dtype=x2.dtype).contiguous().view(ctx.xshape)   # dy [M,N] @ W [N,K]
+        dw = gemm_tn(_pad8(dy2.t().contiguous()), _pad8(x2.t().contiguous()), out_dtype=weight.dtype).contiguous()  # dy^T @ x
         db = dy2.float().sum(0).to(dy.dtype) if ctx.has_bias else None
         return dx, dw, db, None
 
@@ -106,7 +109,7 @@ def newton_schulz(X: torch.Tensor, steps: int, coeffs, precision: str = "bf16") 
     npad = -(-n // 8) * 8
     G = torch.zeros(n, npad, dtype=torch.bfloat16, device=dev)[:, :n]
     P = torch.zeros(n, npad, dtype=torch.bfloat16, device=dev)[:, :n]
-    out32 = torch.empty(r, cc, dtype=torch.float32, device=dev)
+    out32 = torch.empty(r, -(-cc // 4) * 4, dtype=torch.float32, device=dev)[:, :cc]
     for it in range(steps):
         last = it == steps - 1
         src = XTb if tall else Xb

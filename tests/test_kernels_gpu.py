@@ -216,3 +216,33 @@ def test_cuda_graph_capture_of_fused_steps():
     assert a._graph is not None
     for p, q in zip(gpu, ref):
         assert torch.allclose(p, q, rtol=1e-6, atol=1e-8)
+
+
+def test_device_barrier_wait_is_bounded_and_reports_the_peer():
+    """A peer that never signals: the waiter gives up after the deadline, records who it waited for and where, and
+    the CUDA context stays usable.  Nothing traps or hangs; the flag is simply never written."""
+    C = _build.require()
+    mine = torch.zeros(64, dtype=torch.int32, device="cuda")
+    peer = torch.zeros(64, dtype=torch.int32, device="cuda")          # stands in for the pad of a rank that is not there
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    C.dist_barrier([mine.data_ptr(), peer.data_ptr()], 0, 1, status, 0.3, 7)
+    torch.cuda.synchronize()
+    s = int(status.item())
+    assert s & 0xFF == C.STATUS_TIMEOUT and (s >> 8) & 0xFF == 1 and (s >> 16) & 0xFF == 7
+    assert int(peer[0]) == 1                                           # our own arrival was published
+    assert float(torch.ones(8, device="cuda").sum()) == 8.0           # context alive
+    mine[1] = 2                                                        # now the "peer" has arrived at epoch 2
+    status.zero_()
+    C.dist_barrier([mine.data_ptr(), peer.data_ptr()], 0, 2, status, 0.3, 7)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+
+
+def test_engine_reports_comm_timeout():
+    from supergrok15_b200.parallel import CommTimeout, ZeroEngine
+    from supergrok15_b200.models import Transformer
+    eng = ZeroEngine(Transformer(1, 32, 2).cuda(), "adamw", {}, param_dtype=torch.bfloat16)
+    eng.status.fill_(1 | (3 << 8) | (2 << 16))
+    with pytest.raises(CommTimeout, match="peer 3"):
+        eng.check()
+    eng.check()                                                       # cleared

@@ -121,8 +121,8 @@ def newton_schulz(X: torch.Tensor, steps: int, coeffs, precision: str = "bf16") 
             else:
                 gemm_tn(P, XTb, out=out32)                                  # Q X   (B operand = X^T [c, r])
         else:
-            Xn = torch.empty_like(Xb)
-            XTn = torch.empty_like(XTb)
+            Xn = torch.empty(r, cp, dtype=torch.bfloat16, device=dev)[:, :cc]       # padded row pitch (16-byte multiple)
+            XTn = torch.empty(cc, rp, dtype=torch.bfloat16, device=dev)[:, :r]
             if tall:
                 gemm_tn(Xb, P, out=Xn, out_t=XTn)
             else:

@@ -56,7 +56,7 @@ def test_linear_autograd_matches_torch():
     assert torch.allclose(b.grad.float(), br.grad, rtol=3e-2, atol=0.3)
 
 
-@pytest.mark.parametrize("shape", [(256, 128), (128, 256), (512, 512), (264, 136)])
+@pytest.mark.parametrize("shape", [(256, 128), (128, 256), (512, 512), (264, 136), (203, 136), (136, 203)])
 def test_newton_schulz_matches_fp32_iteration(shape):
     torch.manual_seed(2)
     X = torch.randn(shape, device="cuda")

@@ -16,6 +16,12 @@ void sg2_elem(int dtype, const MTArgs& a, float beta2, float lr, float wd_eff, f
               cudaStream_t s);
 size_t sg2_item_bytes();
 size_t sg2_td_bytes();
+size_t sg2_bilevel_smem_bytes();
+int sg2_bilevel_ng();
+int sg2_bilevel_tile();
+void sg2_scan_backward(const void* items_dev, int n_items, int dir1_start, const void* tds_dev, int n_td, const int64_t* snap_base_dev,
+                       const float* gs_sorted, const uint32_t* vals_sorted, const float* dctx, const float* carry, float* agg, float* dcarry,
+                       float* snaps, float* partial, float* grads, cudaStream_t s);
 }
 
 namespace sgb {
@@ -82,6 +88,20 @@ void sg2_elem(const TL& params, const TL& ms, const TL& vs, const TL& mus, const
     });
 }
 
+// Adjoint of the scan: dctx [total,16] -> grads [2, NG] (see csrc/sg2_bilevel.cuh for the layout).  Must follow a forward scan on the
+// same plan / workspace (it re-uses gs, vals and the chunk carry-in states of that forward).
+void sg2_scan_backward(Tensor items, int64_t n_items, int64_t dir1_start, Tensor tds, int64_t n_td, Tensor snap_base, int64_t sorted_buf,
+                       Tensor dctx, py::dict ws, Tensor snaps, Tensor partial, Tensor grads) {
+    c10::cuda::CUDAGuard guard(items.device());
+    auto W = [&](const char* k) { return ws[k].cast<Tensor>(); };
+    TORCH_CHECK(dctx.is_contiguous() && dctx.scalar_type() == at::kFloat, "dctx must be contiguous fp32");
+    const uint32_t* vs = sorted_buf ? u32(W("vals1")) : u32(W("vals0"));
+    sg::sg2_scan_backward(items.data_ptr(), (int)n_items, (int)dir1_start, tds.data_ptr(), (int)n_td, snap_base.data_ptr<int64_t>(),
+                          W("gs").data_ptr<float>(), vs, dctx.data_ptr<float>(), W("carry").data_ptr<float>(), W("agg").data_ptr<float>(),
+                          W("dcarry").data_ptr<float>(), snaps.data_ptr<float>(), partial.data_ptr<float>(), grads.data_ptr<float>(),
+                          at::cuda::getCurrentCUDAStream());
+}
+
 void sg2_upload_weights(Tensor packed) {
     TORCH_CHECK(packed.is_cuda() && packed.scalar_type() == at::kFloat && packed.numel() == sg::SG2Pack::TOTAL && packed.is_contiguous(),
                 "packed weights must be a contiguous fp32 CUDA vector of ", sg::SG2Pack::TOTAL, " floats");
@@ -122,6 +142,9 @@ void register_sg2(pybind11::module_& m) {
     m.def("sg2_upload_weights", &sg2_upload_weights);
     m.def("sg2_sort", &sg2_sort);
     m.def("sg2_layout", &sg2_layout);
+    m.def("sg2_scan_backward", &sg2_scan_backward);
+    m.def("sg2_bilevel_info", []() { py::dict d; d["ng"] = sg::sg2_bilevel_ng(); d["tile"] = sg::sg2_bilevel_tile();
+                                     d["smem"] = (int64_t)sg::sg2_bilevel_smem_bytes(); return d; });
     m.def("sg2_sort_blocks", [](int64_t total) { return (int64_t)sg::sg2_sort_blocks(total); });
 }
 }  // namespace sgb

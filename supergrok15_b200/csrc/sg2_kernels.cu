@@ -558,3 +558,5 @@ size_t sg2_item_bytes() { return sizeof(Item); }
 size_t sg2_td_bytes() { return sizeof(TensorDir); }
 
 }  // namespace sg
+
+#include "sg2_bilevel.cuh"

@@ -280,6 +280,10 @@ def bilevel_backward(opt, named, train_grads: Dict[str, torch.Tensor], val_grads
     instead of keeping every tensor's graph alive at once.
     """
     mn = opt.meta_net
+    first = next((p for _, p in named), None)
+    if first is not None and first.is_cuda and supports_native(mn) and not getattr(opt, "bilevel_force_autograd", False):
+        from .sg2_bilevel import bilevel_backward_cuda
+        return bilevel_backward_cuda(opt, named, train_grads, val_grads)
     used = 0
     for name, p in named:
         if name not in train_grads or name not in val_grads:

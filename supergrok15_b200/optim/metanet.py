@@ -287,6 +287,24 @@ class Mamba3PEERMetaNet(nn.Module):
         smart = g + self.rescale * total / self.num_peer_heads
         return smart.reshape(grad.shape).to(grad.dtype), new_gru, new_fwd, new_bwd
 
+    def soft_head(self, g, s, gru_state, fwd_ctx, bwd_ctx, topk: int = 4):
+        """Everything after the scan of ``forward_for_bilevel`` (GRU, soft top-k routing, experts) for elements whose
+        contexts are given: returns smart_grad [n].  Element-wise over n, so it can be applied to any slice."""
+        gs = torch.stack([g, s], dim=-1)
+        new_gru = self.gru(torch.cat([gs, fwd_ctx, bwd_ctx], dim=-1), gru_state.float())
+        peer_in = torch.cat([new_gru, fwd_ctx, bwd_ctx, gs], dim=-1)
+        half = self.d_model // 2
+        total = torch.zeros_like(g)
+        for h in range(self.num_peer_heads):
+            q = self.peer_queries[h](peer_in)
+            ta, ia = (q[:, :half] @ self.product_keys_A[h].T).topk(topk, dim=-1)
+            tb, ib = (q[:, half:] @ self.product_keys_B[h].T).topk(topk, dim=-1)
+            wa, wb = torch.softmax(ta * 10.0, -1), torch.softmax(tb * 10.0, -1)
+            eidx = (ia.unsqueeze(2) * self.pk_dim + ib.unsqueeze(1)).reshape(g.numel(), -1)
+            w = (wa.unsqueeze(2) * wb.unsqueeze(1)).reshape(g.numel(), -1)
+            total = total + (w * self._expert_out(g, eidx)).sum(-1)
+        return g + self.rescale * total / self.num_peer_heads
+
     # ------------------------------------------------------------------ expert recycling
     @torch.no_grad()
     def _recycle_dead_experts(self, generator: Optional[torch.Generator] = None):

@@ -93,7 +93,7 @@ class _ScanCtx(torch.autograd.Function):
 
 
 def bilevel_backward_cuda(opt, named, train_grads: Dict[str, torch.Tensor], val_grads: Dict[str, torch.Tensor],
-                          slice_elems: int = 1 << 20) -> int:
+                          slice_elems: int = 1 << 18) -> int:
     """Accumulate d(meta_loss)/d(meta-net parameters) into their ``.grad`` with the batched CUDA pipeline."""
     C = _build.require()
     mn = opt.meta_net

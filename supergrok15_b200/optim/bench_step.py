@@ -1,0 +1,97 @@
+"""SuperGrok v2 optimizer-step and bilevel-step latency on one GPU.
+
+Config: the pre-LN bias-free decoder at d_model 256, 4 layers (3,174,144 parameters in 26 tensors), gradients drawn
+from N(0, 1e-3) (seeded), meta-net defaults (d_model 8, d_inner 16, d_state 16, GRU 4, 4 heads, 144 experts of 1-16-1),
+``bilevel_checkpoint_interval=32``.  Reports milliseconds per ``step()`` and per ``bilevel_step()`` (CUDA events, after
+warm-up), for this package or for the reference installed under baseline/_ref (``--impl reference``).
+
+    python -m supergrok15_b200.optim.bench_step [--impl reference] [--steps 20] [--scale medium|large]
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import torch
+import torch.nn as nn
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--scale", default="medium", choices=["small", "medium", "large"])
+    ap.add_argument("--no-bilevel", action="store_true")
+    a = ap.parse_args()
+    root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    sys.path.insert(0, root)
+    from supergrok15_b200.models import MODEL_SCALES, PreLNTransformer
+    sc = MODEL_SCALES[a.scale]
+    dev = torch.device("cuda")
+    torch.manual_seed(0)
+    model = PreLNTransformer(sc["num_layers"], sc["dim_model"], sc["num_heads"], 99, 4).to(dev)
+    if a.impl == "reference":
+        import ctypes
+        ref = os.path.join(root, "baseline", "_ref")
+        sys.path.insert(0, ref)
+        sys.modules.pop("grokking_optimizers", None)
+        shim = os.path.join(ref, "libref_shim.so")
+        if os.path.exists(shim):
+            ctypes.CDLL(shim, mode=ctypes.RTLD_GLOBAL)
+        try:
+            import grokking_optimizers as go
+            assert "baseline/_ref" in go.__file__.replace("\\", "/")
+            opt = go.SuperGrok2(model.parameters(), bilevel_checkpoint_interval=32)
+        except Exception as e:  # noqa: BLE001
+            print(json.dumps({"impl": "reference", "unavailable": f"{type(e).__name__}: {str(e)[:200]}"}))
+            return
+    else:
+        from supergrok15_b200.optim import SuperGrok2
+        opt = SuperGrok2(model.parameters(), bilevel_checkpoint_interval=32)
+    opt.meta_net.to(dev)
+    g = torch.Generator(device="cuda").manual_seed(1)
+    n_params = sum(p.numel() for p in model.parameters())
+
+    def set_grads():
+        for p in model.parameters():
+            p.grad = torch.randn(p.shape, device=dev, generator=g) * 1e-3
+
+    def timeit(fn, n):
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n
+
+    set_grads()
+    for _ in range(a.warmup):
+        opt.step()
+    step_ms = timeit(opt.step, a.steps)
+    out = {"impl": a.impl, "scale": a.scale, "params": n_params, "tensors": len(list(model.parameters())), "step_ms": step_ms,
+           "step_ms_per_1e9_params": step_ms * 1e9 / n_params}
+    if not a.no_bilevel:
+        x = torch.randint(0, 97, (512, 4), device=dev)
+        y = torch.randint(0, 97, (512,), device=dev)
+        crit = nn.CrossEntropyLoss()
+        mopt = torch.optim.Adam(opt.meta_net.parameters(), lr=1e-4)
+
+        def bilevel():
+            set_grads()
+            opt.bilevel_step(model, x, y, x, y, crit, mopt)
+        try:
+            for _ in range(2):
+                bilevel()
+            out["bilevel_ms"] = timeit(bilevel, max(3, a.steps // 4))
+        except Exception as e:  # noqa: BLE001
+            out["bilevel_error"] = f"{type(e).__name__}: {str(e)[:200]}"
+    print(json.dumps(out))
+
+
+if __name__ == "__main__":
+    main()

@@ -294,15 +294,23 @@ class Mamba3PEERMetaNet(nn.Module):
         new_gru = self.gru(torch.cat([gs, fwd_ctx, bwd_ctx], dim=-1), gru_state.float())
         peer_in = torch.cat([new_gru, fwd_ctx, bwd_ctx, gs], dim=-1)
         half = self.d_model // 2
-        total = torch.zeros_like(g)
+        n = g.numel()
+        # Every head evaluates the SAME experts on the SAME scalar g, so the heads only differ in their routing weights:
+        # total = sum_e (sum_heads R_h[n,e]) * expert_e(g_n).  The routing weights are scattered into a dense [n, E]
+        # matrix (whose backward is a gather) and all E experts are evaluated densely; gathering expert weights per
+        # element instead would turn the backward into hundreds of millions of atomic adds onto E*hidden addresses.
+        route = torch.zeros(n, self.num_experts, device=g.device, dtype=torch.float32)
         for h in range(self.num_peer_heads):
             q = self.peer_queries[h](peer_in)
             ta, ia = (q[:, :half] @ self.product_keys_A[h].T).topk(topk, dim=-1)
             tb, ib = (q[:, half:] @ self.product_keys_B[h].T).topk(topk, dim=-1)
             wa, wb = torch.softmax(ta * 10.0, -1), torch.softmax(tb * 10.0, -1)
-            eidx = (ia.unsqueeze(2) * self.pk_dim + ib.unsqueeze(1)).reshape(g.numel(), -1)
-            w = (wa.unsqueeze(2) * wb.unsqueeze(1)).reshape(g.numel(), -1)
-            total = total + (w * self._expert_out(g, eidx)).sum(-1)
+            eidx = (ia.unsqueeze(2) * self.pk_dim + ib.unsqueeze(1)).reshape(n, -1)
+            w = (wa.unsqueeze(2) * wb.unsqueeze(1)).reshape(n, -1)
+            route = route.scatter_add(1, eidx, w)
+        z = torch.relu(g.view(n, 1, 1) * self.expert_W1.squeeze(-1).unsqueeze(0) + self.expert_b1.unsqueeze(0))   # [n,E,H]
+        out_all = (z * self.expert_W2.squeeze(1).unsqueeze(0)).sum(-1) + self.expert_b2.squeeze(-1).unsqueeze(0)   # [n,E]
+        total = (route * out_all).sum(-1)
         return g + self.rescale * total / self.num_peer_heads
 
     # ------------------------------------------------------------------ expert recycling

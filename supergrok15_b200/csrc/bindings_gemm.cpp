@@ -7,7 +7,7 @@
 namespace sg {
 int gemm_bf16_tn(const void* A, int lda, const void* B, int ldb, int M, int N, int K, float alpha, float beta, const void* D, int ldd,
                  bool d_bf16, const void* bias, bool bias_bf16, float diag, int act, void* C, int ldc, bool c_bf16, void* C2, int ldc2,
-                 int* err, cudaStream_t s);
+                 float* splitk_ws, int64_t splitk_ws_floats, int* err, cudaStream_t s);
 }
 
 namespace sgb {
@@ -17,7 +17,8 @@ using at::Tensor;
 // out = act(alpha * a @ b.T + beta * d + bias + diag * I);  a [M,K], b [N,K] bf16 row-major (last stride 1, row stride multiple of 8).
 // out: bf16 or fp32 [M,N]; out_t (optional): [N,M] receives the transposed result.
 void gemm_tn(const Tensor& a, const Tensor& b, Tensor out, double alpha, double beta, const c10::optional<Tensor>& d,
-             const c10::optional<Tensor>& bias, double diag, int64_t act, const c10::optional<Tensor>& out_t, Tensor err) {
+             const c10::optional<Tensor>& bias, double diag, int64_t act, const c10::optional<Tensor>& out_t, Tensor err,
+             const c10::optional<Tensor>& splitk_ws) {
     TORCH_CHECK(a.is_cuda() && b.is_cuda() && out.is_cuda(), "gemm_tn needs CUDA tensors");
     TORCH_CHECK(a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16, "gemm_tn operands must be bf16");
     TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && a.size(1) == b.size(1), "shape mismatch: a [M,K], b [N,K]");
@@ -36,6 +37,7 @@ void gemm_tn(const Tensor& a, const Tensor& b, Tensor out, double alpha, double 
                                     d.has_value() && d->scalar_type() == at::kBFloat16, bias.has_value() ? bias->data_ptr() : nullptr,
                                     bias.has_value() && bias->scalar_type() == at::kBFloat16, (float)diag, (int)act, out.data_ptr(), (int)out.stride(0),
                                     c_bf16, out_t.has_value() ? out_t->data_ptr() : nullptr, out_t.has_value() ? (int)out_t->stride(0) : 0,
+                                    splitk_ws.has_value() ? splitk_ws->data_ptr<float>() : nullptr, splitk_ws.has_value() ? splitk_ws->numel() : 0,
                                     err.data_ptr<int>(), at::cuda::getCurrentCUDAStream());
     TORCH_CHECK(rc == 0, "gemm_tn launch failed (code ", rc, ")");
 }
@@ -44,6 +46,6 @@ void gemm_tn(const Tensor& a, const Tensor& b, Tensor out, double alpha, double 
 void register_gemm(pybind11::module_& m) {
     m.def("gemm_tn", &gemm_tn, py::arg("a"), py::arg("b"), py::arg("out"), py::arg("alpha") = 1.0, py::arg("beta") = 0.0,
           py::arg("d") = c10::nullopt, py::arg("bias") = c10::nullopt, py::arg("diag") = 0.0, py::arg("act") = 0,
-          py::arg("out_t") = c10::nullopt, py::arg("err"));
+          py::arg("out_t") = c10::nullopt, py::arg("err"), py::arg("splitk_ws") = c10::nullopt);
 }
 }  // namespace sgb

@@ -103,7 +103,7 @@ template <int BN, int STAGES>
 __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                   const __grid_constant__ CUtensorMap map_b,
                                                                   const __grid_constant__ CUtensorMap map_c, int M, int N, int K,
-                                                                  Epilogue ep, int* __restrict__ err) {
+                                                                  int splits, Epilogue ep, int* __restrict__ err) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
@@ -116,8 +116,13 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tn_kernel(const __grid_c
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int KB = (K + BK - 1) / BK;
-    const int n_tiles_n = (N + BN - 1) / BN, n_tiles = n_tiles_n * ((M + BM - 1) / BM);
+    // split-K: work item = (split, m tile, n tile); split s covers k blocks [s*KB, (s+1)*KB) and writes an fp32 partial tile into
+    // rows [s*Mpad, s*Mpad + M) of the workspace that map_c describes (summed by gemm_splitk_reduce_kernel)
+    const int KB_all = (K + BK - 1) / BK;
+    const int KB = (KB_all + splits - 1) / splits;
+    const int n_tiles_n = (N + BN - 1) / BN, n_tiles_m = (M + BM - 1) / BM;
+    const int tiles_per_split = n_tiles_n * n_tiles_m, n_tiles = tiles_per_split * splits;
+    const int Mpad = n_tiles_m * BM;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
@@ -138,14 +143,15 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tn_kernel(const __grid_c
             uint32_t it = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
-                const int m0 = (tile / n_tiles_n) * BM, n0 = (tile % n_tiles_n) * BN;
-                for (int kb = 0; kb < KB; ++kb, ++it) {
+                const int sp = tile / tiles_per_split, tl = tile % tiles_per_split;
+                const int m0 = (tl / n_tiles_n) * BM, n0 = (tl % n_tiles_n) * BN, kb0 = sp * KB;
+                for (int kb = 0; kb < KB; ++kb, ++it) {           // k blocks past the end of K are zero-filled by TMA
                     const int s = it % STAGES;
                     if (it >= (uint32_t)STAGES && !mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1)) { atomicExch(err, 1); ok = false; break; }
                     uint8_t* a_dst = smem + s * STAGE_BYTES;
                     mbar_expect_tx(&full[s], STAGE_BYTES);
-                    tma_load_2d(a_dst, &map_a, kb * BK, m0, &full[s]);
-                    tma_load_2d(a_dst + A_BYTES, &map_b, kb * BK, n0, &full[s]);
+                    tma_load_2d(a_dst, &map_a, (kb0 + kb) * BK, m0, &full[s]);
+                    tma_load_2d(a_dst + A_BYTES, &map_b, (kb0 + kb) * BK, n0, &full[s]);
                 }
             }
         }
@@ -180,7 +186,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tn_kernel(const __grid_c
         uint32_t t = 0, sbuf = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++t) {
-            const int m0 = (tile / n_tiles_n) * BM, n0 = (tile % n_tiles_n) * BN;
+            const int sp = tile / tiles_per_split, tl = tile % tiles_per_split;
+            const int m0 = (tl / n_tiles_n) * BM, n0 = (tl % n_tiles_n) * BN;
             const uint32_t buf = t & 1;
             if (!mbar_wait(&acc_full[buf], (t >> 1) & 1)) { if (lane == 0) atomicExch(err, 3); ok = false; break; }
             tc_fence_after();
@@ -246,7 +253,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tn_kernel(const __grid_c
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 __syncwarp();
                 if (lane == 0) {
-                    tma_store_2d(&map_c, sb, n0 + c, m0 + q * 32);
+                    tma_store_2d(&map_c, sb, n0 + c, sp * Mpad + m0 + q * 32);
                     asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                 }
                 sbuf ^= 1;
@@ -262,6 +269,29 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tn_kernel(const __grid_c
     if (warp == 1) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)(2 * BN)) : "memory");
+    }
+}
+
+// sums the split-K partial tiles (fixed order) and applies the epilogue
+__global__ void __launch_bounds__(256) gemm_splitk_reduce_kernel(const float* __restrict__ ws, int splits, int Mpad, int ldw, int M, int N,
+                                                                 Epilogue ep, void* __restrict__ C, int ldc) {
+    const int64_t idx = (int64_t)blockIdx.x * 256 + threadIdx.x;
+    if (idx >= (int64_t)M * N) return;
+    const int row = (int)(idx / N), col = (int)(idx % N);
+    float acc = 0.f;
+    for (int s = 0; s < splits; ++s) acc += ws[((int64_t)s * Mpad + row) * ldw + col];
+    float v = ep.alpha * acc;
+    if (ep.D) v += ep.beta * (ep.d_is_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(ep.D)[(int64_t)row * ep.ldd + col])
+                                           : reinterpret_cast<const float*>(ep.D)[(int64_t)row * ep.ldd + col]);
+    if (ep.bias) v += ep.bias_is_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(ep.bias)[col]) : reinterpret_cast<const float*>(ep.bias)[col];
+    if (row == col) v += ep.diag;
+    if (ep.act == 1) v = 0.5f * v * (1.f + erff(v * 0.70710678f));
+    else if (ep.act == 2) v = v / (1.f + __expf(-v));
+    if (ep.c_is_bf16) reinterpret_cast<__nv_bfloat16*>(C)[(int64_t)row * ldc + col] = __float2bfloat16_rn(v);
+    else reinterpret_cast<float*>(C)[(int64_t)row * ldc + col] = v;
+    if (ep.C2) {
+        if (ep.c_is_bf16) reinterpret_cast<__nv_bfloat16*>(ep.C2)[(int64_t)col * ep.ldc2 + row] = __float2bfloat16_rn(v);
+        else reinterpret_cast<float*>(ep.C2)[(int64_t)col * ep.ldc2 + row] = v;
     }
 }
 
@@ -289,20 +319,40 @@ int num_sms() {
 }
 
 template <int BN, int STAGES>
-int launch(const void* A, int lda, const void* B, int ldb, int M, int N, int K, const Epilogue& ep, void* C, int ldc, int* err, cudaStream_t s) {
+int launch(const void* A, int lda, const void* B, int ldb, int M, int N, int K, const Epilogue& ep_in, void* C, int ldc, float* ws,
+           int64_t ws_floats, int* err, cudaStream_t s) {
     CUtensorMap ma, mb, mc;
     if (!make_map(&ma, A, M, K, lda, BM, BK, true) || !make_map(&mb, B, N, K, ldb, BN, BK, true)) return 1;
-    if (!make_map(&mc, C, M, N, ldc, 32, ep.c_is_bf16 ? 64 : 32, ep.c_is_bf16 != 0)) return 4;
+    // split-K when the output has too few tiles to fill the GPU and K is long
+    const int tiles_mn = ((N + BN - 1) / BN) * ((M + BM - 1) / BM);
+    const int KB_all = (K + BK - 1) / BK;
+    const int Mpad = ((M + BM - 1) / BM) * BM, ldw = ((N + 3) / 4) * 4;
+    int splits = 1;
+    if (ws != nullptr && tiles_mn * 2 <= num_sms() && KB_all >= 16) {
+        splits = num_sms() / tiles_mn;
+        if (splits > KB_all / 4) splits = KB_all / 4;
+        while (splits > 1 && (int64_t)splits * Mpad * ldw > ws_floats) --splits;
+        if (splits < 1) splits = 1;
+    }
+    Epilogue ep = ep_in;
+    if (splits > 1) {
+        ep = Epilogue{1.f, 0.f, 0.f, nullptr, 0, 0, nullptr, 0, 0, 0, nullptr, 0};      // plain fp32 partial sums
+        if (!make_map(&mc, ws, (int64_t)splits * Mpad, N, ldw, 32, 32, false)) return 4;
+    } else if (!make_map(&mc, C, M, N, ldc, 32, ep.c_is_bf16 ? 64 : 32, ep.c_is_bf16 != 0)) return 4;
     constexpr size_t smem = (size_t)STAGES * (BM * BK * 2 + BN * BK * 2) + 4 * 2 * 4096 + 1024 + 256;
     static bool configured = false;
     if (!configured) {
         if (cudaFuncSetAttribute(gemm_tn_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return 2;
         configured = true;
     }
-    const int tiles = ((N + BN - 1) / BN) * ((M + BM - 1) / BM);
+    const int tiles = tiles_mn * splits;
     const int grid = tiles < num_sms() ? tiles : num_sms();
     count_launch();
-    gemm_tn_kernel<BN, STAGES><<<grid, GEMM_THREADS, smem, s>>>(ma, mb, mc, M, N, K, ep, err);
+    gemm_tn_kernel<BN, STAGES><<<grid, GEMM_THREADS, smem, s>>>(ma, mb, mc, M, N, K, splits, ep, err);
+    if (splits > 1) {
+        count_launch();
+        gemm_splitk_reduce_kernel<<<(unsigned)(((int64_t)M * N + 255) / 256), 256, 0, s>>>(ws, splits, Mpad, ldw, M, N, ep_in, C, ldc);
+    }
     return cudaGetLastError() == cudaSuccess ? 0 : 3;
 }
 
@@ -312,13 +362,13 @@ int launch(const void* A, int lda, const void* B, int ldb, int M, int N, int K, 
 // Returns 0 on success.  `err` (device int, zeroed by the caller) becomes non-zero if a pipeline wait timed out.
 int gemm_bf16_tn(const void* A, int lda, const void* B, int ldb, int M, int N, int K, float alpha, float beta, const void* D, int ldd,
                  bool d_bf16, const void* bias, bool bias_bf16, float diag, int act, void* C, int ldc, bool c_bf16, void* C2, int ldc2,
-                 int* err, cudaStream_t s) {
+                 float* splitk_ws, int64_t splitk_ws_floats, int* err, cudaStream_t s) {
     if (M <= 0 || N <= 0 || K <= 0) return 0;
     Epilogue ep{alpha, beta, diag, D, ldd, d_bf16 ? 1 : 0, bias, bias_bf16 ? 1 : 0, act, c_bf16 ? 1 : 0, C2, ldc2};
     // the output goes through TMA: its base must be 16-byte aligned and its row pitch a multiple of 16 bytes
     if ((reinterpret_cast<uintptr_t>(C) & 15) != 0 || (ldc * (c_bf16 ? 2 : 4)) % 16 != 0) return 5;
-    if (N > 128) return launch<256, 4>(A, lda, B, ldb, M, N, K, ep, C, ldc, err, s);
-    return launch<128, 6>(A, lda, B, ldb, M, N, K, ep, C, ldc, err, s);
+    if (N > 128) return launch<256, 4>(A, lda, B, ldb, M, N, K, ep, C, ldc, splitk_ws, splitk_ws_floats, err, s);
+    return launch<128, 6>(A, lda, B, ldb, M, N, K, ep, C, ldc, splitk_ws, splitk_ws_floats, err, s);
 }
 
 }  // namespace sg

@@ -24,6 +24,18 @@ def _err_flag(dev) -> torch.Tensor:
     return t
 
 
+_ws: Dict[torch.device, torch.Tensor] = {}
+
+
+def _splitk_ws(dev) -> torch.Tensor:
+    """64 MB fp32 scratch for split-K partial tiles (used when the output has too few tiles to fill the GPU)."""
+    t = _ws.get(dev)
+    if t is None:
+        t = torch.empty(16 * 1024 * 1024, dtype=torch.float32, device=dev)
+        _ws[dev] = t
+    return t
+
+
 def check(dev=None) -> None:
     """Raise if a GEMM pipeline wait timed out since the last check (one device-to-host read)."""
     for d, t in _err.items():
@@ -43,7 +55,7 @@ def gemm_tn(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None
         q = 8 if out_dtype == torch.bfloat16 else 4          # the output is written by TMA: 16-byte row pitch
         npad = -(-n // q) * q
         out = torch.empty(a.shape[0], npad, dtype=out_dtype, device=a.device)[:, :n]
-    C.gemm_tn(a, b, out, alpha, beta, d, bias, diag, ACT[act], out_t, _err_flag(a.device))
+    C.gemm_tn(a, b, out, alpha, beta, d, bias, diag, ACT[act], out_t, _err_flag(a.device), _splitk_ws(a.device))
     return out
 
 

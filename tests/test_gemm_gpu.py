@@ -8,7 +8,7 @@ pytestmark = pytest.mark.gpu
 
 
 @pytest.mark.parametrize("M,N,K", [(128, 128, 64), (128, 256, 128), (256, 128, 512), (130, 70, 72), (1000, 520, 264), (64, 40, 8),
-                                   (4096, 512, 512), (300, 1000, 2048)])
+                                   (4096, 512, 512), (300, 1000, 2048), (512, 520, 32768), (136, 72, 8200)])
 def test_gemm_tn_matches_fp32_matmul(M, N, K):
     torch.manual_seed(M + N + K)
     a = torch.randn(M, K, device="cuda").to(torch.bfloat16)

@@ -19,7 +19,18 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
+import os
+
 from ..ops import nn_ops
+
+
+def _linear(x, weight, bias):
+    """nn.Linear forward.  With SG_LINEAR=tcgen05 (and bf16 CUDA tensors) the three GEMMs of the layer run on the
+    hand-written tcgen05 kernel instead of cuBLAS."""
+    if os.environ.get("SG_LINEAR", "cublas") == "tcgen05" and x.is_cuda and x.dtype == torch.bfloat16:
+        from ..ops import gemm
+        return gemm.linear(x, weight, bias)
+    return F.linear(x, weight, bias)
 
 
 class _Attn(nn.Module):
@@ -39,9 +50,9 @@ class _Attn(nn.Module):
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         B, S, D = x.shape
-        qkv = F.linear(x, self.in_proj_weight, self.in_proj_bias)
+        qkv = _linear(x, self.in_proj_weight, self.in_proj_bias)
         if self.fused and nn_ops.attention_small_supported(qkv, self.h):
-            return self.out_proj(nn_ops.attention_small(qkv, self.h, True))
+            return _linear(nn_ops.attention_small(qkv, self.h, True), self.out_proj.weight, self.out_proj.bias)
         qkv = qkv.view(B, S, 3, self.h, D // self.h)
         q, k, v = (qkv[:, :, i].transpose(1, 2) for i in range(3))
         o = F.scaled_dot_product_attention(q, k, v, is_causal=True)
@@ -58,7 +69,8 @@ class DecoderBlock(nn.Module):
     def forward(self, x):
         if x.is_cuda:                    # LayerNorm(x + sublayer) with the add fused into the normalisation kernel
             x = nn_ops.layer_norm(x, self.attn(x), self.n1.weight, self.n1.bias, self.n1.eps)
-            return nn_ops.layer_norm(x, self.ff(x), self.n2.weight, self.n2.bias, self.n2.eps)
+            h = F.gelu(_linear(x, self.ff[0].weight, self.ff[0].bias))
+            return nn_ops.layer_norm(x, _linear(h, self.ff[2].weight, self.ff[2].bias), self.n2.weight, self.n2.bias, self.n2.eps)
         x = self.n1(x + self.attn(x))
         return self.n2(x + self.ff(x))
 

@@ -206,6 +206,56 @@ def run_ours(args, rank, world, local):
     }
 
 
+# ------------------------------------------------------------------------------------------------ Muon on the Llama-style 1.3B model
+def run_llama_muon(args, rank, world, local):
+    """Secondary benchmark (``--config llama_muon``): Llama-style 1.3 B decoder, bf16, sequence 2048, global batch 256 sequences,
+    Muon (5 Newton-Schulz iterations on the tcgen05 GEMM) for the block matrices, AdamW for embedding / head / norms, ZeRO-sharded."""
+    import torch
+    from supergrok15_b200 import _build
+    from supergrok15_b200.models import LLAMA_1P3B, Llama, LlamaConfig
+    from supergrok15_b200.parallel import ZeroEngine
+    C = _build.require()
+    dev = torch.device("cuda", local)
+    torch.manual_seed(0)
+    cfg = LLAMA_1P3B if not args.small else LlamaConfig(n_layers=4, d_model=1024, n_heads=8, d_ff=2752, vocab=32000, max_seq=2048)
+    with torch.device(dev):
+        model = Llama(cfg).to(torch.bfloat16)
+    eng = ZeroEngine(model, "muon", dict(lr=0.02, momentum=0.95, weight_decay=0.01, adamw_lr=1e-3, adamw_names=("embed", "lm_head")),
+                     comm=args.comm, param_dtype=torch.bfloat16)
+    seq, gb = 2048, args.global_batch or 256
+    per_rank = gb // world
+    micro = max(1, per_rank // args.micro_seqs)
+    g = torch.Generator().manual_seed(100 + rank)
+    W, K = args.warmup, args.steps
+    host = [(torch.randint(0, cfg.vocab, (per_rank, seq), generator=g).pin_memory(),) for _ in range(W + K)]
+
+    def step(i):
+        ids = host[i][0].to(dev, non_blocking=True)
+        return eng.train_step(ids[:, :-1].contiguous(), ids[:, 1:].contiguous(), micro_batches=micro)
+    for i in range(W):
+        step(i)
+    eng.check()
+    l0 = C.launch_count()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    losses = []
+    ms = timed_loop(lambda i: losses.append(step(W + i)), K, world)
+    clocks = sampler.stop() if rank == 0 else None
+    eng.check()
+    tokens = gb * seq
+    n_params = sum(p.numel() for p in model.parameters())
+    return {"metric": "train tokens/s (max over ranks), Muon on Llama-style decoder", "value": tokens / (ms * 1e-3), "unit": "tokens/s",
+            "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic: uniform-random token ids; random-init weights",
+            "config": {"model": f"llama {cfg.n_layers}L d{cfg.d_model} h{cfg.n_heads} ff{cfg.d_ff} vocab{cfg.vocab} ({n_params / 1e9:.3f}B params)",
+                       "global_batch": gb, "seq_len": seq, "parallelism": f"zero2-dp{world}, tensor-granular Muon ownership",
+                       "micro_batches": micro, "l2": "inputs and weights far exceed the 126 MB L2"},
+            "clocks": clocks, "gpu_launches": C.launch_count() - l0, "final_loss": float(losses[-1]) if losses else None,
+            "model_flops_per_step": 6.0 * n_params * tokens, "impl": "ours",
+            "h2d_bytes_per_step": per_rank * seq * 8}
+
+
 # ------------------------------------------------------------------------------------------------ reference arm
 def run_reference(args, rank, world, local):
     """The unmodified reference: its own Transformer (grokking_race_v2.py:321-331), its own SuperGrok2 optimizer through
@@ -294,6 +344,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--comm", default=None, choices=[None, "p2p", "nvls", "nccl"])
+    ap.add_argument("--config", default="zero2_sg2", choices=["zero2_sg2", "llama_muon"])
+    ap.add_argument("--small", action="store_true", help="llama_muon: 4-layer d1024 model for quick checks")
+    ap.add_argument("--global-batch", type=int, default=0)
+    ap.add_argument("--micro-seqs", type=int, default=4, help="llama_muon: sequences per micro-batch")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     import torch
@@ -304,7 +358,11 @@ def main():
         raise SystemExit("bench.py needs a CUDA device")
     rank, world, local = dist_setup(args.gpus)
     try:
-        res = run_reference(args, rank, world, local) if args.impl == "reference" else run_ours(args, rank, world, local)
+        if args.config == "llama_muon":
+            res = ({"impl": "reference", "unavailable": "the reference ships no Llama model and no data-parallel Muon"} if args.impl == "reference"
+                   else run_llama_muon(args, rank, world, local))
+        else:
+            res = run_reference(args, rank, world, local) if args.impl == "reference" else run_ours(args, rank, world, local)
     except Exception as e:  # noqa: BLE001
         if args.impl == "reference":
             res = {"impl": "reference", "unavailable": f"reference run failed: {type(e).__name__}: {str(e)[:200]}"}

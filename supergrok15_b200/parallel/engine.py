@@ -58,7 +58,9 @@ class ZeroEngine:
         self.timeout_s = timeout_s
         self.criterion = criterion or F.cross_entropy
         self.model = model.to(param_dtype)
-        self.params = [p for p in self.model.parameters() if p.requires_grad]
+        named = [(n, p) for n, p in self.model.named_parameters() if p.requires_grad]
+        self.param_names = [n for n, _ in named]
+        self.params = [p for _, p in named]
         self.device = self.params[0].device
         self.cuda = self.device.type == "cuda"
         self.pdtype = param_dtype
@@ -138,9 +140,13 @@ class ZeroEngine:
                     self.opt._peer_push = (self.pbuf.peer_ptrs[self.rank], peers)
             self._fix_layer_schedules(own)
         elif self.name == "muon":
-            p2 = [mv for mv in self.master_views if mv.dim() == 2]
-            p1 = [mv for mv in self.master_views if mv.dim() != 2]
-            self.opt = cls(p2 or [torch.nn.Parameter(torch.zeros(1, 1, device=self.device))], p1, **kw)
+            # 2-D weights go to the Newton-Schulz group unless their name matches ``adamw_names`` (embeddings, output head)
+            kw = dict(kw)
+            skip = tuple(kw.pop("adamw_names", ()))
+            is_mat = [mv.dim() == 2 and not any(s_ in self.param_names[i] for s_ in skip) for mv, i in zip(self.master_views, own)]
+            p2 = [mv for mv, f in zip(self.master_views, is_mat) if f]
+            p1 = [mv for mv, f in zip(self.master_views, is_mat) if not f]
+            self.opt = cls(p2 or [torch.nn.Parameter(torch.zeros(8, 8, device=self.device))], p1, **kw)
         else:
             self.opt = cls(self.master_views or [torch.nn.Parameter(torch.zeros(0, device=self.device))], **kw)
             if hasattr(self.opt, "_flat_layer_beta1s"):
@@ -269,17 +275,26 @@ class ZeroEngine:
         self._barrier(2)                                              # every rank's parameters are complete
 
     # ------------------------------------------------------------------ the call a user makes
-    def train_step(self, x: torch.Tensor, y: torch.Tensor, **metrics) -> torch.Tensor:
-        """Host (pinned) or device batch in, loss tensor out: H2D copy, forward, backward, sharded fused step."""
+    def train_step(self, x: torch.Tensor, y: torch.Tensor, micro_batches: int = 1, **metrics) -> torch.Tensor:
+        """Host (pinned) or device batch in, loss tensor out: H2D copy, forward, backward, sharded fused step.
+        ``micro_batches`` > 1 splits the batch and accumulates gradients in the flat buffer (activation memory)."""
         if x.device != self.device:
             x = x.to(self.device, non_blocking=True)
             y = y.to(self.device, non_blocking=True)
         self.zero_grad()
-        logits = self.model(x)
-        loss = self.criterion(logits.float(), y)
-        loss.backward()
+        total = None
+        for xb, yb in zip(x.chunk(micro_batches), y.chunk(micro_batches)):
+            logits = self.model(xb)
+            if logits.dim() == 3:                                     # language modelling: one target per position
+                loss = self.criterion(logits.reshape(-1, logits.shape[-1]).float(), yb.reshape(-1))
+            else:
+                loss = self.criterion(logits.float(), yb)
+            if micro_batches > 1:
+                loss = loss / micro_batches
+            loss.backward()
+            total = loss.detach() if total is None else total + loss.detach()
         self.step(**metrics)
-        return loss.detach()
+        return total
 
     # ------------------------------------------------------------------ introspection
     def state_bytes(self) -> int:

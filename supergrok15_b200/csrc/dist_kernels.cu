@@ -111,16 +111,30 @@ struct FlatStep {
     float* master; float* m; float* v;      // local shard arrays (index 0 = element `off`)
 };
 
-template <int OP, typename G, typename T>
-__global__ void __launch_bounds__(256) fused_rs_step_ag_kernel(PeerPtrs grads, PeerPtrs params, int world, int rank, int64_t off, int64_t n,
-                                                               FlatStep st) {
+// NVLS = true: the gradient sum is ONE multimem.ld_reduce per 16 bytes on the multicast address (the NVSwitch adds the W copies, so
+// each rank receives its shard once instead of W-1 times) and the updated parameters leave as ONE multimem.st (the switch replicates).
+template <int OP, typename G, typename T, bool NVLS>
+__global__ void __launch_bounds__(256) fused_rs_step_ag_kernel(PeerPtrs grads, PeerPtrs params, const void* mc_grad, void* mc_param,
+                                                               int world, int rank, int64_t off, int64_t n, FlatStep st) {
     constexpr int N = 8;
     const int64_t nv = n / N;
     for (int64_t v = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v < nv; v += (int64_t)gridDim.x * blockDim.x) {
         float g[N];
 #pragma unroll
         for (int k = 0; k < N; ++k) g[k] = 0.f;
-        for (int kk = 0; kk < world; ++kk) {
+        if (NVLS) {
+            const char* a = reinterpret_cast<const char*>(mc_grad) + (off + v * N) * sizeof(G);
+            if constexpr (sizeof(G) == 2) {
+                const uint4 t = multimem_ld_reduce_bf16x8(a);
+                const G* h = reinterpret_cast<const G*>(&t);
+#pragma unroll
+                for (int k = 0; k < N; ++k) g[k] = Cvt<G>::to(h[k]);
+            } else {
+                const float4 t0 = multimem_ld_reduce_f32x4(a), t1 = multimem_ld_reduce_f32x4(a + 16);
+                g[0] = t0.x; g[1] = t0.y; g[2] = t0.z; g[3] = t0.w; g[4] = t1.x; g[5] = t1.y; g[6] = t1.z; g[7] = t1.w;
+            }
+        }
+        for (int kk = 0; kk < (NVLS ? 0 : world); ++kk) {
             const int r = (rank + kk) % world;
             const G* src = reinterpret_cast<const G*>(grads.p[r]) + off + v * N;
             if constexpr (sizeof(G) == 2) {
@@ -162,7 +176,19 @@ __global__ void __launch_bounds__(256) fused_rs_step_ag_kernel(PeerPtrs grads, P
             if (OP == 0) reinterpret_cast<float4*>(st.v + i0)[q] = make_float4(vv[4 * q], vv[4 * q + 1], vv[4 * q + 2], vv[4 * q + 3]);
         }
         // all-gather: the updated low-precision parameters go straight to every rank's buffer
-        if constexpr (sizeof(T) == 2) {
+        if (NVLS) {
+            char* d = reinterpret_cast<char*>(mc_param) + (off + i0) * sizeof(T);
+            if constexpr (sizeof(T) == 2) {
+                uint4 o;
+                T* h = reinterpret_cast<T*>(&o);
+#pragma unroll
+                for (int k = 0; k < N; ++k) h[k] = Cvt<T>::from(p[k]);
+                multimem_st_u32x4(d, o);
+            } else {
+                multimem_st_u32x4(d, make_uint4(__float_as_uint(p[0]), __float_as_uint(p[1]), __float_as_uint(p[2]), __float_as_uint(p[3])));
+                multimem_st_u32x4(d + 16, make_uint4(__float_as_uint(p[4]), __float_as_uint(p[5]), __float_as_uint(p[6]), __float_as_uint(p[7])));
+            }
+        } else if constexpr (sizeof(T) == 2) {
             uint4 o;
             T* h = reinterpret_cast<T*>(&o);
 #pragma unroll
@@ -261,20 +287,21 @@ void dist_push(bool nvls, const PeerPtrs& params, void* mc, int world, int rank,
     else push_kernel<false><<<g, 256, 0, s>>>(params, mc, world, rank, off_bytes, n_bytes);
 }
 
-void dist_fused_flat_step(int op, int gdtype, int pdtype, const PeerPtrs& grads, const PeerPtrs& params, int world, int rank, int64_t off,
-                          int64_t n, float lr, float beta1, float beta2, float eps, float wd, float bc1, float bc2, float gscale,
+void dist_fused_flat_step(int op, int gdtype, int pdtype, bool nvls, const PeerPtrs& grads, const PeerPtrs& params, const void* mc_grad,
+                          void* mc_param, int world, int rank, int64_t off, int64_t n, float lr, float beta1, float beta2, float eps, float wd, float bc1, float bc2, float gscale,
                           float* master, float* m, float* v, cudaStream_t s) {
     if (n <= 0) return;
     count_launch();
     FlatStep st{lr, beta1, beta2, eps, wd, bc1, bc2, gscale, master, m, v};
     const int g = grid_for(n / 8);
-#define L2(OPV, G, T) fused_rs_step_ag_kernel<OPV, G, T><<<g, 256, 0, s>>>(grads, params, world, rank, off, n, st)
+#define L2(OPV, G, T) \
+    if (nvls) fused_rs_step_ag_kernel<OPV, G, T, true><<<g, 256, 0, s>>>(grads, params, mc_grad, mc_param, world, rank, off, n, st); \
+    else fused_rs_step_ag_kernel<OPV, G, T, false><<<g, 256, 0, s>>>(grads, params, mc_grad, mc_param, world, rank, off, n, st)
 #define L1(OPV) \
-    if (gdtype == BF16 && pdtype == BF16) L2(OPV, __nv_bfloat16, __nv_bfloat16); \
-    else if (gdtype == F32 && pdtype == BF16) L2(OPV, float, __nv_bfloat16); \
-    else if (gdtype == F32 && pdtype == F32) L2(OPV, float, float); \
-    else if (gdtype == F16 && pdtype == F16) L2(OPV, __half, __half); \
-    else L2(OPV, __nv_bfloat16, float);
+    if (gdtype == BF16 && pdtype == BF16) { L2(OPV, __nv_bfloat16, __nv_bfloat16); } \
+    else if (gdtype == F32 && pdtype == BF16) { L2(OPV, float, __nv_bfloat16); } \
+    else if (gdtype == F32 && pdtype == F32) { L2(OPV, float, float); } \
+    else { L2(OPV, __nv_bfloat16, float); }
     if (op == 0) { L1(0) } else { L1(1) }
 #undef L1
 #undef L2

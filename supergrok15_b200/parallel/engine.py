@@ -94,6 +94,11 @@ class ZeroEngine:
         self.slots = symm.alloc(self.slots_n * max(self.world, 1), torch.float32, self.device, group)
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.epoch = 0
+        # NVLS (in-switch reduction / replication through the multicast mapping) needs multicast addresses for both buffers
+        self.nvls = self.comm == "nvls" and self.world > 1 and self.gbuf.multicast_ptr != 0 and self.pbuf.multicast_ptr != 0
+        if self.comm == "nvls" and self.world > 1 and not self.nvls:
+            import warnings
+            warnings.warn("comm='nvls' requested but no multicast address is available; using plain peer loads / stores")
         # ---- owner state
         n_own = self.my_end - self.my_begin
         self.master = self.pbuf.tensor[self.my_begin:self.my_end].float().clone()          # fp32 master shard
@@ -215,15 +220,17 @@ class ZeroEngine:
             f = [self.hp["lr"], b1, b2, self.hp["eps"], self.hp["weight_decay"], 1 - b1 ** self.steps, 1 - b2 ** self.steps,
                  1.0 / W]
             if n_own:
+                nvls = self.nvls
                 C.dist_fused_flat_step(FLAT_OPTIMIZERS[self.name], _DT[self.pdtype], _DT[self.pdtype], self.gbuf.peer_ptrs,
-                                       self.pbuf.peer_ptrs, r, self.my_begin, n_own, f, self.master, self.m, self.v)
+                                       self.pbuf.peer_ptrs, r, self.my_begin, n_own, f, self.master, self.m, self.v, nvls,
+                                       self.gbuf.multicast_ptr if nvls else 0, self.pbuf.multicast_ptr if nvls else 0)
                 self.launches += 1
             self._barrier(2)
             return
         # ---- reduce-scatter
         if fused:
             if n_own:
-                C.dist_pull_reduce(_DT[self.pdtype], self.comm == "nvls" and self.gbuf.multicast_ptr != 0, self.gbuf.peer_ptrs,
+                C.dist_pull_reduce(_DT[self.pdtype], self.nvls, self.gbuf.peer_ptrs,
                                    self.gbuf.multicast_ptr, r, self.my_begin, n_own, 1.0 / W, self.gred)
                 self.launches += 1
         else:
@@ -261,7 +268,13 @@ class ZeroEngine:
             finally:
                 ew.set_cross_rank_reducer(None)
             if n_own:
-                if fused:
+                if fused and self.nvls:
+                    # cast into the local buffer, then one multimem.st per 16 bytes replicates it through the switch
+                    self.pbuf.tensor[self.my_begin:self.my_end].copy_(self.master[:n_own])
+                    es = self.pbuf.tensor.element_size()
+                    C.dist_push(True, self.pbuf.peer_ptrs, self.pbuf.multicast_ptr, r, self.my_begin * es, n_own * es, self.pbuf.tensor)
+                    self.launches += 1
+                elif fused:
                     C.dist_cast_push(_DT[self.pdtype], self.pbuf.peer_ptrs, r, self.my_begin, n_own, self.master)
                     self.launches += 1
                 else:

@@ -71,7 +71,7 @@ def test_sharded_equals_unsharded_cpu_gloo(optimizer):
 
 @pytest.mark.gpu
 @pytest.mark.dist
-@pytest.mark.parametrize("comm", ["p2p", "nccl"])
+@pytest.mark.parametrize("comm", ["p2p", "nccl", "nvls"])
 @pytest.mark.parametrize("optimizer", ["supergrok2", "adamw", "grokadamw"])
 def test_sharded_equals_unsharded_gpu(optimizer, comm):
     if torch.cuda.device_count() < 2:

@@ -41,45 +41,6 @@ __device__ __forceinline__ void acc_vec(const uint4& v, float (&acc)[N]) {
     for (int k = 0; k < N; ++k) acc[k] += Cvt<T>::to(h[k]);
 }
 
-// ---- reduce-scatter pull: out[i] = scale * sum_r grad_r[off + i], i in [0, n) ----
-// grads.p[r] is rank r's gradient buffer (same layout everywhere).  n and off are multiples of 16 bytes / sizeof(T).
-template <typename T, bool NVLS>
-__global__ void __launch_bounds__(256) pull_reduce_kernel(PeerPtrs grads, const void* mc_grad, int world, int rank, int64_t off, int64_t n,
-                                                          float scale, float* __restrict__ out) {
-    constexpr int N = Vec8<T>::N;
-    const int64_t nv = n / N;
-    for (int64_t v = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v < nv; v += (int64_t)gridDim.x * blockDim.x) {
-        float acc[N];
-#pragma unroll
-        for (int k = 0; k < N; ++k) acc[k] = 0.f;
-        if (NVLS) {
-            const char* a = reinterpret_cast<const char*>(mc_grad) + (off + v * N) * sizeof(T);
-            if constexpr (sizeof(T) == 4) {
-                const float4 t = multimem_ld_reduce_f32x4(a);
-                acc[0] = t.x; acc[1] = t.y; acc[2] = t.z; acc[3] = t.w;
-            } else {
-                const uint4 t = multimem_ld_reduce_bf16x8(a);
-                acc_vec<T, N>(t, acc);
-            }
-        } else {
-            // start with a different peer on every rank so the 8 ranks do not all hit the same GPU at once
-            for (int k = 0; k < world; ++k) {
-                const int r = (rank + k) % world;
-                const uint4 t = *reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(grads.p[r]) + off + v * N);
-                acc_vec<T, N>(t, acc);
-            }
-        }
-#pragma unroll
-        for (int k = 0; k < N; ++k) out[v * N + k] = acc[k] * scale;
-    }
-    // tail (n not a multiple of the vector width): scalar
-    for (int64_t i = nv * N + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
-        float a = 0.f;
-        for (int r = 0; r < world; ++r) a += Cvt<T>::to(reinterpret_cast<const T*>(grads.p[r])[off + i]);
-        out[i] = a * scale;
-    }
-}
-
 // ---- all-gather push: copy [off, off+n) of the local parameter buffer into every peer's buffer ----
 template <bool NVLS>
 __global__ void __launch_bounds__(256) push_kernel(PeerPtrs params, void* mc_param, int world, int rank, int64_t off_bytes, int64_t n_bytes) {
@@ -111,100 +72,158 @@ struct FlatStep {
     float* master; float* m; float* v;      // local shard arrays (index 0 = element `off`)
 };
 
-// NVLS = true: the gradient sum is ONE multimem.ld_reduce per 16 bytes on the multicast address (the NVSwitch adds the W copies, so
-// each rank receives its shard once instead of W-1 times) and the updated parameters leave as ONE multimem.st (the switch replicates).
-template <int OP, typename G, typename T, bool NVLS>
+// Gradient fetch for one 8-element vector.  P2P: all W peer loads are issued before any of them is consumed (W is a compile-time
+// constant so the loop unrolls; with a runtime trip count the first add would stall the warp and serialise the remote loads).
+// NVLS: ONE multimem.ld_reduce per 16 bytes on the multicast address - the NVSwitch adds the W copies, so each rank receives its
+// shard once instead of W-1 times.
+template <typename G, bool NVLS, int W>
+__device__ __forceinline__ void fetch_grad8(const PeerPtrs& grads, const void* mc_grad, int world, int rank, int64_t elem, float (&g)[8]) {
+    constexpr int Q = sizeof(G) == 2 ? 1 : 2;                         // 16-byte pieces per 8 elements
+    if (NVLS) {
+        const char* a = reinterpret_cast<const char*>(mc_grad) + elem * sizeof(G);
+        if constexpr (sizeof(G) == 2) {
+            const uint4 t = multimem_ld_reduce_bf16x8(a);
+            const G* h = reinterpret_cast<const G*>(&t);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) g[k] = Cvt<G>::to(h[k]);
+        } else {
+            const float4 t0 = multimem_ld_reduce_f32x4(a), t1 = multimem_ld_reduce_f32x4(a + 16);
+            g[0] = t0.x; g[1] = t0.y; g[2] = t0.z; g[3] = t0.w; g[4] = t1.x; g[5] = t1.y; g[6] = t1.z; g[7] = t1.w;
+        }
+        return;
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) g[k] = 0.f;
+    if constexpr (W > 0) {
+        uint4 raw[W][Q];
+#pragma unroll
+        for (int kk = 0; kk < W; ++kk) {
+            const int r = (rank + kk) % W;                            // a different first peer on every rank
+            const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const G*>(grads.p[r]) + elem);
+#pragma unroll
+            for (int q = 0; q < Q; ++q) raw[kk][q] = src[q];
+        }
+#pragma unroll
+        for (int kk = 0; kk < W; ++kk) {
+            const G* h = reinterpret_cast<const G*>(&raw[kk][0]);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) g[k] += Cvt<G>::to(h[k]);
+        }
+    } else {
+        for (int kk = 0; kk < world; ++kk) {
+            const int r = (rank + kk) % world;
+            const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const G*>(grads.p[r]) + elem);
+            uint4 raw[Q];
+#pragma unroll
+            for (int q = 0; q < Q; ++q) raw[q] = src[q];
+            const G* h = reinterpret_cast<const G*>(&raw[0]);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) g[k] += Cvt<G>::to(h[k]);
+        }
+    }
+}
+
+// Fused reduce-scatter + optimizer step + all-gather over the flat shard [off, off+n).  U vectors are fetched before the first is
+// consumed (memory-level parallelism for the long-latency multimem loads).  NVLS: the updated parameters leave as ONE multimem.st
+// per 16 bytes (the switch replicates them to every rank).
+template <int OP, typename G, typename T, bool NVLS, int W>
 __global__ void __launch_bounds__(256) fused_rs_step_ag_kernel(PeerPtrs grads, PeerPtrs params, const void* mc_grad, void* mc_param,
                                                                int world, int rank, int64_t off, int64_t n, FlatStep st) {
     constexpr int N = 8;
+    constexpr int U = NVLS ? 4 : 1;
     const int64_t nv = n / N;
-    for (int64_t v = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v < nv; v += (int64_t)gridDim.x * blockDim.x) {
-        float g[N];
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t v0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v0 < nv; v0 += stride * U) {
+        float gg[U][N];
 #pragma unroll
-        for (int k = 0; k < N; ++k) g[k] = 0.f;
-        if (NVLS) {
-            const char* a = reinterpret_cast<const char*>(mc_grad) + (off + v * N) * sizeof(G);
-            if constexpr (sizeof(G) == 2) {
-                const uint4 t = multimem_ld_reduce_bf16x8(a);
-                const G* h = reinterpret_cast<const G*>(&t);
-#pragma unroll
-                for (int k = 0; k < N; ++k) g[k] = Cvt<G>::to(h[k]);
-            } else {
-                const float4 t0 = multimem_ld_reduce_f32x4(a), t1 = multimem_ld_reduce_f32x4(a + 16);
-                g[0] = t0.x; g[1] = t0.y; g[2] = t0.z; g[3] = t0.w; g[4] = t1.x; g[5] = t1.y; g[6] = t1.z; g[7] = t1.w;
-            }
+        for (int u = 0; u < U; ++u) {
+            const int64_t v = v0 + u * stride;
+            if (v < nv) fetch_grad8<G, NVLS, W>(grads, mc_grad, world, rank, off + v * N, gg[u]);
         }
-        for (int kk = 0; kk < (NVLS ? 0 : world); ++kk) {
-            const int r = (rank + kk) % world;
-            const G* src = reinterpret_cast<const G*>(grads.p[r]) + off + v * N;
-            if constexpr (sizeof(G) == 2) {
-                const uint4 t = *reinterpret_cast<const uint4*>(src);
-                const G* h = reinterpret_cast<const G*>(&t);
 #pragma unroll
-                for (int k = 0; k < N; ++k) g[k] += Cvt<G>::to(h[k]);
+        for (int u = 0; u < U; ++u) {
+            const int64_t v = v0 + u * stride;
+            if (v >= nv) break;
+            float (&g)[N] = gg[u];
+            float p[N], mm[N], vv[N];
+            const int64_t i0 = v * N;
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+                const float4 a = reinterpret_cast<const float4*>(st.master + i0)[q];
+                p[4 * q] = a.x; p[4 * q + 1] = a.y; p[4 * q + 2] = a.z; p[4 * q + 3] = a.w;
+                const float4 b = reinterpret_cast<const float4*>(st.m + i0)[q];
+                mm[4 * q] = b.x; mm[4 * q + 1] = b.y; mm[4 * q + 2] = b.z; mm[4 * q + 3] = b.w;
+                if (OP == 0) {
+                    const float4 c = reinterpret_cast<const float4*>(st.v + i0)[q];
+                    vv[4 * q] = c.x; vv[4 * q + 1] = c.y; vv[4 * q + 2] = c.z; vv[4 * q + 3] = c.w;
+                }
+            }
+#pragma unroll
+            for (int k = 0; k < N; ++k) {
+                const float gs = g[k] * st.gscale;
+                if (OP == 0) p[k] = adam_update(p[k], gs, mm[k], vv[k], st.lr, st.beta1, st.beta2, st.eps, st.wd, st.bc1, st.bc2);
+                else         p[k] = lion_update(p[k], gs, mm[k], st.lr, st.beta1, st.beta2, st.wd);
+            }
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+                reinterpret_cast<float4*>(st.master + i0)[q] = make_float4(p[4 * q], p[4 * q + 1], p[4 * q + 2], p[4 * q + 3]);
+                reinterpret_cast<float4*>(st.m + i0)[q] = make_float4(mm[4 * q], mm[4 * q + 1], mm[4 * q + 2], mm[4 * q + 3]);
+                if (OP == 0) reinterpret_cast<float4*>(st.v + i0)[q] = make_float4(vv[4 * q], vv[4 * q + 1], vv[4 * q + 2], vv[4 * q + 3]);
+            }
+            // all-gather: the updated low-precision parameters go straight to every rank's buffer
+            uint4 o[2];
+            constexpr int QO = sizeof(T) == 2 ? 1 : 2;
+            if constexpr (sizeof(T) == 2) {
+                T* h = reinterpret_cast<T*>(&o[0]);
+#pragma unroll
+                for (int k = 0; k < N; ++k) h[k] = Cvt<T>::from(p[k]);
             } else {
+                o[0] = make_uint4(__float_as_uint(p[0]), __float_as_uint(p[1]), __float_as_uint(p[2]), __float_as_uint(p[3]));
+                o[1] = make_uint4(__float_as_uint(p[4]), __float_as_uint(p[5]), __float_as_uint(p[6]), __float_as_uint(p[7]));
+            }
+            if (NVLS) {
+                char* d = reinterpret_cast<char*>(mc_param) + (off + i0) * sizeof(T);
 #pragma unroll
-                for (int q = 0; q < 2; ++q) {
-                    const float4 t = reinterpret_cast<const float4*>(src)[q];
-                    g[4 * q] += t.x; g[4 * q + 1] += t.y; g[4 * q + 2] += t.z; g[4 * q + 3] += t.w;
+                for (int q = 0; q < QO; ++q) multimem_st_u32x4(d + 16 * q, o[q]);
+            } else {
+                for (int kk = 0; kk < world; ++kk) {
+                    const int r = (rank + kk) % world;
+                    uint4* d = reinterpret_cast<uint4*>(reinterpret_cast<T*>(params.p[r]) + off + i0);
+#pragma unroll
+                    for (int q = 0; q < QO; ++q) d[q] = o[q];
                 }
             }
         }
-        float p[N], mm[N], vv[N];
-        const int64_t i0 = v * N;
+    }
+}
+
+// ---- reduce-scatter pull: out[i] = scale * sum_r grad_r[off + i], i in [0, n) ----
+// grads.p[r] is rank r's gradient buffer (same layout everywhere).  off is a multiple of 8 elements.
+template <typename T, bool NVLS, int W>
+__global__ void __launch_bounds__(256) pull_reduce_kernel(PeerPtrs grads, const void* mc_grad, int world, int rank, int64_t off, int64_t n,
+                                                          float scale, float* __restrict__ out) {
+    constexpr int U = NVLS ? 4 : 1;
+    const int64_t nv = n / 8;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t v0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v0 < nv; v0 += stride * U) {
+        float g[U][8];
 #pragma unroll
-        for (int q = 0; q < 2; ++q) {
-            const float4 a = reinterpret_cast<const float4*>(st.master + i0)[q];
-            p[4 * q] = a.x; p[4 * q + 1] = a.y; p[4 * q + 2] = a.z; p[4 * q + 3] = a.w;
-            const float4 b = reinterpret_cast<const float4*>(st.m + i0)[q];
-            mm[4 * q] = b.x; mm[4 * q + 1] = b.y; mm[4 * q + 2] = b.z; mm[4 * q + 3] = b.w;
-            if (OP == 0) {
-                const float4 c = reinterpret_cast<const float4*>(st.v + i0)[q];
-                vv[4 * q] = c.x; vv[4 * q + 1] = c.y; vv[4 * q + 2] = c.z; vv[4 * q + 3] = c.w;
-            }
+        for (int u = 0; u < U; ++u)
+            if (v0 + u * stride < nv) fetch_grad8<T, NVLS, W>(grads, mc_grad, world, rank, off + (v0 + u * stride) * 8, g[u]);
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int64_t v = v0 + u * stride;
+            if (v >= nv) break;
+            float4* o = reinterpret_cast<float4*>(out + v * 8);
+            o[0] = make_float4(g[u][0] * scale, g[u][1] * scale, g[u][2] * scale, g[u][3] * scale);
+            o[1] = make_float4(g[u][4] * scale, g[u][5] * scale, g[u][6] * scale, g[u][7] * scale);
         }
-#pragma unroll
-        for (int k = 0; k < N; ++k) {
-            const float gg = g[k] * st.gscale;
-            if (OP == 0) p[k] = adam_update(p[k], gg, mm[k], vv[k], st.lr, st.beta1, st.beta2, st.eps, st.wd, st.bc1, st.bc2);
-            else         p[k] = lion_update(p[k], gg, mm[k], st.lr, st.beta1, st.beta2, st.wd);
-        }
-#pragma unroll
-        for (int q = 0; q < 2; ++q) {
-            reinterpret_cast<float4*>(st.master + i0)[q] = make_float4(p[4 * q], p[4 * q + 1], p[4 * q + 2], p[4 * q + 3]);
-            reinterpret_cast<float4*>(st.m + i0)[q] = make_float4(mm[4 * q], mm[4 * q + 1], mm[4 * q + 2], mm[4 * q + 3]);
-            if (OP == 0) reinterpret_cast<float4*>(st.v + i0)[q] = make_float4(vv[4 * q], vv[4 * q + 1], vv[4 * q + 2], vv[4 * q + 3]);
-        }
-        // all-gather: the updated low-precision parameters go straight to every rank's buffer
-        if (NVLS) {
-            char* d = reinterpret_cast<char*>(mc_param) + (off + i0) * sizeof(T);
-            if constexpr (sizeof(T) == 2) {
-                uint4 o;
-                T* h = reinterpret_cast<T*>(&o);
-#pragma unroll
-                for (int k = 0; k < N; ++k) h[k] = Cvt<T>::from(p[k]);
-                multimem_st_u32x4(d, o);
-            } else {
-                multimem_st_u32x4(d, make_uint4(__float_as_uint(p[0]), __float_as_uint(p[1]), __float_as_uint(p[2]), __float_as_uint(p[3])));
-                multimem_st_u32x4(d + 16, make_uint4(__float_as_uint(p[4]), __float_as_uint(p[5]), __float_as_uint(p[6]), __float_as_uint(p[7])));
-            }
-        } else if constexpr (sizeof(T) == 2) {
-            uint4 o;
-            T* h = reinterpret_cast<T*>(&o);
-#pragma unroll
-            for (int k = 0; k < N; ++k) h[k] = Cvt<T>::from(p[k]);
-            for (int kk = 0; kk < world; ++kk) {
-                const int r = (rank + kk) % world;
-                *reinterpret_cast<uint4*>(reinterpret_cast<T*>(params.p[r]) + off + i0) = o;
-            }
-        } else {
-            for (int kk = 0; kk < world; ++kk) {
-                const int r = (rank + kk) % world;
-                float4* d = reinterpret_cast<float4*>(reinterpret_cast<float*>(params.p[r]) + off + i0);
-                d[0] = make_float4(p[0], p[1], p[2], p[3]);
-                d[1] = make_float4(p[4], p[5], p[6], p[7]);
-            }
-        }
+    }
+    // tail (n not a multiple of 8): scalar peer loads
+    for (int64_t i = nv * 8 + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        float a = 0.f;
+        for (int r = 0; r < world; ++r) a += Cvt<T>::to(reinterpret_cast<const T*>(grads.p[r])[off + i]);
+        out[i] = a * scale;
     }
 }
 
@@ -271,10 +290,13 @@ void dist_pull_reduce(int dtype, bool nvls, const PeerPtrs& grads, const void* m
                       float* out, cudaStream_t s) {
     if (n <= 0) return;
     count_launch();
-    const int g = grid_for(n / 4);
+    const int g = grid_for(n / 8);
 #define LAUNCH(T) \
-    if (nvls) pull_reduce_kernel<T, true><<<g, 256, 0, s>>>(grads, mc, world, rank, off, n, scale, out); \
-    else pull_reduce_kernel<T, false><<<g, 256, 0, s>>>(grads, mc, world, rank, off, n, scale, out);
+    if (nvls) pull_reduce_kernel<T, true, 0><<<g, 256, 0, s>>>(grads, mc, world, rank, off, n, scale, out); \
+    else if (world == 8) pull_reduce_kernel<T, false, 8><<<g, 256, 0, s>>>(grads, mc, world, rank, off, n, scale, out); \
+    else if (world == 4) pull_reduce_kernel<T, false, 4><<<g, 256, 0, s>>>(grads, mc, world, rank, off, n, scale, out); \
+    else if (world == 2) pull_reduce_kernel<T, false, 2><<<g, 256, 0, s>>>(grads, mc, world, rank, off, n, scale, out); \
+    else pull_reduce_kernel<T, false, 0><<<g, 256, 0, s>>>(grads, mc, world, rank, off, n, scale, out);
     switch (dtype) { case F32: LAUNCH(float) break; case BF16: LAUNCH(__nv_bfloat16) break; default: LAUNCH(__half) break; }
 #undef LAUNCH
 }
@@ -294,9 +316,13 @@ void dist_fused_flat_step(int op, int gdtype, int pdtype, bool nvls, const PeerP
     count_launch();
     FlatStep st{lr, beta1, beta2, eps, wd, bc1, bc2, gscale, master, m, v};
     const int g = grid_for(n / 8);
+#define L3(OPV, G, T, NV, WW) fused_rs_step_ag_kernel<OPV, G, T, NV, WW><<<g, 256, 0, s>>>(grads, params, mc_grad, mc_param, world, rank, off, n, st)
 #define L2(OPV, G, T) \
-    if (nvls) fused_rs_step_ag_kernel<OPV, G, T, true><<<g, 256, 0, s>>>(grads, params, mc_grad, mc_param, world, rank, off, n, st); \
-    else fused_rs_step_ag_kernel<OPV, G, T, false><<<g, 256, 0, s>>>(grads, params, mc_grad, mc_param, world, rank, off, n, st)
+    if (nvls) L3(OPV, G, T, true, 0); \
+    else if (world == 8) L3(OPV, G, T, false, 8); \
+    else if (world == 4) L3(OPV, G, T, false, 4); \
+    else if (world == 2) L3(OPV, G, T, false, 2); \
+    else L3(OPV, G, T, false, 0)
 #define L1(OPV) \
     if (gdtype == BF16 && pdtype == BF16) { L2(OPV, __nv_bfloat16, __nv_bfloat16); } \
     else if (gdtype == F32 && pdtype == BF16) { L2(OPV, float, __nv_bfloat16); } \
@@ -305,6 +331,7 @@ void dist_fused_flat_step(int op, int gdtype, int pdtype, bool nvls, const PeerP
     if (op == 0) { L1(0) } else { L1(1) }
 #undef L1
 #undef L2
+#undef L3
 }
 
 void dist_cast_push(int pdtype, const PeerPtrs& params, int world, int rank, int64_t off, int64_t n, const float* master, cudaStream_t s) {

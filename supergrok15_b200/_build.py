@@ -113,7 +113,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     if jobs or not so.exists():
         tlib = Path(torch.__file__).parent / "lib"
         cmd = ["g++", "-shared", "-o", str(so), *map(str, objs), f"-L{tlib}", f"-L{cuda_home}/lib64", "-lc10",
-               "-ltorch_cpu", "-ltorch", "-ltorch_python", "-lc10_cuda", "-ltorch_cuda", "-lcudart", "-lcuda",
+               "-ltorch_cpu", "-ltorch", "-ltorch_python", "-lc10_cuda", "-ltorch_cuda", "-lcudart",
                f"-Wl,-rpath,{tlib}", f"-Wl,-rpath,{cuda_home}/lib64"]
         _run(cmd)
     return so

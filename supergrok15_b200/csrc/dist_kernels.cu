@@ -11,6 +11,7 @@
 //
 // Cross-GPU ordering uses epoch flags in a signal pad with st.release.sys / ld.acquire.sys; waits are bounded.
 #include "sg_native.h"
+#include <cstdlib>
 #include "comm.cuh"
 #include "optim_math.cuh"
 
@@ -72,92 +73,118 @@ struct FlatStep {
     float* master; float* m; float* v;      // local shard arrays (index 0 = element `off`)
 };
 
-// Gradient fetch for one 8-element vector.  P2P: all W peer loads are issued before any of them is consumed (W is a compile-time
-// constant so the loop unrolls; with a runtime trip count the first add would stall the warp and serialise the remote loads).
-// NVLS: ONE multimem.ld_reduce per 16 bytes on the multicast address - the NVSwitch adds the W copies, so each rank receives its
-// shard once instead of W-1 times.
-template <typename G, bool NVLS, int W>
-__device__ __forceinline__ void fetch_grad8(const PeerPtrs& grads, const void* mc_grad, int world, int rank, int64_t elem, float (&g)[8]) {
-    constexpr int Q = sizeof(G) == 2 ? 1 : 2;                         // 16-byte pieces per 8 elements
-    if (NVLS) {
+// Remote accesses are ONE 16-byte (or 8-byte) access per lane with the lanes of a warp contiguous: a vector is 8 elements when
+// both buffers hold 16-bit values and 4 elements as soon as one of them is fp32.  (Two 16-byte accesses per lane at a 32-byte
+// stride touch every 32-byte sector twice with half of it; over NVLink that halves the useful bandwidth - measured.)
+template <typename T, int N>
+__device__ __forceinline__ void vload(const T* p, float (&v)[N]) {
+    if constexpr (sizeof(T) * N == 16) {
+        const uint4 t = *reinterpret_cast<const uint4*>(p);
+        const T* h = reinterpret_cast<const T*>(&t);
+#pragma unroll
+        for (int k = 0; k < N; ++k) v[k] = Cvt<T>::to(h[k]);
+    } else {
+        static_assert(sizeof(T) * N == 8, "vector of 8 or 16 bytes");
+        const uint2 t = *reinterpret_cast<const uint2*>(p);
+        const T* h = reinterpret_cast<const T*>(&t);
+#pragma unroll
+        for (int k = 0; k < N; ++k) v[k] = Cvt<T>::to(h[k]);
+    }
+}
+template <typename T, int N>
+__device__ __forceinline__ void vpack(const float (&v)[N], uint4& o) {
+    T* h = reinterpret_cast<T*>(&o);
+#pragma unroll
+    for (int k = 0; k < N; ++k) h[k] = Cvt<T>::from(v[k]);
+}
+template <typename T, int N>
+__device__ __forceinline__ void vstore_packed(T* p, const uint4& o) {
+    if constexpr (sizeof(T) * N == 16) *reinterpret_cast<uint4*>(p) = o;
+    else *reinterpret_cast<uint2*>(p) = make_uint2(o.x, o.y);
+}
+
+// Gradient fetch for one vector.  P2P: all W peer loads are issued before any of them is consumed (W is a compile-time constant so
+// the loop unrolls; with a runtime trip count the first add would stall the warp and serialise the remote loads).
+// NVLS: ONE multimem.ld_reduce per 16 bytes on the multicast address - the NVSwitch adds the W copies.
+template <typename G, int N, bool NVLS, int W>
+__device__ __forceinline__ void fetch_grad(const PeerPtrs& grads, const void* mc_grad, int world, int rank, int64_t elem, float (&g)[N]) {
+    if constexpr (NVLS && sizeof(G) * N == 16) {
         const char* a = reinterpret_cast<const char*>(mc_grad) + elem * sizeof(G);
         if constexpr (sizeof(G) == 2) {
             const uint4 t = multimem_ld_reduce_bf16x8(a);
             const G* h = reinterpret_cast<const G*>(&t);
 #pragma unroll
-            for (int k = 0; k < 8; ++k) g[k] = Cvt<G>::to(h[k]);
+            for (int k = 0; k < N; ++k) g[k] = Cvt<G>::to(h[k]);
         } else {
-            const float4 t0 = multimem_ld_reduce_f32x4(a), t1 = multimem_ld_reduce_f32x4(a + 16);
-            g[0] = t0.x; g[1] = t0.y; g[2] = t0.z; g[3] = t0.w; g[4] = t1.x; g[5] = t1.y; g[6] = t1.z; g[7] = t1.w;
+            const float4 t0 = multimem_ld_reduce_f32x4(a);
+            g[0] = t0.x; g[1] = t0.y; g[2] = t0.z; g[3] = t0.w;
         }
         return;
     }
 #pragma unroll
-    for (int k = 0; k < 8; ++k) g[k] = 0.f;
+    for (int k = 0; k < N; ++k) g[k] = 0.f;
     if constexpr (W > 0) {
-        uint4 raw[W][Q];
+        float raw[W][N];
 #pragma unroll
-        for (int kk = 0; kk < W; ++kk) {
-            const int r = (rank + kk) % W;                            // a different first peer on every rank
-            const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const G*>(grads.p[r]) + elem);
+        for (int kk = 0; kk < W; ++kk) vload<G, N>(reinterpret_cast<const G*>(grads.p[(rank + kk) % W]) + elem, raw[kk]);
 #pragma unroll
-            for (int q = 0; q < Q; ++q) raw[kk][q] = src[q];
-        }
+        for (int kk = 0; kk < W; ++kk)
 #pragma unroll
-        for (int kk = 0; kk < W; ++kk) {
-            const G* h = reinterpret_cast<const G*>(&raw[kk][0]);
-#pragma unroll
-            for (int k = 0; k < 8; ++k) g[k] += Cvt<G>::to(h[k]);
-        }
+            for (int k = 0; k < N; ++k) g[k] += raw[kk][k];
     } else {
         for (int kk = 0; kk < world; ++kk) {
-            const int r = (rank + kk) % world;
-            const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const G*>(grads.p[r]) + elem);
-            uint4 raw[Q];
+            float raw[N];
+            vload<G, N>(reinterpret_cast<const G*>(grads.p[(rank + kk) % world]) + elem, raw);
 #pragma unroll
-            for (int q = 0; q < Q; ++q) raw[q] = src[q];
-            const G* h = reinterpret_cast<const G*>(&raw[0]);
-#pragma unroll
-            for (int k = 0; k < 8; ++k) g[k] += Cvt<G>::to(h[k]);
+            for (int k = 0; k < N; ++k) g[k] += raw[k];
         }
     }
 }
 
-// Fused reduce-scatter + optimizer step + all-gather over the flat shard [off, off+n).  U vectors are fetched before the first is
-// consumed (memory-level parallelism for the long-latency multimem loads).  NVLS: the updated parameters leave as ONE multimem.st
-// per 16 bytes (the switch replicates them to every rank).
-template <int OP, typename G, typename T, bool NVLS, int W>
+template <typename G, typename T> struct VecN { static constexpr int value = (sizeof(G) == 2 && sizeof(T) == 2) ? 8 : 4; };
+
+// Fused reduce-scatter + optimizer step + all-gather over the flat shard [off, off+n).  NVLS: the updated parameters leave as ONE
+// multimem.st per 16 bytes (the switch replicates them to every rank); NVLS needs 16-byte vectors of both buffers (same dtype).
+template <int OP, typename G, typename T, bool NVLS, int W, int U>
 __global__ void __launch_bounds__(256) fused_rs_step_ag_kernel(PeerPtrs grads, PeerPtrs params, const void* mc_grad, void* mc_param,
                                                                int world, int rank, int64_t off, int64_t n, FlatStep st) {
-    constexpr int N = 8;
-    constexpr int U = NVLS ? 4 : 1;
+    constexpr int N = VecN<G, T>::value;
     const int64_t nv = n / N;
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
     for (int64_t v0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v0 < nv; v0 += stride * U) {
-        float gg[U][N];
+        // local state first, remote gradients second: every load of this iteration is in flight before the first use stalls the warp
+        float pp[U][N], ms[U][N], vs[U][N], gg[U][N];
 #pragma unroll
         for (int u = 0; u < U; ++u) {
             const int64_t v = v0 + u * stride;
-            if (v < nv) fetch_grad8<G, NVLS, W>(grads, mc_grad, world, rank, off + v * N, gg[u]);
+            if (v >= nv) continue;
+            const int64_t i0 = v * N;
+#pragma unroll
+            for (int q = 0; q < N / 4; ++q) {
+                const float4 a = __ldcs(reinterpret_cast<const float4*>(st.master + i0) + q);
+                pp[u][4 * q] = a.x; pp[u][4 * q + 1] = a.y; pp[u][4 * q + 2] = a.z; pp[u][4 * q + 3] = a.w;
+                const float4 b = __ldcs(reinterpret_cast<const float4*>(st.m + i0) + q);
+                ms[u][4 * q] = b.x; ms[u][4 * q + 1] = b.y; ms[u][4 * q + 2] = b.z; ms[u][4 * q + 3] = b.w;
+                if (OP == 0) {
+                    const float4 c = __ldcs(reinterpret_cast<const float4*>(st.v + i0) + q);
+                    vs[u][4 * q] = c.x; vs[u][4 * q + 1] = c.y; vs[u][4 * q + 2] = c.z; vs[u][4 * q + 3] = c.w;
+                }
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int64_t v = v0 + u * stride;
+            if (v < nv) fetch_grad<G, N, NVLS, W>(grads, mc_grad, world, rank, off + v * N, gg[u]);
         }
 #pragma unroll
         for (int u = 0; u < U; ++u) {
             const int64_t v = v0 + u * stride;
             if (v >= nv) break;
             float (&g)[N] = gg[u];
-            float p[N], mm[N], vv[N];
+            float (&p)[N] = pp[u];
+            float (&mm)[N] = ms[u];
+            float (&vv)[N] = vs[u];
             const int64_t i0 = v * N;
-#pragma unroll
-            for (int q = 0; q < 2; ++q) {
-                const float4 a = reinterpret_cast<const float4*>(st.master + i0)[q];
-                p[4 * q] = a.x; p[4 * q + 1] = a.y; p[4 * q + 2] = a.z; p[4 * q + 3] = a.w;
-                const float4 b = reinterpret_cast<const float4*>(st.m + i0)[q];
-                mm[4 * q] = b.x; mm[4 * q + 1] = b.y; mm[4 * q + 2] = b.z; mm[4 * q + 3] = b.w;
-                if (OP == 0) {
-                    const float4 c = reinterpret_cast<const float4*>(st.v + i0)[q];
-                    vv[4 * q] = c.x; vv[4 * q + 1] = c.y; vv[4 * q + 2] = c.z; vv[4 * q + 3] = c.w;
-                }
-            }
 #pragma unroll
             for (int k = 0; k < N; ++k) {
                 const float gs = g[k] * st.gscale;
@@ -165,33 +192,19 @@ __global__ void __launch_bounds__(256) fused_rs_step_ag_kernel(PeerPtrs grads, P
                 else         p[k] = lion_update(p[k], gs, mm[k], st.lr, st.beta1, st.beta2, st.wd);
             }
 #pragma unroll
-            for (int q = 0; q < 2; ++q) {
-                reinterpret_cast<float4*>(st.master + i0)[q] = make_float4(p[4 * q], p[4 * q + 1], p[4 * q + 2], p[4 * q + 3]);
-                reinterpret_cast<float4*>(st.m + i0)[q] = make_float4(mm[4 * q], mm[4 * q + 1], mm[4 * q + 2], mm[4 * q + 3]);
-                if (OP == 0) reinterpret_cast<float4*>(st.v + i0)[q] = make_float4(vv[4 * q], vv[4 * q + 1], vv[4 * q + 2], vv[4 * q + 3]);
+            for (int q = 0; q < N / 4; ++q) {
+                __stcs(reinterpret_cast<float4*>(st.master + i0) + q, make_float4(p[4 * q], p[4 * q + 1], p[4 * q + 2], p[4 * q + 3]));
+                __stcs(reinterpret_cast<float4*>(st.m + i0) + q, make_float4(mm[4 * q], mm[4 * q + 1], mm[4 * q + 2], mm[4 * q + 3]));
+                if (OP == 0) __stcs(reinterpret_cast<float4*>(st.v + i0) + q, make_float4(vv[4 * q], vv[4 * q + 1], vv[4 * q + 2], vv[4 * q + 3]));
             }
-            // all-gather: the updated low-precision parameters go straight to every rank's buffer
-            uint4 o[2];
-            constexpr int QO = sizeof(T) == 2 ? 1 : 2;
-            if constexpr (sizeof(T) == 2) {
-                T* h = reinterpret_cast<T*>(&o[0]);
-#pragma unroll
-                for (int k = 0; k < N; ++k) h[k] = Cvt<T>::from(p[k]);
+            // all-gather: the updated parameters go straight to every rank's buffer
+            uint4 o;
+            vpack<T, N>(p, o);
+            if constexpr (NVLS && sizeof(T) * N == 16) {
+                multimem_st_u32x4(reinterpret_cast<char*>(mc_param) + (off + i0) * sizeof(T), o);
             } else {
-                o[0] = make_uint4(__float_as_uint(p[0]), __float_as_uint(p[1]), __float_as_uint(p[2]), __float_as_uint(p[3]));
-                o[1] = make_uint4(__float_as_uint(p[4]), __float_as_uint(p[5]), __float_as_uint(p[6]), __float_as_uint(p[7]));
-            }
-            if (NVLS) {
-                char* d = reinterpret_cast<char*>(mc_param) + (off + i0) * sizeof(T);
-#pragma unroll
-                for (int q = 0; q < QO; ++q) multimem_st_u32x4(d + 16 * q, o[q]);
-            } else {
-                for (int kk = 0; kk < world; ++kk) {
-                    const int r = (rank + kk) % world;
-                    uint4* d = reinterpret_cast<uint4*>(reinterpret_cast<T*>(params.p[r]) + off + i0);
-#pragma unroll
-                    for (int q = 0; q < QO; ++q) d[q] = o[q];
-                }
+                for (int kk = 0; kk < world; ++kk)
+                    vstore_packed<T, N>(reinterpret_cast<T*>(params.p[(rank + kk) % world]) + off + i0, o);
             }
         }
     }
@@ -202,25 +215,26 @@ __global__ void __launch_bounds__(256) fused_rs_step_ag_kernel(PeerPtrs grads, P
 template <typename T, bool NVLS, int W>
 __global__ void __launch_bounds__(256) pull_reduce_kernel(PeerPtrs grads, const void* mc_grad, int world, int rank, int64_t off, int64_t n,
                                                           float scale, float* __restrict__ out) {
-    constexpr int U = NVLS ? 4 : 1;
-    const int64_t nv = n / 8;
+    constexpr int N = 16 / sizeof(T);
+    constexpr int U = NVLS ? 4 : 2;
+    const int64_t nv = n / N;
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
     for (int64_t v0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v0 < nv; v0 += stride * U) {
-        float g[U][8];
+        float g[U][N];
 #pragma unroll
         for (int u = 0; u < U; ++u)
-            if (v0 + u * stride < nv) fetch_grad8<T, NVLS, W>(grads, mc_grad, world, rank, off + (v0 + u * stride) * 8, g[u]);
+            if (v0 + u * stride < nv) fetch_grad<T, N, NVLS, W>(grads, mc_grad, world, rank, off + (v0 + u * stride) * N, g[u]);
 #pragma unroll
         for (int u = 0; u < U; ++u) {
             const int64_t v = v0 + u * stride;
             if (v >= nv) break;
-            float4* o = reinterpret_cast<float4*>(out + v * 8);
-            o[0] = make_float4(g[u][0] * scale, g[u][1] * scale, g[u][2] * scale, g[u][3] * scale);
-            o[1] = make_float4(g[u][4] * scale, g[u][5] * scale, g[u][6] * scale, g[u][7] * scale);
+#pragma unroll
+            for (int q = 0; q < N / 4; ++q)
+                __stcs(reinterpret_cast<float4*>(out + v * N) + q, make_float4(g[u][4 * q] * scale, g[u][4 * q + 1] * scale, g[u][4 * q + 2] * scale, g[u][4 * q + 3] * scale));
         }
     }
-    // tail (n not a multiple of 8): scalar peer loads
-    for (int64_t i = nv * 8 + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    // tail (n not a multiple of the vector): scalar peer loads
+    for (int64_t i = nv * N + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
         float a = 0.f;
         for (int r = 0; r < world; ++r) a += Cvt<T>::to(reinterpret_cast<const T*>(grads.p[r])[off + i]);
         out[i] = a * scale;
@@ -231,28 +245,21 @@ __global__ void __launch_bounds__(256) pull_reduce_kernel(PeerPtrs grads, const 
 template <typename T>
 __global__ void __launch_bounds__(256) cast_push_kernel(PeerPtrs params, int world, int rank, int64_t off, int64_t n,
                                                         const float* __restrict__ master) {
-    const int64_t nv = n / 8;
+    constexpr int N = 16 / sizeof(T);                    // one 16-byte store per lane and destination
+    const int64_t nv = n / N;
     for (int64_t v = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v < nv; v += (int64_t)gridDim.x * blockDim.x) {
-        const float4 a = reinterpret_cast<const float4*>(master)[2 * v], b = reinterpret_cast<const float4*>(master)[2 * v + 1];
-        const float p[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-        if constexpr (sizeof(T) == 2) {
-            uint4 o;
-            T* h = reinterpret_cast<T*>(&o);
+        float p[N];
 #pragma unroll
-            for (int k = 0; k < 8; ++k) h[k] = Cvt<T>::from(p[k]);
-            for (int kk = 0; kk < world; ++kk) {
-                const int r = (rank + kk) % world;
-                *reinterpret_cast<uint4*>(reinterpret_cast<T*>(params.p[r]) + off + v * 8) = o;
-            }
-        } else {
-            for (int kk = 0; kk < world; ++kk) {
-                const int r = (rank + kk) % world;
-                float4* d = reinterpret_cast<float4*>(reinterpret_cast<float*>(params.p[r]) + off + v * 8);
-                d[0] = a; d[1] = b;
-            }
+        for (int q = 0; q < N / 4; ++q) {
+            const float4 a = __ldcs(reinterpret_cast<const float4*>(master + v * N) + q);
+            p[4 * q] = a.x; p[4 * q + 1] = a.y; p[4 * q + 2] = a.z; p[4 * q + 3] = a.w;
         }
+        uint4 o;
+        vpack<T, N>(p, o);
+        for (int kk = 0; kk < world; ++kk)
+            vstore_packed<T, N>(reinterpret_cast<T*>(params.p[(rank + kk) % world]) + off + v * N, o);
     }
-    for (int64_t i = nv * 8 + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+    for (int64_t i = nv * N + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
         for (int r = 0; r < world; ++r) reinterpret_cast<T*>(params.p[r])[off + i] = Cvt<T>::from(master[i]);
 }
 
@@ -290,7 +297,7 @@ void dist_pull_reduce(int dtype, bool nvls, const PeerPtrs& grads, const void* m
                       float* out, cudaStream_t s) {
     if (n <= 0) return;
     count_launch();
-    const int g = grid_for(n / 8);
+    const int g = grid_for(n / 4);
 #define LAUNCH(T) \
     if (nvls) pull_reduce_kernel<T, true, 0><<<g, 256, 0, s>>>(grads, mc, world, rank, off, n, scale, out); \
     else if (world == 8) pull_reduce_kernel<T, false, 8><<<g, 256, 0, s>>>(grads, mc, world, rank, off, n, scale, out); \
@@ -315,14 +322,22 @@ void dist_fused_flat_step(int op, int gdtype, int pdtype, bool nvls, const PeerP
     if (n <= 0) return;
     count_launch();
     FlatStep st{lr, beta1, beta2, eps, wd, bc1, bc2, gscale, master, m, v};
-    const int g = grid_for(n / 8);
-#define L3(OPV, G, T, NV, WW) fused_rs_step_ag_kernel<OPV, G, T, NV, WW><<<g, 256, 0, s>>>(grads, params, mc_grad, mc_param, world, rank, off, n, st)
+    if (nvls && gdtype != pdtype) nvls = false;              // the multimem path needs 16-byte vectors of both buffers
+    // Tuning knobs (read once): vectors in flight per thread and CTAs per SM of the grid.
+    static const int unroll = [] { const char* e = getenv("SG_FUSED_UNROLL"); const int u = e ? atoi(e) : 0; return (u == 1 || u == 2 || u == 4) ? u : 0; }();
+    static const int ctas = [] { const char* e = getenv("SG_FUSED_CTAS"); const int c = e ? atoi(e) : 0; return (c >= 1 && c <= 32) ? c : 8; }();
+    const int u_sel = unroll ? unroll : (nvls ? 4 : 2);
+    const int64_t want = (n / 4 + 255) / 256;
+    const int g = (int)(want < 1 ? 1 : (want > 148LL * ctas ? 148LL * ctas : want));
+#define L4(OPV, G, T, NV, WW, UU) fused_rs_step_ag_kernel<OPV, G, T, NV, WW, UU><<<g, 256, 0, s>>>(grads, params, mc_grad, mc_param, world, rank, off, n, st)
+#define L3(OPV, G, T, NV, WW) \
+    if (u_sel == 4) L4(OPV, G, T, NV, WW, 4); else if (u_sel == 2) L4(OPV, G, T, NV, WW, 2); else L4(OPV, G, T, NV, WW, 1)
 #define L2(OPV, G, T) \
-    if (nvls) L3(OPV, G, T, true, 0); \
-    else if (world == 8) L3(OPV, G, T, false, 8); \
-    else if (world == 4) L3(OPV, G, T, false, 4); \
-    else if (world == 2) L3(OPV, G, T, false, 2); \
-    else L3(OPV, G, T, false, 0)
+    if (nvls) { L3(OPV, G, T, true, 0); } \
+    else if (world == 8) { L3(OPV, G, T, false, 8); } \
+    else if (world == 4) { L3(OPV, G, T, false, 4); } \
+    else if (world == 2) { L3(OPV, G, T, false, 2); } \
+    else { L3(OPV, G, T, false, 0); }
 #define L1(OPV) \
     if (gdtype == BF16 && pdtype == BF16) { L2(OPV, __nv_bfloat16, __nv_bfloat16); } \
     else if (gdtype == F32 && pdtype == BF16) { L2(OPV, float, __nv_bfloat16); } \
@@ -332,6 +347,7 @@ void dist_fused_flat_step(int op, int gdtype, int pdtype, bool nvls, const PeerP
 #undef L1
 #undef L2
 #undef L3
+#undef L4
 }
 
 void dist_cast_push(int pdtype, const PeerPtrs& params, int world, int rank, int64_t off, int64_t n, const float* master, cudaStream_t s) {

@@ -144,4 +144,5 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     sgb::register_dist(m);
     sgb::register_gemm(m);
     sgb::register_nn(m);
+    sgb::register_llm(m);
 }

@@ -6,4 +6,5 @@ void register_sg2(pybind11::module_& m);
 void register_dist(pybind11::module_& m);
 void register_gemm(pybind11::module_& m);
 void register_nn(pybind11::module_& m);
+void register_llm(pybind11::module_& m);
 }

@@ -1,0 +1,158 @@
+// Bindings of the decoder-model kernels (rotary embedding, SwiGLU, GELU, embedding, cross-entropy).
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include "bindings_decl.h"
+#include "mt_host.h"
+
+namespace sg {
+void rope(int dtype, const void* x, void* y, const float* cosT, const float* sinT, int64_t B, int S, int H, int HD, bool backward, cudaStream_t st);
+void swiglu(int dtype, bool backward, const void* g, const void* u, const void* dy, void* out0, void* out1, int64_t n, cudaStream_t st);
+void gelu(int dtype, bool backward, const void* x, const void* dy, void* y, int64_t n, cudaStream_t st);
+void embed_fwd(int dtype, const int64_t* ids, const void* W, void* out, int64_t T_tok, int D, int V, cudaStream_t st);
+void embed_keys(const int64_t* ids, uint32_t* keys, uint32_t* vals, int64_t T_tok, int V, cudaStream_t st);
+void embed_bwd(int dtype, const uint32_t* keys, const uint32_t* vals, const void* dout, void* dW, int64_t T_tok, int D, cudaStream_t st);
+void ce_fwd(int dtype, const void* logits, const int64_t* target, float* lse, float* loss, float* mean_out, int64_t rows, int V, int64_t ignore_index,
+            cudaStream_t st);
+void ce_bwd(int dtype, const void* logits, const int64_t* target, const float* lse, const float* mean_out, const float* gout, void* dlogits,
+            int64_t rows, int V, int64_t ignore_index, cudaStream_t st);
+}
+
+namespace sgb {
+namespace py = pybind11;
+namespace {
+using at::Tensor;
+
+void check_act(const Tensor& x, const char* what) {
+    TORCH_CHECK(x.is_cuda() && x.is_contiguous(), what, ": contiguous CUDA tensor expected");
+    TORCH_CHECK(x.scalar_type() == at::kBFloat16 || x.scalar_type() == at::kFloat || x.scalar_type() == at::kHalf, what, ": bf16, fp16 or fp32");
+    TORCH_CHECK(reinterpret_cast<uintptr_t>(x.data_ptr()) % 16 == 0, what, ": storage must be 16-byte aligned");
+}
+
+// x: [B, S, H, HD] -> rotated copy (backward = true applies the inverse rotation to a gradient)
+Tensor rope(const Tensor& x, const Tensor& cosT, const Tensor& sinT, bool backward) {
+    check_act(x, "rope");
+    TORCH_CHECK(x.dim() == 4, "rope: x must be [B, S, H, HD]");
+    const int64_t B = x.size(0);
+    const int S = (int)x.size(1), H = (int)x.size(2), HD = (int)x.size(3);
+    TORCH_CHECK(HD % 8 == 0, "rope: head_dim must be a multiple of 8");
+    TORCH_CHECK(cosT.is_cuda() && cosT.scalar_type() == at::kFloat && cosT.is_contiguous() && cosT.size(0) >= S && cosT.size(1) == HD / 2 &&
+                sinT.is_cuda() && sinT.scalar_type() == at::kFloat && sinT.is_contiguous() && sinT.sizes() == cosT.sizes(),
+                "rope: cos/sin must be contiguous fp32 CUDA tables [>=S, HD/2]");
+    c10::cuda::CUDAGuard guard(x.device());
+    Tensor y = at::empty_like(x);
+    sg::rope(dtype_code(x), x.data_ptr(), y.data_ptr(), cosT.data_ptr<float>(), sinT.data_ptr<float>(), B, S, H, HD, backward,
+             at::cuda::getCurrentCUDAStream());
+    return y;
+}
+
+Tensor swiglu_fwd(const Tensor& g, const Tensor& u) {
+    check_act(g, "swiglu"); check_act(u, "swiglu");
+    TORCH_CHECK(g.sizes() == u.sizes() && g.scalar_type() == u.scalar_type() && g.numel() % 8 == 0, "swiglu: equal shapes, numel multiple of 8");
+    c10::cuda::CUDAGuard guard(g.device());
+    Tensor y = at::empty_like(g);
+    sg::swiglu(dtype_code(g), false, g.data_ptr(), u.data_ptr(), nullptr, y.data_ptr(), nullptr, g.numel(), at::cuda::getCurrentCUDAStream());
+    return y;
+}
+
+std::vector<Tensor> swiglu_bwd(const Tensor& g, const Tensor& u, const Tensor& dy_) {
+    Tensor dy = dy_.contiguous();
+    check_act(dy, "swiglu");
+    c10::cuda::CUDAGuard guard(g.device());
+    Tensor dg = at::empty_like(g), du = at::empty_like(u);
+    sg::swiglu(dtype_code(g), true, g.data_ptr(), u.data_ptr(), dy.data_ptr(), dg.data_ptr(), du.data_ptr(), g.numel(), at::cuda::getCurrentCUDAStream());
+    return {dg, du};
+}
+
+Tensor gelu_fwd(const Tensor& x) {
+    check_act(x, "gelu");
+    TORCH_CHECK(x.numel() % 8 == 0, "gelu: numel multiple of 8");
+    c10::cuda::CUDAGuard guard(x.device());
+    Tensor y = at::empty_like(x);
+    sg::gelu(dtype_code(x), false, x.data_ptr(), nullptr, y.data_ptr(), x.numel(), at::cuda::getCurrentCUDAStream());
+    return y;
+}
+Tensor gelu_bwd(const Tensor& x, const Tensor& dy_) {
+    Tensor dy = dy_.contiguous();
+    check_act(dy, "gelu");
+    c10::cuda::CUDAGuard guard(x.device());
+    Tensor dx = at::empty_like(x);
+    sg::gelu(dtype_code(x), true, x.data_ptr(), dy.data_ptr(), dx.data_ptr(), x.numel(), at::cuda::getCurrentCUDAStream());
+    return dx;
+}
+
+Tensor embedding_fwd(const Tensor& ids, const Tensor& W) {
+    check_act(W, "embedding");
+    TORCH_CHECK(ids.is_cuda() && ids.scalar_type() == at::kLong && ids.is_contiguous(), "embedding: ids must be contiguous int64 CUDA");
+    const int D = (int)W.size(1), V = (int)W.size(0);
+    TORCH_CHECK((D * W.element_size()) % 16 == 0, "embedding: row bytes must be a multiple of 16");
+    c10::cuda::CUDAGuard guard(W.device());
+    auto shape = ids.sizes().vec();
+    shape.push_back(D);
+    Tensor out = at::empty(shape, W.options());
+    sg::embed_fwd(dtype_code(W), ids.data_ptr<int64_t>(), W.data_ptr(), out.data_ptr(), ids.numel(), D, V, at::cuda::getCurrentCUDAStream());
+    return out;
+}
+
+// Deterministic gradient of the gather: stable radix sort of the token ids (the framework's own sort), then one warp per id run.
+Tensor embedding_bwd(const Tensor& ids, const Tensor& dout_, int64_t V) {
+    Tensor dout = dout_.contiguous();
+    check_act(dout, "embedding");
+    const int D = (int)dout.size(-1);
+    const int64_t T_tok = ids.numel();
+    TORCH_CHECK(D % 8 == 0 && T_tok < (int64_t)1 << 31, "embedding: width multiple of 8, fewer than 2^31 tokens");
+    c10::cuda::CUDAGuard guard(dout.device());
+    auto st = at::cuda::getCurrentCUDAStream();
+    auto io = dout.options().dtype(at::kInt);
+    Tensor dW = at::zeros({V, D}, dout.options());
+    if (T_tok == 0) return dW;
+    Tensor kv = at::empty({4, T_tok}, io);
+    const int64_t nb = (int64_t)sg::sg2_sort_blocks(T_tok);
+    Tensor hist = at::empty({256 * nb + 256}, io);
+    Tensor seg = at::zeros({2}, dout.options().dtype(at::kLong));          // one segment: offsets are only read when there are several
+    auto* k0 = reinterpret_cast<uint32_t*>(kv.data_ptr<int>());
+    uint32_t* k1 = k0 + T_tok; uint32_t* v0 = k1 + T_tok; uint32_t* v1 = v0 + T_tok;
+    auto* h = reinterpret_cast<uint32_t*>(hist.data_ptr<int>());
+    sg::embed_keys(ids.data_ptr<int64_t>(), k0, v0, T_tok, (int)V, st);
+    int cur = 0;
+    sg::sg2_segmented_sort(k0, k1, v0, v1, h, h + 256 * nb, seg.data_ptr<int64_t>(), 1, T_tok, &cur, st);
+    sg::embed_bwd(dtype_code(dout), cur ? k1 : k0, cur ? v1 : v0, dout.data_ptr(), dW.data_ptr(), T_tok, D, st);
+    return dW;
+}
+
+// returns (mean loss [1], lse [rows], mean_out [2] = {mean, 1/count})
+std::vector<Tensor> ce_fwd(const Tensor& logits, const Tensor& target, int64_t ignore_index) {
+    check_act(logits, "cross_entropy");
+    TORCH_CHECK(logits.dim() == 2 && logits.size(1) % 8 == 0, "cross_entropy: logits [rows, V] with V a multiple of 8");
+    TORCH_CHECK(target.is_cuda() && target.scalar_type() == at::kLong && target.is_contiguous() && target.numel() == logits.size(0),
+                "cross_entropy: target must be contiguous int64 CUDA [rows]");
+    c10::cuda::CUDAGuard guard(logits.device());
+    const int64_t rows = logits.size(0);
+    auto fo = logits.options().dtype(at::kFloat);
+    Tensor lse = at::empty({rows}, fo), loss = at::empty({rows}, fo), mean_out = at::zeros({2}, fo);
+    sg::ce_fwd(dtype_code(logits), logits.data_ptr(), target.data_ptr<int64_t>(), lse.data_ptr<float>(), loss.data_ptr<float>(),
+               mean_out.data_ptr<float>(), rows, (int)logits.size(1), ignore_index, at::cuda::getCurrentCUDAStream());
+    return {mean_out.narrow(0, 0, 1).reshape({}), lse, mean_out};
+}
+
+Tensor ce_bwd(const Tensor& logits, const Tensor& target, const Tensor& lse, const Tensor& mean_out, const Tensor& gout, int64_t ignore_index) {
+    c10::cuda::CUDAGuard guard(logits.device());
+    Tensor g = gout.to(at::kFloat).contiguous();
+    Tensor d = at::empty_like(logits);
+    sg::ce_bwd(dtype_code(logits), logits.data_ptr(), target.data_ptr<int64_t>(), lse.data_ptr<float>(), mean_out.data_ptr<float>(),
+               g.data_ptr<float>(), d.data_ptr(), logits.size(0), (int)logits.size(1), ignore_index, at::cuda::getCurrentCUDAStream());
+    return d;
+}
+}  // namespace
+
+void register_llm(pybind11::module_& m) {
+    m.def("rope", &rope, py::arg("x"), py::arg("cos"), py::arg("sin"), py::arg("backward") = false);
+    m.def("swiglu_fwd", &swiglu_fwd);
+    m.def("swiglu_bwd", &swiglu_bwd);
+    m.def("gelu_fwd", &gelu_fwd);
+    m.def("gelu_bwd", &gelu_bwd);
+    m.def("embedding_fwd", &embedding_fwd);
+    m.def("embedding_bwd", &embedding_bwd);
+    m.def("ce_fwd", &ce_fwd);
+    m.def("ce_bwd", &ce_bwd);
+}
+}  // namespace sgb

@@ -7,14 +7,15 @@
 namespace sg {
 bool attn_small_supported(int S, int HD);
 void attn_small(int dtype, bool bwd, const void* qkv, const void* dout, void* out, int B, int S, int H, int HD, bool causal, cudaStream_t st);
-void ln_fwd(int dtype, const void* x, const void* r, const void* gamma, const void* beta, void* z, void* y, float* stats, int64_t rows, int D,
-            float eps, cudaStream_t st);
+void ln_fwd(int dtype, bool rms, const void* x, const void* r, const void* gamma, const void* beta, void* z, void* y, float* stats, int64_t rows,
+            int D, float eps, cudaStream_t st);
 int ln_bwd_parts(int64_t rows);
-void ln_bwd(int dtype, const void* z, const void* dy, const void* gamma, const float* stats, void* dz, float* part, void* dgamma, void* dbeta,
-            int64_t rows, int D, cudaStream_t st);
+void ln_bwd(int dtype, bool rms, const void* z, const void* dy, const void* gamma, const float* stats, const void* dz_in, void* dz, float* part,
+            void* dgamma, void* dbeta, int64_t rows, int D, cudaStream_t st);
 }
 
 namespace sgb {
+namespace py = pybind11;
 namespace {
 using at::Tensor;
 
@@ -42,7 +43,9 @@ Tensor attn_small_bwd(const Tensor& qkv, const Tensor& dout, int64_t H, bool cau
 }
 
 // returns (y, z, stats); z is x + r (the LayerNorm input, kept for backward); with no residual z aliases x
-std::vector<Tensor> ln_fwd(const Tensor& x, const c10::optional<Tensor>& r, const Tensor& gamma, const c10::optional<Tensor>& beta, double eps) {
+std::vector<Tensor> ln_fwd(const Tensor& x, const c10::optional<Tensor>& r, const Tensor& gamma, const c10::optional<Tensor>& beta, double eps,
+                           bool rms) {
+    TORCH_CHECK(gamma.scalar_type() == x.scalar_type(), "norm weight and input must have the same dtype");
     TORCH_CHECK(x.is_cuda() && x.is_contiguous(), "x must be contiguous CUDA");
     const int D = (int)x.size(-1);
     TORCH_CHECK(D % 4 == 0, "LayerNorm width must be a multiple of 4");
@@ -51,14 +54,15 @@ std::vector<Tensor> ln_fwd(const Tensor& x, const c10::optional<Tensor>& r, cons
     Tensor y = at::empty_like(x);
     Tensor z = r.has_value() ? at::empty_like(x) : x;
     Tensor stats = at::empty({rows, 2}, x.options().dtype(at::kFloat));
-    sg::ln_fwd(dtype_code(x), x.data_ptr(), r.has_value() ? r->contiguous().data_ptr() : nullptr, gamma.data_ptr(),
+    sg::ln_fwd(dtype_code(x), rms, x.data_ptr(), r.has_value() ? r->contiguous().data_ptr() : nullptr, gamma.data_ptr(),
                beta.has_value() ? beta->data_ptr() : nullptr, z.data_ptr(), y.data_ptr(), stats.data_ptr<float>(), rows, D, (float)eps,
                at::cuda::getCurrentCUDAStream());
     return {y, z, stats};
 }
 
 // returns (dz, dgamma, dbeta)
-std::vector<Tensor> ln_bwd(const Tensor& z, const Tensor& dy, const Tensor& gamma, const Tensor& stats, bool has_beta) {
+std::vector<Tensor> ln_bwd(const Tensor& z, const Tensor& dy, const Tensor& gamma, const Tensor& stats, bool has_beta, bool rms,
+                           const c10::optional<Tensor>& dz_in) {
     const int D = (int)z.size(-1);
     const int64_t rows = z.numel() / D;
     TORCH_CHECK((size_t)8 * 2 * D * sizeof(float) <= 200 * 1024, "LayerNorm width too large for the fused backward");
@@ -68,7 +72,9 @@ std::vector<Tensor> ln_bwd(const Tensor& z, const Tensor& dy, const Tensor& gamm
     Tensor part = at::empty({(int64_t)sg::ln_bwd_parts(rows), 2, D}, z.options().dtype(at::kFloat));
     Tensor dgamma = at::empty_like(gamma);
     Tensor dbeta = has_beta ? at::empty_like(gamma) : Tensor();
-    sg::ln_bwd(dtype_code(z), z.data_ptr(), d.data_ptr(), gamma.data_ptr(), stats.data_ptr<float>(), dz.data_ptr(), part.data_ptr<float>(),
+    Tensor e = dz_in.has_value() ? dz_in->contiguous() : Tensor();
+    sg::ln_bwd(dtype_code(z), rms, z.data_ptr(), d.data_ptr(), gamma.data_ptr(), stats.data_ptr<float>(), dz_in.has_value() ? e.data_ptr() : nullptr,
+               dz.data_ptr(), part.data_ptr<float>(),
                dgamma.data_ptr(), has_beta ? dbeta.data_ptr() : nullptr, rows, D, at::cuda::getCurrentCUDAStream());
     return {dz, dgamma, dbeta};
 }
@@ -78,7 +84,8 @@ void register_nn(pybind11::module_& m) {
     m.def("attn_small_fwd", &attn_small_fwd);
     m.def("attn_small_bwd", &attn_small_bwd);
     m.def("attn_small_supported", [](int64_t S, int64_t HD) { return sg::attn_small_supported((int)S, (int)HD); });
-    m.def("ln_fwd", &ln_fwd);
-    m.def("ln_bwd", &ln_bwd);
+    m.def("ln_fwd", &ln_fwd, py::arg("x"), py::arg("residual"), py::arg("gamma"), py::arg("beta"), py::arg("eps"), py::arg("rms") = false);
+    m.def("ln_bwd", &ln_bwd, py::arg("z"), py::arg("dy"), py::arg("gamma"), py::arg("stats"), py::arg("has_beta"), py::arg("rms") = false,
+          py::arg("dz_in") = c10::optional<Tensor>());
 }
 }  // namespace sgb

@@ -149,7 +149,8 @@ __global__ void __launch_bounds__(256) attn_small_bwd_kernel(const T* __restrict
 
 // ---------------------------------------------------------------------------------------------------- LayerNorm
 // z = x (+ r); y = (z - mean) * rstd * gamma (+ beta).  One warp per row; rows of D <= 8192 elements.
-template <typename T>
+// RMS = true is RMSNorm: the mean is taken as zero (y = z * rsqrt(mean(z^2) + eps) * gamma) and there is no beta.
+template <typename T, bool RMS>
 __global__ void __launch_bounds__(256) ln_fwd_kernel(const T* __restrict__ x, const T* __restrict__ r, const T* __restrict__ gamma,
                                                      const T* __restrict__ beta, T* __restrict__ z, T* __restrict__ y,
                                                      float* __restrict__ stats, int64_t rows, int D, float eps) {
@@ -169,7 +170,7 @@ __global__ void __launch_bounds__(256) ln_fwd_kernel(const T* __restrict__ x, co
         for (int k = 0; k < 4; ++k) { s += a[k]; ss = fmaf(a[k], a[k], ss); }
     }
     s = warp_sum(s); ss = warp_sum(ss);
-    const float mean = s / D;
+    const float mean = RMS ? 0.f : s / D;
     const float var = fmaxf(ss / D - mean * mean, 0.f);
     const float rstd = rsqrtf(var + eps);
     if (lane == 0) { stats[2 * row] = mean; stats[2 * row + 1] = rstd; }
@@ -191,10 +192,10 @@ __global__ void __launch_bounds__(256) ln_fwd_kernel(const T* __restrict__ x, co
 
 // dz = rstd * (dy*g - mean_c(dy*g) - xhat * mean_c(dy*g*xhat)); per-CTA partial sums of dgamma / dbeta over its rows.
 constexpr int LN_ROWS_PER_CTA = 64;
-template <typename T>
+template <typename T, bool RMS>
 __global__ void __launch_bounds__(256) ln_bwd_kernel(const T* __restrict__ z, const T* __restrict__ dy, const T* __restrict__ gamma,
-                                                     const float* __restrict__ stats, T* __restrict__ dz, float* __restrict__ part,
-                                                     int64_t rows, int D) {
+                                                     const float* __restrict__ stats, const T* __restrict__ dz_in, T* __restrict__ dz,
+                                                     float* __restrict__ part, int64_t rows, int D) {
     extern __shared__ float sm[];                       // [8 warps][2][D]  per-warp column partials
     const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
     float* pg = sm + (size_t)w * 2 * D;
@@ -217,13 +218,19 @@ __global__ void __launch_bounds__(256) ln_bwd_kernel(const T* __restrict__ z, co
                 pg[c + k] = fmaf(d[k], xh, pg[c + k]); pb[c + k] += d[k];
             }
         }
-        s1 = warp_sum(s1) / D; s2 = warp_sum(s2) / D;
+        s1 = RMS ? 0.f : warp_sum(s1) / D; s2 = warp_sum(s2) / D;
         for (int c = lane * 4; c < D; c += 128) {
             const int cnt = (D - c >= 4) ? 4 : D - c;
             float a[4], d[4], g[4], o[4];
             ld4<T>(z + row * D, c, cnt, true, a); ld4<T>(dy + row * D, c, cnt, true, d); ld4<T>(gamma, c, cnt, true, g);
 #pragma unroll
             for (int k = 0; k < 4; ++k) { const float xh = (a[k] - mean) * rstd; o[k] = rstd * (d[k] * g[k] - s1 - xh * s2); }
+            if (dz_in) {                                 // gradient that reached z directly (z is also the residual stream)
+                float e[4];
+                ld4<T>(dz_in + row * D, c, cnt, true, e);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) o[k] += e[k];
+            }
             st4<T>(dz + row * D, c, cnt, true, o);
         }
     }
@@ -272,33 +279,43 @@ void attn_small(int dtype, bool bwd, const void* qkv, const void* dout, void* ou
     else attn_dispatch<float>(bwd, (const float*)qkv, (const float*)dout, (float*)out, B, S, H, HD, causal, st);
 }
 
-void ln_fwd(int dtype, const void* x, const void* r, const void* gamma, const void* beta, void* z, void* y, float* stats, int64_t rows, int D,
-            float eps, cudaStream_t st) {
+template <typename T>
+static void ln_fwd_t(bool rms, const void* x, const void* r, const void* gamma, const void* beta, void* z, void* y, float* stats, int64_t rows, int D,
+                     float eps, cudaStream_t st) {
     const unsigned blocks = (unsigned)((rows + 7) / 8);
+    if (rms) ln_fwd_kernel<T, true><<<blocks, 256, 0, st>>>((const T*)x, (const T*)r, (const T*)gamma, nullptr, (T*)z, (T*)y, stats, rows, D, eps);
+    else ln_fwd_kernel<T, false><<<blocks, 256, 0, st>>>((const T*)x, (const T*)r, (const T*)gamma, (const T*)beta, (T*)z, (T*)y, stats, rows, D, eps);
+}
+
+void ln_fwd(int dtype, bool rms, const void* x, const void* r, const void* gamma, const void* beta, void* z, void* y, float* stats, int64_t rows,
+            int D, float eps, cudaStream_t st) {
     count_launch();
-    if (dtype == BF16) ln_fwd_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)r, (const __nv_bfloat16*)gamma,
-                                                                           (const __nv_bfloat16*)beta, (__nv_bfloat16*)z, (__nv_bfloat16*)y, stats, rows, D, eps);
-    else ln_fwd_kernel<float><<<blocks, 256, 0, st>>>((const float*)x, (const float*)r, (const float*)gamma, (const float*)beta, (float*)z, (float*)y,
-                                                      stats, rows, D, eps);
+    if (dtype == BF16) ln_fwd_t<__nv_bfloat16>(rms, x, r, gamma, beta, z, y, stats, rows, D, eps, st);
+    else ln_fwd_t<float>(rms, x, r, gamma, beta, z, y, stats, rows, D, eps, st);
 }
 
 int ln_bwd_parts(int64_t rows) { return (int)((rows + LN_ROWS_PER_CTA - 1) / LN_ROWS_PER_CTA); }
 
-void ln_bwd(int dtype, const void* z, const void* dy, const void* gamma, const float* stats, void* dz, float* part, void* dgamma, void* dbeta,
-            int64_t rows, int D, cudaStream_t st) {
+template <typename T>
+static void ln_bwd_t(bool rms, const void* z, const void* dy, const void* gamma, const float* stats, const void* dz_in, void* dz, float* part,
+                     void* dgamma, void* dbeta, int64_t rows, int D, cudaStream_t st) {
     const int parts = ln_bwd_parts(rows);
     const size_t smem = (size_t)8 * 2 * D * sizeof(float);
-    count_launch(2);
-    if (dtype == BF16) {
-        cudaFuncSetAttribute(ln_bwd_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        ln_bwd_kernel<__nv_bfloat16><<<parts, 256, smem, st>>>((const __nv_bfloat16*)z, (const __nv_bfloat16*)dy, (const __nv_bfloat16*)gamma, stats,
-                                                                (__nv_bfloat16*)dz, part, rows, D);
-        ln_bwd_reduce_kernel<__nv_bfloat16><<<(D + 255) / 256, 256, 0, st>>>(part, parts, D, (__nv_bfloat16*)dgamma, (__nv_bfloat16*)dbeta);
+    if (rms) {
+        cudaFuncSetAttribute(ln_bwd_kernel<T, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        ln_bwd_kernel<T, true><<<parts, 256, smem, st>>>((const T*)z, (const T*)dy, (const T*)gamma, stats, (const T*)dz_in, (T*)dz, part, rows, D);
     } else {
-        cudaFuncSetAttribute(ln_bwd_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        ln_bwd_kernel<float><<<parts, 256, smem, st>>>((const float*)z, (const float*)dy, (const float*)gamma, stats, (float*)dz, part, rows, D);
-        ln_bwd_reduce_kernel<float><<<(D + 255) / 256, 256, 0, st>>>(part, parts, D, (float*)dgamma, (float*)dbeta);
+        cudaFuncSetAttribute(ln_bwd_kernel<T, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        ln_bwd_kernel<T, false><<<parts, 256, smem, st>>>((const T*)z, (const T*)dy, (const T*)gamma, stats, (const T*)dz_in, (T*)dz, part, rows, D);
     }
+    ln_bwd_reduce_kernel<T><<<(D + 255) / 256, 256, 0, st>>>(part, parts, D, (T*)dgamma, (T*)dbeta);
+}
+
+void ln_bwd(int dtype, bool rms, const void* z, const void* dy, const void* gamma, const float* stats, const void* dz_in, void* dz, float* part,
+            void* dgamma, void* dbeta, int64_t rows, int D, cudaStream_t st) {
+    count_launch(2);
+    if (dtype == BF16) ln_bwd_t<__nv_bfloat16>(rms, z, dy, gamma, stats, dz_in, dz, part, dgamma, dbeta, rows, D, st);
+    else ln_bwd_t<float>(rms, z, dy, gamma, stats, dz_in, dz, part, dgamma, dbeta, rows, D, st);
 }
 
 }  // namespace sg

@@ -9,6 +9,8 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
+from ..ops import nn_ops
+
 
 @dataclass
 class LlamaConfig:
@@ -33,19 +35,19 @@ class RMSNorm(nn.Module):
         self.eps = eps
 
     def forward(self, x):
-        return F.rms_norm(x, (x.shape[-1],), self.weight, self.eps)
+        return nn_ops.rms_norm(x, None, self.weight, self.eps)
+
+    def add_norm(self, x, residual):
+        """(RMSNorm(x + residual), x + residual); on CUDA one kernel does the add, the statistics and the scaling."""
+        if residual is None:
+            return self.forward(x), x
+        return nn_ops.norm_residual(x, residual, self.weight, None, self.eps, rms=True)
 
 
 def rope_tables(seq, hd, theta, device, dtype=torch.float32):
     inv = 1.0 / (theta ** (torch.arange(0, hd, 2, device=device, dtype=torch.float32) / hd))
     ang = torch.outer(torch.arange(seq, device=device, dtype=torch.float32), inv)
     return ang.cos().to(dtype), ang.sin().to(dtype)
-
-
-def apply_rope(x, cos, sin):                     # x [B,H,S,hd]
-    x1, x2 = x[..., 0::2], x[..., 1::2]
-    c, s = cos[None, None], sin[None, None]
-    return torch.stack([x1 * c - x2 * s, x1 * s + x2 * c], -1).flatten(-2)
 
 
 class LlamaBlock(nn.Module):
@@ -58,15 +60,16 @@ class LlamaBlock(nn.Module):
         self.w_gate, self.w_up = nn.Linear(d, cfg.d_ff, bias=False), nn.Linear(d, cfg.d_ff, bias=False)
         self.w_down = nn.Linear(cfg.d_ff, d, bias=False)
 
-    def forward(self, x, cos, sin):
+    def forward(self, x, pending, cos, sin):
+        """The residual stream entering the block is x + pending (pending = the previous block's MLP output, not yet added:
+        the add is fused into this block's first norm).  Returns the same pair for the next block."""
         B, S, D = x.shape
-        y = self.attn_norm(x)
-        q, k, v = (w(y).view(B, S, self.h, D // self.h).transpose(1, 2) for w in (self.wq, self.wk, self.wv))
-        q, k = apply_rope(q, cos, sin).to(v.dtype), apply_rope(k, cos, sin).to(v.dtype)
-        o = F.scaled_dot_product_attention(q, k, v, is_causal=True)
-        x = x + self.wo(o.transpose(1, 2).reshape(B, S, D))
-        y = self.mlp_norm(x)
-        return x + self.w_down(F.silu(self.w_gate(y)) * self.w_up(y))
+        y, x = self.attn_norm.add_norm(x, pending)
+        q, k, v = (w(y).view(B, S, self.h, D // self.h) for w in (self.wq, self.wk, self.wv))
+        q, k = nn_ops.rope(q, cos, sin), nn_ops.rope(k, cos, sin)
+        o = nn_ops.attention(q, k, v, causal=True)                      # [B, S, H, hd]
+        y, x = self.mlp_norm.add_norm(self.wo(o.reshape(B, S, D)), x)
+        return x, self.w_down(nn_ops.swiglu(self.w_gate(y), self.w_up(y)))
 
 
 class Llama(nn.Module):
@@ -81,10 +84,11 @@ class Llama(nn.Module):
     def forward(self, ids):
         B, S = ids.shape
         cos, sin = rope_tables(S, self.cfg.d_model // self.cfg.n_heads, self.cfg.rope_theta, ids.device)
-        h = self.embed(ids)
+        h = nn_ops.embedding(ids, self.embed.weight)
+        pending = None
         for l in self.layers:
-            h = l(h, cos, sin)
-        return self.lm_head(self.norm(h))
+            h, pending = l(h, pending, cos, sin)
+        return self.lm_head(self.norm.add_norm(h, pending)[0])
 
     def matrix_params(self):
         """2-D weights of the blocks (Muon group); everything else (embedding, head, norms) goes to AdamW."""

@@ -3,7 +3,12 @@
 ``attention_small(qkv, n_heads)``   causal self-attention for S in {4, 8}, head_dim in {32, 64}; qkv is the
                                     fused projection [B, S, 3*D] and the gradient comes back in the same layout.
 ``layer_norm(x, residual, w, b)``   LayerNorm(x + residual) with the add fused in; backward is deterministic.
-Both fall back to the equivalent PyTorch expression on CPU tensors (used by the CPU tests as the oracle).
+``rms_norm(x, residual, w)``        RMSNorm(x + residual), same kernels with the mean fixed at zero.
+``rope(x, cos, sin)``               rotary position embedding of [B, S, H, hd] (interleaved pairs).
+``swiglu(gate, up)``                silu(gate) * up in one pass; ``gelu(x)`` exact GELU.
+``embedding(ids, weight)``          row gather; the gradient is a deterministic sorted segment sum (no atomics).
+``cross_entropy(logits, target)``   mean softmax cross-entropy with ``ignore_index``; forward reads the logits once.
+All fall back to the equivalent PyTorch expression on CPU tensors (used by the CPU tests as the oracle).
 """
 from __future__ import annotations
 
@@ -51,18 +56,18 @@ def attention_small(qkv: torch.Tensor, n_heads: int, causal: bool = True) -> tor
 
 class _LayerNorm(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, residual, weight, bias, eps):
+    def forward(ctx, x, residual, weight, bias, eps, rms=False):
         C = _build.require()
-        y, z, stats = C.ln_fwd(x.contiguous(), residual, weight, bias, eps)
+        y, z, stats = C.ln_fwd(x.contiguous(), residual, weight, bias, eps, rms)
         ctx.save_for_backward(z, weight, stats)
-        ctx.has_bias, ctx.has_res = bias is not None, residual is not None
+        ctx.has_bias, ctx.has_res, ctx.rms = bias is not None, residual is not None, rms
         return y
 
     @staticmethod
     def backward(ctx, dy):
         z, weight, stats = ctx.saved_tensors
-        dz, dg, db = _build.require().ln_bwd(z, dy, weight, stats, ctx.has_bias)
-        return dz, (dz if ctx.has_res else None), dg, (db if ctx.has_bias else None), None
+        dz, dg, db = _build.require().ln_bwd(z, dy, weight, stats, ctx.has_bias, ctx.rms)
+        return dz, (dz if ctx.has_res else None), dg, (db if ctx.has_bias else None), None, None
 
 
 def layer_norm(x: torch.Tensor, residual: Optional[torch.Tensor], weight: torch.Tensor, bias: Optional[torch.Tensor],
@@ -72,3 +77,164 @@ def layer_norm(x: torch.Tensor, residual: Optional[torch.Tensor], weight: torch.
         z = x if residual is None else x + residual
         return F.layer_norm(z, (x.shape[-1],), weight, bias, eps)
     return _LayerNorm.apply(x, residual, weight, bias, eps)
+
+
+class _NormResidual(torch.autograd.Function):
+    """(y, z) = (norm(x + residual), x + residual): z is the new residual stream, so its own gradient joins the norm's input gradient
+    inside the backward kernel."""
+
+    @staticmethod
+    def forward(ctx, x, residual, weight, bias, eps, rms):
+        y, z, stats = _build.require().ln_fwd(x.contiguous(), residual.contiguous(), weight, bias, eps, rms)
+        ctx.save_for_backward(z, weight, stats)
+        ctx.has_bias, ctx.rms = bias is not None, rms
+        return y, z
+
+    @staticmethod
+    def backward(ctx, dy, dz_out):
+        z, weight, stats = ctx.saved_tensors
+        dz, dg, db = _build.require().ln_bwd(z, dy, weight, stats, ctx.has_bias, ctx.rms, dz_out)
+        return dz, dz, dg, (db if ctx.has_bias else None), None, None
+
+
+def _norm_native(x, weight):
+    return x.is_cuda and x.dtype in (torch.bfloat16, torch.float32) and x.shape[-1] % 4 == 0 and x.shape[-1] <= 3072 and weight.dtype == x.dtype
+
+
+def norm_residual(x: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], eps: float = 1e-5,
+                  rms: bool = False):
+    """Returns (norm(x + residual), x + residual) from one pass over x and residual."""
+    if not _norm_native(x, weight):
+        z = x + residual
+        y = F.rms_norm(z, (x.shape[-1],), weight, eps) if rms else F.layer_norm(z, (x.shape[-1],), weight, bias, eps)
+        return y, z
+    return _NormResidual.apply(x, residual, weight, bias, eps, rms)
+
+
+def attention_reference(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: bool = True) -> torch.Tensor:
+    """q, k, v: [B, S, H, hd] -> [B, S, H, hd]."""
+    o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal=causal)
+    return o.transpose(1, 2)
+
+
+def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: bool = True) -> torch.Tensor:
+    """Multi-head attention over [B, S, H, hd] tensors (heads stay in the projection layout, no transposes)."""
+    return attention_reference(q, k, v, causal)
+
+
+def _native_ok(x: torch.Tensor) -> bool:
+    return x.is_cuda and x.dtype in (torch.bfloat16, torch.float16, torch.float32)
+
+
+def rms_norm(x: torch.Tensor, residual: Optional[torch.Tensor], weight: torch.Tensor, eps: float = 1e-5) -> torch.Tensor:
+    """RMSNorm(x + residual) over the last dimension (residual may be None)."""
+    if not x.is_cuda or x.dtype not in (torch.bfloat16, torch.float32) or x.shape[-1] % 4 or x.shape[-1] > 3072 or weight.dtype != x.dtype:
+        z = x if residual is None else x + residual
+        return F.rms_norm(z, (x.shape[-1],), weight, eps)
+    return _LayerNorm.apply(x, residual, weight, None, eps, True)
+
+
+def rope_reference(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """x [B, S, H, hd]; cos/sin [S, hd/2]; pairs (2i, 2i+1) rotate by the position angle."""
+    x1, x2 = x[..., 0::2].float(), x[..., 1::2].float()
+    c, s = cos[None, : x.shape[1], None], sin[None, : x.shape[1], None]
+    return torch.stack([x1 * c - x2 * s, x1 * s + x2 * c], -1).flatten(-2).to(x.dtype)
+
+
+class _Rope(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, cos, sin):
+        ctx.save_for_backward(cos, sin)
+        return _build.require().rope(x.contiguous(), cos, sin, False)
+
+    @staticmethod
+    def backward(ctx, dy):
+        cos, sin = ctx.saved_tensors
+        return _build.require().rope(dy.contiguous(), cos, sin, True), None, None
+
+
+def rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    if not _native_ok(x) or x.shape[-1] % 8:
+        return rope_reference(x, cos, sin)
+    return _Rope.apply(x, cos.float().contiguous(), sin.float().contiguous())
+
+
+class _SwiGLU(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, g, u):
+        g, u = g.contiguous(), u.contiguous()
+        ctx.save_for_backward(g, u)
+        return _build.require().swiglu_fwd(g, u)
+
+    @staticmethod
+    def backward(ctx, dy):
+        g, u = ctx.saved_tensors
+        dg, du = _build.require().swiglu_bwd(g, u, dy)
+        return dg, du
+
+
+def swiglu(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    if not _native_ok(gate) or gate.numel() % 8 or gate.dtype != up.dtype:
+        return F.silu(gate) * up
+    return _SwiGLU.apply(gate, up)
+
+
+class _Gelu(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x):
+        x = x.contiguous()
+        ctx.save_for_backward(x)
+        return _build.require().gelu_fwd(x)
+
+    @staticmethod
+    def backward(ctx, dy):
+        (x,) = ctx.saved_tensors
+        return _build.require().gelu_bwd(x, dy)
+
+
+def gelu(x: torch.Tensor) -> torch.Tensor:
+    if not _native_ok(x) or x.numel() % 8:
+        return F.gelu(x)
+    return _Gelu.apply(x)
+
+
+class _Embedding(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, ids, weight):
+        ids = ids.contiguous()
+        ctx.save_for_backward(ids)
+        ctx.vocab = weight.shape[0]
+        return _build.require().embedding_fwd(ids, weight)
+
+    @staticmethod
+    def backward(ctx, dout):
+        (ids,) = ctx.saved_tensors
+        return None, _build.require().embedding_bwd(ids, dout, ctx.vocab)
+
+
+def embedding(ids: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    if not _native_ok(weight) or not weight.is_contiguous() or (weight.shape[1] * weight.element_size()) % 16 or weight.shape[1] % 8:
+        return F.embedding(ids, weight)
+    return _Embedding.apply(ids, weight)
+
+
+class _CrossEntropy(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, logits, target, ignore_index):
+        logits, target = logits.contiguous(), target.contiguous()
+        loss, lse, mean_out = _build.require().ce_fwd(logits, target, ignore_index)
+        ctx.save_for_backward(logits, target, lse, mean_out)
+        ctx.ignore_index = ignore_index
+        return loss
+
+    @staticmethod
+    def backward(ctx, gout):
+        logits, target, lse, mean_out = ctx.saved_tensors
+        return _build.require().ce_bwd(logits, target, lse, mean_out, gout.reshape(1), ctx.ignore_index), None, None
+
+
+def cross_entropy(logits: torch.Tensor, target: torch.Tensor, ignore_index: int = -100) -> torch.Tensor:
+    """Mean cross-entropy of logits [rows, V] against int64 targets [rows]; the result is an fp32 scalar."""
+    if not _native_ok(logits) or logits.dim() != 2 or logits.shape[1] % 8:
+        return F.cross_entropy(logits.float(), target, ignore_index=ignore_index)
+    return _CrossEntropy.apply(logits, target, ignore_index)

@@ -8,6 +8,10 @@ namespace sg {
 int gemm_bf16_tn(const void* A, int lda, const void* B, int ldb, int M, int N, int K, float alpha, float beta, const void* D, int ldd,
                  bool d_bf16, const void* bias, bool bias_bf16, float diag, int act, void* C, int ldc, bool c_bf16, void* C2, int ldc2,
                  float* splitk_ws, int64_t splitk_ws_floats, int* err, cudaStream_t s);
+int gemm_bf16_tn_allgather(const void* A, int lda, const PeerPtrs& w_peers, int rank, int world, int M, int N, int K, void* C, int ldc,
+                           bool c_bf16, int* counters, void* sched, int epoch, int n_copy, int* err, cudaStream_t s);
+int gemm_bf16_tn_reducescatter(const void* A, int lda, const void* B, int ldb, int M, int N, int K, const PeerPtrs& slots, const PeerPtrs& flags,
+                               int rank, int world, void* c_local, int ldc, int epoch, unsigned long long timeout_ns, int* err, cudaStream_t s);
 }
 
 namespace sgb {
@@ -41,11 +45,62 @@ void gemm_tn(const Tensor& a, const Tensor& b, Tensor out, double alpha, double 
                                     err.data_ptr<int>(), at::cuda::getCurrentCUDAStream());
     TORCH_CHECK(rc == 0, "gemm_tn launch failed (code ", rc, ")");
 }
+
+// out = a @ Wfull.T where Wfull [N, K] is assembled inside the kernel from the row shards held by `world` ranks:
+// w_ptrs[r] is the address of rank r's [N, K] bf16 buffer (peer-mapped symmetric memory; w_ptrs[rank] is the local one).
+void gemm_tn_allgather(const Tensor& a, const std::vector<int64_t>& w_ptrs, int64_t rank, int64_t N, Tensor out, Tensor counters, int64_t epoch,
+                       int64_t n_copy, Tensor err) {
+    TORCH_CHECK(a.is_cuda() && a.scalar_type() == at::kBFloat16 && a.dim() == 2 && a.stride(1) == 1 && a.stride(0) % 8 == 0, "a must be bf16 [M,K]");
+    const int world = (int)w_ptrs.size();
+    TORCH_CHECK(world >= 1 && world <= sg::MAX_RANKS && rank >= 0 && rank < world, "bad rank / world");
+    const int M = (int)a.size(0), K = (int)a.size(1);
+    TORCH_CHECK(out.size(0) == M && out.size(1) == N && out.stride(1) == 1, "out must be [M,N]");
+    TORCH_CHECK(N % (world * 32) == 0, "N must be a multiple of 32 * world");
+    TORCH_CHECK(counters.is_cuda() && counters.scalar_type() == at::kInt && counters.numel() >= (N + 255) / 256 + 2 &&
+                (reinterpret_cast<uintptr_t>(counters.data_ptr()) & 7) == 0, "counters: int32 [2 + ceil(N/256)], 8-byte aligned");
+    TORCH_CHECK(n_copy >= 1 && n_copy <= 148 && epoch >= 1, "n_copy in [1,148], epoch >= 1");
+    sg::PeerPtrs w{};
+    for (int r = 0; r < world; ++r) {
+        TORCH_CHECK(w_ptrs[r] != 0 && (w_ptrs[r] & 15) == 0, "weight buffers must be mapped and 16-byte aligned");
+        w.p[r] = reinterpret_cast<void*>(w_ptrs[r]);
+    }
+    c10::cuda::CUDAGuard guard(a.device());
+    const bool c_bf16 = out.scalar_type() == at::kBFloat16;
+    const int rc = sg::gemm_bf16_tn_allgather(a.data_ptr(), (int)a.stride(0), w, (int)rank, world, M, (int)N, K, out.data_ptr(), (int)out.stride(0),
+                                              c_bf16, counters.data_ptr<int>() + 2, counters.data_ptr<int>(), (int)epoch, (int)n_copy, err.data_ptr<int>(),
+                                              at::cuda::getCurrentCUDAStream());
+    TORCH_CHECK(rc == 0, "gemm_tn_allgather launch failed (code ", rc, ")");
+}
+
+// out [M / world, N] = this rank's rows of sum_r a_r @ b_r.T (K sharded over the ranks); slot_ptrs / flag_ptrs: every rank's buffers.
+void gemm_tn_reducescatter(const Tensor& a, const Tensor& b, const std::vector<int64_t>& slot_ptrs, const std::vector<int64_t>& flag_ptrs,
+                           int64_t rank, Tensor out, int64_t epoch, double timeout_s, Tensor err) {
+    TORCH_CHECK(a.is_cuda() && b.is_cuda() && a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16, "operands must be CUDA bf16");
+    TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && a.size(1) == b.size(1) && a.stride(1) == 1 && b.stride(1) == 1 && a.stride(0) % 8 == 0 &&
+                b.stride(0) % 8 == 0, "a [M,K], b [N,K], rows 16-byte aligned");
+    const int world = (int)slot_ptrs.size();
+    TORCH_CHECK(world >= 1 && world <= sg::MAX_RANKS && (int)flag_ptrs.size() == world && rank >= 0 && rank < world, "bad rank / world");
+    const int M = (int)a.size(0), N = (int)b.size(0), K = (int)a.size(1);
+    TORCH_CHECK(M % (world * 128) == 0 && N % 64 == 0, "M must be a multiple of 128 * world and N of 64");
+    TORCH_CHECK(out.scalar_type() == at::kBFloat16 && out.size(0) == M / world && out.size(1) == N && out.stride(1) == 1 && out.stride(0) % 8 == 0,
+                "out must be bf16 [M / world, N]");
+    sg::PeerPtrs sl{}, fl{};
+    for (int r = 0; r < world; ++r) { sl.p[r] = reinterpret_cast<void*>(slot_ptrs[r]); fl.p[r] = reinterpret_cast<void*>(flag_ptrs[r]); }
+    c10::cuda::CUDAGuard guard(a.device());
+    const int rc = sg::gemm_bf16_tn_reducescatter(a.data_ptr(), (int)a.stride(0), b.data_ptr(), (int)b.stride(0), M, N, K, sl, fl, (int)rank, world,
+                                                  out.data_ptr(), (int)out.stride(0), (int)epoch, (unsigned long long)(timeout_s * 1e9),
+                                                  err.data_ptr<int>(), at::cuda::getCurrentCUDAStream());
+    TORCH_CHECK(rc == 0, "gemm_tn_reducescatter launch failed (code ", rc, ")");
+}
 }  // namespace
 
 void register_gemm(pybind11::module_& m) {
     m.def("gemm_tn", &gemm_tn, py::arg("a"), py::arg("b"), py::arg("out"), py::arg("alpha") = 1.0, py::arg("beta") = 0.0,
           py::arg("d") = c10::nullopt, py::arg("bias") = c10::nullopt, py::arg("diag") = 0.0, py::arg("act") = 0,
           py::arg("out_t") = c10::nullopt, py::arg("err"), py::arg("splitk_ws") = c10::nullopt);
+    m.def("gemm_tn_reducescatter", &gemm_tn_reducescatter, py::arg("a"), py::arg("b"), py::arg("slot_ptrs"), py::arg("flag_ptrs"), py::arg("rank"),
+          py::arg("out"), py::arg("epoch"), py::arg("timeout_s"), py::arg("err"));
+    m.def("gemm_tn_allgather", &gemm_tn_allgather, py::arg("a"), py::arg("w_ptrs"), py::arg("rank"), py::arg("N"), py::arg("out"),
+          py::arg("counters"), py::arg("epoch"), py::arg("n_copy"), py::arg("err"));
 }
 }  // namespace sgb

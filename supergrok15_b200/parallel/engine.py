@@ -29,6 +29,8 @@ from typing import Dict, List, Optional
 import torch
 import torch.nn.functional as F
 
+from ..ops import nn_ops
+
 from .. import _build
 from .. import optim as O
 from ..ops import elementwise as ew
@@ -56,7 +58,7 @@ class ZeroEngine:
         self.name = optimizer
         self.opt_kwargs = dict(opt_kwargs or {})
         self.timeout_s = timeout_s
-        self.criterion = criterion or F.cross_entropy
+        self.criterion = criterion                                       # None: the fused softmax cross-entropy kernel
         self.model = model.to(param_dtype)
         named = [(n, p) for n, p in self.model.named_parameters() if p.requires_grad]
         self.param_names = [n for n, _ in named]
@@ -299,7 +301,9 @@ class ZeroEngine:
         for xb, yb in zip(x.chunk(micro_batches), y.chunk(micro_batches)):
             logits = self.model(xb)
             if logits.dim() == 3:                                     # language modelling: one target per position
-                loss = self.criterion(logits.reshape(-1, logits.shape[-1]).float(), yb.reshape(-1))
+                logits, yb = logits.reshape(-1, logits.shape[-1]), yb.reshape(-1)
+            if self.criterion is None:                                # reads the low-precision logits directly (fp32 arithmetic inside)
+                loss = nn_ops.cross_entropy(logits, yb)
             else:
                 loss = self.criterion(logits.float(), yb)
             if micro_batches > 1:

@@ -1,0 +1,265 @@
+// Flash attention on the 5th-generation tensor cores (tcgen05 / TMEM / TMA), sm_100a only.  bf16 in, fp32 accumulate.
+//
+//   O[b, s, h, :] = softmax(Q[b, s, h, :] . K[b, :, h, :]^T / sqrt(hd), causal) . V[b, :, h, :]
+//
+// q, k, v, o are [B, S, H, hd] views (hd contiguous, heads adjacent: exactly what the projections produce - no transposes).
+// One CTA owns 128 query rows of one (batch, head) and walks the key blocks of 128:
+//   warp 0      producer: TMA loads Q once, then K_j and V_j into two-deep rings (separate rings: a K slot is free as soon as
+//               S_j = Q K_j^T has been issued and completed, a V slot after P_j V_j)
+//   warp 1      MMA issuer: S_{j+1} = Q K_{j+1}^T into the other S buffer in TMEM (so it runs under the softmax of block j), then
+//               O_blk = P_j V_j.  V is consumed as an MN-major B operand straight from its [keys, hd] TMA tile.
+//   warps 2-5   one query row per thread (TMEM lane = row): running max / sum, P_j written as bf16 into the swizzled K-major
+//               A-operand tile in shared memory, O accumulated in registers (O = O*alpha + O_blk from TMEM)
+// Everything is ordered by mbarriers with bounded waits; a wait that runs out raises the error word and the CTA drains.
+// The log-sum-exp of every row is saved for the backward pass.
+//
+// Replaces nn.MultiheadAttention / F.scaled_dot_product_attention of the model code (the reference model builds its attention
+// from nn.MultiheadAttention, grokking_race_v2.py:313-318) for the long-sequence decoder.
+#include "sg_native.h"
+#include "tc_sm100.cuh"
+#include <cfloat>
+
+namespace sg {
+namespace {
+using namespace tc;
+
+constexpr int FA_THREADS = 192;
+constexpr uint32_t TILE_HALF_BYTES = 128 * 128;          // [128 rows x 64 bf16] = 16 KB
+
+__device__ __forceinline__ float ex2f(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ void mbar_arrive_(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+struct FaBars {
+    uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], s_empty[2], p_full, o_full, o_empty;
+    uint32_t tmem_slot, pad;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(FA_THREADS, 1) flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q,
+                                                                  const __grid_constant__ CUtensorMap map_k,
+                                                                  const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
+                                                                  float* __restrict__ lse, int S, int H, int64_t ld_o, float scale,
+                                                                  int causal, int* __restrict__ err) {
+    constexpr int HALVES = HD / 64;
+    constexpr uint32_t QKV_BYTES = HALVES * TILE_HALF_BYTES;
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t* sQ = smem;
+    uint8_t* sK = sQ + QKV_BYTES;                        // [2][QKV_BYTES]
+    uint8_t* sV = sK + 2 * QKV_BYTES;                    // [2][QKV_BYTES]
+    uint8_t* sP = sV + 2 * QKV_BYTES;                    // [2 halves][16 KB]
+    FaBars* bars = reinterpret_cast<FaBars*>(sP + 2 * TILE_HALF_BYTES);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int qt = (int)gridDim.x - 1 - (int)blockIdx.x;                 // long (late) query tiles start first
+    const int h = blockIdx.y, b = blockIdx.z;
+    const int n_blk = causal ? qt + 1 : S / 128;
+    const int row_q = b * S + qt * 128, col0 = h * HD;
+
+    if (threadIdx.x == 0) {
+        mbar_init(&bars->q_full, 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&bars->k_full[i], 1); mbar_init(&bars->k_empty[i], 1); mbar_init(&bars->v_full[i], 1); mbar_init(&bars->v_empty[i], 1);
+            mbar_init(&bars->s_full[i], 1); mbar_init(&bars->s_empty[i], 128);
+        }
+        mbar_init(&bars->p_full, 128); mbar_init(&bars->o_full, 1); mbar_init(&bars->o_empty, 128);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bars->tmem_slot)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = bars->tmem_slot;
+    const uint32_t tmem_o = tmem_base + 256;                             // S0 [0,128), S1 [128,256), O_blk [256, 256+HD)
+
+    if (warp == 0) {
+        if (lane == 0) {
+            mbar_expect_tx(&bars->q_full, QKV_BYTES);
+            for (int hf = 0; hf < HALVES; ++hf) tma_load_2d(sQ + hf * TILE_HALF_BYTES, &map_q, col0 + hf * 64, row_q, &bars->q_full);
+            for (int j = 0; j < n_blk; ++j) {
+                const int s = j & 1, row_k = b * S + j * 128;
+                if (j >= 2 && !mbar_wait(&bars->k_empty[s], ((j >> 1) & 1) ^ 1)) { atomicExch(err, 11); break; }
+                mbar_expect_tx(&bars->k_full[s], QKV_BYTES);
+                for (int hf = 0; hf < HALVES; ++hf) tma_load_2d(sK + s * QKV_BYTES + hf * TILE_HALF_BYTES, &map_k, col0 + hf * 64, row_k, &bars->k_full[s]);
+                if (j >= 2 && !mbar_wait(&bars->v_empty[s], ((j >> 1) & 1) ^ 1)) { atomicExch(err, 12); break; }
+                mbar_expect_tx(&bars->v_full[s], QKV_BYTES);
+                for (int hf = 0; hf < HALVES; ++hf) tma_load_2d(sV + s * QKV_BYTES + hf * TILE_HALF_BYTES, &map_v, col0 + hf * 64, row_k, &bars->v_full[s]);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc_qk = make_idesc_bf16(128, 128, 0, 0);
+            constexpr uint32_t idesc_pv = make_idesc_bf16(128, HD, 0, 1);     // B = V is MN-major (hd contiguous)
+            bool ok = mbar_wait(&bars->q_full, 0);
+            if (!ok) atomicExch(err, 13);
+            tc_fence_after();
+            auto issue_qk = [&](int j) -> bool {
+                const int s = j & 1;
+                if (!mbar_wait(&bars->k_full[s], (j >> 1) & 1)) { atomicExch(err, 14); return false; }
+                if (j >= 2 && !mbar_wait(&bars->s_empty[s], ((j >> 1) & 1) ^ 1)) { atomicExch(err, 15); return false; }
+                tc_fence_after();
+#pragma unroll
+                for (int kk = 0; kk < HD / 16; ++kk) {
+                    const uint64_t da = make_desc_sw128(smem_u32(sQ + (kk / 4) * TILE_HALF_BYTES)) + 2 * (kk % 4);
+                    const uint64_t db = make_desc_sw128(smem_u32(sK + s * QKV_BYTES + (kk / 4) * TILE_HALF_BYTES)) + 2 * (kk % 4);
+                    tc_mma_bf16(tmem_base + s * 128, da, db, idesc_qk, kk > 0 ? 1u : 0u);
+                }
+                tc_commit(&bars->k_empty[s]);
+                tc_commit(&bars->s_full[s]);
+                return true;
+            };
+            if (ok) ok = issue_qk(0);
+            for (int j = 0; j < n_blk && ok; ++j) {
+                if (j + 1 < n_blk) { ok = issue_qk(j + 1); if (!ok) break; }
+                const int s = j & 1;
+                if (!mbar_wait(&bars->v_full[s], (j >> 1) & 1)) { atomicExch(err, 16); ok = false; break; }
+                if (!mbar_wait(&bars->p_full, j & 1)) { atomicExch(err, 17); ok = false; break; }
+                if (j >= 1 && !mbar_wait(&bars->o_empty, (j - 1) & 1)) { atomicExch(err, 18); ok = false; break; }
+                tc_fence_after();
+#pragma unroll
+                for (int kk = 0; kk < 8; ++kk) {                         // 128 keys = 8 MMAs of K = 16
+                    const uint64_t da = make_desc_sw128(smem_u32(sP + (kk / 4) * TILE_HALF_BYTES)) + 2 * (kk % 4);
+                    const uint64_t db = make_desc_sw128_mn(smem_u32(sV + s * QKV_BYTES + kk * 2048), TILE_HALF_BYTES, 1024);
+                    tc_mma_bf16(tmem_o, da, db, idesc_pv, kk > 0 ? 1u : 0u);
+                }
+                tc_commit(&bars->v_empty[s]);
+                tc_commit(&bars->o_full);
+            }
+        }
+    } else {
+        const int q = warp & 3, row = q * 32 + lane;                     // TMEM lane quarter of this warp; one query row per thread
+        const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
+        const float c2 = scale * 1.4426950408889634f;
+        float o[HD];
+#pragma unroll
+        for (int i = 0; i < HD; ++i) o[i] = 0.f;
+        float m = -FLT_MAX, l = 0.f;
+        bool ok = true;
+        for (int j = 0; j < n_blk && ok; ++j) {
+            const int s = j & 1;
+            if (!mbar_wait(&bars->s_full[s], (j >> 1) & 1)) { atomicExch(err, 19); ok = false; break; }
+            tc_fence_after();
+            const bool diag = causal && j == qt;
+            const uint32_t ts = tmem_base + s * 128 + lane_addr;
+            float mx = -FLT_MAX;
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                uint32_t r[32];
+                tc_ld32(ts + c * 32, r);
+                tc_wait_ld();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const float v = (diag && c * 32 + i > row) ? -FLT_MAX : __uint_as_float(r[i]);
+                    mx = fmaxf(mx, v);
+                }
+            }
+            const float m_new = fmaxf(m, mx);
+            const float alpha = ex2f((m - m_new) * c2);
+            const float mc = m_new * c2;
+            float rowsum = 0.f;
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                uint32_t r[32];
+                tc_ld32(ts + c * 32, r);
+                tc_wait_ld();
+                uint8_t* prow = sP + (c >> 1) * TILE_HALF_BYTES + row * 128;
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    uint4 pk;
+                    __nv_bfloat162* hh = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const int i0 = 8 * k + 2 * u;
+                        float p0 = ex2f(fmaf(__uint_as_float(r[i0]), c2, -mc)), p1 = ex2f(fmaf(__uint_as_float(r[i0 + 1]), c2, -mc));
+                        if (diag) { if (c * 32 + i0 > row) p0 = 0.f; if (c * 32 + i0 + 1 > row) p1 = 0.f; }
+                        hh[u] = __floats2bfloat162_rn(p0, p1);
+                        const float2 back = __bfloat1622float2(hh[u]);   // the sum uses the rounded probabilities that the MMA sees
+                        rowsum += back.x + back.y;
+                    }
+                    const int chunk = (c & 1) * 4 + k;
+                    *reinterpret_cast<uint4*>(prow + ((chunk ^ (row & 7)) << 4)) = pk;
+                }
+            }
+            tc_fence_before();
+            mbar_arrive_(&bars->s_empty[s]);
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbar_arrive_(&bars->p_full);
+            l = l * alpha + rowsum;
+            m = m_new;
+            if (!mbar_wait(&bars->o_full, j & 1)) { atomicExch(err, 20); ok = false; break; }
+            tc_fence_after();
+#pragma unroll
+            for (int c = 0; c < HD / 32; ++c) {
+                uint32_t r[32];
+                tc_ld32(tmem_o + lane_addr + c * 32, r);
+                tc_wait_ld();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) o[c * 32 + i] = fmaf(o[c * 32 + i], alpha, __uint_as_float(r[i]));
+            }
+            tc_fence_before();
+            mbar_arrive_(&bars->o_empty);
+        }
+        if (ok) {
+            const float inv = 1.f / l;
+            const int64_t grow = (int64_t)row_q + row;
+            __nv_bfloat16* orow = out + grow * ld_o + col0;
+#pragma unroll
+            for (int k = 0; k < HD / 8; ++k) {
+                uint4 pk;
+                __nv_bfloat162* hh = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+                for (int u = 0; u < 4; ++u) hh[u] = __floats2bfloat162_rn(o[8 * k + 2 * u] * inv, o[8 * k + 2 * u + 1] * inv);
+                reinterpret_cast<uint4*>(orow)[k] = pk;
+            }
+            lse[((int64_t)b * H + h) * S + qt * 128 + row] = m * scale + logf(l);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+    }
+}
+
+template <int HD>
+int launch_fwd(const void* q, const void* k, const void* v, int64_t ld, void* out, int64_t ld_o, float* lse, int B, int S, int H, float scale,
+               bool causal, int* err, cudaStream_t st) {
+    CUtensorMap mq, mk, mv;
+    const int64_t rows = (int64_t)B * S;
+    if (!make_map(&mq, q, rows, (int64_t)H * HD, ld, 128, 64, true) || !make_map(&mk, k, rows, (int64_t)H * HD, ld, 128, 64, true) ||
+        !make_map(&mv, v, rows, (int64_t)H * HD, ld, 128, 64, true)) return 1;
+    constexpr size_t smem = (size_t)(5 * (HD / 64) + 2) * TILE_HALF_BYTES + sizeof(FaBars) + 1024;
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(flash_fwd_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return 2;
+        configured = true;
+    }
+    count_launch();
+    flash_fwd_kernel<HD><<<dim3(S / 128, H, B), FA_THREADS, smem, st>>>(mq, mk, mv, (__nv_bfloat16*)out, lse, S, H, ld_o, scale, causal ? 1 : 0, err);
+    return cudaGetLastError() == cudaSuccess ? 0 : 3;
+}
+
+}  // namespace
+
+bool flash_attn_supported(int S, int HD) { return S % 128 == 0 && (HD == 64 || HD == 128); }
+
+// q, k, v: bf16 [B, S, H, HD] with a common row pitch `ld` (elements between consecutive positions; >= H*HD); out: [B, S, H, HD] with
+// row pitch ld_o; lse: fp32 [B, H, S].  Returns 0 on success.
+int flash_attn_fwd(const void* q, const void* k, const void* v, int64_t ld, void* out, int64_t ld_o, float* lse, int B, int S, int H, int HD,
+                   float scale, bool causal, int* err, cudaStream_t st) {
+    if (!flash_attn_supported(S, HD)) return 6;
+    if (HD == 128) return launch_fwd<128>(q, k, v, ld, out, ld_o, lse, B, S, H, scale, causal, err, st);
+    return launch_fwd<64>(q, k, v, ld, out, ld_o, lse, B, S, H, scale, causal, err, st);
+}
+
+}  // namespace sg

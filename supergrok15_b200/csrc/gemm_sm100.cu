@@ -485,7 +485,8 @@ __global__ void __launch_bounds__(256) gemm_splitk_reduce_kernel(const float* __
 }
 
 // ---- host side -------------------------------------------------------------------------------------------------
-bool make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int64_t ld_elems, int box_rows, int box_cols, bool bf16) {
+}  // namespace
+bool tc::make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int64_t ld_elems, int box_rows, int box_cols, bool bf16) {
     const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
     const cuuint64_t strides[1] = {(cuuint64_t)ld_elems * (bf16 ? 2 : 4)};
     const cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
@@ -506,6 +507,7 @@ bool make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, in
                                               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS;
 }
+namespace {
 
 int num_sms() {
     static int n = 0;

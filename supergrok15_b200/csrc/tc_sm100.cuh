@@ -74,5 +74,25 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void*
                  ::"l"(map), "r"(smem_u32(src)), "r"(c0), "r"(c1) : "memory");
 }
 
+// MN-major operand tile (the operand's M or N index is the contiguous one), 128-byte swizzle: rows of 128 bytes = 64 bf16 along
+// MN, one row per K index, 8-row groups `sbo` bytes apart (1024 when the rows are dense), successive 64-element MN chunks `lbo`
+// bytes apart.  This is what a TMA box of [K rows x 64 columns] leaves in shared memory.
+__device__ __forceinline__ uint64_t make_desc_sw128_mn(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3ffff) >> 4);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3fff) << 16;
+    d |= (uint64_t)((sbo_bytes >> 4) & 0x3fff) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+// instruction descriptor of kind::f16 with bf16 operands and an fp32 accumulator; b_mn = 1 when B is MN-major
+__host__ __device__ constexpr uint32_t make_idesc_bf16(int M, int N, int a_mn, int b_mn) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)a_mn << 15) | ((uint32_t)b_mn << 16) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+
+// host: 2-D tiled tensor map with 128-byte swizzle over a row-major matrix (defined in gemm_sm100.cu)
+bool make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int64_t ld_elems, int box_rows, int box_cols, bool bf16);
+
 }  // namespace tc
 }  // namespace sg

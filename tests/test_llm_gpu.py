@@ -150,3 +150,24 @@ def test_llama_tiny_matches_reference_ops():
     out_ref.float().pow(2).mean().backward()
     for (n, p), (_, q) in zip(model.named_parameters(), ref.named_parameters()):
         torch.testing.assert_close(p.grad.cpu(), q.grad, rtol=5e-3, atol=2e-4, msg=lambda m, n=n: f"{n}: {m}")
+
+
+@pytest.mark.parametrize("shape", [(1, 128, 1, 128, True), (2, 256, 2, 128, True), (1, 512, 2, 64, True), (2, 384, 3, 128, False)])
+def test_flash_attention_forward(shape):
+    """tcgen05 flash attention (K-major Q/K/P operands, MN-major V operand) against fp32 PyTorch attention."""
+    from supergrok15_b200.ops import gemm, nn_ops
+    dev = _dev()
+    B, S, H, HD, causal = shape
+    torch.manual_seed(6)
+    qkv = torch.randn(B, S, 3, H, HD, device=dev).to(torch.bfloat16)
+    for q, k, v in [tuple(t.contiguous() for t in qkv.unbind(2)), qkv.unbind(2)]:       # contiguous tensors, then strided views
+        if not nn_ops.flash_supported(q, k, v):
+            continue
+        q = q.detach().requires_grad_(True)
+        out = nn_ops.attention(q, k, v, causal, impl="tcgen05")
+        torch.cuda.synchronize()
+        gemm.check(dev)
+        ref = nn_ops.attention_reference(q.detach().float(), k.float(), v.float(), causal)
+        torch.testing.assert_close(out.float(), ref, rtol=2e-2, atol=2e-2)
+        out.float().sum().backward()
+        assert torch.isfinite(q.grad).all()

@@ -24,6 +24,11 @@ void sg2_scan_backward(const void* items_dev, int n_items, int dir1_start, const
                        float* snaps, float* partial, float* grads, cudaStream_t s);
 }
 
+namespace sg {
+void sg2_recycle(int* counts, float* W1, float* b1, float* W2, float* b2, float* const* keyA, float* const* keyB, float threshold,
+                 uint32_t seed, uint32_t call, int* info, cudaStream_t s);
+}
+
 namespace sgb {
 namespace {
 using at::Tensor;
@@ -130,6 +135,26 @@ py::dict sg2_layout() {
     d["sort_tile"] = 4096;
     return d;
 }
+
+// Device-side expert recycling: the parameters are modified in place, the counts are cleared; nothing is read back.
+void sg2_recycle_b(at::Tensor counts, at::Tensor W1, at::Tensor b1, at::Tensor W2, at::Tensor b2, std::vector<at::Tensor> keys_a,
+                   std::vector<at::Tensor> keys_b, double threshold, int64_t seed, int64_t call, at::Tensor info) {
+    TORCH_CHECK(counts.is_cuda() && counts.scalar_type() == at::kInt && counts.numel() == sg::SG2_NE && counts.is_contiguous(), "counts: int32 [144]");
+    auto chk = [](const at::Tensor& t, int64_t n, const char* what) {
+        TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kFloat && t.is_contiguous() && t.numel() == n, what, ": contiguous fp32 CUDA tensor of ", n, " elements");
+    };
+    chk(W1, sg::SG2_NE * sg::SG2_EH, "W1"); chk(b1, sg::SG2_NE * sg::SG2_EH, "b1"); chk(W2, sg::SG2_NE * sg::SG2_EH, "W2"); chk(b2, sg::SG2_NE, "b2");
+    TORCH_CHECK((int)keys_a.size() == sg::SG2_HEADS && (int)keys_b.size() == sg::SG2_HEADS, "four heads of sub-keys expected");
+    float* ka[sg::SG2_HEADS]; float* kb[sg::SG2_HEADS];
+    for (int h = 0; h < sg::SG2_HEADS; ++h) {
+        chk(keys_a[h], sg::SG2_PK * 4, "keys_a"); chk(keys_b[h], sg::SG2_PK * 4, "keys_b");
+        ka[h] = keys_a[h].data_ptr<float>(); kb[h] = keys_b[h].data_ptr<float>();
+    }
+    TORCH_CHECK(info.is_cuda() && info.scalar_type() == at::kInt && info.numel() >= 2, "info: int32 [2]");
+    c10::cuda::CUDAGuard guard(counts.device());
+    sg::sg2_recycle(counts.data_ptr<int>(), W1.data_ptr<float>(), b1.data_ptr<float>(), W2.data_ptr<float>(), b2.data_ptr<float>(), ka, kb,
+                    (float)threshold, (uint32_t)seed, (uint32_t)call, info.data_ptr<int>(), at::cuda::getCurrentCUDAStream());
+}
 }  // namespace
 
 void register_sg2(pybind11::module_& m) {
@@ -142,6 +167,8 @@ void register_sg2(pybind11::module_& m) {
     m.def("sg2_upload_weights", &sg2_upload_weights);
     m.def("sg2_sort", &sg2_sort);
     m.def("sg2_layout", &sg2_layout);
+    m.def("sg2_recycle", &sg2_recycle_b, py::arg("counts"), py::arg("W1"), py::arg("b1"), py::arg("W2"), py::arg("b2"), py::arg("keys_a"),
+          py::arg("keys_b"), py::arg("threshold"), py::arg("seed"), py::arg("call"), py::arg("info"));
     m.def("sg2_scan_backward", &sg2_scan_backward);
     m.def("sg2_bilevel_info", []() { py::dict d; d["ng"] = sg::sg2_bilevel_ng(); d["tile"] = sg::sg2_bilevel_tile();
                                      d["smem"] = (int64_t)sg::sg2_bilevel_smem_bytes(); return d; });

@@ -59,6 +59,7 @@ class SuperGrok2(SuperGrok15):
         # recycling draws come from a private CPU generator so every data-parallel rank makes the same choice
         self._recycle_gen = torch.Generator(device="cpu")
         self._recycle_gen.manual_seed(recycle_seed)
+        self._recycle_seed, self._recycle_calls, self._recycle_info = recycle_seed, 0, None
         self._native_plan = None
 
     # ------------------------------------------------------------------ state
@@ -103,13 +104,27 @@ class SuperGrok2(SuperGrok15):
         sg2_ops.step(self, idx, per, beta2=beta2, lr=lr, wd_eff=wd_eff, eps=eps, clip=self.gradient_clipping)
         self._step_counter += 1
         ri = self.meta_net.recycle_interval
-        if ri > 0 and self._step_counter % ri == 0:
+        if ri > 0 and self._step_counter % ri == 0 and not getattr(self, "_external_recycle", False):
             self.recycle_dead_experts()
         return loss
 
     def recycle_dead_experts(self):
-        """Expert recycling (reference mamba3_peer_metanet.py:437-491) with a reproducible generator."""
-        self.meta_net._recycle_dead_experts(generator=self._recycle_gen)
+        """Expert recycling (reference mamba3_peer_metanet.py:437-491).  On CUDA the whole decision runs in one device kernel
+        (Philox keyed by the recycle seed and the call number: identical on every data-parallel rank, no host read-back);
+        on CPU a private generator makes the draw reproducible."""
+        mn = self.meta_net
+        if mn.expert_counts.is_cuda:
+            from .. import _build
+            C = _build.require()
+            self._recycle_calls = getattr(self, "_recycle_calls", 0) + 1
+            if getattr(self, "_recycle_info", None) is None:
+                self._recycle_info = torch.zeros(2, dtype=torch.int32, device=mn.expert_counts.device)
+            # the parameters keep their shapes ([144,16,1], [144,16], [144,1,16], [144,1]); the kernel sees them as flat rows
+            C.sg2_recycle(mn.expert_counts, mn.expert_W1.data.view(-1), mn.expert_b1.data.view(-1), mn.expert_W2.data.view(-1),
+                          mn.expert_b2.data.view(-1), [k.data for k in mn.product_keys_A], [k.data for k in mn.product_keys_B],
+                          float(mn.recycle_threshold), int(self._recycle_seed), int(self._recycle_calls), self._recycle_info)
+        else:
+            mn._recycle_dead_experts(generator=self._recycle_gen)
         self._weights_dirty = True
 
     # ------------------------------------------------------------------ bilevel
@@ -145,10 +160,12 @@ class SuperGrok2(SuperGrok15):
         ex = super()._extra_state()
         ex["step_counter"] = self._step_counter
         ex["recycle_rng"] = self._recycle_gen.get_state()
+        ex["recycle_calls"] = self._recycle_calls
         return ex
 
     def _load_extra_state(self, extra):
         super()._load_extra_state(extra)
         self._step_counter = int(extra.get("step_counter", 0))
+        self._recycle_calls = int(extra.get("recycle_calls", 0))
         if "recycle_rng" in extra:
             self._recycle_gen.set_state(extra["recycle_rng"])

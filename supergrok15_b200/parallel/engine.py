@@ -138,6 +138,7 @@ class ZeroEngine:
             views = [torch.nn.Parameter(self.params[i].data, requires_grad=False) for i in own] or \
                     [torch.nn.Parameter(torch.zeros(0, device=self.device))]
             self.opt = cls(views, **kw)
+            self.opt._external_recycle = True                         # recycling runs in step() below, after the counts are summed
             if own:
                 self.opt._ensure_state()
                 self.opt._flat_masters = [mv.data.reshape(-1) for mv in self.master_views]
@@ -259,6 +260,17 @@ class ZeroEngine:
                 self.opt.step(**metrics)
             else:
                 self.opt._global_step += 1
+            # Expert recycling is driven here so that every rank does it at the same step on the same counts: each rank routed only
+            # the tensors it owns, so the 144 activation counts are summed over the ranks first (deterministic slot all-reduce).
+            self._v2_steps = getattr(self, "_v2_steps", 0) + 1
+            ri = self.opt.meta_net.recycle_interval
+            if ri > 0 and self._v2_steps % ri == 0:
+                counts = self.opt.meta_net.expert_counts
+                if W > 1:
+                    cf = counts.float()
+                    self.all_reduce_small(cf)
+                    counts.copy_(cf.clamp_(max=2.0e9).to(counts.dtype))
+                self.opt.recycle_dead_experts()
             if not (fused and W > 1):
                 pass                                                  # parameters were written in place by the element kernel
         else:

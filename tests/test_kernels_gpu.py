@@ -246,3 +246,58 @@ def test_engine_reports_comm_timeout():
     with pytest.raises(CommTimeout, match="peer 3"):
         eng.check()
     eng.check()                                                       # cleared
+
+
+def test_device_expert_recycling():
+    """One-CTA device recycling: dead experts become noisy clones of one live donor, fully dead key rows are re-drawn, counts are
+    cleared, nothing happens without activations, and the same (seed, call) gives bit-identical results (rank identity)."""
+    import copy
+    from supergrok15_b200.optim import SuperGrok2
+    dev = torch.device("cuda:0")
+    torch.manual_seed(0)
+    model = torch.nn.Linear(16, 16).to(dev)
+    opt = SuperGrok2(model.parameters(), recycle_seed=5)
+    mn = opt.meta_net
+    assert mn.expert_counts.is_cuda
+    before = copy.deepcopy(mn.state_dict())
+    opt.recycle_dead_experts()                                     # no activations yet: nothing may change
+    torch.cuda.synchronize()
+    for k, v in mn.state_dict().items():
+        assert torch.equal(v, before[k]), k
+    counts = torch.full((144,), 1000, dtype=torch.int32, device=dev)
+    dead = list(range(12)) + [40, 77]                              # a whole row of sub-key A (experts 0..11) plus two singles
+    counts[dead] = 0
+    counts[100] = 500000                                           # the most likely donor
+    opt2 = SuperGrok2(torch.nn.Linear(16, 16).to(dev).parameters(), recycle_seed=5)
+    opt2.meta_net.load_state_dict(mn.state_dict())
+    for o in (opt, opt2):
+        o.meta_net.expert_counts.copy_(counts)
+        o._recycle_calls = 0
+        o.recycle_dead_experts()
+    torch.cuda.synchronize()
+    info = opt._recycle_info.cpu().tolist()
+    assert info[0] == len(dead) and info[1] >= 12 and info[1] not in dead
+    donor = info[1]
+    after = mn.state_dict()
+    for k in after:                                                # identical on two "ranks"
+        assert torch.equal(after[k], opt2.meta_net.state_dict()[k]), k
+    assert int(mn.expert_counts.abs().sum()) == 0
+    W1b, W1a = before["expert_W1"].view(144, 16), after["expert_W1"].view(144, 16)
+    live = [i for i in range(144) if i not in dead]
+    assert torch.equal(W1a[live], W1b[live])
+    noise = (W1a[dead] - W1b[donor]).flatten()
+    assert 0.005 < float(noise.std()) < 0.02 and float(noise.abs().max()) < 0.06
+    b2n = (after["expert_b2"].view(144)[dead] - before["expert_b2"].view(144)[donor])
+    assert float(b2n.abs().max()) < 0.06 and float(b2n.abs().max()) > 0
+    for h in range(4):
+        ka_b, ka_a = before[f"product_keys_A.{h}"], after[f"product_keys_A.{h}"]
+        assert not torch.equal(ka_a[0], ka_b[0]) and torch.equal(ka_a[1:], ka_b[1:])        # only row 0 of A died completely
+        assert float(ka_a[0].abs().max()) < 0.12
+        assert torch.equal(after[f"product_keys_B.{h}"], before[f"product_keys_B.{h}"])
+    # a second call with live counts only clears them
+    mn.expert_counts.fill_(7)
+    snap = copy.deepcopy(mn.state_dict())
+    opt.recycle_dead_experts()
+    torch.cuda.synchronize()
+    assert int(mn.expert_counts.sum()) == 0
+    assert torch.equal(mn.state_dict()["expert_W1"], snap["expert_W1"])

@@ -18,7 +18,7 @@ void ce_bwd(int dtype, const void* logits, const int64_t* target, const float* l
             int64_t rows, int V, int64_t ignore_index, cudaStream_t st);
 bool flash_attn_supported(int S, int HD);
 int flash_attn_fwd(const void* q, const void* k, const void* v, int64_t ld, void* out, int64_t ld_o, float* lse, int B, int S, int H, int HD,
-                   float scale, bool causal, int* err, cudaStream_t st);
+                   float scale, bool causal, int variant, int* err, cudaStream_t st);
 }
 
 namespace sgb {
@@ -154,7 +154,7 @@ void check_qkv(const Tensor& t, const Tensor& q, const char* what) {
                 t.stride(1) % 8 == 0 && (reinterpret_cast<uintptr_t>(t.data_ptr()) & 15) == 0, what, ": unsupported strides");
 }
 
-std::vector<Tensor> flash_fwd(const Tensor& q, const Tensor& k, const Tensor& v, bool causal, Tensor err) {
+std::vector<Tensor> flash_fwd(const Tensor& q, const Tensor& k, const Tensor& v, bool causal, Tensor err, int64_t variant) {
     check_qkv(q, q, "q"); check_qkv(k, q, "k"); check_qkv(v, q, "v");
     const int B = (int)q.size(0), S = (int)q.size(1), H = (int)q.size(2), HD = (int)q.size(3);
     TORCH_CHECK(sg::flash_attn_supported(S, HD), "flash attention: S must be a multiple of 128 and head_dim 64 or 128");
@@ -162,7 +162,7 @@ std::vector<Tensor> flash_fwd(const Tensor& q, const Tensor& k, const Tensor& v,
     Tensor out = at::empty({B, S, H, HD}, q.options());
     Tensor lse = at::empty({B, H, S}, q.options().dtype(at::kFloat));
     const int rc = sg::flash_attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), q.stride(1), out.data_ptr(), (int64_t)H * HD, lse.data_ptr<float>(), B, S,
-                                      H, HD, 1.f / std::sqrt((float)HD), causal, err.data_ptr<int>(), at::cuda::getCurrentCUDAStream());
+                                      H, HD, 1.f / std::sqrt((float)HD), causal, (int)variant, err.data_ptr<int>(), at::cuda::getCurrentCUDAStream());
     TORCH_CHECK(rc == 0, "flash_fwd launch failed (code ", rc, ")");
     return {out, lse};
 }
@@ -176,7 +176,7 @@ void register_llm(pybind11::module_& m) {
     m.def("gelu_bwd", &gelu_bwd);
     m.def("embedding_fwd", &embedding_fwd);
     m.def("embedding_bwd", &embedding_bwd);
-    m.def("flash_fwd", &flash_fwd);
+    m.def("flash_fwd", &flash_fwd, py::arg("q"), py::arg("k"), py::arg("v"), py::arg("causal"), py::arg("err"), py::arg("variant") = 2);
     m.def("flash_supported", [](int64_t S, int64_t HD) { return sg::flash_attn_supported((int)S, (int)HD); });
     m.def("ce_fwd", &ce_fwd);
     m.def("ce_bwd", &ce_bwd);

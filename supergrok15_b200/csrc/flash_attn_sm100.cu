@@ -231,21 +231,229 @@ __global__ void __launch_bounds__(FA_THREADS, 1) flash_fwd_kernel(const __grid_c
     }
 }
 
+
+// ---------------------------------------------------------------------------------------------------------------------------
+// Second forward kernel: nothing of the softmax sits between two MMAs any more.
+//   * P_j never leaves the tensor memory: the softmax threads overwrite the first 64 columns of the S_j buffer with the bf16
+//     probabilities (tcgen05.st) and O += P_j V_j takes its A operand from TMEM;
+//   * O accumulates in TMEM across the key blocks (no per-block read-back).  Each row keeps a reference maximum that is only
+//     moved when the true maximum has grown by more than 8 in the exponent (probabilities then stay below 2^8); only then does
+//     the row rescale O in TMEM, after waiting for the previous P V to finish.  The final division by the row sum uses the same
+//     reference, so the result is exact;
+//   * the MMA warp issues S_{j+1} = Q K_{j+1}^T before it waits for P_j: tcgen05.mma executes in issue order, so S_{j+1} lands in
+//     the buffer whose P_{j-1} has just been consumed, and the tensor pipe alternates QK / PV while the softmax of the next block
+//     runs.
+struct Fa2Bars {
+    uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_full, o_done[2];
+    uint32_t tmem_slot, pad;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(FA_THREADS, 1) flash_fwd2_kernel(const __grid_constant__ CUtensorMap map_q,
+                                                                   const __grid_constant__ CUtensorMap map_k,
+                                                                   const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
+                                                                   float* __restrict__ lse, int S, int H, int64_t ld_o, float scale,
+                                                                   int causal, int* __restrict__ err) {
+    constexpr int HALVES = HD / 64;
+    constexpr uint32_t QKV_BYTES = HALVES * TILE_HALF_BYTES;
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t* sQ = smem;
+    uint8_t* sK = sQ + QKV_BYTES;                        // [2][QKV_BYTES]
+    uint8_t* sV = sK + 2 * QKV_BYTES;                    // [2][QKV_BYTES]
+    Fa2Bars* bars = reinterpret_cast<Fa2Bars*>(sV + 2 * QKV_BYTES);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int qt = (int)gridDim.x - 1 - (int)blockIdx.x;
+    const int h = blockIdx.y, b = blockIdx.z;
+    const int n_blk = causal ? qt + 1 : S / 128;
+    const int row_q = b * S + qt * 128, col0 = h * HD;
+
+    if (threadIdx.x == 0) {
+        mbar_init(&bars->q_full, 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&bars->k_full[i], 1); mbar_init(&bars->k_empty[i], 1); mbar_init(&bars->v_full[i], 1); mbar_init(&bars->v_empty[i], 1);
+            mbar_init(&bars->s_full[i], 1); mbar_init(&bars->o_done[i], 1);
+        }
+        mbar_init(&bars->p_full, 128);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bars->tmem_slot)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = bars->tmem_slot;
+    const uint32_t tmem_o = tmem_base + 256;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            mbar_expect_tx(&bars->q_full, QKV_BYTES);
+            for (int hf = 0; hf < HALVES; ++hf) tma_load_2d(sQ + hf * TILE_HALF_BYTES, &map_q, col0 + hf * 64, row_q, &bars->q_full);
+            for (int j = 0; j < n_blk; ++j) {
+                const int s = j & 1, row_k = b * S + j * 128;
+                if (j >= 2 && !mbar_wait(&bars->k_empty[s], ((j >> 1) & 1) ^ 1)) { atomicExch(err, 21); break; }
+                mbar_expect_tx(&bars->k_full[s], QKV_BYTES);
+                for (int hf = 0; hf < HALVES; ++hf) tma_load_2d(sK + s * QKV_BYTES + hf * TILE_HALF_BYTES, &map_k, col0 + hf * 64, row_k, &bars->k_full[s]);
+                if (j >= 2 && !mbar_wait(&bars->v_empty[s], ((j >> 1) & 1) ^ 1)) { atomicExch(err, 22); break; }
+                mbar_expect_tx(&bars->v_full[s], QKV_BYTES);
+                for (int hf = 0; hf < HALVES; ++hf) tma_load_2d(sV + s * QKV_BYTES + hf * TILE_HALF_BYTES, &map_v, col0 + hf * 64, row_k, &bars->v_full[s]);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc_qk = make_idesc_bf16(128, 128, 0, 0);
+            constexpr uint32_t idesc_pv = make_idesc_bf16(128, HD, 0, 1);
+            bool ok = mbar_wait(&bars->q_full, 0);
+            if (!ok) atomicExch(err, 23);
+            tc_fence_after();
+            auto issue_qk = [&](int j) -> bool {
+                const int s = j & 1;
+                if (!mbar_wait(&bars->k_full[s], (j >> 1) & 1)) { atomicExch(err, 24); return false; }
+                tc_fence_after();
+#pragma unroll
+                for (int kk = 0; kk < HD / 16; ++kk) {
+                    const uint64_t da = make_desc_sw128(smem_u32(sQ + (kk / 4) * TILE_HALF_BYTES)) + 2 * (kk % 4);
+                    const uint64_t db = make_desc_sw128(smem_u32(sK + s * QKV_BYTES + (kk / 4) * TILE_HALF_BYTES)) + 2 * (kk % 4);
+                    tc_mma_bf16(tmem_base + s * 128, da, db, idesc_qk, kk > 0 ? 1u : 0u);
+                }
+                tc_commit(&bars->k_empty[s]);
+                tc_commit(&bars->s_full[s]);
+                return true;
+            };
+            if (ok) ok = issue_qk(0);
+            for (int j = 0; j < n_blk && ok; ++j) {
+                if (j + 1 < n_blk) { ok = issue_qk(j + 1); if (!ok) break; }
+                const int s = j & 1;
+                if (!mbar_wait(&bars->v_full[s], (j >> 1) & 1)) { atomicExch(err, 26); ok = false; break; }
+                if (!mbar_wait(&bars->p_full, j & 1)) { atomicExch(err, 27); ok = false; break; }
+                tc_fence_after();
+#pragma unroll
+                for (int kk = 0; kk < 8; ++kk) {
+                    const uint64_t db = make_desc_sw128_mn(smem_u32(sV + s * QKV_BYTES + kk * 2048), TILE_HALF_BYTES, 1024);
+                    tc_mma_bf16_ta(tmem_o, tmem_base + s * 128 + kk * 8, db, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+                }
+                tc_commit(&bars->v_empty[s]);
+                tc_commit(&bars->o_done[s]);
+            }
+        }
+    } else {
+        const int q = warp & 3, row = q * 32 + lane;
+        const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
+        const float c2 = scale * 1.4426950408889634f;
+        float m_ref = -FLT_MAX, l = 0.f;
+        bool ok = true;
+        for (int j = 0; j < n_blk && ok; ++j) {
+            const int s = j & 1;
+            if (!mbar_wait(&bars->s_full[s], (j >> 1) & 1)) { atomicExch(err, 28); ok = false; break; }
+            tc_fence_after();
+            const bool diag = causal && j == qt;
+            const uint32_t ts = tmem_base + s * 128 + lane_addr;
+            uint32_t r[4][32];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) tc_ld32(ts + c * 32, r[c]);
+            tc_wait_ld();
+            float mx = -FLT_MAX;
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    if (diag && c * 32 + i > row) r[c][i] = __float_as_uint(-FLT_MAX);
+                    mx = fmaxf(mx, __uint_as_float(r[c][i]));
+                }
+            float alpha = 1.f;
+            bool move = false;
+            if (j == 0) m_ref = mx;
+            else if ((mx - m_ref) * c2 > 8.f) { alpha = ex2f((m_ref - mx) * c2); m_ref = mx; move = true; }
+            if (j > 0 && __any_sync(0xffffffffu, move)) {
+                // O holds the sum up to block j-1 relative to the old reference: wait for P_{j-1} V_{j-1}, then rescale this row in place
+                if (!mbar_wait(&bars->o_done[(j - 1) & 1], ((j - 1) >> 1) & 1)) { atomicExch(err, 29); ok = false; break; }
+                tc_fence_after();
+#pragma unroll 1
+                for (int c = 0; c < HD / 32; ++c) {
+                    uint32_t t[32];
+                    tc_ld32(tmem_o + lane_addr + c * 32, t);
+                    tc_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) t[i] = __float_as_uint(__uint_as_float(t[i]) * alpha);
+                    tc_st32(tmem_o + lane_addr + c * 32, t);
+                }
+            }
+            const float mc = m_ref * c2;
+            float rowsum = 0.f;
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {                                // 64 keys -> 32 packed columns per store
+                uint32_t pk[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const int k0 = c * 64 + 2 * i;
+                    const float p0 = ex2f(fmaf(__uint_as_float(r[k0 >> 5][k0 & 31]), c2, -mc));
+                    const float p1 = ex2f(fmaf(__uint_as_float(r[(k0 + 1) >> 5][(k0 + 1) & 31]), c2, -mc));
+                    const __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
+                    const float2 back = __bfloat1622float2(hh);
+                    rowsum += back.x + back.y;
+                    pk[i] = *reinterpret_cast<const uint32_t*>(&hh);
+                }
+                tc_st32(ts + c * 32, pk);
+            }
+            tc_wait_st();
+            tc_fence_before();
+            mbar_arrive_(&bars->p_full);
+            l = l * alpha + rowsum;
+        }
+        if (ok && !mbar_wait(&bars->o_done[(n_blk - 1) & 1], ((n_blk - 1) >> 1) & 1)) { atomicExch(err, 30); ok = false; }
+        if (ok) {
+            tc_fence_after();
+            const float inv = 1.f / l;
+            const int64_t grow = (int64_t)row_q + row;
+            __nv_bfloat16* orow = out + grow * ld_o + col0;
+#pragma unroll 1
+            for (int c = 0; c < HD / 32; ++c) {
+                uint32_t t[32];
+                tc_ld32(tmem_o + lane_addr + c * 32, t);
+                tc_wait_ld();
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    uint4 pk;
+                    __nv_bfloat162* hh = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) hh[u] = __floats2bfloat162_rn(__uint_as_float(t[8 * k + 2 * u]) * inv, __uint_as_float(t[8 * k + 2 * u + 1]) * inv);
+                    reinterpret_cast<uint4*>(orow)[c * 4 + k] = pk;
+                }
+            }
+            lse[((int64_t)b * H + h) * S + qt * 128 + row] = m_ref * scale + logf(l);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+    }
+}
+
 template <int HD>
 int launch_fwd(const void* q, const void* k, const void* v, int64_t ld, void* out, int64_t ld_o, float* lse, int B, int S, int H, float scale,
-               bool causal, int* err, cudaStream_t st) {
+               bool causal, int variant, int* err, cudaStream_t st) {
     CUtensorMap mq, mk, mv;
     const int64_t rows = (int64_t)B * S;
     if (!make_map(&mq, q, rows, (int64_t)H * HD, ld, 128, 64, true) || !make_map(&mk, k, rows, (int64_t)H * HD, ld, 128, 64, true) ||
         !make_map(&mv, v, rows, (int64_t)H * HD, ld, 128, 64, true)) return 1;
     constexpr size_t smem = (size_t)(5 * (HD / 64) + 2) * TILE_HALF_BYTES + sizeof(FaBars) + 1024;
+    constexpr size_t smem2 = (size_t)(5 * (HD / 64)) * TILE_HALF_BYTES + sizeof(Fa2Bars) + 1024;
     static bool configured = false;
     if (!configured) {
         if (cudaFuncSetAttribute(flash_fwd_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return 2;
+        if (cudaFuncSetAttribute(flash_fwd2_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2) != cudaSuccess) return 2;
         configured = true;
     }
     count_launch();
-    flash_fwd_kernel<HD><<<dim3(S / 128, H, B), FA_THREADS, smem, st>>>(mq, mk, mv, (__nv_bfloat16*)out, lse, S, H, ld_o, scale, causal ? 1 : 0, err);
+    if (variant == 2)
+        flash_fwd2_kernel<HD><<<dim3(S / 128, H, B), FA_THREADS, smem2, st>>>(mq, mk, mv, (__nv_bfloat16*)out, lse, S, H, ld_o, scale, causal ? 1 : 0, err);
+    else
+        flash_fwd_kernel<HD><<<dim3(S / 128, H, B), FA_THREADS, smem, st>>>(mq, mk, mv, (__nv_bfloat16*)out, lse, S, H, ld_o, scale, causal ? 1 : 0, err);
     return cudaGetLastError() == cudaSuccess ? 0 : 3;
 }
 
@@ -254,12 +462,13 @@ int launch_fwd(const void* q, const void* k, const void* v, int64_t ld, void* ou
 bool flash_attn_supported(int S, int HD) { return S % 128 == 0 && (HD == 64 || HD == 128); }
 
 // q, k, v: bf16 [B, S, H, HD] with a common row pitch `ld` (elements between consecutive positions; >= H*HD); out: [B, S, H, HD] with
-// row pitch ld_o; lse: fp32 [B, H, S].  Returns 0 on success.
+// row pitch ld_o; lse: fp32 [B, H, S].  variant 1: P through shared memory, O in registers; variant 2: P and O stay in TMEM.
+// Returns 0 on success.
 int flash_attn_fwd(const void* q, const void* k, const void* v, int64_t ld, void* out, int64_t ld_o, float* lse, int B, int S, int H, int HD,
-                   float scale, bool causal, int* err, cudaStream_t st) {
+                   float scale, bool causal, int variant, int* err, cudaStream_t st) {
     if (!flash_attn_supported(S, HD)) return 6;
-    if (HD == 128) return launch_fwd<128>(q, k, v, ld, out, ld_o, lse, B, S, H, scale, causal, err, st);
-    return launch_fwd<64>(q, k, v, ld, out, ld_o, lse, B, S, H, scale, causal, err, st);
+    if (HD == 128) return launch_fwd<128>(q, k, v, ld, out, ld_o, lse, B, S, H, scale, causal, variant, err, st);
+    return launch_fwd<64>(q, k, v, ld, out, ld_o, lse, B, S, H, scale, causal, variant, err, st);
 }
 
 }  // namespace sg

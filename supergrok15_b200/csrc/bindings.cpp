@@ -56,6 +56,10 @@ void mt_apply(int op, const std::vector<std::vector<Tensor>>& roles, const std::
         }
     if (n == 0) return;
     TORCH_CHECK(first != nullptr, "role 0 or 1 must be present");
+    if (first->device().is_cpu()) {                 // fp32 CPU tensors: the C++ CPU kernels (csrc/cpu_kernels.cpp), same ops and formulas
+        sgb::cpu_mt_apply(op, roles, ts, f, clip, dscal, tscal, W1, b1, W2, b2, hidden, write_grad, per_tensor_out);
+        return;
+    }
     TORCH_CHECK(first->is_cuda(), "mt_apply needs CUDA tensors");
     const int dt = dtype_code(*first);
     c10::cuda::CUDAGuard guard(first->device());
@@ -112,6 +116,7 @@ void mt_apply(int op, const std::vector<std::vector<Tensor>>& roles, const std::
 }
 
 void scalar_finalize(int op, const Tensor& per_tensor, int64_t n_tensors, Tensor out, double a0, double a1, double a2) {
+    if (out.device().is_cpu()) { sgb::cpu_scalar_finalize(op, per_tensor, n_tensors, out, a0, a1, a2); return; }
     c10::cuda::CUDAGuard guard(out.device());
     sg::scalar_finalize(op, per_tensor.data_ptr<float>(), (int)n_tensors, out.data_ptr<float>(), (float)a0, (float)a1,
                         (float)a2, at::cuda::getCurrentCUDAStream());
@@ -130,6 +135,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           py::arg("partials") = c10::nullopt, py::arg("per_tensor_out") = c10::nullopt);
     m.def("scalar_finalize", &scalar_finalize);
     m.def("launch_count", []() { return sg::launch_count(); });
+    // kernels that run from a replayed CUDA graph are not enqueued by a launcher: the owner of the graph adds them here
+    m.def("add_launches", [](int64_t n) { sg::count_launch((int)n); });
     py::dict ops;
 #define SG_OP(X) ops[#X] = (int)sg::X;
     SG_OP(OP_ADAMW) SG_OP(OP_LION) SG_OP(OP_GROKFAST_EMA) SG_OP(OP_GROKFAST_ADAMW) SG_OP(OP_GROKADAMW)

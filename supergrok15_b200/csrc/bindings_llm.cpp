@@ -19,6 +19,8 @@ void ce_bwd(int dtype, const void* logits, const int64_t* target, const float* l
 bool flash_attn_supported(int S, int HD);
 int flash_attn_fwd(const void* q, const void* k, const void* v, int64_t ld, void* out, int64_t ld_o, float* lse, int B, int S, int H, int HD,
                    float scale, bool causal, int variant, int* err, cudaStream_t st);
+int flash_attn_bwd(const void* q, const void* k, const void* v, int64_t ld, const void* o, const void* dout, int64_t ld_o, const float* lse,
+                   float* delta, void* dq, void* dk, void* dv, int B, int S, int H, int HD, float scale, bool causal, int* err, cudaStream_t st);
 }
 
 namespace sgb {
@@ -166,6 +168,26 @@ std::vector<Tensor> flash_fwd(const Tensor& q, const Tensor& k, const Tensor& v,
     TORCH_CHECK(rc == 0, "flash_fwd launch failed (code ", rc, ")");
     return {out, lse};
 }
+
+// gradients of flash_fwd: returns (dq, dk, dv), contiguous [B, S, H, HD]
+std::vector<Tensor> flash_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& out, const Tensor& lse, const Tensor& dout_, bool causal,
+                              Tensor err) {
+    check_qkv(q, q, "q"); check_qkv(k, q, "k"); check_qkv(v, q, "v");
+    Tensor dout = dout_.contiguous();
+    TORCH_CHECK(out.is_contiguous() && out.sizes() == q.sizes() && dout.sizes() == q.sizes() && dout.scalar_type() == at::kBFloat16 &&
+                out.scalar_type() == at::kBFloat16, "out / dout must be contiguous bf16 [B, S, H, HD]");
+    const int B = (int)q.size(0), S = (int)q.size(1), H = (int)q.size(2), HD = (int)q.size(3);
+    TORCH_CHECK(lse.is_contiguous() && lse.scalar_type() == at::kFloat && lse.numel() == (int64_t)B * H * S, "lse: fp32 [B, H, S]");
+    c10::cuda::CUDAGuard guard(q.device());
+    Tensor dq = at::empty({B, S, H, HD}, q.options()), dk = at::empty({B, S, H, HD}, q.options()), dv = at::empty({B, S, H, HD}, q.options());
+    Tensor delta = at::empty({B, H, S}, lse.options());
+    const int rc = sg::flash_attn_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), q.stride(1), out.data_ptr(), dout.data_ptr(), (int64_t)H * HD,
+                                      lse.data_ptr<float>(), delta.data_ptr<float>(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), B, S, H, HD,
+                                      1.f / std::sqrt((float)HD), causal, err.data_ptr<int>(), at::cuda::getCurrentCUDAStream());
+    TORCH_CHECK(rc == 0, "flash_bwd launch failed (code ", rc, "): q ", q.data_ptr(), " ld ", q.stride(1), " dout ", dout.data_ptr(), " B ", B, " S ", S, " H ", H,
+                " HD ", HD);
+    return {dq, dk, dv};
+}
 }  // namespace
 
 void register_llm(pybind11::module_& m) {
@@ -177,6 +199,7 @@ void register_llm(pybind11::module_& m) {
     m.def("embedding_fwd", &embedding_fwd);
     m.def("embedding_bwd", &embedding_bwd);
     m.def("flash_fwd", &flash_fwd, py::arg("q"), py::arg("k"), py::arg("v"), py::arg("causal"), py::arg("err"), py::arg("variant") = 2);
+    m.def("flash_bwd", &flash_bwd);
     m.def("flash_supported", [](int64_t S, int64_t HD) { return sg::flash_attn_supported((int)S, (int)HD); });
     m.def("ce_fwd", &ce_fwd);
     m.def("ce_bwd", &ce_bwd);

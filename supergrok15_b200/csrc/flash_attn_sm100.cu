@@ -457,6 +457,281 @@ int launch_fwd(const void* q, const void* k, const void* v, int64_t ld, void* ou
     return cudaGetLastError() == cudaSuccess ? 0 : 3;
 }
 
+
+// ---------------------------------------------------------------------------------------------------------------------------
+// Backward pass: two tcgen05 kernels and one small reduction, no atomics, deterministic.
+//   delta[b,h,s] = sum_d dO * O                                                       (flash_delta_kernel)
+//   kernel A, one CTA per 128 keys:   S^T = K Q_i^T, dP^T = V dO_i^T  ->  P^T, dS^T (threads, one key row each, written as bf16
+//                                     into TMEM)  ->  dV += P^T dO_i, dK += dS^T Q_i   over the query tiles i
+//   kernel B, one CTA per 128 queries: S = Q K_j^T, dP = dO V_j^T -> dS (threads) -> dQ += dS K_j   over the key tiles j
+// with P = exp(S*scale - lse), dS = P * (dP - delta); the factor `scale` of dS is applied once in the epilogues.  The second
+// operand of every accumulating product (dO_i, Q_i, K_j) is the SAME shared-memory tile that served as K-major operand of the
+// first product, read again through an MN-major descriptor - nothing is transposed or loaded twice.
+__global__ void __launch_bounds__(256) flash_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dout,
+                                                          float* __restrict__ delta, int64_t rows, int S, int H, int HD, int64_t ld_o,
+                                                          int64_t ld_do) {
+    const int lane = threadIdx.x & 31;
+    const int64_t item = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);          // (b*S + s) * H + h
+    if (item >= rows * H) return;
+    const int64_t bs = item / H;
+    const int h = (int)(item % H);
+    const __nv_bfloat16* po = o + bs * ld_o + (int64_t)h * HD;
+    const __nv_bfloat16* pd = dout + bs * ld_do + (int64_t)h * HD;
+    float acc = 0.f;
+    for (int c = lane * 2; c < HD; c += 64) {
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(po + c));
+        const float2 d = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(pd + c));
+        acc += a.x * d.x + a.y * d.y;
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+    if (lane == 0) delta[((bs / S) * H + h) * S + bs % S] = acc;
+}
+
+struct FbBars {
+    uint64_t res_full, ring_full[2], ring_empty[2], a_full, b_full, pa_full, pb_full, done;
+    uint32_t tmem_slot, pad;
+};
+
+// KV = true: kernel A (resident K, V; ring of Q_i, dO_i; outputs dK, dV).  KV = false: kernel B (resident Q, dO; ring of K_j, V_j;
+// output dQ).  In both, "first" products X = R0 . T0^T and Y = R1 . T1^T (R resident, T ring) land in TMEM columns [0,128) and
+// [128,256); the threads turn them into bf16 operands in place; the accumulating products read them from TMEM.
+template <int HD, bool KV>
+__global__ void __launch_bounds__(FA_THREADS, 1) flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q,
+                                                                  const __grid_constant__ CUtensorMap map_k,
+                                                                  const __grid_constant__ CUtensorMap map_v,
+                                                                  const __grid_constant__ CUtensorMap map_do, const float* __restrict__ lse,
+                                                                  const float* __restrict__ delta, __nv_bfloat16* __restrict__ out0,
+                                                                  __nv_bfloat16* __restrict__ out1, int S, int H, int64_t ld_out, float scale,
+                                                                  int causal, int* __restrict__ err) {
+    constexpr int HALVES = HD / 64;
+    constexpr uint32_t QKV_BYTES = HALVES * TILE_HALF_BYTES;
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t* sR0 = smem;                                 // resident: K (A) or Q (B)
+    uint8_t* sR1 = sR0 + QKV_BYTES;                      // resident: V (A) or dO (B)
+    uint8_t* sT0 = sR1 + QKV_BYTES;                      // ring [2]: Q_i (A) or K_j (B)
+    uint8_t* sT1 = sT0 + 2 * QKV_BYTES;                  // ring [2]: dO_i (A) or V_j (B)
+    float* s_lse = reinterpret_cast<float*>(sT1 + 2 * QKV_BYTES);       // [2][128] (kernel A: per-query vectors of the current tile)
+    float* s_del = s_lse + 256;                                          // [2][128]
+    FbBars* bars = reinterpret_cast<FbBars*>(s_del + 256);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nt = S / 128;
+    const int tile = KV ? (int)blockIdx.x : (int)gridDim.x - 1 - (int)blockIdx.x;     // kernel B: long query tiles first
+    const int h = blockIdx.y, b = blockIdx.z;
+    // tiles of the other sequence axis that interact with this one
+    const int first = KV ? (causal ? tile : 0) : 0;
+    const int n_it = KV ? nt - first : (causal ? tile + 1 : nt);
+    const int row_res = b * S + tile * 128, col0 = h * HD;
+
+    if (threadIdx.x == 0) {
+        mbar_init(&bars->res_full, 1);
+        for (int i = 0; i < 2; ++i) { mbar_init(&bars->ring_full[i], 1); mbar_init(&bars->ring_empty[i], 1); }
+        mbar_init(&bars->a_full, 1); mbar_init(&bars->b_full, 1); mbar_init(&bars->pa_full, 128); mbar_init(&bars->pb_full, 128);
+        mbar_init(&bars->done, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bars->tmem_slot)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = bars->tmem_slot;
+    const uint32_t tm_x = tmem_base, tm_y = tmem_base + 128, tm_acc0 = tmem_base + 256, tm_acc1 = tmem_base + 384;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            mbar_expect_tx(&bars->res_full, 2 * QKV_BYTES);
+            for (int hf = 0; hf < HALVES; ++hf) {
+                tma_load_2d(sR0 + hf * TILE_HALF_BYTES, KV ? &map_k : &map_q, col0 + hf * 64, row_res, &bars->res_full);
+                tma_load_2d(sR1 + hf * TILE_HALF_BYTES, KV ? &map_v : &map_do, col0 + hf * 64, row_res, &bars->res_full);
+            }
+            for (int it = 0; it < n_it; ++it) {
+                const int s = it & 1, row_t = b * S + (first + it) * 128;
+                if (it >= 2 && !mbar_wait(&bars->ring_empty[s], ((it >> 1) & 1) ^ 1)) { atomicExch(err, 31); break; }
+                mbar_expect_tx(&bars->ring_full[s], 2 * QKV_BYTES);
+                for (int hf = 0; hf < HALVES; ++hf) {
+                    tma_load_2d(sT0 + s * QKV_BYTES + hf * TILE_HALF_BYTES, KV ? &map_q : &map_k, col0 + hf * 64, row_t, &bars->ring_full[s]);
+                    tma_load_2d(sT1 + s * QKV_BYTES + hf * TILE_HALF_BYTES, KV ? &map_do : &map_v, col0 + hf * 64, row_t, &bars->ring_full[s]);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc_first = make_idesc_bf16(128, 128, 0, 0);
+            constexpr uint32_t idesc_acc = make_idesc_bf16(128, HD, 0, 1);
+            bool ok = mbar_wait(&bars->res_full, 0);
+            if (!ok) atomicExch(err, 32);
+            for (int it = 0; it < n_it && ok; ++it) {
+                const int s = it & 1;
+                if (!mbar_wait(&bars->ring_full[s], (it >> 1) & 1)) { atomicExch(err, 33); ok = false; break; }
+                tc_fence_after();
+                const uint32_t t0 = smem_u32(sT0 + s * QKV_BYTES), t1 = smem_u32(sT1 + s * QKV_BYTES);
+#pragma unroll
+                for (int kk = 0; kk < HD / 16; ++kk)
+                    tc_mma_bf16(tm_x, make_desc_sw128(smem_u32(sR0 + (kk / 4) * TILE_HALF_BYTES)) + 2 * (kk % 4),
+                                make_desc_sw128(t0 + (kk / 4) * TILE_HALF_BYTES) + 2 * (kk % 4), idesc_first, kk > 0 ? 1u : 0u);
+                tc_commit(&bars->a_full);
+#pragma unroll
+                for (int kk = 0; kk < HD / 16; ++kk)
+                    tc_mma_bf16(tm_y, make_desc_sw128(smem_u32(sR1 + (kk / 4) * TILE_HALF_BYTES)) + 2 * (kk % 4),
+                                make_desc_sw128(t1 + (kk / 4) * TILE_HALF_BYTES) + 2 * (kk % 4), idesc_first, kk > 0 ? 1u : 0u);
+                tc_commit(&bars->b_full);
+                if (KV) {                                                // dV += P^T . dO_i   (A = P^T in the X columns, B = dO_i MN-major)
+                    if (!mbar_wait(&bars->pa_full, it & 1)) { atomicExch(err, 34); ok = false; break; }
+                    tc_fence_after();
+#pragma unroll
+                    for (int kk = 0; kk < 8; ++kk)
+                        tc_mma_bf16_ta(tm_acc0, tm_x + kk * 8, make_desc_sw128_mn(t1 + kk * 2048, TILE_HALF_BYTES, 1024), idesc_acc, (it > 0 || kk > 0) ? 1u : 0u);
+                }
+                // dK += dS^T . Q_i  (kernel A)   /   dQ += dS . K_j  (kernel B):  A = dS in the Y columns, B = ring tile 0 MN-major
+                if (!mbar_wait(&bars->pb_full, it & 1)) { atomicExch(err, 35); ok = false; break; }
+                tc_fence_after();
+#pragma unroll
+                for (int kk = 0; kk < 8; ++kk)
+                    tc_mma_bf16_ta(KV ? tm_acc1 : tm_acc0, tm_y + kk * 8, make_desc_sw128_mn(t0 + kk * 2048, TILE_HALF_BYTES, 1024), idesc_acc, (it > 0 || kk > 0) ? 1u : 0u);
+                tc_commit(&bars->ring_empty[s]);
+            }
+            tc_commit(&bars->done);
+        }
+    } else {
+        const int q = warp & 3, row = q * 32 + lane, tl = (int)threadIdx.x - 64;
+        const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
+        const float c2 = scale * 1.4426950408889634f;
+        const int64_t vec0 = ((int64_t)b * H + h) * S;
+        float lse_row = 0.f, del_row = 0.f;
+        if (!KV) { lse_row = lse[vec0 + tile * 128 + row] * 1.4426950408889634f; del_row = delta[vec0 + tile * 128 + row]; }
+        bool ok = true;
+        for (int it = 0; it < n_it && ok; ++it) {
+            const int other = first + it, bs = it & 1;
+            if (KV) {                                                    // per-query vectors of this query tile, shared by all key rows
+                s_lse[bs * 128 + tl] = lse[vec0 + other * 128 + tl] * 1.4426950408889634f;
+                s_del[bs * 128 + tl] = delta[vec0 + other * 128 + tl];
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+            }
+            if (!mbar_wait(&bars->a_full, it & 1)) { atomicExch(err, 36); ok = false; break; }
+            tc_fence_after();
+            const bool diag = causal && other == tile;
+            uint32_t r[4][32];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) tc_ld32(tm_x + lane_addr + c * 32, r[c]);
+            tc_wait_ld();
+            // P (kernel B: row = query, column = key) or P^T (kernel A: row = key, column = query), kept in fp32 for dS
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const int col = c * 32 + i;
+                    const float ls = KV ? s_lse[bs * 128 + col] : lse_row;
+                    float p = ex2f(fmaf(__uint_as_float(r[c][i]), c2, -ls));
+                    if (diag && (KV ? col < row : col > row)) p = 0.f;     // key index must not exceed the query index
+                    r[c][i] = __float_as_uint(p);
+                }
+            if (KV) {
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    uint32_t pk[32];
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const int k0 = c * 64 + 2 * i;
+                        const __nv_bfloat162 hh = __floats2bfloat162_rn(__uint_as_float(r[k0 >> 5][k0 & 31]), __uint_as_float(r[(k0 + 1) >> 5][(k0 + 1) & 31]));
+                        pk[i] = *reinterpret_cast<const uint32_t*>(&hh);
+                    }
+                    tc_st32(tm_x + lane_addr + c * 32, pk);
+                }
+                tc_wait_st();
+                tc_fence_before();
+                mbar_arrive_(&bars->pa_full);
+            }
+            if (!mbar_wait(&bars->b_full, it & 1)) { atomicExch(err, 37); ok = false; break; }
+            tc_fence_after();
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                uint32_t d0[32], d1[32], pk[32];
+                tc_ld32(tm_y + lane_addr + c * 64, d0);
+                tc_ld32(tm_y + lane_addr + c * 64 + 32, d1);
+                tc_wait_ld();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const int k0 = c * 64 + 2 * i;                        // columns k0, k0+1
+                    const float dp0 = __uint_as_float(i < 16 ? d0[2 * i] : d1[2 * i - 32]);
+                    const float dp1 = __uint_as_float(i < 16 ? d0[2 * i + 1] : d1[2 * i - 31]);
+                    const float de0 = KV ? s_del[bs * 128 + k0] : del_row, de1 = KV ? s_del[bs * 128 + k0 + 1] : del_row;
+                    const float ds0 = __uint_as_float(r[k0 >> 5][k0 & 31]) * (dp0 - de0);
+                    const float ds1 = __uint_as_float(r[(k0 + 1) >> 5][(k0 + 1) & 31]) * (dp1 - de1);
+                    const __nv_bfloat162 hh = __floats2bfloat162_rn(ds0, ds1);
+                    pk[i] = *reinterpret_cast<const uint32_t*>(&hh);
+                }
+                // all four loads of this row precede the stores that overwrite the first 64 columns: c = 0 writes columns [0,32)
+                // after reading [0,64); c = 1 writes [32,64) after reading [64,128)
+                tc_st32(tm_y + lane_addr + c * 32, pk);
+            }
+            tc_wait_st();
+            tc_fence_before();
+            mbar_arrive_(&bars->pb_full);
+        }
+        if (ok && !mbar_wait(&bars->done, 0)) { atomicExch(err, 38); ok = false; }
+        if (ok) {
+            tc_fence_after();
+            const int64_t grow = (int64_t)row_res + row;
+#pragma unroll 1
+            for (int which = 0; which < (KV ? 2 : 1); ++which) {
+                __nv_bfloat16* orow = (which == 0 ? out0 : out1) + grow * ld_out + col0;
+                const float f = (KV && which == 0) ? 1.f : scale;         // dV needs no scale; dK and dQ carry the softmax scale
+#pragma unroll 1
+                for (int c = 0; c < HD / 32; ++c) {
+                    uint32_t t[32];
+                    tc_ld32((which == 0 ? tm_acc0 : tm_acc1) + lane_addr + c * 32, t);
+                    tc_wait_ld();
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        uint4 pk;
+                        __nv_bfloat162* hh = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) hh[u] = __floats2bfloat162_rn(__uint_as_float(t[8 * k + 2 * u]) * f, __uint_as_float(t[8 * k + 2 * u + 1]) * f);
+                        reinterpret_cast<uint4*>(orow)[c * 4 + k] = pk;
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+    }
+}
+
+template <int HD>
+int launch_bwd(const void* q, const void* k, const void* v, int64_t ld, const void* o, const void* dout, int64_t ld_o, const float* lse, float* delta,
+               void* dq, void* dk, void* dv, int B, int S, int H, float scale, bool causal, int* err, cudaStream_t st) {
+    CUtensorMap mq, mk, mv, md;
+    const int64_t rows = (int64_t)B * S;
+    if (!make_map(&mq, q, rows, (int64_t)H * HD, ld, 128, 64, true)) return 11;
+    if (!make_map(&mk, k, rows, (int64_t)H * HD, ld, 128, 64, true)) return 12;
+    if (!make_map(&mv, v, rows, (int64_t)H * HD, ld, 128, 64, true)) return 13;
+    if (!make_map(&md, dout, rows, (int64_t)H * HD, ld_o, 128, 64, true)) return 14;
+    constexpr size_t smem = (size_t)(6 * (HD / 64)) * TILE_HALF_BYTES + 2048 + sizeof(FbBars) + 1024;
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(flash_bwd_kernel<HD, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return 2;
+        if (cudaFuncSetAttribute(flash_bwd_kernel<HD, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return 2;
+        configured = true;
+    }
+    count_launch(3);
+    flash_delta_kernel<<<(unsigned)((rows * H + 7) / 8), 256, 0, st>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)dout, delta, rows, S, H, HD, ld_o, ld_o);
+    const int64_t ld_out = (int64_t)H * HD;
+    flash_bwd_kernel<HD, true><<<dim3(S / 128, H, B), FA_THREADS, smem, st>>>(mq, mk, mv, md, lse, delta, (__nv_bfloat16*)dv, (__nv_bfloat16*)dk, S, H,
+                                                                             ld_out, scale, causal ? 1 : 0, err);
+    flash_bwd_kernel<HD, false><<<dim3(S / 128, H, B), FA_THREADS, smem, st>>>(mq, mk, mv, md, lse, delta, (__nv_bfloat16*)dq, nullptr, S, H, ld_out,
+                                                                              scale, causal ? 1 : 0, err);
+    return cudaGetLastError() == cudaSuccess ? 0 : 3;
+}
+
 }  // namespace
 
 bool flash_attn_supported(int S, int HD) { return S % 128 == 0 && (HD == 64 || HD == 128); }
@@ -469,6 +744,15 @@ int flash_attn_fwd(const void* q, const void* k, const void* v, int64_t ld, void
     if (!flash_attn_supported(S, HD)) return 6;
     if (HD == 128) return launch_fwd<128>(q, k, v, ld, out, ld_o, lse, B, S, H, scale, causal, variant, err, st);
     return launch_fwd<64>(q, k, v, ld, out, ld_o, lse, B, S, H, scale, causal, variant, err, st);
+}
+
+// Gradients of flash_attn_fwd.  o and dout: [B, S, H, HD] with row pitch ld_o; dq, dk, dv: contiguous [B, S, H, HD]; delta: fp32
+// scratch [B, H, S].
+int flash_attn_bwd(const void* q, const void* k, const void* v, int64_t ld, const void* o, const void* dout, int64_t ld_o, const float* lse,
+                   float* delta, void* dq, void* dk, void* dv, int B, int S, int H, int HD, float scale, bool causal, int* err, cudaStream_t st) {
+    if (!flash_attn_supported(S, HD)) return 6;
+    if (HD == 128) return launch_bwd<128>(q, k, v, ld, o, dout, ld_o, lse, delta, dq, dk, dv, B, S, H, scale, causal, err, st);
+    return launch_bwd<64>(q, k, v, ld, o, dout, ld_o, lse, delta, dq, dk, dv, B, S, H, scale, causal, err, st);
 }
 
 }  // namespace sg

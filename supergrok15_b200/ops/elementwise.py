@@ -1,12 +1,16 @@
 """Dispatch of the element-wise optimizer updates.
 
 CUDA tensors go to the sm_100a multi-tensor kernels (``csrc/mt_kernels.cu``) and raise if the
-extension is missing; CPU tensors go to the PyTorch oracle (``ops/oracle.py``).  Global scalars
+extension is missing.  fp32 CPU tensors go to the C++ CPU kernels (``csrc/cpu_kernels.cpp``, the same ops through the
+same entry points) when the extension is built and ``SG_CPU_NATIVE`` is not ``0``; everything else on the CPU (other
+dtypes, no extension) goes to the PyTorch oracle (``ops/oracle.py``), which is also what the tests compare both native
+paths against.  Global scalars
 (clip coefficient, Prodigy ``d_lr``, cosine gates, SAM scale) stay on the device: the functions
 return device tensors and never call ``.item()``.
 """
 from __future__ import annotations
 
+import os
 from typing import Dict, List, Optional, Sequence
 
 import torch
@@ -18,11 +22,28 @@ Tensors = List[torch.Tensor]
 _ws: Dict[torch.device, Dict[str, torch.Tensor]] = {}
 
 
+CPU_NATIVE = os.environ.get("SG_CPU_NATIVE", "1") != "0"
+
+
 def _is_cuda(ts: Sequence[Optional[torch.Tensor]]) -> bool:
     for t in ts:
         if t is not None:
             return t.is_cuda
     return False
+
+
+def _native(*lists: Sequence[Optional[torch.Tensor]]) -> bool:
+    """True when the native kernels take these tensors: CUDA always (the extension is then mandatory), CPU when every
+    tensor is contiguous fp32, the extension is available and the C++ CPU path is enabled."""
+    if _is_cuda(lists[0]):
+        return True
+    if not CPU_NATIVE or not _build.native_available():
+        return False
+    for l in lists:
+        for t in l:
+            if t is not None and (t.dtype != torch.float32 or not t.is_contiguous() or t.device.type != "cpu"):
+                return False
+    return True
 
 
 def workspace(dev: torch.device, name: str, numel: int, dtype=torch.float32) -> torch.Tensor:
@@ -100,27 +121,27 @@ def _global_totals(pt: torch.Tensor, n: int, dev) -> torch.Tensor:
 
 # --------------------------------------------------------------------------- steps
 def adamw(params, grads, ms, vs, steps, lr, b1, b2, eps, wd):
-    if not _is_cuda(params):
+    if not _native(params, grads, ms, vs):
         return oracle.adamw_(params, grads, ms, vs, steps, lr, b1, b2, eps, wd)
     ts = [[1 - b1 ** s, 1 - b2 ** s] for s in steps]
     _build.require().mt_apply(_op("OP_ADAMW"), [params, grads, ms, vs], ts, [lr, b1, b2, eps, wd])
 
 
 def lion(params, grads, ms, lr, b1, b2, wd):
-    if not _is_cuda(params):
+    if not _native(params, grads, ms):
         return oracle.lion_(params, grads, ms, lr, b1, b2, wd)
     _build.require().mt_apply(_op("OP_LION"), [params, grads, ms], [], [lr, b1, b2, 0.0, wd])
 
 
 def grokfast_ema(grads, emas, alpha, lamb):
-    if not _is_cuda(grads):
+    if not _native(grads, emas):
         return oracle.grokfast_ema_(grads, emas, alpha, lamb)
     _build.require().mt_apply(_op("OP_GROKFAST_EMA"), [[], grads, emas], [], [0, 0, 0, 0, 0, alpha, lamb])
 
 
 def grokfast_adamw(params, grads, ms, vs, emas, steps, lr, b1, b2, eps, wd, alpha, lamb):
     """EMA filter + amplification + AdamW in one pass (the gradient is amplified in place)."""
-    if not _is_cuda(params):
+    if not _native(params, grads, ms, vs, emas):
         oracle.grokfast_ema_(grads, emas, alpha, lamb)
         return oracle.adamw_(params, grads, ms, vs, steps, lr, b1, b2, eps, wd)
     ts = [[1 - b1 ** s, 1 - b2 ** s] for s in steps]
@@ -129,7 +150,7 @@ def grokfast_adamw(params, grads, ms, vs, emas, steps, lr, b1, b2, eps, wd, alph
 
 
 def grokadamw(params, grads, ms, vs, emas, steps, lr, b1, b2, eps, wd, alpha, lamb, grad_clip):
-    if not _is_cuda(params):
+    if not _native(params, grads, ms, vs, emas):
         return oracle.grokadamw_(params, grads, ms, vs, emas, steps, lr, b1, b2, eps, wd, alpha, lamb, grad_clip)
     clip = clip_coef_device(grads, grad_clip)[1:2] if grad_clip > 0 else None
     ts = [[1 - b1 ** s, 1 - b2 ** s] for s in steps]
@@ -139,25 +160,31 @@ def grokadamw(params, grads, ms, vs, emas, steps, lr, b1, b2, eps, wd, alpha, la
 
 def prodigy_dlr(params, grads, ss, p0s, d_lr_dev: Optional[torch.Tensor], d_lr: float):
     """Global distance estimate.  CPU: returns the new float.  CUDA: updates ``d_lr_dev`` ([1] fp32) in place."""
-    if not _is_cuda(params):
+    if not _native(params, grads, ss, p0s):
         return oracle.prodigy_dlr(params, grads, ss, p0s, d_lr)
     C = _build.require()
     pt = _reduce("OP_PRODIGY_REDUCE", [params, grads, p0s, ss], len(params), params[0].device, "prodigy")
     tot = _global_totals(pt, len(params), params[0].device)
+    if not params[0].is_cuda:                                    # CPU callers keep d_lr as a float
+        d_lr_dev = torch.tensor([float(d_lr)], dtype=torch.float32)
+        C.scalar_finalize(_op("SC_PRODIGY"), tot, 1, d_lr_dev, 0.0, 0.0, 0.0)
+        return max(float(d_lr), float(d_lr_dev[0]))              # the estimate never decreases; fp32 rounding of the old value must not lower it
     C.scalar_finalize(_op("SC_PRODIGY"), tot, 1, d_lr_dev, 0.0, 0.0, 0.0)
     return d_lr_dev
 
 
 def prodigy_step(params, grads, ms, vs, ss, steps, d_lr, lr, b1, b2, eps, wd):
     """``d_lr`` is a float on CPU and the [1] device tensor on CUDA."""
-    if not _is_cuda(params):
+    if not _native(params, grads, ms, vs, ss):
         return oracle.prodigy_step_(params, grads, ms, vs, ss, steps, d_lr, lr, b1, b2, eps, wd)
     ts = [[1 - b1 ** s, 1 - b2 ** s] for s in steps]
+    if not torch.is_tensor(d_lr):
+        d_lr = torch.tensor([float(d_lr)], dtype=torch.float32, device=params[0].device)
     _build.require().mt_apply(_op("OP_PRODIGY"), [params, grads, ms, vs, ss], ts, [lr, b1, b2, eps, wd], dscal=d_lr)
 
 
 def neuralgrok(params, grads, ms, vs, steps, W1, b1w, W2, b2w, alpha, beta, lr, b1, b2, eps, wd, grad_clip):
-    if not _is_cuda(params):
+    if not _native(params, grads, ms, vs):
         return oracle.neuralgrok_(params, grads, ms, vs, steps, W1, b1w, W2, b2w, alpha, beta, lr, b1, b2, eps, wd,
                                   grad_clip)
     clip = clip_coef_device(grads, grad_clip)[1:2] if grad_clip > 0 else None
@@ -172,7 +199,7 @@ def neuralgrok(params, grads, ms, vs, steps, W1, b1w, W2, b2w, alpha, beta, lr, 
 
 def sg15(params, grads, ms, vs, mus, sharps, bc_steps, layer_alphas, layer_beta1s, W1, b1w, W2, b2w, rescale, beta2,
          lr, wd_eff, eps, lamb, ramp, gate, grad_clip, exact_gelu=False):
-    if not _is_cuda(params):
+    if not _native(params, grads, ms, vs, mus, sharps):
         return oracle.sg15_(params, grads, ms, vs, mus, sharps, bc_steps, layer_alphas, layer_beta1s, W1, b1w, W2,
                             b2w, rescale, beta2, lr, wd_eff, eps, lamb, ramp, gate, grad_clip, exact_gelu)
     clip = clip_coef_device(grads, grad_clip)[1:2] if grad_clip > 0 else None
@@ -189,7 +216,7 @@ def sg15(params, grads, ms, vs, mus, sharps, bc_steps, layer_alphas, layer_beta1
 def sg11(params, grads, ms, vs, mus, sharps, bc_steps, layer_alphas, layer_beta1s, W1, b1w, W2, b2w, rescale, beta2,
          lr, wd_eff, eps, lamb, ramp, gate_temperature, grad_clip, exact_gelu=False):
     """Returns the per-tensor gates (list of floats on CPU, device tensor [n] on CUDA)."""
-    if not _is_cuda(params):
+    if not _native(params, grads, ms, vs, mus, sharps):
         return oracle.sg11_(params, grads, ms, vs, mus, sharps, bc_steps, layer_alphas, layer_beta1s, W1, b1w, W2,
                             b2w, rescale, beta2, lr, wd_eff, eps, lamb, ramp, gate_temperature, grad_clip, exact_gelu)
     C = _build.require()
@@ -214,7 +241,7 @@ def sg11(params, grads, ms, vs, mus, sharps, bc_steps, layer_alphas, layer_beta1
     C.scalar_finalize(_op("SC_SG11_GATES"), pt, n, gates, float(gate_temperature), float(ramp), float(lamb))
     ts = [[b1_i, 1 - b1_i ** s, 1 - beta2 ** s] for b1_i, s in zip(layer_beta1s, bc_steps)]
     C.mt_apply(_op("OP_SG11_B"), [params, smart, ms, vs, mus], ts, [lr, 0.0, beta2, eps, wd_eff], tscal=gates)
-    return gates[n:2 * n]
+    return gates[n:2 * n] if dev.type == "cuda" else gates[n:2 * n].tolist()
 
 
 # --------------------------------------------------------------------------- SAM helpers
@@ -229,21 +256,21 @@ def sam_scale_device(grads: Tensors, rho: float) -> torch.Tensor:
 
 
 def perturb(params, grads, backups, rho):
-    if not _is_cuda(params):
+    if not _native(params, grads, backups):
         return oracle.looksam_perturb_(params, grads, backups, rho)
     sc = sam_scale_device(grads, rho)
     _build.require().mt_apply(_op("OP_PERTURB"), [params, grads, backups], [], [], dscal=sc)
 
 
 def restore(params, backups):
-    if not _is_cuda(params):
+    if not _native(params, backups):
         return oracle.looksam_restore_(params, backups)
     _build.require().mt_apply(_op("OP_RESTORE"), [params, [], backups], [], [])
 
 
 def sharpness_restore(params, grads, backups, sam_grads, sharps):
     """sharp = |g_sam - g| ; p = backup  (reference csrc/supergrok15_kernels.cu:170)."""
-    if not _is_cuda(params):
+    if not _native(params, grads, backups, sam_grads, sharps):
         for p, g, b, gs, s in zip(params, grads, backups, sam_grads, sharps):
             s.view(-1).copy_((gs.reshape(-1).float() - g.reshape(-1).float()).abs())
             p.detach().copy_(b.view(p.shape).to(p.dtype))
@@ -253,7 +280,7 @@ def sharpness_restore(params, grads, backups, sam_grads, sharps):
 
 def looksam_direction_adjust(grads, sam_grads, v_dirs, alpha, do_direction=True):
     """v = (g_sam-g)/||g_sam-g|| per tensor (skipped below 1e-12), then g += alpha*||g||*v."""
-    if not _is_cuda(grads):
+    if not _native(grads, sam_grads if do_direction else [], v_dirs):
         if do_direction:
             oracle.looksam_direction_(v_dirs, sam_grads, grads)
         return oracle.looksam_adjust_(grads, v_dirs, alpha)
@@ -270,7 +297,7 @@ def looksam_direction_adjust(grads, sam_grads, v_dirs, alpha, do_direction=True)
 
 
 def scale_(grads, factor: float):
-    if not _is_cuda(grads):
+    if not _native(grads):
         for g in grads:
             g.mul_(factor)
         return

@@ -131,23 +131,22 @@ def flash_supported(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> bool:
 
 
 class _FlashAttention(torch.autograd.Function):
-    """Forward on the tcgen05 kernel (``csrc/flash_attn_sm100.cu``); it also returns the row log-sum-exp.  The backward pass
-    differentiates a recomputed PyTorch attention (no tcgen05 backward kernel exists yet)."""
+    """Forward and backward on the tcgen05 kernels of ``csrc/flash_attn_sm100.cu`` (the forward also returns the row
+    log-sum-exp that the backward needs; nothing of size S x S is ever stored)."""
 
     @staticmethod
     def forward(ctx, q, k, v, causal):
         from . import gemm as _gemm
         out, lse = _build.require().flash_fwd(q, k, v, causal, _gemm._err_flag(q.device))
-        ctx.save_for_backward(q, k, v)
+        ctx.save_for_backward(q, k, v, out, lse)
         ctx.causal = causal
         return out
 
     @staticmethod
     def backward(ctx, dout):
-        q, k, v = (t.detach().requires_grad_(True) for t in ctx.saved_tensors)
-        with torch.enable_grad():
-            o = attention_reference(q, k, v, ctx.causal)
-        dq, dk, dv = torch.autograd.grad(o, (q, k, v), dout)
+        from . import gemm as _gemm
+        q, k, v, out, lse = ctx.saved_tensors
+        dq, dk, dv = _build.require().flash_bwd(q, k, v, out, lse, dout, ctx.causal, _gemm._err_flag(q.device))
         return dq, dk, dv, None
 
 

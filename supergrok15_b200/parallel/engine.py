@@ -50,7 +50,7 @@ class CommTimeout(RuntimeError):
 class ZeroEngine:
     def __init__(self, model: torch.nn.Module, optimizer: str = "supergrok2", opt_kwargs: Optional[dict] = None,
                  comm: Optional[str] = None, param_dtype: torch.dtype = torch.bfloat16, group=None,
-                 timeout_s: float = 20.0, criterion=None):
+                 timeout_s: float = 20.0, criterion=None, graph: Optional[bool] = None, graph_warmup: int = 3):
         self.comm = comm or os.environ.get("GROK_COMM", "p2p")
         assert self.comm in ("p2p", "nvls", "nccl")
         self.rank, self.world = symm.world_info(group)
@@ -59,6 +59,11 @@ class ZeroEngine:
         self.opt_kwargs = dict(opt_kwargs or {})
         self.timeout_s = timeout_s
         self.criterion = criterion                                       # None: the fused softmax cross-entropy kernel
+        # forward + backward of a step are captured into a CUDA graph per batch shape (after `graph_warmup` eager steps): the
+        # small models of the grokking tasks launch hundreds of short kernels per step and are bound by the host otherwise
+        self.use_graph = (os.environ.get("SG_GRAPH", "1") != "0") if graph is None else bool(graph)
+        self.graph_warmup = graph_warmup
+        self._graphs, self._graph_seen = {}, {}
         self.model = model.to(param_dtype)
         named = [(n, p) for n, p in self.model.named_parameters() if p.requires_grad]
         self.param_names = [n for n, _ in named]
@@ -301,13 +306,8 @@ class ZeroEngine:
                     dist.broadcast(self.pbuf.tensor[b:e], src=rr, group=self.group)
         self._barrier(2)                                              # every rank's parameters are complete
 
-    # ------------------------------------------------------------------ the call a user makes
-    def train_step(self, x: torch.Tensor, y: torch.Tensor, micro_batches: int = 1, **metrics) -> torch.Tensor:
-        """Host (pinned) or device batch in, loss tensor out: H2D copy, forward, backward, sharded fused step.
-        ``micro_batches`` > 1 splits the batch and accumulates gradients in the flat buffer (activation memory)."""
-        if x.device != self.device:
-            x = x.to(self.device, non_blocking=True)
-            y = y.to(self.device, non_blocking=True)
+    def _fwd_bwd(self, x: torch.Tensor, y: torch.Tensor, micro_batches: int) -> torch.Tensor:
+        """Zero the flat gradient buffer, then forward + loss + backward of every micro-batch (gradients accumulate in the buffer)."""
         self.zero_grad()
         total = None
         for xb, yb in zip(x.chunk(micro_batches), y.chunk(micro_batches)):
@@ -322,6 +322,56 @@ class ZeroEngine:
                 loss = loss / micro_batches
             loss.backward()
             total = loss.detach() if total is None else total + loss.detach()
+        return total
+
+    def _fwd_bwd_graphed(self, x: torch.Tensor, y: torch.Tensor, micro_batches: int) -> torch.Tensor:
+        """Forward + backward through a CUDA graph captured per (shape, dtype, micro-batch count).  The first ``graph_warmup``
+        calls of a shape run eagerly (lazy initialisation, workspace growth); a capture that fails switches graphs off."""
+        key = (tuple(x.shape), x.dtype, tuple(y.shape), y.dtype, micro_batches, self.model.training)
+        entry = self._graphs.get(key)
+        if entry is None:
+            seen = self._graph_seen.get(key, 0)
+            self._graph_seen[key] = seen + 1
+            if seen < self.graph_warmup:
+                return self._fwd_bwd(x.to(self.device, non_blocking=True), y.to(self.device, non_blocking=True), micro_batches)
+            sx = torch.empty(x.shape, dtype=x.dtype, device=self.device)
+            sy = torch.empty(y.shape, dtype=y.dtype, device=self.device)
+            sx.copy_(x, non_blocking=True)
+            sy.copy_(y, non_blocking=True)
+            C = _build.require()
+            try:
+                torch.cuda.synchronize(self.device)
+                g = torch.cuda.CUDAGraph()
+                l0 = C.launch_count()
+                with torch.cuda.graph(g):
+                    total = self._fwd_bwd(sx, sy, micro_batches)
+                entry = (g, sx, sy, total, C.launch_count() - l0)
+                C.add_launches(-entry[4])                             # enqueued for the capture only; counted again at every replay
+                self._graphs[key] = entry
+            except Exception as exc:  # noqa: BLE001
+                import warnings
+                warnings.warn(f"CUDA graph capture of forward/backward failed ({type(exc).__name__}: {exc}); running eagerly")
+                self.use_graph = False
+                torch.cuda.synchronize(self.device)
+                return self._fwd_bwd(x.to(self.device, non_blocking=True), y.to(self.device, non_blocking=True), micro_batches)
+        g, sx, sy, total, n_launch = entry
+        sx.copy_(x, non_blocking=True)
+        sy.copy_(y, non_blocking=True)
+        g.replay()
+        _build.require().add_launches(n_launch)
+        return total.clone()                                          # the graph's own loss tensor is overwritten by the next replay
+
+    # ------------------------------------------------------------------ the call a user makes
+    def train_step(self, x: torch.Tensor, y: torch.Tensor, micro_batches: int = 1, **metrics) -> torch.Tensor:
+        """Host (pinned) or device batch in, loss tensor out: H2D copy, forward, backward, sharded fused step.
+        ``micro_batches`` > 1 splits the batch and accumulates gradients in the flat buffer (activation memory)."""
+        if self.use_graph and self.cuda:
+            total = self._fwd_bwd_graphed(x, y, micro_batches)
+        else:
+            if x.device != self.device:
+                x = x.to(self.device, non_blocking=True)
+                y = y.to(self.device, non_blocking=True)
+            total = self._fwd_bwd(x, y, micro_batches)
         self.step(**metrics)
         return total
 

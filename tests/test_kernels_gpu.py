@@ -301,3 +301,28 @@ def test_device_expert_recycling():
     torch.cuda.synchronize()
     assert int(mn.expert_counts.sum()) == 0
     assert torch.equal(mn.state_dict()["expert_W1"], snap["expert_W1"])
+
+
+def test_engine_graphed_forward_backward_equals_eager():
+    """ZeroEngine with the forward/backward CUDA graph produces the same parameters and losses as the eager path."""
+    from supergrok15_b200.models import Transformer
+    from supergrok15_b200.parallel import ZeroEngine
+    dev = torch.device("cuda:0")
+    results = []
+    for use_graph in (False, True):
+        torch.manual_seed(3)
+        model = Transformer(2, 128, 4).to(dev)
+        eng = ZeroEngine(model, "supergrok2", dict(lr=1e-3), param_dtype=torch.bfloat16, graph=use_graph, graph_warmup=2)
+        g = torch.Generator().manual_seed(11)
+        losses = []
+        for _ in range(6):
+            x = torch.randint(0, 97, (256, 4), generator=g).pin_memory()
+            y = torch.randint(0, 97, (256,), generator=g).pin_memory()
+            losses.append(float(eng.train_step(x, y).item()))
+        eng.check()
+        assert eng.use_graph == use_graph and (len(eng._graphs) == 1) == use_graph
+        results.append((losses, [p.detach().float().clone() for p in eng.params]))
+    (l0, p0), (l1, p1) = results
+    assert l0 == l1, (l0, l1)
+    for a, b in zip(p0, p1):
+        assert torch.equal(a, b)

@@ -711,7 +711,7 @@ int launch_bwd(const void* q, const void* k, const void* v, int64_t ld, const vo
                void* dq, void* dk, void* dv, int B, int S, int H, float scale, bool causal, int* err, cudaStream_t st) {
     CUtensorMap mq, mk, mv, md;
     const int64_t rows = (int64_t)B * S;
-    if (!make_map(&mq, q, rows, (int64_t)H * HD, ld, 128, 64, true)) return 11;
+    if (!make_map(&mq, q, rows, (int64_t)H * HD, ld, 128, 64, true)) return 1100 + last_map_error();
     if (!make_map(&mk, k, rows, (int64_t)H * HD, ld, 128, 64, true)) return 12;
     if (!make_map(&mv, v, rows, (int64_t)H * HD, ld, 128, 64, true)) return 13;
     if (!make_map(&md, dout, rows, (int64_t)H * HD, ld_o, 128, 64, true)) return 14;

@@ -486,6 +486,7 @@ __global__ void __launch_bounds__(256) gemm_splitk_reduce_kernel(const float* __
 
 // ---- host side -------------------------------------------------------------------------------------------------
 }  // namespace
+static int g_map_error = 0;                      // CUresult of the most recent encode (diagnostics only)
 bool tc::make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int64_t ld_elems, int box_rows, int box_cols, bool bf16) {
     const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
     const cuuint64_t strides[1] = {(cuuint64_t)ld_elems * (bf16 ? 2 : 4)};
@@ -501,12 +502,21 @@ bool tc::make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols
         if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) fn = nullptr;
         return reinterpret_cast<EncodeFn>(fn);
     }();
-    if (!encode) return false;
-    const CUresult r = encode(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2,
+    if (!encode) { g_map_error = -1; return false; }
+    CUresult r = encode(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2,
                                               const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                                               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r == CUDA_ERROR_INVALID_CONTEXT) {
+        // A host thread that has made no runtime call yet (an autograd worker thread, for one) has no current context for the
+        // driver API: bind the primary context of the current device and try once more.
+        cudaFree(nullptr);
+        r = encode(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    }
+    g_map_error = (int)r;
     return r == CUDA_SUCCESS;
 }
+int tc::last_map_error() { return g_map_error; }
 namespace {
 
 int num_sms() {

@@ -107,6 +107,7 @@ __host__ __device__ constexpr uint32_t make_idesc_bf16(int M, int N, int a_mn, i
 
 // host: 2-D tiled tensor map with 128-byte swizzle over a row-major matrix (defined in gemm_sm100.cu)
 bool make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int64_t ld_elems, int box_rows, int box_cols, bool bf16);
+int last_map_error();                            // CUresult of the most recent encode, -1 if the encoder could not be resolved
 
 }  // namespace tc
 }  // namespace sg

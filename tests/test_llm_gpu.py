@@ -171,3 +171,22 @@ def test_flash_attention_forward(shape):
         torch.testing.assert_close(out.float(), ref, rtol=2e-2, atol=2e-2)
         out.float().sum().backward()
         assert torch.isfinite(q.grad).all()
+
+
+@pytest.mark.parametrize("shape", [(1, 128, 1, 128, True), (1, 256, 2, 128, True), (2, 384, 2, 128, False), (1, 512, 2, 64, True)])
+def test_flash_attention_backward(shape):
+    """tcgen05 backward kernels (dK/dV per key tile, dQ per query tile) against autograd through fp32 PyTorch attention."""
+    from supergrok15_b200.ops import gemm, nn_ops
+    dev = _dev()
+    B, S, H, HD, causal = shape
+    torch.manual_seed(7)
+    q, k, v = (torch.randn(B, S, H, HD, device=dev).to(torch.bfloat16).requires_grad_(True) for _ in range(3))
+    do = torch.randn(B, S, H, HD, device=dev).to(torch.bfloat16)
+    nn_ops.attention(q, k, v, causal, impl="tcgen05").backward(do)
+    torch.cuda.synchronize()
+    gemm.check(dev)
+    qr, kr, vr = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+    nn_ops.attention_reference(qr, kr, vr, causal).backward(do.float())
+    for got, ref in zip((q, k, v), (qr, kr, vr)):
+        err = float((got.grad.float() - ref.grad).abs().max() / ref.grad.abs().max())
+        assert err < 2e-2, err

@@ -1,6 +1,6 @@
 """Install the reference into baseline/_ref for the `bench.py --impl reference` arm (offline, no GPU needed).
 
-What it does, and why each deviation from `pip install /root/reference` is needed:
+What it does, and why each deviation from a plain `pip install <reference tree>` is needed:
   1. copies the read-only reference tree to a scratch directory (the build writes into its source tree);
   2. edits the COPY's setup.py only: drops the "CUDA device must be visible" check (nvcc cross-compiles) and
      replaces the gencode list sm_70..sm_90 (no PTX, so none of it runs on a B200) by sm_100;
@@ -10,7 +10,7 @@ What it does, and why each deviation from `pip install /root/reference` is neede
   5. builds baseline/_ref/libref_shim.so from baseline/ref_shim.cpp (one missing PyTorch symbol, see that file).
 No kernel, dispatch or Python source file of the reference is modified.
 
-usage: python baseline/build_reference.py [/path/to/reference]
+usage: python baseline/build_reference.py /path/to/reference     (or set SG_REFERENCE_SRC)
 """
 import os
 import re
@@ -25,7 +25,9 @@ DEST = os.path.join(HERE, "_ref")
 
 
 def main():
-    src = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    src = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("SG_REFERENCE_SRC")
+    if not src or not os.path.isdir(src):
+        sys.exit("usage: python baseline/build_reference.py /path/to/reference")
     work = os.path.join(tempfile.mkdtemp(prefix="refbuild_"), "src")
     shutil.copytree(src, work)
     sp = os.path.join(work, "setup.py")

@@ -244,6 +244,135 @@ __global__ void __launch_bounds__(256) ln_bwd_kernel(const T* __restrict__ z, co
     }
 }
 
+
+// ---------------------------------------------------------------------------------------------------- wide rows
+// Variants for rows of exactly 32 * VEC * NCH elements (VEC = 16 bytes of T per lane, NCH in {1,2,4,8}): every access is 16 bytes
+// per lane, the forward keeps the row in registers between the statistics and the output pass, and the backward keeps each
+// lane's slice of the weight (and bias) gradient in registers over all the rows a warp visits - no shared-memory read-modify-
+// write per element - before one fixed-order reduction over the eight warps.
+template <typename T> struct RowVec {
+    static constexpr int VEC = 16 / sizeof(T);
+    static __device__ __forceinline__ void ld(const T* p, float (&v)[VEC]) {
+        const uint4 t = *reinterpret_cast<const uint4*>(p);
+        const T* h = reinterpret_cast<const T*>(&t);
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) v[k] = Cvt<T>::to(h[k]);
+    }
+    static __device__ __forceinline__ void st(T* p, const float (&v)[VEC]) {
+        uint4 t;
+        T* h = reinterpret_cast<T*>(&t);
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) h[k] = Cvt<T>::from(v[k]);
+        *reinterpret_cast<uint4*>(p) = t;
+    }
+};
+
+template <typename T, bool RMS, int NCH>
+__global__ void __launch_bounds__(256) norm_fwd_wide_kernel(const T* __restrict__ x, const T* __restrict__ r, const T* __restrict__ gamma,
+                                                            const T* __restrict__ beta, T* __restrict__ z, T* __restrict__ y,
+                                                            float* __restrict__ stats, int64_t rows, float eps) {
+    constexpr int VEC = RowVec<T>::VEC, D = 32 * VEC * NCH;
+    const int lane = threadIdx.x & 31;
+    const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    float a[NCH][VEC];
+    float s = 0.f, ss = 0.f;
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
+        const int col = (c * 32 + lane) * VEC;
+        RowVec<T>::ld(x + row * D + col, a[c]);
+        if (r) {
+            float b[VEC];
+            RowVec<T>::ld(r + row * D + col, b);
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) a[c][k] = Cvt<T>::to(Cvt<T>::from(a[c][k] + b[k]));
+            RowVec<T>::st(z + row * D + col, a[c]);
+        }
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) { s += a[c][k]; ss = fmaf(a[c][k], a[c][k], ss); }
+    }
+    s = warp_sum(s); ss = warp_sum(ss);
+    const float mean = RMS ? 0.f : s / D;
+    const float rstd = rsqrtf(fmaxf(ss / D - mean * mean, 0.f) + eps);
+    if (lane == 0) { stats[2 * row] = mean; stats[2 * row + 1] = rstd; }
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
+        const int col = (c * 32 + lane) * VEC;
+        float g[VEC], bb[VEC], o[VEC];
+        RowVec<T>::ld(gamma + col, g);
+        if (beta) RowVec<T>::ld(beta + col, bb);
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) o[k] = (a[c][k] - mean) * rstd * g[k] + (beta ? bb[k] : 0.f);
+        RowVec<T>::st(y + row * D + col, o);
+    }
+}
+
+template <typename T, bool RMS, int NCH>
+__global__ void __launch_bounds__(256) norm_bwd_wide_kernel(const T* __restrict__ z, const T* __restrict__ dy, const T* __restrict__ gamma,
+                                                            const float* __restrict__ stats, const T* __restrict__ dz_in, T* __restrict__ dz,
+                                                            float* __restrict__ part, int64_t rows) {
+    constexpr int VEC = RowVec<T>::VEC, D = 32 * VEC * NCH;
+    extern __shared__ float sm[];                       // [8 warps][D]
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    float ag[NCH][VEC], ab[RMS ? 1 : NCH][VEC];        // gamma is re-read per row (4 KB, stays in L1): registers go to the accumulators
+#pragma unroll
+    for (int c = 0; c < NCH; ++c)
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) { ag[c][k] = 0.f; if (!RMS) ab[c][k] = 0.f; }
+    for (int64_t row = (int64_t)blockIdx.x * 8 + w; row < rows; row += (int64_t)gridDim.x * 8) {
+        const float mean = stats[2 * row], rstd = stats[2 * row + 1];
+        float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+        for (int c = 0; c < NCH; ++c) {
+            const int col = (c * 32 + lane) * VEC;
+            float a[VEC], d[VEC], g[VEC];
+            RowVec<T>::ld(z + row * D + col, a); RowVec<T>::ld(dy + row * D + col, d); RowVec<T>::ld(gamma + col, g);
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) { const float xh = (a[k] - mean) * rstd, dg = d[k] * g[k]; s1 += dg; s2 = fmaf(dg, xh, s2); }
+            if (NCH >= 8 && (c & 1)) asm volatile("" ::: "memory");      // keep the unrolled loads from being hoisted all at once (register pressure)
+        }
+        s1 = RMS ? 0.f : warp_sum(s1) / D; s2 = warp_sum(s2) / D;
+#pragma unroll
+        for (int c = 0; c < NCH; ++c) {                 // second pass: the row is re-read through L1
+            const int col = (c * 32 + lane) * VEC;
+            float a[VEC], d[VEC], o[VEC], g[VEC];
+            RowVec<T>::ld(z + row * D + col, a); RowVec<T>::ld(dy + row * D + col, d); RowVec<T>::ld(gamma + col, g);
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) {
+                const float xh = (a[k] - mean) * rstd;
+                o[k] = rstd * (d[k] * g[k] - s1 - xh * s2);
+                ag[c][k] = fmaf(d[k], xh, ag[c][k]);
+                if (!RMS) ab[c][k] += d[k];
+            }
+            if (dz_in) {
+                float e[VEC];
+                RowVec<T>::ld(dz_in + row * D + col, e);
+#pragma unroll
+                for (int k = 0; k < VEC; ++k) o[k] += e[k];
+            }
+            RowVec<T>::st(dz + row * D + col, o);
+            if (NCH >= 8) asm volatile("" ::: "memory");
+        }
+    }
+    // fixed-order reduction over the eight warps, first the weight gradient, then (LayerNorm) the bias gradient
+#pragma unroll 1
+    for (int which = 0; which < (RMS ? 1 : 2); ++which) {
+        __syncthreads();
+#pragma unroll
+        for (int c = 0; c < NCH; ++c)
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) sm[w * D + (c * 32 + lane) * VEC + k] = which == 0 ? ag[c][k] : ab[RMS ? 0 : c][k];
+        __syncthreads();
+        for (int col = threadIdx.x; col < D; col += 256) {
+            float acc = 0.f;
+#pragma unroll
+            for (int ww = 0; ww < 8; ++ww) acc += sm[ww * D + col];
+            part[((int64_t)blockIdx.x * 2 + which) * D + col] = acc;
+        }
+    }
+    if (RMS) for (int col = threadIdx.x; col < D; col += 256) part[((int64_t)blockIdx.x * 2 + 1) * D + col] = 0.f;
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256) ln_bwd_reduce_kernel(const float* __restrict__ part, int n_part, int D, T* __restrict__ dgamma,
                                                             T* __restrict__ dbeta) {
@@ -279,10 +408,28 @@ void attn_small(int dtype, bool bwd, const void* qkv, const void* dout, void* ou
     else attn_dispatch<float>(bwd, (const float*)qkv, (const float*)dout, (float*)out, B, S, H, HD, causal, st);
 }
 
+constexpr int WIDE_GRID = 148 * 2;
+static int wide_nch(int D, int elem_bytes) {            // rows of 32 * (16 / elem_bytes) * NCH elements take the wide kernels
+    const int unit = 32 * (16 / elem_bytes);
+    if (D % unit) return 0;
+    const int n = D / unit;
+    return (n == 1 || n == 2 || n == 4 || n == 8) ? n : 0;          // 16 chunks would need 128+ accumulator registers per lane
+}
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
 template <typename T>
 static void ln_fwd_t(bool rms, const void* x, const void* r, const void* gamma, const void* beta, void* z, void* y, float* stats, int64_t rows, int D,
                      float eps, cudaStream_t st) {
     const unsigned blocks = (unsigned)((rows + 7) / 8);
+    const int nch = wide_nch(D, (int)sizeof(T));
+    if (nch && aligned16(x) && aligned16(r) && aligned16(gamma) && aligned16(beta) && aligned16(z) && aligned16(y)) {
+#define WIDE_F(N) \
+        if (rms) norm_fwd_wide_kernel<T, true, N><<<blocks, 256, 0, st>>>((const T*)x, (const T*)r, (const T*)gamma, nullptr, (T*)z, (T*)y, stats, rows, eps); \
+        else norm_fwd_wide_kernel<T, false, N><<<blocks, 256, 0, st>>>((const T*)x, (const T*)r, (const T*)gamma, (const T*)beta, (T*)z, (T*)y, stats, rows, eps);
+        switch (nch) { case 1: WIDE_F(1) break; case 2: WIDE_F(2) break; case 4: WIDE_F(4) break; default: WIDE_F(8) break; }
+#undef WIDE_F
+        return;
+    }
     if (rms) ln_fwd_kernel<T, true><<<blocks, 256, 0, st>>>((const T*)x, (const T*)r, (const T*)gamma, nullptr, (T*)z, (T*)y, stats, rows, D, eps);
     else ln_fwd_kernel<T, false><<<blocks, 256, 0, st>>>((const T*)x, (const T*)r, (const T*)gamma, (const T*)beta, (T*)z, (T*)y, stats, rows, D, eps);
 }
@@ -294,12 +441,31 @@ void ln_fwd(int dtype, bool rms, const void* x, const void* r, const void* gamma
     else ln_fwd_t<float>(rms, x, r, gamma, beta, z, y, stats, rows, D, eps, st);
 }
 
-int ln_bwd_parts(int64_t rows) { return (int)((rows + LN_ROWS_PER_CTA - 1) / LN_ROWS_PER_CTA); }
+// CTA partials of the weight / bias gradient: enough for either backward kernel
+static int wide_grid(int64_t rows) { const int64_t b = (rows + 7) / 8; return (int)(b < WIDE_GRID ? b : WIDE_GRID); }
+int ln_bwd_parts(int64_t rows) {
+    const int a = (int)((rows + LN_ROWS_PER_CTA - 1) / LN_ROWS_PER_CTA), b = wide_grid(rows);
+    return a > b ? a : b;
+}
 
 template <typename T>
 static void ln_bwd_t(bool rms, const void* z, const void* dy, const void* gamma, const float* stats, const void* dz_in, void* dz, float* part,
                      void* dgamma, void* dbeta, int64_t rows, int D, cudaStream_t st) {
-    const int parts = ln_bwd_parts(rows);
+    const int nch = wide_nch(D, (int)sizeof(T));
+    if (nch && aligned16(z) && aligned16(dy) && aligned16(gamma) && aligned16(dz_in) && aligned16(dz)) {
+        const int grid = wide_grid(rows);
+        const size_t smw = (size_t)8 * D * sizeof(float);
+#define WIDE_B2(R, N) \
+        { cudaFuncSetAttribute(norm_bwd_wide_kernel<T, R, N>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smw); \
+          norm_bwd_wide_kernel<T, R, N><<<grid, 256, smw, st>>>((const T*)z, (const T*)dy, (const T*)gamma, stats, (const T*)dz_in, (T*)dz, part, rows); }
+#define WIDE_B(N) if (rms) WIDE_B2(true, N) else WIDE_B2(false, N)
+        switch (nch) { case 1: WIDE_B(1) break; case 2: WIDE_B(2) break; case 4: WIDE_B(4) break; default: WIDE_B(8) break; }
+#undef WIDE_B
+#undef WIDE_B2
+        ln_bwd_reduce_kernel<T><<<(D + 255) / 256, 256, 0, st>>>(part, grid, D, (T*)dgamma, (T*)dbeta);
+        return;
+    }
+    const int parts = (int)((rows + LN_ROWS_PER_CTA - 1) / LN_ROWS_PER_CTA);
     const size_t smem = (size_t)8 * 2 * D * sizeof(float);
     if (rms) {
         cudaFuncSetAttribute(ln_bwd_kernel<T, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

@@ -1,0 +1,109 @@
+"""Device-timed micro-benchmarks of the decoder kernels against their PyTorch counterparts (1 GPU).
+
+    python -m supergrok15_b200.ops.bench_nn --what flash            # tcgen05 flash attention fwd / bwd vs F.scaled_dot_product_attention
+    python -m supergrok15_b200.ops.bench_nn --what ce               # fused cross-entropy fwd / bwd vs F.cross_entropy
+    python -m supergrok15_b200.ops.bench_nn --what norm             # RMSNorm with fused residual vs F.rms_norm(x + r)
+    ... --small                                                      # one modest shape, few iterations (profiler captures)
+
+Timing: CUDA events on the launching stream after warm-up; every shape's working set exceeds the 126 MB L2 except with --small.
+Prints one JSON line per measurement.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+
+import torch
+import torch.nn.functional as F
+
+
+def timed(fn, it, warm=3):
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(it):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / it
+
+
+def bench_flash(small: bool, it: int):
+    from .. import _build
+    from . import gemm, nn_ops
+    C = _build.require()
+    dev = torch.device("cuda:0")
+    shapes = [(4, 1024, 8, 128)] if small else [(8, 2048, 16, 128), (4, 4096, 16, 128), (8, 2048, 32, 64)]
+    for B, S, H, HD in shapes:
+        q, k, v = (torch.randn(B, S, H, HD, device=dev).to(torch.bfloat16).requires_grad_(True) for _ in range(3))
+        do = torch.randn(B, S, H, HD, device=dev).to(torch.bfloat16)
+        err = gemm._err_flag(dev)
+        out, lse = C.flash_fwd(q, k, v, True, err)
+        t_f = timed(lambda: C.flash_fwd(q, k, v, True, err), it)
+        t_b = timed(lambda: C.flash_bwd(q, k, v, out, lse, do, True, err), it)
+        o2 = nn_ops.attention_reference(q, k, v, True)
+        t_rf = timed(lambda: nn_ops.attention_reference(q, k, v, True), it)
+        t_rb = timed(lambda: torch.autograd.grad(o2, (q, k, v), do, retain_graph=True), it)
+        gemm.check(dev)
+        fl = 4.0 * B * H * S * S * HD / 2                      # causal forward FLOPs; backward = 2.5x
+        print(json.dumps({"kernel": "flash_attention_causal", "B": B, "S": S, "H": H, "hd": HD, "fwd_ms": t_f, "fwd_tflops": fl / t_f / 1e9,
+                          "bwd_ms": t_b, "bwd_tflops": 2.5 * fl / t_b / 1e9, "sdpa_fwd_ms": t_rf, "sdpa_bwd_ms": t_rb}), flush=True)
+
+
+def bench_ce(small: bool, it: int):
+    from . import nn_ops
+    dev = torch.device("cuda:0")
+    rows, V = (4096, 32000) if small else (16384, 32000)
+    x = (torch.randn(rows, V, device=dev) * 2).to(torch.bfloat16).requires_grad_(True)
+    t = torch.randint(0, V, (rows,), device=dev)
+
+    def own():
+        x.grad = None
+        nn_ops.cross_entropy(x, t).backward()
+
+    def ref():
+        x.grad = None
+        F.cross_entropy(x.float(), t).backward()
+    t_o, t_r = timed(own, it), timed(ref, it)
+    by = rows * V * 2 * 3                                       # logits read twice, gradient written once
+    print(json.dumps({"kernel": "cross_entropy_fwd_bwd", "rows": rows, "V": V, "ms": t_o, "GBps": by / t_o / 1e6, "torch_ms": t_r}), flush=True)
+
+
+def bench_norm(small: bool, it: int):
+    from . import nn_ops
+    dev = torch.device("cuda:0")
+    rows, D = (16384, 2048) if small else (65536, 2048)
+    x = torch.randn(rows, D, device=dev).to(torch.bfloat16).requires_grad_(True)
+    r = torch.randn(rows, D, device=dev).to(torch.bfloat16).requires_grad_(True)
+    w = torch.ones(D, device=dev, dtype=torch.bfloat16, requires_grad=True)
+    g = torch.randn(rows, D, device=dev).to(torch.bfloat16)
+
+    def own():
+        y, z = nn_ops.norm_residual(x, r, w, None, 1e-5, rms=True)
+        torch.autograd.grad((y, z), (x, r, w), (g, g))
+
+    def ref():
+        z = x + r
+        y = F.rms_norm(z, (D,), w, 1e-5)
+        torch.autograd.grad((y, z), (x, r, w), (g, g))
+    t_o, t_r = timed(own, it), timed(ref, it)
+    by = rows * D * 2 * (4 + 4)                                 # fwd: x, r in, y, z out; bwd: z, dy, dz_in in, dz out
+    print(json.dumps({"kernel": "rmsnorm_residual_fwd_bwd", "rows": rows, "D": D, "ms": t_o, "GBps": by / t_o / 1e6, "torch_ms": t_r}), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--what", default="flash", choices=["flash", "ce", "norm", "all"])
+    ap.add_argument("--small", action="store_true")
+    ap.add_argument("--iters", type=int, default=None)
+    a = ap.parse_args()
+    it = a.iters or (2 if a.small else 20)
+    for name, fn in (("flash", bench_flash), ("ce", bench_ce), ("norm", bench_norm)):
+        if a.what in (name, "all"):
+            fn(a.small, it)
+
+
+if __name__ == "__main__":
+    main()

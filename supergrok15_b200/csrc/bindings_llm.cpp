@@ -198,7 +198,7 @@ void register_llm(pybind11::module_& m) {
     m.def("gelu_bwd", &gelu_bwd);
     m.def("embedding_fwd", &embedding_fwd);
     m.def("embedding_bwd", &embedding_bwd);
-    m.def("flash_fwd", &flash_fwd, py::arg("q"), py::arg("k"), py::arg("v"), py::arg("causal"), py::arg("err"), py::arg("variant") = 2);
+    m.def("flash_fwd", &flash_fwd, py::arg("q"), py::arg("k"), py::arg("v"), py::arg("causal"), py::arg("err"), py::arg("variant") = 3);
     m.def("flash_bwd", &flash_bwd);
     m.def("flash_supported", [](int64_t S, int64_t HD) { return sg::flash_attn_supported((int)S, (int)HD); });
     m.def("ce_fwd", &ce_fwd);

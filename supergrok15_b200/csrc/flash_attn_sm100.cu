@@ -31,6 +31,33 @@ __device__ __forceinline__ float ex2f(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+// two fused multiply-adds in one instruction (packed fp32 pair): y = x * a + b
+__device__ __forceinline__ void fma2(float x0, float x1, float a, float b, float& y0, float& y1) {
+    asm("{\n\t.reg .b64 vx, va, vb, vy;\n\tmov.b64 vx, {%2, %3};\n\tmov.b64 va, {%4, %4};\n\tmov.b64 vb, {%5, %5};\n\t"
+        "fma.rn.f32x2 vy, vx, va, vb;\n\tmov.b64 {%0, %1}, vy;\n\t}"
+        : "=f"(y0), "=f"(y1) : "f"(x0), "f"(x1), "f"(a), "f"(b));
+}
+__device__ __forceinline__ float max3f(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+// Row maximum of 128 scores held in registers (three-input max: 64 instructions instead of 128); on the diagonal block the
+// entries right of the diagonal are first replaced by -FLT_MAX.
+__device__ __forceinline__ float row_max_128(uint32_t (&r)[4][32], bool diag, int row) {
+    if (diag) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+            for (int i = 0; i < 32; ++i) if (c * 32 + i > row) r[c][i] = __float_as_uint(-FLT_MAX);
+    }
+    float mx = -FLT_MAX;
+#pragma unroll
+    for (int c = 0; c < 4; ++c)
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) mx = max3f(mx, __uint_as_float(r[c][i]), __uint_as_float(r[c][i + 1]));
+    return mx;
+}
 __device__ __forceinline__ void mbar_arrive_(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
@@ -355,14 +382,7 @@ __global__ void __launch_bounds__(FA_THREADS, 1) flash_fwd2_kernel(const __grid_
 #pragma unroll
             for (int c = 0; c < 4; ++c) tc_ld32(ts + c * 32, r[c]);
             tc_wait_ld();
-            float mx = -FLT_MAX;
-#pragma unroll
-            for (int c = 0; c < 4; ++c)
-#pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    if (diag && c * 32 + i > row) r[c][i] = __float_as_uint(-FLT_MAX);
-                    mx = fmaxf(mx, __uint_as_float(r[c][i]));
-                }
+            const float mx = row_max_128(r, diag, row);
             float alpha = 1.f;
             bool move = false;
             if (j == 0) m_ref = mx;
@@ -389,11 +409,11 @@ __global__ void __launch_bounds__(FA_THREADS, 1) flash_fwd2_kernel(const __grid_
 #pragma unroll
                 for (int i = 0; i < 32; ++i) {
                     const int k0 = c * 64 + 2 * i;
-                    const float p0 = ex2f(fmaf(__uint_as_float(r[k0 >> 5][k0 & 31]), c2, -mc));
-                    const float p1 = ex2f(fmaf(__uint_as_float(r[(k0 + 1) >> 5][(k0 + 1) & 31]), c2, -mc));
+                    float e0, e1;
+                    fma2(__uint_as_float(r[k0 >> 5][k0 & 31]), __uint_as_float(r[(k0 + 1) >> 5][(k0 + 1) & 31]), c2, -mc, e0, e1);
+                    const float p0 = ex2f(e0), p1 = ex2f(e1);
                     const __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
-                    const float2 back = __bfloat1622float2(hh);
-                    rowsum += back.x + back.y;
+                    rowsum += p0 + p1;
                     pk[i] = *reinterpret_cast<const uint32_t*>(&hh);
                 }
                 tc_st32(ts + c * 32, pk);
@@ -434,6 +454,215 @@ __global__ void __launch_bounds__(FA_THREADS, 1) flash_fwd2_kernel(const __grid_
     }
 }
 
+// ---------------------------------------------------------------------------------------------------------------------------
+// Third forward kernel: two query tiles (A: rows [0,128), B: rows [128,256) of a 256-row block) per CTA in ping-pong, sharing
+// every K_j / V_j tile.  Each tile has its own S/P buffer and O accumulator in TMEM (4 x 128 columns) and its own group of 128
+// softmax threads.  The MMA warp issues
+//     S_A(0), S_B(0), then for j:  O_A += P_A(j) V_j,  S_A(j+1),  O_B += P_B(j) V_j,  S_B(j+1)
+// so while one group works on its scores the tensor pipe runs the other tile's two products: each softmax has two MMA slots to
+// finish in.  P overlays S in TMEM, O is rescaled lazily (as in the second kernel).  With the causal mask tile A stops one key
+// block before tile B.  S must be a multiple of 256.
+constexpr int FA3_THREADS = 320;
+struct Fa3Bars {
+    uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_full[2], o_done[2][2];
+    uint32_t tmem_slot, pad;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(FA3_THREADS, 1) flash_fwd3_kernel(const __grid_constant__ CUtensorMap map_q,
+                                                                    const __grid_constant__ CUtensorMap map_k,
+                                                                    const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
+                                                                    float* __restrict__ lse, int S, int H, int64_t ld_o, float scale,
+                                                                    int causal, int* __restrict__ err) {
+    constexpr int HALVES = HD / 64;
+    constexpr uint32_t QKV_BYTES = HALVES * TILE_HALF_BYTES;
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t* sQ = smem;                                  // [2 tiles][QKV_BYTES]
+    uint8_t* sK = sQ + 2 * QKV_BYTES;                    // [2][QKV_BYTES]
+    uint8_t* sV = sK + 2 * QKV_BYTES;                    // [2][QKV_BYTES]
+    Fa3Bars* bars = reinterpret_cast<Fa3Bars*>(sV + 2 * QKV_BYTES);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // 1-D grid ordered by decreasing work: all (batch, head) pairs of the last 256-row block first, those of block 0 last
+    const int nqb = S / 256, n_hb = (int)gridDim.x / nqb, hb = (int)blockIdx.x % n_hb, qb = nqb - 1 - (int)blockIdx.x / n_hb;
+    const int h = hb % H, b = hb / H;
+    // key blocks per tile: tile t covers rows of 128-tile index 2*qb + t
+    const int nA = causal ? 2 * qb + 1 : S / 128, nB = causal ? 2 * qb + 2 : S / 128;
+    const int row_q = b * S + qb * 256, col0 = h * HD;
+
+    if (threadIdx.x == 0) {
+        mbar_init(&bars->q_full, 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&bars->k_full[i], 1); mbar_init(&bars->k_empty[i], 1); mbar_init(&bars->v_full[i], 1); mbar_init(&bars->v_empty[i], 1);
+            mbar_init(&bars->s_full[i], 1); mbar_init(&bars->p_full[i], 128);
+            mbar_init(&bars->o_done[i][0], 1); mbar_init(&bars->o_done[i][1], 1);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bars->tmem_slot)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = bars->tmem_slot;          // tile t: S/P at t*128, O at 256 + t*128
+
+    if (warp == 0) {
+        if (lane == 0) {
+            mbar_expect_tx(&bars->q_full, 2 * QKV_BYTES);
+            for (int t = 0; t < 2; ++t)
+                for (int hf = 0; hf < HALVES; ++hf)
+                    tma_load_2d(sQ + t * QKV_BYTES + hf * TILE_HALF_BYTES, &map_q, col0 + hf * 64, row_q + t * 128, &bars->q_full);
+            for (int j = 0; j < nB; ++j) {
+                const int s = j & 1, row_k = b * S + j * 128;
+                if (j >= 2 && !mbar_wait(&bars->k_empty[s], ((j >> 1) & 1) ^ 1)) { atomicExch(err, 41); break; }
+                mbar_expect_tx(&bars->k_full[s], QKV_BYTES);
+                for (int hf = 0; hf < HALVES; ++hf) tma_load_2d(sK + s * QKV_BYTES + hf * TILE_HALF_BYTES, &map_k, col0 + hf * 64, row_k, &bars->k_full[s]);
+                if (j >= 2 && !mbar_wait(&bars->v_empty[s], ((j >> 1) & 1) ^ 1)) { atomicExch(err, 42); break; }
+                mbar_expect_tx(&bars->v_full[s], QKV_BYTES);
+                for (int hf = 0; hf < HALVES; ++hf) tma_load_2d(sV + s * QKV_BYTES + hf * TILE_HALF_BYTES, &map_v, col0 + hf * 64, row_k, &bars->v_full[s]);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc_qk = make_idesc_bf16(128, 128, 0, 0);
+            constexpr uint32_t idesc_pv = make_idesc_bf16(128, HD, 0, 1);
+            bool ok = mbar_wait(&bars->q_full, 0);
+            if (!ok) atomicExch(err, 43);
+            tc_fence_after();
+            // S_t(j) = Q_t K_j^T ; the K slot is released after tile B (or after tile A when B does not exist - never: nB >= nA)
+            auto issue_qk = [&](int t, int j) {
+                const int s = j & 1;
+#pragma unroll
+                for (int kk = 0; kk < HD / 16; ++kk) {
+                    const uint64_t da = make_desc_sw128(smem_u32(sQ + t * QKV_BYTES + (kk / 4) * TILE_HALF_BYTES)) + 2 * (kk % 4);
+                    const uint64_t db = make_desc_sw128(smem_u32(sK + s * QKV_BYTES + (kk / 4) * TILE_HALF_BYTES)) + 2 * (kk % 4);
+                    tc_mma_bf16(tmem_base + t * 128, da, db, idesc_qk, kk > 0 ? 1u : 0u);
+                }
+                if (t == 1) tc_commit(&bars->k_empty[s]);
+                tc_commit(&bars->s_full[t]);
+            };
+            auto issue_pv = [&](int t, int j) {
+                const int s = j & 1;
+#pragma unroll
+                for (int kk = 0; kk < 8; ++kk) {
+                    const uint64_t db = make_desc_sw128_mn(smem_u32(sV + s * QKV_BYTES + kk * 2048), TILE_HALF_BYTES, 1024);
+                    tc_mma_bf16_ta(tmem_base + 256 + t * 128, tmem_base + t * 128 + kk * 8, db, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+                }
+                if (t == 1) tc_commit(&bars->v_empty[s]);
+                tc_commit(&bars->o_done[t][j & 1]);
+            };
+            if (ok) {
+                if (!mbar_wait(&bars->k_full[0], 0)) { atomicExch(err, 44); ok = false; }
+                else { tc_fence_after(); issue_qk(0, 0); issue_qk(1, 0); }
+            }
+            for (int j = 0; j < nB && ok; ++j) {
+                const int s = j & 1;
+                if (!mbar_wait(&bars->v_full[s], (j >> 1) & 1)) { atomicExch(err, 45); ok = false; break; }
+                const bool next = j + 1 < nB;
+                if (next && !mbar_wait(&bars->k_full[(j + 1) & 1], ((j + 1) >> 1) & 1)) { atomicExch(err, 46); ok = false; break; }
+                if (j < nA) {
+                    if (!mbar_wait(&bars->p_full[0], j & 1)) { atomicExch(err, 47); ok = false; break; }
+                    tc_fence_after();
+                    issue_pv(0, j);
+                    if (j + 1 < nA) issue_qk(0, j + 1);
+                }
+                if (!mbar_wait(&bars->p_full[1], j & 1)) { atomicExch(err, 48); ok = false; break; }
+                tc_fence_after();
+                issue_pv(1, j);
+                if (next) issue_qk(1, j + 1);
+            }
+        }
+    } else {
+        const int t = (warp - 2) >> 2;                                   // tile of this softmax group
+        const int q = warp & 3, row = q * 32 + lane;
+        const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
+        const uint32_t ts = tmem_base + t * 128 + lane_addr, to = tmem_base + 256 + t * 128 + lane_addr;
+        const float c2 = scale * 1.4426950408889634f;
+        const int n_blk = t == 0 ? nA : nB, diag_j = 2 * qb + t;
+        float m_ref = -FLT_MAX, l = 0.f;
+        bool ok = true;
+        for (int j = 0; j < n_blk && ok; ++j) {
+            if (!mbar_wait(&bars->s_full[t], j & 1)) { atomicExch(err, 49); ok = false; break; }
+            tc_fence_after();
+            const bool diag = causal && j == diag_j;
+            uint32_t r[4][32];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) tc_ld32(ts + c * 32, r[c]);
+            tc_wait_ld();
+            const float mx = row_max_128(r, diag, row);
+            float alpha = 1.f;
+            bool move = false;
+            if (j == 0) m_ref = mx;
+            else if ((mx - m_ref) * c2 > 8.f) { alpha = ex2f((m_ref - mx) * c2); m_ref = mx; move = true; }
+            if (j > 0 && __any_sync(0xffffffffu, move)) {
+                if (!mbar_wait(&bars->o_done[t][(j - 1) & 1], ((j - 1) >> 1) & 1)) { atomicExch(err, 50); ok = false; break; }
+                tc_fence_after();
+#pragma unroll 1
+                for (int c = 0; c < HD / 32; ++c) {
+                    uint32_t u[32];
+                    tc_ld32(to + c * 32, u);
+                    tc_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) u[i] = __float_as_uint(__uint_as_float(u[i]) * alpha);
+                    tc_st32(to + c * 32, u);
+                }
+            }
+            const float mc = m_ref * c2;
+            float rowsum = 0.f, rowsum1 = 0.f;
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                uint32_t pk[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const int k0 = c * 64 + 2 * i;
+                    float e0, e1;
+                    fma2(__uint_as_float(r[k0 >> 5][k0 & 31]), __uint_as_float(r[(k0 + 1) >> 5][(k0 + 1) & 31]), c2, -mc, e0, e1);
+                    const float p0 = ex2f(e0), p1 = ex2f(e1);
+                    const __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
+                    rowsum += p0; rowsum1 += p1;                  // two independent chains (the compiler may pair them)
+                    pk[i] = *reinterpret_cast<const uint32_t*>(&hh);
+                }
+                tc_st32(ts + c * 32, pk);
+            }
+            tc_wait_st();
+            tc_fence_before();
+            mbar_arrive_(&bars->p_full[t]);
+            l = l * alpha + (rowsum + rowsum1);
+        }
+        if (ok && !mbar_wait(&bars->o_done[t][(n_blk - 1) & 1], ((n_blk - 1) >> 1) & 1)) { atomicExch(err, 51); ok = false; }
+        if (ok) {
+            tc_fence_after();
+            const float inv = 1.f / l;
+            const int64_t grow = (int64_t)row_q + t * 128 + row;
+            __nv_bfloat16* orow = out + grow * ld_o + col0;
+#pragma unroll 1
+            for (int c = 0; c < HD / 32; ++c) {
+                uint32_t u[32];
+                tc_ld32(to + c * 32, u);
+                tc_wait_ld();
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    uint4 pk;
+                    __nv_bfloat162* hh = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+                    for (int v = 0; v < 4; ++v) hh[v] = __floats2bfloat162_rn(__uint_as_float(u[8 * k + 2 * v]) * inv, __uint_as_float(u[8 * k + 2 * v + 1]) * inv);
+                    reinterpret_cast<uint4*>(orow)[c * 4 + k] = pk;
+                }
+            }
+            lse[((int64_t)b * H + h) * S + qb * 256 + t * 128 + row] = m_ref * scale + logf(l);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+    }
+}
+
 template <int HD>
 int launch_fwd(const void* q, const void* k, const void* v, int64_t ld, void* out, int64_t ld_o, float* lse, int B, int S, int H, float scale,
                bool causal, int variant, int* err, cudaStream_t st) {
@@ -443,14 +672,18 @@ int launch_fwd(const void* q, const void* k, const void* v, int64_t ld, void* ou
         !make_map(&mv, v, rows, (int64_t)H * HD, ld, 128, 64, true)) return 1;
     constexpr size_t smem = (size_t)(5 * (HD / 64) + 2) * TILE_HALF_BYTES + sizeof(FaBars) + 1024;
     constexpr size_t smem2 = (size_t)(5 * (HD / 64)) * TILE_HALF_BYTES + sizeof(Fa2Bars) + 1024;
+    constexpr size_t smem3 = (size_t)(6 * (HD / 64)) * TILE_HALF_BYTES + sizeof(Fa3Bars) + 1024;
     static bool configured = false;
     if (!configured) {
         if (cudaFuncSetAttribute(flash_fwd_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return 2;
         if (cudaFuncSetAttribute(flash_fwd2_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2) != cudaSuccess) return 2;
+        if (cudaFuncSetAttribute(flash_fwd3_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem3) != cudaSuccess) return 2;
         configured = true;
     }
     count_launch();
-    if (variant == 2)
+    if (variant == 3 && S % 256 == 0)
+        flash_fwd3_kernel<HD><<<dim3((S / 256) * H * B), FA3_THREADS, smem3, st>>>(mq, mk, mv, (__nv_bfloat16*)out, lse, S, H, ld_o, scale, causal ? 1 : 0, err);
+    else if (variant >= 2)
         flash_fwd2_kernel<HD><<<dim3(S / 128, H, B), FA_THREADS, smem2, st>>>(mq, mk, mv, (__nv_bfloat16*)out, lse, S, H, ld_o, scale, causal ? 1 : 0, err);
     else
         flash_fwd_kernel<HD><<<dim3(S / 128, H, B), FA_THREADS, smem, st>>>(mq, mk, mv, (__nv_bfloat16*)out, lse, S, H, ld_o, scale, causal ? 1 : 0, err);
@@ -737,7 +970,8 @@ int launch_bwd(const void* q, const void* k, const void* v, int64_t ld, const vo
 bool flash_attn_supported(int S, int HD) { return S % 128 == 0 && (HD == 64 || HD == 128); }
 
 // q, k, v: bf16 [B, S, H, HD] with a common row pitch `ld` (elements between consecutive positions; >= H*HD); out: [B, S, H, HD] with
-// row pitch ld_o; lse: fp32 [B, H, S].  variant 1: P through shared memory, O in registers; variant 2: P and O stay in TMEM.
+// row pitch ld_o; lse: fp32 [B, H, S].  variant 1: P through shared memory, O in registers; variant 2: P and O stay in TMEM; variant 3: two query tiles per CTA in
+// ping-pong (falls back to 2 when S is not a multiple of 256).
 // Returns 0 on success.
 int flash_attn_fwd(const void* q, const void* k, const void* v, int64_t ld, void* out, int64_t ld_o, float* lse, int B, int S, int H, int HD,
                    float scale, bool causal, int variant, int* err, cudaStream_t st) {

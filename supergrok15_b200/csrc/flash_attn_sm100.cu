@@ -37,6 +37,12 @@ __device__ __forceinline__ void fma2(float x0, float x1, float a, float b, float
         "fma.rn.f32x2 vy, vx, va, vb;\n\tmov.b64 {%0, %1}, vy;\n\t}"
         : "=f"(y0), "=f"(y1) : "f"(x0), "f"(x1), "f"(a), "f"(b));
 }
+// general packed pair: y = x * a + b with every operand a pair
+__device__ __forceinline__ void fma2g(float x0, float x1, float a0, float a1, float b0, float b1, float& y0, float& y1) {
+    asm("{\n\t.reg .b64 vx, va, vb, vy;\n\tmov.b64 vx, {%2, %3};\n\tmov.b64 va, {%4, %5};\n\tmov.b64 vb, {%6, %7};\n\t"
+        "fma.rn.f32x2 vy, vx, va, vb;\n\tmov.b64 {%0, %1}, vy;\n\t}"
+        : "=f"(y0), "=f"(y1) : "f"(x0), "f"(x1), "f"(a0), "f"(a1), "f"(b0), "f"(b1));
+}
 __device__ __forceinline__ float max3f(float a, float b, float c) {
     float d;
     asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
@@ -703,22 +709,30 @@ int launch_fwd(const void* q, const void* k, const void* v, int64_t ld, void* ou
 __global__ void __launch_bounds__(256) flash_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dout,
                                                           float* __restrict__ delta, int64_t rows, int S, int H, int HD, int64_t ld_o,
                                                           int64_t ld_do) {
-    const int lane = threadIdx.x & 31;
-    const int64_t item = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);          // (b*S + s) * H + h
-    if (item >= rows * H) return;
-    const int64_t bs = item / H;
-    const int h = (int)(item % H);
-    const __nv_bfloat16* po = o + bs * ld_o + (int64_t)h * HD;
-    const __nv_bfloat16* pd = dout + bs * ld_do + (int64_t)h * HD;
+    // HD / 8 lanes per (position, head) row, 16 bytes of O and of dO per lane; the lanes of a row sit in one warp
+    const int lpr = HD / 8;                                              // 8 or 16
+    const int64_t gid = (int64_t)blockIdx.x * 256 + threadIdx.x;
+    const int64_t item = gid / lpr;                                      // (b*S + s) * H + h
+    const int part = (int)(gid % lpr);
     float acc = 0.f;
-    for (int c = lane * 2; c < HD; c += 64) {
-        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(po + c));
-        const float2 d = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(pd + c));
-        acc += a.x * d.x + a.y * d.y;
-    }
+    const bool live = item < rows * H;
+    int64_t bs = 0;
+    int h = 0;
+    if (live) {
+        bs = item / H;
+        h = (int)(item % H);
+        const uint4 a = *reinterpret_cast<const uint4*>(o + bs * ld_o + (int64_t)h * HD + part * 8);
+        const uint4 d = *reinterpret_cast<const uint4*>(dout + bs * ld_do + (int64_t)h * HD + part * 8);
+        const __nv_bfloat162* ah = reinterpret_cast<const __nv_bfloat162*>(&a);
+        const __nv_bfloat162* dh = reinterpret_cast<const __nv_bfloat162*>(&d);
 #pragma unroll
-    for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
-    if (lane == 0) delta[((bs / S) * H + h) * S + bs % S] = acc;
+        for (int k = 0; k < 4; ++k) {
+            const float2 x = __bfloat1622float2(ah[k]), y = __bfloat1622float2(dh[k]);
+            acc = fmaf(x.x, y.x, fmaf(x.y, y.y, acc));
+        }
+    }
+    for (int off = lpr >> 1; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+    if (live && part == 0) delta[((bs / S) * H + h) * S + bs % S] = acc;
 }
 
 struct FbBars {
@@ -751,8 +765,11 @@ __global__ void __launch_bounds__(FA_THREADS, 1) flash_bwd_kernel(const __grid_c
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nt = S / 128;
-    const int tile = KV ? (int)blockIdx.x : (int)gridDim.x - 1 - (int)blockIdx.x;     // kernel B: long query tiles first
-    const int h = blockIdx.y, b = blockIdx.z;
+    // 1-D grid ordered by decreasing work: kernel A starts with key tile 0 (visited by every query tile), kernel B with the last
+    // query tile; all (batch, head) pairs of one tile index are adjacent
+    const int n_hb = (int)gridDim.x / nt, hb = (int)blockIdx.x % n_hb, ord = (int)blockIdx.x / n_hb;
+    const int tile = KV ? ord : nt - 1 - ord;
+    const int h = hb % H, b = hb / H;
     // tiles of the other sequence axis that interact with this one
     const int first = KV ? (causal ? tile : 0) : 0;
     const int n_it = KV ? nt - first : (causal ? tile + 1 : nt);
@@ -838,13 +855,17 @@ __global__ void __launch_bounds__(FA_THREADS, 1) flash_bwd_kernel(const __grid_c
         float lse_row = 0.f, del_row = 0.f;
         if (!KV) { lse_row = lse[vec0 + tile * 128 + row] * 1.4426950408889634f; del_row = delta[vec0 + tile * 128 + row]; }
         bool ok = true;
+        if (KV) {                                                        // per-query vectors of the first query tile
+            s_lse[tl] = -lse[vec0 + first * 128 + tl] * 1.4426950408889634f;
+            s_del[tl] = delta[vec0 + first * 128 + tl];
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+        }
         for (int it = 0; it < n_it && ok; ++it) {
             const int other = first + it, bs = it & 1;
-            if (KV) {                                                    // per-query vectors of this query tile, shared by all key rows
-                s_lse[bs * 128 + tl] = lse[vec0 + other * 128 + tl] * 1.4426950408889634f;
-                s_del[bs * 128 + tl] = delta[vec0 + other * 128 + tl];
-                asm volatile("bar.sync 1, 128;" ::: "memory");
-            }
+            // kernel A: the per-query vectors of the NEXT tile are fetched now and parked in the other buffer at the end of this
+            // iteration, so their global-memory latency hides behind the work on this tile
+            float nx_lse = 0.f, nx_del = 0.f;
+            if (KV && it + 1 < n_it) { nx_lse = lse[vec0 + (other + 1) * 128 + tl]; nx_del = delta[vec0 + (other + 1) * 128 + tl]; }
             if (!mbar_wait(&bars->a_full, it & 1)) { atomicExch(err, 36); ok = false; break; }
             tc_fence_after();
             const bool diag = causal && other == tile;
@@ -852,17 +873,26 @@ __global__ void __launch_bounds__(FA_THREADS, 1) flash_bwd_kernel(const __grid_c
 #pragma unroll
             for (int c = 0; c < 4; ++c) tc_ld32(tm_x + lane_addr + c * 32, r[c]);
             tc_wait_ld();
-            // P (kernel B: row = query, column = key) or P^T (kernel A: row = key, column = query), kept in fp32 for dS
+            // P (kernel B: row = query, column = key) or P^T (kernel A: row = key, column = query), kept in fp32 for dS.
+            // s_lse holds -lse*log2(e), read four columns per shared-memory load; two scores per packed fma.
 #pragma unroll
             for (int c = 0; c < 4; ++c)
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const int col = c * 32 + i;
-                    const float ls = KV ? s_lse[bs * 128 + col] : lse_row;
-                    float p = ex2f(fmaf(__uint_as_float(r[c][i]), c2, -ls));
-                    if (diag && (KV ? col < row : col > row)) p = 0.f;     // key index must not exceed the query index
-                    r[c][i] = __float_as_uint(p);
+                for (int i = 0; i < 32; i += 4) {
+                    float4 nl = make_float4(-lse_row, -lse_row, -lse_row, -lse_row);
+                    if (KV) nl = *reinterpret_cast<const float4*>(s_lse + bs * 128 + c * 32 + i);
+                    float e0, e1, e2, e3;
+                    fma2g(__uint_as_float(r[c][i]), __uint_as_float(r[c][i + 1]), c2, c2, nl.x, nl.y, e0, e1);
+                    fma2g(__uint_as_float(r[c][i + 2]), __uint_as_float(r[c][i + 3]), c2, c2, nl.z, nl.w, e2, e3);
+                    r[c][i] = __float_as_uint(ex2f(e0)); r[c][i + 1] = __float_as_uint(ex2f(e1));
+                    r[c][i + 2] = __float_as_uint(ex2f(e2)); r[c][i + 3] = __float_as_uint(ex2f(e3));
                 }
+            if (diag) {                                                  // key index must not exceed the query index
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) if (KV ? c * 32 + i < row : c * 32 + i > row) r[c][i] = 0u;
+            }
             if (KV) {
 #pragma unroll
                 for (int c = 0; c < 2; ++c) {
@@ -892,9 +922,11 @@ __global__ void __launch_bounds__(FA_THREADS, 1) flash_bwd_kernel(const __grid_c
                     const int k0 = c * 64 + 2 * i;                        // columns k0, k0+1
                     const float dp0 = __uint_as_float(i < 16 ? d0[2 * i] : d1[2 * i - 32]);
                     const float dp1 = __uint_as_float(i < 16 ? d0[2 * i + 1] : d1[2 * i - 31]);
-                    const float de0 = KV ? s_del[bs * 128 + k0] : del_row, de1 = KV ? s_del[bs * 128 + k0 + 1] : del_row;
-                    const float ds0 = __uint_as_float(r[k0 >> 5][k0 & 31]) * (dp0 - de0);
-                    const float ds1 = __uint_as_float(r[(k0 + 1) >> 5][(k0 + 1) & 31]) * (dp1 - de1);
+                    float2 de = make_float2(del_row, del_row);
+                    if (KV) de = *reinterpret_cast<const float2*>(s_del + bs * 128 + k0);
+                    float t0, t1, ds0, ds1;
+                    fma2g(de.x, de.y, -1.f, -1.f, dp0, dp1, t0, t1);                                  // dP - delta
+                    fma2g(__uint_as_float(r[k0 >> 5][k0 & 31]), __uint_as_float(r[(k0 + 1) >> 5][(k0 + 1) & 31]), t0, t1, 0.f, 0.f, ds0, ds1);
                     const __nv_bfloat162 hh = __floats2bfloat162_rn(ds0, ds1);
                     pk[i] = *reinterpret_cast<const uint32_t*>(&hh);
                 }
@@ -905,6 +937,10 @@ __global__ void __launch_bounds__(FA_THREADS, 1) flash_bwd_kernel(const __grid_c
             tc_wait_st();
             tc_fence_before();
             mbar_arrive_(&bars->pb_full);
+            if (KV) {                                                    // buffer (it+1)&1 was last read in iteration it-1
+                if (it + 1 < n_it) { s_lse[(bs ^ 1) * 128 + tl] = -nx_lse * 1.4426950408889634f; s_del[(bs ^ 1) * 128 + tl] = nx_del; }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+            }
         }
         if (ok && !mbar_wait(&bars->done, 0)) { atomicExch(err, 38); ok = false; }
         if (ok) {
@@ -956,11 +992,11 @@ int launch_bwd(const void* q, const void* k, const void* v, int64_t ld, const vo
         configured = true;
     }
     count_launch(3);
-    flash_delta_kernel<<<(unsigned)((rows * H + 7) / 8), 256, 0, st>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)dout, delta, rows, S, H, HD, ld_o, ld_o);
+    flash_delta_kernel<<<(unsigned)((rows * H * (HD / 8) + 255) / 256), 256, 0, st>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)dout, delta, rows, S, H, HD, ld_o, ld_o);
     const int64_t ld_out = (int64_t)H * HD;
-    flash_bwd_kernel<HD, true><<<dim3(S / 128, H, B), FA_THREADS, smem, st>>>(mq, mk, mv, md, lse, delta, (__nv_bfloat16*)dv, (__nv_bfloat16*)dk, S, H,
+    flash_bwd_kernel<HD, true><<<dim3((S / 128) * H * B), FA_THREADS, smem, st>>>(mq, mk, mv, md, lse, delta, (__nv_bfloat16*)dv, (__nv_bfloat16*)dk, S, H,
                                                                              ld_out, scale, causal ? 1 : 0, err);
-    flash_bwd_kernel<HD, false><<<dim3(S / 128, H, B), FA_THREADS, smem, st>>>(mq, mk, mv, md, lse, delta, (__nv_bfloat16*)dq, nullptr, S, H, ld_out,
+    flash_bwd_kernel<HD, false><<<dim3((S / 128) * H * B), FA_THREADS, smem, st>>>(mq, mk, mv, md, lse, delta, (__nv_bfloat16*)dq, nullptr, S, H, ld_out,
                                                                               scale, causal ? 1 : 0, err);
     return cudaGetLastError() == cudaSuccess ? 0 : 3;
 }

@@ -326,3 +326,24 @@ def test_engine_graphed_forward_backward_equals_eager():
     assert l0 == l1, (l0, l1)
     for a, b in zip(p0, p1):
         assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("optimizer", ["muon", "adamw"])
+def test_engine_language_model_path(optimizer):
+    """Tiny Llama-style decoder through ZeroEngine on one GPU: embedding, rotary, RMSNorm + residual, SwiGLU, fused cross-entropy on
+    [B*S, V] logits, micro-batching; the loss must fall and match the eager PyTorch loss of the same model at step 0."""
+    from supergrok15_b200.models.llama import Llama, LLAMA_TINY
+    from supergrok15_b200.parallel import ZeroEngine
+    dev = torch.device("cuda:0")
+    torch.manual_seed(0)
+    model = Llama(LLAMA_TINY).to(dev)
+    ids = torch.randint(0, LLAMA_TINY.vocab, (8, 33), device=dev)
+    x, y = ids[:, :-1].contiguous(), ids[:, 1:].contiguous()
+    with torch.no_grad():
+        ref0 = float(F.cross_entropy(model(x).float().reshape(-1, LLAMA_TINY.vocab), y.reshape(-1)))
+    kw = dict(lr=0.02, momentum=0.95, adamw_lr=3e-3, adamw_names=("embed", "lm_head")) if optimizer == "muon" else dict(lr=3e-3)
+    eng = ZeroEngine(model, optimizer, kw, param_dtype=torch.bfloat16, graph=True, graph_warmup=2)
+    losses = [float(eng.train_step(x, y, micro_batches=2).item()) for _ in range(12)]
+    eng.check()
+    assert abs(losses[0] - ref0) < 0.05 * ref0, (losses[0], ref0)
+    assert losses[-1] < 0.8 * losses[0], losses

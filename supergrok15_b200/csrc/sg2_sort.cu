@@ -87,6 +87,10 @@ __global__ void __launch_bounds__(256) sort_scan_rows_kernel(uint32_t* __restric
     if (threadIdx.x == 0) tot[blockIdx.x] = carry_s;
 }
 
+// Stable scatter of one tile.  The keys are first ranked (warp-private match_any ranking, then a scan over the warps) and parked in
+// shared memory in their digit order inside the tile; the tile is then written out entry by entry, so that the entries of one
+// digit - which go to consecutive global positions - are stored by consecutive lanes (runs of ~16 keys = 64 bytes instead of
+// isolated 4-byte writes).
 __global__ void __launch_bounds__(SORT_THREADS) sort_scatter_kernel(const uint32_t* __restrict__ keys_in,
                                                                     const uint32_t* __restrict__ vals_in,
                                                                     uint32_t* __restrict__ keys_out, uint32_t* __restrict__ vals_out,
@@ -94,9 +98,12 @@ __global__ void __launch_bounds__(SORT_THREADS) sort_scatter_kernel(const uint32
                                                                     const uint32_t* __restrict__ tot,
                                                                     const int64_t* __restrict__ seg_off, int n_seg, int64_t total,
                                                                     int pass, int n_blocks) {
-    __shared__ uint32_t wcnt[SORT_WARPS][256];        // per-warp running digit counts -> warp bases
-    __shared__ uint32_t gbase[256];
+    __shared__ uint32_t wcnt[SORT_WARPS][256];        // per-warp running digit counts -> warp bases inside the tile's digit run
+    __shared__ uint32_t gbase[256];                   // global position of this tile's first key of digit d
+    __shared__ uint32_t tstart[256];                  // position of digit d inside the tile (exclusive scan of the tile's digit counts)
     __shared__ uint32_t wtot[SORT_WARPS];
+    __shared__ uint32_t s_key[SORT_TILE], s_val[SORT_TILE];
+    __shared__ uint8_t s_dig[SORT_TILE];
     const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
     for (int i = threadIdx.x; i < SORT_WARPS * 256; i += SORT_THREADS) (&wcnt[0][0])[i] = 0;
     {   // digit base = exclusive scan of the 256 digit totals (thread d owns digit d)
@@ -112,7 +119,9 @@ __global__ void __launch_bounds__(SORT_THREADS) sort_scatter_kernel(const uint32
         gbase[threadIdx.x] = woff + (inc - t) + hist[(int64_t)threadIdx.x * n_blocks + blockIdx.x];
     }
     __syncthreads();
-    const int64_t wbase = (int64_t)blockIdx.x * SORT_TILE + (int64_t)w * (32 * SORT_IPT);
+    const int64_t tile0 = (int64_t)blockIdx.x * SORT_TILE;
+    const int64_t wbase = tile0 + (int64_t)w * (32 * SORT_IPT);
+    const int n_tile = (int)((total - tile0 < SORT_TILE) ? total - tile0 : SORT_TILE);
     uint32_t k[SORT_IPT], v[SORT_IPT], d[SORT_IPT], rk[SORT_IPT];
 #pragma unroll
     for (int r = 0; r < SORT_IPT; ++r) {
@@ -130,20 +139,40 @@ __global__ void __launch_bounds__(SORT_THREADS) sort_scatter_kernel(const uint32
         __syncwarp();
     }
     __syncthreads();
-    {   // exclusive scan over warps for digit = threadIdx.x
+    uint32_t my_cnt;
+    {   // exclusive scan over warps for digit = threadIdx.x; the total is the tile's count of that digit
         uint32_t run = 0;
 #pragma unroll
         for (int ww = 0; ww < SORT_WARPS; ++ww) { const uint32_t c = wcnt[ww][threadIdx.x]; wcnt[ww][threadIdx.x] = run; run += c; }
+        my_cnt = run;
+    }
+    {   // exclusive scan of the tile's digit counts over the 256 digits
+        uint32_t inc = my_cnt;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) { const uint32_t u = __shfl_up_sync(0xffffffffu, inc, o); if (lane >= o) inc += u; }
+        __syncthreads();                              // wtot is reused
+        if (lane == 31) wtot[w] = inc;
+        __syncthreads();
+        uint32_t woff = 0;
+#pragma unroll
+        for (int ww = 0; ww < SORT_WARPS; ++ww) if (ww < w) woff += wtot[ww];
+        tstart[threadIdx.x] = woff + (inc - my_cnt);
     }
     __syncthreads();
 #pragma unroll
     for (int r = 0; r < SORT_IPT; ++r) {
         const int64_t i = wbase + r * 32 + lane;
         if (i < total) {
-            const int64_t pos = (int64_t)gbase[d[r]] + wcnt[w][d[r]] + rk[r];
-            keys_out[pos] = k[r];
-            vals_out[pos] = v[r];
+            const uint32_t lp = tstart[d[r]] + wcnt[w][d[r]] + rk[r];
+            s_key[lp] = k[r]; s_val[lp] = v[r]; s_dig[lp] = (uint8_t)d[r];
         }
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < n_tile; e += SORT_THREADS) {
+        const uint32_t dg = s_dig[e];
+        const int64_t pos = (int64_t)gbase[dg] + ((uint32_t)e - tstart[dg]);
+        keys_out[pos] = s_key[e];
+        vals_out[pos] = s_val[e];
     }
 }
 

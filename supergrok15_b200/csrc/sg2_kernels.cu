@@ -379,9 +379,15 @@ struct ElemParams {
 template <typename T>
 __global__ void __launch_bounds__(MT_THREADS) sg2_elem_kernel(const __grid_constant__ MTArgs a, const __grid_constant__ ElemParams prm,
                                                               float lamb_eff) {
-    __shared__ float sW1[SG2_NE * SG2_EH], sB1[SG2_NE * SG2_EH], sW2[SG2_NE * SG2_EH], sB2[SG2_NE];
+    // Expert rows are padded to 17 floats: lanes pick different experts, and with a row pitch of 16 the word k of every expert
+    // falls into one of only two banks (16-way conflicts); with 17 the rows of 32 consecutive experts spread over all banks.
+    constexpr int EP = SG2_EH + 1;
+    __shared__ float sW1[SG2_NE * EP], sB1[SG2_NE * EP], sW2[SG2_NE * EP], sB2[SG2_NE];
     __shared__ int scount[SG2_NE];
-    for (int i = threadIdx.x; i < SG2_NE * SG2_EH; i += MT_THREADS) { sW1[i] = c_w[P::EW1 + i]; sB1[i] = c_w[P::EB1 + i]; sW2[i] = c_w[P::EW2 + i]; }
+    for (int i = threadIdx.x; i < SG2_NE * SG2_EH; i += MT_THREADS) {
+        const int j = (i / SG2_EH) * EP + i % SG2_EH;
+        sW1[j] = c_w[P::EW1 + i]; sB1[j] = c_w[P::EB1 + i]; sW2[j] = c_w[P::EW2 + i];
+    }
     for (int i = threadIdx.x; i < SG2_NE; i += MT_THREADS) { sB2[i] = c_w[P::EB2 + i]; scount[i] = 0; }
     __syncthreads();
     int lo = 0, hi = a.n;
@@ -466,7 +472,7 @@ __global__ void __launch_bounds__(MT_THREADS) sg2_elem_kernel(const __grid_const
             if (prm.expert_counts) atomicAdd(&scount[e], 1);
             float ho = sB2[e];
 #pragma unroll
-            for (int k = 0; k < SG2_EH; ++k) ho = fmaf(sW2[e * SG2_EH + k], fmaxf(fmaf(sW1[e * SG2_EH + k], g, sB1[e * SG2_EH + k]), 0.f), ho);
+            for (int k = 0; k < SG2_EH; ++k) ho = fmaf(sW2[e * EP + k], fmaxf(fmaf(sW1[e * EP + k], g, sB1[e * EP + k]), 0.f), ho);
             total += ho;
         }
         const float smart = g + prm.rescale * total * (1.f / SG2_HEADS);

@@ -25,6 +25,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--scale", default="medium", choices=["small", "medium", "large"])
     ap.add_argument("--no-bilevel", action="store_true")
+    ap.add_argument("--kernels", action="store_true", help="also print the device time of every kernel of one step (torch.profiler)")
     a = ap.parse_args()
     root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
     sys.path.insert(0, root)
@@ -75,6 +76,21 @@ def main():
     step_ms = timeit(opt.step, a.steps)
     out = {"impl": a.impl, "scale": a.scale, "params": n_params, "tensors": len(list(model.parameters())), "step_ms": step_ms,
            "step_ms_per_1e9_params": step_ms * 1e9 / n_params}
+    if a.kernels:
+        from torch.profiler import ProfilerActivity, profile
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            for _ in range(3):
+                opt.step()
+            torch.cuda.synchronize()
+        rows = sorted((e for e in prof.key_averages() if e.device_time_total > 0), key=lambda e: -e.device_time_total)
+        tot = sum(e.device_time_total for e in rows)
+        import re
+
+        def short(name):                                   # "void ns::(anonymous namespace)::kernel<3>(args)" -> "kernel<3>"
+            m = re.search(r"([A-Za-z_]\w*(?:<[^()]*>)?)\(", name.replace("(anonymous namespace)", ""))
+            return (m.group(1) if m else name)[:48]
+        out["kernels_us_per_step"] = [[short(e.key), round(e.device_time_total / 3, 1), e.count // 3,
+                                       round(100 * e.device_time_total / tot, 1)] for e in rows[:12]]
     if not a.no_bilevel:
         x = torch.randint(0, 97, (512, 4), device=dev)
         y = torch.randint(0, 97, (512,), device=dev)

@@ -7,7 +7,7 @@
 namespace sg {
 int gemm_bf16_tn(const void* A, int lda, const void* B, int ldb, int M, int N, int K, float alpha, float beta, const void* D, int ldd,
                  bool d_bf16, const void* bias, bool bias_bf16, float diag, int act, void* C, int ldc, bool c_bf16, void* C2, int ldc2,
-                 float* splitk_ws, int64_t splitk_ws_floats, int* err, cudaStream_t s);
+                 float* splitk_ws, int64_t splitk_ws_floats, int* err, cudaStream_t s, bool a_t, bool b_t);
 int gemm_bf16_tn_allgather(const void* A, int lda, const PeerPtrs& w_peers, int rank, int world, int M, int N, int K, void* C, int ldc,
                            bool c_bf16, int* counters, void* sched, int epoch, int n_copy, int* err, cudaStream_t s);
 int gemm_bf16_tn_reducescatter(const void* A, int lda, const void* B, int ldb, int M, int N, int K, const PeerPtrs& slots, const PeerPtrs& flags,
@@ -22,14 +22,16 @@ using at::Tensor;
 // out: bf16 or fp32 [M,N]; out_t (optional): [N,M] receives the transposed result.
 void gemm_tn(const Tensor& a, const Tensor& b, Tensor out, double alpha, double beta, const c10::optional<Tensor>& d,
              const c10::optional<Tensor>& bias, double diag, int64_t act, const c10::optional<Tensor>& out_t, Tensor err,
-             const c10::optional<Tensor>& splitk_ws) {
+             const c10::optional<Tensor>& splitk_ws, bool a_t, bool b_t) {
     TORCH_CHECK(a.is_cuda() && b.is_cuda() && out.is_cuda(), "gemm_tn needs CUDA tensors");
     TORCH_CHECK(a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16, "gemm_tn operands must be bf16");
-    TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && a.size(1) == b.size(1), "shape mismatch: a [M,K], b [N,K]");
+    // a_t: a is stored [K, M]; b_t: b is stored [K, N]
+    TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && a.size(a_t ? 0 : 1) == b.size(b_t ? 0 : 1), "shape mismatch: a [M,K] (or [K,M]), b [N,K] (or [K,N])");
+    TORCH_CHECK(!a_t || b_t, "a_t without b_t is not supported");
     TORCH_CHECK(a.stride(1) == 1 && b.stride(1) == 1 && out.stride(1) == 1, "innermost stride must be 1");
     TORCH_CHECK(a.stride(0) % 8 == 0 && b.stride(0) % 8 == 0, "row strides must be multiples of 8 elements (16 bytes)");
     TORCH_CHECK((reinterpret_cast<uintptr_t>(a.data_ptr()) & 15) == 0 && (reinterpret_cast<uintptr_t>(b.data_ptr()) & 15) == 0, "operands must be 16-byte aligned");
-    const int M = (int)a.size(0), N = (int)b.size(0), K = (int)a.size(1);
+    const int M = (int)a.size(a_t ? 1 : 0), N = (int)b.size(b_t ? 1 : 0), K = (int)a.size(a_t ? 0 : 1);
     TORCH_CHECK(out.size(0) == M && out.size(1) == N, "out must be [M,N]");
     const bool c_bf16 = out.scalar_type() == at::kBFloat16;
     TORCH_CHECK(c_bf16 || out.scalar_type() == at::kFloat, "out must be bf16 or fp32");
@@ -42,7 +44,7 @@ void gemm_tn(const Tensor& a, const Tensor& b, Tensor out, double alpha, double 
                                     bias.has_value() && bias->scalar_type() == at::kBFloat16, (float)diag, (int)act, out.data_ptr(), (int)out.stride(0),
                                     c_bf16, out_t.has_value() ? out_t->data_ptr() : nullptr, out_t.has_value() ? (int)out_t->stride(0) : 0,
                                     splitk_ws.has_value() ? splitk_ws->data_ptr<float>() : nullptr, splitk_ws.has_value() ? splitk_ws->numel() : 0,
-                                    err.data_ptr<int>(), at::cuda::getCurrentCUDAStream());
+                                    err.data_ptr<int>(), at::cuda::getCurrentCUDAStream(), a_t, b_t);
     TORCH_CHECK(rc == 0, "gemm_tn launch failed (code ", rc, ")");
 }
 
@@ -97,7 +99,7 @@ void gemm_tn_reducescatter(const Tensor& a, const Tensor& b, const std::vector<i
 void register_gemm(pybind11::module_& m) {
     m.def("gemm_tn", &gemm_tn, py::arg("a"), py::arg("b"), py::arg("out"), py::arg("alpha") = 1.0, py::arg("beta") = 0.0,
           py::arg("d") = c10::nullopt, py::arg("bias") = c10::nullopt, py::arg("diag") = 0.0, py::arg("act") = 0,
-          py::arg("out_t") = c10::nullopt, py::arg("err"), py::arg("splitk_ws") = c10::nullopt);
+          py::arg("out_t") = c10::nullopt, py::arg("err"), py::arg("splitk_ws") = c10::nullopt, py::arg("a_t") = false, py::arg("b_t") = false);
     m.def("gemm_tn_reducescatter", &gemm_tn_reducescatter, py::arg("a"), py::arg("b"), py::arg("slot_ptrs"), py::arg("flag_ptrs"), py::arg("rank"),
           py::arg("out"), py::arg("epoch"), py::arg("timeout_s"), py::arg("err"));
     m.def("gemm_tn_allgather", &gemm_tn_allgather, py::arg("a"), py::arg("w_ptrs"), py::arg("rank"), py::arg("N"), py::arg("out"),

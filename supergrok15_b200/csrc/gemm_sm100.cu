@@ -140,7 +140,10 @@ __device__ __forceinline__ void ag_tile_coords(const AgArgs& ag, int N, int n_ti
 // Persistent kernel: CTA b computes tiles b, b + gridDim.x, ...  The accumulator is double-buffered in TMEM (2 x BN columns) so
 // the epilogue of tile i overlaps the MMAs of tile i+1.  The epilogue converts 32 rows x 128 bytes at a time, parks them in
 // shared memory in the 128-byte-swizzled layout and lets TMA store them (coalesced, clipped at the matrix edge).
-template <int BN, int STAGES, int MODE>
+// A_MN / B_MN: the operand is stored transposed, [K, M] resp. [K, N] row-major (its M / N index contiguous).  Its stage is then
+// loaded as 64-column boxes of BK rows (chunk c = columns [64c, 64c+64) at c * 8 KB) and read through an MN-major descriptor, so
+// dgrad (dX = dY . W) and wgrad (dW = dY^T . X) take their operands where the forward pass left them - no transposed copies.
+template <int BN, int STAGES, int MODE, bool A_MN = false, bool B_MN = false>
 __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                   const __grid_constant__ CUtensorMap map_b,
                                                                   const __grid_constant__ CUtensorMap map_c, int M, int N, int K,
@@ -234,15 +237,21 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tn_kernel(const __grid_c
                     if (it >= (uint32_t)STAGES && !mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1)) { atomicExch(err, 1); ok = false; break; }
                     uint8_t* a_dst = smem + s * STAGE_BYTES;
                     mbar_expect_tx(&full[s], STAGE_BYTES);
-                    tma_load_2d(a_dst, &map_a, (kb0 + kb) * BK, m0, &full[s]);
-                    tma_load_2d(a_dst + A_BYTES, &map_b, (kb0 + kb) * BK, n0, &full[s]);
+                    if constexpr (A_MN) {
+#pragma unroll
+                        for (int c = 0; c < BM / 64; ++c) tma_load_2d(a_dst + c * (BK * 128), &map_a, m0 + 64 * c, (kb0 + kb) * BK, &full[s]);
+                    } else tma_load_2d(a_dst, &map_a, (kb0 + kb) * BK, m0, &full[s]);
+                    if constexpr (B_MN) {
+#pragma unroll
+                        for (int c = 0; c < BN / 64; ++c) tma_load_2d(a_dst + A_BYTES + c * (BK * 128), &map_b, n0 + 64 * c, (kb0 + kb) * BK, &full[s]);
+                    } else tma_load_2d(a_dst + A_BYTES, &map_b, (kb0 + kb) * BK, n0, &full[s]);
                 }
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
             // instruction descriptor: D fp32, A/B bf16, both K-major, N>>3 at bit 17, M>>4 at bit 24
-            constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+            constexpr uint32_t idesc = make_idesc_bf16(BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
             uint32_t it = 0, t = 0;
             bool ok = true;
             for (int tile = cta; ok; tile += n_cta, ++t) {
@@ -261,10 +270,13 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tn_kernel(const __grid_c
                     if (!mbar_wait(&full[s], (it / STAGES) & 1)) { atomicExch(err, 2); ok = false; break; }
                     tc_fence_after();
                     const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES);
-                    const uint64_t da = make_desc_sw128(a_addr), db = make_desc_sw128(a_addr + A_BYTES);
+                    // K-major: 16 bf16 = 32 bytes per MMA, the start address advances by 2 (16-byte units); MN-major: 16 K rows of
+                    // 128 bytes = 2048 bytes per MMA, 64-column chunks BK * 128 bytes apart
+                    const uint64_t da = A_MN ? make_desc_sw128_mn(a_addr, BK * 128, 1024) : make_desc_sw128(a_addr);
+                    const uint64_t db = B_MN ? make_desc_sw128_mn(a_addr + A_BYTES, BK * 128, 1024) : make_desc_sw128(a_addr + A_BYTES);
 #pragma unroll
-                    for (int k4 = 0; k4 < BK / 16; ++k4)          // 16 bf16 = 32 bytes per MMA: advance the start address by 2 (16-byte units)
-                        tc_mma_bf16(tmem_d, da + 2 * k4, db + 2 * k4, idesc, (kb > 0 || k4 > 0) ? 1u : 0u);
+                    for (int k4 = 0; k4 < BK / 16; ++k4)
+                        tc_mma_bf16(tmem_d, da + (A_MN ? 128 : 2) * k4, db + (B_MN ? 128 : 2) * k4, idesc, (kb > 0 || k4 > 0) ? 1u : 0u);
                     tc_commit(&empty[s]);                         // slot reusable once these MMAs have read it
                 }
                 tc_commit(&acc_full[buf]);                        // accumulator of this tile complete (also arrives when bailing out)
@@ -530,11 +542,13 @@ int num_sms() {
     return n;
 }
 
-template <int BN, int STAGES, int MODE = 0>
+template <int BN, int STAGES, int MODE = 0, bool A_MN = false, bool B_MN = false>
 int launch(const void* A, int lda, const void* B, int ldb, int M, int N, int K, const Epilogue& ep_in, void* C, int ldc, float* ws,
            int64_t ws_floats, int* err, cudaStream_t s, const AgArgs& ag = AgArgs{}) {
     CUtensorMap ma, mb, mc;
-    if (!make_map(&ma, A, M, K, lda, BM, BK, true) || !make_map(&mb, B, N, K, ldb, BN, BK, true)) return 1;
+    // K-major operand: [rows = M or N, cols = K], box BM (BN) x 64; transposed operand: [rows = K, cols = M or N], box 64 x 64
+    if (!(A_MN ? make_map(&ma, A, K, M, lda, BK, 64, true) : make_map(&ma, A, M, K, lda, BM, BK, true))) return 1;
+    if (!(B_MN ? make_map(&mb, B, K, N, ldb, BK, 64, true) : make_map(&mb, B, N, K, ldb, BN, BK, true))) return 1;
     // split-K when the output has too few tiles to fill the GPU and K is long
     const int tiles_mn = ((N + BN - 1) / BN) * ((M + BM - 1) / BM);
     const int KB_all = (K + BK - 1) / BK;
@@ -554,14 +568,14 @@ int launch(const void* A, int lda, const void* B, int ldb, int M, int N, int K, 
     constexpr size_t smem = (size_t)STAGES * (BM * BK * 2 + BN * BK * 2) + 4 * 2 * 4096 + 1024 + 256;
     static bool configured = false;
     if (!configured) {
-        if (cudaFuncSetAttribute(gemm_tn_kernel<BN, STAGES, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return 2;
+        if (cudaFuncSetAttribute(gemm_tn_kernel<BN, STAGES, MODE, A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return 2;
         configured = true;
     }
     const int tiles = tiles_mn * splits;
     // copier CTAs (all-gather mode) come first in the grid; an SM that ran one takes a GEMM CTA afterwards
     const int grid = (tiles < num_sms() ? tiles : num_sms()) + (MODE == 1 ? ag.n_copy : 0);
     count_launch();
-    gemm_tn_kernel<BN, STAGES, MODE><<<grid, GEMM_THREADS, smem, s>>>(ma, mb, mc, M, N, K, splits, ep, err, ag);
+    gemm_tn_kernel<BN, STAGES, MODE, A_MN, B_MN><<<grid, GEMM_THREADS, smem, s>>>(ma, mb, mc, M, N, K, splits, ep, err, ag);
     if (splits > 1) {
         count_launch();
         gemm_splitk_reduce_kernel<<<(unsigned)(((int64_t)M * N + 255) / 256), 256, 0, s>>>(ws, splits, Mpad, ldw, M, N, ep_in, C, ldc);
@@ -572,16 +586,23 @@ int launch(const void* A, int lda, const void* B, int ldb, int M, int N, int K, 
 }  // namespace
 
 // C = act(alpha * A[M,K] . B[N,K]^T + beta * D + bias + diag*I); A, B bf16 with leading dimensions lda / ldb (elements, multiples of 8).
+// a_t / b_t: the operand is passed transposed, as a [K, M] resp. [K, N] row-major matrix (supported: none, b_t, a_t && b_t).
 // Returns 0 on success.  `err` (device int, zeroed by the caller) becomes non-zero if a pipeline wait timed out.
 int gemm_bf16_tn(const void* A, int lda, const void* B, int ldb, int M, int N, int K, float alpha, float beta, const void* D, int ldd,
                  bool d_bf16, const void* bias, bool bias_bf16, float diag, int act, void* C, int ldc, bool c_bf16, void* C2, int ldc2,
-                 float* splitk_ws, int64_t splitk_ws_floats, int* err, cudaStream_t s) {
+                 float* splitk_ws, int64_t splitk_ws_floats, int* err, cudaStream_t s, bool a_t, bool b_t) {
     if (M <= 0 || N <= 0 || K <= 0) return 0;
     Epilogue ep{alpha, beta, diag, D, ldd, d_bf16 ? 1 : 0, bias, bias_bf16 ? 1 : 0, act, c_bf16 ? 1 : 0, C2, ldc2};
     // the output goes through TMA: its base must be 16-byte aligned and its row pitch a multiple of 16 bytes
     if ((reinterpret_cast<uintptr_t>(C) & 15) != 0 || (ldc * (c_bf16 ? 2 : 4)) % 16 != 0) return 5;
-    if (N > 128) return launch<256, 4>(A, lda, B, ldb, M, N, K, ep, C, ldc, splitk_ws, splitk_ws_floats, err, s);
-    return launch<128, 6>(A, lda, B, ldb, M, N, K, ep, C, ldc, splitk_ws, splitk_ws_floats, err, s);
+    if (a_t && !b_t) return 7;                               // not instantiated (no caller needs A^T . B^T-free form)
+#define SG_GEMM_GO(AT, BT) \
+    { if (N > 128) return launch<256, 4, 0, AT, BT>(A, lda, B, ldb, M, N, K, ep, C, ldc, splitk_ws, splitk_ws_floats, err, s); \
+      return launch<128, 6, 0, AT, BT>(A, lda, B, ldb, M, N, K, ep, C, ldc, splitk_ws, splitk_ws_floats, err, s); }
+    if (a_t) SG_GEMM_GO(true, true)
+    if (b_t) SG_GEMM_GO(false, true)
+    SG_GEMM_GO(false, false)
+#undef SG_GEMM_GO
 }
 
 // C[M, N] = A[M, K] . Wfull[N, K]^T where Wfull is assembled inside the kernel from the row shards of `world` ranks (see AgArgs).

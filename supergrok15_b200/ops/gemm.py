@@ -48,14 +48,16 @@ def check(dev=None) -> None:
 
 def gemm_tn(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None, *, alpha: float = 1.0, beta: float = 0.0,
             d: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None, diag: float = 0.0, act=None,
-            out_dtype=torch.bfloat16, out_t: Optional[torch.Tensor] = None) -> torch.Tensor:
+            out_dtype=torch.bfloat16, out_t: Optional[torch.Tensor] = None, a_t: bool = False, b_t: bool = False) -> torch.Tensor:
+    """``a_t`` / ``b_t``: the operand is passed transposed (``a`` as [K, M], ``b`` as [K, N]) and read in place through an
+    MN-major descriptor; supported combinations: none, ``b_t``, ``a_t and b_t``."""
     C = _build.require()
     if out is None:
-        n = b.shape[0]
+        n = b.shape[1 if b_t else 0]
         q = 8 if out_dtype == torch.bfloat16 else 4          # the output is written by TMA: 16-byte row pitch
         npad = -(-n // q) * q
-        out = torch.empty(a.shape[0], npad, dtype=out_dtype, device=a.device)[:, :n]
-    C.gemm_tn(a, b, out, alpha, beta, d, bias, diag, ACT[act], out_t, _err_flag(a.device), _splitk_ws(a.device))
+        out = torch.empty(a.shape[1 if a_t else 0], npad, dtype=out_dtype, device=a.device)[:, :n]
+    C.gemm_tn(a, b, out, alpha, beta, d, bias, diag, ACT[act], out_t, _err_flag(a.device), _splitk_ws(a.device), a_t, b_t)
     return out
 
 
@@ -87,8 +89,9 @@ class _Linear(torch.autograd.Function):
         x2, weight = ctx.saved_tensors
         dy2 = dy.reshape(-1, dy.shape[-1])
         dyb = _pad8(dy2)
-        dx = gemm_tn(dyb, _pad8(weight.t().contiguous()), out_dtype=x2.dtype).contiguous().view(ctx.xshape)   # dy [M,N] @ W [N,K]
-        dw = gemm_tn(_pad8(dy2.t().contiguous()), _pad8(x2.t().contiguous()), out_dtype=weight.dtype).contiguous()  # dy^T @ x
+        # dgrad and wgrad read W, dy and x where they are (transposed operands through MN-major descriptors): no copies
+        dx = gemm_tn(dyb, _pad8(weight), out_dtype=x2.dtype, b_t=True).contiguous().view(ctx.xshape)          # dy [M,N] @ W [N,K]
+        dw = gemm_tn(dyb, _pad8(x2), out_dtype=weight.dtype, a_t=True, b_t=True).contiguous()                   # dy^T [N,M] @ x [M,K]
         db = dy2.float().sum(0).to(dy.dtype) if ctx.has_bias else None
         return dx, dw, db, None
 

@@ -21,6 +21,20 @@ def test_gemm_tn_matches_fp32_matmul(M, N, K):
     assert torch.allclose(outb.float(), ref, rtol=2e-2, atol=0.5)
 
 
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (256, 512, 192), (200, 136, 72), (520, 264, 384), (72, 1000, 2056), (264, 520, 16384)])
+@pytest.mark.parametrize("a_t", [False, True])
+def test_gemm_transposed_operands_read_in_place(M, N, K, a_t):
+    """b (and a) stored [K, N] ([K, M]) are consumed through MN-major descriptors: same result as the K-major call."""
+    torch.manual_seed(M + N + K)
+    a = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+    b = torch.randn(N, K, device="cuda").to(torch.bfloat16)
+    ref = a.float() @ b.float().t()
+    out = gemm.gemm_tn(a.t().contiguous() if a_t else a, b.t().contiguous(), out_dtype=torch.float32, a_t=a_t, b_t=True)
+    gemm.check()
+    assert out.shape == ref.shape
+    assert torch.allclose(out, ref, rtol=1e-3, atol=1e-3 * (K ** 0.5)), (out - ref).abs().max()
+
+
 def test_gemm_epilogue_and_transposed_output():
     torch.manual_seed(0)
     M, N, K = 200, 200, 136

@@ -12,6 +12,8 @@ void ln_fwd(int dtype, bool rms, const void* x, const void* r, const void* gamma
 int ln_bwd_parts(int64_t rows);
 void ln_bwd(int dtype, bool rms, const void* z, const void* dy, const void* gamma, const float* stats, const void* dz_in, void* dz, float* part,
             void* dgamma, void* dbeta, int64_t rows, int D, cudaStream_t st);
+int col_sum_parts(int64_t rows, int C, int elem_bytes);
+void col_sum(int dtype, const void* x, int64_t ld, int64_t rows, int C, float* part, void* out, cudaStream_t st);
 }
 
 namespace sgb {
@@ -78,12 +80,27 @@ std::vector<Tensor> ln_bwd(const Tensor& z, const Tensor& dy, const Tensor& gamm
                dgamma.data_ptr(), has_beta ? dbeta.data_ptr() : nullptr, rows, D, at::cuda::getCurrentCUDAStream());
     return {dz, dgamma, dbeta};
 }
+
+// column sums of x [rows, C] (innermost stride 1) in x's dtype, accumulated in fp32 in a fixed order: the bias gradient of a Linear layer
+Tensor col_sum(const Tensor& x) {
+    TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.stride(1) == 1, "col_sum needs a CUDA matrix whose innermost stride is 1");
+    TORCH_CHECK(x.scalar_type() == at::kBFloat16 || x.scalar_type() == at::kFloat || x.scalar_type() == at::kHalf, "col_sum: fp32, bf16 or fp16");
+    const int64_t rows = x.size(0);
+    const int C = (int)x.size(1);
+    c10::cuda::CUDAGuard guard(x.device());
+    Tensor out = at::empty({C}, x.options());
+    if (rows == 0 || C == 0) return out.zero_();
+    Tensor part = at::empty({(int64_t)sg::col_sum_parts(rows, C, (int)x.element_size()), C}, x.options().dtype(at::kFloat));
+    sg::col_sum(dtype_code(x), x.data_ptr(), x.stride(0), rows, C, part.data_ptr<float>(), out.data_ptr(), at::cuda::getCurrentCUDAStream());
+    return out;
+}
 }  // namespace
 
 void register_nn(pybind11::module_& m) {
     m.def("attn_small_fwd", &attn_small_fwd);
     m.def("attn_small_bwd", &attn_small_bwd);
     m.def("attn_small_supported", [](int64_t S, int64_t HD) { return sg::attn_small_supported((int)S, (int)HD); });
+    m.def("col_sum", &col_sum);
     m.def("ln_fwd", &ln_fwd, py::arg("x"), py::arg("residual"), py::arg("gamma"), py::arg("beta"), py::arg("eps"), py::arg("rms") = false);
     m.def("ln_bwd", &ln_bwd, py::arg("z"), py::arg("dy"), py::arg("gamma"), py::arg("stats"), py::arg("has_beta"), py::arg("rms") = false,
           py::arg("dz_in") = c10::optional<Tensor>());

@@ -378,15 +378,21 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tn_kernel(const __grid_c
                     }
                     const bool plain = (ep.D == nullptr) && (ep.bias == nullptr) && ep.diag == 0.f && ep.act == 0 && ep.alpha == 1.f;
                     if (!plain) {
+                        // bias of these 32 columns: one load per lane, handed round by shuffles (a load per element made the
+                        // epilogue wait on memory 32 times per chunk)
+                        float bias_l = 0.f;
+                        if (ep.bias && n0 + c + h + lane < N)
+                            bias_l = ep.bias_is_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(ep.bias)[n0 + c + h + lane])
+                                                     : reinterpret_cast<const float*>(ep.bias)[n0 + c + h + lane];
 #pragma unroll
                         for (int j = 0; j < 32; ++j) {
                             const int col = n0 + c + h + j;
                             float v = ep.alpha * __uint_as_float(r[j]);
+                            const float bias_j = __shfl_sync(0xffffffffu, bias_l, j);
                             if (row < M && col < N) {
                                 if (ep.D) v += ep.beta * (ep.d_is_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(ep.D)[(int64_t)row * ep.ldd + col])
                                                                        : reinterpret_cast<const float*>(ep.D)[(int64_t)row * ep.ldd + col]);
-                                if (ep.bias) v += ep.bias_is_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(ep.bias)[col])
-                                                                  : reinterpret_cast<const float*>(ep.bias)[col];
+                                v += bias_j;
                             }
                             if (row == col) v += ep.diag;
                             if (ep.act == 1) v = 0.5f * v * (1.f + erff(v * 0.70710678f));

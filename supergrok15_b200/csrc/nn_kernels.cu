@@ -484,4 +484,103 @@ void ln_bwd(int dtype, bool rms, const void* z, const void* dy, const void* gamm
     else ln_bwd_t<float>(rms, z, dy, gamma, stats, dz_in, dz, part, dgamma, dbeta, rows, D, st);
 }
 
+
+// ---------------------------------------------------------------------------------------------------------------------------
+// Column sums of a row-major [rows, C] matrix: the bias gradient of a Linear layer (db = sum over tokens of dy).  Two stages in
+// a fixed order (no atomics): CTA (bx, by) sums rows [by * rows_per_cta, ...) of a slab of 32 sixteen-byte vectors, eight row
+// lanes per column vector with fp32 accumulators, and writes one partial row; the second kernel adds the partial rows in order.
+namespace {
+template <typename T>
+__global__ void __launch_bounds__(256) col_sum_part_kernel(const T* __restrict__ x, int64_t ld, int64_t rows, int C, int64_t rows_per_cta,
+                                                           bool vec, float* __restrict__ part) {
+    constexpr int VEC = 16 / (int)sizeof(T);
+    __shared__ float sh[8][32 * VEC + 1];
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    const int c0 = (blockIdx.x * 32 + tx) * VEC;
+    const int64_t r0 = (int64_t)blockIdx.y * rows_per_cta;
+    const int64_t r1 = r0 + rows_per_cta < rows ? r0 + rows_per_cta : rows;
+    float acc[VEC];
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) acc[j] = 0.f;
+    if (c0 < C) {
+        if (vec) {
+            int64_t r = r0 + ty;
+            for (; r + 24 < r1; r += 32) {                    // four independent 16-byte loads in flight per thread
+                uint4 v[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) v[u] = *reinterpret_cast<const uint4*>(x + (r + 8 * u) * ld + c0);
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const T* e = reinterpret_cast<const T*>(&v[u]);
+#pragma unroll
+                    for (int j = 0; j < VEC; ++j) acc[j] += Cvt<T>::to(e[j]);
+                }
+            }
+            for (; r < r1; r += 8) {
+                const uint4 v = *reinterpret_cast<const uint4*>(x + r * ld + c0);
+                const T* e = reinterpret_cast<const T*>(&v);
+#pragma unroll
+                for (int j = 0; j < VEC; ++j) acc[j] += Cvt<T>::to(e[j]);
+            }
+        } else {
+            for (int64_t r = r0 + ty; r < r1; r += 8)
+#pragma unroll
+                for (int j = 0; j < VEC; ++j)
+                    if (c0 + j < C) acc[j] += Cvt<T>::to(x[r * ld + c0 + j]);
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) sh[ty][tx * VEC + j] = acc[j];
+    __syncthreads();
+    for (int c = threadIdx.x; c < 32 * VEC; c += 256) {
+        const int col = blockIdx.x * 32 * VEC + c;
+        if (col < C) {
+            float t = 0.f;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) t += sh[k][c];
+            part[(int64_t)blockIdx.y * C + col] = t;
+        }
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) col_sum_final_kernel(const float* __restrict__ part, int parts, int C, T* __restrict__ out) {
+    const int c = blockIdx.x * 256 + threadIdx.x;
+    if (c >= C) return;
+    float t = 0.f;
+    for (int p = 0; p < parts; ++p) t += part[(int64_t)p * C + c];
+    out[c] = Cvt<T>::from(t);
+}
+}  // namespace
+
+// number of partial rows the first stage writes for a [rows, C] input (the caller provides parts * C floats of scratch)
+int col_sum_parts(int64_t rows, int C, int elem_bytes) {
+    const int vecw = 32 * (16 / elem_bytes);
+    const int bx = (C + vecw - 1) / vecw;
+    int64_t parts = (4 * 148 + bx - 1) / bx;
+    const int64_t max_parts = (rows + 63) / 64;
+    if (parts > max_parts) parts = max_parts;
+    return parts < 1 ? 1 : (int)parts;
+}
+
+void col_sum(int dtype, const void* x, int64_t ld, int64_t rows, int C, float* part, void* out, cudaStream_t st) {
+    const int es = dtype == F32 ? 4 : 2;
+    const int parts = col_sum_parts(rows, C, es);
+    const int64_t rpc = (rows + parts - 1) / parts;
+    const int vecw = 32 * (16 / es);
+    const dim3 grid((C + vecw - 1) / vecw, parts);
+    const bool vec = C % (16 / es) == 0 && (ld * es) % 16 == 0 && aligned16(x);
+    count_launch(2);
+    if (dtype == BF16) {
+        col_sum_part_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, ld, rows, C, rpc, vec, part);
+        col_sum_final_kernel<__nv_bfloat16><<<(C + 255) / 256, 256, 0, st>>>(part, parts, C, (__nv_bfloat16*)out);
+    } else if (dtype == F16) {
+        col_sum_part_kernel<__half><<<grid, 256, 0, st>>>((const __half*)x, ld, rows, C, rpc, vec, part);
+        col_sum_final_kernel<__half><<<(C + 255) / 256, 256, 0, st>>>(part, parts, C, (__half*)out);
+    } else {
+        col_sum_part_kernel<float><<<grid, 256, 0, st>>>((const float*)x, ld, rows, C, rpc, vec, part);
+        col_sum_final_kernel<float><<<(C + 255) / 256, 256, 0, st>>>(part, parts, C, (float*)out);
+    }
+}
+
 }  // namespace sg

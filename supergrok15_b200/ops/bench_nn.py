@@ -3,6 +3,7 @@
     python -m supergrok15_b200.ops.bench_nn --what flash            # tcgen05 flash attention fwd / bwd vs F.scaled_dot_product_attention
     python -m supergrok15_b200.ops.bench_nn --what ce               # fused cross-entropy fwd / bwd vs F.cross_entropy
     python -m supergrok15_b200.ops.bench_nn --what norm             # RMSNorm with fused residual vs F.rms_norm(x + r)
+    python -m supergrok15_b200.ops.bench_nn --what linear           # tcgen05 Linear (forward, dgrad, wgrad) vs cuBLAS on the flagship's layer shapes
     ... --small                                                      # one modest shape, few iterations (profiler captures)
 
 Timing: CUDA events on the launching stream after warm-up; every shape's working set exceeds the 126 MB L2 except with --small.
@@ -93,14 +94,54 @@ def bench_norm(small: bool, it: int):
     print(json.dumps({"kernel": "rmsnorm_residual_fwd_bwd", "rows": rows, "D": D, "ms": t_o, "GBps": by / t_o / 1e6, "torch_ms": t_r}), flush=True)
 
 
+def bench_linear(small: bool, it: int):
+    """Forward, dgrad and wgrad GEMMs of a Linear layer on the tcgen05 kernel (dgrad / wgrad read W, dy and x in place through
+    MN-major descriptors) against torch.matmul (cuBLAS), then the whole autograd function against F.linear.  Four sets of
+    operands are used in rotation so that consecutive calls do not find their inputs in L2."""
+    from . import gemm
+    dev = torch.device("cuda:0")
+    T = 8192 if small else 32768
+    for din, dout in ([(512, 1536)] if small else [(512, 1536), (512, 512), (512, 2048), (2048, 512)]):
+        sets = [(torch.randn(T, din, device=dev).to(torch.bfloat16), (torch.randn(dout, din, device=dev) * 0.05).to(torch.bfloat16),
+                 torch.randn(T, dout, device=dev).to(torch.bfloat16)) for _ in range(4)]
+        k = [0]
+
+        def nxt():
+            k[0] = (k[0] + 1) % len(sets)
+            return sets[k[0]]
+
+        def run(fn):
+            return timed(lambda: fn(*nxt()), it)
+        r = {"kernel": "linear_gemms", "tokens": T, "in": din, "out": dout}
+        r["fwd_us"] = 1e3 * run(lambda x, w, dy: gemm.gemm_tn(x, w))
+        r["dgrad_us"] = 1e3 * run(lambda x, w, dy: gemm.gemm_tn(dy, w, b_t=True))
+        r["wgrad_us"] = 1e3 * run(lambda x, w, dy: gemm.gemm_tn(dy, x, a_t=True, b_t=True))
+        r["cublas_fwd_us"] = 1e3 * run(lambda x, w, dy: x @ w.t())
+        r["cublas_dgrad_us"] = 1e3 * run(lambda x, w, dy: dy @ w)
+        r["cublas_wgrad_us"] = 1e3 * run(lambda x, w, dy: dy.t() @ x)
+        bias = torch.zeros(dout, device=dev, dtype=torch.bfloat16, requires_grad=True)
+
+        def auto(lin):
+            def f(x, w, dy):
+                x.requires_grad_(True), w.requires_grad_(True)
+                torch.autograd.grad(lin(x, w, bias), (x, w, bias), dy)
+            return f
+        r["autograd_us"] = 1e3 * run(auto(gemm.linear))
+        r["cublas_autograd_us"] = 1e3 * run(auto(F.linear))
+        gemm.check(dev)
+        fl = 2.0 * T * din * dout
+        r["fwd_tflops"], r["dgrad_tflops"], r["wgrad_tflops"] = (fl / r[k_] / 1e6 for k_ in ("fwd_us", "dgrad_us", "wgrad_us"))
+        print(json.dumps({k_: (round(v, 1) if isinstance(v, float) else v) for k_, v in r.items()}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--what", default="flash", choices=["flash", "ce", "norm", "all"])
+    ap.add_argument("--what", default="flash", choices=["flash", "ce", "norm", "linear", "all"])
     ap.add_argument("--small", action="store_true")
     ap.add_argument("--iters", type=int, default=None)
     a = ap.parse_args()
     it = a.iters or (2 if a.small else 20)
-    for name, fn in (("flash", bench_flash), ("ce", bench_ce), ("norm", bench_norm)):
+    for name, fn in (("flash", bench_flash), ("ce", bench_ce), ("norm", bench_norm), ("linear", bench_linear)):
         if a.what in (name, "all"):
             fn(a.small, it)
 

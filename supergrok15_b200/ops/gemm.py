@@ -92,7 +92,7 @@ class _Linear(torch.autograd.Function):
         # dgrad and wgrad read W, dy and x where they are (transposed operands through MN-major descriptors): no copies
         dx = gemm_tn(dyb, _pad8(weight), out_dtype=x2.dtype, b_t=True).contiguous().view(ctx.xshape)          # dy [M,N] @ W [N,K]
         dw = gemm_tn(dyb, _pad8(x2), out_dtype=weight.dtype, a_t=True, b_t=True).contiguous()                   # dy^T [N,M] @ x [M,K]
-        db = dy2.float().sum(0).to(dy.dtype) if ctx.has_bias else None
+        db = _build.require().col_sum(dyb) if ctx.has_bias else None                 # two-stage fp32 column sum, fixed order
         return dx, dw, db, None
 
 

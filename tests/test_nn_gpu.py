@@ -53,3 +53,19 @@ def test_layer_norm_residual_forward_backward(rows, D, res, bias, dtype):
     assert torch.allclose(w.grad.float(), wf.grad, **wt)
     if bias:
         assert torch.allclose(b.grad.float(), bf.grad, **wt)
+
+
+@pytest.mark.parametrize("rows,C,dtype", [(32768, 1536, torch.bfloat16), (1000, 520, torch.bfloat16), (777, 99, torch.bfloat16),
+                                          (4096, 260, torch.float32), (65, 8, torch.float16), (3, 2050, torch.float32)])
+def test_col_sum_matches_fp32_sum(rows, C, dtype):
+    """Bias gradient of a Linear layer: column sums with fp32 accumulation; strided rows (a padded view) are read in place."""
+    from supergrok15_b200 import _build
+    torch.manual_seed(rows + C)
+    buf = torch.randn(rows, C + 8, device="cuda").to(dtype)
+    for x in (buf[:, :C].contiguous(), buf[:, :C]):
+        out = _build.require().col_sum(x)
+        ref = x.float().sum(0)
+        tol = 1e-4 if dtype == torch.float32 else 1e-2
+        assert out.dtype == dtype and out.shape == (C,)
+        assert torch.allclose(out.float(), ref, rtol=tol, atol=tol * rows ** 0.5), (out.float() - ref).abs().max()
+        assert torch.equal(out, _build.require().col_sum(x))                 # fixed summation order: bitwise reproducible

@@ -29,6 +29,16 @@ void sg2_recycle(int* counts, float* W1, float* b1, float* W2, float* b2, float*
                  uint32_t seed, uint32_t call, int* info, cudaStream_t s);
 }
 
+namespace sg {
+bool routed_experts_supported(int heads, int E, int hidden, int topk);
+int routed_experts_bwd_ctas(int64_t n, int heads);
+int routed_experts_fwd(const float* g, const int* ia, const int* ib, const float* wa, const float* wb, const float* W1, const float* b1,
+                       const float* W2, const float* b2, int64_t n, int heads, int E, int pk, float* total, cudaStream_t s);
+int routed_experts_bwd(const float* g, const int* ia, const int* ib, const float* wa, const float* wb, const float* W1, const float* b1,
+                       const float* W2, const float* b2, const float* dtotal, int64_t n, int heads, int E, int pk, float* dwa, float* dwb,
+                       float* partial, float* dparams, cudaStream_t s);
+}
+
 namespace sgb {
 namespace {
 using at::Tensor;
@@ -155,9 +165,58 @@ void sg2_recycle_b(at::Tensor counts, at::Tensor W1, at::Tensor b1, at::Tensor W
     sg::sg2_recycle(counts.data_ptr<int>(), W1.data_ptr<float>(), b1.data_ptr<float>(), W2.data_ptr<float>(), b2.data_ptr<float>(), ka, kb,
                     (float)threshold, (uint32_t)seed, (uint32_t)call, info.data_ptr<int>(), at::cuda::getCurrentCUDAStream());
 }
+
+// ---- routed expert evaluation of the bilevel tail (csrc/sg2_experts.cu)
+struct XShape { int64_t n; int heads, E, hidden; };
+XShape routed_check(const Tensor& g, const Tensor& ia, const Tensor& ib, const Tensor& wa, const Tensor& wb, const Tensor& W1, const Tensor& b1,
+                    const Tensor& W2, const Tensor& b2) {
+    auto f32 = [](const Tensor& t, const char* nm) { TORCH_CHECK(t.is_cuda() && t.is_contiguous() && t.scalar_type() == at::kFloat, nm, ": contiguous fp32 CUDA tensor"); };
+    auto i32 = [](const Tensor& t, const char* nm) { TORCH_CHECK(t.is_cuda() && t.is_contiguous() && t.scalar_type() == at::kInt, nm, ": contiguous int32 CUDA tensor"); };
+    f32(g, "g"); f32(wa, "wa"); f32(wb, "wb"); f32(W1, "W1"); f32(b1, "b1"); f32(W2, "W2"); f32(b2, "b2"); i32(ia, "ia"); i32(ib, "ib");
+    TORCH_CHECK(g.dim() == 1 && ia.dim() == 3 && ia.size(0) == g.size(0) && ia.size(2) == 4, "ia must be [n, heads, 4]");
+    TORCH_CHECK(ib.sizes() == ia.sizes() && wa.sizes() == ia.sizes() && wb.sizes() == ia.sizes(), "ia, ib, wa, wb must have the same shape");
+    TORCH_CHECK(W1.dim() == 2 && b1.sizes() == W1.sizes() && W2.sizes() == W1.sizes() && b2.dim() == 1 && b2.size(0) == W1.size(0), "expert tables: W1, b1, W2 [E, hidden], b2 [E]");
+    XShape s{g.size(0), (int)ia.size(1), (int)W1.size(0), (int)W1.size(1)};
+    TORCH_CHECK(sg::routed_experts_supported(s.heads, s.E, s.hidden, 4), "routed_experts: unsupported configuration (heads ", s.heads, ", experts ", s.E, ", hidden ", s.hidden, ")");
+    return s;
+}
+
+Tensor routed_experts_fwd(const Tensor& g, const Tensor& ia, const Tensor& ib, const Tensor& wa, const Tensor& wb, const Tensor& W1, const Tensor& b1,
+                          const Tensor& W2, const Tensor& b2, int64_t pk) {
+    const XShape s = routed_check(g, ia, ib, wa, wb, W1, b1, W2, b2);
+    c10::cuda::CUDAGuard guard(g.device());
+    Tensor total = at::empty({s.n}, g.options());
+    const int rc = sg::routed_experts_fwd(g.data_ptr<float>(), ia.data_ptr<int>(), ib.data_ptr<int>(), wa.data_ptr<float>(), wb.data_ptr<float>(),
+                                          W1.data_ptr<float>(), b1.data_ptr<float>(), W2.data_ptr<float>(), b2.data_ptr<float>(), s.n, s.heads, s.E,
+                                          (int)pk, total.data_ptr<float>(), at::cuda::getCurrentCUDAStream());
+    TORCH_CHECK(rc == 0, "routed_experts_fwd launch failed (code ", rc, ")");
+    return total;
+}
+
+// returns (d wa, d wb, d [W1 | b1 | W2 | b2] flat)
+std::vector<Tensor> routed_experts_bwd(const Tensor& g, const Tensor& ia, const Tensor& ib, const Tensor& wa, const Tensor& wb, const Tensor& W1,
+                                       const Tensor& b1, const Tensor& W2, const Tensor& b2, int64_t pk, const Tensor& dtotal) {
+    const XShape s = routed_check(g, ia, ib, wa, wb, W1, b1, W2, b2);
+    TORCH_CHECK(dtotal.is_cuda() && dtotal.is_contiguous() && dtotal.scalar_type() == at::kFloat && dtotal.numel() == s.n, "dtotal: fp32 [n]");
+    c10::cuda::CUDAGuard guard(g.device());
+    const int64_t ng = 3 * (int64_t)s.E * s.hidden + s.E;
+    Tensor dwa = at::empty_like(wa), dwb = at::empty_like(wb);
+    Tensor partial = at::empty({(int64_t)sg::routed_experts_bwd_ctas(s.n, s.heads), ng}, g.options());
+    Tensor dparams = at::empty({ng}, g.options());
+    const int rc = sg::routed_experts_bwd(g.data_ptr<float>(), ia.data_ptr<int>(), ib.data_ptr<int>(), wa.data_ptr<float>(), wb.data_ptr<float>(),
+                                          W1.data_ptr<float>(), b1.data_ptr<float>(), W2.data_ptr<float>(), b2.data_ptr<float>(),
+                                          dtotal.data_ptr<float>(), s.n, s.heads, s.E, (int)pk, dwa.data_ptr<float>(), dwb.data_ptr<float>(),
+                                          partial.data_ptr<float>(), dparams.data_ptr<float>(), at::cuda::getCurrentCUDAStream());
+    TORCH_CHECK(rc == 0, "routed_experts_bwd launch failed (code ", rc, ")");
+    return {dwa, dwb, dparams};
+}
 }  // namespace
 
 void register_sg2(pybind11::module_& m) {
+    m.def("sg2_routed_experts_supported", [](int64_t heads, int64_t E, int64_t hidden, int64_t topk) {
+        return sg::routed_experts_supported((int)heads, (int)E, (int)hidden, (int)topk); });
+    m.def("sg2_routed_experts_fwd", &routed_experts_fwd);
+    m.def("sg2_routed_experts_bwd", &routed_experts_bwd);
     m.def("sg2_prepare", &sg2_prepare);
     m.def("sg2_scan", &sg2_scan);
     m.def("sg2_elem", &sg2_elem, py::arg("params"), py::arg("ms"), py::arg("vs"), py::arg("mus"), py::arg("grus"), py::arg("masters"),

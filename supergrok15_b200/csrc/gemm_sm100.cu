@@ -402,10 +402,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tn_kernel(const __grid_c
                     }
                     if (ep.C2 && row < M) {
                         if (ep.c_is_bf16) { __nv_bfloat16* d2 = reinterpret_cast<__nv_bfloat16*>(ep.C2);
-#pragma unroll 4
+#pragma unroll                                                    // full unroll: r[] must stay in registers (no dynamic index)
                             for (int j = 0; j < 32; ++j) if (n0 + c + h + j < N) d2[(int64_t)(n0 + c + h + j) * ep.ldc2 + row] = __float2bfloat16_rn(__uint_as_float(r[j]));
                         } else { float* d2 = reinterpret_cast<float*>(ep.C2);
-#pragma unroll 4
+#pragma unroll
                             for (int j = 0; j < 32; ++j) if (n0 + c + h + j < N) d2[(int64_t)(n0 + c + h + j) * ep.ldc2 + row] = __uint_as_float(r[j]);
                         }
                     }

@@ -7,6 +7,11 @@ kernels turn that into gradients of A_log, rope_freq, D, out_proj and of the fol
 ``scan_params`` (a few 16x16 matrix products) carries the table gradients to input_proj / in_proj / dt_proj / B_proj / C_proj.
 The result equals autograd of ``Mamba3PEERMetaNet.forward_for_bilevel`` (tested), including the cross-column terms that
 the reference kernel drops.
+
+``routed_experts`` is the expert stage of that tail as one forward and one backward kernel (``csrc/sg2_experts.cu``): the
+16 experts per head selected by the top-4 x top-4 product keys are evaluated on the element's gradient and weighted; the
+backward pass returns the routing-weight gradients per element and the expert-parameter gradients summed over all
+elements in a fixed order.  Without it the stage materialises [n, experts, hidden] tensors in both passes.
 """
 from __future__ import annotations
 
@@ -17,6 +22,37 @@ import torch
 
 from .. import _build
 from . import sg2 as sg2_ops
+
+
+class _RoutedExperts(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, g, ia, ib, wa, wb, W1, b1, W2, b2, pk):
+        C = _build.require()
+        args = [t.contiguous() for t in (g.float(), ia.int(), ib.int(), wa.float(), wb.float(), W1.float(), b1.float(), W2.float(), b2.float())]
+        ctx.save_for_backward(*args)
+        ctx.pk = int(pk)
+        return C.sg2_routed_experts_fwd(*args, ctx.pk)
+
+    @staticmethod
+    def backward(ctx, dtotal):
+        C = _build.require()
+        g, ia, ib, wa, wb, W1, b1, W2, b2 = ctx.saved_tensors
+        dwa, dwb, dp = C.sg2_routed_experts_bwd(g, ia, ib, wa, wb, W1, b1, W2, b2, ctx.pk, dtotal.contiguous().float())
+        E, H = W1.shape
+        return (None, None, None, dwa, dwb, dp[:E * H].view(E, H), dp[E * H:2 * E * H].view(E, H), dp[2 * E * H:3 * E * H].view(E, H),
+                dp[3 * E * H:].view(E), None)
+
+
+def routed_experts_supported(heads: int, experts: int, hidden: int, topk: int) -> bool:
+    return bool(_build.require().sg2_routed_experts_supported(heads, experts, hidden, topk))
+
+
+def routed_experts(g, ia, ib, wa, wb, W1, b1, W2, b2, pk: int) -> torch.Tensor:
+    """total[n] = sum over heads h and key pairs (a, b) of wa[n,h,a] * wb[n,h,b] * expert_{ia[n,h,a]*pk + ib[n,h,b]}(g[n]).
+
+    g [n]; ia, ib int [n, heads, 4]; wa, wb [n, heads, 4]; W1, b1, W2 [experts, 16]; b2 [experts].  Differentiable with
+    respect to wa, wb and the four expert tables (not g, which is data on this path)."""
+    return _RoutedExperts.apply(g, ia, ib, wa, wb, W1, b1, W2, b2, pk)
 
 
 def scan_params(meta_net) -> List[torch.Tensor]:
@@ -93,10 +129,17 @@ class _ScanCtx(torch.autograd.Function):
 
 
 def bilevel_backward_cuda(opt, named, train_grads: Dict[str, torch.Tensor], val_grads: Dict[str, torch.Tensor],
-                          slice_elems: int = 1 << 18) -> int:
-    """Accumulate d(meta_loss)/d(meta-net parameters) into their ``.grad`` with the batched CUDA pipeline."""
+                          slice_elems: int = 0) -> int:
+    """Accumulate d(meta_loss)/d(meta-net parameters) into their ``.grad`` with the batched CUDA pipeline.
+    ``slice_elems``: elements per slice of the element-wise tail (0: 2M with the expert kernel, 256K with the dense PyTorch
+    expert stage, whose [slice, experts, hidden] intermediates bound the slice)."""
+    import os
     C = _build.require()
     mn = opt.meta_net
+    if slice_elems <= 0:
+        kernel = os.environ.get("SG_BILEVEL_EXPERTS", "kernel") != "dense" and \
+            routed_experts_supported(mn.num_peer_heads, mn.num_experts, mn.expert_hidden, 4)
+        slice_elems = (1 << 21) if kernel else (1 << 18)
     sel = []
     for name, p in named:
         if name not in train_grads or name not in val_grads or p.numel() == 0:

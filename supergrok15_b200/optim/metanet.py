@@ -20,6 +20,7 @@ timestep; the literal recurrence) and ``chunked`` (a work-efficient blocked pref
 from __future__ import annotations
 
 import math
+import os
 from typing import Dict, Optional, Tuple
 
 import torch
@@ -299,15 +300,31 @@ class Mamba3PEERMetaNet(nn.Module):
         # total = sum_e (sum_heads R_h[n,e]) * expert_e(g_n).  The routing weights are scattered into a dense [n, E]
         # matrix (whose backward is a gather) and all E experts are evaluated densely; gathering expert weights per
         # element instead would turn the backward into hundreds of millions of atomic adds onto E*hidden addresses.
-        route = torch.zeros(n, self.num_experts, device=g.device, dtype=torch.float32)
+        # On CUDA (g being data, not differentiated) the expert stage is one kernel each way instead; SG_BILEVEL_EXPERTS=dense
+        # keeps the dense PyTorch formulation.
+        use_kernel = False
+        if g.is_cuda and not g.requires_grad and os.environ.get("SG_BILEVEL_EXPERTS", "kernel") != "dense":
+            from ..ops import sg2_bilevel
+            use_kernel = sg2_bilevel.routed_experts_supported(self.num_peer_heads, self.num_experts, self.expert_hidden, topk)
+        route = None if use_kernel else torch.zeros(n, self.num_experts, device=g.device, dtype=torch.float32)
+        ias, ibs, was, wbs = [], [], [], []
         for h in range(self.num_peer_heads):
             q = self.peer_queries[h](peer_in)
             ta, ia = (q[:, :half] @ self.product_keys_A[h].T).topk(topk, dim=-1)
             tb, ib = (q[:, half:] @ self.product_keys_B[h].T).topk(topk, dim=-1)
             wa, wb = torch.softmax(ta * 10.0, -1), torch.softmax(tb * 10.0, -1)
+            if use_kernel:
+                ias.append(ia), ibs.append(ib), was.append(wa), wbs.append(wb)
+                continue
             eidx = (ia.unsqueeze(2) * self.pk_dim + ib.unsqueeze(1)).reshape(n, -1)
             w = (wa.unsqueeze(2) * wb.unsqueeze(1)).reshape(n, -1)
             route = route.scatter_add(1, eidx, w)
+        if use_kernel:
+            # one kernel evaluates the 16 selected experts of every head; its backward sums the expert gradients in a fixed order
+            total = sg2_bilevel.routed_experts(g.reshape(-1), torch.stack(ias, 1), torch.stack(ibs, 1), torch.stack(was, 1),
+                                               torch.stack(wbs, 1), self.expert_W1.squeeze(-1), self.expert_b1, self.expert_W2.squeeze(1),
+                                               self.expert_b2.squeeze(-1), self.pk_dim)
+            return g + self.rescale * total / self.num_peer_heads
         z = torch.relu(g.view(n, 1, 1) * self.expert_W1.squeeze(-1).unsqueeze(0) + self.expert_b1.unsqueeze(0))   # [n,E,H]
         out_all = (z * self.expert_W2.squeeze(1).unsqueeze(0)).sum(-1) + self.expert_b2.squeeze(-1).unsqueeze(0)   # [n,E]
         total = (route * out_all).sum(-1)

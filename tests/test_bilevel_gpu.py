@@ -68,3 +68,67 @@ def test_bilevel_step_runs_on_cuda_and_keeps_persistent_states():
     mo.step()
     assert not torch.equal(w0, opt.meta_net.mamba_fwd.A_log)
     assert all(torch.equal(a, b) for a, b in zip(before, opt._flat_mamba_fwd_states))
+
+
+def _dense_routed(g, ia, ib, wa, wb, W1, b1, W2, b2, pk):
+    """PyTorch statement of the routed expert stage (float64): every selected expert evaluated through gathered tables."""
+    n, heads, _ = ia.shape
+    e = (ia.unsqueeze(3) * pk + ib.unsqueeze(2)).reshape(n, heads * 16).long()                    # [n, heads*16]
+    w = (wa.unsqueeze(3) * wb.unsqueeze(2)).reshape(n, heads * 16)
+    z = torch.relu(g.view(n, 1, 1) * W1[e] + b1[e])                                               # [n, heads*16, hidden]
+    out = (z * W2[e]).sum(-1) + b2[e]
+    return (w * out).sum(-1)
+
+
+@pytest.mark.parametrize("n,heads,E,pk", [(50, 4, 144, 12), (1000, 4, 144, 12), (70001, 4, 144, 12), (333, 2, 64, 8), (257, 8, 100, 10)])
+def test_routed_experts_kernel_matches_dense_formulation(n, heads, E, pk):
+    from supergrok15_b200.ops import sg2_bilevel
+    torch.manual_seed(n + heads)
+    dev = "cuda"
+    g = torch.randn(n, device=dev)
+    ia = torch.rand(n, heads, pk, device=dev).topk(4, dim=-1).indices.int()
+    ib = torch.rand(n, heads, pk, device=dev).topk(4, dim=-1).indices.int()
+    wa = torch.softmax(torch.randn(n, heads, 4, device=dev), -1).requires_grad_(True)
+    wb = torch.softmax(torch.randn(n, heads, 4, device=dev), -1).requires_grad_(True)
+    W1, b1, W2 = (torch.randn(E, 16, device=dev).requires_grad_(True) for _ in range(3))
+    b2 = torch.randn(E, device=dev).requires_grad_(True)
+    dt = torch.randn(n, device=dev)
+    leaves = (wa, wb, W1, b1, W2, b2)
+    total = sg2_bilevel.routed_experts(g, ia, ib, wa, wb, W1, b1, W2, b2, pk)
+    grads = torch.autograd.grad(total, leaves, dt)
+    dl = [t.detach().double().requires_grad_(True) for t in leaves]
+    ref = _dense_routed(g.double(), ia.long(), ib.long(), *dl, pk)
+    rgrads = torch.autograd.grad(ref, dl, dt.double())
+    assert torch.allclose(total.double(), ref, rtol=1e-4, atol=1e-4), (total.double() - ref).abs().max()
+    for name, a, b in zip(("wa", "wb", "W1", "b1", "W2", "b2"), grads, rgrads):
+        scale = b.abs().max().clamp_min(1e-6)
+        assert (a.double() - b).abs().max() / scale < 2e-4, (name, float((a.double() - b).abs().max()), float(scale))
+    again = torch.autograd.grad(sg2_bilevel.routed_experts(g, ia, ib, wa, wb, W1, b1, W2, b2, pk), leaves, dt)
+    for a, b in zip(grads, again):
+        assert torch.equal(a, b)                                                                  # fixed summation order
+
+
+def test_soft_head_expert_kernel_matches_dense_path(monkeypatch):
+    opt, named, tg, vg = _setup([(3000,)])
+    mn = opt.meta_net
+    n = 3000
+    torch.manual_seed(5)
+    g = torch.randn(n, device="cuda") * 1e-2
+    s = torch.rand(n, device="cuda") * 1e-2
+    gru = torch.randn(n, mn.gru_hidden, device="cuda") * 0.1
+    ctx = torch.randn(n, 16, device="cuda") * 0.1
+    vu = torch.randn(n, device="cuda")
+    res = {}
+    for mode in ("kernel", "dense"):
+        monkeypatch.setenv("SG_BILEVEL_EXPERTS", mode)
+        mn.zero_grad(set_to_none=True)
+        c = ctx.clone().requires_grad_(True)
+        smart = mn.soft_head(g, s, gru, c[:, :8], c[:, 8:])
+        (smart * vu).sum().backward()
+        res[mode] = (smart.detach(), c.grad.clone(), {k: p.grad.clone() for k, p in mn.named_parameters() if p.grad is not None})
+    assert torch.allclose(res["kernel"][0], res["dense"][0], rtol=1e-5, atol=1e-7)
+    assert torch.allclose(res["kernel"][1], res["dense"][1], rtol=1e-3, atol=1e-6 + 1e-3 * float(res["dense"][1].abs().max()))
+    assert set(res["kernel"][2]) == set(res["dense"][2])
+    for k, gd in res["dense"][2].items():
+        gk = res["kernel"][2][k]
+        assert (gk - gd).abs().max() <= 1e-3 * gd.abs().max() + 1e-9, (k, float((gk - gd).abs().max()), float(gd.abs().max()))

@@ -63,8 +63,9 @@ def save(engine, path: str) -> None:
     os.makedirs(path, exist_ok=True)
     payload = {"rank": engine.rank, "world": engine.world, "tensors": _per_tensor_state(engine), "steps": engine.steps}
     if engine.flat_mode:
-        n = engine.my_end - engine.my_begin
-        payload["flat"] = {"begin": engine.my_begin, "end": engine.my_end, "master": engine.master[:n].cpu().clone(),
+        # the flat ranges this rank owns (one, or one per bucket when the step overlaps backward) and their state, concatenated
+        n = engine.n_own
+        payload["flat"] = {"segments": [[b, e] for b, e, _ in engine.segments], "master": engine.master[:n].cpu().clone(),
                            "m": engine.m[:n].cpu().clone(), "v": engine.v[:n].cpu().clone() if engine.v is not None else None}
     elif engine.opt is not None:
         sd = engine.opt.state_dict()
@@ -126,8 +127,18 @@ def consolidate(path: str) -> dict:
             flat_parts.append(p["flat"])
     out = {"masters": masters, "state": state, "extra": extra, "manifest": man}
     if flat_parts:
-        flat_parts.sort(key=lambda d: d["begin"])
-        out["flat"] = {k: (torch.cat([d[k] for d in flat_parts]) if flat_parts[0][k] is not None else None) for k in ("master", "m", "v")}
+        # scatter every rank's segments back to their positions of the flat buffer (positions do not depend on the world size)
+        total = int(man["total"])
+        full = {k: (torch.zeros(total) if flat_parts[0][k] is not None else None) for k in ("master", "m", "v")}
+        for d in flat_parts:
+            segs = d["segments"] if "segments" in d else [[d["begin"], d["end"]]]
+            pos = 0
+            for b, e in segs:
+                for k in ("master", "m", "v"):
+                    if full[k] is not None:
+                        full[k][b:e] = d[k][pos:pos + e - b]
+                pos += e - b
+        out["flat"] = full
     return out
 
 
@@ -140,11 +151,14 @@ def load(engine, path: str) -> None:
     with torch.no_grad():
         if engine.flat_mode:
             fl = full["flat"]
-            n = engine.my_end - engine.my_begin
-            engine.master[:n].copy_(fl["master"][engine.my_begin:engine.my_end])
-            engine.m[:n].copy_(fl["m"][engine.my_begin:engine.my_end])
-            if engine.v is not None:
-                engine.v[:n].copy_(fl["v"][engine.my_begin:engine.my_end])
+            if fl["master"].numel() < engine.total:                # a larger world pads the flat buffer further
+                pad = engine.total - fl["master"].numel()
+                fl = {k: (torch.cat([t, torch.zeros(pad)]) if t is not None else None) for k, t in fl.items()}
+            for b, e, so in engine.segments:
+                engine.master[so:so + e - b].copy_(fl["master"][b:e])
+                engine.m[so:so + e - b].copy_(fl["m"][b:e])
+                if engine.v is not None:
+                    engine.v[so:so + e - b].copy_(fl["v"][b:e])
             p0 = torch.load(os.path.join(path, "rank_0.pt"), weights_only=False)
             engine.steps = int(p0.get("steps", 0))
             engine.pbuf.tensor.copy_(fl["master"][: engine.total].to(engine.pdtype))

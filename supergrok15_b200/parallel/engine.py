@@ -18,6 +18,13 @@ scalars (clip norm, Prodigy numerator / denominator, SAM norm) are combined acro
 deterministic slot all-reduce.  ``comm="nccl"`` runs the same sharded step around NCCL all-reduce /
 broadcast and is the baseline the fused path is measured against.
 
+``overlap=True`` (AdamW / Lion) cuts the flat buffer into buckets of consecutive parameters, last parameters first, and
+gives every rank an equal slice of EACH bucket.  A hook on the gradient accumulation of every parameter marks its bucket;
+as soon as a bucket is complete (buckets are issued strictly in order, so that every rank issues the same sequence) a side
+stream waits for that point of the backward stream, runs a barrier over the ranks and the fused reduce-scatter + step +
+all-gather kernel on this rank's slice of the bucket, while backward carries on with the earlier layers on the main stream.
+With ``comm="nccl"`` (and on CPU / gloo) the bucket's all-reduce is started asynchronously at the same point instead.
+
 Waits on peers are bounded on the device (``timeout_s``); ``check()`` raises ``CommTimeout`` when a wait
 ran out, leaving the CUDA context usable.
 """
@@ -50,7 +57,8 @@ class CommTimeout(RuntimeError):
 class ZeroEngine:
     def __init__(self, model: torch.nn.Module, optimizer: str = "supergrok2", opt_kwargs: Optional[dict] = None,
                  comm: Optional[str] = None, param_dtype: torch.dtype = torch.bfloat16, group=None,
-                 timeout_s: float = 20.0, criterion=None, graph: Optional[bool] = None, graph_warmup: int = 3):
+                 timeout_s: float = 20.0, criterion=None, graph: Optional[bool] = None, graph_warmup: int = 3,
+                 overlap: bool = False, bucket_numel: int = 1 << 24):
         self.comm = comm or os.environ.get("GROK_COMM", "p2p")
         assert self.comm in ("p2p", "nvls", "nccl")
         self.rank, self.world = symm.world_info(group)
@@ -73,6 +81,8 @@ class ZeroEngine:
         self.pdtype = param_dtype
         numels = [p.numel() for p in self.params]
         self.flat_mode = optimizer in FLAT_OPTIMIZERS
+        self.overlap = bool(overlap) and self.flat_mode                  # bucket-by-bucket overlap of the sharded step with backward
+        self.buckets: List[dict] = []
         # ---- layout of the flat parameter / gradient buffers
         if self.flat_mode:
             self.owner = [0] * len(numels)
@@ -83,10 +93,24 @@ class ZeroEngine:
             total = -(-pos // (8 * self.world)) * 8 * self.world
             self.offsets, self.total = offs, total
             self.regions = ownership.flat_ranges(total, self.world)
+            if self.overlap:
+                # every rank owns an equal slice of every bucket: its state is the concatenation of those slices
+                so = 0
+                for lo, hi, idx in ownership.reverse_buckets(offs, numels, int(bucket_numel)):
+                    sl = ownership.bucket_slices(lo, hi, self.world)
+                    b, e = sl[self.rank]
+                    self.buckets.append({"lo": lo, "hi": hi, "params": idx, "slices": sl, "mine": (b, e), "state_off": so})
+                    so += e - b
         else:
             self.owner = ownership.assign_tensors(numels, self.world)
             self.offsets, self.regions, self.total = ownership.grouped_layout(numels, self.owner, self.world)
         self.my_begin, self.my_end = self.regions[self.rank]
+        # (begin, end, offset into this rank's state) of every flat range this rank owns: one range, or one per bucket
+        if self.overlap:
+            self.segments = [(bk["mine"][0], bk["mine"][1], bk["state_off"]) for bk in self.buckets if bk["mine"][1] > bk["mine"][0]]
+        else:
+            self.segments = [(self.my_begin, self.my_end, 0)] if self.my_end > self.my_begin else []
+        self.n_own = sum(e - b for b, e, _ in self.segments)
         self.pbuf = symm.alloc(self.total, param_dtype, self.device, group)
         self.gbuf = symm.alloc(self.total, param_dtype, self.device, group)
         with torch.no_grad():
@@ -107,12 +131,22 @@ class ZeroEngine:
             import warnings
             warnings.warn("comm='nvls' requested but no multicast address is available; using plain peer loads / stores")
         # ---- owner state
-        n_own = self.my_end - self.my_begin
-        self.master = self.pbuf.tensor[self.my_begin:self.my_end].float().clone()          # fp32 master shard
+        n_own = self.n_own
+        self.master = (torch.cat([self.pbuf.tensor[b:e].float() for b, e, _ in self.segments]) if self.segments
+                       else torch.zeros(0, dtype=torch.float32, device=self.device))       # fp32 master shard
         self.gred = torch.zeros(max(n_own, 1), dtype=torch.float32, device=self.device)    # reduced fp32 gradient shard
         self._build_optimizer()
         self.steps = 0
         self.launches = 0
+        if self.overlap:
+            import functools
+            self.use_graph = False                    # epochs and bias corrections are host-side arguments of the bucket kernels
+            self._ostream = torch.cuda.Stream(self.device) if self.cuda else None
+            self._armed, self._next = False, 0
+            for k, bk in enumerate(self.buckets):
+                bk["pending"], bk["ready"], bk["handle"] = len(bk["params"]), False, None
+                for i in bk["params"]:
+                    self.params[i].register_post_accumulate_grad_hook(functools.partial(self._on_grad, k))
 
     # ------------------------------------------------------------------ construction
     def _owned(self):
@@ -121,7 +155,7 @@ class ZeroEngine:
     def _build_optimizer(self):
         kw = self.opt_kwargs
         if self.flat_mode:
-            n = self.my_end - self.my_begin
+            n = self.n_own
             self.m = torch.zeros(max(n, 8), dtype=torch.float32, device=self.device)
             self.v = torch.zeros(max(n, 8), dtype=torch.float32, device=self.device) if self.name == "adamw" else None
             self.hp = dict(lr=kw.get("lr", 1e-3 if self.name == "adamw" else 3e-4),
@@ -215,24 +249,111 @@ class ZeroEngine:
     def zero_grad(self):
         self.gbuf.tensor.zero_()
 
+    # ------------------------------------------------------------------ flat optimizers (AdamW / Lion)
+    def _flat_args(self, step_no: int) -> List[float]:
+        b1, b2 = self.hp["betas"]
+        return [self.hp["lr"], b1, b2, self.hp["eps"], self.hp["weight_decay"], 1 - b1 ** step_no, 1 - b2 ** step_no, 1.0 / self.world]
+
+    def _flat_fused_segment(self, b: int, e: int, so: int, f: List[float]):
+        """Fused reduce-scatter + step + all-gather kernel on the owned flat range [b, e), whose state starts at ``so``."""
+        nvls = self.nvls
+        _build.require().dist_fused_flat_step(FLAT_OPTIMIZERS[self.name], _DT[self.pdtype], _DT[self.pdtype], self.gbuf.peer_ptrs,
+                                              self.pbuf.peer_ptrs, self.rank, b, e - b, f, self.master[so:], self.m[so:],
+                                              self.v[so:] if self.v is not None else None, nvls,
+                                              self.gbuf.multicast_ptr if nvls else 0, self.pbuf.multicast_ptr if nvls else 0)
+        self.launches += 1
+
+    def _flat_host_segment(self, b: int, e: int, so: int, step_no: int):
+        """CPU / NCCL path: the gradient range is already summed over the ranks; step on the fp32 master, cast back."""
+        n = e - b
+        g = self.gred[so:so + n].copy_(self.gbuf.tensor[b:e])
+        if self.world > 1:
+            g.mul_(1.0 / self.world)
+        b1, b2 = self.hp["betas"]
+        mp = [self.master[so:so + n]]
+        if self.name == "adamw":
+            ew.adamw(mp, [g], [self.m[so:so + n]], [self.v[so:so + n]], [step_no], self.hp["lr"], b1, b2, self.hp["eps"], self.hp["weight_decay"])
+        else:
+            ew.lion(mp, [g], [self.m[so:so + n]], self.hp["lr"], b1, b2, self.hp["weight_decay"])
+        self.pbuf.tensor[b:e].copy_(self.master[so:so + n])
+
+    # ------------------------------------------------------------------ overlap with backward, bucket by bucket
+    def _arm(self):
+        """Called before the backward pass whose gradients complete the step: from now on finished buckets are issued."""
+        for bk in self.buckets:
+            bk["pending"], bk["ready"], bk["handle"] = len(bk["params"]), False, None
+        self._next, self._armed = 0, True
+
+    def _on_grad(self, k: int, _param):
+        if not self._armed:
+            return
+        bk = self.buckets[k]
+        bk["pending"] -= 1
+        if bk["pending"] == 0:
+            bk["ready"] = True
+            while self._next < len(self.buckets) and self.buckets[self._next]["ready"]:     # strictly in order: same sequence on every rank
+                self._issue_bucket(self._next)
+                self._next += 1
+
+    @torch.no_grad()
+    def _issue_bucket(self, k: int):
+        bk = self.buckets[k]
+        if self.cuda and self.comm != "nccl":
+            ev = torch.cuda.Event()
+            ev.record()                                               # this bucket's gradients are complete at this point of backward
+            with torch.cuda.stream(self._ostream):
+                self._ostream.wait_event(ev)
+                self._barrier(10)                                     # ... on every rank
+                b, e = bk["mine"]
+                if e > b:
+                    self._flat_fused_segment(b, e, bk["state_off"], self._flat_args(self.steps + 1))
+        elif self.world > 1:
+            import torch.distributed as dist
+            bk["handle"] = dist.all_reduce(self.gbuf.tensor[bk["lo"]:bk["hi"]], group=self.group, async_op=True)
+
+    @torch.no_grad()
+    def _finish_overlapped_step(self):
+        while self._next < len(self.buckets):                         # buckets that no hook completed (unused parameters, manual backward)
+            self._issue_bucket(self._next)
+            self._next += 1
+        self._armed = False
+        self.steps += 1
+        if self.cuda and self.comm != "nccl":
+            ev = torch.cuda.Event()
+            ev.record(self._ostream)
+            torch.cuda.current_stream(self.device).wait_event(ev)
+        else:
+            import torch.distributed as dist
+            for bk in self.buckets:
+                if bk["handle"] is not None:
+                    bk["handle"].wait()
+                    bk["handle"] = None
+                b, e = bk["mine"]
+                if e > b:
+                    self._flat_host_segment(b, e, bk["state_off"], self.steps)
+            if self.world > 1:
+                for bk in self.buckets:
+                    for rr, (b, e) in enumerate(bk["slices"]):
+                        if e > b:
+                            dist.broadcast(self.pbuf.tensor[b:e], src=rr, group=self.group)
+        self._barrier(2)                                              # every rank's parameters are complete
+
     @torch.no_grad()
     def step(self, **metrics):
         W, r = self.world, self.rank
         C = _build.require() if self.cuda else None
-        n_own = self.my_end - self.my_begin
+        n_own = self.n_own
         fused = self.cuda and self.comm != "nccl"
+        if self.overlap:
+            if not self._armed:                                       # step() after a backward that train_step did not drive
+                self._arm()
+            return self._finish_overlapped_step()
         self._barrier(1)                                              # every rank's backward has written its gradients
         if self.flat_mode and fused:
             self.steps += 1
-            b1, b2 = self.hp["betas"]
-            f = [self.hp["lr"], b1, b2, self.hp["eps"], self.hp["weight_decay"], 1 - b1 ** self.steps, 1 - b2 ** self.steps,
-                 1.0 / W]
-            if n_own:
-                nvls = self.nvls
-                C.dist_fused_flat_step(FLAT_OPTIMIZERS[self.name], _DT[self.pdtype], _DT[self.pdtype], self.gbuf.peer_ptrs,
-                                       self.pbuf.peer_ptrs, r, self.my_begin, n_own, f, self.master, self.m, self.v, nvls,
-                                       self.gbuf.multicast_ptr if nvls else 0, self.pbuf.multicast_ptr if nvls else 0)
-                self.launches += 1
+            f = self._flat_args(self.steps)
+            for b, e, so in self.segments:
+                self._flat_fused_segment(b, e, so, f)
             self._barrier(2)
             return
         # ---- reduce-scatter
@@ -252,14 +373,8 @@ class ZeroEngine:
         # ---- sharded optimizer step
         if self.flat_mode:                                            # CPU / NCCL path of AdamW / Lion on the flat shard
             self.steps += 1
-            b1, b2 = self.hp["betas"]
-            mp = [self.master[:n_own]]
-            if self.name == "adamw":
-                ew.adamw(mp, [self.gred[:n_own]], [self.m[:n_own]], [self.v[:n_own]], [self.steps], self.hp["lr"], b1, b2,
-                         self.hp["eps"], self.hp["weight_decay"])
-            else:
-                ew.lion(mp, [self.gred[:n_own]], [self.m[:n_own]], self.hp["lr"], b1, b2, self.hp["weight_decay"])
-            self.pbuf.tensor[self.my_begin:self.my_end].copy_(self.master[:n_own])
+            for b, e, so in self.segments:
+                self._flat_host_segment(b, e, so, self.steps)
         elif self.name == "supergrok2":
             if self.own_idx:
                 self.opt.step(**metrics)
@@ -310,7 +425,10 @@ class ZeroEngine:
         """Zero the flat gradient buffer, then forward + loss + backward of every micro-batch (gradients accumulate in the buffer)."""
         self.zero_grad()
         total = None
-        for xb, yb in zip(x.chunk(micro_batches), y.chunk(micro_batches)):
+        chunks = list(zip(x.chunk(micro_batches), y.chunk(micro_batches)))
+        for k, (xb, yb) in enumerate(chunks):
+            if self.overlap and k == len(chunks) - 1:
+                self._arm()                                           # the gradients of this backward pass complete the step
             logits = self.model(xb)
             if logits.dim() == 3:                                     # language modelling: one target per position
                 logits, yb = logits.reshape(-1, logits.shape[-1]), yb.reshape(-1)
@@ -386,5 +504,5 @@ class ZeroEngine:
     def nvlink_bytes_per_step(self) -> Dict[str, int]:
         """Bytes this rank moves over NVLink per step on the fused path: pull ingress, push egress."""
         es = torch.tensor([], dtype=self.pdtype).element_size()
-        n_own = self.my_end - self.my_begin
+        n_own = self.n_own
         return {"rs_ingress": (self.world - 1) * n_own * es, "ag_egress": (self.world - 1) * n_own * es}

@@ -52,3 +52,27 @@ def grouped_layout(numels: Sequence[int], owner: Sequence[int], world: int, alig
                 pos += -(-int(n) // align) * align
         regions.append((begin, pos))
     return offsets, regions, pos
+
+
+def reverse_buckets(offsets: Sequence[int], numels: Sequence[int], bucket_numel: int, align: int = 8):
+    """Buckets of consecutive parameters for overlapping the sharded step with backward: [(lo, hi, [tensor indices])].
+
+    Backward produces the gradients of the last parameters first, so bucket 0 holds the LAST parameters of the flat buffer.
+    A bucket is closed once it holds at least ``bucket_numel`` elements; [lo, hi) is its range of the flat buffer (``offsets``
+    are the aligned flat offsets of the tensors, in parameter order)."""
+    out, cur, hi = [], [], None
+    for i in range(len(numels) - 1, -1, -1):
+        end = int(offsets[i]) + -(-int(numels[i]) // align) * align
+        if hi is None:
+            hi = end
+        cur.append(i)
+        if hi - int(offsets[i]) >= bucket_numel or i == 0:
+            out.append((int(offsets[i]), hi, cur))
+            cur, hi = [], None
+    return out
+
+
+def bucket_slices(lo: int, hi: int, world: int, align: int = 8) -> List[Tuple[int, int]]:
+    """Every rank's [begin, end) of the flat range [lo, hi): equal slices of a multiple of ``align`` elements (the last may be short or empty)."""
+    per = -(-(hi - lo) // (world * align)) * align
+    return [(min(lo + r * per, hi), min(lo + (r + 1) * per, hi)) for r in range(world)]

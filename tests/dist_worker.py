@@ -29,12 +29,16 @@ def run(rank, world, port, optimizer, out_path, device, comm, steps, dtype):
         dev = torch.device("cpu")
     from supergrok15_b200.parallel import ZeroEngine
     m, x, y = make_problem()
-    eng = ZeroEngine(m.to(dev), optimizer, OPT_KW.get(optimizer, {}), comm=comm, param_dtype=dtype, timeout_s=10.0)
+    # "adamw+overlap": the sharded step is issued bucket by bucket from gradient hooks (several buckets on this small model);
+    # "adamw+overlap2": the same with two micro-batches (only the last backward pass issues buckets)
+    optimizer, _, flag = optimizer.partition("+")
+    eng = ZeroEngine(m.to(dev), optimizer, OPT_KW.get(optimizer, {}), comm=comm, param_dtype=dtype, timeout_s=10.0,
+                     overlap=flag.startswith("overlap"), bucket_numel=3000)
     per = x.shape[0] // world
     xs, ys = x[rank * per:(rank + 1) * per].to(dev), y[rank * per:(rank + 1) * per].to(dev)
     losses = []
     for _ in range(steps):
-        losses.append(float(eng.train_step(xs, ys)))
+        losses.append(float(eng.train_step(xs, ys, micro_batches=2 if flag == "overlap2" else 1)))
     if dev.type == "cuda":
         eng.check()
     flat = torch.cat([p.detach().float().reshape(-1).cpu() for p in eng.params])
@@ -47,7 +51,7 @@ def run(rank, world, port, optimizer, out_path, device, comm, steps, dtype):
     else:
         dist.gather(flat, gathered, dst=0)
     if rank == 0:
-        torch.save({"params": gathered, "losses": losses, "owner": eng.owner}, out_path)
+        torch.save({"params": gathered, "losses": losses, "owner": eng.owner, "buckets": len(eng.buckets)}, out_path)
     dist.barrier()
     dist.destroy_process_group()
 

@@ -40,6 +40,32 @@ def test_checkpoint_round_trip_world1(opt, tmp_path):
     assert full["manifest"]["world"] == 1 and (opt in ("adamw",) or all(m is not None for m in full["masters"]))
 
 
+def test_flat_checkpoint_moves_between_bucketed_and_plain_layouts(tmp_path):
+    """AdamW state saved by an engine whose step overlaps backward (one owned range per bucket) loads into a plain engine and back."""
+    def eng(overlap):
+        m, x, y = dist_worker.make_problem()
+        return ZeroEngine(m, "adamw", dist_worker.OPT_KW["adamw"], param_dtype=torch.float32, overlap=overlap, bucket_numel=3000), x, y
+    e1, x, y = eng(True)
+    assert len(e1.buckets) >= 3 and len(e1.segments) == len(e1.buckets)
+    for _ in range(2):
+        e1.train_step(x, y)
+    checkpoint.save(e1, str(tmp_path / "a"))
+    assert checkpoint.verify(str(tmp_path / "a")) == []
+    e2, _, _ = eng(False)
+    checkpoint.load(e2, str(tmp_path / "a"))
+    e1.train_step(x, y)
+    e2.train_step(x, y)
+    for p, q in zip(e1.params, e2.params):
+        assert torch.equal(p, q)
+    checkpoint.save(e2, str(tmp_path / "b"))
+    e3, _, _ = eng(True)
+    checkpoint.load(e3, str(tmp_path / "b"))
+    e2.train_step(x, y)
+    e3.train_step(x, y)
+    for p, q in zip(e2.params, e3.params):
+        assert torch.equal(p, q)
+
+
 def _free_port():
     s = socket.socket(); s.bind(("127.0.0.1", 0)); p = s.getsockname()[1]; s.close(); return p
 

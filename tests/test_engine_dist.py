@@ -69,6 +69,38 @@ def test_sharded_equals_unsharded_cpu_gloo(optimizer):
     assert len(set(res["owner"])) == (1 if optimizer in ("adamw", "lion") else 2)
 
 
+@pytest.mark.dist
+@pytest.mark.parametrize("optimizer", ["adamw+overlap", "lion+overlap", "adamw+overlap2"])
+def test_bucketed_overlap_equals_unsharded_cpu_gloo(optimizer):
+    """The step issued bucket by bucket from gradient hooks (asynchronous all-reduce per bucket on this path) gives the
+    parameters of the plain optimizer on the full batch."""
+    steps = 3
+    res = _launch(2, optimizer, "cpu", "nccl", steps)
+    ref = dist_worker.reference_run(optimizer.partition("+")[0], steps)
+    assert res["buckets"] >= 3
+    for got in res["params"]:
+        assert torch.allclose(got, ref, rtol=2e-4, atol=2e-6), (got - ref).abs().max()
+    assert torch.equal(res["params"][0], res["params"][1])
+
+
+def test_bucket_layout_covers_the_flat_buffer():
+    from supergrok15_b200.parallel.ownership import bucket_slices, reverse_buckets
+    numels = [12672, 512, 49152, 384, 16384, 128, 128, 128, 65536, 512, 65536, 128, 128, 128, 128, 128, 12672, 99]
+    offs, pos = [], 0
+    for n in numels:
+        offs.append(pos)
+        pos += -(-n // 8) * 8
+    bks = reverse_buckets(offs, numels, 60000)
+    assert bks[0][1] == pos and bks[-1][0] == 0 and bks[0][2][0] == len(numels) - 1
+    assert all(a[0] == b[1] for a, b in zip(bks[:-1], bks[1:]))                       # contiguous, last parameters first
+    assert sorted(i for _, _, ix in bks for i in ix) == list(range(len(numels)))
+    assert all(hi - lo >= 60000 for lo, hi, _ in bks[:-1])
+    for lo, hi, _ in bks:
+        sl = bucket_slices(lo, hi, 8)
+        assert sl[0][0] == lo and sl[-1][1] == hi and all(a[1] == b[0] for a, b in zip(sl[:-1], sl[1:]))
+        assert all(b % 8 == 0 and e % 8 == 0 for b, e in sl)
+
+
 @pytest.mark.gpu
 @pytest.mark.dist
 @pytest.mark.parametrize("comm", ["p2p", "nccl", "nvls"])
@@ -82,3 +114,19 @@ def test_sharded_equals_unsharded_gpu(optimizer, comm):
     for got in res["params"]:
         assert torch.allclose(got, ref, rtol=5e-4, atol=5e-6), (got - ref).abs().max()
     assert torch.equal(res["params"][0], res["params"][1])
+
+
+@pytest.mark.gpu
+@pytest.mark.dist
+@pytest.mark.skipif(os.environ.get("SG_TEST_OVERLAP_GPU") != "1",
+                    reason="bucketed overlap on GPUs (side stream + per-bucket barrier and fused kernel) is opt-in: set SG_TEST_OVERLAP_GPU=1")
+@pytest.mark.parametrize("comm", ["p2p", "nccl"])
+@pytest.mark.parametrize("optimizer", ["adamw+overlap", "adamw+overlap2"])
+def test_bucketed_overlap_equals_unsharded_gpu(optimizer, comm):
+    world = min(torch.cuda.device_count(), 2)
+    steps = 3
+    res = _launch(world, optimizer, "cuda", comm, steps)
+    ref = dist_worker.reference_run("adamw", steps, device="cuda")
+    for got in res["params"]:
+        assert torch.allclose(got, ref, rtol=5e-4, atol=5e-6), (got - ref).abs().max()
+    assert all(torch.equal(res["params"][0], p) for p in res["params"])

@@ -75,33 +75,42 @@ def batches(tx, ty, n_steps, per_rank, rank, seed):
 
 
 class ClockSampler:
-    """Samples SM clock / throttle reasons with nvidia-smi while the timed region runs (rank 0 only)."""
+    """Samples SM clock / throttle reasons with nvidia-smi (rank 0 only).  The query loop is started before the warm-up steps so
+    that it is in steady state when the timed region begins; only samples that arrived between ``mark_begin()`` and ``stop()``
+    (the device-timed loop and the end-to-end loop) are reported."""
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, gpu_index=0):
-        self.proc, self.lines, self.gpu = None, [], gpu_index
+    def __init__(self, gpu_index=0, period_ms=100):
+        self.proc, self.lines, self.gpu, self.period_ms, self.t0 = None, [], gpu_index, period_ms, None
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200",
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", str(self.period_ms),
                                           "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except Exception:  # noqa: BLE001
             self.proc = None
 
+    def mark_begin(self):
+        self.t0 = time.monotonic()
+
     def _read(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.monotonic(), line.strip()))
 
     def stop(self):
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.25)
+        t1 = time.monotonic()
+        time.sleep(0.25)                                   # a query that started under load may still be printing
         self.proc.terminate()
+        t0 = self.t0 if self.t0 is not None else 0.0
         sm, mx, reasons = [], [], set()
-        for l in self.lines:
-            f = [t.strip() for t in l.split(",")]
+        for t, l in self.lines:
+            if t < t0 or t > t1 + 0.25:
+                continue
+            f = [x.strip() for x in l.split(",")]
             if len(f) < 9:
                 continue
             try:
@@ -113,7 +122,7 @@ class ClockSampler:
                     reasons.add(name)
         sm.sort()
         return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons),
-                "samples": len(sm)}
+                "samples": len(sm), "window_s": round(t1 - t0, 3)}
 
 
 def timed_loop(step_fn, K, world):
@@ -174,14 +183,15 @@ def run_ours(args, rank, world, local):
     # its first calls of a batch shape eagerly, then captures), so that neither falls into the warm-up or the timed region
     for i in range(eng.graph_warmup + 2):
         eng.train_step(*dev_batches[i % len(dev_batches)])
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()                                  # query loop up and running before the warm-up ends
     for i in range(W):
         eng.train_step(*dev_batches[i])
     eng.check()
     C = _build.require()
     l0 = C.launch_count()
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
+    sampler.mark_begin()
     ms = timed_loop(lambda i: eng.train_step(*dev_batches[W + i]), K, world)
     launches_region = C.launch_count() - l0          # kernels of this package enqueued inside the timed region
     losses = []
@@ -236,13 +246,14 @@ def run_llama_muon(args, rank, world, local):
     def step(i):
         ids = host[i][0].to(dev, non_blocking=True)
         return eng.train_step(ids[:, :-1].contiguous(), ids[:, 1:].contiguous(), micro_batches=micro)
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
     for i in range(W):
         step(i)
     eng.check()
     l0 = C.launch_count()
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
+    sampler.mark_begin()
     losses = []
     ms = timed_loop(lambda i: losses.append(step(W + i)), K, world)
     clocks = sampler.stop() if rank == 0 else None
@@ -315,11 +326,12 @@ def run_reference(args, rank, world, local):
         opt.step()
         return loss.detach()
 
-    for i in range(W):
-        train_step(*dev_batches[i])
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
+    for i in range(W):
+        train_step(*dev_batches[i])
+    sampler.mark_begin()
     ms = timed_loop(lambda i: train_step(*dev_batches[W + i]), K, world)
     losses = []
     e2e_ms = wall_loop(lambda i: losses.append(float(train_step(*host[W + K + i]).item())), K, world)

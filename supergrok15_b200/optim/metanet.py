@@ -294,7 +294,6 @@ class Mamba3PEERMetaNet(nn.Module):
         gs = torch.stack([g, s], dim=-1)
         new_gru = self.gru(torch.cat([gs, fwd_ctx, bwd_ctx], dim=-1), gru_state.float())
         peer_in = torch.cat([new_gru, fwd_ctx, bwd_ctx, gs], dim=-1)
-        half = self.d_model // 2
         n = g.numel()
         # Every head evaluates the SAME experts on the SAME scalar g, so the heads only differ in their routing weights:
         # total = sum_e (sum_heads R_h[n,e]) * expert_e(g_n).  The routing weights are scattered into a dense [n, E]
@@ -306,25 +305,24 @@ class Mamba3PEERMetaNet(nn.Module):
         if g.is_cuda and not g.requires_grad and os.environ.get("SG_BILEVEL_EXPERTS", "kernel") != "dense":
             from ..ops import sg2_bilevel
             use_kernel = sg2_bilevel.routed_experts_supported(self.num_peer_heads, self.num_experts, self.expert_hidden, topk)
-        route = None if use_kernel else torch.zeros(n, self.num_experts, device=g.device, dtype=torch.float32)
-        ias, ibs, was, wbs = [], [], [], []
-        for h in range(self.num_peer_heads):
-            q = self.peer_queries[h](peer_in)
-            ta, ia = (q[:, :half] @ self.product_keys_A[h].T).topk(topk, dim=-1)
-            tb, ib = (q[:, half:] @ self.product_keys_B[h].T).topk(topk, dim=-1)
-            wa, wb = torch.softmax(ta * 10.0, -1), torch.softmax(tb * 10.0, -1)
-            if use_kernel:
-                ias.append(ia), ibs.append(ib), was.append(wa), wbs.append(wb)
-                continue
-            eidx = (ia.unsqueeze(2) * self.pk_dim + ib.unsqueeze(1)).reshape(n, -1)
-            w = (wa.unsqueeze(2) * wb.unsqueeze(1)).reshape(n, -1)
-            route = route.scatter_add(1, eidx, w)
+        # All heads at once: one matrix product for the queries, one against a block-diagonal key matrix for the 2 * heads
+        # score vectors, ONE top-k and ONE softmax over [n, heads, 2, pk] (instead of 2 * heads of each).
+        H, pk = self.num_peer_heads, self.pk_dim
+        Wq = torch.cat([lin.weight for lin in self.peer_queries], 0)                                # [H * d_model, peer_in]
+        q = peer_in @ Wq.T                                                                          # [n, H * d_model]
+        keys = torch.block_diag(*[blk for h in range(H) for blk in (self.product_keys_A[h].T, self.product_keys_B[h].T)])
+        scores = (q @ keys).view(n, H, 2, pk)                                                       # [..., 0, :] sub-key A, [..., 1, :] sub-key B
+        top, idx = scores.topk(topk, dim=-1)
+        w = torch.softmax(top * 10.0, -1)
+        ia, ib, wa, wb = idx[:, :, 0], idx[:, :, 1], w[:, :, 0], w[:, :, 1]                          # [n, H, topk] each
         if use_kernel:
             # one kernel evaluates the 16 selected experts of every head; its backward sums the expert gradients in a fixed order
-            total = sg2_bilevel.routed_experts(g.reshape(-1), torch.stack(ias, 1), torch.stack(ibs, 1), torch.stack(was, 1),
-                                               torch.stack(wbs, 1), self.expert_W1.squeeze(-1), self.expert_b1, self.expert_W2.squeeze(1),
-                                               self.expert_b2.squeeze(-1), self.pk_dim)
+            total = sg2_bilevel.routed_experts(g.reshape(-1), ia, ib, wa, wb, self.expert_W1.squeeze(-1), self.expert_b1,
+                                               self.expert_W2.squeeze(1), self.expert_b2.squeeze(-1), pk)
             return g + self.rescale * total / self.num_peer_heads
+        eidx = (ia.unsqueeze(3) * pk + ib.unsqueeze(2)).reshape(n, -1)                               # [n, H * topk * topk]
+        wr = (wa.unsqueeze(3) * wb.unsqueeze(2)).reshape(n, -1)
+        route = torch.zeros(n, self.num_experts, device=g.device, dtype=wr.dtype).scatter_add(1, eidx, wr)
         z = torch.relu(g.view(n, 1, 1) * self.expert_W1.squeeze(-1).unsqueeze(0) + self.expert_b1.unsqueeze(0))   # [n,E,H]
         out_all = (z * self.expert_W2.squeeze(1).unsqueeze(0)).sum(-1) + self.expert_b2.squeeze(-1).unsqueeze(0)   # [n,E]
         total = (route * out_all).sum(-1)

@@ -312,3 +312,51 @@ def test_cpp_cpu_kernels_match_pytorch_oracle(name):
     for a, b in zip(*results):
         torch.testing.assert_close(a, b, rtol=2e-5, atol=2e-6)
     assert any(not torch.equal(a, p0) for a, p0 in zip(results[1], make_params(shapes, seed=3)))     # something moved
+
+
+def test_soft_head_batched_routing_matches_per_head_statement():
+    """soft_head routes all heads with one query product, one block-diagonal key product, one top-k and one softmax; the plain
+    statement below does it head by head with gathered expert tables (as forward_for_bilevel does)."""
+    from supergrok15_b200.optim.metanet import Mamba3PEERMetaNet
+    torch.manual_seed(3)
+    mn = Mamba3PEERMetaNet().double()
+    with torch.no_grad():
+        mn.expert_W1.mul_(30); mn.expert_W2.mul_(30); mn.expert_b1.normal_(0, 0.1); mn.expert_b2.normal_(0, 0.1)
+        for k in list(mn.product_keys_A) + list(mn.product_keys_B):
+            k.mul_(10)
+    n = 500
+    g = torch.randn(n, dtype=torch.float64) * 1e-2
+    s = torch.rand(n, dtype=torch.float64) * 1e-2
+    gru = (torch.randn(n, mn.gru_hidden) * 0.1).double()                 # soft_head reads the GRU state through fp32
+    ctx = (torch.randn(n, 16, dtype=torch.float64) * 0.1).requires_grad_(True)
+    vu = torch.randn(n, dtype=torch.float64)
+
+    def per_head(c):
+        gs = torch.stack([g, s], -1)
+        new_gru = mn.gru(torch.cat([gs, c[:, :8], c[:, 8:]], -1), gru)
+        pin = torch.cat([new_gru, c[:, :8], c[:, 8:], gs], -1)
+        half, total = mn.d_model // 2, 0.0
+        for h in range(mn.num_peer_heads):
+            q = mn.peer_queries[h](pin)
+            ta, ia = (q[:, :half] @ mn.product_keys_A[h].T).topk(4, dim=-1)
+            tb, ib = (q[:, half:] @ mn.product_keys_B[h].T).topk(4, dim=-1)
+            wa, wb = torch.softmax(ta * 10.0, -1), torch.softmax(tb * 10.0, -1)
+            e = (ia.unsqueeze(2) * mn.pk_dim + ib.unsqueeze(1)).reshape(n, -1)
+            w = (wa.unsqueeze(2) * wb.unsqueeze(1)).reshape(n, -1)
+            z = torch.relu(g.view(n, 1, 1) * mn.expert_W1.squeeze(-1)[e] + mn.expert_b1[e])
+            total = total + (w * ((z * mn.expert_W2.squeeze(1)[e]).sum(-1) + mn.expert_b2.squeeze(-1)[e])).sum(-1)
+        return g + mn.rescale * total / mn.num_peer_heads
+
+    names = [k for k, _ in mn.named_parameters()]
+    out = {}
+    for tag, fn in (("batched", lambda c: mn.soft_head(g, s, gru, c[:, :8], c[:, 8:])), ("per_head", per_head)):
+        mn.zero_grad(set_to_none=True)
+        ctx.grad = None
+        y = fn(ctx)
+        (y * vu).sum().backward()
+        out[tag] = (y.detach(), ctx.grad.clone(), {k: p.grad.clone() for k, p in mn.named_parameters() if p.grad is not None})
+    assert torch.allclose(out["batched"][0], out["per_head"][0], rtol=1e-10, atol=1e-12)
+    assert torch.allclose(out["batched"][1], out["per_head"][1], rtol=1e-8, atol=1e-12)
+    assert set(out["batched"][2]) == set(out["per_head"][2]) and len(out["batched"][2]) > 10
+    for k in out["per_head"][2]:
+        assert torch.allclose(out["batched"][2][k], out["per_head"][2][k], rtol=1e-8, atol=1e-12), k

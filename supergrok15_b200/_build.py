@@ -119,12 +119,49 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     return so
 
 
+def build_sanitized(out_dir) -> Path:
+    """Host-code check build: every ``csrc/*.cpp`` compiled with ``-Wall -Werror -fsanitize=address,undefined`` and linked with
+    the regular CUDA objects into ``out_dir``.  Load it by setting ``SG_EXT_SO`` to the returned path in a process started with
+    ``LD_PRELOAD=$(gcc -print-file-name=libasan.so)`` (the CPU kernels and the binding layer then run under ASan / UBSan)."""
+    import torch
+    from torch.utils import cpp_extension as ce
+    build()                                                           # the CUDA objects come from the regular build
+    out_dir = Path(out_dir)
+    out_dir.mkdir(parents=True, exist_ok=True)
+    cuda_home = str(Path(_nvcc()).parent.parent)
+    inc = [f"-I{_CSRC}", "-isystem", f"{cuda_home}/include"]
+    for p in list(ce.include_paths()) + [sysconfig.get_paths()["include"]]:
+        inc += ["-isystem", p]                                        # third-party headers are not held to -Werror
+    jobs, objs = [], []
+    for src in _sources():
+        if src.suffix == ".cu":
+            objs.append(_OBJ / (src.name + ".o"))
+            continue
+        obj = out_dir / (src.name + ".san.o")
+        objs.append(obj)
+        jobs.append(["g++", "-O1", "-g", "-std=c++17", "-fPIC", "-fsanitize=address,undefined", "-fno-omit-frame-pointer", "-Wall", "-Werror",
+                     "-DTORCH_EXTENSION_NAME=" + _NAME, "-DTORCH_API_INCLUDE_EXTENSION_H",
+                     "-D_GLIBCXX_USE_CXX11_ABI=" + str(int(torch._C._GLIBCXX_USE_CXX11_ABI)), *inc, "-c", str(src), "-o", str(obj)])
+    with ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:
+        list(ex.map(_run, jobs))
+    so = out_dir / _so_path().name
+    tlib = Path(torch.__file__).parent / "lib"
+    _run(["g++", "-shared", "-fsanitize=address,undefined", "-o", str(so), *map(str, objs), f"-L{tlib}", f"-L{cuda_home}/lib64", "-lc10",
+          "-ltorch_cpu", "-ltorch", "-ltorch_python", "-lc10_cuda", "-ltorch_cuda", "-lcudart", f"-Wl,-rpath,{tlib}",
+          f"-Wl,-rpath,{cuda_home}/lib64"])
+    return so
+
+
 def load(build_if_needed: bool = True):
-    """Return the extension module, or None (with the reason in ``load_error()``)."""
+    """Return the extension module, or None (with the reason in ``load_error()``).  ``SG_EXT_SO`` names a shared object to load
+    instead of the in-tree one (the sanitizer build of ``build_sanitized``)."""
     global _mod, _err
     if _mod is not None:
         return _mod
     so = _so_path()
+    override = os.environ.get("SG_EXT_SO")
+    if override:
+        so, build_if_needed = Path(override), False
     try:
         if build_if_needed and _nvcc() is not None and os.environ.get("SG_NO_BUILD") != "1":
             build()

@@ -23,6 +23,9 @@ _ws: Dict[torch.device, Dict[str, torch.Tensor]] = {}
 
 
 CPU_NATIVE = os.environ.get("SG_CPU_NATIVE", "1") != "0"
+# GROK_DEBUG=1: every scratch buffer handed out is filled with NaN first, so a kernel that reads scratch it has not written
+# (a stale value from an earlier call would otherwise look plausible) shows up as a non-finite result
+DEBUG_POISON = os.environ.get("GROK_DEBUG", "0") not in ("", "0")
 
 
 def _is_cuda(ts: Sequence[Optional[torch.Tensor]]) -> bool:
@@ -53,6 +56,8 @@ def workspace(dev: torch.device, name: str, numel: int, dtype=torch.float32) -> 
     if t is None or t.numel() < numel or t.dtype != dtype:
         t = torch.empty(max(numel, 1024), dtype=dtype, device=dev)
         d[name] = t
+    if DEBUG_POISON and t.is_floating_point():
+        t[:max(numel, 1)].fill_(float("nan"))
     return t
 
 

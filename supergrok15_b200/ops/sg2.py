@@ -179,6 +179,11 @@ class Plan:
             "agg": torch.empty(max(self.n_items, 1) * 16 * 48, **f32),
             "carry": torch.empty(max(self.n_items, 1) * 16 * 16, **f32),
         }
+        from . import elementwise as _ew
+        if _ew.DEBUG_POISON:                                          # GROK_DEBUG=1: float scratch starts as NaN (see ops/elementwise.py)
+            for t in self.ws.values():
+                if t.is_floating_point():
+                    t.fill_(float("nan"))
 
     def workspace_bytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in self.ws.values())

@@ -1,5 +1,6 @@
 """CPU tests of the optimizer API and of the PyTorch oracle (no GPU needed)."""
 import math
+import os
 
 import pytest
 import torch
@@ -360,3 +361,60 @@ def test_soft_head_batched_routing_matches_per_head_statement():
     assert set(out["batched"][2]) == set(out["per_head"][2]) and len(out["batched"][2]) > 10
     for k in out["per_head"][2]:
         assert torch.allclose(out["batched"][2][k], out["per_head"][2][k], rtol=1e-8, atol=1e-12), k
+
+
+_POISON_SCRIPT = r'''
+import torch, torch.nn.functional as F
+from supergrok15_b200 import optim as O
+from supergrok15_b200.ops import elementwise as ew
+torch.manual_seed(0)
+x, y = torch.randn(64, 16), torch.randint(0, 10, (64,))
+for name in ("GrokAdamW", "Prodigy", "NeuralGrok", "SuperGrok15", "SuperGrok11", "LookSAM", "Lion"):
+    torch.manual_seed(1)
+    m = torch.nn.Sequential(torch.nn.Linear(16, 32), torch.nn.ReLU(), torch.nn.Linear(32, 10))
+    opt = getattr(O, name)(m.parameters())
+    for _ in range(3):
+        opt.zero_grad()
+        F.cross_entropy(m(x), y).backward()
+        opt.step()
+    flat = torch.cat([p.detach().reshape(-1) for p in m.parameters()])
+    assert torch.isfinite(flat).all(), name
+    print(name, ew.DEBUG_POISON, "%.9e" % float(flat.double().abs().sum()))
+'''
+
+
+def test_grok_debug_poisoned_scratch_changes_nothing():
+    """GROK_DEBUG=1 fills every scratch buffer with NaN before it is handed out; a step that read scratch it had not written
+    would turn non-finite or differ from the normal run."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    outs = []
+    for flag in ("0", "1"):
+        r = subprocess.run([sys.executable, "-c", _POISON_SCRIPT], env=dict(os.environ, GROK_DEBUG=flag, PYTHONPATH=root),
+                           capture_output=True, text=True, timeout=600)
+        assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+        outs.append([l.split() for l in r.stdout.strip().splitlines()])
+    assert all(l[1] == "False" for l in outs[0]) and all(l[1] == "True" for l in outs[1])
+    assert [(l[0], l[2]) for l in outs[0]] == [(l[0], l[2]) for l in outs[1]]
+
+
+@pytest.mark.skipif(os.environ.get("SG_TEST_SANITIZE") != "1",
+                    reason="compiles every binding file with -Wall -Werror -fsanitize=address,undefined (minutes): set SG_TEST_SANITIZE=1")
+def test_host_code_under_asan_ubsan(tmp_path):
+    """The C++ CPU kernels and the binding layer run three steps of every element-wise optimizer under ASan + UBSan."""
+    import subprocess
+    import sys
+    from supergrok15_b200 import _build
+    asan = subprocess.run(["gcc", "-print-file-name=libasan.so"], capture_output=True, text=True).stdout.strip()
+    if not os.path.isabs(asan) or not os.path.exists(asan):
+        pytest.skip("libasan not installed")
+    so = _build.build_sanitized(tmp_path)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, SG_EXT_SO=str(so), LD_PRELOAD=asan, PYTHONPATH=root, GROK_DEBUG="1",
+               ASAN_OPTIONS="detect_leaks=0:abort_on_error=1", UBSAN_OPTIONS="halt_on_error=1:print_stacktrace=1")
+    r = subprocess.run([sys.executable, "-c", _POISON_SCRIPT], env=env, capture_output=True, text=True, timeout=1800)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-6000:]
+    assert "runtime error" not in r.stderr and "AddressSanitizer" not in r.stderr, r.stderr[-6000:]
+    assert len(r.stdout.strip().splitlines()) == 7

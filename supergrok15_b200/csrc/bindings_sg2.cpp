@@ -3,6 +3,7 @@
 #include <c10/cuda/CUDAGuard.h>
 #include "bindings_decl.h"
 #include "mt_host.h"
+#include "sg2_routing_math.h"
 
 namespace sg {
 void sg2_upload_weights(const float* packed_dev, cudaStream_t s);
@@ -37,6 +38,16 @@ int routed_experts_fwd(const float* g, const int* ia, const int* ib, const float
 int routed_experts_bwd(const float* g, const int* ia, const int* ib, const float* wa, const float* wb, const float* W1, const float* b1,
                        const float* W2, const float* b2, const float* dtotal, int64_t n, int heads, int E, int pk, float* dwa, float* dwb,
                        float* partial, float* dparams, cudaStream_t s);
+}
+
+namespace sg {
+bool routing_supported(int heads, int P, int pk, int d_model, int topk);
+int routing_bwd_ctas(int64_t n, int heads);
+int routing_ng(int heads, int P, int pk);
+int routing_fwd(const float* pin, const float* Wq, const float* KA, const float* KB, int64_t n, int heads, int P, int pk, int* ia, int* ib,
+                float* wa, float* wb, cudaStream_t s);
+int routing_bwd(const float* pin, const float* Wq, const float* KA, const float* KB, const int* ia, const int* ib, const float* wa, const float* wb,
+                const float* dwa, const float* dwb, int64_t n, int heads, int P, int pk, float* dpin, float* partial, float* dparams, cudaStream_t s);
 }
 
 namespace sgb {
@@ -210,9 +221,99 @@ std::vector<Tensor> routed_experts_bwd(const Tensor& g, const Tensor& ia, const 
     TORCH_CHECK(rc == 0, "routed_experts_bwd launch failed (code ", rc, ")");
     return {dwa, dwb, dparams};
 }
+
+// ---- product-key routing of the bilevel tail (csrc/sg2_routing.cu on CUDA; the same arithmetic, csrc/sg2_routing_math.h, in a loop on CPU)
+struct RShape { int64_t n; int heads, P, pk; };
+RShape routing_check(const Tensor& pin, const Tensor& Wq, const Tensor& KA, const Tensor& KB) {
+    for (const Tensor* t : {&pin, &Wq, &KA, &KB})
+        TORCH_CHECK(t->is_contiguous() && t->scalar_type() == at::kFloat && t->device() == pin.device(), "routing: contiguous fp32 tensors on one device");
+    TORCH_CHECK(pin.dim() == 2 && Wq.dim() == 2 && Wq.size(1) == pin.size(1) && Wq.size(0) % sg::routing::RD == 0, "pin [n, P], Wq [heads * 8, P]");
+    RShape s{pin.size(0), (int)(Wq.size(0) / sg::routing::RD), (int)pin.size(1), (int)KA.size(1)};
+    TORCH_CHECK(KA.dim() == 3 && KA.size(0) == s.heads && KA.size(2) == sg::routing::RH && KB.sizes() == KA.sizes(), "KA, KB [heads, pk, 4]");
+    TORCH_CHECK(sg::routing_supported(s.heads, s.P, s.pk, sg::routing::RD, sg::routing::RK), "routing: unsupported configuration");
+    return s;
+}
+
+// returns (ia, ib int32 [n, heads, 4], wa, wb fp32 [n, heads, 4])
+std::vector<Tensor> routing_fwd(const Tensor& pin, const Tensor& Wq, const Tensor& KA, const Tensor& KB) {
+    const RShape s = routing_check(pin, Wq, KA, KB);
+    auto io = pin.options().dtype(at::kInt);
+    Tensor ia = at::empty({s.n, s.heads, 4}, io), ib = at::empty({s.n, s.heads, 4}, io);
+    Tensor wa = at::empty({s.n, s.heads, 4}, pin.options()), wb = at::empty({s.n, s.heads, 4}, pin.options());
+    if (pin.is_cuda()) {
+        c10::cuda::CUDAGuard guard(pin.device());
+        const int rc = sg::routing_fwd(pin.data_ptr<float>(), Wq.data_ptr<float>(), KA.data_ptr<float>(), KB.data_ptr<float>(), s.n, s.heads, s.P, s.pk,
+                                       ia.data_ptr<int>(), ib.data_ptr<int>(), wa.data_ptr<float>(), wb.data_ptr<float>(), at::cuda::getCurrentCUDAStream());
+        TORCH_CHECK(rc == 0, "routing_fwd launch failed (code ", rc, ")");
+        return {ia, ib, wa, wb};
+    }
+    const float *x = pin.data_ptr<float>(), *wq = Wq.data_ptr<float>(), *ka = KA.data_ptr<float>(), *kb = KB.data_ptr<float>();
+    for (int64_t e = 0; e < s.n; ++e)
+        for (int h = 0; h < s.heads; ++h) {
+            float q[sg::routing::RD];
+            const int64_t r = (e * s.heads + h) * 4;
+            sg::routing::route_fwd(x + e * s.P, s.P, wq + h * sg::routing::RD * s.P, ka + h * s.pk * 4, kb + h * s.pk * 4, s.pk, q,
+                                   ia.data_ptr<int>() + r, ib.data_ptr<int>() + r, wa.data_ptr<float>() + r, wb.data_ptr<float>() + r);
+        }
+    return {ia, ib, wa, wb};
+}
+
+// returns (d pin [n, P], d [Wq | KA | KB] flat)
+std::vector<Tensor> routing_bwd(const Tensor& pin, const Tensor& Wq, const Tensor& KA, const Tensor& KB, const Tensor& ia, const Tensor& ib,
+                                const Tensor& wa, const Tensor& wb, const Tensor& dwa, const Tensor& dwb) {
+    const RShape s = routing_check(pin, Wq, KA, KB);
+    for (const Tensor* t : {&wa, &wb, &dwa, &dwb})
+        TORCH_CHECK(t->is_contiguous() && t->scalar_type() == at::kFloat && t->numel() == s.n * s.heads * 4 && t->device() == pin.device(), "wa, wb, dwa, dwb: fp32 [n, heads, 4]");
+    for (const Tensor* t : {&ia, &ib})
+        TORCH_CHECK(t->is_contiguous() && t->scalar_type() == at::kInt && t->numel() == s.n * s.heads * 4 && t->device() == pin.device(), "ia, ib: int32 [n, heads, 4]");
+    const int ng = sg::routing_ng(s.heads, s.P, s.pk);
+    Tensor dpin = at::empty_like(pin), dparams = at::empty({ng}, pin.options());
+    if (pin.is_cuda()) {
+        c10::cuda::CUDAGuard guard(pin.device());
+        Tensor partial = at::empty({(int64_t)sg::routing_bwd_ctas(s.n, s.heads), ng}, pin.options());
+        const int rc = sg::routing_bwd(pin.data_ptr<float>(), Wq.data_ptr<float>(), KA.data_ptr<float>(), KB.data_ptr<float>(), ia.data_ptr<int>(),
+                                       ib.data_ptr<int>(), wa.data_ptr<float>(), wb.data_ptr<float>(), dwa.data_ptr<float>(), dwb.data_ptr<float>(), s.n,
+                                       s.heads, s.P, s.pk, dpin.data_ptr<float>(), partial.data_ptr<float>(), dparams.data_ptr<float>(),
+                                       at::cuda::getCurrentCUDAStream());
+        TORCH_CHECK(rc == 0, "routing_bwd launch failed (code ", rc, ")");
+        return {dpin, dparams};
+    }
+    using namespace sg::routing;
+    const float *x = pin.data_ptr<float>(), *wq = Wq.data_ptr<float>(), *ka = KA.data_ptr<float>(), *kb = KB.data_ptr<float>();
+    const int n_wq = s.heads * RD * s.P, n_k = s.heads * s.pk * RH;
+    std::vector<double> acc(ng, 0.0);
+    float* dp = dpin.data_ptr<float>();
+    for (int64_t e = 0; e < s.n; ++e) {
+        for (int j = 0; j < s.P; ++j) dp[e * s.P + j] = 0.f;
+        for (int h = 0; h < s.heads; ++h) {
+            const int64_t r = (e * s.heads + h) * 4;
+            float q[RD], dt[2 * RK], dq[RD];
+            query(x + e * s.P, s.P, wq + h * RD * s.P, q);
+            route_bwd(ia.data_ptr<int>() + r, ib.data_ptr<int>() + r, wa.data_ptr<float>() + r, wb.data_ptr<float>() + r, dwa.data_ptr<float>() + r,
+                      dwb.data_ptr<float>() + r, ka + h * s.pk * RH, kb + h * s.pk * RH, dt, dq);
+            for (int o = 0; o < RD; ++o)
+                for (int j = 0; j < s.P; ++j) {
+                    dp[e * s.P + j] += wq[(h * RD + o) * s.P + j] * dq[o];
+                    acc[(h * RD + o) * s.P + j] += (double)dq[o] * x[e * s.P + j];
+                }
+            for (int k = 0; k < RK; ++k)
+                for (int d = 0; d < RH; ++d) {
+                    acc[n_wq + (h * s.pk + ia.data_ptr<int>()[r + k]) * RH + d] += (double)dt[k] * q[d];
+                    acc[n_wq + n_k + (h * s.pk + ib.data_ptr<int>()[r + k]) * RH + d] += (double)dt[RK + k] * q[RH + d];
+                }
+        }
+    }
+    float* out = dparams.data_ptr<float>();
+    for (int i = 0; i < ng; ++i) out[i] = (float)acc[i];
+    return {dpin, dparams};
+}
 }  // namespace
 
 void register_sg2(pybind11::module_& m) {
+    m.def("sg2_routing_supported", [](int64_t heads, int64_t P, int64_t pk, int64_t d_model, int64_t topk) {
+        return sg::routing_supported((int)heads, (int)P, (int)pk, (int)d_model, (int)topk); });
+    m.def("sg2_routing_fwd", &routing_fwd);
+    m.def("sg2_routing_bwd", &routing_bwd);
     m.def("sg2_routed_experts_supported", [](int64_t heads, int64_t E, int64_t hidden, int64_t topk) {
         return sg::routed_experts_supported((int)heads, (int)E, (int)hidden, (int)topk); });
     m.def("sg2_routed_experts_fwd", &routed_experts_fwd);

@@ -55,6 +55,38 @@ def routed_experts(g, ia, ib, wa, wb, W1, b1, W2, b2, pk: int) -> torch.Tensor:
     return _RoutedExperts.apply(g, ia, ib, wa, wb, W1, b1, W2, b2, pk)
 
 
+class _Routing(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, pin, Wq, KA, KB):
+        C = _build.require()
+        a = [t.detach().contiguous().float() for t in (pin, Wq, KA, KB)]
+        ia, ib, wa, wb = C.sg2_routing_fwd(*a)
+        ctx.save_for_backward(*a, ia, ib, wa, wb)
+        ctx.mark_non_differentiable(ia, ib)
+        return ia, ib, wa, wb
+
+    @staticmethod
+    def backward(ctx, _dia, _dib, dwa, dwb):
+        C = _build.require()
+        pin, Wq, KA, KB, ia, ib, wa, wb = ctx.saved_tensors
+        dwa = torch.zeros_like(wa) if dwa is None else dwa.contiguous().float()
+        dwb = torch.zeros_like(wb) if dwb is None else dwb.contiguous().float()
+        dpin, dp = C.sg2_routing_bwd(pin, Wq, KA, KB, ia, ib, wa, wb, dwa, dwb)
+        nq, nk = Wq.numel(), KA.numel()
+        return dpin, dp[:nq].view_as(Wq), dp[nq:nq + nk].view_as(KA), dp[nq + nk:].view_as(KB)
+
+
+def routing_supported(heads: int, width: int, pk: int, d_model: int, topk: int) -> bool:
+    return bool(_build.require().sg2_routing_supported(heads, width, pk, d_model, topk))
+
+
+def routing(pin, Wq, KA, KB):
+    """Product-key routing of all heads: pin [n, P], Wq [heads * 8, P], KA / KB [heads, pk, 4] ->
+    (ia, ib int32 [n, heads, 4], wa, wb [n, heads, 4]); differentiable with respect to pin, Wq, KA and KB through wa and wb.
+    CUDA tensors run ``csrc/sg2_routing.cu``, CPU tensors the same arithmetic in a C++ loop (``csrc/sg2_routing_math.h``)."""
+    return _Routing.apply(pin, Wq, KA, KB)
+
+
 def scan_params(meta_net) -> List[torch.Tensor]:
     """Differentiable tensors the adjoint kernel reports gradients for, per direction:
     A_log [16,16], rope [16,8], D [16], U_x, U_z, U_dt, U_B, U_C [16,3] each, out_proj [8,16]."""

@@ -309,12 +309,18 @@ class Mamba3PEERMetaNet(nn.Module):
         # score vectors, ONE top-k and ONE softmax over [n, heads, 2, pk] (instead of 2 * heads of each).
         H, pk = self.num_peer_heads, self.pk_dim
         Wq = torch.cat([lin.weight for lin in self.peer_queries], 0)                                # [H * d_model, peer_in]
-        q = peer_in @ Wq.T                                                                          # [n, H * d_model]
-        keys = torch.block_diag(*[blk for h in range(H) for blk in (self.product_keys_A[h].T, self.product_keys_B[h].T)])
-        scores = (q @ keys).view(n, H, 2, pk)                                                       # [..., 0, :] sub-key A, [..., 1, :] sub-key B
-        top, idx = scores.topk(topk, dim=-1)
-        w = torch.softmax(top * 10.0, -1)
-        ia, ib, wa, wb = idx[:, :, 0], idx[:, :, 1], w[:, :, 0], w[:, :, 1]                          # [n, H, topk] each
+        if os.environ.get("SG_BILEVEL_ROUTING", "torch") == "kernel" and peer_in.dtype == torch.float32:
+            # opt-in: queries, scores, top-4 and softmax of all heads in one native kernel each way (ops/sg2_bilevel.py: routing)
+            from ..ops import sg2_bilevel as _sb
+            assert _sb.routing_supported(H, peer_in.shape[1], pk, self.d_model, topk), "SG_BILEVEL_ROUTING=kernel: unsupported meta-net shape"
+            ia, ib, wa, wb = _sb.routing(peer_in, Wq, torch.stack(list(self.product_keys_A)), torch.stack(list(self.product_keys_B)))
+        else:
+            q = peer_in @ Wq.T                                                                      # [n, H * d_model]
+            keys = torch.block_diag(*[blk for h in range(H) for blk in (self.product_keys_A[h].T, self.product_keys_B[h].T)])
+            scores = (q @ keys).view(n, H, 2, pk)                                                   # [..., 0, :] sub-key A, [..., 1, :] sub-key B
+            top, idx = scores.topk(topk, dim=-1)
+            w = torch.softmax(top * 10.0, -1)
+            ia, ib, wa, wb = idx[:, :, 0], idx[:, :, 1], w[:, :, 0], w[:, :, 1]                      # [n, H, topk] each
         if use_kernel:
             # one kernel evaluates the 16 selected experts of every head; its backward sums the expert gradients in a fixed order
             total = sg2_bilevel.routed_experts(g.reshape(-1), ia, ib, wa, wb, self.expert_W1.squeeze(-1), self.expert_b1,

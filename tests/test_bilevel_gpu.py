@@ -132,3 +132,25 @@ def test_soft_head_expert_kernel_matches_dense_path(monkeypatch):
     for k, gd in res["dense"][2].items():
         gk = res["kernel"][2][k]
         assert (gk - gd).abs().max() <= 1e-3 * gd.abs().max() + 1e-9, (k, float((gk - gd).abs().max()), float(gd.abs().max()))
+
+
+@pytest.mark.skipif(__import__("os").environ.get("SG_TEST_ROUTING_GPU") != "1",
+                    reason="the routing kernels (csrc/sg2_routing.cu) are opt-in (SG_BILEVEL_ROUTING=kernel); set SG_TEST_ROUTING_GPU=1 to test them")
+@pytest.mark.parametrize("n,heads,P,pk", [(1, 4, 22, 12), (1000, 4, 22, 12), (70001, 4, 22, 12), (333, 2, 14, 8)])
+def test_routing_kernels_match_cpu_loop(n, heads, P, pk):
+    """The CUDA routing kernels against the C++ CPU loop over the same per-element functions (csrc/sg2_routing_math.h)."""
+    from supergrok15_b200.ops import sg2_bilevel
+    torch.manual_seed(n)
+    cpu = [torch.randn(n, P), torch.randn(heads * 8, P) * 0.3, torch.randn(heads, pk, 4), torch.randn(heads, pk, 4)]
+    gwa, gwb = torch.randn(n, heads, 4), torch.randn(n, heads, 4)
+    outs = []
+    for dev in ("cpu", "cuda"):
+        leaves = [t.to(dev).requires_grad_(True) for t in cpu]
+        ia, ib, wa, wb = sg2_bilevel.routing(*leaves)
+        grads = torch.autograd.grad((wa * gwa.to(dev)).sum() + (wb * gwb.to(dev)).sum(), leaves)
+        outs.append([t.cpu() for t in (ia, ib, wa, wb, *grads)])
+    same = (outs[0][0] == outs[1][0]).all(-1).all(-1) & (outs[0][1] == outs[1][1]).all(-1).all(-1)
+    assert same.float().mean() > 0.999                       # a near-tie may be ordered differently by fused multiply-adds
+    assert torch.allclose(outs[0][2][same], outs[1][2][same], rtol=1e-4, atol=1e-5)
+    for a, b in zip(outs[0][4:], outs[1][4:]):
+        assert (a - b).abs().max() <= 2e-3 * a.abs().max() + 1e-6

@@ -418,3 +418,59 @@ def test_host_code_under_asan_ubsan(tmp_path):
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-6000:]
     assert "runtime error" not in r.stderr and "AddressSanitizer" not in r.stderr, r.stderr[-6000:]
     assert len(r.stdout.strip().splitlines()) == 7
+
+
+@pytest.mark.parametrize("n,heads,P,pk", [(1, 4, 22, 12), (257, 4, 22, 12), (90, 2, 14, 8), (64, 4, 30, 16)])
+def test_native_routing_matches_pytorch_statement(n, heads, P, pk):
+    """csrc/sg2_routing_math.h (run here through its C++ CPU loop; the CUDA kernels execute the same functions) against the
+    PyTorch statement: per head a query product, two score products, top-4 and softmax(10 x), gradients through the weights."""
+    from supergrok15_b200 import _build
+    if not _build.native_available():
+        pytest.skip("native extension not built")
+    from supergrok15_b200.ops import sg2_bilevel
+    torch.manual_seed(n + heads)
+    pin = torch.randn(n, P, requires_grad=True)
+    Wq = (torch.randn(heads * 8, P) * 0.3).requires_grad_(True)
+    KA = torch.randn(heads, pk, 4, requires_grad=True)
+    KB = torch.randn(heads, pk, 4, requires_grad=True)
+    gwa, gwb = torch.randn(n, heads, 4), torch.randn(n, heads, 4)
+    leaves = (pin, Wq, KA, KB)
+    ia, ib, wa, wb = sg2_bilevel.routing(pin, Wq, KA, KB)
+    grads = torch.autograd.grad((wa * gwa).sum() + (wb * gwb).sum(), leaves)
+    dl = [t.detach().double().requires_grad_(True) for t in leaves]
+    q = (dl[0] @ dl[1].T).view(n, heads, 8)
+    ta, ra = torch.einsum("nhd,hkd->nhk", q[..., :4], dl[2]).topk(4, dim=-1)
+    tb, rb = torch.einsum("nhd,hkd->nhk", q[..., 4:], dl[3]).topk(4, dim=-1)
+    wa_r, wb_r = torch.softmax(ta * 10.0, -1), torch.softmax(tb * 10.0, -1)
+    rgrads = torch.autograd.grad((wa_r * gwa.double()).sum() + (wb_r * gwb.double()).sum(), dl)
+    assert torch.equal(ia.long(), ra) and torch.equal(ib.long(), rb)
+    assert torch.allclose(wa.double(), wa_r, rtol=1e-4, atol=1e-5) and torch.allclose(wb.double(), wb_r, rtol=1e-4, atol=1e-5)
+    for name, a, b in zip(("pin", "Wq", "KA", "KB"), grads, rgrads):
+        assert (a.double() - b).abs().max() <= 2e-4 * b.abs().max() + 1e-7, (name, float((a.double() - b).abs().max()), float(b.abs().max()))
+
+
+def test_soft_head_with_native_routing_matches_torch_routing(monkeypatch):
+    from supergrok15_b200 import _build
+    if not _build.native_available():
+        pytest.skip("native extension not built")
+    torch.manual_seed(4)
+    mn = Mamba3PEERMetaNet()
+    with torch.no_grad():
+        mn.expert_W1.mul_(30); mn.expert_W2.mul_(30)
+        for k in list(mn.product_keys_A) + list(mn.product_keys_B):
+            k.mul_(10)
+    n = 300
+    g, s = torch.randn(n) * 1e-2, torch.rand(n) * 1e-2
+    gru, vu = torch.randn(n, mn.gru_hidden) * 0.1, torch.randn(n)
+    ctx = (torch.randn(n, 16) * 0.1).requires_grad_(True)
+    res = {}
+    for mode in ("torch", "kernel"):
+        monkeypatch.setenv("SG_BILEVEL_ROUTING", mode)
+        mn.zero_grad(set_to_none=True)
+        ctx.grad = None
+        (mn.soft_head(g, s, gru, ctx[:, :8], ctx[:, 8:]) * vu).sum().backward()
+        res[mode] = (ctx.grad.clone(), {k: p.grad.clone() for k, p in mn.named_parameters() if p.grad is not None})
+    assert torch.allclose(res["kernel"][0], res["torch"][0], rtol=1e-3, atol=1e-7)
+    assert set(res["kernel"][1]) == set(res["torch"][1])
+    for k, gt in res["torch"][1].items():
+        assert (res["kernel"][1][k] - gt).abs().max() <= 1e-3 * gt.abs().max() + 1e-9, k

@@ -4,6 +4,7 @@
 #include "bindings_decl.h"
 #include "mt_host.h"
 #include "sg2_routing_math.h"
+#include "sg2_gru_math.h"
 
 namespace sg {
 void sg2_upload_weights(const float* packed_dev, cudaStream_t s);
@@ -48,6 +49,15 @@ int routing_fwd(const float* pin, const float* Wq, const float* KA, const float*
                 float* wa, float* wb, cudaStream_t s);
 int routing_bwd(const float* pin, const float* Wq, const float* KA, const float* KB, const int* ia, const int* ib, const float* wa, const float* wb,
                 const float* dwa, const float* dwb, int64_t n, int heads, int P, int pk, float* dpin, float* partial, float* dparams, cudaStream_t s);
+}
+
+namespace sg {
+int gru_ng(int IN);
+bool gru_supported(int IN, int hidden);
+int gru_bwd_ctas(int64_t n);
+int gru_fwd(const float* x, const float* h, const float* W, const float* b, int64_t n, int IN, float* hn, cudaStream_t s);
+int gru_bwd(const float* x, const float* h, const float* W, const float* b, const float* dhn, int64_t n, int IN, float* dx, float* partial,
+            float* dparams, cudaStream_t s);
 }
 
 namespace sgb {
@@ -307,9 +317,77 @@ std::vector<Tensor> routing_bwd(const Tensor& pin, const Tensor& Wq, const Tenso
     for (int i = 0; i < ng; ++i) out[i] = (float)acc[i];
     return {dpin, dparams};
 }
+
+// ---- per-element GRU of the meta-net (csrc/sg2_gru.cu on CUDA; the same arithmetic, csrc/sg2_gru_math.h, in a loop on CPU)
+int gru_check(const Tensor& x, const Tensor& h, const Tensor& W, const Tensor& b) {
+    for (const Tensor* t : {&x, &h, &W, &b})
+        TORCH_CHECK(t->is_contiguous() && t->scalar_type() == at::kFloat && t->device() == x.device(), "gru: contiguous fp32 tensors on one device");
+    const int IN = (int)x.size(1);
+    TORCH_CHECK(x.dim() == 2 && h.dim() == 2 && h.size(0) == x.size(0) && h.size(1) == sg::gru::GH, "x [n, IN], h [n, 4]");
+    TORCH_CHECK(W.numel() == 3 * sg::gru::GH * (IN + sg::gru::GH) && b.numel() == 3 * sg::gru::GH, "W [3, 4, IN + 4], b [3, 4]");
+    TORCH_CHECK(sg::gru_supported(IN, (int)h.size(1)), "gru: unsupported width");
+    return IN;
+}
+
+Tensor gru_fwd(const Tensor& x, const Tensor& h, const Tensor& W, const Tensor& b) {
+    const int IN = gru_check(x, h, W, b);
+    const int64_t n = x.size(0);
+    Tensor hn = at::empty_like(h);
+    if (x.is_cuda()) {
+        c10::cuda::CUDAGuard guard(x.device());
+        const int rc = sg::gru_fwd(x.data_ptr<float>(), h.data_ptr<float>(), W.data_ptr<float>(), b.data_ptr<float>(), n, IN, hn.data_ptr<float>(),
+                                   at::cuda::getCurrentCUDAStream());
+        TORCH_CHECK(rc == 0, "gru_fwd launch failed (code ", rc, ")");
+        return hn;
+    }
+    using namespace sg::gru;
+    for (int64_t e = 0; e < n; ++e) {
+        float z[GH], r[GH], c[GH];
+        gru_gates(x.data_ptr<float>() + e * IN, h.data_ptr<float>() + e * GH, IN, W.data_ptr<float>(), b.data_ptr<float>(), z, r, c, hn.data_ptr<float>() + e * GH);
+    }
+    return hn;
+}
+
+// returns (d x [n, IN], d [W | b] flat)
+std::vector<Tensor> gru_bwd(const Tensor& x, const Tensor& h, const Tensor& W, const Tensor& b, const Tensor& dhn) {
+    const int IN = gru_check(x, h, W, b);
+    const int64_t n = x.size(0);
+    TORCH_CHECK(dhn.is_contiguous() && dhn.scalar_type() == at::kFloat && dhn.sizes() == h.sizes() && dhn.device() == x.device(), "dhn: fp32 [n, 4]");
+    const int ng = sg::gru_ng(IN);
+    Tensor dx = at::empty_like(x), dparams = at::empty({ng}, x.options());
+    if (x.is_cuda()) {
+        c10::cuda::CUDAGuard guard(x.device());
+        Tensor partial = at::empty({(int64_t)sg::gru_bwd_ctas(n), ng}, x.options());
+        const int rc = sg::gru_bwd(x.data_ptr<float>(), h.data_ptr<float>(), W.data_ptr<float>(), b.data_ptr<float>(), dhn.data_ptr<float>(), n, IN,
+                                   dx.data_ptr<float>(), partial.data_ptr<float>(), dparams.data_ptr<float>(), at::cuda::getCurrentCUDAStream());
+        TORCH_CHECK(rc == 0, "gru_bwd launch failed (code ", rc, ")");
+        return {dx, dparams};
+    }
+    using namespace sg::gru;
+    const int P = IN + GH, nw = 3 * GH * P;
+    std::vector<double> acc(ng, 0.0);
+    for (int64_t e = 0; e < n; ++e) {
+        const float* xe = x.data_ptr<float>() + e * IN;
+        const float* he = h.data_ptr<float>() + e * GH;
+        float dpre[3 * GH], rh[GH];
+        gru_adjoint(xe, he, IN, W.data_ptr<float>(), b.data_ptr<float>(), dhn.data_ptr<float>() + e * GH, dpre, rh, dx.data_ptr<float>() + e * IN);
+        for (int gi = 0; gi < 3 * GH; ++gi) {
+            for (int j = 0; j < P; ++j) {
+                const float src = j < IN ? xe[j] : (gi >= 2 * GH ? rh[j - IN] : he[j - IN]);
+                acc[gi * P + j] += (double)dpre[gi] * src;
+            }
+            acc[nw + gi] += dpre[gi];
+        }
+    }
+    for (int i = 0; i < ng; ++i) dparams.data_ptr<float>()[i] = (float)acc[i];
+    return {dx, dparams};
+}
 }  // namespace
 
 void register_sg2(pybind11::module_& m) {
+    m.def("sg2_gru_supported", [](int64_t IN, int64_t hidden) { return sg::gru_supported((int)IN, (int)hidden); });
+    m.def("sg2_gru_fwd", &gru_fwd);
+    m.def("sg2_gru_bwd", &gru_bwd);
     m.def("sg2_routing_supported", [](int64_t heads, int64_t P, int64_t pk, int64_t d_model, int64_t topk) {
         return sg::routing_supported((int)heads, (int)P, (int)pk, (int)d_model, (int)topk); });
     m.def("sg2_routing_fwd", &routing_fwd);

@@ -87,6 +87,33 @@ def routing(pin, Wq, KA, KB):
     return _Routing.apply(pin, Wq, KA, KB)
 
 
+class _Gru(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, h, W, b):
+        C = _build.require()
+        a = [t.detach().contiguous().float() for t in (x, h, W, b)]
+        ctx.save_for_backward(*a)
+        return C.sg2_gru_fwd(*a)
+
+    @staticmethod
+    def backward(ctx, dhn):
+        C = _build.require()
+        x, h, W, b = ctx.saved_tensors
+        dx, dp = C.sg2_gru_bwd(x, h, W, b, dhn.contiguous().float())
+        return dx, None, dp[:W.numel()].view_as(W), dp[W.numel():].view_as(b)
+
+
+def gru_supported(width: int, hidden: int) -> bool:
+    return bool(_build.require().sg2_gru_supported(width, hidden))
+
+
+def gru(x, h, W, b):
+    """New GRU state [n, 4] from inputs x [n, IN] and the previous state h [n, 4] (data: no gradient); W [3, 4, IN + 4] and
+    b [3, 4] hold the z, r and candidate gates.  Differentiable with respect to x, W and b.  CUDA tensors run ``csrc/sg2_gru.cu``,
+    CPU tensors the same arithmetic in a C++ loop (``csrc/sg2_gru_math.h``)."""
+    return _Gru.apply(x, h, W, b)
+
+
 def scan_params(meta_net) -> List[torch.Tensor]:
     """Differentiable tensors the adjoint kernel reports gradients for, per direction:
     A_log [16,16], rope [16,8], D [16], U_x, U_z, U_dt, U_B, U_C [16,3] each, out_proj [8,16]."""

@@ -292,7 +292,18 @@ class Mamba3PEERMetaNet(nn.Module):
         """Everything after the scan of ``forward_for_bilevel`` (GRU, soft top-k routing, experts) for elements whose
         contexts are given: returns smart_grad [n].  Element-wise over n, so it can be applied to any slice."""
         gs = torch.stack([g, s], dim=-1)
-        new_gru = self.gru(torch.cat([gs, fwd_ctx, bwd_ctx], dim=-1), gru_state.float())
+        # SG_BILEVEL_TAIL=native (opt-in): the GRU and the product-key routing run as native kernels each way (ops/sg2_bilevel.py:
+        # gru, routing) instead of the PyTorch statements below
+        native_tail = os.environ.get("SG_BILEVEL_TAIL", "torch") == "native" and g.dtype == torch.float32 and fwd_ctx.dtype == torch.float32
+        gru_in = torch.cat([gs, fwd_ctx, bwd_ctx], dim=-1)
+        if native_tail:
+            from ..ops import sg2_bilevel as _sb
+            assert _sb.gru_supported(gru_in.shape[1], self.gru_hidden), "SG_BILEVEL_TAIL=native: unsupported GRU shape"
+            Wg = torch.stack([self.gru.W_z.weight, self.gru.W_r.weight, self.gru.W_h.weight])
+            bg = torch.stack([self.gru.W_z.bias, self.gru.W_r.bias, self.gru.W_h.bias])
+            new_gru = _sb.gru(gru_in, gru_state.float(), Wg, bg)
+        else:
+            new_gru = self.gru(gru_in, gru_state.float())
         peer_in = torch.cat([new_gru, fwd_ctx, bwd_ctx, gs], dim=-1)
         n = g.numel()
         # Every head evaluates the SAME experts on the SAME scalar g, so the heads only differ in their routing weights:
@@ -309,10 +320,9 @@ class Mamba3PEERMetaNet(nn.Module):
         # score vectors, ONE top-k and ONE softmax over [n, heads, 2, pk] (instead of 2 * heads of each).
         H, pk = self.num_peer_heads, self.pk_dim
         Wq = torch.cat([lin.weight for lin in self.peer_queries], 0)                                # [H * d_model, peer_in]
-        if os.environ.get("SG_BILEVEL_ROUTING", "torch") == "kernel" and peer_in.dtype == torch.float32:
-            # opt-in: queries, scores, top-4 and softmax of all heads in one native kernel each way (ops/sg2_bilevel.py: routing)
-            from ..ops import sg2_bilevel as _sb
-            assert _sb.routing_supported(H, peer_in.shape[1], pk, self.d_model, topk), "SG_BILEVEL_ROUTING=kernel: unsupported meta-net shape"
+        if native_tail:
+            # queries, scores, top-4 and softmax of all heads in one native kernel each way
+            assert _sb.routing_supported(H, peer_in.shape[1], pk, self.d_model, topk), "SG_BILEVEL_TAIL=native: unsupported routing shape"
             ia, ib, wa, wb = _sb.routing(peer_in, Wq, torch.stack(list(self.product_keys_A)), torch.stack(list(self.product_keys_B)))
         else:
             q = peer_in @ Wq.T                                                                      # [n, H * d_model]

@@ -449,7 +449,36 @@ def test_native_routing_matches_pytorch_statement(n, heads, P, pk):
         assert (a.double() - b).abs().max() <= 2e-4 * b.abs().max() + 1e-7, (name, float((a.double() - b).abs().max()), float(b.abs().max()))
 
 
-def test_soft_head_with_native_routing_matches_torch_routing(monkeypatch):
+@pytest.mark.parametrize("n,IN", [(1, 18), (300, 18), (513, 10)])
+def test_native_gru_matches_minigru(n, IN):
+    """csrc/sg2_gru_math.h through its C++ CPU loop against the PyTorch MiniGRU: new state, input gradient, weight gradients."""
+    from supergrok15_b200 import _build
+    if not _build.native_available():
+        pytest.skip("native extension not built")
+    from supergrok15_b200.ops import sg2_bilevel
+    from supergrok15_b200.optim.metanet import MiniGRU
+    torch.manual_seed(n)
+    cell = MiniGRU(IN, 4)
+    with torch.no_grad():
+        for p in cell.parameters():
+            p.mul_(3)
+    x = torch.randn(n, IN, requires_grad=True)
+    h = torch.randn(n, 4)
+    gout = torch.randn(n, 4)
+    ref = cell(x, h)
+    rg = torch.autograd.grad((ref * gout).sum(), [x, *cell.parameters()])
+    W = torch.stack([cell.W_z.weight, cell.W_r.weight, cell.W_h.weight]).detach().requires_grad_(True)
+    b = torch.stack([cell.W_z.bias, cell.W_r.bias, cell.W_h.bias]).detach().requires_grad_(True)
+    out = sg2_bilevel.gru(x, h, W, b)
+    gx, gW, gb = torch.autograd.grad((out * gout).sum(), [x, W, b])
+    assert torch.allclose(out, ref, rtol=1e-5, atol=1e-6)
+    assert torch.allclose(gx, rg[0], rtol=1e-4, atol=1e-6)
+    for k, (wr, br) in enumerate(((rg[1], rg[2]), (rg[3], rg[4]), (rg[5], rg[6]))):      # parameters() order: W_z, W_r, W_h (weight, bias)
+        assert torch.allclose(gW[k], wr, rtol=1e-4, atol=1e-5 * float(wr.abs().max())), k
+        assert torch.allclose(gb[k], br, rtol=1e-4, atol=1e-5 * float(br.abs().max())), k
+
+
+def test_soft_head_with_native_tail_matches_torch_tail(monkeypatch):
     from supergrok15_b200 import _build
     if not _build.native_available():
         pytest.skip("native extension not built")
@@ -464,13 +493,13 @@ def test_soft_head_with_native_routing_matches_torch_routing(monkeypatch):
     gru, vu = torch.randn(n, mn.gru_hidden) * 0.1, torch.randn(n)
     ctx = (torch.randn(n, 16) * 0.1).requires_grad_(True)
     res = {}
-    for mode in ("torch", "kernel"):
-        monkeypatch.setenv("SG_BILEVEL_ROUTING", mode)
+    for mode in ("torch", "native"):                             # native: GRU and routing through their C++ / CUDA implementations
+        monkeypatch.setenv("SG_BILEVEL_TAIL", mode)
         mn.zero_grad(set_to_none=True)
         ctx.grad = None
         (mn.soft_head(g, s, gru, ctx[:, :8], ctx[:, 8:]) * vu).sum().backward()
         res[mode] = (ctx.grad.clone(), {k: p.grad.clone() for k, p in mn.named_parameters() if p.grad is not None})
-    assert torch.allclose(res["kernel"][0], res["torch"][0], rtol=1e-3, atol=1e-7)
-    assert set(res["kernel"][1]) == set(res["torch"][1])
+    assert torch.allclose(res["native"][0], res["torch"][0], rtol=1e-3, atol=1e-7)
+    assert set(res["native"][1]) == set(res["torch"][1])
     for k, gt in res["torch"][1].items():
-        assert (res["kernel"][1][k] - gt).abs().max() <= 1e-3 * gt.abs().max() + 1e-9, k
+        assert (res["native"][1][k] - gt).abs().max() <= 1e-3 * gt.abs().max() + 1e-9, k

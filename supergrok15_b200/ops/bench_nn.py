@@ -4,6 +4,7 @@
     python -m supergrok15_b200.ops.bench_nn --what ce               # fused cross-entropy fwd / bwd vs F.cross_entropy
     python -m supergrok15_b200.ops.bench_nn --what norm             # RMSNorm with fused residual vs F.rms_norm(x + r)
     python -m supergrok15_b200.ops.bench_nn --what linear           # tcgen05 Linear (forward, dgrad, wgrad) vs cuBLAS on the flagship's layer shapes
+    ... --what linear --kernels                                      # plus the device time of every kernel of one autograd call
     ... --small                                                      # one modest shape, few iterations (profiler captures)
 
 Timing: CUDA events on the launching stream after warm-up; every shape's working set exceeds the 126 MB L2 except with --small.
@@ -128,18 +129,33 @@ def bench_linear(small: bool, it: int):
             return f
         r["autograd_us"] = 1e3 * run(auto(gemm.linear))
         r["cublas_autograd_us"] = 1e3 * run(auto(F.linear))
+        if KERNELS:                                                  # device time of every kernel of one forward + backward of the layer
+            from torch.profiler import ProfilerActivity, profile
+            fn = auto(gemm.linear)
+            with profile(activities=[ProfilerActivity.CUDA]) as prof:
+                for _ in range(3):
+                    fn(*nxt())
+                torch.cuda.synchronize()
+            rows = sorted((e for e in prof.key_averages() if e.device_time_total > 0), key=lambda e: -e.device_time_total)
+            r["autograd_kernels_us"] = [[e.key[:60], round(e.device_time_total / 3, 1), e.count // 3] for e in rows[:10]]
         gemm.check(dev)
         fl = 2.0 * T * din * dout
         r["fwd_tflops"], r["dgrad_tflops"], r["wgrad_tflops"] = (fl / r[k_] / 1e6 for k_ in ("fwd_us", "dgrad_us", "wgrad_us"))
         print(json.dumps({k_: (round(v, 1) if isinstance(v, float) else v) for k_, v in r.items()}), flush=True)
 
 
+KERNELS = False
+
+
 def main():
+    global KERNELS
     ap = argparse.ArgumentParser()
+    ap.add_argument("--kernels", action="store_true", help="linear: also list the device time of every kernel of one autograd call (torch.profiler)")
     ap.add_argument("--what", default="flash", choices=["flash", "ce", "norm", "linear", "all"])
     ap.add_argument("--small", action="store_true")
     ap.add_argument("--iters", type=int, default=None)
     a = ap.parse_args()
+    KERNELS = a.kernels
     it = a.iters or (2 if a.small else 20)
     for name, fn in (("flash", bench_flash), ("ce", bench_ce), ("norm", bench_norm), ("linear", bench_linear)):
         if a.what in (name, "all"):

@@ -18,14 +18,18 @@ __device__ __forceinline__ void stage(float* sm, const float* __restrict__ W, co
     for (int i = threadIdx.x; i < 3 * GH; i += GT) sm[nw + i] = b[i];
 }
 
+// CIN > 0: the input width is a compile-time constant (loops unroll, the per-element arrays stay in registers); 0: run-time width
+template <int CIN>
 __global__ void __launch_bounds__(GT) gru_fwd_kernel(const float* __restrict__ x, const float* __restrict__ h, const float* __restrict__ W,
-                                                     const float* __restrict__ b, int64_t n, int IN, float* __restrict__ hn) {
+                                                     const float* __restrict__ b, int64_t n, int IN_rt, float* __restrict__ hn) {
+    const int IN = CIN > 0 ? CIN : IN_rt;
     extern __shared__ float sm[];
     stage(sm, W, b, IN);
     __syncthreads();
     const int64_t e = (int64_t)blockIdx.x * GT + threadIdx.x;
     if (e >= n) return;
-    float xv[GIN_MAX], hv[GH], z[GH], r[GH], c[GH], o[GH];
+    float xv[CIN > 0 ? CIN : GIN_MAX], hv[GH], z[GH], r[GH], c[GH], o[GH];
+#pragma unroll
     for (int j = 0; j < IN; ++j) xv[j] = x[e * IN + j];
     const float4 h4 = *reinterpret_cast<const float4*>(h + e * GH);
     hv[0] = h4.x; hv[1] = h4.y; hv[2] = h4.z; hv[3] = h4.w;
@@ -34,9 +38,11 @@ __global__ void __launch_bounds__(GT) gru_fwd_kernel(const float* __restrict__ x
 }
 
 // partial: [gridDim.x, 3*GH*(IN+GH) + 3*GH]   (d W | d b)
+template <int CIN>
 __global__ void __launch_bounds__(GT) gru_bwd_kernel(const float* __restrict__ x, const float* __restrict__ h, const float* __restrict__ W,
-                                                     const float* __restrict__ b, const float* __restrict__ dhn, int64_t n, int IN,
+                                                     const float* __restrict__ b, const float* __restrict__ dhn, int64_t n, int IN_rt,
                                                      float* __restrict__ dx, float* __restrict__ partial) {
+    const int IN = CIN > 0 ? CIN : IN_rt;
     extern __shared__ float sm[];
     const int P = IN + GH, nw = 3 * GH * P, ng = nw + 3 * GH;
     const int pitch = IN + 2 * GH + 3 * GH + 1;                  // x | h | r*h | dpre, odd pitch
@@ -52,14 +58,17 @@ __global__ void __launch_bounds__(GT) gru_bwd_kernel(const float* __restrict__ x
         const int64_t left = n - tile * GT;
         const int cnt = left < GT ? (int)left : GT;
         if (e < n) {
-            float xv[GIN_MAX], hv[GH], dh[GH], dpre[3 * GH], rh[GH], dxv[GIN_MAX];
+            float xv[CIN > 0 ? CIN : GIN_MAX], hv[GH], dh[GH], dpre[3 * GH], rh[GH], dxv[CIN > 0 ? CIN : GIN_MAX];
+#pragma unroll
             for (int j = 0; j < IN; ++j) xv[j] = x[e * IN + j];
             const float4 h4 = *reinterpret_cast<const float4*>(h + e * GH), d4 = *reinterpret_cast<const float4*>(dhn + e * GH);
             hv[0] = h4.x; hv[1] = h4.y; hv[2] = h4.z; hv[3] = h4.w;
             dh[0] = d4.x; dh[1] = d4.y; dh[2] = d4.z; dh[3] = d4.w;
             gru_adjoint(xv, hv, IN, sm, sm + nw, dh, dpre, rh, dxv);
+#pragma unroll
             for (int j = 0; j < IN; ++j) dx[e * IN + j] = dxv[j];
             float* row = s_el + threadIdx.x * pitch;
+#pragma unroll
             for (int j = 0; j < IN; ++j) row[j] = xv[j];
 #pragma unroll
             for (int j = 0; j < GH; ++j) { row[IN + j] = hv[j]; row[IN + GH + j] = rh[j]; }
@@ -110,7 +119,10 @@ int gru_bwd_ctas(int64_t n) {
 int gru_fwd(const float* x, const float* h, const float* W, const float* b, int64_t n, int IN, float* hn, cudaStream_t s) {
     if (n <= 0) return 0;
     count_launch();
-    gru_fwd_kernel<<<(unsigned)((n + GT - 1) / GT), GT, (size_t)gru_ng(IN) * sizeof(float), s>>>(x, h, W, b, n, IN, hn);
+    const unsigned grid = (unsigned)((n + GT - 1) / GT);
+    const size_t smem = (size_t)gru_ng(IN) * sizeof(float);
+    if (IN == 18) gru_fwd_kernel<18><<<grid, GT, smem, s>>>(x, h, W, b, n, IN, hn);          // 2 + 2 * d_model of the default meta-net
+    else gru_fwd_kernel<0><<<grid, GT, smem, s>>>(x, h, W, b, n, IN, hn);
     return cudaGetLastError() == cudaSuccess ? 0 : 3;
 }
 
@@ -119,10 +131,11 @@ int gru_bwd(const float* x, const float* h, const float* W, const float* b, cons
     const int ng = gru_ng(IN);
     if (n <= 0) return cudaMemsetAsync(dparams, 0, (size_t)ng * sizeof(float), s) == cudaSuccess ? 0 : 3;
     const size_t smem = (size_t)(ng + GT * (IN + 5 * gru::GH + 1)) * sizeof(float);
-    if (cudaFuncSetAttribute(gru_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return 2;
+    // the adjoint keeps the run-time width: fully unrolled for 18 inputs it needs 255 registers and spills (-Xptxas -v)
+    if (cudaFuncSetAttribute(gru_bwd_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return 2;
     const int ctas = gru_bwd_ctas(n);
     count_launch(2);
-    gru_bwd_kernel<<<ctas, GT, smem, s>>>(x, h, W, b, dhn, n, IN, dx, partial);
+    gru_bwd_kernel<0><<<ctas, GT, smem, s>>>(x, h, W, b, dhn, n, IN, dx, partial);
     gru_reduce_kernel<<<(ng + 255) / 256, 256, 0, s>>>(partial, ctas, ng, dparams);
     return cudaGetLastError() == cudaSuccess ? 0 : 3;
 }

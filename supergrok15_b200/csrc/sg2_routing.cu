@@ -31,10 +31,13 @@ __device__ __forceinline__ RWeights stage_weights(float* sm, const float* __rest
 }
 __host__ __device__ inline int weights_floats(int heads, int P, int pk) { return heads * RD * P + 2 * heads * pk * RH; }
 
+// CP / CPK > 0: input width and key rows are compile-time constants (loops unroll, the per-element arrays stay in registers)
+template <int CP, int CPK>
 __global__ void __launch_bounds__(RT) routing_fwd_kernel(const float* __restrict__ pin, const float* __restrict__ Wq, const float* __restrict__ KA,
-                                                         const float* __restrict__ KB, int64_t n, int heads, int P, int pk,
+                                                         const float* __restrict__ KB, int64_t n, int heads, int P_rt, int pk_rt,
                                                          int4* __restrict__ ia, int4* __restrict__ ib, float4* __restrict__ wa,
                                                          float4* __restrict__ wb) {
+    const int P = CP > 0 ? CP : P_rt, pk = CPK > 0 ? CPK : pk_rt;
     extern __shared__ float sm[];
     const RWeights w = stage_weights(sm, Wq, KA, KB, heads, P, pk);
     __syncthreads();
@@ -42,8 +45,9 @@ __global__ void __launch_bounds__(RT) routing_fwd_kernel(const float* __restrict
     const int le = threadIdx.x / heads, h = threadIdx.x % heads;
     const int64_t elem = (int64_t)blockIdx.x * epc + le;
     if (le >= epc || elem >= n) return;
-    float x[RP_MAX], q[RD], a_w[RK], b_w[RK];
+    float x[CP > 0 ? CP : RP_MAX], q[RD], a_w[RK], b_w[RK];
     int a_i[RK], b_i[RK];
+#pragma unroll
     for (int j = 0; j < P; ++j) x[j] = pin[elem * P + j];
     route_fwd(x, P, w.wq + h * RD * P, w.ka + h * pk * RH, w.kb + h * pk * RH, pk, q, a_i, b_i, a_w, b_w);
     const int64_t r = elem * heads + h;
@@ -174,10 +178,15 @@ int routing_fwd(const float* pin, const float* Wq, const float* KA, const float*
                 float* wa, float* wb, cudaStream_t s) {
     if (n <= 0) return 0;
     const size_t smem = fwd_smem(heads, P, pk);
-    if (cudaFuncSetAttribute(routing_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return 2;
+    if (cudaFuncSetAttribute(routing_fwd_kernel<22, 12>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess ||
+        cudaFuncSetAttribute(routing_fwd_kernel<0, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return 2;
     const int epc = RT / heads;
+    const unsigned grid = (unsigned)((n + epc - 1) / epc);
     count_launch();
-    routing_fwd_kernel<<<(unsigned)((n + epc - 1) / epc), RT, smem, s>>>(pin, Wq, KA, KB, n, heads, P, pk, (int4*)ia, (int4*)ib, (float4*)wa, (float4*)wb);
+    if (P == 22 && pk == 12)                                          // the default meta-net: gru 4 + 2 * d_model 16 + 2 inputs, 144 experts
+        routing_fwd_kernel<22, 12><<<grid, RT, smem, s>>>(pin, Wq, KA, KB, n, heads, P, pk, (int4*)ia, (int4*)ib, (float4*)wa, (float4*)wb);
+    else
+        routing_fwd_kernel<0, 0><<<grid, RT, smem, s>>>(pin, Wq, KA, KB, n, heads, P, pk, (int4*)ia, (int4*)ib, (float4*)wa, (float4*)wb);
     return cudaGetLastError() == cudaSuccess ? 0 : 3;
 }
 

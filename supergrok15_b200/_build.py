@@ -99,7 +99,8 @@ def build(force: bool = False, verbose: bool = False) -> Path:
             cmd = [nvcc, *NVCC_ARCH, "-O3", "-lineinfo", "-std=c++17", "--expt-relaxed-constexpr", "-Xcompiler",
                    "-fPIC", "-Xptxas", "-v" if verbose else "-warn-spills", *inc, "-c", str(src), "-o", str(obj)]
         else:
-            cmd = ["g++", "-O2", "-std=c++17", "-fPIC", "-DTORCH_EXTENSION_NAME=" + _NAME,
+            # -fopenmp: at::parallel_for is a header template around "#pragma omp parallel"; without the flag it runs serially
+            cmd = ["g++", "-O2", "-std=c++17", "-fPIC", "-fopenmp", "-DTORCH_EXTENSION_NAME=" + _NAME,
                    "-DTORCH_API_INCLUDE_EXTENSION_H", "-D_GLIBCXX_USE_CXX11_ABI=" + str(int(torch._C._GLIBCXX_USE_CXX11_ABI)),
                    *inc, *torch_inc, "-c", str(src), "-o", str(obj)]
         jobs.append((src.name, key, cmd))
@@ -112,7 +113,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     so = _so_path()
     if jobs or not so.exists():
         tlib = Path(torch.__file__).parent / "lib"
-        cmd = ["g++", "-shared", "-o", str(so), *map(str, objs), f"-L{tlib}", f"-L{cuda_home}/lib64", "-lc10",
+        cmd = ["g++", "-shared", "-fopenmp", "-o", str(so), *map(str, objs), f"-L{tlib}", f"-L{cuda_home}/lib64", "-lc10",
                "-ltorch_cpu", "-ltorch", "-ltorch_python", "-lc10_cuda", "-ltorch_cuda", "-lcudart",
                f"-Wl,-rpath,{tlib}", f"-Wl,-rpath,{cuda_home}/lib64"]
         _run(cmd)
@@ -139,14 +140,14 @@ def build_sanitized(out_dir) -> Path:
             continue
         obj = out_dir / (src.name + ".san.o")
         objs.append(obj)
-        jobs.append(["g++", "-O1", "-g", "-std=c++17", "-fPIC", "-fsanitize=address,undefined", "-fno-omit-frame-pointer", "-Wall", "-Werror",
+        jobs.append(["g++", "-O1", "-g", "-std=c++17", "-fPIC", "-fopenmp", "-fsanitize=address,undefined", "-fno-omit-frame-pointer", "-Wall", "-Werror",
                      "-DTORCH_EXTENSION_NAME=" + _NAME, "-DTORCH_API_INCLUDE_EXTENSION_H",
                      "-D_GLIBCXX_USE_CXX11_ABI=" + str(int(torch._C._GLIBCXX_USE_CXX11_ABI)), *inc, "-c", str(src), "-o", str(obj)])
     with ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:
         list(ex.map(_run, jobs))
     so = out_dir / _so_path().name
     tlib = Path(torch.__file__).parent / "lib"
-    _run(["g++", "-shared", "-fsanitize=address,undefined", "-o", str(so), *map(str, objs), f"-L{tlib}", f"-L{cuda_home}/lib64", "-lc10",
+    _run(["g++", "-shared", "-fopenmp", "-fsanitize=address,undefined", "-o", str(so), *map(str, objs), f"-L{tlib}", f"-L{cuda_home}/lib64", "-lc10",
           "-ltorch_cpu", "-ltorch", "-ltorch_python", "-lc10_cuda", "-ltorch_cuda", "-lcudart", f"-Wl,-rpath,{tlib}",
           f"-Wl,-rpath,{cuda_home}/lib64"])
     return so

@@ -25,12 +25,6 @@ inline float lion_update(float p, float g, float& m, float lr, float b1, float b
     m = b2 * m + (1.f - b2) * g;
     return p - lr * (s + wd * p);
 }
-inline float amp_mlp(float g, const float* W1, const float* b1, const float* W2, float b2, int H) {
-    float acc = b2;
-    for (int h = 0; h < H; ++h) acc = std::fma(W2[h], std::fmax(std::fma(W1[h], g, b1[h]), 0.f), acc);
-    return acc;
-}
-
 // ---- the sharpness MLP over a block of elements -------------------------------------------------------------------------------
 // Per element the MLP costs `hidden` exponentials; element by element through std::exp that is most of a CPU step of SuperGrok
 // v1.5 / v1.1.  Here the hidden units are the outer loop and a block of elements the inner one, with a polynomial exponential
@@ -69,6 +63,17 @@ void sharp_mlp_block(const float* __restrict__ g, const float* __restrict__ s, i
             const float z = w0 * g[b] + (w1 * s[b] + bb);
             out[b] += w2 * (z / (1.f + poly_expf(-1.702f * z)));
         }
+    }
+}
+
+// the NeuralGrok amplifier (1 -> hidden -> 1, ReLU) over a block of elements, same scheme
+__attribute__((target_clones("avx2", "default"), optimize("O3", "no-trapping-math", "no-math-errno", "finite-math-only")))
+void amp_mlp_block(const float* __restrict__ g, int nb, const float* __restrict__ W1, const float* __restrict__ b1, const float* __restrict__ W2,
+                   float b2, int H, float* __restrict__ out) {
+    for (int b = 0; b < nb; ++b) out[b] = b2;
+    for (int h = 0; h < H; ++h) {
+        const float w1 = W1[h], bb = b1[h], w2 = W2[h];
+        for (int b = 0; b < nb; ++b) out[b] += w2 * __builtin_fmaxf(w1 * g[b] + bb, 0.f);
     }
 }
 
@@ -115,6 +120,22 @@ void run_chunk(int op, float* const P[6], const float ts[4], const Prm& q, int t
         acc[0] = a0; acc[1] = a1; acc[2] = a2;
         return;
     }
+    if (op == OP_NEURALGROK) {
+        float gb[MLP_BLOCK], out[MLP_BLOCK];
+        for (int64_t i0 = lo; i0 < hi; i0 += MLP_BLOCK) {
+            const int nb = (int)(hi - i0 < MLP_BLOCK ? hi - i0 : MLP_BLOCK);
+            for (int b = 0; b < nb; ++b) gb[b] = P1[i0 + b] * clip;
+            amp_mlp_block(gb, nb, q.W1, q.b1, q.W2, b2s, H, out);
+            for (int b = 0; b < nb; ++b) {
+                const int64_t i = i0 + b;
+                const float ag = gb[b] * (q.alpha * out[b] + q.rescale);
+                P0[i] = adam_update(P0[i], ag, P2[i], P3[i], lr, b1, b2, eps, wd, ts[0], ts[1]);
+                if (q.write_grad) P1[i] = gb[b];
+            }
+        }
+        acc[0] = acc[1] = acc[2] = 0.f;
+        return;
+    }
     for (int64_t i = lo; i < hi; ++i) {
         switch (op) {
             case OP_ADAMW: P0[i] = adam_update(P0[i], P1[i] * clip, P2[i], P3[i], lr, b1, b2, eps, wd, ts[0], ts[1]); break;
@@ -134,13 +155,6 @@ void run_chunk(int op, float* const P[6], const float ts[4], const Prm& q, int t
                 P2[i] = b1 * P2[i] + (1.f - b1) * dg;
                 P3[i] = b2 * P3[i] + (1.f - b2) * dg * dg;
                 P0[i] = P0[i] * (1.f - lr * d * wd) - (lr / ts[0]) * P2[i] / (std::sqrt(P3[i] / ts[1]) + d * eps);
-                break;
-            }
-            case OP_NEURALGROK: {
-                const float g = P1[i] * clip;
-                const float ag = g * (q.alpha * amp_mlp(g, q.W1, q.b1, q.W2, b2s, H) + q.rescale);
-                P0[i] = adam_update(P0[i], ag, P2[i], P3[i], lr, b1, b2, eps, wd, ts[0], ts[1]);
-                if (q.write_grad) P1[i] = g;
                 break;
             }
             case OP_SG11_B: P0[i] = adam_update(P0[i], P1[i] + q.tscal[t_global] * P4[i], P2[i], P3[i], lr, ts[0], b2, eps, wd, ts[1], ts[2]); break;

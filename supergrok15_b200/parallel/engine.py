@@ -82,6 +82,10 @@ class ZeroEngine:
         numels = [p.numel() for p in self.params]
         self.flat_mode = optimizer in FLAT_OPTIMIZERS
         self.overlap = bool(overlap) and self.flat_mode                  # bucket-by-bucket overlap of the sharded step with backward
+        if overlap and not self.flat_mode:
+            import warnings
+            warnings.warn(f"overlap=True is implemented for the flat optimizers ({', '.join(FLAT_OPTIMIZERS)}); '{optimizer}' needs "
+                          "global scalars or whole tensors before its first update and runs its step after backward")
         self.buckets: List[dict] = []
         # ---- layout of the flat parameter / gradient buffers
         if self.flat_mode:

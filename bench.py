@@ -33,6 +33,9 @@ NL, D, H = 6, 512, 8
 GLOBAL_BATCH = 8192
 NTOK = P_MOD + 2
 BASELINE_VALUE = None          # the reference publishes no throughput number
+# identical in both arms; what differs between the arms is reported under "arm"
+CONFIG = {"model": "6-layer post-LN decoder d512 h8 mlp2048 (19.0M params)", "global_batch": GLOBAL_BATCH, "seq_len": SEQ,
+          "l2": "per-step working set (optimizer state + sort/scan workspace, > 1 GB per rank) exceeds the 126 MB L2"}
 
 
 def dist_setup(n):
@@ -163,6 +166,67 @@ def wall_loop(step_fn, K, world):
 
 
 # ------------------------------------------------------------------------------------------------ this framework
+def correctness_probe(rank, world, local, comm):
+    """Sharded == unsharded on a small fp32 problem at this world size (outside every timed region): two steps of the engine
+    (one rank per GPU, in-kernel collectives, each rank a slice of a 64-row batch) against two steps of the plain
+    optimizer on the whole batch in one process.  Returns the largest absolute parameter difference and whether every rank
+    ends with bitwise identical parameters."""
+    import torch
+    import torch.distributed as dist
+    import torch.nn.functional as F
+    from supergrok15_b200 import optim as O
+    from supergrok15_b200.models import Transformer
+    from supergrok15_b200.parallel import ZeroEngine
+    dev = torch.device("cuda", local)
+    kw = dict(warmup_steps=0, warmup_ramp=1, eps=1e-3)
+
+    def problem():
+        torch.manual_seed(0)
+        m = Transformer(1, 32, 2).to(dev)
+        g = torch.Generator().manual_seed(5)
+        return m, torch.randint(0, 97, (64, 4), generator=g).to(dev), torch.randint(0, 97, (64,), generator=g).to(dev)
+    m, x, y = problem()
+    eng = ZeroEngine(m, "supergrok2", kw, comm=comm, param_dtype=torch.float32, graph=False)
+    per = 64 // world
+    for _ in range(2):
+        eng.train_step(x[rank * per:(rank + 1) * per], y[rank * per:(rank + 1) * per])
+    eng.check()
+    flat = torch.cat([p.detach().float().reshape(-1) for p in eng.params])
+    m2, x2, y2 = problem()
+    opt = O.SuperGrok2(m2.parameters(), **kw)
+    for _ in range(2):
+        opt.zero_grad()
+        F.cross_entropy(m2(x2), y2).backward()
+        opt.step()
+    ref = torch.cat([p.detach().float().reshape(-1) for p in m2.parameters()])
+    diff = (flat - ref).abs().max()
+    lo, hi = flat.clone(), flat.clone()
+    if world > 1:
+        dist.all_reduce(diff, op=dist.ReduceOp.MAX)
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+    return {"what": "2 steps of ZeRO SuperGrok v2 on a 1-layer d32 fp32 decoder, 64 rows split over the ranks, vs the unsharded "
+                    "optimizer on the whole batch in one process", "max_abs_param_diff": float(diff),
+            "ref_abs_max": float(ref.abs().max()), "replicas_bitwise_equal": bool(torch.equal(lo, hi))}
+
+
+def median(v):
+    v = sorted(v)
+    return v[len(v) // 2]
+
+
+def phase_times(eng, batch, world, n=3):
+    """Per-phase device times of a step (CUDA events, median of n eager steps, max over ranks)."""
+    import torch
+    import torch.distributed as dist
+    runs = [eng.profile_step(*batch) for _ in range(n)]
+    keys = list(runs[0])
+    t = torch.tensor([median([r[k] for r in runs]) for k in keys], device="cuda")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return {k: round(v, 4) for k, v in zip(keys, t.tolist())}
+
+
 def run_ours(args, rank, world, local):
     import torch
     from supergrok15_b200 import _build
@@ -183,6 +247,7 @@ def run_ours(args, rank, world, local):
     # its first calls of a batch shape eagerly, then captures), so that neither falls into the warm-up or the timed region
     for i in range(eng.graph_warmup + 2):
         eng.train_step(*dev_batches[i % len(dev_batches)])
+    probe = correctness_probe(rank, world, local, args.comm)
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()                                  # query loop up and running before the warm-up ends
@@ -190,33 +255,54 @@ def run_ours(args, rank, world, local):
         eng.train_step(*dev_batches[i])
     eng.check()
     C = _build.require()
-    l0 = C.launch_count()
+    R = max(1, args.repeats)
     sampler.mark_begin()
-    ms = timed_loop(lambda i: eng.train_step(*dev_batches[W + i]), K, world)
-    launches_region = C.launch_count() - l0          # kernels of this package enqueued inside the timed region
+    l0 = C.launch_count()
+    ms_runs = [timed_loop(lambda i: eng.train_step(*dev_batches[W + i]), K, world) for _ in range(R)]
+    launches_region = (C.launch_count() - l0) // R    # kernels of this package enqueued inside one timed region of K steps
+    ms = median(ms_runs)
     losses = []
 
     def e2e_step(i):
         x, y = host[W + K + i]
         losses.append(float(eng.train_step(x, y).item()))       # H2D of the batch, D2H of the loss, every step
-    e2e_ms = wall_loop(e2e_step, K, world)
+    e2e_ms = median([wall_loop(e2e_step, K, world) for _ in range(R)])
     clocks = sampler.stop() if rank == 0 else None
     eng.check()
+    phases = phase_times(eng, dev_batches[W], world)
+    eng.check()
+    # every rank must hold bitwise identical bf16 parameters after the run (the all-gather is part of the step)
+    import torch.distributed as dist
+    pb = eng.pbuf.tensor.view(torch.int16).to(torch.int32)
+    lo, hi = pb.clone(), pb.clone()
+    if world > 1:
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+    probe["flagship_replicas_bitwise_equal"] = bool(torch.equal(lo, hi))
     tokens = GLOBAL_BATCH * SEQ
-    gpu_launches = launches_region
+    # roofline of the two phases that cross NVLink: each rank pulls its tensors' gradients from W-1 peers and pushes its updated
+    # parameters to W-1 peers; every link direction carries both one rank's pulls and another rank's pushes
+    from supergrok15_b200.utils import roofline
+    link_bytes = 2 * (world - 1) * eng.n_own * 2
+    fr = {}
+    if world > 1:
+        fr["reduce+prep"] = roofline.fraction(phases.get("reduce+prep", 0.0), nvlink_bytes=link_bytes / 2, hbm_bytes=eng.n_own * 22)
+        fr["elem+push"] = roofline.fraction(phases.get("elem+push", 0.0), nvlink_bytes=link_bytes / 2, hbm_bytes=eng.n_own * 130)
     return {
         "metric": "train tokens/s (max over ranks), ZeRO-2 SuperGrok v2", "value": tokens / (ms * 1e-3), "unit": "tokens/s",
         "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": (tokens / (ms * 1e-3) / BASELINE_VALUE) if BASELINE_VALUE else None, "dtype": "bf16",
         "data": "synthetic: seeded batches drawn from the mod-113 division train split; random-init weights",
-        "config": {"model": "6-layer post-LN decoder d512 h8 mlp2048 (19.0M params)", "global_batch": GLOBAL_BATCH, "seq_len": SEQ,
-                   "parallelism": f"zero2-dp{world}", "optimizer": "SuperGrok v2 (fp32 master, bf16 model)", "comm": eng.comm,
-                   "l2": "per-step working set (optimizer state + sort/scan workspace, > 1 GB per rank) exceeds the 126 MB L2"},
+        "config": dict(CONFIG, parallelism=f"dp{world}"),
+        "arm": {"parallelism": f"zero2-dp{world}", "optimizer": "SuperGrok v2 (fp32 master, bf16 model)", "comm": eng.comm,
+                "whole_step_cuda_graph": bool(eng.use_graph and eng.device_step)},
+        "repeats": R, "ms_per_step_runs": [round(m, 4) for m in ms_runs],
         "clocks": clocks,
         "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": per_rank * SEQ * 8 + per_rank * 8, "d2h_bytes_per_step": 4,
                 "api": "supergrok15_b200.parallel.ZeroEngine.train_step(pinned_x, pinned_y).item()"},
-        "gpu_launches": gpu_launches, "final_loss": losses[-1] if losses else None, "impl": "ours",
+        "gpu_launches": launches_region, "phases_ms": phases, "phase_roofline": fr, "correctness": probe,
+        "final_loss": losses[-1] if losses else None, "impl": "ours",
     }
 
 
@@ -341,10 +427,9 @@ def run_reference(args, rank, world, local):
         "metric": "train tokens/s (max over ranks), ZeRO-2 SuperGrok v2", "value": tokens / (ms * 1e-3), "unit": "tokens/s",
         "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic: seeded batches drawn from the mod-113 division train split; random-init weights",
-        "config": {"model": "6-layer post-LN decoder d512 h8 mlp2048 (19.0M params)", "global_batch": GLOBAL_BATCH, "seq_len": SEQ,
-                   "parallelism": f"ddp{world} (the reference has no sharding; replicated optimizer)",
-                   "optimizer": "reference SuperGrok2, fp32 parameters, bf16 autocast",
-                   "l2": "per-step working set exceeds the 126 MB L2"},
+        "config": dict(CONFIG, parallelism=f"dp{world}"),
+        "arm": {"parallelism": f"ddp{world} (the reference has no sharding; replicated optimizer)",
+                "optimizer": "reference SuperGrok2, fp32 parameters, bf16 autocast"},
         "clocks": clocks,
         "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": per_rank * SEQ * 8 + per_rank * 8, "d2h_bytes_per_step": 4},
@@ -358,6 +443,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--repeats", type=int, default=5, help="the K-step timed loop is run this many times; the median is reported")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--comm", default=None, choices=[None, "p2p", "nvls", "nccl"])
     ap.add_argument("--config", default="zero2_sg2", choices=["zero2_sg2", "llama_muon"])

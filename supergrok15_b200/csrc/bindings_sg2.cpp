@@ -1,4 +1,5 @@
 // Bindings of the SuperGrok v2 step pipeline (sort, scan, element step).
+#include <cstring>
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
 #include "bindings_decl.h"
@@ -9,11 +10,15 @@
 namespace sg {
 void sg2_upload_weights(const float* packed_dev, cudaStream_t s);
 void sg2_sqnorm(int dtype, const MTArgs& a, float* partials, cudaStream_t s);
-void sg2_prep(int dtype, const MTArgs& a, const float* tclip, float* g_packed, float* s_packed, uint32_t* keys, uint32_t* vals, cudaStream_t s);
+void sg2_prep(int dtype, bool packed_src, const MTArgs& a, const float* tclip, float* g_packed, float* s_packed, uint32_t* keys, uint32_t* vals,
+              cudaStream_t s);
+void sg2_pull_sqnorm(int dtype, const MTArgs& a, const PeerPtrs& bases, int world, int rank, void* local_base, float scale, float* g_packed,
+                     float* partials, cudaStream_t s);
 void sg2_gather(const uint32_t* vals_sorted, const float* g_packed, const float* s_packed, float* gs_sorted, int64_t total, cudaStream_t s);
 void sg2_scan(const void* items_dev, int n_items, int dir1_start, const void* tds_dev, int n_td, bool any_multi, const float* gs_sorted,
-              const uint32_t* vals_sorted, float* agg, float* carry, float* ctx, cudaStream_t s);
-void sg2_elem(int dtype, const MTArgs& a, float beta2, float lr, float wd_eff, float eps, float rescale, float lamb_eff, const float* g_packed,
+              const uint32_t* vals_sorted, float* agg, float* carry, float* ctx, const int* status, cudaStream_t s);
+void sg2_elem(int dtype, const MTArgs& a, float beta2, float eps, float rescale, const float* dyn, const float* w_global, const int* status,
+              const float* g_packed,
               const float* s_packed, const float* ctx, int* expert_counts, int n_peers, void* local_base, void* const* peer_base,
               cudaStream_t s);
 size_t sg2_item_bytes();
@@ -67,9 +72,12 @@ using TL = std::vector<Tensor>;
 
 uint32_t* u32(const Tensor& t) { return reinterpret_cast<uint32_t*>(t.data_ptr()); }
 
-// ws: dict of workspace tensors allocated by the caller (see ops/sg2.py for the sizes)
+// ws: dict of workspace tensors allocated by the caller (see ops/sg2.py for the sizes).
+// pull_bases (optional): base address of every rank's gradient buffer; `grads` are then this rank's tensors inside its own buffer
+// (base pull_bases[pull_rank]) and the first kernel reduces the W copies itself (reduce-scatter fused into the pipeline).
+// stage: 0 = everything, 1 = norm + clip + keys only, 2 = sort + gather only (per-phase timing).
 int64_t sg2_prepare(const TL& grads, const TL& sharps, const std::vector<int64_t>& offsets, int64_t total, Tensor seg_off, double clip,
-                    py::dict ws) {
+                    py::dict ws, const std::vector<int64_t>& pull_bases, int64_t pull_rank, double pull_scale, int64_t stage) {
     TORCH_CHECK(!grads.empty(), "no gradients");
     c10::cuda::CUDAGuard guard(grads[0].device());
     cudaStream_t st = at::cuda::getCurrentCUDAStream();
@@ -78,14 +86,35 @@ int64_t sg2_prepare(const TL& grads, const TL& sharps, const std::vector<int64_t
     Tensor partials = W("partials"), tnorm = W("tnorm"), tclip = W("tclip"), g = W("g"), s = W("s");
     Tensor k0 = W("keys0"), k1 = W("keys1"), v0 = W("vals0"), v1 = W("vals1"), hist = W("hist"), tot = W("tot"), gs = W("gs");
     const int n = (int)grads.size();
-    for_each_launch({{}, grads}, {}, nullptr, [&](sg::MTArgs& a) {
-        sg::sg2_sqnorm(dt, a, partials.data_ptr<float>(), st);
-        sg::mt_finalize_per_tensor(a, partials.data_ptr<float>(), tnorm.data_ptr<float>(), st);
-    });
-    sg::scalar_finalize(sg::SC_SG2_CLIP, tnorm.data_ptr<float>(), n, tclip.data_ptr<float>(), (float)clip, 0.f, 0.f, st);
-    for_each_launch({{}, grads, sharps}, {}, &offsets, [&](sg::MTArgs& a) {
-        sg::sg2_prep(dt, a, tclip.data_ptr<float>(), g.data_ptr<float>(), s.data_ptr<float>(), u32(k0), u32(v0), st);
-    });
+    const bool pull = !pull_bases.empty();
+    if (stage != 2) {
+        if (pull) {
+            TORCH_CHECK(pull_bases.size() <= (size_t)sg::MAX_RANKS && pull_rank >= 0 && pull_rank < (int64_t)pull_bases.size(), "bad peer table");
+            sg::PeerPtrs bases{};
+            for (size_t r = 0; r < pull_bases.size(); ++r) bases.p[r] = reinterpret_cast<void*>(static_cast<intptr_t>(pull_bases[r]));
+            const int64_t esz = grads[0].element_size();
+            for (const Tensor& t : grads) {
+                const int64_t d = reinterpret_cast<char*>(t.data_ptr()) - reinterpret_cast<char*>(bases.p[pull_rank]);
+                TORCH_CHECK(d >= 0 && d % 16 == 0 && (int)dtype_code(t) == dt && t.element_size() == esz,
+                            "pulled gradients must be 16-byte aligned slices of this rank's gradient buffer, all of one dtype");
+            }
+            for_each_launch({{}, grads}, {}, &offsets, [&](sg::MTArgs& a) {
+                sg::sg2_pull_sqnorm(dt, a, bases, (int)pull_bases.size(), (int)pull_rank, bases.p[pull_rank], (float)pull_scale,
+                                    g.data_ptr<float>(), partials.data_ptr<float>(), st);
+                sg::mt_finalize_per_tensor(a, partials.data_ptr<float>(), tnorm.data_ptr<float>(), st);
+            });
+        } else {
+            for_each_launch({{}, grads}, {}, nullptr, [&](sg::MTArgs& a) {
+                sg::sg2_sqnorm(dt, a, partials.data_ptr<float>(), st);
+                sg::mt_finalize_per_tensor(a, partials.data_ptr<float>(), tnorm.data_ptr<float>(), st);
+            });
+        }
+        sg::scalar_finalize(sg::SC_SG2_CLIP, tnorm.data_ptr<float>(), n, tclip.data_ptr<float>(), (float)clip, 0.f, 0.f, st);
+        for_each_launch({{}, grads, sharps}, {}, &offsets, [&](sg::MTArgs& a) {
+            sg::sg2_prep(dt, pull, a, tclip.data_ptr<float>(), g.data_ptr<float>(), s.data_ptr<float>(), u32(k0), u32(v0), st);
+        });
+        if (stage == 1) return 0;
+    }
     int cur = 0;
     sg::sg2_segmented_sort(u32(k0), u32(k1), u32(v0), u32(v1), u32(hist), u32(tot), seg_off.data_ptr<int64_t>(), n, total, &cur, st);
     const uint32_t* vs = cur ? u32(v1) : u32(v0);
@@ -93,35 +122,61 @@ int64_t sg2_prepare(const TL& grads, const TL& sharps, const std::vector<int64_t
     return cur;
 }
 
-void sg2_scan(Tensor items, int64_t n_items, int64_t dir1_start, Tensor tds, int64_t n_td, bool any_multi, int64_t sorted_buf, py::dict ws) {
+const int* status_ptr(const c10::optional<Tensor>& st) {
+    if (!st.has_value() || !st->defined()) return nullptr;
+    TORCH_CHECK(st->is_cuda() && st->scalar_type() == at::kInt && st->numel() >= 1, "status: int32 CUDA tensor");
+    return st->data_ptr<int>();
+}
+
+void sg2_scan(Tensor items, int64_t n_items, int64_t dir1_start, Tensor tds, int64_t n_td, bool any_multi, int64_t sorted_buf, py::dict ws,
+              c10::optional<Tensor> status) {
     c10::cuda::CUDAGuard guard(items.device());
     cudaStream_t st = at::cuda::getCurrentCUDAStream();
     auto W = [&](const char* k) { return ws[k].cast<Tensor>(); };
     const uint32_t* vs = sorted_buf ? u32(W("vals1")) : u32(W("vals0"));
     sg::sg2_scan(items.data_ptr(), (int)n_items, (int)dir1_start, tds.data_ptr(), (int)n_td, any_multi, W("gs").data_ptr<float>(), vs,
-                 W("agg").data_ptr<float>(), W("carry").data_ptr<float>(), W("ctx").data_ptr<float>(), st);
+                 W("agg").data_ptr<float>(), W("carry").data_ptr<float>(), W("ctx").data_ptr<float>(), status_ptr(status), st);
 }
 
 // masters: empty, or one fp32 tensor per parameter.  peer_ptrs: base addresses of the peers' parameter buffers (same layout as
 // the local buffer starting at local_base); the updated parameters are also stored there (all-gather fused into the step).
-void sg2_elem(const TL& params, const TL& ms, const TL& vs, const TL& mus, const TL& grus, const TL& masters,
-              const std::vector<std::vector<double>>& ts, const std::vector<int64_t>& offsets, double beta2, double lr, double wd_eff,
-              double eps, double rescale, double lamb_eff, c10::optional<Tensor> expert_counts, py::dict ws, int64_t local_base,
-              const std::vector<int64_t>& peer_ptrs) {
+// dyn: device table of step scalars (sg_native.h: DYN_*); packed: the packed meta-net weights (global-memory copy).
+void sg2_elem(const TL& params, const TL& ms, const TL& vs, const TL& mus, const TL& grus, const TL& masters, Tensor dyn, Tensor packed,
+              const std::vector<int64_t>& offsets, double beta2, double eps, double rescale, c10::optional<Tensor> expert_counts, py::dict ws,
+              int64_t local_base, const std::vector<int64_t>& peer_ptrs, c10::optional<Tensor> status) {
     c10::cuda::CUDAGuard guard(params[0].device());
     cudaStream_t st = at::cuda::getCurrentCUDAStream();
     const int dt = dtype_code(params[0]);
     auto W = [&](const char* k) { return ws[k].cast<Tensor>(); };
     Tensor g = W("g"), s = W("s"), ctx = W("ctx");
+    TORCH_CHECK(dyn.is_cuda() && dyn.scalar_type() == at::kFloat && dyn.is_contiguous() &&
+                dyn.numel() >= sg::DYN_TS + 4 * (int64_t)params.size(), "dyn: fp32 table of at least 16 + 4 * tensors words");
+    TORCH_CHECK(packed.is_cuda() && packed.scalar_type() == at::kFloat && packed.is_contiguous() && packed.numel() == sg::SG2Pack::TOTAL,
+                "packed meta-net weights expected");
     int* ec = expert_counts.has_value() ? expert_counts->data_ptr<int>() : nullptr;
     TORCH_CHECK(peer_ptrs.size() <= 8, "at most 8 peers");
     void* peers[8] = {nullptr};
     for (size_t r = 0; r < peer_ptrs.size(); ++r) peers[r] = reinterpret_cast<void*>(static_cast<intptr_t>(peer_ptrs[r]));
-    for_each_launch({params, ms, vs, mus, grus, masters}, ts, &offsets, [&](sg::MTArgs& a) {
-        sg::sg2_elem(dt, a, (float)beta2, (float)lr, (float)wd_eff, (float)eps, (float)rescale, (float)lamb_eff, g.data_ptr<float>(),
+    if (!peer_ptrs.empty())
+        for (const Tensor& t : params)
+            TORCH_CHECK((reinterpret_cast<char*>(t.data_ptr()) - reinterpret_cast<char*>(static_cast<intptr_t>(local_base))) % 16 == 0,
+                        "pushed parameters must be 16-byte aligned slices of the parameter buffer");
+    for_each_launch({params, ms, vs, mus, grus, masters}, {}, &offsets, [&](sg::MTArgs& a) {
+        sg::sg2_elem(dt, a, (float)beta2, (float)eps, (float)rescale, dyn.data_ptr<float>(), packed.data_ptr<float>(), status_ptr(status), g.data_ptr<float>(),
                      s.data_ptr<float>(), ctx.data_ptr<float>(), ec, (int)peer_ptrs.size(),
                      reinterpret_cast<void*>(static_cast<intptr_t>(local_base)), peers, st);
     });
+}
+
+// dst[0 .. n) = 32-bit words: `uints` first, then the bit patterns of `floats` (the per-step scalar table; no host buffer is kept)
+void write_table(Tensor dst, const std::vector<int64_t>& uints, const std::vector<double>& floats) {
+    TORCH_CHECK(dst.is_cuda() && dst.is_contiguous() && dst.element_size() == 4 && dst.numel() >= (int64_t)(uints.size() + floats.size()),
+                "table too small");
+    c10::cuda::CUDAGuard guard(dst.device());
+    std::vector<uint32_t> w(uints.size() + floats.size());
+    for (size_t i = 0; i < uints.size(); ++i) w[i] = (uint32_t)uints[i];
+    for (size_t i = 0; i < floats.size(); ++i) { const float f = (float)floats[i]; memcpy(&w[uints.size() + i], &f, 4); }
+    sg::write_words(reinterpret_cast<uint32_t*>(dst.data_ptr()), w.data(), (int)w.size(), at::cuda::getCurrentCUDAStream());
 }
 
 // Adjoint of the scan: dctx [total,16] -> grads [2, NG] (see csrc/sg2_bilevel.cuh for the layout).  Must follow a forward scan on the
@@ -396,12 +451,18 @@ void register_sg2(pybind11::module_& m) {
         return sg::routed_experts_supported((int)heads, (int)E, (int)hidden, (int)topk); });
     m.def("sg2_routed_experts_fwd", &routed_experts_fwd);
     m.def("sg2_routed_experts_bwd", &routed_experts_bwd);
-    m.def("sg2_prepare", &sg2_prepare);
-    m.def("sg2_scan", &sg2_scan);
+    m.def("sg2_prepare", &sg2_prepare, py::arg("grads"), py::arg("sharps"), py::arg("offsets"), py::arg("total"), py::arg("seg_off"),
+          py::arg("clip"), py::arg("ws"), py::arg("pull_bases") = std::vector<int64_t>(), py::arg("pull_rank") = 0,
+          py::arg("pull_scale") = 1.0, py::arg("stage") = 0);
+    m.def("write_table", &write_table);
+    m.attr("DYN_TS") = (int)sg::DYN_TS; m.attr("DYN_LR") = (int)sg::DYN_LR; m.attr("DYN_WD") = (int)sg::DYN_WD;
+    m.attr("DYN_LAMB") = (int)sg::DYN_LAMB; m.attr("DYN_EPOCH") = (int)sg::DYN_EPOCH;
+    m.def("sg2_scan", &sg2_scan, py::arg("items"), py::arg("n_items"), py::arg("dir1_start"), py::arg("tds"), py::arg("n_td"), py::arg("any_multi"),
+          py::arg("sorted_buf"), py::arg("ws"), py::arg("status") = c10::optional<Tensor>());
     m.def("sg2_elem", &sg2_elem, py::arg("params"), py::arg("ms"), py::arg("vs"), py::arg("mus"), py::arg("grus"), py::arg("masters"),
-          py::arg("ts"), py::arg("offsets"), py::arg("beta2"), py::arg("lr"), py::arg("wd_eff"), py::arg("eps"), py::arg("rescale"),
-          py::arg("lamb_eff"), py::arg("expert_counts"), py::arg("ws"), py::arg("local_base") = 0,
-          py::arg("peer_ptrs") = std::vector<int64_t>());
+          py::arg("dyn"), py::arg("packed"), py::arg("offsets"), py::arg("beta2"), py::arg("eps"), py::arg("rescale"),
+          py::arg("expert_counts"), py::arg("ws"), py::arg("local_base") = 0, py::arg("peer_ptrs") = std::vector<int64_t>(),
+          py::arg("status") = c10::optional<Tensor>());
     m.def("sg2_upload_weights", &sg2_upload_weights);
     m.def("sg2_sort", &sg2_sort);
     m.def("sg2_layout", &sg2_layout);

@@ -14,32 +14,27 @@
 #include <cstdlib>
 #include "comm.cuh"
 #include "optim_math.cuh"
+#include "peer_fetch.cuh"
 
 namespace sg {
 namespace {
 
 // ---- barrier: rank r publishes `epoch` in slot r of every pad, then waits for all slots of its own pad ----
-__global__ void barrier_kernel(PeerPtrs pads, int rank, int world, uint32_t epoch, int* status, unsigned long long timeout_ns, int site) {
+// The epoch is `epoch` itself, or, when `dyn` is given, the step's base epoch in the device table of step scalars plus `epoch`:
+// a barrier captured in a CUDA graph then advances with every replay (the host rewrites the table before each one).
+// A rank whose status word already records a timeout still publishes its epoch (its peers are not held up) but does not wait.
+__global__ void barrier_kernel(PeerPtrs pads, int rank, int world, uint32_t epoch, const uint32_t* __restrict__ dyn, int* status,
+                               unsigned long long timeout_ns, int site) {
     const int r = threadIdx.x;
+    if (dyn) epoch += dyn[DYN_EPOCH];
     if (r < world) {
         __threadfence_system();
         st_release_sys(reinterpret_cast<uint32_t*>(pads.p[r]) + rank, epoch);
-        if (!wait_flag_ge(reinterpret_cast<uint32_t*>(pads.p[rank]) + r, epoch, timeout_ns))
+        const bool failed = (*reinterpret_cast<volatile int*>(status) & 0xff) != STATUS_OK;
+        if (!failed && !wait_flag_ge(reinterpret_cast<uint32_t*>(pads.p[rank]) + r, epoch, timeout_ns))
             atomicCAS(status, STATUS_OK, STATUS_TIMEOUT | (r << 8) | (site << 16));
         __threadfence_system();
     }
-}
-
-template <typename T> struct Vec8;      // 16-byte vector of a gradient dtype
-template <> struct Vec8<float> { static constexpr int N = 4; };
-template <> struct Vec8<__nv_bfloat16> { static constexpr int N = 8; };
-template <> struct Vec8<__half> { static constexpr int N = 8; };
-
-template <typename T, int N>
-__device__ __forceinline__ void acc_vec(const uint4& v, float (&acc)[N]) {
-    const T* h = reinterpret_cast<const T*>(&v);
-#pragma unroll
-    for (int k = 0; k < N; ++k) acc[k] += Cvt<T>::to(h[k]);
 }
 
 // ---- all-gather push: copy [off, off+n) of the local parameter buffer into every peer's buffer ----
@@ -71,75 +66,8 @@ __global__ void __launch_bounds__(256) push_kernel(PeerPtrs params, void* mc_par
 struct FlatStep {
     float lr, beta1, beta2, eps, wd, bc1, bc2, gscale;
     float* master; float* m; float* v;      // local shard arrays (index 0 = element `off`)
+    const float* dyn;                       // optional device table: lr at DYN_LR, bc1 / bc2 at DYN_TS + 2 / + 3 (CUDA-graph replays)
 };
-
-// Remote accesses are ONE 16-byte (or 8-byte) access per lane with the lanes of a warp contiguous: a vector is 8 elements when
-// both buffers hold 16-bit values and 4 elements as soon as one of them is fp32.  (Two 16-byte accesses per lane at a 32-byte
-// stride touch every 32-byte sector twice with half of it; over NVLink that halves the useful bandwidth - measured.)
-template <typename T, int N>
-__device__ __forceinline__ void vload(const T* p, float (&v)[N]) {
-    if constexpr (sizeof(T) * N == 16) {
-        const uint4 t = *reinterpret_cast<const uint4*>(p);
-        const T* h = reinterpret_cast<const T*>(&t);
-#pragma unroll
-        for (int k = 0; k < N; ++k) v[k] = Cvt<T>::to(h[k]);
-    } else {
-        static_assert(sizeof(T) * N == 8, "vector of 8 or 16 bytes");
-        const uint2 t = *reinterpret_cast<const uint2*>(p);
-        const T* h = reinterpret_cast<const T*>(&t);
-#pragma unroll
-        for (int k = 0; k < N; ++k) v[k] = Cvt<T>::to(h[k]);
-    }
-}
-template <typename T, int N>
-__device__ __forceinline__ void vpack(const float (&v)[N], uint4& o) {
-    T* h = reinterpret_cast<T*>(&o);
-#pragma unroll
-    for (int k = 0; k < N; ++k) h[k] = Cvt<T>::from(v[k]);
-}
-template <typename T, int N>
-__device__ __forceinline__ void vstore_packed(T* p, const uint4& o) {
-    if constexpr (sizeof(T) * N == 16) *reinterpret_cast<uint4*>(p) = o;
-    else *reinterpret_cast<uint2*>(p) = make_uint2(o.x, o.y);
-}
-
-// Gradient fetch for one vector.  P2P: all W peer loads are issued before any of them is consumed (W is a compile-time constant so
-// the loop unrolls; with a runtime trip count the first add would stall the warp and serialise the remote loads).
-// NVLS: ONE multimem.ld_reduce per 16 bytes on the multicast address - the NVSwitch adds the W copies.
-template <typename G, int N, bool NVLS, int W>
-__device__ __forceinline__ void fetch_grad(const PeerPtrs& grads, const void* mc_grad, int world, int rank, int64_t elem, float (&g)[N]) {
-    if constexpr (NVLS && sizeof(G) * N == 16) {
-        const char* a = reinterpret_cast<const char*>(mc_grad) + elem * sizeof(G);
-        if constexpr (sizeof(G) == 2) {
-            const uint4 t = multimem_ld_reduce_bf16x8(a);
-            const G* h = reinterpret_cast<const G*>(&t);
-#pragma unroll
-            for (int k = 0; k < N; ++k) g[k] = Cvt<G>::to(h[k]);
-        } else {
-            const float4 t0 = multimem_ld_reduce_f32x4(a);
-            g[0] = t0.x; g[1] = t0.y; g[2] = t0.z; g[3] = t0.w;
-        }
-        return;
-    }
-#pragma unroll
-    for (int k = 0; k < N; ++k) g[k] = 0.f;
-    if constexpr (W > 0) {
-        float raw[W][N];
-#pragma unroll
-        for (int kk = 0; kk < W; ++kk) vload<G, N>(reinterpret_cast<const G*>(grads.p[(rank + kk) % W]) + elem, raw[kk]);
-#pragma unroll
-        for (int kk = 0; kk < W; ++kk)
-#pragma unroll
-            for (int k = 0; k < N; ++k) g[k] += raw[kk][k];
-    } else {
-        for (int kk = 0; kk < world; ++kk) {
-            float raw[N];
-            vload<G, N>(reinterpret_cast<const G*>(grads.p[(rank + kk) % world]) + elem, raw);
-#pragma unroll
-            for (int k = 0; k < N; ++k) g[k] += raw[k];
-        }
-    }
-}
 
 template <typename G, typename T> struct VecN { static constexpr int value = (sizeof(G) == 2 && sizeof(T) == 2) ? 8 : 4; };
 
@@ -151,6 +79,7 @@ __global__ void __launch_bounds__(256) fused_rs_step_ag_kernel(PeerPtrs grads, P
     constexpr int N = VecN<G, T>::value;
     const int64_t nv = n / N;
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    if (st.dyn) { st.lr = st.dyn[DYN_LR]; st.bc1 = st.dyn[DYN_TS + 2]; st.bc2 = st.dyn[DYN_TS + 3]; }
     for (int64_t v0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v0 < nv; v0 += stride * U) {
         // local state first, remote gradients second: every load of this iteration is in flight before the first use stalls the warp
         float pp[U][N], ms[U][N], vs[U][N], gg[U][N];
@@ -288,9 +217,10 @@ int grid_for(int64_t work_items) {
 
 }  // namespace
 
-void dist_barrier(const PeerPtrs& pads, int rank, int world, uint32_t epoch, int* status, unsigned long long timeout_ns, int site, cudaStream_t s) {
+void dist_barrier(const PeerPtrs& pads, int rank, int world, uint32_t epoch, const uint32_t* dyn, int* status, unsigned long long timeout_ns,
+                  int site, cudaStream_t s) {
     count_launch();
-    barrier_kernel<<<1, 32, 0, s>>>(pads, rank, world, epoch, status, timeout_ns, site);
+    barrier_kernel<<<1, 32, 0, s>>>(pads, rank, world, epoch, dyn, status, timeout_ns, site);
 }
 
 void dist_pull_reduce(int dtype, bool nvls, const PeerPtrs& grads, const void* mc, int world, int rank, int64_t off, int64_t n, float scale,
@@ -318,10 +248,10 @@ void dist_push(bool nvls, const PeerPtrs& params, void* mc, int world, int rank,
 
 void dist_fused_flat_step(int op, int gdtype, int pdtype, bool nvls, const PeerPtrs& grads, const PeerPtrs& params, const void* mc_grad,
                           void* mc_param, int world, int rank, int64_t off, int64_t n, float lr, float beta1, float beta2, float eps, float wd, float bc1, float bc2, float gscale,
-                          float* master, float* m, float* v, cudaStream_t s) {
+                          float* master, float* m, float* v, const float* dyn, cudaStream_t s) {
     if (n <= 0) return;
     count_launch();
-    FlatStep st{lr, beta1, beta2, eps, wd, bc1, bc2, gscale, master, m, v};
+    FlatStep st{lr, beta1, beta2, eps, wd, bc1, bc2, gscale, master, m, v, dyn};
     if (nvls && gdtype != pdtype) nvls = false;              // the multimem path needs 16-byte vectors of both buffers
     // Tuning knobs (read once): vectors in flight per thread and CTAs per SM of the grid.
     static const int unroll = [] { const char* e = getenv("SG_FUSED_UNROLL"); const int u = e ? atoi(e) : 0; return (u == 1 || u == 2 || u == 4) ? u : 0; }();

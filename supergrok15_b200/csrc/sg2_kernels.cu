@@ -23,6 +23,7 @@
 // shared memory by the element kernel because their index is data dependent.
 #include "sg_native.h"
 #include "optim_math.cuh"
+#include "peer_fetch.cuh"
 
 namespace sg {
 
@@ -42,9 +43,10 @@ __device__ __forceinline__ float sigmoidf(float x) { return 1.f / (1.f + __expf(
 
 // ---------------------------------------------------------------------------------------------------- prep
 // roles: 1 = grad (launch dtype), 2 = sharpness (fp32), 6 = packed offset (integer smuggled in the pointer slot)
-template <typename T>
+// PACKED: the gradient is read from g_packed itself (fp32, reduced over the ranks and scrubbed by sg2_pull_sqnorm_kernel)
+template <typename T, bool PACKED>
 __global__ void __launch_bounds__(MT_THREADS) sg2_prep_kernel(const __grid_constant__ MTArgs a, const float* __restrict__ tclip,
-                                                              float* __restrict__ g_packed, float* __restrict__ s_packed,
+                                                              float* g_packed, float* __restrict__ s_packed,
                                                               uint32_t* __restrict__ keys, uint32_t* __restrict__ vals) {
     int lo = 0, hi = a.n;
     const int b = blockIdx.x;
@@ -58,7 +60,7 @@ __global__ void __launch_bounds__(MT_THREADS) sg2_prep_kernel(const __grid_const
     const float* sh = reinterpret_cast<const float*>(a.ptr[2][t]);
     const float clip = tclip[a.t_off + t];
     for (int64_t i = begin + threadIdx.x; i < end; i += MT_THREADS) {
-        float gv = Cvt<T>::to(g[i]);
+        float gv = PACKED ? g_packed[off + i] : Cvt<T>::to(g[i]);
         float sv = sh[i];
         gv = isfinite(gv) ? gv * clip : 0.f;
         if (!isfinite(gv)) gv = 0.f;
@@ -86,6 +88,62 @@ __global__ void __launch_bounds__(MT_THREADS) sg2_sqnorm_kernel(const __grid_con
     for (int64_t i = begin + threadIdx.x; i < end; i += MT_THREADS) {
         const float gv = Cvt<T>::to(g[i]);
         if (isfinite(gv)) acc = fmaf(gv, gv, acc);
+    }
+    const float r = block_sum(acc, red);
+    if (threadIdx.x == 0) { float* o = partials + 3 * (int64_t)(a.blk_off + b); o[0] = r; o[1] = 0.f; o[2] = 0.f; }
+}
+
+// Reduce-scatter fused into the first kernel of the pipeline (ZeRO engine): every rank's gradient buffer has the same layout and
+// is mapped into this process; the owner of a tensor reads the tensor's slice of ALL W buffers with 16-byte peer loads (all W
+// loads of a vector are in flight before the first is used), sums in fp32, scales by 1/W, scrubs non-finite values, writes the
+// packed fp32 gradient that the rest of the pipeline consumes and accumulates the tensor's sum of squares for the per-tensor
+// clip.  No reduced copy of the gradient shard exists anywhere else.  The buffers are padded to 8 elements per tensor, so whole
+// vectors are read; only elements below the tensor's length are written or counted.
+struct PullParams {
+    int world, rank;
+    float scale;
+    char* local_base;            // base of this rank's gradient buffer (the tensors' role-1 pointers point into it)
+    PeerPtrs base;               // base of every rank's buffer in this process's address space (base.p[rank] == local_base)
+};
+
+template <typename T, int W>
+__global__ void __launch_bounds__(MT_THREADS) sg2_pull_sqnorm_kernel(const __grid_constant__ MTArgs a, const __grid_constant__ PullParams pp,
+                                                                     float* __restrict__ g_packed, float* __restrict__ partials) {
+    constexpr int N = 16 / sizeof(T);
+    __shared__ float red[32];
+    int lo = 0, hi = a.n;
+    const int b = blockIdx.x;
+    while (hi - lo > 1) { const int mid = (lo + hi) >> 1; if (a.blk_start[mid] <= b) lo = mid; else hi = mid; }
+    const int t = lo;
+    const int64_t begin = (int64_t)(b - a.blk_start[t]) * MT_CHUNK;
+    const int64_t n = a.numel[t];
+    const int64_t end = (begin + MT_CHUNK < n) ? begin + MT_CHUNK : n;
+    const int64_t off = (int64_t)reinterpret_cast<intptr_t>(a.ptr[6][t]);
+    const int64_t elem0 = (reinterpret_cast<char*>(a.ptr[1][t]) - pp.local_base) / (int64_t)sizeof(T);   // tensor start in the flat buffer
+    const int nvec = (int)((end - begin + N - 1) / N);
+    float acc = 0.f;
+    for (int v0 = threadIdx.x; v0 < nvec; v0 += 2 * MT_THREADS) {
+        float g[2][N];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const int v = v0 + u * MT_THREADS;
+            if (v < nvec) fetch_grad<T, N, false, W>(pp.base, nullptr, pp.world, pp.rank, elem0 + begin + (int64_t)v * N, g[u]);
+        }
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const int v = v0 + u * MT_THREADS;
+            if (v >= nvec) break;
+            const int64_t i0 = begin + (int64_t)v * N;
+#pragma unroll
+            for (int k = 0; k < N; ++k) {
+                if (i0 + k < end) {
+                    float gv = g[u][k] * pp.scale;
+                    if (!isfinite(gv)) gv = 0.f;
+                    g_packed[off + i0 + k] = gv;
+                    acc = fmaf(gv, gv, acc);
+                }
+            }
+        }
     }
     const float r = block_sum(acc, red);
     if (threadIdx.x == 0) { float* o = partials + 3 * (int64_t)(a.blk_off + b); o[0] = r; o[1] = 0.f; o[2] = 0.f; }
@@ -259,8 +317,8 @@ __device__ void scan_phase3(const Item& it, const TensorDir* __restrict__ tds, c
 
 // PHASE 1: aggregate affine map (M, b) of a chunk:  h_end = M h_in + b.
 // The chunk is walked BACKWARDS in time with the suffix product S = M_last ... M_{t+1}:  b += S b_t ; S <- S M_t.
-// With contracting dynamics every entry of S falls below 2^-100 after a few hundred steps; from then on an earlier
-// timestep can change b by at most 2^-100 |b_t|, far below fp32 resolution of any state that matters, so the walk
+// With contracting dynamics every entry of S falls below 2^-48 after a few hundred steps; from then on an earlier
+// timestep can change b by at most 2^-48 |b_t|, 2^-24 of an fp32 ulp of a state of the size of its own inputs, so the walk
 // stops (all 16 columns of the item agree by ballot).  Exact zero cannot be the test: a denormal times 0.7 rounds
 // back to the smallest denormal and never reaches zero.  Without contraction the whole chunk is walked.
 template <int DIR>
@@ -309,7 +367,7 @@ __device__ void scan_phase1(const Item& it, const float2* __restrict__ gs, float
         }
         bool zero = true;
 #pragma unroll
-        for (int k = 0; k < 32; ++k) zero = zero && (fabsf(m[k]) < 7.8886e-31f);   // 2^-100
+        for (int k = 0; k < 32; ++k) zero = zero && (fabsf(m[k]) < 3.5527e-15f);   // 2^-48
         __syncwarp(hmask);
         if (__all_sync(hmask, zero)) break;
     }
@@ -327,8 +385,10 @@ template <int PHASE>
 __global__ void __launch_bounds__(SCAN_THREADS, 4) sg2_scan_kernel(const Item* __restrict__ items, int n_items, int dir1_start,
                                                                    const TensorDir* __restrict__ tds, const float2* __restrict__ gs,
                                                                    const uint32_t* __restrict__ vals_sorted, float* __restrict__ agg,
-                                                                   const float* __restrict__ carry, float* __restrict__ ctx) {
+                                                                   const float* __restrict__ carry, float* __restrict__ ctx,
+                                                                   const int* __restrict__ status) {
     __shared__ __align__(16) float tiles[ITEMS_PER_CTA][TILE_T * ROW];
+    if (status && (*status & 0xff) != STATUS_OK) return;              // a wait on a peer timed out earlier in this step: the persistent scan states stay
     const int slot = threadIdx.x >> 4, j = threadIdx.x & 15;
     const int item_idx = blockIdx.x * ITEMS_PER_CTA + slot;
     const unsigned hmask = 0xffffu << (16 * ((threadIdx.x >> 4) & 1));
@@ -345,28 +405,48 @@ __global__ void __launch_bounds__(SCAN_THREADS, 4) sg2_scan_kernel(const Item* _
     }
 }
 
-// Phase 2: carry-in of every chunk.  One CTA of 128 threads (column j, pair p) per (tensor, direction).
+// Phase 2: carry-in of every chunk.  One CTA of 128 threads (column j, pair p) per (tensor, direction).  The recurrence over the
+// chunks is serial, but the aggregates do not depend on it: they are loaded eight chunks ahead, so a step of the chain costs four
+// dependent FMAs instead of a global-memory round trip (a 1 M-element tensor in 700-step chunks has 1,500 links).
 __global__ void __launch_bounds__(128) sg2_carry_kernel(const TensorDir* __restrict__ tds, const float* __restrict__ agg,
                                                         float* __restrict__ carry) {
+    constexpr int PF = 8;
     const TensorDir td = tds[blockIdx.x];
     const int j = threadIdx.x >> 3, p = threadIdx.x & 7;
     float he = td.h[j * 16 + 2 * p], ho = td.h[j * 16 + 2 * p + 1];
-    for (int c = 0; c < td.nc; ++c) {
-        const int64_t idx = (int64_t)(td.item0 + c);
-        float* co = carry + (idx * 16 + j) * 16 + 2 * p;
-        co[0] = he; co[1] = ho;
-        if (c + 1 < td.nc) {
-            const float* a = agg + (idx * 16 + j) * 48 + 6 * p;
-            const float ne = fmaf(a[0], he, fmaf(a[1], ho, a[4]));
-            const float no = fmaf(a[2], he, fmaf(a[3], ho, a[5]));
-            he = ne; ho = no;
+    for (int c0 = 0; c0 < td.nc; c0 += PF) {
+        float a[PF][6];
+#pragma unroll
+        for (int u = 0; u < PF; ++u) {
+            const int c = c0 + u;
+            if (c + 1 < td.nc) {
+                const float2* src = reinterpret_cast<const float2*>(agg + ((int64_t)(td.item0 + c) * 16 + j) * 48 + 6 * p);
+                const float2 q0 = src[0], q1 = src[1], q2 = src[2];
+                a[u][0] = q0.x; a[u][1] = q0.y; a[u][2] = q1.x; a[u][3] = q1.y; a[u][4] = q2.x; a[u][5] = q2.y;
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < PF; ++u) {
+            const int c = c0 + u;
+            if (c < td.nc) {
+                float* co = carry + ((int64_t)(td.item0 + c) * 16 + j) * 16 + 2 * p;
+                *reinterpret_cast<float2*>(co) = make_float2(he, ho);
+                if (c + 1 < td.nc) {
+                    const float ne = fmaf(a[u][0], he, fmaf(a[u][1], ho, a[u][4]));
+                    const float no = fmaf(a[u][2], he, fmaf(a[u][3], ho, a[u][5]));
+                    he = ne; ho = no;
+                }
+            }
         }
     }
 }
 
 // ---------------------------------------------------------------------------------------------------- element step
 struct ElemParams {
-    float beta2, lr, wd_eff, eps, rescale;
+    float beta2, eps, rescale;
+    const float* dyn;                  // device table: lr, effective weight decay, lambda_eff and the per-tensor scalars
+    const float* w_global;             // packed meta-net weights in global memory (source of the shared-memory expert tables)
+    const int* status;                 // optional status word of the collectives: once a wait on a peer has timed out, nothing is updated
     const float* g_packed; const float* s_packed; const float* ctx;
     int* expert_counts;                // [144] or nullptr
     // optional replication of the updated parameter into the same offset of peer buffers (fused all-gather):
@@ -374,21 +454,22 @@ struct ElemParams {
     int n_peers; char* local_base; char* peer_base[8];
 };
 
-// roles: 0 = param (launch dtype), 1 = m, 2 = v, 3 = mu, 4 = gru [n,4], 6 = packed offset.  ts = alpha, beta1, bc1, bc2; lamb_eff in ts? no:
-// ts[0]=alpha ts[1]=beta1 ts[2]=bc1 ts[3]=bc2, lamb_eff is global.
+// roles: 0 = param (launch dtype), 1 = m, 2 = v, 3 = mu, 4 = gru [n,4], 5 = fp32 master (optional), 6 = packed offset.
+// Step scalars come from the device table prm.dyn (layout: DYN_* in sg_native.h).
 template <typename T>
-__global__ void __launch_bounds__(MT_THREADS) sg2_elem_kernel(const __grid_constant__ MTArgs a, const __grid_constant__ ElemParams prm,
-                                                              float lamb_eff) {
+__global__ void __launch_bounds__(MT_THREADS) sg2_elem_kernel(const __grid_constant__ MTArgs a, const __grid_constant__ ElemParams prm) {
     // Expert rows are padded to 17 floats: lanes pick different experts, and with a row pitch of 16 the word k of every expert
     // falls into one of only two banks (16-way conflicts); with 17 the rows of 32 consecutive experts spread over all banks.
     constexpr int EP = SG2_EH + 1;
+    if (prm.status && (*prm.status & 0xff) != STATUS_OK) return;      // gradients of a timed-out step are incomplete: keep every state as it is
     __shared__ float sW1[SG2_NE * EP], sB1[SG2_NE * EP], sW2[SG2_NE * EP], sB2[SG2_NE];
     __shared__ int scount[SG2_NE];
     for (int i = threadIdx.x; i < SG2_NE * SG2_EH; i += MT_THREADS) {
         const int j = (i / SG2_EH) * EP + i % SG2_EH;
-        sW1[j] = c_w[P::EW1 + i]; sB1[j] = c_w[P::EB1 + i]; sW2[j] = c_w[P::EW2 + i];
+        // lanes read consecutive words: from global memory that is one coalesced request, from __constant__ memory 32 serial ones
+        sW1[j] = prm.w_global[P::EW1 + i]; sB1[j] = prm.w_global[P::EB1 + i]; sW2[j] = prm.w_global[P::EW2 + i];
     }
-    for (int i = threadIdx.x; i < SG2_NE; i += MT_THREADS) { sB2[i] = c_w[P::EB2 + i]; scount[i] = 0; }
+    for (int i = threadIdx.x; i < SG2_NE; i += MT_THREADS) { sB2[i] = prm.w_global[P::EB2 + i]; scount[i] = 0; }
     __syncthreads();
     int lo = 0, hi = a.n;
     const int b = blockIdx.x;
@@ -405,7 +486,9 @@ __global__ void __launch_bounds__(MT_THREADS) sg2_elem_kernel(const __grid_const
     float4* GRU = reinterpret_cast<float4*>(a.ptr[4][t]);
     float* MASTER = reinterpret_cast<float*>(a.ptr[5][t]);       // fp32 master copy of a low-precision parameter (may be null)
     const ptrdiff_t pdelta = reinterpret_cast<char*>(param) - prm.local_base;
-    const float alpha = a.ts[t][0], beta1 = a.ts[t][1], bc1 = a.ts[t][2], bc2 = a.ts[t][3];
+    const float* ts = prm.dyn + DYN_TS + 4 * (a.t_off + t);
+    const float alpha = ts[0], beta1 = ts[1], bc1 = ts[2], bc2 = ts[3];
+    const float lr = prm.dyn[DYN_LR], wd_eff = prm.dyn[DYN_WD], lamb_eff = prm.dyn[DYN_LAMB];
 
     for (int64_t i = begin + threadIdx.x; i < end; i += MT_THREADS) {
         const float g = prm.g_packed[off + i], s = prm.s_packed[off + i];
@@ -482,12 +565,26 @@ __global__ void __launch_bounds__(MT_THREADS) sg2_elem_kernel(const __grid_const
         const float fg = smart + lamb_eff * mu;
         float mm = M[i], vv = V[i];
         const float pold = MASTER ? MASTER[i] : Cvt<T>::to(param[i]);
-        const float pnew = adam_update(pold, fg, mm, vv, prm.lr, beta1, prm.beta2, prm.eps, prm.wd_eff, bc1, bc2);
+        const float pnew = adam_update(pold, fg, mm, vv, lr, beta1, prm.beta2, prm.eps, wd_eff, bc1, bc2);
         M[i] = mm; V[i] = vv;
         if (MASTER) MASTER[i] = pnew;
         const T pt = Cvt<T>::from(pnew);
         param[i] = pt;
-        for (int r = 0; r < prm.n_peers; ++r) reinterpret_cast<T*>(prm.peer_base[r] + pdelta)[i] = pt;
+    }
+    if (prm.n_peers > 0) {
+        // All-gather fused into the step: the chunk this CTA just wrote is replicated into every peer's parameter buffer with one
+        // 16-byte store per lane and peer (512 contiguous bytes per warp and store; 2-byte stores from the element loop would put
+        // 64 bytes per warp on the link).  The chunk is re-read from this GPU's own memory (L1 / L2 hits).  Tensors are padded to
+        // 8 elements in every rank's buffer, so whole vectors are copied.
+        __syncthreads();
+        constexpr int N = 16 / sizeof(T);
+        const int nvec = (int)((end - begin + N - 1) / N);
+        const uint4* src = reinterpret_cast<const uint4*>(param + begin);
+        for (int v = threadIdx.x; v < nvec; v += MT_THREADS) {
+            const uint4 val = src[v];
+            for (int r = 0; r < prm.n_peers; ++r)
+                reinterpret_cast<uint4*>(reinterpret_cast<T*>(prm.peer_base[r] + pdelta) + begin)[v] = val;
+        }
     }
     if (prm.expert_counts) {
         __syncthreads();
@@ -514,16 +611,35 @@ void sg2_sqnorm(int dtype, const MTArgs& a, float* partials, cudaStream_t s) {
     }
 }
 
-void sg2_prep(int dtype, const MTArgs& a, const float* tclip, float* g_packed, float* s_packed, uint32_t* keys, uint32_t* vals,
-              cudaStream_t s) {
+void sg2_prep(int dtype, bool packed_src, const MTArgs& a, const float* tclip, float* g_packed, float* s_packed, uint32_t* keys,
+              uint32_t* vals, cudaStream_t s) {
     const int blocks = a.blk_start[a.n];
     if (blocks <= 0) return;
     count_launch();
+    if (packed_src) { sg2_prep_kernel<float, true><<<blocks, MT_THREADS, 0, s>>>(a, tclip, g_packed, s_packed, keys, vals); return; }
     switch (dtype) {
-        case F32:  sg2_prep_kernel<float><<<blocks, MT_THREADS, 0, s>>>(a, tclip, g_packed, s_packed, keys, vals); break;
-        case BF16: sg2_prep_kernel<__nv_bfloat16><<<blocks, MT_THREADS, 0, s>>>(a, tclip, g_packed, s_packed, keys, vals); break;
-        default:   sg2_prep_kernel<__half><<<blocks, MT_THREADS, 0, s>>>(a, tclip, g_packed, s_packed, keys, vals); break;
+        case F32:  sg2_prep_kernel<float, false><<<blocks, MT_THREADS, 0, s>>>(a, tclip, g_packed, s_packed, keys, vals); break;
+        case BF16: sg2_prep_kernel<__nv_bfloat16, false><<<blocks, MT_THREADS, 0, s>>>(a, tclip, g_packed, s_packed, keys, vals); break;
+        default:   sg2_prep_kernel<__half, false><<<blocks, MT_THREADS, 0, s>>>(a, tclip, g_packed, s_packed, keys, vals); break;
     }
+}
+
+// Gradient reduce-scatter + NaN scrub + per-tensor sum of squares in one kernel (role 1 = the tensors' slices of the LOCAL gradient
+// buffer, whose base is local_base; bases = every rank's buffer, same layout).
+void sg2_pull_sqnorm(int dtype, const MTArgs& a, const PeerPtrs& bases, int world, int rank, void* local_base, float scale,
+                     float* g_packed, float* partials, cudaStream_t s) {
+    const int blocks = a.blk_start[a.n];
+    if (blocks <= 0) return;
+    count_launch();
+    PullParams pp{};
+    pp.world = world; pp.rank = rank; pp.scale = scale; pp.local_base = reinterpret_cast<char*>(local_base); pp.base = bases;
+#define PULL(T) \
+    if (world == 8) sg2_pull_sqnorm_kernel<T, 8><<<blocks, MT_THREADS, 0, s>>>(a, pp, g_packed, partials); \
+    else if (world == 4) sg2_pull_sqnorm_kernel<T, 4><<<blocks, MT_THREADS, 0, s>>>(a, pp, g_packed, partials); \
+    else if (world == 2) sg2_pull_sqnorm_kernel<T, 2><<<blocks, MT_THREADS, 0, s>>>(a, pp, g_packed, partials); \
+    else sg2_pull_sqnorm_kernel<T, 0><<<blocks, MT_THREADS, 0, s>>>(a, pp, g_packed, partials);
+    switch (dtype) { case F32: PULL(float) break; case BF16: PULL(__nv_bfloat16) break; default: PULL(__half) break; }
+#undef PULL
 }
 
 void sg2_gather(const uint32_t* vals_sorted, const float* g_packed, const float* s_packed, float* gs_sorted, int64_t total,
@@ -535,33 +651,52 @@ void sg2_gather(const uint32_t* vals_sorted, const float* g_packed, const float*
 }
 
 void sg2_scan(const void* items_dev, int n_items, int dir1_start, const void* tds_dev, int n_td, bool any_multi,
-              const float* gs_sorted, const uint32_t* vals_sorted, float* agg, float* carry, float* ctx, cudaStream_t s) {
+              const float* gs_sorted, const uint32_t* vals_sorted, float* agg, float* carry, float* ctx, const int* status, cudaStream_t s) {
     if (n_items <= 0) return;
     const int blocks = (n_items + ITEMS_PER_CTA - 1) / ITEMS_PER_CTA;
     const Item* items = reinterpret_cast<const Item*>(items_dev);
     const TensorDir* tds = reinterpret_cast<const TensorDir*>(tds_dev);
     const float2* gs = reinterpret_cast<const float2*>(gs_sorted);
     count_launch(any_multi ? 3 : 2);
-    if (any_multi) sg2_scan_kernel<1><<<blocks, SCAN_THREADS, 0, s>>>(items, n_items, dir1_start, tds, gs, vals_sorted, agg, carry, ctx);
+    if (any_multi) sg2_scan_kernel<1><<<blocks, SCAN_THREADS, 0, s>>>(items, n_items, dir1_start, tds, gs, vals_sorted, agg, carry, ctx, status);
     sg2_carry_kernel<<<n_td, 128, 0, s>>>(tds, agg, carry);
-    sg2_scan_kernel<3><<<blocks, SCAN_THREADS, 0, s>>>(items, n_items, dir1_start, tds, gs, vals_sorted, agg, carry, ctx);
+    sg2_scan_kernel<3><<<blocks, SCAN_THREADS, 0, s>>>(items, n_items, dir1_start, tds, gs, vals_sorted, agg, carry, ctx, status);
 }
 
-void sg2_elem(int dtype, const MTArgs& a, float beta2, float lr, float wd_eff, float eps, float rescale, float lamb_eff,
+void sg2_elem(int dtype, const MTArgs& a, float beta2, float eps, float rescale, const float* dyn, const float* w_global, const int* status,
               const float* g_packed, const float* s_packed, const float* ctx, int* expert_counts, int n_peers, void* local_base,
               void* const* peer_base, cudaStream_t s) {
     const int blocks = a.blk_start[a.n];
     if (blocks <= 0) return;
     count_launch();
     ElemParams p{};
-    p.beta2 = beta2; p.lr = lr; p.wd_eff = wd_eff; p.eps = eps; p.rescale = rescale;
+    p.beta2 = beta2; p.eps = eps; p.rescale = rescale; p.dyn = dyn; p.w_global = w_global; p.status = status;
     p.g_packed = g_packed; p.s_packed = s_packed; p.ctx = ctx; p.expert_counts = expert_counts;
     p.n_peers = n_peers; p.local_base = reinterpret_cast<char*>(local_base);
     for (int r = 0; r < n_peers && r < 8; ++r) p.peer_base[r] = reinterpret_cast<char*>(peer_base[r]);
     switch (dtype) {
-        case F32:  sg2_elem_kernel<float><<<blocks, MT_THREADS, 0, s>>>(a, p, lamb_eff); break;
-        case BF16: sg2_elem_kernel<__nv_bfloat16><<<blocks, MT_THREADS, 0, s>>>(a, p, lamb_eff); break;
-        default:   sg2_elem_kernel<__half><<<blocks, MT_THREADS, 0, s>>>(a, p, lamb_eff); break;
+        case F32:  sg2_elem_kernel<float><<<blocks, MT_THREADS, 0, s>>>(a, p); break;
+        case BF16: sg2_elem_kernel<__nv_bfloat16><<<blocks, MT_THREADS, 0, s>>>(a, p); break;
+        default:   sg2_elem_kernel<__half><<<blocks, MT_THREADS, 0, s>>>(a, p); break;
+    }
+}
+
+// Writes up to WORDS_MAX 32-bit words, passed as kernel arguments, to device memory: the per-step scalars reach the device
+// without a host buffer whose lifetime would have to outlast the copy.
+namespace {
+constexpr int WORDS_MAX = 960;
+struct Words { uint32_t w[WORDS_MAX]; int n; };
+__global__ void __launch_bounds__(256) write_words_kernel(const __grid_constant__ Words v, uint32_t* __restrict__ dst) {
+    for (int i = threadIdx.x; i < v.n; i += 256) dst[i] = v.w[i];
+}
+}  // namespace
+void write_words(uint32_t* dst, const uint32_t* host_words, int n, cudaStream_t s) {
+    for (int o = 0; o < n; o += WORDS_MAX) {
+        Words v;
+        v.n = (n - o < WORDS_MAX) ? n - o : WORDS_MAX;
+        for (int i = 0; i < v.n; ++i) v.w[i] = host_words[o + i];
+        count_launch();
+        write_words_kernel<<<1, 256, 0, s>>>(v, dst + o);
     }
 }
 

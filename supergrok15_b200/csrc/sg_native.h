@@ -143,6 +143,12 @@ struct SG2Pack {
     static constexpr int TOTAL = AFF1 + AFF_SIZE;        // 12,060
 };
 
+// Layout of the device table of per-step scalars (32-bit words).  The host rewrites it before every step (one tiny kernel whose
+// arguments are the values), so the kernels that read it can sit in a CUDA graph that is replayed unchanged step after step.
+constexpr int DYN_EPOCH = 0;             // uint32: barrier epoch base of the step (barrier_kernel, csrc/dist_kernels.cu)
+constexpr int DYN_LR = 8, DYN_WD = 9, DYN_LAMB = 10;
+constexpr int DYN_TS = 16;               // per tensor t: alpha, beta1, bc1, bc2 at DYN_TS + 4 t
+
 struct SG2Tensor {          // one entry per parameter tensor handled by a v2 step
     int64_t off;            // offset of the tensor in every packed [total_N] array
     int64_t n;              // elements
@@ -184,4 +190,5 @@ constexpr int MAX_RANKS = 8;
 constexpr int STATUS_OK = 0;
 constexpr int STATUS_TIMEOUT = 1;     // status word = STATUS_TIMEOUT | (peer << 8) | (site << 16)
 struct PeerPtrs { void* p[MAX_RANKS]; };
+void write_words(uint32_t* dst, const uint32_t* host_words, int n, cudaStream_t s);
 }  // namespace sg

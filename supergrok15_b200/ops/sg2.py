@@ -201,45 +201,106 @@ def _plan_for(opt, idx: List[int]) -> Plan:
 
 
 def _packed_weights(opt, dev) -> Tuple[torch.Tensor, bool]:
-    if opt._weights_dirty or getattr(opt, "_packed_w", None) is None or opt._packed_w.device != dev:
-        opt._packed_w = pack_metanet(opt.meta_net).to(dev)
+    """Packed meta-net weights of ``opt`` on ``dev``.  The buffer is allocated once and refreshed in place, so kernels captured
+    in a CUDA graph keep reading the right address."""
+    cur = getattr(opt, "_packed_w", None)
+    if opt._weights_dirty or cur is None or cur.device != dev:
+        w = pack_metanet(opt.meta_net).to(dev)
+        if cur is not None and cur.device == dev and cur.numel() == w.numel():
+            cur.copy_(w)
+        else:
+            opt._packed_w = w
         opt._weights_dirty = False
         return opt._packed_w, True
-    return opt._packed_w, False
+    return cur, False
 
 
 # the constant-memory copy of the weights is per process: remember whose weights it holds
 _resident = {"owner": None}
+
+DYN_WORDS = 16          # words of the table of step scalars before the per-tensor entries (csrc/sg_native.h: DYN_*)
+
+
+def refresh_weights(opt, dev) -> torch.Tensor:
+    """Make the device copies of the meta-net weights (global-memory vector and ``__constant__`` copy) current.  Runs outside
+    any CUDA graph: the kernels of a captured step read both copies."""
+    w, fresh = _packed_weights(opt, dev)
+    if fresh or _resident["owner"] is not opt:
+        _build.require().sg2_upload_weights(w)
+        _resident["owner"] = opt
+    return w
+
+
+def dyn_table(opt, n_tensors: int, dev) -> torch.Tensor:
+    """Device table of the scalars that change from step to step (learning rate, effective weight decay, lambda_eff, per-tensor
+    alpha / beta1 / bias corrections, barrier epoch).  Its address is fixed, so the kernels that read it can be replayed from a
+    CUDA graph; ``write_scalars`` refreshes it before every step."""
+    t = getattr(opt, "_dyn", None)
+    need = DYN_WORDS + 4 * max(n_tensors, 1)
+    if t is None or t.device != dev or t.numel() < need:
+        opt._dyn = t = torch.zeros(need, dtype=torch.float32, device=dev)
+    return t
+
+
+def write_scalars(opt, per, *, lr, wd_eff, dev, epoch_base: int = 0):
+    """One tiny kernel whose arguments are the values: no host staging buffer that a later step could overwrite too early."""
+    t = dyn_table(opt, len(per), dev)
+    floats = [lr, wd_eff, per[0][1] if per else 0.0, 0.0, 0.0, 0.0, 0.0, 0.0]
+    for (a, _l, b1, bc1, bc2) in per:
+        floats += [a, b1, bc1, bc2]
+    _build.require().write_table(t, [int(epoch_base) & 0xffffffff, 0, 0, 0, 0, 0, 0, 0], floats)
+    return t
+
+
+@torch.no_grad()
+def launch(opt, idx: List[int], *, beta2, eps, clip, pull=None, status=None, stage_hook=None):
+    """Enqueue the kernels of one v2 update of tensors ``idx``; every scalar that changes between steps is read from the device
+    table, so the same sequence can be captured once and replayed.  ``pull = (bases, rank, scale)``: the gradients are this
+    rank's slices of its flat gradient buffer (``opt._pull_grads``) and the first kernel sums the copies of all ranks
+    (reduce-scatter fused in).  ``stage_hook(name)`` is called between the phases (per-phase CUDA-event timing)."""
+    C = _build.require()
+    params = [opt._flat_params[i] for i in idx]
+    dev = params[0].device
+    plan = _plan_for(opt, idx)
+    sharps = [opt._flat_sharpness[i] for i in idx]
+    offs = plan.offsets[:-1]
+    hook = stage_hook or (lambda _n: None)
+    if pull is not None:
+        grads = [opt._pull_grads[i] for i in idx]
+        kw = dict(pull_bases=list(pull[0]), pull_rank=int(pull[1]), pull_scale=float(pull[2]))
+    else:
+        gsrc = getattr(opt, "_grad_override", None)     # reduced fp32 gradients supplied by the ZeRO engine (NCCL / CPU paths)
+        grads = [gsrc[i] for i in idx] if gsrc else [p.grad for p in params]
+        kw = {}
+    if stage_hook is None:
+        buf = C.sg2_prepare(grads, sharps, offs, plan.total, plan.seg_off, float(clip), plan.ws, **kw)
+    else:
+        C.sg2_prepare(grads, sharps, offs, plan.total, plan.seg_off, float(clip), plan.ws, stage=1, **kw)
+        hook("reduce+prep")
+        buf = C.sg2_prepare(grads, sharps, offs, plan.total, plan.seg_off, float(clip), plan.ws, stage=2, **kw)
+        hook("sort")
+    C.sg2_scan(plan.items, plan.n_items, plan.dir1_start, plan.tds, plan.n_td, plan.any_multi, buf, plan.ws, status=status)
+    hook("scan")
+    counts = opt.meta_net.expert_counts if opt.meta_net.training else None
+    masters = getattr(opt, "_flat_masters", None)
+    push = getattr(opt, "_peer_push", None)         # (local_base, [peer bases]) set by the ZeRO engine
+    C.sg2_elem(params, [opt._flat_exp_avgs[i] for i in idx], [opt._flat_exp_avg_sqs[i] for i in idx],
+               [opt._flat_mus[i] for i in idx], [opt._flat_gru_states[i] for i in idx],
+               [masters[i] for i in idx] if masters else [], dyn_table(opt, len(idx), dev), opt._packed_w, offs, beta2, eps,
+               float(opt.meta_net.rescale), counts, plan.ws, push[0] if push else 0, push[1] if push else [], status=status)
+    hook("elem+push")
 
 
 @torch.no_grad()
 def step(opt, idx: List[int], per: List[Tuple[float, float, float, float, float]], *, beta2, lr, wd_eff, eps, clip):
     """One v2 update of tensors ``idx`` of ``opt``; ``per[k] = (alpha, lamb_eff, beta1, bc1, bc2)``."""
     params = [opt._flat_params[i] for i in idx]
-    gsrc = getattr(opt, "_grad_override", None)     # reduced fp32 gradients supplied by the ZeRO engine
-    grads = [gsrc[i] for i in idx] if gsrc else [p.grad for p in params]
     if not params[0].is_cuda:
         return _step_cpu(opt, idx, per, beta2=beta2, lr=lr, wd_eff=wd_eff, eps=eps, clip=clip)
-    C = _build.require()
     dev = params[0].device
-    plan = _plan_for(opt, idx)
-    w, fresh = _packed_weights(opt, dev)
-    if fresh or _resident["owner"] is not opt:
-        C.sg2_upload_weights(w)
-        _resident["owner"] = opt
-    sharps = [opt._flat_sharpness[i] for i in idx]
-    offs = plan.offsets[:-1]
-    buf = C.sg2_prepare(grads, sharps, offs, plan.total, plan.seg_off, float(clip), plan.ws)
-    C.sg2_scan(plan.items, plan.n_items, plan.dir1_start, plan.tds, plan.n_td, plan.any_multi, buf, plan.ws)
-    ts = [[a, b1, bc1, bc2] for (a, _l, b1, bc1, bc2) in per]
-    counts = opt.meta_net.expert_counts if opt.meta_net.training else None
-    masters = getattr(opt, "_flat_masters", None)
-    push = getattr(opt, "_peer_push", None)         # (local_base, [peer bases]) set by the ZeRO engine
-    C.sg2_elem(params, [opt._flat_exp_avgs[i] for i in idx], [opt._flat_exp_avg_sqs[i] for i in idx],
-               [opt._flat_mus[i] for i in idx], [opt._flat_gru_states[i] for i in idx],
-               [masters[i] for i in idx] if masters else [], ts, offs, beta2, lr, wd_eff,
-               eps, float(opt.meta_net.rescale), float(per[0][1]), counts, plan.ws,
-               push[0] if push else 0, push[1] if push else [])
+    refresh_weights(opt, dev)
+    write_scalars(opt, per, lr=lr, wd_eff=wd_eff, dev=dev)
+    launch(opt, idx, beta2=beta2, eps=eps, clip=clip)
 
 
 def clip_scrub(g: torch.Tensor, clip: float) -> torch.Tensor:

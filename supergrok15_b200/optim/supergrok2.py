@@ -79,9 +79,10 @@ class SuperGrok2(SuperGrok15):
         self._native_plan = None
 
     # ------------------------------------------------------------------ step
-    @torch.no_grad()
-    def step(self, closure=None, train_loss=None, val_loss=None, train_acc=None):
-        loss = run_closure(closure)
+    def _prepare_step(self, train_loss=None, val_loss=None, train_acc=None):
+        """Host side of a step: schedules, step counters and the scalars every tensor needs.  Returns
+        ``(idx, per, hyper)``: the tensors that take part, ``per[k] = (alpha, lamb_eff, beta1, bc1, bc2)`` and the keyword
+        arguments of ``ops.sg2.step``.  The tensor lists are cached: they only change when gradients appear or disappear."""
         self._ensure_state()
         self._schedule_tick(train_loss, val_loss, train_acc)
         ramp, gate = self._get_ramp_factor(), self._get_gate_signal()
@@ -89,23 +90,37 @@ class SuperGrok2(SuperGrok15):
         lr, beta2, eps = group["lr"], group["betas"][1], group["eps"]
         wd_eff = self._get_effective_wd(group["weight_decay"])
         lamb_eff = self.lamb * ramp * gate
-        gsrc = getattr(self, "_grad_override", None)       # reduced gradients handed in by the ZeRO engine
-        idx = [i for i, p in enumerate(self._flat_params)
-               if p.numel() > 0 and (gsrc is not None or p.grad is not None)]
-        if not idx:
-            return loss
+        ext = getattr(self, "_grad_override", None) is not None or getattr(self, "_pull_grads", None) is not None
+        if ext:                                            # the ZeRO engine hands in gradients for every tensor, every step
+            idx = getattr(self, "_all_idx", None)
+            if idx is None or len(idx) != sum(1 for p in self._flat_params if p.numel() > 0):
+                self._all_idx = idx = [i for i, p in enumerate(self._flat_params) if p.numel() > 0]
+        else:
+            idx = [i for i, p in enumerate(self._flat_params) if p.numel() > 0 and p.grad is not None]
         per = []
+        ca, steps, b1s, las = self._cached_alpha, self._flat_steps, self._flat_layer_beta1s, self._flat_layer_alphas
         for i in idx:
-            self._flat_steps[i] += 1
-            s = self._flat_steps[i]
-            b1 = self._flat_layer_beta1s[i]
-            a = max(0.0, min(1.0, self._cached_alpha * self._flat_layer_alphas[i]))
+            steps[i] += 1
+            s = steps[i]
+            b1 = b1s[i]
+            a = max(0.0, min(1.0, ca * las[i]))
             per.append((a, lamb_eff, b1, 1.0 - b1 ** s, 1.0 - beta2 ** s))
-        sg2_ops.step(self, idx, per, beta2=beta2, lr=lr, wd_eff=wd_eff, eps=eps, clip=self.gradient_clipping)
+        return idx, per, dict(beta2=beta2, lr=lr, wd_eff=wd_eff, eps=eps, clip=self.gradient_clipping)
+
+    def _after_step(self):
         self._step_counter += 1
         ri = self.meta_net.recycle_interval
         if ri > 0 and self._step_counter % ri == 0 and not getattr(self, "_external_recycle", False):
             self.recycle_dead_experts()
+
+    @torch.no_grad()
+    def step(self, closure=None, train_loss=None, val_loss=None, train_acc=None):
+        loss = run_closure(closure)
+        idx, per, hyper = self._prepare_step(train_loss, val_loss, train_acc)
+        if not idx:
+            return loss
+        sg2_ops.step(self, idx, per, **hyper)
+        self._after_step()
         return loss
 
     def recycle_dead_experts(self):

@@ -58,7 +58,7 @@ class ZeroEngine:
     def __init__(self, model: torch.nn.Module, optimizer: str = "supergrok2", opt_kwargs: Optional[dict] = None,
                  comm: Optional[str] = None, param_dtype: torch.dtype = torch.bfloat16, group=None,
                  timeout_s: float = 20.0, criterion=None, graph: Optional[bool] = None, graph_warmup: int = 3,
-                 overlap: bool = False, bucket_numel: int = 1 << 24):
+                 overlap: bool = False, bucket_numel: int = 1 << 24, heartbeat=None):
         self.comm = comm or os.environ.get("GROK_COMM", "p2p")
         assert self.comm in ("p2p", "nvls", "nccl")
         self.rank, self.world = symm.world_info(group)
@@ -108,6 +108,11 @@ class ZeroEngine:
         else:
             self.owner = ownership.assign_tensors(numels, self.world)
             self.offsets, self.regions, self.total = ownership.grouped_layout(numels, self.owner, self.world)
+            if optimizer != "supergrok2" and len(set(self.owner)) < self.world:
+                # the element-wise optimizers combine global scalars (clip norm, Prodigy sums, ...) across the ranks from inside
+                # their step; a rank without tensors would skip those collectives and the sequences would diverge
+                raise ValueError(f"'{optimizer}' shards whole tensors: {len(numels)} parameter tensors cannot give each of "
+                                 f"{self.world} ranks one; use fewer ranks, or 'adamw' / 'lion' / 'supergrok2'")
         self.my_begin, self.my_end = self.regions[self.rank]
         # (begin, end, offset into this rank's state) of every flat range this rank owns: one range, or one per bucket
         if self.overlap:
@@ -129,6 +134,10 @@ class ZeroEngine:
         self.slots = symm.alloc(self.slots_n * max(self.world, 1), torch.float32, self.device, group)
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.epoch = 0
+        # the status word is copied to pinned host memory after every step and looked at before the next one is launched
+        self._status_host = torch.zeros(1, dtype=torch.int32).pin_memory() if self.cuda else None
+        self._status_event = None
+        self.heartbeat = heartbeat
         # NVLS (in-switch reduction / replication through the multicast mapping) needs multicast addresses for both buffers
         self.nvls = self.comm == "nvls" and self.world > 1 and self.gbuf.multicast_ptr != 0 and self.pbuf.multicast_ptr != 0
         if self.comm == "nvls" and self.world > 1 and not self.nvls:
@@ -142,6 +151,17 @@ class ZeroEngine:
         self._build_optimizer()
         self.steps = 0
         self.launches = 0
+        # In-kernel collectives with every per-step scalar in a device table: the whole step (barrier, reduce-scatter + optimizer +
+        # all-gather, barrier) is a fixed launch sequence and is captured into the same CUDA graph as forward / backward.
+        self.fused = self.cuda and self.comm != "nccl"
+        self.device_step = self.fused and not self.overlap and (self.flat_mode or (self.name == "supergrok2" and self._sg2_native))
+        if self.device_step:
+            from ..ops import sg2 as sg2_ops
+            if self.name == "supergrok2":
+                self.dyn = sg2_ops.dyn_table(self.opt, len(self.own_idx), self.device)
+            else:
+                self.dyn = torch.zeros(sg2_ops.DYN_WORDS + 4, dtype=torch.float32, device=self.device)
+        self._step_hp = None
         if self.overlap:
             import functools
             self.use_graph = False                    # epochs and bias corrections are host-side arguments of the bucket kernels
@@ -182,10 +202,18 @@ class ZeroEngine:
                     [torch.nn.Parameter(torch.zeros(0, device=self.device))]
             self.opt = cls(views, **kw)
             self.opt._external_recycle = True                         # recycling runs in step() below, after the counts are summed
+            from ..ops import sg2 as sg2_ops
+            self._sg2_native = self.cuda and sg2_ops.supports_native(self.opt.meta_net)
+            if self.cuda:
+                self.opt.meta_net.to(self.device)
             if own:
                 self.opt._ensure_state()
                 self.opt._flat_masters = [mv.data.reshape(-1) for mv in self.master_views]
-                self.opt._grad_override = [g.reshape(-1) for g in self.grad_views]
+                if self.cuda and self.comm != "nccl" and self._sg2_native:
+                    # the first kernel of the v2 pipeline reads this rank's tensors out of every rank's gradient buffer itself
+                    self.opt._pull_grads = [self.params[i].grad.reshape(-1) for i in own]
+                else:
+                    self.opt._grad_override = [g.reshape(-1) for g in self.grad_views]
                 if self.cuda and self.world > 1 and self.comm != "nccl":
                     peers = [p for r, p in enumerate(self.pbuf.peer_ptrs) if r != self.rank]
                     self.opt._peer_push = (self.pbuf.peer_ptrs[self.rank], peers)
@@ -224,6 +252,13 @@ class ZeroEngine:
             import torch.distributed as dist
             dist.barrier(self.group)
 
+    def _barrier_dyn(self, k: int, site: int):
+        """Barrier k (1 or 2) of a device step: its epoch is the step's base epoch in the device table plus k, so the launch is
+        the same every step and can be replayed from a CUDA graph."""
+        if self.world > 1:
+            _build.require().dist_barrier(self.pads.peer_ptrs, self.rank, k, self.status, self.timeout_s, site, self.dyn)
+            self.launches += 1
+
     def all_reduce_small(self, vec: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
         """In-place deterministic sum of a small fp32 vector over the ranks (bitwise identical everywhere)."""
         if self.world == 1:
@@ -242,12 +277,35 @@ class ZeroEngine:
         dist.all_reduce(vec, group=self.group)
         return vec.mul_(scale) if scale != 1.0 else vec
 
+    def _raise_timeout(self, s: int):
+        self.status.zero_()
+        raise CommTimeout(f"rank {self.rank}: wait on peer {(s >> 8) & 0xff} timed out at site {(s >> 16) & 0xff}")
+
     def check(self):
         """Raise if a device-side wait timed out since the last check (reads one int from the device)."""
         s = int(self.status.item())
         if s & 0xff:
-            self.status.zero_()
-            raise CommTimeout(f"rank {self.rank}: wait on peer {(s >> 8) & 0xff} timed out at site {(s >> 16) & 0xff}")
+            self._raise_timeout(s)
+
+    def _poll_status(self):
+        """Called before a step is launched: looks at the copy of the status word that the previous step left in pinned host
+        memory.  Once a wait has timed out the kernels that update optimizer state return without touching it (they read the
+        status word), so no state is corrupted between the timeout and this raise.  Also asks the heartbeat, when one is given,
+        whether a peer stopped beating before any kernel that would wait for it is launched."""
+        if self.heartbeat is not None:
+            from .fault import guard_step
+            guard_step(self.heartbeat)
+        if self._status_event is not None and self._status_event.query():
+            self._status_event = None
+            s = int(self._status_host[0])
+            if s & 0xff:
+                self._raise_timeout(s)
+
+    def _publish_status(self):
+        if self.cuda and self.world > 1 and self._status_event is None:
+            self._status_host.copy_(self.status, non_blocking=True)
+            self._status_event = torch.cuda.Event()
+            self._status_event.record()
 
     # ------------------------------------------------------------------ step
     def zero_grad(self):
@@ -258,13 +316,13 @@ class ZeroEngine:
         b1, b2 = self.hp["betas"]
         return [self.hp["lr"], b1, b2, self.hp["eps"], self.hp["weight_decay"], 1 - b1 ** step_no, 1 - b2 ** step_no, 1.0 / self.world]
 
-    def _flat_fused_segment(self, b: int, e: int, so: int, f: List[float]):
+    def _flat_fused_segment(self, b: int, e: int, so: int, f: List[float], dyn=None):
         """Fused reduce-scatter + step + all-gather kernel on the owned flat range [b, e), whose state starts at ``so``."""
         nvls = self.nvls
         _build.require().dist_fused_flat_step(FLAT_OPTIMIZERS[self.name], _DT[self.pdtype], _DT[self.pdtype], self.gbuf.peer_ptrs,
                                               self.pbuf.peer_ptrs, self.rank, b, e - b, f, self.master[so:], self.m[so:],
                                               self.v[so:] if self.v is not None else None, nvls,
-                                              self.gbuf.multicast_ptr if nvls else 0, self.pbuf.multicast_ptr if nvls else 0)
+                                              self.gbuf.multicast_ptr if nvls else 0, self.pbuf.multicast_ptr if nvls else 0, dyn)
         self.launches += 1
 
     def _flat_host_segment(self, b: int, e: int, so: int, step_no: int):
@@ -342,6 +400,71 @@ class ZeroEngine:
                             dist.broadcast(self.pbuf.tensor[b:e], src=rr, group=self.group)
         self._barrier(2)                                              # every rank's parameters are complete
 
+    # ------------------------------------------------------------------ device step: host part, kernel sequence, host part
+    def _host_pre(self, metrics: dict):
+        """Host side of a device step: schedules and counters, then ONE tiny kernel that writes this step's scalars (barrier
+        epoch base, learning rate, weight decay, per-tensor bias corrections) into the device table."""
+        from ..ops import sg2 as sg2_ops
+        C = _build.require()
+        base = self.epoch
+        if self.world > 1:
+            self.epoch += 2                                           # the two barriers of the step use base + 1 and base + 2
+        if self.flat_mode:
+            self.steps += 1
+            f = self._flat_args(self.steps)
+            C.write_table(self.dyn, [base & 0xffffffff, 0, 0, 0, 0, 0, 0, 0], [f[0], f[4], 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, f[5], f[6]])
+            self.launches += 1
+            return
+        if self.own_idx:
+            idx, per, hp = self.opt._prepare_step(**metrics)
+            self._step_hp = (idx, hp)
+            sg2_ops.refresh_weights(self.opt, self.device)
+            sg2_ops.write_scalars(self.opt, per, lr=hp["lr"], wd_eff=hp["wd_eff"], dev=self.device, epoch_base=base)
+        else:
+            self.opt._global_step += 1
+            C.write_table(self.dyn, [base & 0xffffffff], [])
+        self.launches += 1
+
+    def _device_step(self, hook=None):
+        """The kernels of a step, identical every step (safe to capture): barrier, sharded step with the reduce-scatter in its
+        first kernel and the all-gather in its last, barrier."""
+        stage = hook                                                  # None: the pipeline is enqueued without phase marks
+        hook = hook or (lambda _n: None)
+        self._barrier_dyn(1, 1)                                       # every rank's backward has written its gradients
+        hook("barrier")
+        if self.flat_mode:
+            f = self._flat_args(1)
+            for b, e, so in self.segments:
+                self._flat_fused_segment(b, e, so, f, dyn=self.dyn)
+            hook("reduce+step+gather")
+        elif self.own_idx:
+            from ..ops import sg2 as sg2_ops
+            idx, hp = self._step_hp
+            sg2_ops.launch(self.opt, idx, beta2=hp["beta2"], eps=hp["eps"], clip=hp["clip"],
+                           pull=(self.gbuf.peer_ptrs, self.rank, 1.0 / self.world), status=self.status, stage_hook=stage)
+        self._barrier_dyn(2, 2)                                       # every rank's parameters are complete
+        hook("barrier2")
+
+    def _host_post(self):
+        if self.name == "supergrok2":
+            if self.own_idx:
+                self.opt._after_step()
+            self._recycle_if_due()
+        self._publish_status()
+
+    def _recycle_if_due(self):
+        """Expert recycling is driven here so that every rank does it at the same step on the same counts: each rank routed only
+        the tensors it owns, so the 144 activation counts are summed over the ranks first (deterministic slot all-reduce)."""
+        self._v2_steps = getattr(self, "_v2_steps", 0) + 1
+        ri = self.opt.meta_net.recycle_interval
+        if ri > 0 and self._v2_steps % ri == 0:
+            counts = self.opt.meta_net.expert_counts
+            if self.world > 1:
+                cf = counts.float()
+                self.all_reduce_small(cf)
+                counts.copy_(cf.clamp_(max=2.0e9).to(counts.dtype))
+            self.opt.recycle_dead_experts()
+
     @torch.no_grad()
     def step(self, **metrics):
         W, r = self.world, self.rank
@@ -352,14 +475,14 @@ class ZeroEngine:
             if not self._armed:                                       # step() after a backward that train_step did not drive
                 self._arm()
             return self._finish_overlapped_step()
-        self._barrier(1)                                              # every rank's backward has written its gradients
-        if self.flat_mode and fused:
-            self.steps += 1
-            f = self._flat_args(self.steps)
-            for b, e, so in self.segments:
-                self._flat_fused_segment(b, e, so, f)
-            self._barrier(2)
+        if self.cuda:
+            self._poll_status()
+        if self.device_step:
+            self._host_pre(metrics)
+            self._device_step()
+            self._host_post()
             return
+        self._barrier(1)                                              # every rank's backward has written its gradients
         # ---- reduce-scatter
         if fused:
             if n_own:
@@ -384,19 +507,7 @@ class ZeroEngine:
                 self.opt.step(**metrics)
             else:
                 self.opt._global_step += 1
-            # Expert recycling is driven here so that every rank does it at the same step on the same counts: each rank routed only
-            # the tensors it owns, so the 144 activation counts are summed over the ranks first (deterministic slot all-reduce).
-            self._v2_steps = getattr(self, "_v2_steps", 0) + 1
-            ri = self.opt.meta_net.recycle_interval
-            if ri > 0 and self._v2_steps % ri == 0:
-                counts = self.opt.meta_net.expert_counts
-                if W > 1:
-                    cf = counts.float()
-                    self.all_reduce_small(cf)
-                    counts.copy_(cf.clamp_(max=2.0e9).to(counts.dtype))
-                self.opt.recycle_dead_experts()
-            if not (fused and W > 1):
-                pass                                                  # parameters were written in place by the element kernel
+            self._recycle_if_due()
         else:
             for mv, g in zip(self.master_views, self.grad_views):
                 mv.grad = g
@@ -424,6 +535,7 @@ class ZeroEngine:
                 if e > b:
                     dist.broadcast(self.pbuf.tensor[b:e], src=rr, group=self.group)
         self._barrier(2)                                              # every rank's parameters are complete
+        self._publish_status()
 
     def _fwd_bwd(self, x: torch.Tensor, y: torch.Tensor, micro_batches: int) -> torch.Tensor:
         """Zero the flat gradient buffer, then forward + loss + backward of every micro-batch (gradients accumulate in the buffer)."""
@@ -446,16 +558,23 @@ class ZeroEngine:
             total = loss.detach() if total is None else total + loss.detach()
         return total
 
-    def _fwd_bwd_graphed(self, x: torch.Tensor, y: torch.Tensor, micro_batches: int) -> torch.Tensor:
-        """Forward + backward through a CUDA graph captured per (shape, dtype, micro-batch count).  The first ``graph_warmup``
-        calls of a shape run eagerly (lazy initialisation, workspace growth); a capture that fails switches graphs off."""
-        key = (tuple(x.shape), x.dtype, tuple(y.shape), y.dtype, micro_batches, self.model.training)
+    def _fwd_bwd_graphed(self, x: torch.Tensor, y: torch.Tensor, micro_batches: int, with_step: bool = False) -> torch.Tensor:
+        """Forward + backward (and, ``with_step``, the kernels of the sharded step) through a CUDA graph captured per
+        (shape, dtype, micro-batch count).  The first ``graph_warmup`` calls of a shape run eagerly (lazy initialisation,
+        workspace growth); a capture that fails switches graphs off.  Every rank captures at the same call, and the barriers
+        inside the graph take their epochs from the device table, so a replay is a complete step."""
+        def body(xx, yy):
+            total = self._fwd_bwd(xx, yy, micro_batches)
+            if with_step:
+                self._device_step()
+            return total
+        key = (tuple(x.shape), x.dtype, tuple(y.shape), y.dtype, micro_batches, self.model.training, with_step)
         entry = self._graphs.get(key)
         if entry is None:
             seen = self._graph_seen.get(key, 0)
             self._graph_seen[key] = seen + 1
             if seen < self.graph_warmup:
-                return self._fwd_bwd(x.to(self.device, non_blocking=True), y.to(self.device, non_blocking=True), micro_batches)
+                return body(x.to(self.device, non_blocking=True), y.to(self.device, non_blocking=True))
             sx = torch.empty(x.shape, dtype=x.dtype, device=self.device)
             sy = torch.empty(y.shape, dtype=y.dtype, device=self.device)
             sx.copy_(x, non_blocking=True)
@@ -466,16 +585,16 @@ class ZeroEngine:
                 g = torch.cuda.CUDAGraph()
                 l0 = C.launch_count()
                 with torch.cuda.graph(g):
-                    total = self._fwd_bwd(sx, sy, micro_batches)
+                    total = body(sx, sy)
                 entry = (g, sx, sy, total, C.launch_count() - l0)
                 C.add_launches(-entry[4])                             # enqueued for the capture only; counted again at every replay
                 self._graphs[key] = entry
             except Exception as exc:  # noqa: BLE001
                 import warnings
-                warnings.warn(f"CUDA graph capture of forward/backward failed ({type(exc).__name__}: {exc}); running eagerly")
+                warnings.warn(f"CUDA graph capture of the step failed ({type(exc).__name__}: {exc}); running eagerly")
                 self.use_graph = False
                 torch.cuda.synchronize(self.device)
-                return self._fwd_bwd(x.to(self.device, non_blocking=True), y.to(self.device, non_blocking=True), micro_batches)
+                return body(x.to(self.device, non_blocking=True), y.to(self.device, non_blocking=True))
         g, sx, sy, total, n_launch = entry
         sx.copy_(x, non_blocking=True)
         sy.copy_(y, non_blocking=True)
@@ -487,6 +606,13 @@ class ZeroEngine:
     def train_step(self, x: torch.Tensor, y: torch.Tensor, micro_batches: int = 1, **metrics) -> torch.Tensor:
         """Host (pinned) or device batch in, loss tensor out: H2D copy, forward, backward, sharded fused step.
         ``micro_batches`` > 1 splits the batch and accumulates gradients in the flat buffer (activation memory)."""
+        if self.use_graph and self.cuda and self.device_step:
+            # the whole step is one graph launch: host work is the schedule update and one table-writing kernel
+            self._poll_status()
+            self._host_pre(metrics)
+            total = self._fwd_bwd_graphed(x, y, micro_batches, with_step=True)
+            self._host_post()
+            return total
         if self.use_graph and self.cuda:
             total = self._fwd_bwd_graphed(x, y, micro_batches)
         else:
@@ -496,6 +622,25 @@ class ZeroEngine:
             total = self._fwd_bwd(x, y, micro_batches)
         self.step(**metrics)
         return total
+
+    def profile_step(self, x: torch.Tensor, y: torch.Tensor, micro_batches: int = 1, **metrics) -> Dict[str, float]:
+        """One eager step with CUDA events between its phases; returns milliseconds per phase on this rank.  The launches are
+        queued behind a short device-side delay so that the phases run back to back, as they do when replayed from the graph
+        (the host needs longer to enqueue the ~300 kernels of forward / backward than the GPU needs to run them)."""
+        assert self.cuda and self.device_step, "per-phase timing covers the device step (in-kernel collectives)"
+        from ..utils.timers import StepTimer
+        timer = StepTimer()
+        x, y = x.to(self.device), y.to(self.device)
+        self._poll_status()
+        self._host_pre(metrics)
+        torch.cuda.synchronize(self.device)
+        torch.cuda._sleep(int(3e7))
+        timer.start()
+        self._fwd_bwd(x, y, micro_batches)
+        timer.mark("fwd+bwd")
+        self._device_step(hook=timer.mark)
+        self._host_post()
+        return timer.finish()
 
     # ------------------------------------------------------------------ introspection
     def state_bytes(self) -> int:

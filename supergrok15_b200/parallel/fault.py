@@ -46,8 +46,15 @@ class Heartbeat:
         self._stop.set()
 
     def last_seen(self, r: int) -> Optional[float]:
+        """Time of rank r's last beat, or None if it never beat.  A ``torch.distributed`` store blocks in ``get`` until the key
+        exists (up to the store's timeout, minutes by default), so the key is looked up with ``check`` first where the store
+        has it: a peer that never joined is reported at once."""
         try:
-            return float(self.store.get(self._key(r)).decode())
+            check = getattr(self.store, "check", None)
+            if check is not None and not check([self._key(r)]):
+                return None
+            v = self.store.get(self._key(r))
+            return float(v.decode() if isinstance(v, (bytes, bytearray)) else v)
         except Exception:  # noqa: BLE001
             return None
 

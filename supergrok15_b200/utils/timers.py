@@ -31,6 +31,30 @@ class StepTimer:
             torch.cuda.nvtx.range_pop()
             self._ev[name].append((e0, e1))
 
+    # ---- consecutive phases of one step: start(), mark(name) after each phase, finish() -> {name: ms} on this rank
+    def start(self):
+        self._marks = []
+        if self.enabled:
+            e = torch.cuda.Event(enable_timing=True)
+            e.record()
+            self._marks.append((None, e))
+
+    def mark(self, name: str):
+        if self.enabled:
+            e = torch.cuda.Event(enable_timing=True)
+            e.record()
+            self._marks.append((name, e))
+
+    def finish(self) -> Dict[str, float]:
+        if not self.enabled or not getattr(self, "_marks", None):
+            return {}
+        torch.cuda.synchronize()
+        out: Dict[str, float] = {}
+        for (_, a), (name, b) in zip(self._marks[:-1], self._marks[1:]):
+            out[name] = out.get(name, 0.0) + a.elapsed_time(b)
+        self._marks = []
+        return out
+
     def summary(self, reset: bool = True) -> Dict[str, float]:
         if not self.enabled:
             return {}

@@ -118,13 +118,71 @@ def test_truncated_shard_is_detected(tmp_path):
     e1.train_step(x, y)
     checkpoint.save(e1, str(tmp_path))
     assert checkpoint.verify(str(tmp_path)) == []
-    f = tmp_path / "rank_0.pt"
+    f = __import__("pathlib").Path(checkpoint.resolve(str(tmp_path))) / "rank_0.pt"
     payload = torch.load(f, weights_only=False)
     next(iter(payload["tensors"].values()))["master"][0] += 1.0        # silent corruption of one value
     torch.save(payload, f)
     assert checkpoint.verify(str(tmp_path)) == [0]
     f.write_bytes(f.read_bytes()[:100])                                # truncated file
     assert checkpoint.verify(str(tmp_path)) == [0]
+
+
+def test_save_interrupted_before_the_manifest_keeps_the_previous_checkpoint(tmp_path, monkeypatch):
+    """A rank that dies between its shard and the manifest (modelled by an exception at that point of ``save``) leaves ``latest``
+    on the previous, complete save; its m / v / optimizer state are covered by the checksum, not only the master weights."""
+    e1, x, y = _engine("grokadamw")
+    e1.train_step(x, y)
+    d1 = checkpoint.save(e1, str(tmp_path))
+    want = torch.cat([p.detach().reshape(-1).clone() for p in e1.params])
+    e1.train_step(x, y)
+
+    def die(_engine):
+        raise KeyboardInterrupt("rank killed mid-save")
+    monkeypatch.setattr(checkpoint, "_before_manifest", die)
+    with pytest.raises(KeyboardInterrupt):
+        checkpoint.save(e1, str(tmp_path))
+    monkeypatch.undo()
+    assert checkpoint.resolve(str(tmp_path)) == d1 and checkpoint.verify(str(tmp_path)) == []
+    e2, _, _ = _engine("grokadamw")
+    checkpoint.load(e2, str(tmp_path))
+    assert torch.equal(torch.cat([p.detach().reshape(-1) for p in e2.params]), want)
+    # a flipped value in an optimizer moment (not a master weight) is caught
+    f = __import__("pathlib").Path(d1) / "rank_0.pt"
+    payload = torch.load(f, weights_only=False)
+    st = next(iter(payload["tensors"].values()))["state"]
+    st["exp_avg"].view(-1)[0] += 1.0
+    torch.save(payload, f)
+    assert checkpoint.verify(str(tmp_path)) == [0]
+    with pytest.raises(RuntimeError, match="corrupted"):
+        checkpoint.load(e2, str(tmp_path))
+
+
+def test_a_timed_out_step_is_not_followed_by_a_save(tmp_path):
+    """The status word of the collectives says that a wait on a peer ran out: ``save`` raises before it writes anything, and
+    the next step raises before it launches anything."""
+    from supergrok15_b200.parallel import CommTimeout
+    e1, x, y = _engine("supergrok2")
+    e1.train_step(x, y)
+    e1.status.fill_(1 | (1 << 8) | (2 << 16))
+    with pytest.raises(CommTimeout, match="peer 1"):
+        checkpoint.save(e1, str(tmp_path))
+    assert not any(tmp_path.iterdir())
+    e1.train_step(x, y)                                            # the raise cleared the word: training can go on after a reload
+
+
+def test_heartbeat_on_a_real_store_reports_a_rank_that_never_joined_at_once():
+    """``TCPStore.get`` blocks until the key exists; the heartbeat must not: a peer that never joined is reported within its timeout."""
+    from datetime import timedelta
+    import torch.distributed as dist
+    store = dist.TCPStore("127.0.0.1", _free_port(), 1, True, timeout=timedelta(seconds=30))
+    a = Heartbeat(store, 0, 2, interval_s=0.05).start()
+    t0 = time.time()
+    assert a.dead_peers(timeout_s=0.3) == [1]
+    assert time.time() - t0 < 5.0
+    b = Heartbeat(store, 1, 2, interval_s=0.05).start()
+    time.sleep(0.2)
+    assert a.dead_peers(timeout_s=0.5) == []
+    a.stop(); b.stop()
 
 
 class _DictStore:

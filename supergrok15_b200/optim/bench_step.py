@@ -104,6 +104,16 @@ def main():
             for _ in range(2):
                 bilevel()
             out["bilevel_ms"] = timeit(bilevel, max(3, a.steps // 4))
+            if a.kernels:
+                from torch.profiler import ProfilerActivity, profile
+                with profile(activities=[ProfilerActivity.CUDA]) as prof:
+                    bilevel()
+                    torch.cuda.synchronize()
+                rows = sorted((e for e in prof.key_averages() if e.device_time_total > 0), key=lambda e: -e.device_time_total)
+                tot = sum(e.device_time_total for e in rows)
+                out["bilevel_device_ms"] = round(tot / 1e3, 3)
+                out["bilevel_kernels_us"] = [[e.key.replace("(anonymous namespace)::", "")[:56], round(e.device_time_total, 1), e.count,
+                                              round(100 * e.device_time_total / tot, 1)] for e in rows[:16]]
         except Exception as e:  # noqa: BLE001
             out["bilevel_error"] = f"{type(e).__name__}: {str(e)[:200]}"
     print(json.dumps(out))

@@ -292,13 +292,18 @@ class Mamba3PEERMetaNet(nn.Module):
         """Everything after the scan of ``forward_for_bilevel`` (GRU, soft top-k routing, experts) for elements whose
         contexts are given: returns smart_grad [n].  Element-wise over n, so it can be applied to any slice."""
         gs = torch.stack([g, s], dim=-1)
-        # SG_BILEVEL_TAIL=native (opt-in): the GRU and the product-key routing run as native kernels each way (ops/sg2_bilevel.py:
-        # gru, routing) instead of the PyTorch statements below
-        native_tail = os.environ.get("SG_BILEVEL_TAIL", "torch") == "native" and g.dtype == torch.float32 and fwd_ctx.dtype == torch.float32
-        gru_in = torch.cat([gs, fwd_ctx, bwd_ctx], dim=-1)
+        # On CUDA the GRU and the product-key routing run as native kernels each way (ops/sg2_bilevel.py: gru, routing) when the
+        # shapes are the ones they are built for; SG_BILEVEL_TAIL=torch keeps the PyTorch statements below, =native also takes
+        # the C++ loops on CPU
+        mode = os.environ.get("SG_BILEVEL_TAIL", "native" if g.is_cuda else "torch")
+        native_tail = mode == "native" and g.dtype == torch.float32 and fwd_ctx.dtype == torch.float32
         if native_tail:
             from ..ops import sg2_bilevel as _sb
-            assert _sb.gru_supported(gru_in.shape[1], self.gru_hidden), "SG_BILEVEL_TAIL=native: unsupported GRU shape"
+            native_tail = (_sb.gru_supported(2 + fwd_ctx.shape[1] + bwd_ctx.shape[1], self.gru_hidden) and
+                           _sb.routing_supported(self.num_peer_heads, self.gru_hidden + fwd_ctx.shape[1] + bwd_ctx.shape[1] + 2,
+                                                 self.pk_dim, self.d_model, topk))
+        gru_in = torch.cat([gs, fwd_ctx, bwd_ctx], dim=-1)
+        if native_tail:
             Wg = torch.stack([self.gru.W_z.weight, self.gru.W_r.weight, self.gru.W_h.weight])
             bg = torch.stack([self.gru.W_z.bias, self.gru.W_r.bias, self.gru.W_h.bias])
             new_gru = _sb.gru(gru_in, gru_state.float(), Wg, bg)
@@ -322,7 +327,6 @@ class Mamba3PEERMetaNet(nn.Module):
         Wq = torch.cat([lin.weight for lin in self.peer_queries], 0)                                # [H * d_model, peer_in]
         if native_tail:
             # queries, scores, top-4 and softmax of all heads in one native kernel each way
-            assert _sb.routing_supported(H, peer_in.shape[1], pk, self.d_model, topk), "SG_BILEVEL_TAIL=native: unsupported routing shape"
             ia, ib, wa, wb = _sb.routing(peer_in, Wq, torch.stack(list(self.product_keys_A)), torch.stack(list(self.product_keys_B)))
         else:
             q = peer_in @ Wq.T                                                                      # [n, H * d_model]

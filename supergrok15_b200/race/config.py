@@ -28,8 +28,8 @@ DEFAULT_CONFIG: Dict = {
 OPTIMIZER_CONFIGS: Dict[str, Dict] = {
     "adamw": {"weight_decay": 1.0},
     "grokadamw": {"weight_decay": 1.0, "grokadamw_alpha": 0.98, "grokadamw_lamb": 5.0, "grokadamw_grad_clip": 1.0},
-    "neuralgrok": {"weight_decay": 1.0, "neuralgrok_alpha": 10.0, "neuralgrok_beta": 4.0, "neuralgrok_hidden": 128,
-                   "neuralgrok_layers": 3, "neuralgrok_inner_lr": 1e-3},
+    "neuralgrok": {"weight_decay": 1.0, "neural_alpha": 10.0, "neural_beta": 4.0, "neural_layers": 3, "neural_hidden": 128,
+                   "inner_steps": 1},
     "supergrok11": {"weight_decay": 1.0, "supergrok11_lamb": 5.0, "supergrok11_gate_temperature": 5.0,
                     "supergrok11_alpha_update_freq": 50, "supergrok11_meta_freq": 5, "supergrok11_sam_freq": 10},
     "supergrok15": {"weight_decay": 1.0, "supergrok15_lamb": 2.0, "supergrok15_alpha_update_freq": 50},

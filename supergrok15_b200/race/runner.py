@@ -52,14 +52,40 @@ def _gpu_worker(gpu: int, tasks, results, base_cfg):
 
 def run_pipeline(base_cfg: Optional[dict] = None, optimizers: Sequence[str] = ALL_OPTIMIZERS, seeds: Sequence[int] = (42,),
                  device: str = "auto", gpus: Optional[List[int]] = None, save_dir: Optional[str] = "results", plot: bool = True,
-                 verbose: bool = True, result_timeout: float = 7200.0) -> Dict[str, List[TrainResult]]:
+                 verbose: bool = True, result_timeout: float = 7200.0, resume: bool = False) -> Dict[str, List[TrainResult]]:
+    """``resume``: every finished (optimizer, seed) job is appended to ``<save_dir>/progress_<model>_ft<pct>.json`` as soon as it
+    ends; a later call with ``resume=True`` and the same cell (model type, split) takes those results from the file and runs only
+    the jobs that are missing (a race of 11 optimizers x 5 seeds x 20,000 steps that was interrupted does not start over)."""
     c = copy.deepcopy(DEFAULT_CONFIG)
     c.update(COMMON)
     c.update(base_cfg or {})
     t0 = time.time()
     tasks = [(n, s) for n in optimizers for s in seeds]
-    status.reset(len(tasks))
     rbo: Dict[str, List[TrainResult]] = {n: [] for n in optimizers}
+    prog_path = os.path.join(save_dir, f"progress_{c.get('model_type', 'decoder')}_ft{int(c.get('frac_train', 0.5) * 100)}.json") if save_dir else None
+    done: Dict[str, dict] = {}
+    if resume and prog_path and os.path.exists(prog_path):
+        with open(prog_path) as f:
+            done = json.load(f)
+        for n, s in tasks:
+            if f"{n}/{s}" in done:
+                rbo[n].append(TrainResult.from_dict(n, done[f"{n}/{s}"]))
+        tasks = [(n, s) for n, s in tasks if f"{n}/{s}" not in done]
+        if verbose:
+            print(f"  resuming: {len(done)} finished jobs found in {prog_path}, {len(tasks)} to run", flush=True)
+    elif prog_path and os.path.exists(prog_path):
+        os.remove(prog_path)                                    # a fresh run does not inherit an older run's jobs
+
+    def record(name, seed, res):
+        if prog_path is None or res is None:
+            return
+        os.makedirs(save_dir, exist_ok=True)
+        done[f"{name}/{seed}"] = res.to_dict()
+        tmp = prog_path + ".tmp"
+        with open(tmp, "w") as f:
+            json.dump(done, f)
+        os.replace(tmp, prog_path)
+    status.reset(len(tasks))
     multi = gpus is not None and len(gpus) > 1 and torch.cuda.is_available()
     if multi:
         import torch.multiprocessing as mp
@@ -80,6 +106,7 @@ def run_pipeline(base_cfg: Optional[dict] = None, optimizers: Sequence[str] = AL
                 break
             if res is not None:
                 rbo[name].append(res)
+                record(name, seed, res)
             status.job_done(name, seed, {"grok": res.grokking_step} if res else None, err)
         for p in procs:
             p.join(60)
@@ -93,6 +120,7 @@ def run_pipeline(base_cfg: Optional[dict] = None, optimizers: Sequence[str] = AL
             try:
                 res = _run_one(name, seed, c, dev, status.update)
                 rbo[name].append(res)
+                record(name, seed, res)
                 status.job_done(name, seed, {"grok": res.grokking_step})
                 if verbose:
                     print(f"  {DISPLAY_NAMES.get(name, name):<14} seed {seed:<5} steps {res.total_steps:>6} grok {res.grokking_step} "
@@ -201,7 +229,7 @@ def main(argv=None):
     ap.add_argument("--reference-compat", action="store_true", help="reproduce the reference's SAM / bias-correction / amplifier quirks")
     ap.add_argument("--cuda-graph", action="store_true")
     ap.add_argument("--save-dir", default="results")
-    ap.add_argument("--world-size", type=int, default=1, help="(reserved) data-parallel ranks per run; the race itself is one GPU per job")
+    ap.add_argument("--resume", action="store_true", help="skip the (optimizer, seed) jobs already recorded in the save directory's progress file")
     a = ap.parse_args(argv)
     if a.setup:
         from .. import _build
@@ -221,7 +249,7 @@ def main(argv=None):
         except OSError:
             pass
     status.ntfy(a.ntfy, f"race started: mode {a.mode}, {len(opts)} optimizers, {len(seeds)} seeds")
-    kw = dict(optimizers=opts, seeds=seeds, gpus=gpus if gpus and len(gpus) > 1 else None, save_dir=a.save_dir)
+    kw = dict(optimizers=opts, seeds=seeds, gpus=gpus if gpus and len(gpus) > 1 else None, save_dir=a.save_dir, resume=a.resume)
     if a.mode == "A":
         run_pipeline(base, **kw)
     elif a.mode == "B":

@@ -40,6 +40,14 @@ class TrainResult:
                                               "total_steps", "grokking_step", "grokking_wall", "final_val_acc", "final_train_acc",
                                               "model_type", "frac_train", "events", "step_ms")}
 
+    @classmethod
+    def from_dict(cls, name: str, d: Dict) -> "TrainResult":
+        r = cls(name, d.get("seed", 42), d.get("model_type", "decoder"), d.get("frac_train", 0.5))
+        for k, v in d.items():
+            if k in cls.__slots__:
+                setattr(r, k, v)
+        return r
+
 
 class EarlyStopper:
     """Records the first evaluation with val_acc >= threshold; stops after `patience` consecutive qualifying evaluations."""

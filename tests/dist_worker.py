@@ -51,7 +51,8 @@ def run(rank, world, port, optimizer, out_path, device, comm, steps, dtype):
     else:
         dist.gather(flat, gathered, dst=0)
     if rank == 0:
-        torch.save({"params": gathered, "losses": losses, "owner": eng.owner, "buckets": len(eng.buckets)}, out_path)
+        torch.save({"params": gathered, "losses": losses, "owner": eng.owner, "buckets": len(eng.buckets), "graphs": len(eng._graphs),
+                    "device_step": bool(getattr(eng, "device_step", False))}, out_path)
     dist.barrier()
     dist.destroy_process_group()
 

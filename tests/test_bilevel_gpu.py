@@ -134,12 +134,6 @@ def test_soft_head_expert_kernel_matches_dense_path(monkeypatch):
         assert (gk - gd).abs().max() <= 1e-3 * gd.abs().max() + 1e-9, (k, float((gk - gd).abs().max()), float(gd.abs().max()))
 
 
-_TAIL_GPU = pytest.mark.skipif(__import__("os").environ.get("SG_TEST_TAIL_GPU") != "1",
-                               reason="the GRU and routing kernels (csrc/sg2_gru.cu, csrc/sg2_routing.cu) are opt-in (SG_BILEVEL_TAIL=native); "
-                                      "set SG_TEST_TAIL_GPU=1 to test them")
-
-
-@_TAIL_GPU
 @pytest.mark.parametrize("n,IN", [(1, 18), (1000, 18), (70001, 18), (300, 10)])
 def test_gru_kernels_match_cpu_loop(n, IN):
     """The CUDA GRU kernels against the C++ CPU loop over the same per-element functions (csrc/sg2_gru_math.h)."""
@@ -157,7 +151,6 @@ def test_gru_kernels_match_cpu_loop(n, IN):
         assert (a - b_).abs().max() <= 1e-3 * a.abs().max() + 1e-6
 
 
-@_TAIL_GPU
 @pytest.mark.parametrize("n,heads,P,pk", [(1, 4, 22, 12), (1000, 4, 22, 12), (70001, 4, 22, 12), (333, 2, 14, 8)])
 def test_routing_kernels_match_cpu_loop(n, heads, P, pk):
     """The CUDA routing kernels against the C++ CPU loop over the same per-element functions (csrc/sg2_routing_math.h)."""

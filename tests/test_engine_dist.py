@@ -101,13 +101,17 @@ def test_bucket_layout_covers_the_flat_buffer():
         assert all(b % 8 == 0 and e % 8 == 0 for b, e in sl)
 
 
+def _need_gpus(n):
+    if torch.cuda.device_count() < n:
+        pytest.skip(f"needs {n} GPUs")
+
+
 @pytest.mark.gpu
 @pytest.mark.dist
 @pytest.mark.parametrize("comm", ["p2p", "nccl", "nvls"])
 @pytest.mark.parametrize("optimizer", ["supergrok2", "adamw", "grokadamw"])
 def test_sharded_equals_unsharded_gpu(optimizer, comm):
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs 2 GPUs")
+    _need_gpus(2)
     steps = 2
     res = _launch(2, optimizer, "cuda", comm, steps)
     ref = dist_worker.reference_run(optimizer, steps, device="cuda")
@@ -118,12 +122,30 @@ def test_sharded_equals_unsharded_gpu(optimizer, comm):
 
 @pytest.mark.gpu
 @pytest.mark.dist
-@pytest.mark.skipif(os.environ.get("SG_TEST_OVERLAP_GPU") != "1",
-                    reason="bucketed overlap on GPUs (side stream + per-bucket barrier and fused kernel) is opt-in: set SG_TEST_OVERLAP_GPU=1")
+@pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("optimizer", ["supergrok2", "adamw"])
+def test_whole_step_graph_sharded_equals_unsharded_gpu(optimizer, world):
+    """Five steps with the in-kernel collectives: three eager ones, then the whole step (forward, backward, barrier, gradient
+    pull + sharded optimizer + parameter push, barrier) is captured into one CUDA graph on every rank and replayed.  The
+    parameters of every rank must equal those of the plain optimizer on the full batch, and one another bit for bit."""
+    _need_gpus(world)
+    steps = 5
+    res = _launch(world, optimizer, "cuda", "p2p", steps)
+    assert res["graphs"] == 1 and res["device_step"]
+    ref = dist_worker.reference_run(optimizer, steps, device="cuda")
+    for got in res["params"]:
+        assert torch.allclose(got, ref, rtol=1e-3, atol=1e-5), (got - ref).abs().max()
+    assert all(torch.equal(res["params"][0], p) for p in res["params"])
+    assert len(set(res["owner"])) == (1 if optimizer == "adamw" else min(world, 18))
+
+
+@pytest.mark.gpu
+@pytest.mark.dist
 @pytest.mark.parametrize("comm", ["p2p", "nccl"])
 @pytest.mark.parametrize("optimizer", ["adamw+overlap", "adamw+overlap2"])
 def test_bucketed_overlap_equals_unsharded_gpu(optimizer, comm):
-    world = min(torch.cuda.device_count(), 2)
+    _need_gpus(2)
+    world = 2
     steps = 3
     res = _launch(world, optimizer, "cuda", comm, steps)
     ref = dist_worker.reference_run("adamw", steps, device="cuda")

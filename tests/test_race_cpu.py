@@ -69,3 +69,28 @@ def test_reference_import_surface():
     for n in ("SuperGrok15", "SuperGrok11", "GrokAdamW", "NeuralGrok", "Prodigy", "Grokfast", "Lion", "LookSAM", "Muon",
               "CUDAGraphOptimizer", "SharpnessMetaNet"):
         assert hasattr(go, n)
+
+
+def test_resume_skips_finished_jobs(tmp_path):
+    """An interrupted race picks up where it stopped: finished (optimizer, seed) jobs come from the progress file."""
+    from supergrok15_b200.race import runner
+    base = dict(dim_model=32, num_heads=2, num_layers=1, max_steps=30, p=23, log_every=10)
+    kw = dict(save_dir=str(tmp_path), plot=False, verbose=False, device="cpu")
+    first = runner.run_pipeline(base, optimizers=["adamw"], seeds=[1, 2], **kw)
+    assert len(first["adamw"]) == 2
+    calls = []
+    orig = runner._run_one
+
+    def spy(name, seed, *a, **k):
+        calls.append((name, seed))
+        return orig(name, seed, *a, **k)
+    runner._run_one = spy
+    try:
+        again = runner.run_pipeline(base, optimizers=["adamw", "lion"], seeds=[1, 2], resume=True, **kw)
+    finally:
+        runner._run_one = orig
+    assert calls == [("lion", 1), ("lion", 2)]                       # the two AdamW jobs were not run again
+    assert len(again["adamw"]) == 2 and len(again["lion"]) == 2
+    assert again["adamw"][0].train_losses == first["adamw"][0].train_losses
+    assert runner.main(["--no-status-server", "--optimizers", "adamw", "--seeds", "1", "--max-steps", "5", "--save-dir", str(tmp_path / "cli"),
+                        "--resume"]) == 0

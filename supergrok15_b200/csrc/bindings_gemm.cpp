@@ -9,7 +9,8 @@ int gemm_bf16_tn(const void* A, int lda, const void* B, int ldb, int M, int N, i
                  bool d_bf16, const void* bias, bool bias_bf16, float diag, int act, void* C, int ldc, bool c_bf16, void* C2, int ldc2,
                  float* splitk_ws, int64_t splitk_ws_floats, int* err, cudaStream_t s, bool a_t, bool b_t);
 int gemm_bf16_tn_allgather(const void* A, int lda, const PeerPtrs& w_peers, int rank, int world, int M, int N, int K, void* C, int ldc,
-                           bool c_bf16, int* counters, void* sched, int epoch, int n_copy, int* err, cudaStream_t s);
+                           bool c_bf16, int* counters, void* sched, int epoch, int n_copy, int* err, cudaStream_t s, float alpha,
+                           float beta, const void* D, int ldd, bool d_bf16, float diag, int diag_off, void* C2, int ldc2);
 int gemm_bf16_tn_reducescatter(const void* A, int lda, const void* B, int ldb, int M, int N, int K, const PeerPtrs& slots, const PeerPtrs& flags,
                                int rank, int world, void* c_local, int ldc, int epoch, unsigned long long timeout_ns, int* err, cudaStream_t s);
 }
@@ -50,8 +51,10 @@ void gemm_tn(const Tensor& a, const Tensor& b, Tensor out, double alpha, double 
 
 // out = a @ Wfull.T where Wfull [N, K] is assembled inside the kernel from the row shards held by `world` ranks:
 // w_ptrs[r] is the address of rank r's [N, K] bf16 buffer (peer-mapped symmetric memory; w_ptrs[rank] is the local one).
+// Optional epilogue: out = alpha * acc + beta * d + diag * [m + diag_off == n]; out_t [N, M] receives the transposed result.
 void gemm_tn_allgather(const Tensor& a, const std::vector<int64_t>& w_ptrs, int64_t rank, int64_t N, Tensor out, Tensor counters, int64_t epoch,
-                       int64_t n_copy, Tensor err) {
+                       int64_t n_copy, Tensor err, double alpha, double beta, const c10::optional<Tensor>& d, double diag, int64_t diag_off,
+                       const c10::optional<Tensor>& out_t) {
     TORCH_CHECK(a.is_cuda() && a.scalar_type() == at::kBFloat16 && a.dim() == 2 && a.stride(1) == 1 && a.stride(0) % 8 == 0, "a must be bf16 [M,K]");
     const int world = (int)w_ptrs.size();
     TORCH_CHECK(world >= 1 && world <= sg::MAX_RANKS && rank >= 0 && rank < world, "bad rank / world");
@@ -68,9 +71,13 @@ void gemm_tn_allgather(const Tensor& a, const std::vector<int64_t>& w_ptrs, int6
     }
     c10::cuda::CUDAGuard guard(a.device());
     const bool c_bf16 = out.scalar_type() == at::kBFloat16;
+    if (d.has_value()) TORCH_CHECK(d->size(0) == M && d->size(1) == N && d->stride(1) == 1, "d must be [M,N]");
+    if (out_t.has_value()) TORCH_CHECK(out_t->size(0) == N && out_t->size(1) == M && out_t->stride(1) == 1 && out_t->scalar_type() == out.scalar_type(), "out_t must be [N,M] of out's dtype");
     const int rc = sg::gemm_bf16_tn_allgather(a.data_ptr(), (int)a.stride(0), w, (int)rank, world, M, (int)N, K, out.data_ptr(), (int)out.stride(0),
                                               c_bf16, counters.data_ptr<int>() + 2, counters.data_ptr<int>(), (int)epoch, (int)n_copy, err.data_ptr<int>(),
-                                              at::cuda::getCurrentCUDAStream());
+                                              at::cuda::getCurrentCUDAStream(), (float)alpha, (float)beta, d.has_value() ? d->data_ptr() : nullptr,
+                                              d.has_value() ? (int)d->stride(0) : 0, d.has_value() && d->scalar_type() == at::kBFloat16, (float)diag,
+                                              (int)diag_off, out_t.has_value() ? out_t->data_ptr() : nullptr, out_t.has_value() ? (int)out_t->stride(0) : 0);
     TORCH_CHECK(rc == 0, "gemm_tn_allgather launch failed (code ", rc, ")");
 }
 
@@ -103,6 +110,7 @@ void register_gemm(pybind11::module_& m) {
     m.def("gemm_tn_reducescatter", &gemm_tn_reducescatter, py::arg("a"), py::arg("b"), py::arg("slot_ptrs"), py::arg("flag_ptrs"), py::arg("rank"),
           py::arg("out"), py::arg("epoch"), py::arg("timeout_s"), py::arg("err"));
     m.def("gemm_tn_allgather", &gemm_tn_allgather, py::arg("a"), py::arg("w_ptrs"), py::arg("rank"), py::arg("N"), py::arg("out"),
-          py::arg("counters"), py::arg("epoch"), py::arg("n_copy"), py::arg("err"));
+          py::arg("counters"), py::arg("epoch"), py::arg("n_copy"), py::arg("err"), py::arg("alpha") = 1.0, py::arg("beta") = 0.0,
+          py::arg("d") = c10::nullopt, py::arg("diag") = 0.0, py::arg("diag_off") = 0, py::arg("out_t") = c10::nullopt);
 }
 }  // namespace sgb

@@ -28,6 +28,7 @@ struct Epilogue {
     int act;                       // 0 none, 1 gelu (erf), 2 silu
     int c_is_bf16;
     void* C2; int ldc2;            // optional second output: C2[n, m] = C[m, n] (transposed copy, same dtype)
+    int diag_off;                  // the identity is added where m + diag_off == n (a row block of a larger square matrix)
 };
 
 // All-gather fused into the GEMM (AG = true).  B (the weight, [N, K] row-major, K contiguous, ld == K) is sharded by rows over
@@ -394,7 +395,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tn_kernel(const __grid_c
                                                                        : reinterpret_cast<const float*>(ep.D)[(int64_t)row * ep.ldd + col]);
                                 v += bias_j;
                             }
-                            if (row == col) v += ep.diag;
+                            if (row + ep.diag_off == col) v += ep.diag;
                             if (ep.act == 1) v = 0.5f * v * (1.f + erff(v * 0.70710678f));
                             else if (ep.act == 2) v = v / (1.f + __expf(-v));
                             r[j] = __float_as_uint(v);
@@ -491,7 +492,7 @@ __global__ void __launch_bounds__(256) gemm_splitk_reduce_kernel(const float* __
     if (ep.D) v += ep.beta * (ep.d_is_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(ep.D)[(int64_t)row * ep.ldd + col])
                                            : reinterpret_cast<const float*>(ep.D)[(int64_t)row * ep.ldd + col]);
     if (ep.bias) v += ep.bias_is_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(ep.bias)[col]) : reinterpret_cast<const float*>(ep.bias)[col];
-    if (row == col) v += ep.diag;
+    if (row + ep.diag_off == col) v += ep.diag;
     if (ep.act == 1) v = 0.5f * v * (1.f + erff(v * 0.70710678f));
     else if (ep.act == 2) v = v / (1.f + __expf(-v));
     if (ep.c_is_bf16) reinterpret_cast<__nv_bfloat16*>(C)[(int64_t)row * ldc + col] = __float2bfloat16_rn(v);
@@ -568,7 +569,7 @@ int launch(const void* A, int lda, const void* B, int ldb, int M, int N, int K, 
     }
     Epilogue ep = ep_in;
     if (splits > 1) {
-        ep = Epilogue{1.f, 0.f, 0.f, nullptr, 0, 0, nullptr, 0, 0, 0, nullptr, 0};      // plain fp32 partial sums
+        ep = Epilogue{1.f, 0.f, 0.f, nullptr, 0, 0, nullptr, 0, 0, 0, nullptr, 0, 0};   // plain fp32 partial sums
         if (!make_map(&mc, ws, (int64_t)splits * Mpad, N, ldw, 32, 32, false)) return 4;
     } else if (!make_map(&mc, C, MODE == 2 ? M / ag.world : M, N, ldc, 32, ep.c_is_bf16 ? 64 : 32, ep.c_is_bf16 != 0)) return 4;
     constexpr size_t smem = (size_t)STAGES * (BM * BK * 2 + BN * BK * 2) + 4 * 2 * 4096 + 1024 + 256;
@@ -598,7 +599,7 @@ int gemm_bf16_tn(const void* A, int lda, const void* B, int ldb, int M, int N, i
                  bool d_bf16, const void* bias, bool bias_bf16, float diag, int act, void* C, int ldc, bool c_bf16, void* C2, int ldc2,
                  float* splitk_ws, int64_t splitk_ws_floats, int* err, cudaStream_t s, bool a_t, bool b_t) {
     if (M <= 0 || N <= 0 || K <= 0) return 0;
-    Epilogue ep{alpha, beta, diag, D, ldd, d_bf16 ? 1 : 0, bias, bias_bf16 ? 1 : 0, act, c_bf16 ? 1 : 0, C2, ldc2};
+    Epilogue ep{alpha, beta, diag, D, ldd, d_bf16 ? 1 : 0, bias, bias_bf16 ? 1 : 0, act, c_bf16 ? 1 : 0, C2, ldc2, 0};
     // the output goes through TMA: its base must be 16-byte aligned and its row pitch a multiple of 16 bytes
     if ((reinterpret_cast<uintptr_t>(C) & 15) != 0 || (ldc * (c_bf16 ? 2 : 4)) % 16 != 0) return 5;
     if (a_t && !b_t) return 7;                               // not instantiated (no caller needs A^T . B^T-free form)
@@ -615,12 +616,15 @@ int gemm_bf16_tn(const void* A, int lda, const void* B, int ldb, int M, int N, i
 // w_peers[r] is rank r's [N, K] bf16 buffer (contiguous rows); counters: int[ceil(N / 256)] in local memory, zeroed once by the
 // caller; sched: one 64-bit ticket counter, zeroed once by the caller; epoch counts the calls that used these counters (1, 2, ...)
 // and every call with the same counters must have the same M, N and grid.  N must be a multiple of world * 32.
+// Epilogue: C = alpha * acc + beta * D + diag * [m + diag_off == n], optional transposed copy C2 (the row-sharded Newton-Schulz
+// iteration of Muon builds its polynomial a I + b G + c G G and hands X on in both layouts from here).
 int gemm_bf16_tn_allgather(const void* A, int lda, const PeerPtrs& w_peers, int rank, int world, int M, int N, int K, void* C, int ldc,
-                           bool c_bf16, int* counters, void* sched, int epoch, int n_copy, int* err, cudaStream_t s) {
+                           bool c_bf16, int* counters, void* sched, int epoch, int n_copy, int* err, cudaStream_t s, float alpha,
+                           float beta, const void* D, int ldd, bool d_bf16, float diag, int diag_off, void* C2, int ldc2) {
     if (M <= 0 || N <= 0 || K <= 0) return 0;
     if (world < 1 || world > MAX_RANKS || N % (world * AG_ROWS) != 0 || K % 8 != 0) return 6;
     if ((reinterpret_cast<uintptr_t>(C) & 15) != 0 || (ldc * (c_bf16 ? 2 : 4)) % 16 != 0) return 5;
-    Epilogue ep{1.f, 0.f, 0.f, nullptr, 0, 0, nullptr, 0, 0, c_bf16 ? 1 : 0, nullptr, 0};
+    Epilogue ep{alpha, beta, diag, D, ldd, d_bf16 ? 1 : 0, nullptr, 0, 0, c_bf16 ? 1 : 0, C2, ldc2, diag_off};
     AgArgs ag{};
     ag.w = w_peers; ag.rank = rank; ag.world = world; ag.n_copy = world > 1 ? n_copy : 0; ag.counters = counters; ag.epoch = epoch;
     ag.sched = reinterpret_cast<unsigned long long*>(sched);
@@ -637,7 +641,7 @@ int gemm_bf16_tn_reducescatter(const void* A, int lda, const void* B, int ldb, i
                                int rank, int world, void* c_local, int ldc, int epoch, unsigned long long timeout_ns, int* err, cudaStream_t s) {
     if (M <= 0 || N <= 0 || K <= 0) return 0;
     if (world < 1 || world > MAX_RANKS || M % (world * BM) != 0 || N % 64 != 0 || ldc % 8 != 0) return 6;
-    Epilogue ep{1.f, 0.f, 0.f, nullptr, 0, 0, nullptr, 0, 0, 1, nullptr, 0};
+    Epilogue ep{1.f, 0.f, 0.f, nullptr, 0, 0, nullptr, 0, 0, 1, nullptr, 0, 0};
     AgArgs ag{};
     ag.w = slots; ag.aux = flags; ag.rank = rank; ag.world = world; ag.epoch = epoch; ag.m_tiles_loc = M / world / BM;
     ag.timeout_ns = timeout_ns; ag.c_local = c_local; ag.ldc = ldc;

@@ -1,0 +1,69 @@
+"""Row-sharded Newton-Schulz (collectives inside the tcgen05 GEMMs) against the fp32 iteration on the whole matrix."""
+import os
+import subprocess
+import sys
+import tempfile
+
+import pytest
+import torch
+
+from test_engine_dist import _free_port
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def test_supported_shapes():
+    from supergrok15_b200.ops.muon_sharded import arena_bytes, supported
+    assert supported(2048, 2048, 8) and supported(5504, 2048, 8) and supported(2048, 5504, 8)       # the 1.3 B decoder's block matrices
+    assert supported(4096, 4096, 8) and supported(4096, 4096, 2)
+    assert not supported(2048, 1000, 8) and not supported(100, 2048, 8) and not supported(2048, 2048, 3)
+    assert arena_bytes([(2048, 2048)], 8) > 2 * 2048 * 2048 * 2
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("shape", [(512, 256), (256, 256), (256, 640)])
+def test_row_sharded_newton_schulz_world_of_one(shape):
+    """One rank holds all rows: the same three fused kernels per iteration run without peers."""
+    from supergrok15_b200.ops import gemm, oracle
+    from supergrok15_b200.ops.muon_sharded import RowShardedNewtonSchulz
+    torch.manual_seed(2)
+    X = torch.randn(shape, device="cuda")
+    X = X / (X.norm() + 1e-7)
+    ns = RowShardedNewtonSchulz([shape], X.device)
+    for _ in range(2):
+        out = ns.run([X], 5)[0]
+    torch.cuda.synchronize()
+    gemm.check()
+    ref = oracle.newton_schulz(X.double(), 5).float()
+    assert (out - ref).norm() / ref.norm() < 0.06
+    k = min(shape)
+    Q = out @ out.t() if shape[0] <= shape[1] else out.t() @ out
+    Qr = ref @ ref.t() if shape[0] <= shape[1] else ref.t() @ ref
+    assert (Q - Qr).norm() / k ** 0.5 < 0.1
+
+
+@pytest.mark.gpu
+@pytest.mark.dist
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_row_sharded_newton_schulz_equals_whole_matrix(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    port = _free_port()
+    out = os.path.join(tempfile.mkdtemp(), "out.pt")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    procs = [subprocess.Popen([sys.executable, os.path.join(HERE, "muon_sharded_worker.py"), str(r), str(world), str(port), out], env=env,
+                              stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True) for r in range(world)]
+    logs = []
+    for p in procs:
+        try:
+            o, _ = p.communicate(timeout=400)
+        except subprocess.TimeoutExpired:
+            for q in procs:
+                q.kill()
+            raise
+        logs.append(o)
+    assert all(p.returncode == 0 for p in procs), "\n".join(l[-3000:] for l in logs)
+    res = torch.load(out)
+    assert len(res) == 6
+    for key, e in res.items():
+        assert e["rel_vs_fp32"] < 0.06 and e["orth_vs_fp32"] < 0.1 and e["rel_vs_whole_bf16"] < 0.06, (key, e)

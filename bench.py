@@ -320,7 +320,8 @@ def run_llama_muon(args, rank, world, local):
     cfg = LLAMA_1P3B if not args.small else LlamaConfig(n_layers=4, d_model=1024, n_heads=8, d_ff=2752, vocab=32000, max_seq=2048)
     with torch.device(dev):
         model = Llama(cfg).to(torch.bfloat16)
-    eng = ZeroEngine(model, "muon", dict(lr=0.02, momentum=0.95, weight_decay=0.01, adamw_lr=1e-3, adamw_names=("embed", "lm_head")),
+    eng = ZeroEngine(model, "muon", dict(lr=0.02, momentum=0.95, weight_decay=0.01, adamw_lr=1e-3, adamw_names=("embed", "lm_head"),
+                                         sharding=args.muon_sharding),
                      comm=args.comm, param_dtype=torch.bfloat16, graph=False)     # GPU-bound step: nothing to gain from a graph
     seq, gb = 2048, args.global_batch or 256
     per_rank = gb // world
@@ -344,16 +345,23 @@ def run_llama_muon(args, rank, world, local):
     ms = timed_loop(lambda i: losses.append(step(W + i)), K, world)
     clocks = sampler.stop() if rank == 0 else None
     eng.check()
+    opt_ms = timed_loop(lambda i: eng.step(), 5, world)       # the sharded optimizer step alone (reduce-scatter, Muon / AdamW, all-gather)
+    eng.check()
+    from supergrok15_b200.ops import gemm as _g
+    _g.check(dev)
     tokens = gb * seq
     n_params = sum(p.numel() for p in model.parameters())
     return {"metric": "train tokens/s (max over ranks), Muon on Llama-style decoder", "value": tokens / (ms * 1e-3), "unit": "tokens/s",
             "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic: uniform-random token ids; random-init weights",
             "config": {"model": f"llama {cfg.n_layers}L d{cfg.d_model} h{cfg.n_heads} ff{cfg.d_ff} vocab{cfg.vocab} ({n_params / 1e9:.3f}B params)",
-                       "global_batch": gb, "seq_len": seq, "parallelism": f"zero2-dp{world}, tensor-granular Muon ownership",
+                       "global_batch": gb, "seq_len": seq, "parallelism": f"zero2-dp{world}, Muon matrices " + ("split by rows over the ranks (collectives inside the Newton-Schulz GEMMs)"
+                                                                          if getattr(eng, "rs_idx", None) else "owned whole by one rank each"),
+                       "row_sharded_matrices": len(getattr(eng, "rs_idx", []) or []),
                        "micro_batches": micro, "l2": "inputs and weights far exceed the 126 MB L2"},
             "clocks": clocks, "gpu_launches": C.launch_count() - l0, "final_loss": float(losses[-1]) if losses else None,
-            "model_flops_per_step": 6.0 * n_params * tokens, "impl": "ours",
+            "model_flops_per_step": 6.0 * n_params * tokens, "impl": "ours", "optimizer_step_ms": opt_ms,
+            "optimizer_step_ms_per_1e9_params": opt_ms * 1e9 / n_params,
             "h2d_bytes_per_step": per_rank * seq * 8}
 
 
@@ -450,6 +458,8 @@ def main():
     ap.add_argument("--small", action="store_true", help="llama_muon: 4-layer d1024 model for quick checks")
     ap.add_argument("--global-batch", type=int, default=0)
     ap.add_argument("--micro-seqs", type=int, default=4, help="llama_muon: sequences per micro-batch")
+    ap.add_argument("--muon-sharding", default="tensors", choices=["tensors", "rows"],
+                    help="llama_muon: whole matrices per rank, or rows of every matrix over the ranks (fused collectives in the NS GEMMs)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     import torch

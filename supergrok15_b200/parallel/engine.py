@@ -48,6 +48,8 @@ OPTIMIZERS = {"supergrok2": O.SuperGrok2, "supergrok15": O.SuperGrok15, "supergr
               "grokadamw": O.GrokAdamW, "neuralgrok": O.NeuralGrok, "prodigy": O.Prodigy, "grokfast": O.Grokfast,
               "lion": O.Lion, "looksam": O.LookSAM, "muon": O.Muon, "adamw": O.AdamW}
 _DT = {torch.float32: "f32", torch.bfloat16: "bf16", torch.float16: "f16"}
+# optimizers whose step combines global scalars across the ranks (every rank must take part in every such reduction)
+_REDUCING = {"grokadamw", "neuralgrok", "supergrok15", "supergrok11", "prodigy", "looksam"}
 
 
 class CommTimeout(RuntimeError):
@@ -106,9 +108,27 @@ class ZeroEngine:
                     self.buckets.append({"lo": lo, "hi": hi, "params": idx, "slices": sl, "mine": (b, e), "state_off": so})
                     so += e - b
         else:
-            self.owner = ownership.assign_tensors(numels, self.world)
+            # Muon with sharding="rows": the rows of every block matrix the fused kernels take are split over the ranks (the
+            # Newton-Schulz GEMMs then carry their own collectives, ops/muon_sharded.py); everything else is owned whole
+            self.rs_idx: List[int] = []
+            if optimizer == "muon" and self.opt_kwargs.pop("sharding", "tensors") == "rows":
+                from ..ops import muon_sharded
+                if not (self.cuda and self.comm != "nccl"):
+                    raise ValueError("Muon with sharding='rows' runs on the in-kernel collectives (CUDA, comm 'p2p' or 'nvls')")
+                skip = tuple(self.opt_kwargs.get("adamw_names", ()))
+                self.rs_idx = [i for i, p in enumerate(self.params) if p.dim() == 2 and not any(s_ in self.param_names[i] for s_ in skip)
+                               and muon_sharded.supported(p.shape[0], p.shape[1], self.world)]
+            rs = set(self.rs_idx)
+            whole = [i for i in range(len(numels)) if i not in rs]
+            sub = ownership.assign_tensors([numels[i] for i in whole], self.world)
+            self.owner = [-1] * len(numels)
+            for i, o in zip(whole, sub):
+                self.owner[i] = o
             self.offsets, self.regions, self.total = ownership.grouped_layout(numels, self.owner, self.world)
-            if optimizer != "supergrok2" and len(set(self.owner)) < self.world:
+            for i in self.rs_idx:                                     # row-sharded tensors follow the owned regions
+                self.offsets[i] = self.total
+                self.total += -(-numels[i] // 8) * 8
+            if optimizer in _REDUCING and len(set(o for o in self.owner if o >= 0)) < self.world:
                 # the element-wise optimizers combine global scalars (clip norm, Prodigy sums, ...) across the ranks from inside
                 # their step; a rank without tensors would skip those collectives and the sequences would diverge
                 raise ValueError(f"'{optimizer}' shards whole tensors: {len(numels)} parameter tensors cannot give each of "
@@ -226,10 +246,61 @@ class ZeroEngine:
             p2 = [mv for mv, f in zip(self.master_views, is_mat) if f]
             p1 = [mv for mv, f in zip(self.master_views, is_mat) if not f]
             self.opt = cls(p2 or [torch.nn.Parameter(torch.zeros(8, 8, device=self.device))], p1, **kw)
+            if self.rs_idx:
+                self._build_row_sharded(kw)
         else:
             self.opt = cls(self.master_views or [torch.nn.Parameter(torch.zeros(0, device=self.device))], **kw)
             if hasattr(self.opt, "_flat_layer_beta1s"):
                 self._fix_layer_schedules(own)
+
+    def _build_row_sharded(self, kw):
+        """State of the row-sharded matrices: this rank's rows of the fp32 master and of the momentum, and the fused
+        Newton-Schulz object (its symmetric buffers are one allocation for all matrices)."""
+        from ..ops import muon_sharded
+        W, r = self.world, self.rank
+        self.rs_hp = dict(lr=kw.get("lr", 0.02), momentum=kw.get("momentum", 0.95), weight_decay=kw.get("weight_decay", 1.0),
+                          ns_steps=kw.get("ns_steps", 5))
+        shapes = [tuple(self.params[i].shape) for i in self.rs_idx]
+        sizes = [(R // W) * C for R, C in shapes]
+        tot = sum(sizes)
+        self.rs_master = torch.empty(tot, dtype=torch.float32, device=self.device)
+        self.rs_mom = torch.zeros(tot, dtype=torch.float32, device=self.device)
+        self.rs_gred = torch.zeros(tot, dtype=torch.float32, device=self.device)
+        self.rs_views, pos = [], 0
+        for i, (R, C), n in zip(self.rs_idx, shapes, sizes):
+            lo = self.offsets[i] + r * n                              # this rank's rows are one contiguous range of the flat buffers
+            self.rs_master[pos:pos + n].copy_(self.pbuf.tensor[lo:lo + n])
+            self.rs_views.append(dict(flat_lo=lo, n=n, master=self.rs_master[pos:pos + n], mom=self.rs_mom[pos:pos + n],
+                                      gred=self.rs_gred[pos:pos + n], shape=(R // W, C)))
+            pos += n
+        self.rs_ns = muon_sharded.RowShardedNewtonSchulz(shapes, self.device, self.group, barrier=lambda: self._barrier(20))
+        C = _build.require()
+        nb = C.mt_num_blocks(sizes)
+        self.rs_partials = torch.empty(3 * max(nb, 1), dtype=torch.float32, device=self.device)
+        self.rs_pt = torch.zeros(3 * len(sizes), dtype=torch.float32, device=self.device)
+        self.rs_inv = torch.zeros(len(sizes), dtype=torch.float32, device=self.device)
+
+    @torch.no_grad()
+    def _step_row_sharded(self):
+        """Muon on the row-sharded matrices: gradient rows pulled from every rank, momentum, norm of the whole matrix (partial
+        sums combined over the ranks), five Newton-Schulz iterations whose GEMMs carry the collectives, update of the master
+        rows, and the new low-precision rows stored into every rank's parameter buffer."""
+        C = _build.require()
+        hp, W, r = self.rs_hp, self.world, self.rank
+        dt = _DT[self.pdtype]
+        for v in self.rs_views:
+            C.dist_pull_reduce(dt, self.nvls, self.gbuf.peer_ptrs, self.gbuf.multicast_ptr, r, v["flat_lo"], v["n"], 1.0 / W, v["gred"])
+        grads, moms = [v["gred"] for v in self.rs_views], [v["mom"] for v in self.rs_views]
+        C.mt_apply(C.ops["OP_MUON_MOMENTUM"], [[], grads, moms], [], [0, 0, 0, 0, 0, hp["momentum"]], partials=self.rs_partials,
+                   per_tensor_out=self.rs_pt)
+        self.all_reduce_small(self.rs_pt)                             # sum of squares of the WHOLE matrices
+        C.scalar_finalize(C.ops["SC_MUON_NORMS"], self.rs_pt, len(self.rs_views), self.rs_inv, 0.0, 0.0, 0.0)
+        outs = self.rs_ns.run([v["mom"].view(v["shape"]) for v in self.rs_views], hp["ns_steps"], scales=self.rs_inv)
+        C.mt_apply(C.ops["OP_MUON_UPDATE"], [[v["master"] for v in self.rs_views], [o.view(-1) for o in outs]], [],
+                   [0, 0, 0, 0, 0, 0, 0, 0, -0.2 * hp["lr"], 1.0 - hp["lr"] * hp["weight_decay"]])
+        for v in self.rs_views:
+            C.dist_cast_push(dt, self.pbuf.peer_ptrs, r, v["flat_lo"], v["n"], v["master"])
+        self.launches += 4 * len(self.rs_views)
 
     def _fix_layer_schedules(self, own):
         """Layer-wise beta1 / alpha factors are functions of the parameter's index in the FULL model."""
@@ -509,6 +580,8 @@ class ZeroEngine:
                 self.opt._global_step += 1
             self._recycle_if_due()
         else:
+            if getattr(self, "rs_idx", None):
+                self._step_row_sharded()
             for mv, g in zip(self.master_views, self.grad_views):
                 mv.grad = g
             ew.set_cross_rank_reducer(self.all_reduce_small if W > 1 else None)

@@ -28,7 +28,7 @@ int sg2_bilevel_ng();
 int sg2_bilevel_tile();
 void sg2_scan_backward(const void* items_dev, int n_items, int dir1_start, const void* tds_dev, int n_td, const int64_t* snap_base_dev,
                        const float* gs_sorted, const uint32_t* vals_sorted, const float* dctx, const float* carry, float* agg, float* dcarry,
-                       float* snaps, float* partial, float* grads, cudaStream_t s);
+                       float* snaps, float* partial, float* grads, int snap_every, cudaStream_t s);
 }
 
 namespace sg {
@@ -182,7 +182,7 @@ void write_table(Tensor dst, const std::vector<int64_t>& uints, const std::vecto
 // Adjoint of the scan: dctx [total,16] -> grads [2, NG] (see csrc/sg2_bilevel.cuh for the layout).  Must follow a forward scan on the
 // same plan / workspace (it re-uses gs, vals and the chunk carry-in states of that forward).
 void sg2_scan_backward(Tensor items, int64_t n_items, int64_t dir1_start, Tensor tds, int64_t n_td, Tensor snap_base, int64_t sorted_buf,
-                       Tensor dctx, py::dict ws, Tensor snaps, Tensor partial, Tensor grads) {
+                       Tensor dctx, py::dict ws, Tensor snaps, Tensor partial, Tensor grads, int64_t snap_every) {
     c10::cuda::CUDAGuard guard(items.device());
     auto W = [&](const char* k) { return ws[k].cast<Tensor>(); };
     TORCH_CHECK(dctx.is_contiguous() && dctx.scalar_type() == at::kFloat, "dctx must be contiguous fp32");
@@ -190,7 +190,7 @@ void sg2_scan_backward(Tensor items, int64_t n_items, int64_t dir1_start, Tensor
     sg::sg2_scan_backward(items.data_ptr(), (int)n_items, (int)dir1_start, tds.data_ptr(), (int)n_td, snap_base.data_ptr<int64_t>(),
                           W("gs").data_ptr<float>(), vs, dctx.data_ptr<float>(), W("carry").data_ptr<float>(), W("agg").data_ptr<float>(),
                           W("dcarry").data_ptr<float>(), snaps.data_ptr<float>(), partial.data_ptr<float>(), grads.data_ptr<float>(),
-                          at::cuda::getCurrentCUDAStream());
+                          (int)snap_every, at::cuda::getCurrentCUDAStream());
 }
 
 void sg2_upload_weights(Tensor packed) {
@@ -468,7 +468,9 @@ void register_sg2(pybind11::module_& m) {
     m.def("sg2_layout", &sg2_layout);
     m.def("sg2_recycle", &sg2_recycle_b, py::arg("counts"), py::arg("W1"), py::arg("b1"), py::arg("W2"), py::arg("b2"), py::arg("keys_a"),
           py::arg("keys_b"), py::arg("threshold"), py::arg("seed"), py::arg("call"), py::arg("info"));
-    m.def("sg2_scan_backward", &sg2_scan_backward);
+    m.def("sg2_scan_backward", &sg2_scan_backward, py::arg("items"), py::arg("n_items"), py::arg("dir1_start"), py::arg("tds"), py::arg("n_td"),
+          py::arg("snap_base"), py::arg("sorted_buf"), py::arg("dctx"), py::arg("ws"), py::arg("snaps"), py::arg("partial"), py::arg("grads"),
+          py::arg("snap_every") = 1);
     m.def("sg2_bilevel_info", []() { py::dict d; d["ng"] = sg::sg2_bilevel_ng(); d["tile"] = sg::sg2_bilevel_tile();
                                      d["smem"] = (int64_t)sg::sg2_bilevel_smem_bytes(); return d; });
     m.def("sg2_sort_blocks", [](int64_t total) { return (int64_t)sg::sg2_sort_blocks(total); });

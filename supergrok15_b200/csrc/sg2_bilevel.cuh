@@ -150,12 +150,35 @@ __global__ void __launch_bounds__(128) sg2_adj2_kernel(const TensorDir* __restri
     }
 }
 
+// forward recurrence through the cnt timesteps of one tile whose rows stage_a has parked in `tile` (state only: no outputs)
+template <int DIR>
+__device__ __forceinline__ void bl_advance_tile(const ColConst<DIR>& cc, const float* __restrict__ tile, int cnt, float (&h)[16]) {
+    for (int l = 0; l < cnt; ++l) {
+        const float* row = tile + l * ROW;
+        const float2 v = *reinterpret_cast<const float2*>(row + 32);
+        const float x = fmaf(cc.ux[0], v.x, fmaf(cc.ux[1], v.y, cc.ux[2]));
+        const float dt = softplus20(fmaf(cc.ud[0], v.x, fmaf(cc.ud[1], v.y, cc.ud[2])));
+        const float dtx = dt * x;
+#pragma unroll
+        for (int p = 0; p < 8; ++p) {
+            float abe, abo, cs, sn;
+            pair_coeffs(dt, cc.ah[2 * p], cc.ah[2 * p + 1], cc.f[p], abe, abo, cs, sn);
+            const float he = h[2 * p], ho = h[2 * p + 1];
+            h[2 * p] = fmaf(abe, he * cs - ho * sn, dtx * row[2 * p]);
+            h[2 * p + 1] = fmaf(abo, ho * cs + he * sn, dtx * row[2 * p + 1]);
+        }
+    }
+}
+
 // ---- adj 3: the adjoint proper ----
+// State snapshots are kept at the start of every `snap_every`-th tile (checkpoint interval = snap_every * BL_TILE timesteps); a tile
+// that does not start at a snapshot is reached by re-running the forward recurrence from the snapshot before it, which trades
+// (snap_every - 1) / 2 extra tile passes on average for 1 / snap_every of the snapshot memory.  The gradients do not depend on it.
 template <int DIR>
 __device__ void bl_adj3(const Item& it, const float2* __restrict__ gs, const uint32_t* __restrict__ vals_sorted, const float* __restrict__ dctx,
                         const float* __restrict__ carry, const float* __restrict__ dcarry, float* __restrict__ snaps, int64_t snap_base,
                         float* __restrict__ partial, float* __restrict__ tile, float* __restrict__ hist, float* __restrict__ sacc,
-                        int item_idx, int j, unsigned hmask) {
+                        int item_idx, int j, unsigned hmask, int snap_every) {
     ColConst<DIR> cc;
     cc.load(j);
     const int len = it.ue - it.ub;
@@ -170,27 +193,15 @@ __device__ void bl_adj3(const Item& it, const float2* __restrict__ gs, const uin
     for (int tI = 0; tI < ntile; ++tI) {
         const int u0 = it.ub + tI * BL_TILE;
         const int cnt = (it.ue - u0 < BL_TILE) ? (it.ue - u0) : BL_TILE;
-        float* sp = snaps + ((snap_base + tI) * 16 + j) * 16;
+        if (tI % snap_every == 0) {
+            float* sp = snaps + ((snap_base + tI / snap_every) * 16 + j) * 16;
 #pragma unroll
-        for (int q = 0; q < 4; ++q) reinterpret_cast<float4*>(sp)[q] = make_float4(h[4 * q], h[4 * q + 1], h[4 * q + 2], h[4 * q + 3]);
+            for (int q = 0; q < 4; ++q) reinterpret_cast<float4*>(sp)[q] = make_float4(h[4 * q], h[4 * q + 1], h[4 * q + 2], h[4 * q + 3]);
+        }
         if (tI == ntile - 1) break;                        // the last tile is recomputed by the backward loop anyway
         stage_a<DIR>(tile, gs, it.off, it.n, u0 + j, j < cnt, j);      // rows of the forward layout (ROW floats)
         __syncwarp(hmask);
-        for (int l = 0; l < cnt; ++l) {
-            const float* row = tile + l * ROW;
-            const float2 v = *reinterpret_cast<const float2*>(row + 32);
-            const float x = fmaf(cc.ux[0], v.x, fmaf(cc.ux[1], v.y, cc.ux[2]));
-            const float dt = softplus20(fmaf(cc.ud[0], v.x, fmaf(cc.ud[1], v.y, cc.ud[2])));
-            const float dtx = dt * x;
-#pragma unroll
-            for (int p = 0; p < 8; ++p) {
-                float abe, abo, cs, sn;
-                pair_coeffs(dt, cc.ah[2 * p], cc.ah[2 * p + 1], cc.f[p], abe, abo, cs, sn);
-                const float he = h[2 * p], ho = h[2 * p + 1];
-                h[2 * p] = fmaf(abe, he * cs - ho * sn, dtx * row[2 * p]);
-                h[2 * p + 1] = fmaf(abo, ho * cs + he * sn, dtx * row[2 * p + 1]);
-            }
-        }
+        bl_advance_tile<DIR>(cc, tile, cnt, h);
         __syncwarp(hmask);
     }
     // ---- backward over the tiles
@@ -210,10 +221,19 @@ __device__ void bl_adj3(const Item& it, const float2* __restrict__ gs, const uin
     for (int tI = ntile - 1; tI >= 0; --tI) {
         const int u0 = it.ub + tI * BL_TILE;
         const int cnt = (it.ue - u0 < BL_TILE) ? (it.ue - u0) : BL_TILE;
-        bl_stage_a<DIR>(tile, gs, vals_sorted, dctx, it.off, it.n, u0 + j, j < cnt, j);
-        const float* sp = snaps + ((snap_base + tI) * 16 + j) * 16;
+        {   // state at the start of this tile: the snapshot, advanced through the tiles between the snapshot and this one
+            const int t0 = tI - tI % snap_every;
+            const float* sp = snaps + ((snap_base + t0 / snap_every) * 16 + j) * 16;
 #pragma unroll
-        for (int q = 0; q < 4; ++q) { const float4 t = reinterpret_cast<const float4*>(sp)[q]; h[4 * q] = t.x; h[4 * q + 1] = t.y; h[4 * q + 2] = t.z; h[4 * q + 3] = t.w; }
+            for (int q = 0; q < 4; ++q) { const float4 t = reinterpret_cast<const float4*>(sp)[q]; h[4 * q] = t.x; h[4 * q + 1] = t.y; h[4 * q + 2] = t.z; h[4 * q + 3] = t.w; }
+            for (int t = t0; t < tI; ++t) {                // full tiles (only the last tile of a chunk can be short)
+                stage_a<DIR>(tile, gs, it.off, it.n, it.ub + t * BL_TILE + j, true, j);
+                __syncwarp(hmask);
+                bl_advance_tile<DIR>(cc, tile, BL_TILE, h);
+                __syncwarp(hmask);
+            }
+        }
+        bl_stage_a<DIR>(tile, gs, vals_sorted, dctx, it.off, it.n, u0 + j, j < cnt, j);
         __syncwarp(hmask);
         // forward through the tile, keeping h BEFORE each step: hist[(l*16 + s) * 16 + j]
         for (int l = 0; l < cnt; ++l) {
@@ -320,7 +340,7 @@ __global__ void __launch_bounds__(BL_THREADS) sg2_adj3_kernel(const Item* __rest
                                                               const int64_t* __restrict__ snap_base, const float2* __restrict__ gs,
                                                               const uint32_t* __restrict__ vals_sorted, const float* __restrict__ dctx,
                                                               const float* __restrict__ carry, const float* __restrict__ dcarry,
-                                                              float* __restrict__ snaps, float* __restrict__ partial) {
+                                                              float* __restrict__ snaps, float* __restrict__ partial, int snap_every) {
     extern __shared__ __align__(16) float bl_smem[];
     float* tiles = bl_smem;                                             // [BL_ITEMS][BL_TILE*BL_ROW]  (BL_ROW >= ROW)
     float* hist = tiles + BL_ITEMS * BL_TILE * BL_ROW;                  // [BL_ITEMS][BL_TILE*16*16]
@@ -336,8 +356,8 @@ __global__ void __launch_bounds__(BL_THREADS) sg2_adj3_kernel(const Item* __rest
     }
     float* tile = tiles + slot * BL_TILE * BL_ROW;
     float* hs = hist + slot * BL_TILE * 256;
-    if (item_idx < dir1_start) bl_adj3<0>(it, gs, vals_sorted, dctx, carry, dcarry, snaps, snap_base[item_idx], partial, tile, hs, sacc, item_idx, j, hmask);
-    else                       bl_adj3<1>(it, gs, vals_sorted, dctx, carry, dcarry, snaps, snap_base[item_idx], partial, tile, hs, sacc, item_idx, j, hmask);
+    if (item_idx < dir1_start) bl_adj3<0>(it, gs, vals_sorted, dctx, carry, dcarry, snaps, snap_base[item_idx], partial, tile, hs, sacc, item_idx, j, hmask, snap_every);
+    else                       bl_adj3<1>(it, gs, vals_sorted, dctx, carry, dcarry, snaps, snap_base[item_idx], partial, tile, hs, sacc, item_idx, j, hmask, snap_every);
 }
 
 // ---- adj 4: fixed-order sum over the items of each direction; d(A/2) -> d A_log ----
@@ -362,11 +382,13 @@ int sg2_bilevel_ng() { return BL_NG; }
 int sg2_bilevel_tile() { return BL_TILE; }
 
 // dctx [total,16] (original order) -> grads [2][BL_NG].  Uses the forward scan's carry (chunk carry-in states of THIS forward),
-// agg/dcarry scratch of the same sizes as the forward ones, snaps [n_snap_tiles,16,16] and partial [n_items, BL_NG].
+// agg/dcarry scratch of the same sizes as the forward ones, snaps [sum over items of ceil(tiles / snap_every), 16, 16] and
+// partial [n_items, BL_NG].  snap_base[item] = index of the item's first snapshot.
 void sg2_scan_backward(const void* items_dev, int n_items, int dir1_start, const void* tds_dev, int n_td, const int64_t* snap_base_dev,
                        const float* gs_sorted, const uint32_t* vals_sorted, const float* dctx, const float* carry, float* agg, float* dcarry,
-                       float* snaps, float* partial, float* grads, cudaStream_t s) {
+                       float* snaps, float* partial, float* grads, int snap_every, cudaStream_t s) {
     if (n_items <= 0) return;
+    if (snap_every < 1) snap_every = 1;
     const Item* items = reinterpret_cast<const Item*>(items_dev);
     const TensorDir* tds = reinterpret_cast<const TensorDir*>(tds_dev);
     const float2* gs = reinterpret_cast<const float2*>(gs_sorted);
@@ -377,7 +399,7 @@ void sg2_scan_backward(const void* items_dev, int n_items, int dir1_start, const
     count_launch(4);
     sg2_adj1_kernel<<<blocks, BL_THREADS, 0, s>>>(items, n_items, dir1_start, gs, vals_sorted, dctx, agg);
     sg2_adj2_kernel<<<n_td, 128, 0, s>>>(tds, agg, dcarry);
-    sg2_adj3_kernel<<<blocks, BL_THREADS, smem, s>>>(items, n_items, dir1_start, snap_base_dev, gs, vals_sorted, dctx, carry, dcarry, snaps, partial);
+    sg2_adj3_kernel<<<blocks, BL_THREADS, smem, s>>>(items, n_items, dir1_start, snap_base_dev, gs, vals_sorted, dctx, carry, dcarry, snaps, partial, snap_every);
     sg2_adj4_kernel<<<dim3((BL_NG + 255) / 256, 2), 256, 0, s>>>(partial, n_items, dir1_start, grads);
 }
 

@@ -104,15 +104,55 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
     return _Linear.apply(x, weight, bias, act)
 
 
+def _split(x32: torch.Tensor):
+    """fp32 matrix -> (hi, lo) bf16 with hi + lo = x to ~16 bits (row pitch padded to 8 elements for TMA)."""
+    r, c = x32.shape
+    cp = -(-c // 8) * 8
+    hi = torch.zeros(r, cp, dtype=torch.bfloat16, device=x32.device)[:, :c]
+    lo = torch.zeros(r, cp, dtype=torch.bfloat16, device=x32.device)[:, :c]
+    hi.copy_(x32)
+    lo.copy_(x32 - hi.float())
+    return hi, lo
+
+
+def _mm3(a32: torch.Tensor, b32: torch.Tensor, *, alpha=1.0, beta=0.0, d=None, diag=0.0) -> torch.Tensor:
+    """alpha * a @ b.T + beta * d + diag * I in fp32 from three bf16 tensor-core products (hi.hi + hi.lo + lo.hi): the dropped
+    lo.lo term is 2^-16 of the result, so the product carries ~16 bits instead of bf16's 8."""
+    ah, al = _split(a32)
+    bh, bl = _split(b32)
+    m, n = a32.shape[0], b32.shape[0]
+    out = torch.empty(m, -(-n // 4) * 4, dtype=torch.float32, device=a32.device)[:, :n]
+    gemm_tn(ah, bl, out=out, alpha=alpha, beta=beta, d=d, diag=diag)
+    gemm_tn(al, bh, out=out, alpha=alpha, beta=1.0, d=out)
+    gemm_tn(ah, bh, out=out, alpha=alpha, beta=1.0, d=out)
+    return out
+
+
 def newton_schulz(X: torch.Tensor, steps: int, coeffs, precision: str = "bf16") -> torch.Tensor:
     """X <- aX + b(XX^T)X + c(XX^T)^2X, `steps` times, on the tcgen05 GEMM.  X fp32 [r,c] -> fp32 [r,c].
 
     rows >= cols: right-Gram form  G = X^T X, P = aI + bG + cG^2, X <- X P   (cols^2-sized intermediates);
     rows <  cols: left form        A = X X^T, Q = aI + bA + cA^2, X <- Q X.
-    Both X and X^T are kept in bf16 (the last GEMM of an iteration writes both), so every GEMM is K-major on both operands.
+    ``precision="bf16"``: operands are rounded to bf16 once per product (fp32 accumulation in TMEM); X and X^T are both kept,
+    so every GEMM is K-major on both operands.  The reference iterates in fp32 (``torch::mm`` with TF32 off, reference
+    csrc/ops.cpp:713-727); the bf16 iteration differs from it by a few per cent in Frobenius norm, which Muon tolerates (the
+    iteration is a contraction towards the orthogonal factor).  ``precision="bf16x3"``: every product is three bf16 products of
+    hi / lo splits with fp32 results carried between the products (~16 bits per product, 3x the tensor-core work): within
+    2e-3 of the fp32 iteration, for callers who want the reference's numerics.
     """
+    if precision not in ("bf16", "bf16x3"):
+        raise ValueError("precision must be 'bf16' or 'bf16x3'")
     a, b, c = coeffs
     r, cc = X.shape
+    if precision == "bf16x3":
+        X32 = X.float().contiguous()
+        tall = r >= cc
+        for _ in range(steps):
+            src = X32.t().contiguous() if tall else X32                  # Gram matrix of the short side
+            G = _mm3(src, src)
+            Pm = _mm3(G, G, alpha=c, beta=b, d=G, diag=a)                # symmetric
+            X32 = _mm3(X32, Pm) if tall else _mm3(Pm, X32.t().contiguous())
+        return X32
     rp, cp = -(-r // 8) * 8, -(-cc // 8) * 8
     dev = X.device
     Xb = torch.zeros(r, cp, dtype=torch.bfloat16, device=dev)[:, :cc]
@@ -125,6 +165,9 @@ def newton_schulz(X: torch.Tensor, steps: int, coeffs, precision: str = "bf16") 
     G = torch.zeros(n, npad, dtype=torch.bfloat16, device=dev)[:, :n]
     P = torch.zeros(n, npad, dtype=torch.bfloat16, device=dev)[:, :n]
     out32 = torch.empty(r, -(-cc // 4) * 4, dtype=torch.float32, device=dev)[:, :cc]
+    # ping-pong operand buffers allocated once per call (not once per iteration)
+    Xn = torch.empty(r, cp, dtype=torch.bfloat16, device=dev)[:, :cc]
+    XTn = torch.empty(cc, rp, dtype=torch.bfloat16, device=dev)[:, :r]
     for it in range(steps):
         last = it == steps - 1
         src = XTb if tall else Xb
@@ -136,11 +179,10 @@ def newton_schulz(X: torch.Tensor, steps: int, coeffs, precision: str = "bf16") 
             else:
                 gemm_tn(P, XTb, out=out32)                                  # Q X   (B operand = X^T [c, r])
         else:
-            Xn = torch.empty(r, cp, dtype=torch.bfloat16, device=dev)[:, :cc]       # padded row pitch (16-byte multiple)
-            XTn = torch.empty(cc, rp, dtype=torch.bfloat16, device=dev)[:, :r]
             if tall:
                 gemm_tn(Xb, P, out=Xn, out_t=XTn)
             else:
                 gemm_tn(P, XTb, out=Xn, out_t=XTn)
-            Xb, XTb = Xn, XTn
+            Xb, Xn = Xn, Xb
+            XTb, XTn = XTn, XTb
     return out32

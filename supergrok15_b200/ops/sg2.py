@@ -342,14 +342,15 @@ def bilevel_backward(opt, named, train_grads: Dict[str, torch.Tensor], val_grads
     meta_loss = -sum_tensors <smart_grad(train_grad, sharpness), vg/||vg||>; gradients do not flow into the
     inputs, the sort permutation, the previous GRU state or the initial scan state
     (reference supergrok2.py:815-1019).  Returns the number of tensors that contributed.
-    ``checkpoint_interval`` > 1 recomputes the per-tensor forward during backward (activation checkpointing)
-    instead of keeping every tensor's graph alive at once.
+    ``checkpoint_interval`` C: on CUDA a scan state is kept every max(16, 16 * ceil(C / 16)) timesteps and the steps between
+    are recomputed in the adjoint (``ops/sg2_bilevel.py: snapshot_tiles``); the PyTorch path processes one tensor at a time and
+    keeps no scan states beyond that tensor's autograd graph.  The gradients do not depend on the interval.
     """
     mn = opt.meta_net
     first = next((p for _, p in named), None)
     if first is not None and first.is_cuda and supports_native(mn) and not getattr(opt, "bilevel_force_autograd", False):
         from .sg2_bilevel import bilevel_backward_cuda
-        return bilevel_backward_cuda(opt, named, train_grads, val_grads)
+        return bilevel_backward_cuda(opt, named, train_grads, val_grads, checkpoint_interval=checkpoint_interval)
     used = 0
     for name, p in named:
         if name not in train_grads or name not in val_grads:

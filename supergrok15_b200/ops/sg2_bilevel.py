@@ -138,15 +138,17 @@ _SLICES = [(0, 256, (16, 16)), (256, 384, (16, 8)), (384, 400, (16,)), (400, 448
 class _Workspace:
     """Plan + scratch for a batched bilevel call over a fixed list of tensor sizes."""
 
-    def __init__(self, numels, device):
+    def __init__(self, numels, device, snap_every: int = 1):
         C = _build.require()
         info = C.sg2_bilevel_info()
+        self.snap_every = max(1, int(snap_every))
         self.h_fwd = [torch.zeros(16, 16, device=device) for _ in numels]
         self.h_bwd = [torch.zeros(16, 16, device=device) for _ in numels]
         self.plan = sg2_ops.Plan(numels, self.h_fwd, self.h_bwd, device)
         p = self.plan
         items = p.items.cpu().numpy().view(sg2_ops.Plan.ITEM)
         tiles = np.where(items["tensor"] >= 0, -(-(items["ue"] - items["ub"]) // info["tile"]), 0).astype(np.int64)
+        tiles = -(-tiles // self.snap_every)                                  # one state snapshot per snap_every tiles
         base = np.concatenate([[0], np.cumsum(tiles)[:-1]]).astype(np.int64)
         self.snap_base = torch.from_numpy(base).to(device)
         n_snap = int(tiles.sum())
@@ -177,7 +179,7 @@ class _ScanCtx(torch.autograd.Function):
         C = _build.require()
         wsp, p = ctx.wsp, ctx.wsp.plan
         C.sg2_scan_backward(p.items, p.n_items, p.dir1_start, p.tds, p.n_td, wsp.snap_base, ctx.buf, dctx.contiguous().float(), p.ws,
-                            wsp.snaps, wsp.partial, wsp.grads)
+                            wsp.snaps, wsp.partial, wsp.grads, snap_every=wsp.snap_every)
         g = wsp.grads.view(2, wsp.ng)
         outs = []
         for d in range(2):
@@ -187,8 +189,16 @@ class _ScanCtx(torch.autograd.Function):
         return (None, None, None, None, None, *outs)
 
 
+def snapshot_tiles(checkpoint_interval: int) -> int:
+    """Tiles of 16 timesteps per saved scan state for a requested checkpoint interval C (reference supergrok2.py:93, 667-674:
+    every C-th state is kept and segments of C steps are recomputed).  The adjoint works on 16-step tiles, so intervals up to 16
+    keep a state per tile (64 bytes per element, already 1/16 of the reference's C = 1) and larger ones keep one per
+    ceil(C / 16) tiles; the gradients are the same for every interval."""
+    return max(1, -(-int(checkpoint_interval) // 16))
+
+
 def bilevel_backward_cuda(opt, named, train_grads: Dict[str, torch.Tensor], val_grads: Dict[str, torch.Tensor],
-                          slice_elems: int = 0) -> int:
+                          slice_elems: int = 0, checkpoint_interval: int = 1) -> int:
     """Accumulate d(meta_loss)/d(meta-net parameters) into their ``.grad`` with the batched CUDA pipeline.
     ``slice_elems``: elements per slice of the element-wise tail (0: 2M with the expert kernel, 256K with the dense PyTorch
     expert stage, whose [slice, experts, hidden] intermediates bound the slice)."""
@@ -219,10 +229,11 @@ def bilevel_backward_cuda(opt, named, train_grads: Dict[str, torch.Tensor], val_
         vus.append(torch.where(ok & (n > 1e-12), 1.0 / n.clamp_min(1e-30), torch.where(ok, torch.ones_like(n), torch.zeros_like(n)))
                    * torch.where(torch.isfinite(vg), vg, torch.zeros_like(vg)))
     numels = tuple(g.numel() for _, g, _ in sel)
-    key = (numels, str(dev))
+    g_snap = snapshot_tiles(checkpoint_interval)
+    key = (numels, str(dev), g_snap)
     cache = getattr(opt, "_bilevel_ws", None)
     if cache is None or cache[0] != key:
-        opt._bilevel_ws = cache = (key, _Workspace(list(numels), dev))
+        opt._bilevel_ws = cache = (key, _Workspace(list(numels), dev, g_snap))
     wsp = cache[1]
     w = sg2_ops.pack_metanet(mn).to(dev)
     C.sg2_upload_weights(w)

@@ -128,7 +128,9 @@ class SuperGrok2(SuperGrok15):
         (Philox keyed by the recycle seed and the call number: identical on every data-parallel rank, no host read-back);
         on CPU a private generator makes the draw reproducible."""
         mn = self.meta_net
-        if mn.expert_counts.is_cuda:
+        # the device kernel is built for the default expert width (16 hidden units); other widths (the race driver's
+        # expert_hidden = 4) take the seeded host routine, which reads the counts back once per recycle_interval steps
+        if mn.expert_counts.is_cuda and mn.expert_hidden == 16 and mn.num_experts == 144:
             from .. import _build
             C = _build.require()
             self._recycle_calls = getattr(self, "_recycle_calls", 0) + 1

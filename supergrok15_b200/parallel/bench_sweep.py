@@ -43,6 +43,7 @@ def main():
     ap.add_argument("--optimizers", default="all")
     ap.add_argument("--comm", default="p2p")
     ap.add_argument("--dtype", default="fp32", choices=["fp32", "bf16"])
+    ap.add_argument("--muon-sharding", default="tensors", choices=["tensors", "rows"])
     ap.add_argument("--pg-timeout", type=int, default=180, help="seconds before a stuck NCCL bootstrap collective aborts the job")
     ap.add_argument("--progress-dir", dest="log", default=None, help="directory for per-rank progress logs")
     a = ap.parse_args()
@@ -70,6 +71,8 @@ def main():
         kw = {}
         if name in ("supergrok2", "supergrok15", "supergrok11"):
             kw = dict(warmup_steps=0, warmup_ramp=1)
+        if name == "muon":
+            kw = dict(sharding=a.muon_sharding)
         try:
             eng = ZeroEngine(model, name, kw, comm=a.comm, param_dtype=dt)
             g = torch.Generator(device="cuda").manual_seed(1234 + rank)
@@ -102,8 +105,9 @@ def main():
             if rank == 0:
                 print(json.dumps({"optimizer": name, "n_gpus": world, "params": n_params, "ms_per_step": float(ms),
                                   "ms_per_1e9_params": float(ms) * 1e9 / n_params, "comm": eng.comm, "dtype": a.dtype, "finite": ok,
-                                  "nvlink_ingress_bytes_per_rank": nv["rs_ingress"], "nvlink_egress_bytes_per_rank": nv["ag_egress"],
-                                  "nvlink_floor_ms": max(nv.values()) / 770e9 * 1e3}), flush=True)
+                                  "nvlink_bytes_per_direction_per_rank": nv["per_direction"],
+                                  "nvlink_floor_ms": nv["per_direction"] / 770e9 * 1e3,
+                                  "nvlink_fraction": (nv["per_direction"] / 770e9 * 1e3) / float(ms) if float(ms) > 0 else None}), flush=True)
         except Exception as e:  # noqa: BLE001
             note(f"  FAILED {type(e).__name__}: {str(e)[:300]}")
             if rank == 0:

@@ -56,6 +56,16 @@ def _per_tensor_state(engine) -> Dict[int, dict]:
     return out
 
 
+def _row_shards(engine) -> Dict[int, dict]:
+    """Muon with the rows of its matrices split over the ranks: this rank's rows of the fp32 master and of the momentum."""
+    out = {}
+    for i, v in zip(getattr(engine, "rs_idx", None) or [], getattr(engine, "rs_views", None) or []):
+        rl, c = v["shape"]
+        out[i] = {"rows": [engine.rank * rl, (engine.rank + 1) * rl], "master": v["master"].view(rl, c).detach().cpu().clone(),
+                  "momentum_buffer": v["mom"].view(rl, c).detach().cpu().clone()}
+    return out
+
+
 def _walk(obj, prefix, out):
     if torch.is_tensor(obj):
         out.append((prefix, obj))
@@ -127,6 +137,9 @@ def save(engine, path: str, keep: int = 2) -> str:
     d = os.path.join(path, name)
     os.makedirs(d, exist_ok=True)
     payload = {"rank": engine.rank, "world": engine.world, "tensors": _per_tensor_state(engine), "steps": engine.steps, "save_id": save_id}
+    rows = _row_shards(engine)
+    if rows:
+        payload["row_shards"] = rows
     if engine.flat_mode:
         # the flat ranges this rank owns (one, or one per bucket when the step overlaps backward) and their state, concatenated
         n = engine.n_own
@@ -203,6 +216,7 @@ def consolidate(path: str) -> dict:
     state: Dict[int, dict] = {}
     extra = None
     flat_parts = []
+    row_parts: Dict[int, list] = {}
     for r in range(man["world"]):
         p = _load_shard(path, r)
         for i, rec in p["tensors"].items():
@@ -212,6 +226,12 @@ def consolidate(path: str) -> dict:
             extra = p["extra"]
         if "flat" in p:
             flat_parts.append(p["flat"])
+        for i, rec in p.get("row_shards", {}).items():
+            row_parts.setdefault(int(i), []).append(rec)
+    for i, parts in row_parts.items():                      # matrices stored as row blocks: put the blocks back together
+        parts.sort(key=lambda rec: rec["rows"][0])
+        masters[i] = torch.cat([rec["master"] for rec in parts], 0).reshape(-1)
+        state[i] = {"momentum_buffer": torch.cat([rec["momentum_buffer"] for rec in parts], 0)}
     out = {"masters": masters, "state": state, "extra": extra, "manifest": man}
     if flat_parts:
         # scatter every rank's segments back to their positions of the flat buffer (positions do not depend on the world size)
@@ -274,6 +294,13 @@ def load(engine, path: str) -> None:
                 ex = dict(full["extra"])
                 ex.pop("flat_steps", None)               # per-tensor steps were restored above in this rank's own numbering
                 opt._load_extra_state(ex)
+            for i, v in zip(getattr(engine, "rs_idx", None) or [], getattr(engine, "rs_views", None) or []):
+                rl, c = v["shape"]
+                lo = engine.rank * rl
+                v["master"].copy_(full["masters"][i].view(-1, c)[lo:lo + rl].reshape(-1))
+                mom = full["state"].get(i, {}).get("momentum_buffer")
+                if mom is not None:
+                    v["mom"].copy_(mom.reshape(-1, c)[lo:lo + rl].reshape(-1))
             # every rank rebuilds the full low-precision parameter buffer from the consolidated masters
             for i, p in enumerate(engine.params):
                 p.data.copy_(full["masters"][i].view(p.shape).to(engine.pdtype))

@@ -724,7 +724,11 @@ class ZeroEngine:
         return n
 
     def nvlink_bytes_per_step(self) -> Dict[str, int]:
-        """Bytes this rank moves over NVLink per step on the fused path: pull ingress, push egress."""
+        """Bytes over NVLink per step and rank on the fused path.  A rank pulls its shard of the gradients from the W - 1 peers
+        and pushes its shard of the parameters to them; its INGRESS direction therefore carries its own pulls and the peers'
+        pushes into its buffer (and the egress direction the mirror image), so every direction moves both amounts."""
         es = torch.tensor([], dtype=self.pdtype).element_size()
-        n_own = self.n_own
-        return {"rs_ingress": (self.world - 1) * n_own * es, "ag_egress": (self.world - 1) * n_own * es}
+        n_shard = self.n_own + sum(v["n"] for v in getattr(self, "rs_views", []))
+        pull = (self.world - 1) * n_shard * es
+        pushed_to_me = (self.total - n_shard) * es if self.world > 1 else 0
+        return {"rs_ingress": pull, "ag_egress": pull, "per_direction": pull + pushed_to_me}

@@ -1,4 +1,4 @@
-"""One rank of the fused all-gather GEMM test: argv = rank world port out_path [bench]."""
+"""One rank of the fused all-gather / reduce-scatter GEMM test: argv = rank world port out_path."""
 import os
 import sys
 
@@ -10,7 +10,6 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 def main():
     rank, world, port, out_path = int(sys.argv[1]), int(sys.argv[2]), sys.argv[3], sys.argv[4]
-    bench = len(sys.argv) > 5 and sys.argv[5] == "bench"
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=port, RANK=str(rank), WORLD_SIZE=str(world))
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
@@ -18,7 +17,7 @@ def main():
     from supergrok15_b200.ops import gemm
     from supergrok15_b200.parallel.comm_gemm import ShardedWeight
     res = {}
-    for (M, N, K) in ([(512, 1024, 512), (1000, 2048, 1024)] if not bench else [(16384, 2048, 2048), (16384, 8192, 2048)]):
+    for (M, N, K) in [(512, 1024, 512), (1000, 2048, 1024)]:
         w = ShardedWeight(N, K, dev)
         errs = []
         for call in range(2):                                    # second call: new shard contents, same counters (epoch 2)
@@ -37,34 +36,9 @@ def main():
             assert torch.equal(w.full.cpu(), w_full), "gathered weight differs"
             dist.barrier()
         res[(M, N, K)] = errs
-        if bench:
-            def timed(fn, it=10):
-                for _ in range(3):
-                    fn()
-                dist.barrier(); torch.cuda.synchronize()
-                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                e0.record()
-                for _ in range(it):
-                    fn()
-                e1.record(); torch.cuda.synchronize()
-                t = torch.tensor([e0.elapsed_time(e1) / it], device=dev)
-                dist.all_reduce(t, op=dist.ReduceOp.MAX)
-                return float(t)
-            gathered = torch.empty(N, K, dtype=torch.bfloat16, device=dev)
-            shard = w.shard.clone()
-
-            def baseline():
-                dist.all_gather_into_tensor(gathered, shard)
-                return x @ gathered.t()
-            t_fused = timed(lambda: w.matmul(x))
-            t_base = timed(baseline)
-            t_gemm = timed(lambda: gemm.gemm_tn(x, w.full))
-            t_cublas = timed(lambda: x @ gathered.t())
-            res[("bench", M, N, K)] = dict(fused_ms=t_fused, nccl_ag_plus_cublas_ms=t_base, own_gemm_only_ms=t_gemm, cublas_only_ms=t_cublas,
-                                           fused_tflops=2.0 * M * N * K / t_fused / 1e9)
         del w
     from supergrok15_b200.parallel.comm_gemm import ReduceScatterGemm
-    for (M, N, K) in ([(256 * world, 512, 256), (1024 * world, 1024 + 64, 512)] if not bench else [(16384, 2048, 5504 // world // 8 * 8), (16384, 8192, 2048)]):
+    for (M, N, K) in [(256 * world, 512, 256), (1024 * world, 1024 + 64, 512)]:
         op = ReduceScatterGemm(M, N, dev)
         errs = []
         for call in range(3):                                    # three calls: both parities and the reuse of the first
@@ -80,27 +54,6 @@ def main():
             ref = part[rank * mloc:(rank + 1) * mloc]
             errs.append(float((y.float() - ref).abs().max() / ref.abs().max()))
         res[("rs", M, N, K)] = errs
-        if bench:
-            full = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
-            outb = torch.empty(M // world, N, dtype=torch.bfloat16, device=dev)
-
-            def baseline():
-                torch.matmul(a, b.t(), out=full)
-                dist.reduce_scatter_tensor(outb, full)
-            def timed(fn, it=10):
-                for _ in range(3):
-                    fn()
-                dist.barrier(); torch.cuda.synchronize()
-                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                e0.record()
-                for _ in range(it):
-                    fn()
-                e1.record(); torch.cuda.synchronize()
-                t = torch.tensor([e0.elapsed_time(e1) / it], device=dev)
-                dist.all_reduce(t, op=dist.ReduceOp.MAX)
-                return float(t)
-            res[("rs_bench", M, N, K)] = dict(fused_ms=timed(lambda: op(a, b)), cublas_plus_nccl_rs_ms=timed(baseline),
-                                              own_gemm_only_ms=timed(lambda: gemm.gemm_tn(a, b)), cublas_only_ms=timed(lambda: torch.matmul(a, b.t(), out=full)))
         del op
     if rank == 0:
         torch.save(res, out_path)

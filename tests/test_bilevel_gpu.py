@@ -58,6 +58,29 @@ def test_cuda_bilevel_gradients_match_autograd(shapes, chunk):
         assert err < 5e-3, (k, float(err), float(scale))
 
 
+@pytest.mark.parametrize("interval", [8, 32, 100])
+def test_checkpoint_interval_does_not_change_the_gradients(interval):
+    """States kept every 16, 32 or 112 timesteps (intervals 8, 32, 100): the recomputation between snapshots is exact, so the
+    meta-net gradients are those of interval 1, bit for bit."""
+    from supergrok15_b200.ops import sg2_bilevel
+    opt, named, tg, vg = _setup([(2500,), (700,), (33,)])
+    mn = opt.meta_net
+    sg2_ops._MIN_CHUNK, old = 512, sg2_ops._MIN_CHUNK
+    try:
+        mn.zero_grad()
+        sg2_ops.bilevel_backward(opt, named, tg, vg, 1)
+        ref = {k: p.grad.clone() for k, p in mn.named_parameters() if p.grad is not None}
+        mn.zero_grad()
+        sg2_ops.bilevel_backward(opt, named, tg, vg, interval)
+        got = {k: p.grad.clone() for k, p in mn.named_parameters() if p.grad is not None}
+    finally:
+        sg2_ops._MIN_CHUNK = old
+    assert opt._bilevel_ws[1].snap_every == sg2_bilevel.snapshot_tiles(interval) == -(-interval // 16)
+    assert set(got) == set(ref)
+    for k in ref:
+        assert torch.equal(got[k], ref[k]), k
+
+
 def test_bilevel_step_runs_on_cuda_and_keeps_persistent_states():
     opt, named, tg, vg = _setup([(600,), (33, 9)])
     before = [s.clone() for s in opt._flat_mamba_fwd_states]

@@ -70,6 +70,22 @@ def test_linear_autograd_matches_torch():
     assert torch.allclose(b.grad.float(), br.grad, rtol=3e-2, atol=0.3)
 
 
+@pytest.mark.parametrize("shape", [(256, 128), (128, 256), (200, 136)])
+def test_newton_schulz_split_precision_tracks_the_fp32_iteration(shape):
+    """precision="bf16x3": three bf16 products per GEMM on hi / lo splits; an order of magnitude closer to fp32 than plain bf16."""
+    torch.manual_seed(3)
+    X = torch.randn(shape, device="cuda")
+    X = X / (X.norm() + 1e-7)
+    ref = oracle.newton_schulz(X.double(), 5).float()
+    out3 = gemm.newton_schulz(X, 5, oracle.NS_COEFFS, precision="bf16x3")
+    out1 = gemm.newton_schulz(X, 5, oracle.NS_COEFFS, precision="bf16")
+    gemm.check()
+    e3, e1 = (out3 - ref).norm() / ref.norm(), (out1 - ref).norm() / ref.norm()
+    assert e3 < 2e-3 and e3 < 0.2 * e1, (float(e3), float(e1))
+    with pytest.raises(ValueError):
+        gemm.newton_schulz(X, 5, oracle.NS_COEFFS, precision="fp64")
+
+
 @pytest.mark.parametrize("shape", [(256, 128), (128, 256), (512, 512), (264, 136), (203, 136), (136, 203)])
 def test_newton_schulz_matches_fp32_iteration(shape):
     torch.manual_seed(2)

@@ -347,3 +347,19 @@ def test_engine_language_model_path(optimizer):
     eng.check()
     assert abs(losses[0] - ref0) < 0.05 * ref0, (losses[0], ref0)
     assert losses[-1] < 0.8 * losses[0], losses
+
+
+def test_recycling_with_a_narrow_expert_width_uses_the_host_routine():
+    """expert_hidden = 4 (the race driver's v2 configuration): the device recycling kernel is built for 16 hidden units, so the
+    seeded host routine runs instead; 100 steps cross one recycle_interval without an error."""
+    from supergrok15_b200.optim import SuperGrok2
+    torch.manual_seed(0)
+    model = torch.nn.Linear(32, 32).cuda()
+    opt = SuperGrok2(model.parameters(), expert_hidden=4, recycle_interval=5)
+    for _ in range(6):
+        for p in model.parameters():
+            p.grad = torch.randn_like(p) * 1e-2
+        opt.step()
+    torch.cuda.synchronize()
+    assert all(bool(torch.isfinite(p).all()) for p in model.parameters())
+    assert int(opt.meta_net.expert_counts.sum()) < 4 * 6 * sum(p.numel() for p in model.parameters())     # cleared at step 5

@@ -12,7 +12,7 @@ void dist_pull_reduce(int dtype, bool nvls, const PeerPtrs& grads, const void* m
 void dist_push(bool nvls, const PeerPtrs& params, void* mc, int world, int rank, int64_t off_bytes, int64_t n_bytes, cudaStream_t s);
 void dist_fused_flat_step(int op, int gdtype, int pdtype, bool nvls, const PeerPtrs& grads, const PeerPtrs& params, const void* mc_grad,
                           void* mc_param, int world, int rank, int64_t off, int64_t n, float lr, float beta1, float beta2, float eps, float wd, float bc1, float bc2, float gscale,
-                          float* master, float* m, float* v, const float* dyn, cudaStream_t s);
+                          float* master, float* m, float* v, const float* dyn, bool push, cudaStream_t s);
 void dist_scatter_slots(const PeerPtrs& slots, int world, int rank, const float* vec, int n, cudaStream_t s);
 void dist_cast_push(int pdtype, const PeerPtrs& params, int world, int rank, int64_t off, int64_t n, const float* master, cudaStream_t s);
 void dist_reduce_slots(const float* my_slots, int world, float* out, int n, float scale, cudaStream_t s);
@@ -56,7 +56,7 @@ void push(bool nvls, const std::vector<int64_t>& params, int64_t mc, int64_t ran
 }
 void fused_flat_step(int64_t op, const std::string& gdtype, const std::string& pdtype, const std::vector<int64_t>& grads,
                      const std::vector<int64_t>& params, int64_t rank, int64_t off, int64_t n, const std::vector<double>& f, Tensor master,
-                     Tensor m, c10::optional<Tensor> v, bool nvls, int64_t mc_grad, int64_t mc_param, c10::optional<Tensor> dyn) {
+                     Tensor m, c10::optional<Tensor> v, bool nvls, int64_t mc_grad, int64_t mc_param, c10::optional<Tensor> dyn, bool push) {
     c10::cuda::CUDAGuard guard(master.device());
     TORCH_CHECK(off % 8 == 0 && n % 8 == 0, "shard offset and length must be multiples of 8 elements");
     TORCH_CHECK(f.size() >= 8, "f = lr beta1 beta2 eps wd bc1 bc2 gscale");
@@ -65,7 +65,7 @@ void fused_flat_step(int64_t op, const std::string& gdtype, const std::string& p
     sg::dist_fused_flat_step((int)op, dcode(gdtype), dcode(pdtype), nvls, peers(grads), peers(params), vp(mc_grad), vp(mc_param),
                              (int)grads.size(), (int)rank, off, n, (float)f[0],
                              (float)f[1], (float)f[2], (float)f[3], (float)f[4], (float)f[5], (float)f[6], (float)f[7], master.data_ptr<float>(),
-                             m.data_ptr<float>(), v.has_value() ? v->data_ptr<float>() : nullptr, dyn_ptr(dyn), at::cuda::getCurrentCUDAStream());
+                             m.data_ptr<float>(), v.has_value() ? v->data_ptr<float>() : nullptr, dyn_ptr(dyn), push, at::cuda::getCurrentCUDAStream());
 }
 void cast_push(const std::string& pdtype, const std::vector<int64_t>& params, int64_t rank, int64_t off, int64_t n, Tensor master) {
     c10::cuda::CUDAGuard guard(master.device());
@@ -90,7 +90,7 @@ void register_dist(pybind11::module_& m) {
     m.def("dist_push", &push);
     m.def("dist_fused_flat_step", &fused_flat_step, py::arg("op"), py::arg("gdtype"), py::arg("pdtype"), py::arg("grads"), py::arg("params"),
           py::arg("rank"), py::arg("off"), py::arg("n"), py::arg("f"), py::arg("master"), py::arg("m"), py::arg("v"), py::arg("nvls") = false,
-          py::arg("mc_grad") = 0, py::arg("mc_param") = 0, py::arg("dyn") = c10::optional<Tensor>());
+          py::arg("mc_grad") = 0, py::arg("mc_param") = 0, py::arg("dyn") = c10::optional<Tensor>(), py::arg("push") = true);
     m.def("dist_scatter_slots", &scatter_slots);
     m.def("dist_cast_push", &cast_push);
     m.def("dist_reduce_slots", &reduce_slots);

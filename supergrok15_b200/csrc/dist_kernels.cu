@@ -75,7 +75,7 @@ template <typename G, typename T> struct VecN { static constexpr int value = (si
 // multimem.st per 16 bytes (the switch replicates them to every rank); NVLS needs 16-byte vectors of both buffers (same dtype).
 template <int OP, typename G, typename T, bool NVLS, int W, int U>
 __global__ void __launch_bounds__(256) fused_rs_step_ag_kernel(PeerPtrs grads, PeerPtrs params, const void* mc_grad, void* mc_param,
-                                                               int world, int rank, int64_t off, int64_t n, FlatStep st) {
+                                                               int world, int rank, int64_t off, int64_t n, FlatStep st, int n_push) {
     constexpr int N = VecN<G, T>::value;
     const int64_t nv = n / N;
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
@@ -129,10 +129,12 @@ __global__ void __launch_bounds__(256) fused_rs_step_ag_kernel(PeerPtrs grads, P
             // all-gather: the updated parameters go straight to every rank's buffer
             uint4 o;
             vpack<T, N>(p, o);
-            if constexpr (NVLS && sizeof(T) * N == 16) {
+            // n_push = world: every rank's buffer (all-gather fused into the step); n_push = 1: only this rank's own buffer (the
+            // peers fetch these rows from inside the first GEMM that consumes the weight)
+            if (NVLS && sizeof(T) * N == 16 && n_push == world) {
                 multimem_st_u32x4(reinterpret_cast<char*>(mc_param) + (off + i0) * sizeof(T), o);
             } else {
-                for (int kk = 0; kk < world; ++kk)
+                for (int kk = 0; kk < n_push; ++kk)
                     vstore_packed<T, N>(reinterpret_cast<T*>(params.p[(rank + kk) % world]) + off + i0, o);
             }
         }
@@ -248,8 +250,9 @@ void dist_push(bool nvls, const PeerPtrs& params, void* mc, int world, int rank,
 
 void dist_fused_flat_step(int op, int gdtype, int pdtype, bool nvls, const PeerPtrs& grads, const PeerPtrs& params, const void* mc_grad,
                           void* mc_param, int world, int rank, int64_t off, int64_t n, float lr, float beta1, float beta2, float eps, float wd, float bc1, float bc2, float gscale,
-                          float* master, float* m, float* v, const float* dyn, cudaStream_t s) {
+                          float* master, float* m, float* v, const float* dyn, bool push, cudaStream_t s) {
     if (n <= 0) return;
+    const int n_push = push ? world : 1;
     count_launch();
     FlatStep st{lr, beta1, beta2, eps, wd, bc1, bc2, gscale, master, m, v, dyn};
     if (nvls && gdtype != pdtype) nvls = false;              // the multimem path needs 16-byte vectors of both buffers
@@ -259,7 +262,7 @@ void dist_fused_flat_step(int op, int gdtype, int pdtype, bool nvls, const PeerP
     const int u_sel = unroll ? unroll : (nvls ? 4 : 2);
     const int64_t want = (n / 4 + 255) / 256;
     const int g = (int)(want < 1 ? 1 : (want > 148LL * ctas ? 148LL * ctas : want));
-#define L4(OPV, G, T, NV, WW, UU) fused_rs_step_ag_kernel<OPV, G, T, NV, WW, UU><<<g, 256, 0, s>>>(grads, params, mc_grad, mc_param, world, rank, off, n, st)
+#define L4(OPV, G, T, NV, WW, UU) fused_rs_step_ag_kernel<OPV, G, T, NV, WW, UU><<<g, 256, 0, s>>>(grads, params, mc_grad, mc_param, world, rank, off, n, st, n_push)
 #define L3(OPV, G, T, NV, WW) \
     if (u_sel == 4) L4(OPV, G, T, NV, WW, 4); else if (u_sel == 2) L4(OPV, G, T, NV, WW, 2); else L4(OPV, G, T, NV, WW, 1)
 #define L2(OPV, G, T) \

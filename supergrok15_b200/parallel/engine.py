@@ -60,7 +60,7 @@ class ZeroEngine:
     def __init__(self, model: torch.nn.Module, optimizer: str = "supergrok2", opt_kwargs: Optional[dict] = None,
                  comm: Optional[str] = None, param_dtype: torch.dtype = torch.bfloat16, group=None,
                  timeout_s: float = 20.0, criterion=None, graph: Optional[bool] = None, graph_warmup: int = 3,
-                 overlap: bool = False, bucket_numel: int = 1 << 24, heartbeat=None):
+                 overlap: bool = False, bucket_numel: int = 1 << 24, heartbeat=None, gather: str = "push"):
         self.comm = comm or os.environ.get("GROK_COMM", "p2p")
         assert self.comm in ("p2p", "nvls", "nccl")
         self.rank, self.world = symm.world_info(group)
@@ -89,14 +89,34 @@ class ZeroEngine:
             warnings.warn(f"overlap=True is implemented for the flat optimizers ({', '.join(FLAT_OPTIMIZERS)}); '{optimizer}' needs "
                           "global scalars or whole tensors before its first update and runs its step after backward")
         self.buckets: List[dict] = []
+        # gather="gemm" (AdamW / Lion): the rows of every Linear weight the fused kernel takes are owned by the ranks in turn; the
+        # step updates only the owner's rows and the all-gather happens inside the first GEMM that consumes the weight
+        assert gather in ("push", "gemm")
+        self.gw_idx: List[int] = []
+        self._gather_mods = []
+        if gather == "gemm":
+            if not (self.flat_mode and self.cuda and self.comm != "nccl" and not overlap):
+                raise ValueError("gather='gemm' needs a flat optimizer (adamw / lion) on the in-kernel collectives, without overlap")
+            by_id = {id(p): i for i, p in enumerate(self.params)}
+            for mod in self.model.modules():
+                if isinstance(mod, torch.nn.Linear) and id(mod.weight) in by_id:
+                    n_out, n_in = mod.weight.shape
+                    if n_out % (32 * self.world) == 0 and n_in % 8 == 0 and param_dtype == torch.bfloat16:
+                        self.gw_idx.append(by_id[id(mod.weight)])
+                        self._gather_mods.append(mod)
         # ---- layout of the flat parameter / gradient buffers
         if self.flat_mode:
             self.owner = [0] * len(numels)
-            offs, pos = [], 0
-            for n in numels:
-                offs.append(pos)
-                pos += -(-n // 8) * 8
-            total = -(-pos // (8 * self.world)) * 8 * self.world
+            gw = set(self.gw_idx)
+            order = self.gw_idx + [i for i in range(len(numels)) if i not in gw]     # row-owned weights first, the rest after them
+            offs, pos = [0] * len(numels), 0
+            self.rest_lo = 0
+            for k, i in enumerate(order):
+                if k == len(self.gw_idx) and self.gw_idx:               # the rest starts on a boundary every rank's slice can share
+                    pos = self.rest_lo = -(-pos // (8 * self.world)) * 8 * self.world
+                offs[i] = pos
+                pos += -(-numels[i] // 8) * 8
+            total = self.rest_lo + -(-(pos - self.rest_lo) // (8 * self.world)) * 8 * self.world
             self.offsets, self.total = offs, total
             self.regions = ownership.flat_ranges(total, self.world)
             if self.overlap:
@@ -135,8 +155,20 @@ class ZeroEngine:
                                  f"{self.world} ranks one; use fewer ranks, or 'adamw' / 'lion' / 'supergrok2'")
         self.my_begin, self.my_end = self.regions[self.rank]
         # (begin, end, offset into this rank's state) of every flat range this rank owns: one range, or one per bucket
+        self.seg_push: Dict[int, bool] = {}                             # segment begin -> False when the all-gather is left to the first GEMM
         if self.overlap:
             self.segments = [(bk["mine"][0], bk["mine"][1], bk["state_off"]) for bk in self.buckets if bk["mine"][1] > bk["mine"][0]]
+        elif self.gw_idx:
+            self.segments, so = [], 0
+            for i in self.gw_idx:                                        # this rank's rows of every row-owned weight
+                per = numels[i] // self.world
+                b = self.offsets[i] + self.rank * per
+                self.segments.append((b, b + per, so))
+                self.seg_push[b] = False
+                so += per
+            per = (self.total - self.rest_lo) // self.world               # an equal slice of everything else
+            if per:
+                self.segments.append((self.rest_lo + self.rank * per, self.rest_lo + (self.rank + 1) * per, so))
         else:
             self.segments = [(self.my_begin, self.my_end, 0)] if self.my_end > self.my_begin else []
         self.n_own = sum(e - b for b, e, _ in self.segments)
@@ -171,6 +203,11 @@ class ZeroEngine:
         self._build_optimizer()
         self.steps = 0
         self.launches = 0
+        self.param_version = 0                                         # bumped by every step: a weight gathered at an older version is stale
+        if self.gw_idx:
+            from . import gather_linear
+            gather_linear.install(self, self._gather_mods, self.gw_idx)
+            self.use_graph = False            # the gathering GEMMs take their call number by value: forward is not replayed from a graph
         # In-kernel collectives with every per-step scalar in a device table: the whole step (barrier, reduce-scatter + optimizer +
         # all-gather, barrier) is a fixed launch sequence and is captured into the same CUDA graph as forward / backward.
         self.fused = self.cuda and self.comm != "nccl"
@@ -393,7 +430,8 @@ class ZeroEngine:
         _build.require().dist_fused_flat_step(FLAT_OPTIMIZERS[self.name], _DT[self.pdtype], _DT[self.pdtype], self.gbuf.peer_ptrs,
                                               self.pbuf.peer_ptrs, self.rank, b, e - b, f, self.master[so:], self.m[so:],
                                               self.v[so:] if self.v is not None else None, nvls,
-                                              self.gbuf.multicast_ptr if nvls else 0, self.pbuf.multicast_ptr if nvls else 0, dyn)
+                                              self.gbuf.multicast_ptr if nvls else 0, self.pbuf.multicast_ptr if nvls else 0, dyn,
+                                              self.seg_push.get(b, True))
         self.launches += 1
 
     def _flat_host_segment(self, b: int, e: int, so: int, step_no: int):
@@ -517,6 +555,7 @@ class ZeroEngine:
         hook("barrier2")
 
     def _host_post(self):
+        self.param_version += 1
         if self.name == "supergrok2":
             if self.own_idx:
                 self.opt._after_step()
@@ -608,6 +647,7 @@ class ZeroEngine:
                 if e > b:
                     dist.broadcast(self.pbuf.tensor[b:e], src=rr, group=self.group)
         self._barrier(2)                                              # every rank's parameters are complete
+        self.param_version += 1
         self._publish_status()
 
     def _fwd_bwd(self, x: torch.Tensor, y: torch.Tensor, micro_batches: int) -> torch.Tensor:
@@ -714,6 +754,21 @@ class ZeroEngine:
         self._device_step(hook=timer.mark)
         self._host_post()
         return timer.finish()
+
+    @torch.no_grad()
+    def gather_params(self):
+        """gather="gemm": make every rank's parameter buffer complete NOW (each owner stores its rows into the peers' buffers),
+        for code that reads the weights outside a forward pass: evaluation through other modules, export, comparisons."""
+        if not self.gw_idx or self.world == 1:
+            return
+        C = _build.require()
+        es = self.pbuf.tensor.element_size()
+        for b, e, _ in self.segments:
+            if self.seg_push.get(b, True) is False:
+                C.dist_push(False, self.pbuf.peer_ptrs, 0, self.rank, b * es, (e - b) * es, self.pbuf.tensor)
+        self._barrier(5)
+        for mod in self._gather_mods:
+            mod._sg_gather.version = self.param_version
 
     # ------------------------------------------------------------------ introspection
     def state_bytes(self) -> int:

@@ -81,3 +81,26 @@ def plot_heatmap(table: Dict[str, Dict[str, float]], title: str, path: str) -> b
     fig.savefig(path, dpi=120)
     plt.close(fig)
     return True
+
+
+def plot_grouped_bars(table: Dict[str, Dict[str, float]], title: str, path: str) -> bool:
+    """One group of bars per row of ``table`` (train split or architecture), one bar per optimizer
+    (reference grokking_race_v2.py:1359-1478)."""
+    plt = _plt()
+    if plt is None or not table:
+        return False
+    groups = list(table)
+    names = sorted({n for row in table.values() for n in row})
+    fig, ax = plt.subplots(figsize=(max(6, 1.2 * len(groups) * max(len(names), 1) / 3), 4))
+    w = 0.8 / max(len(names), 1)
+    for k, n in enumerate(names):
+        ax.bar([g + k * w for g in range(len(groups))], [table[g].get(n, 0.0) for g in groups], width=w, label=n)
+    ax.set_xticks([g + 0.4 - w / 2 for g in range(len(groups))])
+    ax.set_xticklabels(groups)
+    ax.set_ylabel("steps")
+    ax.set_title(title)
+    ax.legend(fontsize=7, ncol=2)
+    fig.tight_layout()
+    fig.savefig(path, dpi=120)
+    plt.close(fig)
+    return True

@@ -175,16 +175,30 @@ def save_json(rbo, save_dir="results", total_wall=None, model_type="decoder", fr
     return path
 
 
+def _grok_table(cells: Dict) -> Dict[str, Dict[str, float]]:
+    """{row label: {optimizer: mean steps to grok (total steps when a run did not grok)}}."""
+    return {str(k): {n: float(np.mean([r.grokking_step or r.total_steps for r in runs])) for n, runs in rbo.items()} for k, rbo in cells.items()}
+
+
 def run_multi_split(base_cfg=None, splits=TRAIN_SPLITS, **kw):
     out = {}
     for ft in splits:
         c = dict(base_cfg or {}, frac_train=ft)
         out[ft] = run_pipeline(c, **kw)
+    if kw.get("save_dir") and kw.get("plot", True):
+        from .plots import plot_grouped_bars
+        plot_grouped_bars(_grok_table({f"{int(ft * 100)}% train": r for ft, r in out.items()}), "steps to grok by train split",
+                          os.path.join(kw["save_dir"], "split_comparison.png"))
     return out
 
 
 def run_architecture_comparison(base_cfg=None, archs=("decoder", "vit", "mamba"), **kw):
-    return {a: run_pipeline(dict(base_cfg or {}, model_type=a), **kw) for a in archs}
+    out = {a: run_pipeline(dict(base_cfg or {}, model_type=a), **kw) for a in archs}
+    if kw.get("save_dir") and kw.get("plot", True):
+        from .plots import plot_grouped_bars
+        plot_grouped_bars(_grok_table({MODEL_LABELS.get(a, a): r for a, r in out.items()}), "steps to grok by architecture",
+                          os.path.join(kw["save_dir"], "architecture_comparison.png"))
+    return out
 
 
 def run_scale_comparison(base_cfg=None, scales=("small", "medium", "large"), **kw):
@@ -228,6 +242,7 @@ def main(argv=None):
     ap.add_argument("--dtype", default="fp32", choices=["fp32", "bf16", "fp16"])
     ap.add_argument("--reference-compat", action="store_true", help="reproduce the reference's SAM / bias-correction / amplifier quirks")
     ap.add_argument("--cuda-graph", action="store_true")
+    ap.add_argument("--compile-model", action="store_true", help="wrap the model in torch.compile (reference grokking_race_v2.py:432-443); off by default")
     ap.add_argument("--save-dir", default="results")
     ap.add_argument("--resume", action="store_true", help="skip the (optimizer, seed) jobs already recorded in the save directory's progress file")
     a = ap.parse_args(argv)
@@ -242,12 +257,13 @@ def main(argv=None):
     opts = list(ALL_OPTIMIZERS) if a.optimizers == "all" else [o.strip() for o in a.optimizers.split(",")]
     seeds = SEEDS if a.seeds == "all" else [int(s) for s in a.seeds.split(",")]
     base = dict(MODEL_SCALES[a.model_scale], model_type=a.model_type, task=a.task, frac_train=a.frac_train, max_steps=a.max_steps,
-                use_amp=a.dtype != "fp32", amp_dtype=a.dtype, reference_compat=a.reference_compat, use_cuda_graph=a.cuda_graph)
+                use_amp=a.dtype != "fp32", amp_dtype=a.dtype, reference_compat=a.reference_compat, use_cuda_graph=a.cuda_graph, compile_model=a.compile_model)
     if not a.no_status_server:
         try:
             status.start_status_server(a.port)
         except OSError:
             pass
+    status.start_ntfy_listener(a.ntfy)
     status.ntfy(a.ntfy, f"race started: mode {a.mode}, {len(opts)} optimizers, {len(seeds)} seeds")
     kw = dict(optimizers=opts, seeds=seeds, gpus=gpus if gpus and len(gpus) > 1 else None, save_dir=a.save_dir, resume=a.resume)
     if a.mode == "A":

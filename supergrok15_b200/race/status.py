@@ -76,3 +76,55 @@ def ntfy(topic: Optional[str], message: str, title: str = "grokking race") -> bo
         return True
     except Exception:  # noqa: BLE001
         return False
+
+
+def status_text(snap: Optional[dict] = None) -> str:
+    """Progress report as the reply to a "status" query (reference grokking_race_v2.py:176-193)."""
+    s = snap or snapshot()
+    res = s.get("results", {})
+    grokked = sum(1 for r in res.values() if r and r.get("grok") is not None)
+    lines = [f"{s['done_jobs']}/{s['total_jobs']} runs complete", f"{grokked} grokked | {len(res) - grokked} DNF | {len(s['errors'])} errors"]
+    if "elapsed_s" in s:
+        lines.append(f"elapsed {int(s['elapsed_s'])} s, ETA {int(s['eta_s'])} s")
+    if s.get("current"):
+        lines.append("current: " + ", ".join(f"{k} step {v['step']} val {v['val_acc']:.3f}" for k, v in list(s["current"].items())[:4]))
+    return "\n".join(lines)
+
+
+QUERIES = ("status", "progress", "update", "?", "eta")
+
+
+def handle_ntfy_line(topic: str, line: bytes, send=None) -> bool:
+    """One line of the topic's JSON stream: a message whose text is one of QUERIES is answered with the progress report."""
+    try:
+        msg = json.loads(line)
+    except Exception:  # noqa: BLE001
+        return False
+    if msg.get("event") != "message" or msg.get("message", "").strip().lower() not in QUERIES:
+        return False
+    (send or ntfy)(topic, status_text(), "Progress Report")
+    return True
+
+
+def start_ntfy_listener(topic: Optional[str]) -> Optional[threading.Thread]:
+    """Listen on ntfy.sh/<topic>/json and answer "status" / "progress" / "eta" / "?" with the progress report
+    (reference grokking_race_v2.py:161-203).  Without a topic, without `requests` or without network it does nothing."""
+    if not topic:
+        return None
+
+    def listen():
+        try:
+            import requests
+        except Exception:  # noqa: BLE001
+            return
+        while True:
+            try:
+                r = requests.get(f"https://ntfy.sh/{topic}/json", stream=True, timeout=600)
+                for line in r.iter_lines():
+                    if line:
+                        handle_ntfy_line(topic, line)
+            except Exception:  # noqa: BLE001
+                time.sleep(10)                        # reconnect
+    t = threading.Thread(target=listen, daemon=True)
+    t.start()
+    return t

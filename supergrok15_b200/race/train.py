@@ -281,6 +281,16 @@ def train(name: str, c: dict, init_state, tx, ty, vx, vy, dev, bp: int = 0, prog
     r = TrainResult(DISPLAY_NAMES.get(name, name), c["seed"], c.get("model_type", "decoder"), c.get("frac_train", 0.5))
     m = build_model(c, dev)
     m.load_state_dict(copy.deepcopy(init_state), strict=True)
+    if c.get("compile_model", False) and hasattr(torch, "compile"):
+        # the reference wraps the model in torch.compile when asked (grokking_race_v2.py:432-443, 540-546); the parameters stay
+        # those of ``m`` (the optimizers hold them), a failed compilation keeps the eager module
+        try:
+            fwd = torch.compile(m, mode="reduce-overhead", fullgraph=False)
+            with torch.no_grad():
+                fwd(tx[:2])
+            m.forward = fwd.forward if hasattr(fwd, "forward") else m.forward
+        except Exception as exc:  # noqa: BLE001
+            warnings.warn(f"torch.compile failed ({type(exc).__name__}); running the eager model")
     ctx = spec.build(m, c, dev)
     opt = ctx["opt"]
     if c.get("use_cuda_graph", False) and dev.type == "cuda" and not spec.adaptive:

@@ -73,7 +73,7 @@ def _run_engine(world, sharding, steps=3):
     port = _free_port()
     out = os.path.join(tempfile.mkdtemp(), "out.pt")
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
-    procs = [subprocess.Popen([sys.executable, os.path.join(HERE, "muon_engine_worker.py"), str(r), str(world), str(port), out, sharding, str(steps)],
+    procs = [subprocess.Popen([sys.executable, os.path.join(HERE, "llama_engine_worker.py"), str(r), str(world), str(port), out, sharding, str(steps)],
                               env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True) for r in range(world)]
     logs = []
     for p in procs:
@@ -95,8 +95,8 @@ def test_engine_muon_row_sharded_matches_whole_matrix_ownership():
     run with every matrix owned whole by one rank.  Both iterate in bf16; the parameters agree to a fraction of the update."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
-    rows = _run_engine(2, "rows")
-    whole = _run_engine(2, "tensors")
+    rows = _run_engine(2, "muon/rows")
+    whole = _run_engine(2, "muon/tensors")
     assert rows["row_sharded"] == 7 and whole["row_sharded"] == 0          # wq wk wv wo w1 w3 (tall / square), w2 (wide)
     assert all(torch.equal(rows["params"][0], p) for p in rows["params"])   # every rank ends with the same parameters
     # bf16 parameters: the two runs may round an update to neighbouring bf16 values (one unit in the last place of the largest
@@ -107,3 +107,22 @@ def test_engine_muon_row_sharded_matches_whole_matrix_ownership():
     moved = (b - whole["init"]).abs()
     assert float(((a - b).abs() > 0.25 * moved.max()).float().mean()) < 0.01
     assert rows["losses"][-1] < rows["losses"][0]
+
+
+@pytest.mark.gpu
+@pytest.mark.dist
+def test_engine_allgather_inside_the_first_gemm_matches_the_push_path():
+    """AdamW on two ranks: Linear weights whose rows are owned in turn and gathered inside the first consuming GEMM of the next
+    forward, against the path that pushes every updated parameter at the end of the step.  Same arithmetic on the same values:
+    the parameters must agree bit for bit, on every rank."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    fused = _run_engine(2, "adamw/gemm", steps=4)
+    push = _run_engine(2, "adamw/push", steps=4)
+    assert fused["gathered_in_gemm"] == 8 and push["gathered_in_gemm"] == 0          # 7 block matrices + the output head
+    assert all(torch.equal(fused["params"][0], p) for p in fused["params"])
+    # the forward GEMM differs (own tcgen05 kernel vs the library one), so the runs agree to bf16 rounding, not bitwise
+    a, b = fused["params"][0], push["params"][0]
+    ulp = 2.0 ** -7 * float(b.abs().max())
+    assert float((a - b).abs().max()) <= 2 * ulp, float((a - b).abs().max())
+    assert fused["losses"][-1] < fused["losses"][0] and abs(fused["losses"][-1] - push["losses"][-1]) < 0.05

@@ -94,3 +94,23 @@ def test_resume_skips_finished_jobs(tmp_path):
     assert again["adamw"][0].train_losses == first["adamw"][0].train_losses
     assert runner.main(["--no-status-server", "--optimizers", "adamw", "--seeds", "1", "--max-steps", "5", "--save-dir", str(tmp_path / "cli"),
                         "--resume"]) == 0
+
+
+def test_ntfy_status_query_is_answered_with_the_progress_report():
+    from supergrok15_b200.race import status
+    status.reset(4)
+    status.job_done("adamw", 1, {"grok": 120})
+    status.job_done("lion", 1, {"grok": None})
+    sent = []
+    line = b'{"event": "message", "message": " Status "}'
+    assert status.handle_ntfy_line("topic", line, send=lambda t, m, title: sent.append((t, m, title)))
+    assert sent and "2/4 runs complete" in sent[0][1] and "1 grokked | 1 DNF" in sent[0][1]
+    assert not status.handle_ntfy_line("topic", b'{"event": "message", "message": "hello"}', send=lambda *a: sent.append(a))
+    assert not status.handle_ntfy_line("topic", b'{"event": "open"}') and status.start_ntfy_listener(None) is None
+
+
+def test_grouped_bar_chart(tmp_path):
+    from supergrok15_b200.race.plots import plot_grouped_bars
+    ok = plot_grouped_bars({"25% train": {"adamw": 900.0, "lion": 700.0}, "50% train": {"adamw": 400.0, "lion": 350.0}}, "steps to grok",
+                           str(tmp_path / "bars.png"))
+    assert ok is False or (tmp_path / "bars.png").stat().st_size > 0       # False only when matplotlib is not installed

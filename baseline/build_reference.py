@@ -27,7 +27,7 @@ DEST = os.path.join(HERE, "_ref")
 def main():
     src = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("SG_REFERENCE_SRC")
     if not src or not os.path.isdir(src):
-        sys.exit("usage: python baseline/build_reference.py /path/to/reference")
+        sys.exit("usage: python baseline/build_reference.py /path/to/reference [wheel directory]")
     work = os.path.join(tempfile.mkdtemp(prefix="refbuild_"), "src")
     shutil.copytree(src, work)
     sp = os.path.join(work, "setup.py")
@@ -38,8 +38,12 @@ def main():
     s = s.replace('"-lineinfo",', '"-lineinfo",\n            "-gencode=arch=compute_100,code=sm_100",')
     open(sp, "w").write(s)
     env = dict(os.environ, TORCH_CUDA_ARCH_LIST="10.0", MAX_JOBS=os.environ.get("MAX_JOBS", "6"))
-    subprocess.check_call([sys.executable, "-m", "pip", "install", "--no-index", "--no-build-isolation", "--no-deps", "--find-links",
-                           "/opt/wheelhouse", "--target", DEST, "--upgrade", work], env=env)
+    # offline wheel directory for pip's --find-links: second argument, or $PIP_FIND_LINKS / $WHEELHOUSE, or none
+    wheels = sys.argv[2] if len(sys.argv) > 2 else (os.environ.get("PIP_FIND_LINKS") or os.environ.get("WHEELHOUSE"))
+    cmd = [sys.executable, "-m", "pip", "install", "--no-index", "--no-build-isolation", "--no-deps"]
+    if wheels:
+        cmd += ["--find-links", wheels]
+    subprocess.check_call(cmd + ["--target", DEST, "--upgrade", work], env=env)
     shutil.copy(os.path.join(src, "grokking_race_v2.py"), DEST)
     build_shim()
 

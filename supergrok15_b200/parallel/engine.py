@@ -186,6 +186,7 @@ class ZeroEngine:
         self.slots = symm.alloc(self.slots_n * max(self.world, 1), torch.float32, self.device, group)
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.epoch = 0
+        self._calls = 0                                                  # steps started so far (start-up steps wait longer for their peers)
         # the status word is copied to pinned host memory after every step and looked at before the next one is launched
         self._status_host = torch.zeros(1, dtype=torch.int32).pin_memory() if self.cuda else None
         self._status_event = None
@@ -349,12 +350,21 @@ class ZeroEngine:
             o._flat_layer_alphas[k] = 1.0 if o.gamma_alpha == 0.0 else (1.0 - o.gamma_alpha) ** (max(n_all - 1, 1) - i)
 
     # ------------------------------------------------------------------ collectives
+    def _wait_limit(self) -> float:
+        """Seconds a device-side wait on a peer may last.  The first steps of a run see seconds of skew between the ranks that has
+        nothing to do with a lost peer (lazy library initialisation, kernel loading, CUDA-graph capture and instantiation under
+        whatever load the host has), so they get at least a minute; afterwards ``timeout_s`` applies (a captured barrier keeps
+        the limit it was captured with, and capture happens after the start-up steps)."""
+        if self.cuda and torch.cuda.is_current_stream_capturing():
+            return self.timeout_s
+        return max(self.timeout_s, 60.0) if self._calls <= self.graph_warmup + 1 else self.timeout_s
+
     def _barrier(self, site: int):
         if self.world == 1:
             return
         if self.cuda and self.comm != "nccl":
             self.epoch += 1
-            _build.require().dist_barrier(self.pads.peer_ptrs, self.rank, self.epoch, self.status, self.timeout_s, site)
+            _build.require().dist_barrier(self.pads.peer_ptrs, self.rank, self.epoch, self.status, self._wait_limit(), site)
             self.launches += 1
         else:
             import torch.distributed as dist
@@ -364,7 +374,7 @@ class ZeroEngine:
         """Barrier k (1 or 2) of a device step: its epoch is the step's base epoch in the device table plus k, so the launch is
         the same every step and can be replayed from a CUDA graph."""
         if self.world > 1:
-            _build.require().dist_barrier(self.pads.peer_ptrs, self.rank, k, self.status, self.timeout_s, site, self.dyn)
+            _build.require().dist_barrier(self.pads.peer_ptrs, self.rank, k, self.status, self._wait_limit(), site, self.dyn)
             self.launches += 1
 
     def all_reduce_small(self, vec: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
@@ -515,6 +525,7 @@ class ZeroEngine:
         epoch base, learning rate, weight decay, per-tensor bias corrections) into the device table."""
         from ..ops import sg2 as sg2_ops
         C = _build.require()
+        self._calls += 1
         base = self.epoch
         if self.world > 1:
             self.epoch += 2                                           # the two barriers of the step use base + 1 and base + 2
@@ -592,6 +603,7 @@ class ZeroEngine:
             self._device_step()
             self._host_post()
             return
+        self._calls += 1
         self._barrier(1)                                              # every rank's backward has written its gradients
         # ---- reduce-scatter
         if fused:

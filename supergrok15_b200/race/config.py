@@ -83,7 +83,7 @@ class RaceConfig:
 
 def merged(base: Dict, name: str, extra: Optional[Dict] = None) -> Dict:
     c = dict(base)
-    c.update(OPTIMIZER_CONFIGS.get(name, {}))
+    c.update(OPTIMIZER_CONFIGS.get("supergrok11" if name == "supergrok" else name, {}))
     if extra:
         c.update(extra)
     return c

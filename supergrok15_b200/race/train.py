@@ -355,3 +355,6 @@ def _make_train_fn(name):
 
 
 OPTIMIZER_REGISTRY = {name: _make_train_fn(name) for name in SPECS}
+# the reference registers SuperGrok v1.1 under "supergrok" (grokking_race_v2.py:940-947): accept that key too
+OPTIMIZER_REGISTRY["supergrok"] = OPTIMIZER_REGISTRY["supergrok11"]
+SPECS["supergrok"] = SPECS["supergrok11"]

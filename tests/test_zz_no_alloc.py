@@ -38,6 +38,11 @@ def test_no_alloc_matches_regular_path_twice_in_a_row():
         assert rc == 0
         assert torch.cuda.memory_allocated() == before
         assert torch.allclose(out, ref, rtol=2e-5, atol=1e-6), (out, ref)
+        # and against a sum this library had no part in: float64 on the same values
+        sq = float(g.double().pow(2).sum())
+        norm = sq ** 0.5
+        want = torch.tensor([sq, max_norm / (norm + 1e-6) if norm > max_norm else 1.0, norm], dtype=torch.float64)
+        assert torch.allclose(out.double().cpu(), want, rtol=2e-5, atol=1e-6), (out, want)
 
 
 def test_no_alloc_rejects_oversize_and_null():

@@ -16,6 +16,7 @@ void dist_fused_flat_step(int op, int gdtype, int pdtype, bool nvls, const PeerP
 void dist_scatter_slots(const PeerPtrs& slots, int world, int rank, const float* vec, int n, cudaStream_t s);
 void dist_cast_push(int pdtype, const PeerPtrs& params, int world, int rank, int64_t off, int64_t n, const float* master, cudaStream_t s);
 void dist_reduce_slots(const float* my_slots, int world, float* out, int n, float scale, cudaStream_t s);
+void dist_bump(int* counter, cudaStream_t s);
 }
 
 namespace sgb {
@@ -83,7 +84,14 @@ void reduce_slots(Tensor my_slots, int64_t world, Tensor out, double scale) {
 }
 }  // namespace
 
+void bump(Tensor counter) {
+    TORCH_CHECK(counter.is_cuda() && counter.scalar_type() == at::kInt && counter.numel() >= 1, "counter: int32 CUDA tensor");
+    c10::cuda::CUDAGuard guard(counter.device());
+    sg::dist_bump(counter.data_ptr<int>(), at::cuda::getCurrentCUDAStream());
+}
+
 void register_dist(pybind11::module_& m) {
+    m.def("dist_bump", &bump);
     m.def("dist_barrier", &barrier, py::arg("pads"), py::arg("rank"), py::arg("epoch"), py::arg("status"), py::arg("timeout_s"), py::arg("site"),
           py::arg("dyn") = c10::optional<Tensor>());
     m.def("dist_pull_reduce", &pull_reduce);

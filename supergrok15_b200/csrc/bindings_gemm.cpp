@@ -10,9 +10,10 @@ int gemm_bf16_tn(const void* A, int lda, const void* B, int ldb, int M, int N, i
                  float* splitk_ws, int64_t splitk_ws_floats, int* err, cudaStream_t s, bool a_t, bool b_t);
 int gemm_bf16_tn_allgather(const void* A, int lda, const PeerPtrs& w_peers, int rank, int world, int M, int N, int K, void* C, int ldc,
                            bool c_bf16, int* counters, void* sched, int epoch, int n_copy, int* err, cudaStream_t s, float alpha,
-                           float beta, const void* D, int ldd, bool d_bf16, float diag, int diag_off, void* C2, int ldc2);
+                           float beta, const void* D, int ldd, bool d_bf16, float diag, int diag_off, void* C2, int ldc2, const int* epoch_ptr);
 int gemm_bf16_tn_reducescatter(const void* A, int lda, const void* B, int ldb, int M, int N, int K, const PeerPtrs& slots, const PeerPtrs& flags,
-                               int rank, int world, void* c_local, int ldc, int epoch, unsigned long long timeout_ns, int* err, cudaStream_t s);
+                               int rank, int world, void* c_local, int ldc, int epoch, unsigned long long timeout_ns, int* err, cudaStream_t s,
+                               const int* epoch_ptr);
 }
 
 namespace sgb {
@@ -54,7 +55,7 @@ void gemm_tn(const Tensor& a, const Tensor& b, Tensor out, double alpha, double 
 // Optional epilogue: out = alpha * acc + beta * d + diag * [m + diag_off == n]; out_t [N, M] receives the transposed result.
 void gemm_tn_allgather(const Tensor& a, const std::vector<int64_t>& w_ptrs, int64_t rank, int64_t N, Tensor out, Tensor counters, int64_t epoch,
                        int64_t n_copy, Tensor err, double alpha, double beta, const c10::optional<Tensor>& d, double diag, int64_t diag_off,
-                       const c10::optional<Tensor>& out_t) {
+                       const c10::optional<Tensor>& out_t, const c10::optional<Tensor>& epoch_dev) {
     TORCH_CHECK(a.is_cuda() && a.scalar_type() == at::kBFloat16 && a.dim() == 2 && a.stride(1) == 1 && a.stride(0) % 8 == 0, "a must be bf16 [M,K]");
     const int world = (int)w_ptrs.size();
     TORCH_CHECK(world >= 1 && world <= sg::MAX_RANKS && rank >= 0 && rank < world, "bad rank / world");
@@ -63,7 +64,12 @@ void gemm_tn_allgather(const Tensor& a, const std::vector<int64_t>& w_ptrs, int6
     TORCH_CHECK(N % (world * 32) == 0, "N must be a multiple of 32 * world");
     TORCH_CHECK(counters.is_cuda() && counters.scalar_type() == at::kInt && counters.numel() >= (N + 255) / 256 + 2 &&
                 (reinterpret_cast<uintptr_t>(counters.data_ptr()) & 7) == 0, "counters: int32 [2 + ceil(N/256)], 8-byte aligned");
-    TORCH_CHECK(n_copy >= 1 && n_copy <= 148 && epoch >= 1, "n_copy in [1,148], epoch >= 1");
+    TORCH_CHECK(n_copy >= 1 && n_copy <= 148 && (epoch >= 1 || epoch_dev.has_value()), "n_copy in [1,148], epoch >= 1");
+    const int* ep_ptr = nullptr;
+    if (epoch_dev.has_value()) {
+        TORCH_CHECK(epoch_dev->is_cuda() && epoch_dev->scalar_type() == at::kInt && epoch_dev->numel() >= 1, "epoch_dev: int32 CUDA tensor");
+        ep_ptr = epoch_dev->data_ptr<int>();
+    }
     sg::PeerPtrs w{};
     for (int r = 0; r < world; ++r) {
         TORCH_CHECK(w_ptrs[r] != 0 && (w_ptrs[r] & 15) == 0, "weight buffers must be mapped and 16-byte aligned");
@@ -77,13 +83,13 @@ void gemm_tn_allgather(const Tensor& a, const std::vector<int64_t>& w_ptrs, int6
                                               c_bf16, counters.data_ptr<int>() + 2, counters.data_ptr<int>(), (int)epoch, (int)n_copy, err.data_ptr<int>(),
                                               at::cuda::getCurrentCUDAStream(), (float)alpha, (float)beta, d.has_value() ? d->data_ptr() : nullptr,
                                               d.has_value() ? (int)d->stride(0) : 0, d.has_value() && d->scalar_type() == at::kBFloat16, (float)diag,
-                                              (int)diag_off, out_t.has_value() ? out_t->data_ptr() : nullptr, out_t.has_value() ? (int)out_t->stride(0) : 0);
+                                              (int)diag_off, out_t.has_value() ? out_t->data_ptr() : nullptr, out_t.has_value() ? (int)out_t->stride(0) : 0, ep_ptr);
     TORCH_CHECK(rc == 0, "gemm_tn_allgather launch failed (code ", rc, ")");
 }
 
 // out [M / world, N] = this rank's rows of sum_r a_r @ b_r.T (K sharded over the ranks); slot_ptrs / flag_ptrs: every rank's buffers.
 void gemm_tn_reducescatter(const Tensor& a, const Tensor& b, const std::vector<int64_t>& slot_ptrs, const std::vector<int64_t>& flag_ptrs,
-                           int64_t rank, Tensor out, int64_t epoch, double timeout_s, Tensor err) {
+                           int64_t rank, Tensor out, int64_t epoch, double timeout_s, Tensor err, const c10::optional<Tensor>& epoch_dev) {
     TORCH_CHECK(a.is_cuda() && b.is_cuda() && a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16, "operands must be CUDA bf16");
     TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && a.size(1) == b.size(1) && a.stride(1) == 1 && b.stride(1) == 1 && a.stride(0) % 8 == 0 &&
                 b.stride(0) % 8 == 0, "a [M,K], b [N,K], rows 16-byte aligned");
@@ -98,7 +104,8 @@ void gemm_tn_reducescatter(const Tensor& a, const Tensor& b, const std::vector<i
     c10::cuda::CUDAGuard guard(a.device());
     const int rc = sg::gemm_bf16_tn_reducescatter(a.data_ptr(), (int)a.stride(0), b.data_ptr(), (int)b.stride(0), M, N, K, sl, fl, (int)rank, world,
                                                   out.data_ptr(), (int)out.stride(0), (int)epoch, (unsigned long long)(timeout_s * 1e9),
-                                                  err.data_ptr<int>(), at::cuda::getCurrentCUDAStream());
+                                                  err.data_ptr<int>(), at::cuda::getCurrentCUDAStream(),
+                                                  epoch_dev.has_value() ? epoch_dev->data_ptr<int>() : nullptr);
     TORCH_CHECK(rc == 0, "gemm_tn_reducescatter launch failed (code ", rc, ")");
 }
 }  // namespace
@@ -108,9 +115,10 @@ void register_gemm(pybind11::module_& m) {
           py::arg("d") = c10::nullopt, py::arg("bias") = c10::nullopt, py::arg("diag") = 0.0, py::arg("act") = 0,
           py::arg("out_t") = c10::nullopt, py::arg("err"), py::arg("splitk_ws") = c10::nullopt, py::arg("a_t") = false, py::arg("b_t") = false);
     m.def("gemm_tn_reducescatter", &gemm_tn_reducescatter, py::arg("a"), py::arg("b"), py::arg("slot_ptrs"), py::arg("flag_ptrs"), py::arg("rank"),
-          py::arg("out"), py::arg("epoch"), py::arg("timeout_s"), py::arg("err"));
+          py::arg("out"), py::arg("epoch"), py::arg("timeout_s"), py::arg("err"), py::arg("epoch_dev") = c10::nullopt);
     m.def("gemm_tn_allgather", &gemm_tn_allgather, py::arg("a"), py::arg("w_ptrs"), py::arg("rank"), py::arg("N"), py::arg("out"),
           py::arg("counters"), py::arg("epoch"), py::arg("n_copy"), py::arg("err"), py::arg("alpha") = 1.0, py::arg("beta") = 0.0,
-          py::arg("d") = c10::nullopt, py::arg("diag") = 0.0, py::arg("diag_off") = 0, py::arg("out_t") = c10::nullopt);
+          py::arg("d") = c10::nullopt, py::arg("diag") = 0.0, py::arg("diag_off") = 0, py::arg("out_t") = c10::nullopt,
+          py::arg("epoch_dev") = c10::nullopt);
 }
 }  // namespace sgb

@@ -44,6 +44,8 @@ struct AgArgs {
     int rank, world, n_copy;
     int* counters;              // [n tiles of BN rows] monotone counters in local memory
     int epoch;                  // call number (1, 2, ...): a tile is ready when counter >= epoch * remote_groups(tile)
+    const int* epoch_ptr;       // optional: the call number is read from device memory (a launch replayed from a CUDA graph sees
+                                // the value a preceding kernel of the same graph has bumped)
     PeerPtrs aux;               // RS mode: every rank's flag array
     int m_tiles_loc;            // RS mode: 128-row tiles per rank
     unsigned long long timeout_ns;
@@ -150,6 +152,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tn_kernel(const __grid_c
                                                                   const __grid_constant__ CUtensorMap map_c, int M, int N, int K,
                                                                   int splits, Epilogue ep, int* __restrict__ err, AgArgs ag) {
     constexpr bool AG = MODE == 1, RS = MODE == 2;
+    if constexpr (MODE != 0) {
+        if (ag.epoch_ptr) ag.epoch = *ag.epoch_ptr;
+    }
     if constexpr (AG) {
         if ((int)blockIdx.x < ag.n_copy) { ag_copier<BN>(ag, N, K); return; }
     }
@@ -620,13 +625,13 @@ int gemm_bf16_tn(const void* A, int lda, const void* B, int ldb, int M, int N, i
 // iteration of Muon builds its polynomial a I + b G + c G G and hands X on in both layouts from here).
 int gemm_bf16_tn_allgather(const void* A, int lda, const PeerPtrs& w_peers, int rank, int world, int M, int N, int K, void* C, int ldc,
                            bool c_bf16, int* counters, void* sched, int epoch, int n_copy, int* err, cudaStream_t s, float alpha,
-                           float beta, const void* D, int ldd, bool d_bf16, float diag, int diag_off, void* C2, int ldc2) {
+                           float beta, const void* D, int ldd, bool d_bf16, float diag, int diag_off, void* C2, int ldc2, const int* epoch_ptr) {
     if (M <= 0 || N <= 0 || K <= 0) return 0;
     if (world < 1 || world > MAX_RANKS || N % (world * AG_ROWS) != 0 || K % 8 != 0) return 6;
     if ((reinterpret_cast<uintptr_t>(C) & 15) != 0 || (ldc * (c_bf16 ? 2 : 4)) % 16 != 0) return 5;
     Epilogue ep{alpha, beta, diag, D, ldd, d_bf16 ? 1 : 0, nullptr, 0, 0, c_bf16 ? 1 : 0, C2, ldc2, diag_off};
     AgArgs ag{};
-    ag.w = w_peers; ag.rank = rank; ag.world = world; ag.n_copy = world > 1 ? n_copy : 0; ag.counters = counters; ag.epoch = epoch;
+    ag.w = w_peers; ag.rank = rank; ag.world = world; ag.n_copy = world > 1 ? n_copy : 0; ag.counters = counters; ag.epoch = epoch; ag.epoch_ptr = epoch_ptr;
     ag.sched = reinterpret_cast<unsigned long long*>(sched);
     // one tile width (256 rows) for every shape, so the counters have a fixed meaning; a tile that straddles two shards simply
     // waits for the remote groups of both
@@ -638,12 +643,13 @@ int gemm_bf16_tn_allgather(const void* A, int lda, const PeerPtrs& w_peers, int 
 // slots[o] / flags[o]: rank o's slot and flag buffers (layouts above the kernel); flags are zeroed once by the caller and epoch
 // counts the calls (1, 2, ...).  M must be a multiple of world * 128 and N of 64.
 int gemm_bf16_tn_reducescatter(const void* A, int lda, const void* B, int ldb, int M, int N, int K, const PeerPtrs& slots, const PeerPtrs& flags,
-                               int rank, int world, void* c_local, int ldc, int epoch, unsigned long long timeout_ns, int* err, cudaStream_t s) {
+                               int rank, int world, void* c_local, int ldc, int epoch, unsigned long long timeout_ns, int* err, cudaStream_t s,
+                               const int* epoch_ptr) {
     if (M <= 0 || N <= 0 || K <= 0) return 0;
     if (world < 1 || world > MAX_RANKS || M % (world * BM) != 0 || N % 64 != 0 || ldc % 8 != 0) return 6;
     Epilogue ep{1.f, 0.f, 0.f, nullptr, 0, 0, nullptr, 0, 0, 1, nullptr, 0, 0};
     AgArgs ag{};
-    ag.w = slots; ag.aux = flags; ag.rank = rank; ag.world = world; ag.epoch = epoch; ag.m_tiles_loc = M / world / BM;
+    ag.w = slots; ag.aux = flags; ag.rank = rank; ag.world = world; ag.epoch = epoch; ag.epoch_ptr = epoch_ptr; ag.m_tiles_loc = M / world / BM;
     ag.timeout_ns = timeout_ns; ag.c_local = c_local; ag.ldc = ldc;
     if (N > 128) return launch<256, 4, 2>(A, lda, B, ldb, M, N, K, ep, c_local, ldc, nullptr, 0, err, s, ag);
     return launch<128, 6, 2>(A, lda, B, ldb, M, N, K, ep, c_local, ldc, nullptr, 0, err, s, ag);

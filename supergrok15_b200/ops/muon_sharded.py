@@ -81,8 +81,10 @@ def arena_bytes(shapes: Sequence[Tuple[int, int]], world: int) -> int:
 class _Mat:
     """Buffers and the three phases of one row-sharded matrix."""
 
-    def __init__(self, R: int, C: int, arena: SymmArena, n_copy: int):
+    def __init__(self, R: int, C: int, arena: SymmArena, n_copy: int, it_dev: torch.Tensor):
         self.R, self.C, self.W, self.rank = R, C, arena.world, arena.rank
+        self.it_dev = it_dev                                                      # device counter of Newton-Schulz iterations so far: the call
+                                                                                  # number of every fused GEMM (one call per iteration each)
         W, r = self.W, self.rank
         self.Rl = R // W
         self.tall = R >= C
@@ -90,7 +92,6 @@ class _Mat:
         bf = dict(dtype=torch.bfloat16, device=dev)
         self.err = _gemm._err_flag(dev)
         self.n_copy = n_copy
-        self.ep = 0                                                               # calls so far (each AG counter set sees one call per iteration)
         if self.tall:
             Cl = C // W
             self.X = [torch.empty(self.Rl, C, **bf) for _ in range(2)]
@@ -127,72 +128,124 @@ class _Mat:
     def phase1(self, it: int):
         C = _build.require()
         q = it & 1
-        self.ep += 1
         if self.tall:            # G_r = rows r of sum over ranks of X_r^T X_r      (GEMM -> reduce-scatter)
-            C.gemm_tn_reducescatter(self.XT[q], self.XT[q], self.slot_ptrs, self.flag_ptrs, self.rank, self.G_own, self.ep, 10.0, self.err)
+            C.gemm_tn_reducescatter(self.XT[q], self.XT[q], self.slot_ptrs, self.flag_ptrs, self.rank, self.G_own, 0, 10.0, self.err,
+                                    epoch_dev=self.it_dev)
         else:                    # A_r = X_r X^T                                    (all-gather of X -> GEMM)
-            C.gemm_tn_allgather(self.X[q], self.Xs_ptrs[q], self.rank, self.R, self.A_own, self.cnt_x, self.ep, self.n_copy, self.err)
+            C.gemm_tn_allgather(self.X[q], self.Xs_ptrs[q], self.rank, self.R, self.A_own, self.cnt_x, 0, self.n_copy, self.err,
+                                epoch_dev=self.it_dev)
 
     def phase2(self, it: int, coeffs):
         C = _build.require()
         a, b, c = coeffs
         if self.tall:            # P_r = a I_r + b G_r + c G_r G                    (all-gather of G -> GEMM)
-            C.gemm_tn_allgather(self.G_own, self.G_ptrs, self.rank, self.C, self.P_own, self.cnt_g, self.ep, self.n_copy, self.err,
-                                alpha=c, beta=b, d=self.G_own, diag=a, diag_off=self.diag_off)
+            C.gemm_tn_allgather(self.G_own, self.G_ptrs, self.rank, self.C, self.P_own, self.cnt_g, 0, self.n_copy, self.err,
+                                alpha=c, beta=b, d=self.G_own, diag=a, diag_off=self.diag_off, epoch_dev=self.it_dev)
         else:                    # B_r = a I_r + b A_r + c A_r A                    (all-gather of A -> GEMM)
-            C.gemm_tn_allgather(self.A_own, self.A_ptrs, self.rank, self.R, self.B, self.cnt_a, self.ep, self.n_copy, self.err,
-                                alpha=c, beta=b, d=self.A_own, diag=a, diag_off=self.diag_off)
+            C.gemm_tn_allgather(self.A_own, self.A_ptrs, self.rank, self.R, self.B, self.cnt_a, 0, self.n_copy, self.err,
+                                alpha=c, beta=b, d=self.A_own, diag=a, diag_off=self.diag_off, epoch_dev=self.it_dev)
 
     def phase3(self, it: int, last: bool):
         C = _build.require()
         q = it & 1
         if self.tall:            # X_r <- X_r P                                     (all-gather of P -> GEMM), both layouts
             if last:
-                C.gemm_tn_allgather(self.X[q], self.P_ptrs, self.rank, self.C, self.out32, self.cnt_p, self.ep, self.n_copy, self.err)
+                C.gemm_tn_allgather(self.X[q], self.P_ptrs, self.rank, self.C, self.out32, self.cnt_p, 0, self.n_copy, self.err,
+                                    epoch_dev=self.it_dev)
             else:
-                C.gemm_tn_allgather(self.X[q], self.P_ptrs, self.rank, self.C, self.X[q ^ 1], self.cnt_p, self.ep, self.n_copy, self.err,
-                                    out_t=self.XT[q ^ 1])
+                C.gemm_tn_allgather(self.X[q], self.P_ptrs, self.rank, self.C, self.X[q ^ 1], self.cnt_p, 0, self.n_copy, self.err,
+                                    out_t=self.XT[q ^ 1], epoch_dev=self.it_dev)
         else:                    # X_r <- B_r X                                     (X was gathered into local memory by phase 1)
             _gemm.gemm_tn(self.B, self.Xs[q], out=self.out32 if last else self.X[q ^ 1], b_t=True)
 
 
 class RowShardedNewtonSchulz:
-    """Newton-Schulz over a fixed list of row-sharded matrices.  ``barrier()`` must order the ranks on the current stream (the
-    ZeRO engine passes its in-kernel barrier; tests pass ``torch.distributed.barrier``)."""
+    """Newton-Schulz over a fixed list of row-sharded matrices.
+
+    Everything a step needs lives on the device: the call number of the fused GEMMs (``it``, bumped by a one-thread kernel at
+    the start of every iteration) and the epoch of the barriers between the phases (own signal pad; bumped the same way).  The
+    launch sequence of a step is therefore identical every time, and from the third call with the same inputs on it is replayed
+    from ONE CUDA graph (every rank captures at the same call): ~3 launches per matrix and iteration would otherwise be issued from
+    Python, slower than the GPU runs them.  ``barrier``: a callable that orders the ranks on the current stream replaces the
+    in-kernel barrier (and disables the graph); ``status``: the int32 status word that records a timed-out wait."""
 
     def __init__(self, shapes: Sequence[Tuple[int, int]], device, group=None, barrier: Optional[Callable[[], None]] = None,
-                 n_copy_ctas: int = 16):
+                 n_copy_ctas: int = 16, status: Optional[torch.Tensor] = None, timeout_s: float = 20.0, graph: bool = True):
         from ..parallel import symm
         self.rank, self.world = symm.world_info(group)
         for R, C in shapes:
             if not supported(R, C, self.world):
                 raise ValueError(f"row-sharded Newton-Schulz does not take a {R} x {C} matrix on {self.world} ranks")
         self.arena = SymmArena(arena_bytes(shapes, self.world), device, group)
-        self.mats = [_Mat(R, C, self.arena, n_copy_ctas) for R, C in shapes]
-        self.barrier = barrier or (lambda: None)
-        if self.world > 1 and barrier is None:
-            import torch.distributed as dist
-            self.barrier = lambda: dist.barrier(group)
+        self.it = torch.zeros(1, dtype=torch.int32, device=device)
+        self.mats = [_Mat(R, C, self.arena, n_copy_ctas, self.it) for R, C in shapes]
+        self.user_barrier = barrier
+        self.timeout_s = timeout_s
+        self.status = status if status is not None else torch.zeros(1, dtype=torch.int32, device=device)
+        self.bar_epoch = torch.zeros(16, dtype=torch.int32, device=device)         # word 0: epoch of the next barrier
+        self.pads = symm.alloc(64, torch.int32, device, group) if self.world > 1 and barrier is None else None
+        self.use_graph = bool(graph) and barrier is None
+        self._graphs, self._calls = {}, 0
+
+    def barrier(self, site: int = 30):
+        if self.world == 1:
+            return
+        if self.user_barrier is not None:
+            return self.user_barrier()
+        C = _build.require()
+        C.dist_bump(self.bar_epoch)
+        limit = self.timeout_s if torch.cuda.is_current_stream_capturing() or self._calls > 2 else max(self.timeout_s, 60.0)
+        C.dist_barrier(self.pads.peer_ptrs, self.rank, 0, self.status, limit, site, self.bar_epoch.view(torch.float32))
+
+    def _body(self, shards, steps, scales, coeffs):
+        C = _build.require()
+        for i, (m, x) in enumerate(zip(self.mats, shards)):
+            m.load(x, None if scales is None else scales[i])
+        self.barrier(30)                                 # wide form: every X_r is in place before anybody gathers it
+        for it in range(steps):
+            last = it == steps - 1
+            C.dist_bump(self.it)
+            for m in self.mats:
+                m.phase1(it)
+            self.barrier(31)
+            for m in self.mats:
+                m.phase2(it, coeffs)
+            self.barrier(32)
+            for m in self.mats:
+                m.phase3(it, last)
+            self.barrier(33)
 
     def run(self, shards: Sequence[torch.Tensor], steps: int, scales: Optional[torch.Tensor] = None, coeffs=NS_COEFFS) -> List[torch.Tensor]:
         """``shards[i]``: fp32 [R_i / W, C_i], this rank's rows of matrix i (``scales[i]``, a device scalar, is multiplied in:
         1 / (norm + eps) of the whole matrix).  Returns this rank's rows of the orthogonalised matrices (fp32, owned by this
         object and overwritten by the next call)."""
-        for i, (m, x) in enumerate(zip(self.mats, shards)):
-            m.load(x, None if scales is None else scales[i])
-        self.barrier()                                   # wide form: every X_r is in place before anybody gathers it
-        for it in range(steps):
-            last = it == steps - 1
-            for m in self.mats:
-                m.phase1(it)
-            self.barrier()
-            for m in self.mats:
-                m.phase2(it, coeffs)
-            self.barrier()
-            for m in self.mats:
-                m.phase3(it, last)
-            self.barrier()
-        return [m.out32 for m in self.mats]
+        self._calls += 1
+        outs = [m.out32 for m in self.mats]
+        if not self.use_graph or torch.cuda.is_current_stream_capturing():
+            self._body(shards, steps, scales, coeffs)
+            return outs
+        key = (tuple(x.data_ptr() for x in shards), steps, None if scales is None else scales.data_ptr(), tuple(coeffs))
+        ent = self._graphs.get(key, 0)
+        if isinstance(ent, int) and ent < 2:              # two eager calls (lazy initialisation, both buffer parities), then capture
+            self._graphs[key] = ent + 1
+            self._body(shards, steps, scales, coeffs)
+            return outs
+        if isinstance(ent, int):
+            try:
+                torch.cuda.synchronize(shards[0].device)
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    self._body(shards, steps, scales, coeffs)
+                ent = self._graphs[key] = g
+            except Exception as exc:  # noqa: BLE001
+                import warnings
+                warnings.warn(f"CUDA graph capture of the row-sharded Newton-Schulz failed ({type(exc).__name__}: {exc}); running eagerly")
+                self.use_graph = False
+                torch.cuda.synchronize(shards[0].device)
+                self._body(shards, steps, scales, coeffs)
+                return outs
+        ent.replay()
+        return outs
 
     def nvlink_bytes_per_iteration(self) -> int:
         """Bytes this rank receives per iteration: (W - 1) / W of two square matrices per matrix (bf16)."""

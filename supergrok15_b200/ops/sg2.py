@@ -19,9 +19,23 @@ import torch
 from .. import _build
 from . import oracle
 
-# target number of concurrently resident scan items: 148 SMs x 3 CTAs x 8 items, two waves
-_TARGET_ITEMS = 148 * 3 * 8 * 2
+# Scan items that are resident at once: 148 SMs x 4 CTAs (112 registers, 26.6 KB shared memory each) x 8 items per CTA.  All chunks
+# take about the same time, so the items should fill WHOLE waves of that many: one item too many starts a second wave that costs as
+# much as the first.  One wave for small steps (longer chunks: the per-chunk aggregate pass of phase 1 costs a fixed ~300 timesteps
+# per chunk), two for large ones.
+_WAVE_ITEMS = 148 * 4 * 8
 _MIN_CHUNK = 512
+
+
+def _pick_chunk_len(numels: Sequence[int]) -> int:
+    total2 = 2 * sum(numels)
+    waves = 1 if total2 <= _WAVE_ITEMS * 2048 else 2
+    cap = _WAVE_ITEMS * waves - 8                     # the forward-direction items are padded to a multiple of 8
+    L = max(_MIN_CHUNK, -(-total2 // cap))
+    L = -(-L // 16) * 16
+    while 2 * sum(max(1, -(-n // L)) for n in numels) > cap and L < (1 << 30):      # partial last chunks of the tensors must fit as well
+        L += 16
+    return L
 
 _FALLBACK_LAYOUT = None
 
@@ -143,7 +157,7 @@ class Plan:
         if max(self.numels) >= 2 ** 31 or self.total >= 2 ** 32:
             raise ValueError("a v2 step handles < 2^31 elements per tensor and < 2^32 in total per call")
         if chunk_len <= 0:
-            chunk_len = max(_MIN_CHUNK, -(-2 * self.total // _TARGET_ITEMS))
+            chunk_len = _pick_chunk_len(self.numels)
         chunk_len = -(-chunk_len // 16) * 16
         self.chunk_len = chunk_len
         items, tds = [], []

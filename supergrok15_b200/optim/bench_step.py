@@ -26,6 +26,9 @@ def main():
     ap.add_argument("--scale", default="medium", choices=["small", "medium", "large"])
     ap.add_argument("--no-bilevel", action="store_true")
     ap.add_argument("--kernels", action="store_true", help="also print the device time of every kernel of one step (torch.profiler)")
+    ap.add_argument("--engine", default="none", choices=["none", "fp32", "bf16"],
+                    help="run the step through ZeroEngine on this one GPU (world of one) with parameters of that dtype and fp32 masters: "
+                         "the path of the data-parallel benchmark (gradient pull fused into the first kernel, device table of step scalars)")
     a = ap.parse_args()
     root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
     sys.path.insert(0, root)
@@ -49,6 +52,28 @@ def main():
         except Exception as e:  # noqa: BLE001
             print(json.dumps({"impl": "reference", "unavailable": f"{type(e).__name__}: {str(e)[:200]}"}))
             return
+    elif a.engine != "none":
+        from supergrok15_b200.parallel import ZeroEngine
+        dt = torch.float32 if a.engine == "fp32" else torch.bfloat16
+        eng = ZeroEngine(model, "supergrok2", {}, param_dtype=dt, graph=False)
+        ge = torch.Generator(device="cuda").manual_seed(1)
+
+        def eng_step():
+            eng.gbuf.tensor.copy_((torch.randn(eng.gbuf.tensor.shape, device=dev, generator=ge) * 1e-3).to(dt))
+            eng.step()
+        for _ in range(a.warmup):
+            eng_step()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(a.steps):
+            eng_step()
+        e1.record()
+        torch.cuda.synchronize()
+        n_params = sum(p.numel() for p in model.parameters())
+        print(json.dumps({"impl": "ours", "engine": a.engine, "scale": a.scale, "params": n_params,
+                          "step_ms_including_gradient_fill": e0.elapsed_time(e1) / a.steps}))
+        return
     else:
         from supergrok15_b200.optim import SuperGrok2
         opt = SuperGrok2(model.parameters(), bilevel_checkpoint_interval=32)

@@ -311,7 +311,7 @@ class ZeroEngine:
             self.rs_views.append(dict(flat_lo=lo, n=n, master=self.rs_master[pos:pos + n], mom=self.rs_mom[pos:pos + n],
                                       gred=self.rs_gred[pos:pos + n], shape=(R // W, C)))
             pos += n
-        self.rs_ns = muon_sharded.RowShardedNewtonSchulz(shapes, self.device, self.group, barrier=lambda: self._barrier(20))
+        self.rs_ns = muon_sharded.RowShardedNewtonSchulz(shapes, self.device, self.group, status=self.status, timeout_s=self.timeout_s)
         C = _build.require()
         nb = C.mt_num_blocks(sizes)
         self.rs_partials = torch.empty(3 * max(nb, 1), dtype=torch.float32, device=self.device)

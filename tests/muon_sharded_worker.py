@@ -25,7 +25,7 @@ def main():
         full.append((X / (X.norm() + 1e-7)).to(dev))
     ns = RowShardedNewtonSchulz(SHAPES, dev)
     res = {}
-    for rep in range(2):                                  # the second call re-uses every counter and buffer
+    for rep in range(4):                                  # two eager calls, the capture of the whole step into one CUDA graph, one replay
         shards = [X[rank * (X.shape[0] // world):(rank + 1) * (X.shape[0] // world)].contiguous() for X in full]
         outs = ns.run(shards, 5)
         torch.cuda.synchronize()

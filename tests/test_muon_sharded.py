@@ -30,9 +30,10 @@ def test_row_sharded_newton_schulz_world_of_one(shape):
     X = torch.randn(shape, device="cuda")
     X = X / (X.norm() + 1e-7)
     ns = RowShardedNewtonSchulz([shape], X.device)
-    for _ in range(2):
+    for _ in range(4):                                   # eager, eager, captured into one CUDA graph, replayed
         out = ns.run([X], 5)[0]
     torch.cuda.synchronize()
+    assert len(ns._graphs) == 1 and not isinstance(next(iter(ns._graphs.values())), int)
     gemm.check()
     ref = oracle.newton_schulz(X.double(), 5).float()
     assert (out - ref).norm() / ref.norm() < 0.06
@@ -64,7 +65,7 @@ def test_row_sharded_newton_schulz_equals_whole_matrix(world):
         logs.append(o)
     assert all(p.returncode == 0 for p in procs), "\n".join(l[-3000:] for l in logs)
     res = torch.load(out)
-    assert len(res) == 6
+    assert len(res) == 12
     for key, e in res.items():
         assert e["rel_vs_fp32"] < 0.06 and e["orth_vs_fp32"] < 0.1 and e["rel_vs_whole_bf16"] < 0.06, (key, e)
 
@@ -113,8 +114,8 @@ def test_engine_muon_row_sharded_matches_whole_matrix_ownership():
 @pytest.mark.dist
 def test_engine_allgather_inside_the_first_gemm_matches_the_push_path():
     """AdamW on two ranks: Linear weights whose rows are owned in turn and gathered inside the first consuming GEMM of the next
-    forward, against the path that pushes every updated parameter at the end of the step.  Same arithmetic on the same values:
-    the parameters must agree bit for bit, on every rank."""
+    forward, against the path that pushes every updated parameter at the end of the step.  Every rank must end with the same
+    parameters, and the two paths must agree to bf16 rounding (their forward GEMMs are different kernels)."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     fused = _run_engine(2, "adamw/gemm", steps=4)

@@ -181,9 +181,7 @@ struct TensorDir {     // 32 bytes
 // fp64.  Per timestep the precompute is then 160 FMAs instead of 1040, and x / z / dt are evaluated by the column's own lane.
 //
 // Stage A: lane l = timestep (u0 + l): B[16], C[16] and (g, s) of that timestep go to its shared-memory row.
-// PERM: B and C are parked as (e_2q, e_2q+1, o_2q, o_2q+1) per group q of two RoPE pairs (e / o = even / odd state of a pair), the
-// order the packed recurrence of phase 3 loads them in; otherwise in natural order.
-template <int DIR, bool PERM = false>
+template <int DIR>
 __device__ __forceinline__ void stage_a(float* __restrict__ tile, const float2* __restrict__ gs, int64_t off, int n, int u, bool valid,
                                         int l) {
     constexpr int AF = (DIR == 0) ? P::AFF0 : P::AFF1;
@@ -198,8 +196,7 @@ __device__ __forceinline__ void stage_a(float* __restrict__ tile, const float2* 
         bc[k] = fmaf(c_w[w], v.x, fmaf(c_w[w + 1], v.y, c_w[w + 2]));
     }
 #pragma unroll
-    for (int q = 0; q < 8; ++q)
-        row[q] = PERM ? make_float4(bc[4 * q], bc[4 * q + 2], bc[4 * q + 1], bc[4 * q + 3]) : make_float4(bc[4 * q], bc[4 * q + 1], bc[4 * q + 2], bc[4 * q + 3]);
+    for (int q = 0; q < 8; ++q) row[q] = make_float4(bc[4 * q], bc[4 * q + 1], bc[4 * q + 2], bc[4 * q + 3]);
     row[8] = make_float4(v.x, v.y, 0.f, 0.f);
 }
 
@@ -208,17 +205,6 @@ __device__ __forceinline__ float rcp_approx(float x) {
     asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
     return r;
 }
-
-// Packed pairs of fp32 in one 64-bit register: Blackwell's FMA pipe takes two independent fp32 operations per instruction
-// (fma / mul / add .f32x2), which halves the issue slots of the recurrence.  A pair holds the SAME quantity of two different RoPE
-// pairs (2q and 2q + 1), so every operation is element-wise and no lane of a pair ever needs its neighbour.
-typedef unsigned long long f2_t;
-__device__ __forceinline__ f2_t pack2(float lo, float hi) { f2_t r; asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi)); return r; }
-__device__ __forceinline__ void unpack2(f2_t v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
-__device__ __forceinline__ f2_t fma2(f2_t a, f2_t b, f2_t c) { f2_t d; asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c)); return d; }
-__device__ __forceinline__ f2_t mul2(f2_t a, f2_t b) { f2_t d; asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b)); return d; }
-__device__ __forceinline__ f2_t add2(f2_t a, f2_t b) { f2_t d; asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b)); return d; }
-__device__ __forceinline__ f2_t neg2(f2_t a) { return a ^ 0x8000000080000000ULL; }
 
 // per (column, pair) transition: Abar_e, Abar_o, cos, sin from dt.   Abar = (1+a)/(1-a) = 2/(1-a) - 1 with a = dt*A/2 <= 0.
 __device__ __forceinline__ void pair_coeffs(float dt, float ah_e, float ah_o, float f, float& abe, float& abo, float& cs, float& sn) {
@@ -254,12 +240,9 @@ struct ColConst {
 };
 
 // PHASE 3: run a chunk forward from its carry-in; apply SiLU gate, D skip and out_proj; write the contexts.
-// The recurrence runs on packed pairs (fma.rn.f32x2): group q holds RoPE pairs 2q and 2q + 1, he2 / ho2 their even / odd states.
-// Per group and timestep: 25 FMA-pipe instructions and 2 reciprocals, against 38 + 6 special-function results for the same two
-// pairs in scalar form.  sin / cos of the rotation angle dt * f come from a polynomial on the FMA pipe while |dt| * max|f| <= 1/4
-// (rope_freq is initialised at N(0, 0.01^2): always, unless the meta-net has learned large frequencies); the truncation error,
-// 1.2e-8 for sin and 4e-10 for cos at the bound, is below that of sin.approx / cos.approx.  Beyond the bound the group falls
-// back to the special-function unit (decided per item and timestep by a vote of its 16 lanes: no divergence inside an item).
+// The recurrence stays scalar with sin.approx / cos.approx on the special-function unit: two rewrites that take the sincos off
+// that unit (packed f32x2 arithmetic over pairs of RoPE pairs; degree-5 / degree-6 polynomials for |theta| <= 0.25) were measured
+// at 18.9 M parameters and ran this phase in 23.5 ms and 24.2 ms against 6.4 ms for this form.
 template <int DIR>
 __device__ void scan_phase3(const Item& it, const TensorDir* __restrict__ tds, const float2* __restrict__ gs,
                             const uint32_t* __restrict__ vals_sorted, const float* __restrict__ carry, float* __restrict__ ctx,
@@ -267,29 +250,15 @@ __device__ void scan_phase3(const Item& it, const TensorDir* __restrict__ tds, c
     constexpr int W = (DIR == 0) ? P::DIR0 : P::DIR1;
     ColConst<DIR> cc;
     cc.load(j);
-    f2_t ahe2[4], aho2[4], f2[4], he2[4], ho2[4];
-    float fmax = 0.f;
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {
-        ahe2[q] = pack2(cc.ah[4 * q], cc.ah[4 * q + 2]);
-        aho2[q] = pack2(cc.ah[4 * q + 1], cc.ah[4 * q + 3]);
-        f2[q] = pack2(cc.f[2 * q], cc.f[2 * q + 1]);
-        fmax = fmaxf(fmax, fmaxf(fabsf(cc.f[2 * q]), fabsf(cc.f[2 * q + 1])));
-    }
+    float h[16];
     {
         const float* cin = carry + ((int64_t)item_idx * 16 + j) * 16;
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-            const float4 t = reinterpret_cast<const float4*>(cin)[q];          // states 4q .. 4q+3 = (e, o) of pair 2q, (e, o) of pair 2q+1
-            he2[q] = pack2(t.x, t.z); ho2[q] = pack2(t.y, t.w);
-        }
+        for (int q = 0; q < 4; ++q) { const float4 t = reinterpret_cast<const float4*>(cin)[q]; h[4 * q] = t.x; h[4 * q + 1] = t.y; h[4 * q + 2] = t.z; h[4 * q + 3] = t.w; }
     }
-    const f2_t one2 = pack2(1.f, 1.f), mone2 = pack2(-1.f, -1.f);
-    const f2_t c3 = pack2(-1.f / 6.f, -1.f / 6.f), c5 = pack2(1.f / 120.f, 1.f / 120.f);
-    const f2_t c2 = pack2(-0.5f, -0.5f), c4 = pack2(1.f / 24.f, 1.f / 24.f), c6 = pack2(-1.f / 720.f, -1.f / 720.f);
     for (int u0 = it.ub; u0 < it.ue; u0 += TILE_T) {
         const int cnt = (it.ue - u0 < TILE_T) ? (it.ue - u0) : TILE_T;
-        stage_a<DIR, true>(tile, gs, it.off, it.n, u0 + j, j < cnt, j);
+        stage_a<DIR>(tile, gs, it.off, it.n, u0 + j, j < cnt, j);
         __syncwarp(hmask);
         for (int l = 0; l < cnt; ++l) {                 // lane j = column
             float* row = tile + l * ROW;
@@ -297,45 +266,27 @@ __device__ void scan_phase3(const Item& it, const TensorDir* __restrict__ tds, c
             const float x = fmaf(cc.ux[0], v.x, fmaf(cc.ux[1], v.y, cc.ux[2]));
             const float z = fmaf(cc.uz[0], v.x, fmaf(cc.uz[1], v.y, cc.uz[2]));
             const float dt = softplus20(fmaf(cc.ud[0], v.x, fmaf(cc.ud[1], v.y, cc.ud[2])));
-            const float dtx = dt * x;
-            const f2_t dt2 = pack2(dt, dt), ndt2 = pack2(-dt, -dt), dtx2 = pack2(dtx, dtx);
-            const bool small = __all_sync(hmask, dt * fmax <= 0.25f);
-            f2_t y2 = pack2(0.f, 0.f);
+            float B[16], C[16];
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
-                // (Be_2q, Be_2q+1, Bo_2q, Bo_2q+1) and the same for C: two 64-bit pairs per 16-byte load
-                const ulonglong2 bq = reinterpret_cast<const ulonglong2*>(row)[q];
-                const ulonglong2 cq = reinterpret_cast<const ulonglong2*>(row + 16)[q];
-                // Abar = 2 / (1 - dt A / 2) - 1 for both states of both pairs from ONE reciprocal per pair: 1/de = dn / (de dn)
-                const f2_t de2 = fma2(ndt2, ahe2[q], one2), dn2 = fma2(ndt2, aho2[q], one2);
-                float p0, p1;
-                unpack2(mul2(de2, dn2), p0, p1);
-                const float r0 = rcp_approx(p0), r1 = rcp_approx(p1);
-                const f2_t R2 = pack2(r0 + r0, r1 + r1);
-                const f2_t abe2 = fma2(dn2, R2, mone2), abo2 = fma2(de2, R2, mone2);
-                const f2_t th2 = mul2(dt2, f2[q]);
-                f2_t sn2, cs2;
-                if (small) {
-                    const f2_t t2 = mul2(th2, th2);
-                    sn2 = mul2(th2, fma2(t2, fma2(t2, c5, c3), one2));
-                    cs2 = fma2(t2, fma2(t2, fma2(t2, c6, c4), c2), one2);
-                } else {
-                    float t0, t1, s0, s1, k0, k1;
-                    unpack2(th2, t0, t1);
-                    __sincosf(t0, &s0, &k0);
-                    __sincosf(t1, &s1, &k1);
-                    sn2 = pack2(s0, s1); cs2 = pack2(k0, k1);
-                }
-                const f2_t re2 = fma2(ho2[q], neg2(sn2), mul2(he2[q], cs2));      // even' = e cos - o sin
-                const f2_t ro2 = fma2(he2[q], sn2, mul2(ho2[q], cs2));            // odd'  = o cos + e sin
-                const f2_t ne2 = fma2(abe2, re2, mul2(dtx2, bq.x));
-                const f2_t no2 = fma2(abo2, ro2, mul2(dtx2, bq.y));
-                he2[q] = ne2; ho2[q] = no2;
-                y2 = fma2(ne2, cq.x, fma2(no2, cq.y, y2));
+                const float4 t = reinterpret_cast<const float4*>(row)[q];
+                B[4 * q] = t.x; B[4 * q + 1] = t.y; B[4 * q + 2] = t.z; B[4 * q + 3] = t.w;
+                const float4 c = reinterpret_cast<const float4*>(row + 16)[q];
+                C[4 * q] = c.x; C[4 * q + 1] = c.y; C[4 * q + 2] = c.z; C[4 * q + 3] = c.w;
             }
-            float y0, y1;
-            unpack2(y2, y0, y1);
-            row[36 + j] = fmaf(y0 + y1, silu(z), cc.Dj * x);    // out_j of this timestep
+            const float dtx = dt * x;
+            float y = 0.f;
+#pragma unroll
+            for (int p = 0; p < 8; ++p) {
+                float abe, abo, cs, sn;
+                pair_coeffs(dt, cc.ah[2 * p], cc.ah[2 * p + 1], cc.f[p], abe, abo, cs, sn);
+                const float he = h[2 * p], ho = h[2 * p + 1];
+                const float ne = fmaf(abe, he * cs - ho * sn, dtx * B[2 * p]);
+                const float no = fmaf(abo, ho * cs + he * sn, dtx * B[2 * p + 1]);
+                h[2 * p] = ne; h[2 * p + 1] = no;
+                y = fmaf(ne, C[2 * p], fmaf(no, C[2 * p + 1], y));
+            }
+            row[36 + j] = fmaf(y, silu(z), cc.Dj * x);    // out_j of this timestep
         }
         __syncwarp(hmask);
         if (j < cnt) {                                    // lane = timestep again: ctx = out_proj . out at the ORIGINAL index
@@ -363,12 +314,7 @@ __device__ void scan_phase3(const Item& it, const TensorDir* __restrict__ tds, c
     if (it.last) {
         float* dst = tds[it.td].h + j * 16;
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-            float e0, e1, o0, o1;
-            unpack2(he2[q], e0, e1);
-            unpack2(ho2[q], o0, o1);
-            reinterpret_cast<float4*>(dst)[q] = make_float4(e0, o0, e1, o1);
-        }
+        for (int q = 0; q < 4; ++q) reinterpret_cast<float4*>(dst)[q] = make_float4(h[4 * q], h[4 * q + 1], h[4 * q + 2], h[4 * q + 3]);
     }
 }
 

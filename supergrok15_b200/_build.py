@@ -153,6 +153,33 @@ def build_sanitized(out_dir) -> Path:
     return so
 
 
+def build_bounds_checked(out_dir) -> Path:
+    """Device-code check build: ``csrc/mt_kernels.cu`` compiled with ``-DGROK_BOUNDS_CHECK`` (every element access of the
+    multi-tensor optimizer kernels is compared with the driver's record of the allocation; a violation is skipped and
+    recorded, never a trap) and linked with the regular objects into ``out_dir``.  Load it with ``SG_EXT_SO``; run with
+    ``PYTORCH_NO_CUDA_MEMORY_CACHING=1`` so that every tensor is an allocation of its own; read ``_C.bounds_report()``."""
+    import torch
+    build()
+    out_dir = Path(out_dir)
+    out_dir.mkdir(parents=True, exist_ok=True)
+    nvcc = _nvcc()
+    cuda_home = str(Path(nvcc).parent.parent)
+    objs = []
+    for src in _sources():
+        if src.name == "mt_kernels.cu":
+            obj = out_dir / "mt_kernels.checked.o"
+            _run([nvcc, *NVCC_ARCH, "-O3", "-lineinfo", "-std=c++17", "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC", "-DGROK_BOUNDS_CHECK",
+                  f"-I{_CSRC}", f"-I{cuda_home}/include", "-c", str(src), "-o", str(obj)])
+            objs.append(obj)
+        else:
+            objs.append(_OBJ / (src.name + ".o"))
+    so = out_dir / _so_path().name
+    tlib = Path(torch.__file__).parent / "lib"
+    _run(["g++", "-shared", "-fopenmp", "-o", str(so), *map(str, objs), f"-L{tlib}", f"-L{cuda_home}/lib64", "-lc10", "-ltorch_cpu", "-ltorch",
+          "-ltorch_python", "-lc10_cuda", "-ltorch_cuda", "-lcudart", f"-Wl,-rpath,{tlib}", f"-Wl,-rpath,{cuda_home}/lib64"])
+    return so
+
+
 def load(build_if_needed: bool = True):
     """Return the extension module, or None (with the reason in ``load_error()``).  ``SG_EXT_SO`` names a shared object to load
     instead of the in-tree one (the sanitizer build of ``build_sanitized``)."""
@@ -197,5 +224,7 @@ def require():
 
 
 if __name__ == "__main__":
-    p = build(force="--force" in sys.argv, verbose="-v" in sys.argv)
-    print("built", p)
+    if "--bounds-check" in sys.argv:                     # python -m supergrok15_b200._build --bounds-check <dir>
+        print("built", build_bounds_checked(sys.argv[sys.argv.index("--bounds-check") + 1]))
+    else:
+        print("built", build(force="--force" in sys.argv, verbose="-v" in sys.argv))

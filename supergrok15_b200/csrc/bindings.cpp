@@ -135,6 +135,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           py::arg("partials") = c10::nullopt, py::arg("per_tensor_out") = c10::nullopt);
     m.def("scalar_finalize", &scalar_finalize);
     m.def("launch_count", []() { return sg::launch_count(); });
+    m.def("bounds_check_enabled", []() { return sg::bounds_check_enabled(); });
+    m.def("bounds_reset", []() { sg::bounds_reset(); });
+    m.def("bounds_report", []() { int v[8]; sg::bounds_report(v); return std::vector<int64_t>(v, v + 8); });
+    m.def("bounds_cap", [](int64_t bytes) { sg::bounds_cap((long long)bytes); });
+    m.def("bounds_extent_of", [](const at::Tensor& t) { return (int64_t)sg::bounds_extent_of(t.data_ptr()); });
     // kernels that run from a replayed CUDA graph are not enqueued by a launcher: the owner of the graph adds them here
     m.def("add_launches", [](int64_t n) { sg::count_launch((int)n); });
     py::dict ops;

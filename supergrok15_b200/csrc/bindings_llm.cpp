@@ -12,6 +12,8 @@ void gelu(int dtype, bool backward, const void* x, const void* dy, void* y, int6
 void embed_fwd(int dtype, const int64_t* ids, const void* W, void* out, int64_t T_tok, int D, int V, cudaStream_t st);
 void embed_keys(const int64_t* ids, uint32_t* keys, uint32_t* vals, int64_t T_tok, int V, cudaStream_t st);
 void embed_bwd(int dtype, const uint32_t* keys, const uint32_t* vals, const void* dout, void* dW, int64_t T_tok, int D, cudaStream_t st);
+bool embed_bwd_small_ok(int64_t T_tok, int V);
+void embed_bwd_small(int dtype, const int64_t* ids, const void* dout, void* dW, int64_t T_tok, int D, int V, bool accumulate, cudaStream_t st);
 void ce_fwd(int dtype, const void* logits, const int64_t* target, float* lse, float* loss, float* mean_out, int64_t rows, int V, int64_t ignore_index,
             cudaStream_t st);
 void ce_bwd(int dtype, const void* logits, const int64_t* target, const float* lse, const float* mean_out, const float* gout, void* dlogits,
@@ -100,15 +102,25 @@ Tensor embedding_fwd(const Tensor& ids, const Tensor& W) {
 }
 
 // Deterministic gradient of the gather: stable radix sort of the token ids (the framework's own sort), then one warp per id run.
-Tensor embedding_bwd(const Tensor& ids, const Tensor& dout_, int64_t V) {
+// Gradient of the table.  With acc the result is ADDED to that tensor (the table's own gradient buffer), which is returned.
+Tensor embedding_bwd(const Tensor& ids, const Tensor& dout_, int64_t V, const c10::optional<Tensor>& acc) {
     Tensor dout = dout_.contiguous();
     check_act(dout, "embedding");
     const int D = (int)dout.size(-1);
     const int64_t T_tok = ids.numel();
     TORCH_CHECK(D % 8 == 0 && T_tok < (int64_t)1 << 31, "embedding: width multiple of 8, fewer than 2^31 tokens");
+    if (acc.has_value())
+        TORCH_CHECK(acc->is_contiguous() && acc->dim() == 2 && acc->size(0) == V && acc->size(1) == D && acc->scalar_type() == dout.scalar_type() &&
+                    acc->device() == dout.device(), "embedding_bwd: acc must be a contiguous [V, D] tensor of the gradient's dtype and device");
     c10::cuda::CUDAGuard guard(dout.device());
     auto st = at::cuda::getCurrentCUDAStream();
     auto io = dout.options().dtype(at::kInt);
+    if (sg::embed_bwd_small_ok(T_tok, (int)V)) {                         // small table: one kernel, no sort, no zero fill
+        Tensor out = acc.has_value() ? *acc : at::empty({V, D}, dout.options());
+        sg::embed_bwd_small(dtype_code(dout), ids.data_ptr<int64_t>(), dout.data_ptr(), out.data_ptr(), T_tok, D, (int)V, acc.has_value(), st);
+        return out;
+    }
+    if (acc.has_value()) return acc->add_(embedding_bwd(ids, dout, V, c10::nullopt));
     Tensor dW = at::zeros({V, D}, dout.options());
     if (T_tok == 0) return dW;
     Tensor kv = at::empty({4, T_tok}, io);
@@ -197,7 +209,7 @@ void register_llm(pybind11::module_& m) {
     m.def("gelu_fwd", &gelu_fwd);
     m.def("gelu_bwd", &gelu_bwd);
     m.def("embedding_fwd", &embedding_fwd);
-    m.def("embedding_bwd", &embedding_bwd);
+    m.def("embedding_bwd", &embedding_bwd, py::arg("ids"), py::arg("dout"), py::arg("vocab"), py::arg("acc") = c10::optional<Tensor>());
     m.def("flash_fwd", &flash_fwd, py::arg("q"), py::arg("k"), py::arg("v"), py::arg("causal"), py::arg("err"), py::arg("variant") = 3);
     m.def("flash_bwd", &flash_bwd);
     m.def("flash_supported", [](int64_t S, int64_t HD) { return sg::flash_attn_supported((int)S, (int)HD); });

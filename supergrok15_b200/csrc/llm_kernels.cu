@@ -155,6 +155,54 @@ __global__ void __launch_bounds__(256) embed_bwd_kernel(const uint32_t* __restri
     }
 }
 
+// Small tables (vocabulary x tokens <= 2^24, the modular-arithmetic models): no sort.  CTA (v, slab) owns row v of dW and 256 of its
+// columns.  Its 8 warps split the token positions into 8 contiguous ranges; a warp reads 32 ids at a time, finds the positions whose
+// id is v with a ballot and adds their rows of dout in position order (lane = 8 columns); the 8 range sums are then added in warp
+// order.  Every CTA reads all ids (from L2), which is what limits the table size.  accumulate: dW already holds other contributions.
+template <typename T>
+__global__ void __launch_bounds__(256) embed_bwd_small_kernel(const int64_t* __restrict__ ids, const T* __restrict__ dout, T* __restrict__ dW,
+                                                              int64_t T_tok, int D, int V, bool accumulate) {
+    __shared__ float sh[8][256 + 8];
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    const int v = blockIdx.x;
+    const int c = blockIdx.y * 256 + lane * 8;
+    const int64_t per = ((T_tok + 7) / 8 + 31) / 32 * 32;              // positions per warp, a multiple of 32
+    const int64_t t0 = w * per, t1 = (t0 + per < T_tok) ? t0 + per : T_tok;
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int64_t t = t0; t < t1; t += 32) {
+        int64_t id = (t + lane < t1) ? ids[t + lane] : -1;
+        if (id >= V) id = V - 1;                                       // same clamp as the forward gather
+        if (id < 0 && t + lane < t1) id = 0;
+        unsigned m = __ballot_sync(0xffffffffu, id == v);
+        while (m) {
+            const int k = __ffs(m) - 1;
+            m &= m - 1;
+            if (c < D) {
+                float d[8];
+                Vec8<T>::ld(dout + (t + k) * D + c, d);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[j] += d[j];
+            }
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) sh[w][lane * 8 + j] = acc[j];
+    __syncthreads();
+    if (w == 0 && c < D) {
+        float o[8];
+        if (accumulate) Vec8<T>::ld(dW + (int64_t)v * D + c, o);
+        else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o[j] = 0.f;
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o[j] += sh[k][lane * 8 + j];
+        Vec8<T>::st(dW + (int64_t)v * D + c, o);
+    }
+}
+
 // ------------------------------------------------------------------------------------------------ cross-entropy
 // One CTA per row of logits [rows, V] (V a multiple of 8).  Forward: log-sum-exp (online max) and the row loss lse - x[target];
 // rows whose target equals ignore_index contribute nothing.
@@ -288,6 +336,15 @@ void embed_bwd(int dtype, const uint32_t* keys, const uint32_t* vals, const void
     if (T_tok <= 0) return;
     count_launch();
     DISPATCH_T(dtype, embed_bwd_kernel<T><<<(unsigned)((T_tok + 7) / 8), 256, 0, st>>>(keys, vals, (const T*)dout, (T*)dW, T_tok, D);)
+}
+
+bool embed_bwd_small_ok(int64_t T_tok, int V) { return V > 0 && V <= 65535 && T_tok * (int64_t)V <= ((int64_t)1 << 24); }
+
+void embed_bwd_small(int dtype, const int64_t* ids, const void* dout, void* dW, int64_t T_tok, int D, int V, bool accumulate, cudaStream_t st) {
+    if (V <= 0 || D <= 0) return;
+    count_launch();
+    const dim3 grid((unsigned)V, (unsigned)((D + 255) / 256));
+    DISPATCH_T(dtype, embed_bwd_small_kernel<T><<<grid, 256, 0, st>>>(ids, (const T*)dout, (T*)dW, T_tok, D, V, accumulate);)
 }
 
 void ce_fwd(int dtype, const void* logits, const int64_t* target, float* lse, float* loss, float* mean_out, int64_t rows, int V, int64_t ignore_index,

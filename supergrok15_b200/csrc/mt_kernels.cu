@@ -15,6 +15,46 @@ namespace sg {
 
 namespace {
 
+#ifdef GROK_BOUNDS_CHECK
+// Checked build (-DGROK_BOUNDS_CHECK, this file only): every element access of the multi-tensor kernel is compared with the
+// number of bytes that are really addressable from its base pointer.  That extent does not come from the launch descriptor (which
+// is what is being checked) but from the driver: before a launch the host asks cuMemGetAddressRange for the allocation that
+// holds each pointer and uploads "end of allocation - pointer" to g_extent.  An access past it is NOT made: the lanes read zeros /
+// drop the store, and the first violation is recorded in g_viol {count, op, role, tensor, index low 31 bits, index >> 31, 1 =
+// store}.  Nothing traps and the context stays usable.  With PyTorch's caching allocator an allocation is a whole segment, so
+// the check is exact only under PYTORCH_NO_CUDA_MEMORY_CACHING=1 (one cudaMalloc per tensor).
+__device__ unsigned long long g_extent[MT_NP][MT_MAX];
+__device__ int g_viol[8];
+
+struct CPtr {
+    void* p; unsigned long long bytes; int role, t, op;
+    __device__ __forceinline__ operator void*() const { return p; }
+};
+
+__device__ __forceinline__ bool checked_ok(const CPtr& P, int64_t i, int cnt, size_t esz, int store) {
+    if (P.bytes == 0 || (unsigned long long)(i + cnt) * esz <= P.bytes) return true;        // 0: extent unknown (not a device allocation)
+    if (atomicAdd(&g_viol[0], 1) == 0) {
+        g_viol[1] = P.op; g_viol[2] = P.role; g_viol[3] = P.t; g_viol[4] = (int)(i & 0x7fffffff); g_viol[5] = (int)(i >> 31); g_viol[6] = store;
+    }
+    return false;
+}
+
+template <typename T>
+__device__ __forceinline__ void ld4(const CPtr& P, int64_t i, int cnt, bool vec, float v[4]) {
+    if (checked_ok(P, i, cnt, sizeof(T), 0)) { sg::ld4<T>((const void*)P.p, i, cnt, vec, v); return; }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) v[k] = 0.f;
+}
+
+template <typename T>
+__device__ __forceinline__ void st4(const CPtr& P, int64_t i, int cnt, bool vec, const float v[4]) {
+    if (checked_ok(P, i, cnt, sizeof(T), 1)) sg::st4<T>((void*)P.p, i, cnt, vec, v);
+}
+#define MT_PTR(r) CPtr{a.ptr[r][t], g_extent[r][t], r, t, OP}
+#else
+#define MT_PTR(r) a.ptr[r][t]
+#endif
+
 struct Loc { int t; int64_t begin, end; };
 
 __device__ __forceinline__ Loc locate(const MTArgs& a) {
@@ -39,8 +79,8 @@ __global__ void __launch_bounds__(MT_THREADS) mt_kernel(const __grid_constant__ 
     extern __shared__ float smem[];           // MLP weights (SG15 / SG11_A / NEURALGROK)
     const Loc L = locate(a);
     const int t = L.t;
-    void* P0 = a.ptr[0][t]; void* P1 = a.ptr[1][t]; void* P2 = a.ptr[2][t]; void* P3 = a.ptr[3][t];
-    void* P4 = a.ptr[4][t]; void* P5 = a.ptr[5][t];
+    const auto P0 = MT_PTR(0); const auto P1 = MT_PTR(1); const auto P2 = MT_PTR(2); const auto P3 = MT_PTR(3);
+    const auto P4 = MT_PTR(4); const auto P5 = MT_PTR(5);
     const float ts0 = a.ts[t][0], ts1 = a.ts[t][1], ts2 = a.ts[t][2], ts3 = a.ts[t][3];
     const float clip = prm.clip ? *prm.clip : 1.f;
     const int H = prm.hidden;
@@ -306,8 +346,62 @@ static std::atomic<long long> g_launches{0};
 void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 long long launch_count() { return g_launches.load(std::memory_order_relaxed); }
 
+#ifdef GROK_BOUNDS_CHECK
+namespace {
+using AddressRangeFn = int (*)(unsigned long long*, size_t*, unsigned long long);
+long long g_cap = -1;                                  // test hook: upper limit on every extent (bytes), -1 = none
+
+AddressRangeFn address_range_fn() {
+    static AddressRangeFn fn = [] {
+        void* f = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuMemGetAddressRange", &f, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) f = nullptr;
+        return (AddressRangeFn)f;
+    }();
+    return fn;
+}
+
+unsigned long long extent_of(const void* ptr) {
+    AddressRangeFn fn = address_range_fn();
+    unsigned long long base = 0;
+    size_t size = 0;
+    if (!ptr || !fn || fn(&base, &size, (unsigned long long)(uintptr_t)ptr) != 0) return 0;
+    unsigned long long e = base + size - (unsigned long long)(uintptr_t)ptr;
+    if (g_cap >= 0 && e > (unsigned long long)g_cap) e = (unsigned long long)g_cap;
+    return e;
+}
+
+// The table is one device symbol shared by all launches: wait for the stream (an earlier launch may still read it), then copy.
+// A launch recorded into a CUDA graph keeps whatever the table holds when the graph runs, so it goes unchecked (zeros).
+void upload_extents(const MTArgs& a, cudaStream_t s) {
+    static unsigned long long host[MT_NP][MT_MAX];
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    cudaStreamIsCapturing(s, &cap);
+    if (cap != cudaStreamCaptureStatusNone) return;
+    for (int r = 0; r < MT_NP; ++r)
+        for (int t = 0; t < MT_MAX; ++t) host[r][t] = (t < a.n) ? extent_of(a.ptr[r][t]) : 0;
+    cudaStreamSynchronize(s);
+    cudaMemcpyToSymbol(g_extent, host, sizeof(host));
+}
+}  // namespace
+bool bounds_check_enabled() { return true; }
+void bounds_reset() { int z[8] = {0, 0, 0, 0, 0, 0, 0, 0}; cudaDeviceSynchronize(); cudaMemcpyToSymbol(g_viol, z, sizeof(z)); }
+void bounds_report(int out[8]) { cudaDeviceSynchronize(); cudaMemcpyFromSymbol(out, g_viol, 8 * sizeof(int)); }
+void bounds_cap(long long bytes) { g_cap = bytes; }
+long long bounds_extent_of(const void* ptr) { return (long long)extent_of(ptr); }
+#else
+bool bounds_check_enabled() { return false; }
+void bounds_reset() {}
+void bounds_report(int out[8]) { for (int k = 0; k < 8; ++k) out[k] = 0; }
+void bounds_cap(long long) {}
+long long bounds_extent_of(const void*) { return 0; }
+#endif
+
 void mt_launch(int op, int dtype, const MTArgs& a, const MTParams& p, cudaStream_t s) {
     if (a.blk_start[a.n] > 0) count_launch();
+#ifdef GROK_BOUNDS_CHECK
+    if (a.blk_start[a.n] > 0) upload_extents(a, s);
+#endif
     switch (op) {
 #define SG_CASE(X) case X: launch_typed<X>(dtype, a, p, s); break;
         SG_CASE(OP_ADAMW) SG_CASE(OP_LION) SG_CASE(OP_GROKFAST_EMA) SG_CASE(OP_GROKFAST_ADAMW) SG_CASE(OP_GROKADAMW)

@@ -373,15 +373,41 @@ __global__ void __launch_bounds__(256) norm_bwd_wide_kernel(const T* __restrict_
     if (RMS) for (int col = threadIdx.x; col < D; col += 256) part[((int64_t)blockIdx.x * 2 + 1) * D + col] = 0.f;
 }
 
+// Second stage of the parameter gradients: column c of dgamma / dbeta is the sum of its n_part partial rows.  A CTA owns 32
+// columns; its 8 warps take the partial rows p = warp, warp + 8, ... (four loads in flight each) and the 8 sub-sums are added in
+// warp order, so the result does not depend on timing.
 template <typename T>
 __global__ void __launch_bounds__(256) ln_bwd_reduce_kernel(const float* __restrict__ part, int n_part, int D, T* __restrict__ dgamma,
-                                                            T* __restrict__ dbeta) {
-    const int c = blockIdx.x * 256 + threadIdx.x;
-    if (c >= D) return;
+                                                            T* __restrict__ dbeta, bool accumulate) {
+    __shared__ float sh[2][8][33];
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    const int c = blockIdx.x * 32 + lane;
     float a = 0.f, b = 0.f;
-    for (int p = 0; p < n_part; ++p) { a += part[((int64_t)p * 2) * D + c]; b += part[((int64_t)p * 2 + 1) * D + c]; }
-    dgamma[c] = Cvt<T>::from(a);
-    if (dbeta) dbeta[c] = Cvt<T>::from(b);
+    if (c < D) {
+        int p = w;
+        for (; p + 24 < n_part; p += 32) {
+            float va[4], vb[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                va[u] = part[((int64_t)(p + 8 * u) * 2) * D + c];
+                vb[u] = part[((int64_t)(p + 8 * u) * 2 + 1) * D + c];
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) { a += va[u]; b += vb[u]; }
+        }
+        for (; p < n_part; p += 8) { a += part[((int64_t)p * 2) * D + c]; b += part[((int64_t)p * 2 + 1) * D + c]; }
+    }
+    sh[0][w][lane] = a; sh[1][w][lane] = b;
+    __syncthreads();
+    if (w == 0 && c < D) {
+        a = 0.f; b = 0.f;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) { a += sh[0][k][lane]; b += sh[1][k][lane]; }
+        // accumulate: dgamma / dbeta are the parameters' gradient buffers and already hold other contributions of this step
+        if (accumulate) { a += Cvt<T>::to(dgamma[c]); if (dbeta) b += Cvt<T>::to(dbeta[c]); }
+        dgamma[c] = Cvt<T>::from(a);
+        if (dbeta) dbeta[c] = Cvt<T>::from(b);
+    }
 }
 
 }  // namespace
@@ -450,7 +476,7 @@ int ln_bwd_parts(int64_t rows) {
 
 template <typename T>
 static void ln_bwd_t(bool rms, const void* z, const void* dy, const void* gamma, const float* stats, const void* dz_in, void* dz, float* part,
-                     void* dgamma, void* dbeta, int64_t rows, int D, cudaStream_t st) {
+                     void* dgamma, void* dbeta, bool accumulate, int64_t rows, int D, cudaStream_t st) {
     const int nch = wide_nch(D, (int)sizeof(T));
     if (nch && aligned16(z) && aligned16(dy) && aligned16(gamma) && aligned16(dz_in) && aligned16(dz)) {
         const int grid = wide_grid(rows);
@@ -462,7 +488,7 @@ static void ln_bwd_t(bool rms, const void* z, const void* dy, const void* gamma,
         switch (nch) { case 1: WIDE_B(1) break; case 2: WIDE_B(2) break; case 4: WIDE_B(4) break; default: WIDE_B(8) break; }
 #undef WIDE_B
 #undef WIDE_B2
-        ln_bwd_reduce_kernel<T><<<(D + 255) / 256, 256, 0, st>>>(part, grid, D, (T*)dgamma, (T*)dbeta);
+        ln_bwd_reduce_kernel<T><<<(D + 31) / 32, 256, 0, st>>>(part, grid, D, (T*)dgamma, (T*)dbeta, accumulate);
         return;
     }
     const int parts = (int)((rows + LN_ROWS_PER_CTA - 1) / LN_ROWS_PER_CTA);
@@ -474,14 +500,14 @@ static void ln_bwd_t(bool rms, const void* z, const void* dy, const void* gamma,
         cudaFuncSetAttribute(ln_bwd_kernel<T, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         ln_bwd_kernel<T, false><<<parts, 256, smem, st>>>((const T*)z, (const T*)dy, (const T*)gamma, stats, (const T*)dz_in, (T*)dz, part, rows, D);
     }
-    ln_bwd_reduce_kernel<T><<<(D + 255) / 256, 256, 0, st>>>(part, parts, D, (T*)dgamma, (T*)dbeta);
+    ln_bwd_reduce_kernel<T><<<(D + 31) / 32, 256, 0, st>>>(part, parts, D, (T*)dgamma, (T*)dbeta, accumulate);
 }
 
 void ln_bwd(int dtype, bool rms, const void* z, const void* dy, const void* gamma, const float* stats, const void* dz_in, void* dz, float* part,
-            void* dgamma, void* dbeta, int64_t rows, int D, cudaStream_t st) {
+            void* dgamma, void* dbeta, bool accumulate, int64_t rows, int D, cudaStream_t st) {
     count_launch(2);
-    if (dtype == BF16) ln_bwd_t<__nv_bfloat16>(rms, z, dy, gamma, stats, dz_in, dz, part, dgamma, dbeta, rows, D, st);
-    else ln_bwd_t<float>(rms, z, dy, gamma, stats, dz_in, dz, part, dgamma, dbeta, rows, D, st);
+    if (dtype == BF16) ln_bwd_t<__nv_bfloat16>(rms, z, dy, gamma, stats, dz_in, dz, part, dgamma, dbeta, accumulate, rows, D, st);
+    else ln_bwd_t<float>(rms, z, dy, gamma, stats, dz_in, dz, part, dgamma, dbeta, accumulate, rows, D, st);
 }
 
 
@@ -543,13 +569,34 @@ __global__ void __launch_bounds__(256) col_sum_part_kernel(const T* __restrict__
     }
 }
 
+// Second stage: 32 columns per CTA; warp w adds the partial rows w, w + 8, ... and the 8 sub-sums are added in warp order.
 template <typename T>
-__global__ void __launch_bounds__(256) col_sum_final_kernel(const float* __restrict__ part, int parts, int C, T* __restrict__ out) {
-    const int c = blockIdx.x * 256 + threadIdx.x;
-    if (c >= C) return;
+__global__ void __launch_bounds__(256) col_sum_final_kernel(const float* __restrict__ part, int parts, int C, T* __restrict__ out,
+                                                            bool accumulate) {
+    __shared__ float sh[8][33];
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    const int c = blockIdx.x * 32 + lane;
     float t = 0.f;
-    for (int p = 0; p < parts; ++p) t += part[(int64_t)p * C + c];
-    out[c] = Cvt<T>::from(t);
+    if (c < C) {
+        int p = w;
+        for (; p + 24 < parts; p += 32) {
+            float v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) v[u] = part[(int64_t)(p + 8 * u) * C + c];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) t += v[u];
+        }
+        for (; p < parts; p += 8) t += part[(int64_t)p * C + c];
+    }
+    sh[w][lane] = t;
+    __syncthreads();
+    if (w == 0 && c < C) {
+        t = 0.f;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) t += sh[k][lane];
+        if (accumulate) t += Cvt<T>::to(out[c]);
+        out[c] = Cvt<T>::from(t);
+    }
 }
 }  // namespace
 
@@ -563,7 +610,7 @@ int col_sum_parts(int64_t rows, int C, int elem_bytes) {
     return parts < 1 ? 1 : (int)parts;
 }
 
-void col_sum(int dtype, const void* x, int64_t ld, int64_t rows, int C, float* part, void* out, cudaStream_t st) {
+void col_sum(int dtype, const void* x, int64_t ld, int64_t rows, int C, float* part, void* out, bool accumulate, cudaStream_t st) {
     const int es = dtype == F32 ? 4 : 2;
     const int parts = col_sum_parts(rows, C, es);
     const int64_t rpc = (rows + parts - 1) / parts;
@@ -573,13 +620,13 @@ void col_sum(int dtype, const void* x, int64_t ld, int64_t rows, int C, float* p
     count_launch(2);
     if (dtype == BF16) {
         col_sum_part_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, ld, rows, C, rpc, vec, part);
-        col_sum_final_kernel<__nv_bfloat16><<<(C + 255) / 256, 256, 0, st>>>(part, parts, C, (__nv_bfloat16*)out);
+        col_sum_final_kernel<__nv_bfloat16><<<(C + 31) / 32, 256, 0, st>>>(part, parts, C, (__nv_bfloat16*)out, accumulate);
     } else if (dtype == F16) {
         col_sum_part_kernel<__half><<<grid, 256, 0, st>>>((const __half*)x, ld, rows, C, rpc, vec, part);
-        col_sum_final_kernel<__half><<<(C + 255) / 256, 256, 0, st>>>(part, parts, C, (__half*)out);
+        col_sum_final_kernel<__half><<<(C + 31) / 32, 256, 0, st>>>(part, parts, C, (__half*)out, accumulate);
     } else {
         col_sum_part_kernel<float><<<grid, 256, 0, st>>>((const float*)x, ld, rows, C, rpc, vec, part);
-        col_sum_final_kernel<float><<<(C + 255) / 256, 256, 0, st>>>(part, parts, C, (float*)out);
+        col_sum_final_kernel<float><<<(C + 31) / 32, 256, 0, st>>>(part, parts, C, (float*)out, accumulate);
     }
 }
 

@@ -32,6 +32,15 @@ struct MTArgs {
 
 enum DType : int { F32 = 0, BF16 = 1, F16 = 2 };
 
+// Bounds-checked build of the multi-tensor kernels (mt_kernels.cu compiled with -DGROK_BOUNDS_CHECK): accesses beyond the driver's
+// record of each allocation are skipped and the first one is reported {count, op, role, tensor, index low, index high, is_store, 0}.
+// In the regular build these report "disabled" / zeros.
+bool bounds_check_enabled();
+void bounds_reset();
+void bounds_report(int out[8]);
+void bounds_cap(long long bytes);               // test hook: treat every allocation as at most this many bytes (-1: off)
+long long bounds_extent_of(const void* ptr);    // bytes addressable from ptr according to the driver (0: unknown)
+
 // Number of kernels of this library enqueued so far by this process (every launcher counts its launches).
 void count_launch(int n = 1);
 long long launch_count();

@@ -30,7 +30,7 @@ def _linear(x, weight, bias):
     if os.environ.get("SG_LINEAR", "cublas") == "tcgen05" and x.is_cuda and x.dtype == torch.bfloat16:
         from ..ops import gemm
         return gemm.linear(x, weight, bias)
-    return F.linear(x, weight, bias)
+    return nn_ops.linear(x, weight, bias)
 
 
 class _Attn(nn.Module):
@@ -85,10 +85,16 @@ class Transformer(nn.Module):
         self.register_buffer("pos_ids", torch.arange(seq).unsqueeze(0), persistent=False)
 
     def forward(self, x):
+        if x.is_cuda:        # token gather and (in backward) its small-table gradient kernel; final LayerNorm on the fused kernel
+            h = nn_ops.embedding(x, self.tok.weight) + self.pos(self.pos_ids[:, : x.shape[1]])
+            for l in self.layers:
+                h = l(h)
+            last = nn_ops.layer_norm(h[:, -1].contiguous(), None, self.norm.weight, self.norm.bias, self.norm.eps)
+            return _linear(last, self.out.weight, self.out.bias)
         h = self.tok(x) + self.pos(self.pos_ids[:, : x.shape[1]])
         for l in self.layers:
             h = l(h)
-        return self.out(self.norm(h[:, -1]))
+        return _linear(self.norm(h[:, -1]), self.out.weight, self.out.bias)
 
 
 class PreLNBlock(nn.Module):

@@ -4,6 +4,7 @@
     python -m supergrok15_b200.ops.bench_nn --what ce               # fused cross-entropy fwd / bwd vs F.cross_entropy
     python -m supergrok15_b200.ops.bench_nn --what norm             # RMSNorm with fused residual vs F.rms_norm(x + r)
     python -m supergrok15_b200.ops.bench_nn --what linear           # tcgen05 Linear (forward, dgrad, wgrad) vs cuBLAS on the flagship's layer shapes
+    python -m supergrok15_b200.ops.bench_nn --what small_ops        # GELU, bias-gradient column sums, small-table embedding gradient, LayerNorm backward
     ... --what linear --kernels                                      # plus the device time of every kernel of one autograd call
     ... --small                                                      # one modest shape, few iterations (profiler captures)
 
@@ -147,17 +148,55 @@ def bench_linear(small: bool, it: int):
 KERNELS = False
 
 
+def bench_small_ops(small: bool, it: int):
+    """The memory-bound kernels around the flagship decoder's GEMMs (32,768 tokens, d512, mlp 2048, 115 tokens in the table)."""
+    from . import nn_ops
+    from .. import _build
+    C = _build.require()
+    dev = torch.device("cuda:0")
+    rows, D, F4, V = (4096 if small else 32768), 512, 2048, 115
+    h = torch.randn(rows, F4, device=dev).to(torch.bfloat16).requires_grad_(True)
+    g = torch.randn(rows, F4, device=dev).to(torch.bfloat16)
+    for name, fn in (("gelu_own", nn_ops.gelu), ("gelu_torch", F.gelu)):
+        t_f = timed(lambda: fn(h), it)
+        y = fn(h)
+        t_b = timed(lambda: torch.autograd.grad(y, h, g, retain_graph=True), it)
+        print(json.dumps({"kernel": name, "rows": rows, "C": F4, "fwd_ms": t_f, "bwd_ms": t_b, "fwd_GBps": rows * F4 * 4 / t_f / 1e6,
+                          "bwd_GBps": rows * F4 * 6 / t_b / 1e6}), flush=True)
+    for Cw in (D, 3 * D, F4):
+        dy = torch.randn(rows, Cw, device=dev).to(torch.bfloat16)
+        t_o, t_r = timed(lambda: C.col_sum(dy), it), timed(lambda: dy.sum(0), it)
+        print(json.dumps({"kernel": "col_sum", "rows": rows, "C": Cw, "ms": t_o, "GBps": rows * Cw * 2 / t_o / 1e6, "torch_ms": t_r}), flush=True)
+    ids = torch.randint(0, V, (rows // 4, 4), device=dev)
+    W = torch.randn(V, D, device=dev).to(torch.bfloat16).requires_grad_(True)
+    dout = torch.randn(rows // 4, 4, D, device=dev).to(torch.bfloat16)
+    t_o = timed(lambda: C.embedding_bwd(ids, dout, V), it)
+    e = F.embedding(ids, W)
+    t_r = timed(lambda: torch.autograd.grad(e, W, dout, retain_graph=True), it)
+    print(json.dumps({"kernel": "embedding_bwd_small_table", "tokens": rows, "V": V, "D": D, "ms": t_o, "torch_ms": t_r}), flush=True)
+    x = torch.randn(rows, D, device=dev).to(torch.bfloat16).requires_grad_(True)
+    r = torch.randn(rows, D, device=dev).to(torch.bfloat16).requires_grad_(True)
+    w = torch.ones(D, device=dev, dtype=torch.bfloat16, requires_grad=True)
+    b = torch.zeros(D, device=dev, dtype=torch.bfloat16, requires_grad=True)
+    gy = torch.randn(rows, D, device=dev).to(torch.bfloat16)
+    y = nn_ops.layer_norm(x, r, w, b)
+    t_o = timed(lambda: torch.autograd.grad(y, (x, r, w, b), gy, retain_graph=True), it)
+    y2 = F.layer_norm(x + r, (D,), w, b)
+    t_r = timed(lambda: torch.autograd.grad(y2, (x, r, w, b), gy, retain_graph=True), it)
+    print(json.dumps({"kernel": "layernorm_residual_bwd", "rows": rows, "D": D, "ms": t_o, "torch_ms": t_r}), flush=True)
+
+
 def main():
     global KERNELS
     ap = argparse.ArgumentParser()
     ap.add_argument("--kernels", action="store_true", help="linear: also list the device time of every kernel of one autograd call (torch.profiler)")
-    ap.add_argument("--what", default="flash", choices=["flash", "ce", "norm", "linear", "all"])
+    ap.add_argument("--what", default="flash", choices=["flash", "ce", "norm", "linear", "small_ops", "all"])
     ap.add_argument("--small", action="store_true")
     ap.add_argument("--iters", type=int, default=None)
     a = ap.parse_args()
     KERNELS = a.kernels
     it = a.iters or (2 if a.small else 20)
-    for name, fn in (("flash", bench_flash), ("ce", bench_ce), ("norm", bench_norm), ("linear", bench_linear)):
+    for name, fn in (("flash", bench_flash), ("ce", bench_ce), ("norm", bench_norm), ("linear", bench_linear), ("small_ops", bench_small_ops)):
         if a.what in (name, "all"):
             fn(a.small, it)
 

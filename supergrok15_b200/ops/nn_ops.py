@@ -8,10 +8,14 @@
 ``swiglu(gate, up)``                silu(gate) * up in one pass; ``gelu(x)`` exact GELU.
 ``embedding(ids, weight)``          row gather; the gradient is a deterministic sorted segment sum (no atomics).
 ``cross_entropy(logits, target)``   mean softmax cross-entropy with ``ignore_index``; forward reads the logits once.
+``linear(x, w, b)`` / ``grad_sink``  F.linear whose backward, inside a ``grad_sink`` block, adds the weight and bias gradients
+                                    straight into ``w.grad`` / ``b.grad`` (the wgrad GEMM runs with beta = 1 on a side stream,
+                                    next to the dgrad GEMM) instead of returning them for a separate accumulation kernel.
 All fall back to the equivalent PyTorch expression on CPU tensors (used by the CPU tests as the oracle).
 """
 from __future__ import annotations
 
+import contextlib
 from typing import Optional
 
 import torch
@@ -54,6 +58,44 @@ def attention_small(qkv: torch.Tensor, n_heads: int, causal: bool = True) -> tor
     return _AttnSmall.apply(qkv, n_heads, causal)
 
 
+class _GradSink:
+    """State of the gradient sink.  While ``on``, the backward functions of this module add parameter gradients to the
+    parameters' ``.grad`` tensors themselves and return None for them: autograd then launches no accumulation kernel (one per
+    parameter otherwise) and allocates no temporary.  ``stream``: side stream of the weight-gradient GEMMs; ``keep`` holds
+    their operands until the main stream has waited for them, so the caching allocator cannot hand the memory out earlier."""
+
+    def __init__(self):
+        self.on, self.stream, self.forked, self.keep = False, None, False, []
+
+    def join(self):
+        if self.forked:
+            torch.cuda.current_stream().wait_stream(self.stream)
+            self.forked = False
+        self.keep = []
+
+
+_SINK = _GradSink()
+
+
+@contextlib.contextmanager
+def grad_sink(enabled: bool = True, side_stream: Optional["torch.cuda.Stream"] = None):
+    """Inside the block, ``linear`` and ``layer_norm`` write parameter gradients in place (see ``_GradSink``).  The caller
+    guarantees that every ``.grad`` involved exists, is zero or holds this step's earlier contributions, and that nothing
+    relies on autograd's accumulation hooks.  Leaving the block joins the side stream."""
+    prev = (_SINK.on, _SINK.stream)
+    _SINK.on, _SINK.stream = enabled, side_stream
+    try:
+        yield _SINK
+    finally:
+        _SINK.join()
+        _SINK.on, _SINK.stream = prev
+
+
+def _sink_target(p: Optional[torch.Tensor], like: torch.Tensor) -> Optional[torch.Tensor]:
+    g = None if p is None else p.grad
+    return g if g is not None and g.dtype == like.dtype and g.is_contiguous() and g.device == like.device else None
+
+
 class _LayerNorm(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, residual, weight, bias, eps, rms=False):
@@ -61,13 +103,72 @@ class _LayerNorm(torch.autograd.Function):
         y, z, stats = C.ln_fwd(x.contiguous(), residual, weight, bias, eps, rms)
         ctx.save_for_backward(z, weight, stats)
         ctx.has_bias, ctx.has_res, ctx.rms = bias is not None, residual is not None, rms
+        ctx.params = (weight, bias)
         return y
 
     @staticmethod
     def backward(ctx, dy):
         z, weight, stats = ctx.saved_tensors
-        dz, dg, db = _build.require().ln_bwd(z, dy, weight, stats, ctx.has_bias, ctx.rms)
+        C = _build.require()
+        if _SINK.on:
+            gw, gb = _sink_target(ctx.params[0], z), _sink_target(ctx.params[1], z)
+            if gw is not None and (gb is not None or not ctx.has_bias):
+                dz = C.ln_bwd(z, dy, weight, stats, ctx.has_bias, ctx.rms, None, gw, gb)[0]
+                return dz, (dz if ctx.has_res else None), None, None, None, None
+        dz, dg, db = C.ln_bwd(z, dy, weight, stats, ctx.has_bias, ctx.rms)
         return dz, (dz if ctx.has_res else None), dg, (db if ctx.has_bias else None), None, None
+
+
+class _LinearSink(torch.autograd.Function):
+    """F.linear; the backward adds dW = dy^T x into ``weight.grad`` with the GEMM's beta = 1 and db into ``bias.grad``, on the
+    sink's side stream when it has one, while the dgrad GEMM runs on the main stream."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias):
+        ctx.save_for_backward(x, weight)
+        ctx.params = (weight, bias)
+        return F.linear(x, weight, bias)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, weight = ctx.saved_tensors
+        wp, bp = ctx.params
+        dy2, x2 = dy.reshape(-1, dy.shape[-1]), x.reshape(-1, x.shape[-1])
+        gw = _sink_target(wp, dy2) if _SINK.on else None
+        gb = _sink_target(bp, dy2) if _SINK.on else None
+        if gw is None or (bp is not None and gb is None):
+            dx = (dy2 @ weight).view(x.shape) if ctx.needs_input_grad[0] else None
+            return dx, dy2.t() @ x2, (dy2.sum(0) if bp is not None else None)
+        _SINK.join()                                   # the previous layer's side work becomes a dependency; its operands are released
+        side = _SINK.stream if dy2.is_cuda else None
+        if side is not None:
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                _LinearSink._param_grads(gw, gb, dy2, x2)
+            _SINK.keep, _SINK.forked = [dy2, x2], True
+        else:
+            _LinearSink._param_grads(gw, gb, dy2, x2)
+        dx = (dy2 @ weight).view(x.shape) if ctx.needs_input_grad[0] else None
+        return dx, None, None
+
+
+def _param_grads(gw, gb, dy2, x2):
+    gw.addmm_(dy2.t(), x2)                                             # the GEMM's beta = 1: no temporary, no separate add
+    if gb is not None:
+        if dy2.is_cuda and dy2.stride(-1) == 1 and dy2.dtype in (torch.bfloat16, torch.float32, torch.float16):
+            _build.require().col_sum(dy2, gb)                          # two-stage fp32 column sum added to the bias gradient
+        else:
+            gb.add_(dy2.sum(0))
+
+
+_LinearSink._param_grads = staticmethod(_param_grads)
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``F.linear``; inside a ``grad_sink`` block (CUDA) the parameter gradients go straight into ``.grad``."""
+    if _SINK.on and torch.is_grad_enabled() and weight.requires_grad and weight.grad is not None:
+        return _LinearSink.apply(x, weight, bias)
+    return F.linear(x, weight, bias)
 
 
 def layer_norm(x: torch.Tensor, residual: Optional[torch.Tensor], weight: torch.Tensor, bias: Optional[torch.Tensor],
@@ -244,12 +345,16 @@ class _Embedding(torch.autograd.Function):
     def forward(ctx, ids, weight):
         ids = ids.contiguous()
         ctx.save_for_backward(ids)
-        ctx.vocab = weight.shape[0]
+        ctx.vocab, ctx.table = weight.shape[0], weight
         return _build.require().embedding_fwd(ids, weight)
 
     @staticmethod
     def backward(ctx, dout):
         (ids,) = ctx.saved_tensors
+        gw = _sink_target(ctx.table, dout) if _SINK.on else None
+        if gw is not None:
+            _build.require().embedding_bwd(ids, dout, ctx.vocab, gw)
+            return None, None
         return None, _build.require().embedding_bwd(ids, dout, ctx.vocab)
 
 

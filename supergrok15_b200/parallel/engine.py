@@ -187,6 +187,7 @@ class ZeroEngine:
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.epoch = 0
         self._calls = 0                                                  # steps started so far (start-up steps wait longer for their peers)
+        self._sink_stream = None                                         # side stream of the weight-gradient GEMMs (see _fwd_bwd)
         # the status word is copied to pinned host memory after every step and looked at before the next one is launched
         self._status_host = torch.zeros(1, dtype=torch.int32).pin_memory() if self.cuda else None
         self._status_event = None
@@ -667,20 +668,26 @@ class ZeroEngine:
         self.zero_grad()
         total = None
         chunks = list(zip(x.chunk(micro_batches), y.chunk(micro_batches)))
-        for k, (xb, yb) in enumerate(chunks):
-            if self.overlap and k == len(chunks) - 1:
-                self._arm()                                           # the gradients of this backward pass complete the step
-            logits = self.model(xb)
-            if logits.dim() == 3:                                     # language modelling: one target per position
-                logits, yb = logits.reshape(-1, logits.shape[-1]), yb.reshape(-1)
-            if self.criterion is None:                                # reads the low-precision logits directly (fp32 arithmetic inside)
-                loss = nn_ops.cross_entropy(logits, yb)
-            else:
-                loss = self.criterion(logits.float(), yb)
-            if micro_batches > 1:
-                loss = loss / micro_batches
-            loss.backward()
-            total = loss.detach() if total is None else total + loss.detach()
+        # Parameter gradients are added to the flat buffer by the backward kernels themselves (no accumulation kernel per
+        # parameter; weight-gradient GEMMs on a side stream).  Not with overlap: its buckets fire from autograd's accumulation hooks.
+        sink = self.cuda and not self.overlap and os.environ.get("SG_GRAD_SINK", "1") != "0"
+        if sink and self._sink_stream is None:
+            self._sink_stream = torch.cuda.Stream(self.device)
+        with nn_ops.grad_sink(sink, self._sink_stream if sink else None):
+            for k, (xb, yb) in enumerate(chunks):
+                if self.overlap and k == len(chunks) - 1:
+                    self._arm()                                       # the gradients of this backward pass complete the step
+                logits = self.model(xb)
+                if logits.dim() == 3:                                 # language modelling: one target per position
+                    logits, yb = logits.reshape(-1, logits.shape[-1]), yb.reshape(-1)
+                if self.criterion is None:                            # reads the low-precision logits directly (fp32 arithmetic inside)
+                    loss = nn_ops.cross_entropy(logits, yb)
+                else:
+                    loss = self.criterion(logits.float(), yb)
+                if micro_batches > 1:
+                    loss = loss / micro_batches
+                loss.backward()
+                total = loss.detach() if total is None else total + loss.detach()
         return total
 
     def _fwd_bwd_graphed(self, x: torch.Tensor, y: torch.Tensor, micro_batches: int, with_step: bool = False) -> torch.Tensor:

@@ -1,5 +1,6 @@
 """GPU tests: every sm_100a kernel against the plain-PyTorch fp32 oracle of the same op."""
 import copy
+import os
 
 import pytest
 import torch
@@ -363,3 +364,46 @@ def test_recycling_with_a_narrow_expert_width_uses_the_host_routine():
     torch.cuda.synchronize()
     assert all(bool(torch.isfinite(p).all()) for p in model.parameters())
     assert int(opt.meta_net.expert_counts.sum()) < 4 * 6 * sum(p.numel() for p in model.parameters())     # cleared at step 5
+
+
+def test_bounds_checked_build_of_the_elementwise_kernels(tmp_path):
+    """The multi-tensor kernels rebuilt with -DGROK_BOUNDS_CHECK run the edge-size oracle tests (1 ... 8193 elements, three dtypes,
+    every element-wise optimizer) with one allocation per tensor: no access leaves its allocation, and a deliberately understated
+    extent is caught, skipped and reported (see the test below, which the child process runs last)."""
+    import subprocess
+    import sys
+    from supergrok15_b200 import _build
+    if _build.require().bounds_check_enabled():
+        pytest.skip("already inside the checked build")
+    so = _build.build_bounds_checked(tmp_path)
+    env = dict(os.environ, SG_EXT_SO=str(so), PYTORCH_NO_CUDA_MEMORY_CACHING="1")
+    r = subprocess.run([sys.executable, "-m", "pytest", __file__, "-q", "-x", "-m", "gpu", "-p", "no:cacheprovider",
+                        "-k", "elementwise_optimizer_matches_oracle or looksam_ops or zz_bounds_report"],
+                       env=env, capture_output=True, text=True, timeout=1500)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-2000:]
+    assert " passed" in r.stdout and "zz_bounds_report" not in r.stdout.split("short test summary")[-1]
+
+
+def test_zz_bounds_report_is_clean_and_catches_an_understated_extent():
+    """Checked build only.  After the tests above ran in this process, no violation was recorded.  Then every allocation is
+    declared 12,288 bytes long while AdamW steps a 4,096-float tensor: elements from 3,072 on are flagged, left untouched, and
+    the report names the tensor and an index in that range; nothing outside real memory is ever addressed."""
+    from supergrok15_b200 import _build
+    C = _build.require()
+    if not C.bounds_check_enabled():
+        pytest.skip("regular build")
+    assert C.bounds_report()[0] == 0, C.bounds_report()
+    p = torch.nn.Parameter(torch.zeros(4096, device="cuda"))
+    p.grad = torch.ones(4096, device="cuda")
+    assert C.bounds_extent_of(p.data) >= 4096 * 4
+    C.bounds_reset()
+    C.bounds_cap(12288)
+    try:
+        O.AdamW([p], lr=1e-2).step()
+        rep = C.bounds_report()
+    finally:
+        C.bounds_cap(-1)
+        C.bounds_reset()
+    count, _, role, tensor, lo, hi, _, _ = rep
+    assert count > 0 and tensor == 0 and 0 <= role < 7 and hi == 0 and 3072 <= lo < 4096, rep
+    assert bool((p.detach()[3072:] == 0).all()) and bool((p.detach()[:3072] != 0).all())

@@ -94,11 +94,12 @@ def test_swiglu_gelu(dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_embedding(dtype):
+@pytest.mark.parametrize("V,D", [(300, 128), (115, 520), (5000, 128)])     # small tables: one kernel without a sort; the last one sorts
+def test_embedding(dtype, V, D):
+    from supergrok15_b200 import _build
     from supergrok15_b200.ops import nn_ops
     dev = _dev()
     torch.manual_seed(3)
-    V, D = 300, 128
     W = torch.randn(V, D, device=dev, dtype=dtype, requires_grad=True)
     ids = torch.randint(0, V, (7, 1000), device=dev)
     ids[0, :200] = 5                                   # a long run of one token
@@ -113,6 +114,10 @@ def test_embedding(dtype):
     W.grad = None
     nn_ops.embedding(ids, W).backward(g)
     assert torch.equal(first, W.grad), "embedding gradient must be bitwise reproducible"
+    base = torch.randn(V, D, device=dev, dtype=dtype)                       # accumulation into an existing gradient buffer
+    acc = base.clone()
+    assert _build.require().embedding_bwd(ids, g, V, acc).data_ptr() == acc.data_ptr()
+    torch.testing.assert_close(acc.float(), ref + base.float(), **tol)
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])

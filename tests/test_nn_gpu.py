@@ -69,3 +69,31 @@ def test_col_sum_matches_fp32_sum(rows, C, dtype):
         assert out.dtype == dtype and out.shape == (C,)
         assert torch.allclose(out.float(), ref, rtol=tol, atol=tol * rows ** 0.5), (out.float() - ref).abs().max()
         assert torch.equal(out, _build.require().col_sum(x))                 # fixed summation order: bitwise reproducible
+
+
+@pytest.mark.parametrize("side_stream", [False, True])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_grad_sink_equals_autograd_accumulation(dtype, side_stream):
+    """Inside ``grad_sink`` the Linear and LayerNorm backward kernels add the parameter gradients to ``.grad`` themselves (weight
+    gradients on a side stream): after two backward passes every ``.grad`` equals what autograd's own accumulation produces."""
+    import copy
+    from supergrok15_b200.models import Transformer
+    torch.manual_seed(3)
+    a = Transformer(2, 128, 4, 99, 4).cuda().to(dtype)
+    b = copy.deepcopy(a)
+    x = torch.randint(0, 99, (256, 4), device="cuda")
+    y = torch.randint(0, 99, (256,), device="cuda")
+    for p in list(a.parameters()) + list(b.parameters()):
+        p.grad = torch.zeros_like(p)
+    stream = torch.cuda.Stream() if side_stream else None
+    with nn_ops.grad_sink(True, stream):
+        for k in range(2):
+            F.cross_entropy(a(x[k::2]).float(), y[k::2]).backward()
+    for k in range(2):
+        F.cross_entropy(b(x[k::2]).float(), y[k::2]).backward()
+    torch.cuda.synchronize()
+    for (n, p), q in zip(a.named_parameters(), b.parameters()):
+        scale = q.grad.float().abs().max().item() + 1e-12
+        tol = 1e-5 if dtype == torch.float32 else 1.6e-2          # bf16: the second pass is added in fp32 before rounding, autograd rounds twice
+        assert (p.grad.float() - q.grad.float()).abs().max().item() <= tol * scale, n
+        assert p.grad.float().abs().max().item() > 0, n

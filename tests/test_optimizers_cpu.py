@@ -503,3 +503,25 @@ def test_soft_head_with_native_tail_matches_torch_tail(monkeypatch):
     assert set(res["native"][1]) == set(res["torch"][1])
     for k, gt in res["torch"][1].items():
         assert (res["native"][1][k] - gt).abs().max() <= 1e-3 * gt.abs().max() + 1e-9, k
+
+
+def test_grad_sink_linear_adds_into_existing_grads():
+    """``nn_ops.linear`` inside ``grad_sink``: weight and bias gradients are added to the tensors already in ``.grad`` and autograd
+    receives None for them; outside the block (or without a ``.grad``) it is plain ``F.linear``."""
+    from supergrok15_b200.ops import nn_ops
+    torch.manual_seed(0)
+    w = torch.randn(6, 5, requires_grad=True)
+    b = torch.randn(6, requires_grad=True)
+    x = torch.randn(3, 4, 5, requires_grad=True)
+    (F.linear(x, w, b) ** 2).sum().backward()
+    gw, gb, gx = w.grad.clone(), b.grad.clone(), x.grad.clone()
+    w.grad, b.grad, x.grad = torch.ones_like(w), torch.ones_like(b), None
+    held = (w.grad, b.grad)
+    with nn_ops.grad_sink(True):
+        (nn_ops.linear(x, w, b) ** 2).sum().backward()
+    assert w.grad is held[0] and b.grad is held[1]
+    assert torch.allclose(w.grad, gw + 1, atol=1e-5) and torch.allclose(b.grad, gb + 1, atol=1e-5) and torch.allclose(x.grad, gx, atol=1e-5)
+    w.grad, b.grad, x.grad = None, None, None
+    with nn_ops.grad_sink(True):                                    # no .grad to add to: autograd's own path
+        (nn_ops.linear(x, w, b) ** 2).sum().backward()
+    assert torch.allclose(w.grad, gw, atol=1e-5) and torch.allclose(b.grad, gb, atol=1e-5)

@@ -69,7 +69,8 @@ class DecoderBlock(nn.Module):
     def forward(self, x):
         if x.is_cuda:                    # LayerNorm(x + sublayer) with the add fused into the normalisation kernel
             x = nn_ops.layer_norm(x, self.attn(x), self.n1.weight, self.n1.bias, self.n1.eps)
-            h = F.gelu(_linear(x, self.ff[0].weight, self.ff[0].bias))
+            u = _linear(x, self.ff[0].weight, self.ff[0].bias)
+            h = nn_ops.gelu(u) if u.dtype != torch.float32 else F.gelu(u)   # 16-bit: the kernel with the cheaper erf
             return nn_ops.layer_norm(x, _linear(h, self.ff[2].weight, self.ff[2].bias), self.n2.weight, self.n2.bias, self.n2.eps)
         x = self.n1(x + self.attn(x))
         return self.n2(x + self.ff(x))

@@ -195,3 +195,22 @@ def test_flash_attention_backward(shape):
     for got, ref in zip((q, k, v), (qr, kr, vr)):
         err = float((got.grad.float() - ref.grad).abs().max() / ref.grad.abs().max())
         assert err < 2e-2, err
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_gelu_16bit_rational_erf_is_within_one_ulp(dtype):
+    """16-bit GELU uses a rational erf approximation (absolute error 1.5e-7): forward and derivative stay within one unit in the
+    last place of the 16-bit result of the fp64 erf formula over [-12, 12], tails included."""
+    from supergrok15_b200.ops import nn_ops
+    dev = _dev()
+    x = torch.linspace(-12, 12, 8 * 40001, device=dev).to(dtype).requires_grad_(True)
+    xd = x.detach().double()
+    cdf = 0.5 * (1 + torch.erf(xd / 2 ** 0.5))
+    ref = xd * cdf
+    dref = cdf + xd * torch.exp(-0.5 * xd * xd) / (2 * torch.pi) ** 0.5
+    y = nn_ops.gelu(x)
+    y.backward(torch.ones_like(y))
+    ulp = 2.0 ** (-8 if dtype == torch.bfloat16 else -11)
+    for got, want in ((y, ref), (x.grad, dref)):
+        err = (got.double() - want).abs()
+        assert bool((err <= ulp * want.abs() + 2e-6).all()), (err - ulp * want.abs()).max().item()

@@ -453,6 +453,8 @@ def run_reference(args, rank, world, local):
 
 
 def main():
+    import faulthandler
+    faulthandler.enable()                            # a fatal signal in any rank leaves the Python stack of every thread in the log
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
@@ -487,10 +489,21 @@ def main():
         else:
             raise
     if rank == 0:
-        print(json.dumps(res))
+        print(json.dumps(res), flush=True)
+    sys.stdout.flush()
+    sys.stderr.flush()
     if world > 1:
+        # Nobody leaves while another rank still computes or prints; then every rank ends WITHOUT interpreter finalisation.
+        # At interpreter exit the destructors of CUDA graphs, side streams, peer mappings and NCCL communicators run in no
+        # defined order across the processes: one of four 8-GPU runs lost a rank to SIGSEGV there, after its work was done, and
+        # the launcher then killed rank 0 before it had printed its line.  The driver frees everything when the process ends.
         import torch.distributed as dist
-        dist.destroy_process_group()
+        try:
+            torch.cuda.synchronize()
+            dist.barrier()
+        except Exception:  # noqa: BLE001
+            pass
+        os._exit(0)
 
 
 if __name__ == "__main__":

@@ -466,6 +466,7 @@ void register_sg2(pybind11::module_& m) {
     m.def("sg2_upload_weights", &sg2_upload_weights);
     m.def("sg2_sort", &sg2_sort);
     m.def("sg2_layout", &sg2_layout);
+    m.def("sg2_scan_ctas_per_sm", []() { return sg::sg2_scan_ctas_per_sm(); });
     m.def("sg2_recycle", &sg2_recycle_b, py::arg("counts"), py::arg("W1"), py::arg("b1"), py::arg("W2"), py::arg("b2"), py::arg("keys_a"),
           py::arg("keys_b"), py::arg("threshold"), py::arg("seed"), py::arg("call"), py::arg("info"));
     m.def("sg2_scan_backward", &sg2_scan_backward, py::arg("items"), py::arg("n_items"), py::arg("dir1_start"), py::arg("tds"), py::arg("n_td"),

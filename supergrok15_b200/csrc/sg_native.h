@@ -199,5 +199,6 @@ constexpr int MAX_RANKS = 8;
 constexpr int STATUS_OK = 0;
 constexpr int STATUS_TIMEOUT = 1;     // status word = STATUS_TIMEOUT | (peer << 8) | (site << 16)
 struct PeerPtrs { void* p[MAX_RANKS]; };
+int sg2_scan_ctas_per_sm();          // resident CTAs per SM the scan kernel is compiled for (the host sizes its chunks in whole waves)
 void write_words(uint32_t* dst, const uint32_t* host_words, int n, cudaStream_t s);
 }  // namespace sg

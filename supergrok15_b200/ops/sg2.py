@@ -23,14 +23,20 @@ from . import oracle
 # take about the same time, so the items should fill WHOLE waves of that many: one item too many starts a second wave that costs as
 # much as the first.  One wave for small steps (longer chunks: the per-chunk aggregate pass of phase 1 costs a fixed ~300 timesteps
 # per chunk), two for large ones.
-_WAVE_ITEMS = 148 * 4 * 8
 _MIN_CHUNK = 512
+
+
+def _wave_items() -> int:
+    C = _build.load()
+    ctas = C.sg2_scan_ctas_per_sm() if C is not None and hasattr(C, "sg2_scan_ctas_per_sm") else 4
+    return 148 * ctas * 8
 
 
 def _pick_chunk_len(numels: Sequence[int]) -> int:
     total2 = 2 * sum(numels)
-    waves = 1 if total2 <= _WAVE_ITEMS * 2048 else 2
-    cap = _WAVE_ITEMS * waves - 8                     # the forward-direction items are padded to a multiple of 8
+    wave = _wave_items()
+    waves = 1 if total2 <= wave * 2048 else 2
+    cap = wave * waves - 8                            # the forward-direction items are padded to a multiple of 8
     L = max(_MIN_CHUNK, -(-total2 // cap))
     L = -(-L // 16) * 16
     while 2 * sum(max(1, -(-n // L)) for n in numels) > cap and L < (1 << 30):      # partial last chunks of the tensors must fit as well

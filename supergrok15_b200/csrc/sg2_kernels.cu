@@ -36,11 +36,9 @@ constexpr int TILE_T = 16;                 // timesteps per tile
 constexpr int ROW = 52;                    // floats per timestep row in shared memory: B[16] C[16] (g,s,-,-) out[16]; 13 float4 (odd) keeps 128-bit stores conflict free
 constexpr int SCAN_THREADS = 128;          // 8 items per CTA
 #ifndef SG_SCAN_MINB
-#define SG_SCAN_MINB 4                     // resident CTAs per SM the scan kernel is compiled for (register cap 65536 / (128 * MINB))
+#define SG_SCAN_MINB 3                     // resident CTAs per SM the scan kernel is compiled for (phase 3 at 18.9 M parameters: 6.07 / 6.00 / 6.39 ms with 2 / 3 / 4)
 #endif
-#ifndef SG_SCAN_UNROLL
-#define SG_SCAN_UNROLL 1                   // timesteps of phase 3 unrolled together
-#endif
+
 constexpr int ITEMS_PER_CTA = SCAN_THREADS / 16;
 
 __device__ __forceinline__ float softplus20(float x) { return x > 20.f ? x : __logf(1.f + __expf(x)); }
@@ -245,27 +243,11 @@ struct ColConst {
     }
 };
 
-#ifndef SG_SCAN_PIPE
-#define SG_SCAN_PIPE 0
-#endif
-// Everything of one timestep of column j that does not depend on the state.
-struct StepCoef { float abe[8], abo[8], cs[8], sn[8], dtx, gz, dx; };
-
-template <int DIR>
-__device__ __forceinline__ void step_coeffs(const ColConst<DIR>& cc, const float* __restrict__ row, StepCoef& k) {
-    const float2 v = *reinterpret_cast<const float2*>(row + 32);
-    const float x = fmaf(cc.ux[0], v.x, fmaf(cc.ux[1], v.y, cc.ux[2]));
-    const float z = fmaf(cc.uz[0], v.x, fmaf(cc.uz[1], v.y, cc.uz[2]));
-    const float dt = softplus20(fmaf(cc.ud[0], v.x, fmaf(cc.ud[1], v.y, cc.ud[2])));
-    k.dtx = dt * x; k.gz = silu(z); k.dx = cc.Dj * x;
-#pragma unroll
-    for (int p = 0; p < 8; ++p) pair_coeffs(dt, cc.ah[2 * p], cc.ah[2 * p + 1], cc.f[p], k.abe[p], k.abo[p], k.cs[p], k.sn[p]);
-}
-
 // PHASE 3: run a chunk forward from its carry-in; apply SiLU gate, D skip and out_proj; write the contexts.
 // The recurrence stays scalar with sin.approx / cos.approx on the special-function unit: two rewrites that take the sincos off
 // that unit (packed f32x2 arithmetic over pairs of RoPE pairs; degree-5 / degree-6 polynomials for |theta| <= 0.25) were measured
-// at 18.9 M parameters and ran this phase in 23.5 ms and 24.2 ms against 6.4 ms for this form.
+// at 18.9 M parameters and ran this phase in 23.5 ms and 24.2 ms against 6.4 ms for this form; so did a hand-made software
+// pipeline that computes the coefficients of step l + 1 during the recurrence of step l (10.5 ms at two CTAs per SM, 34.8 ms at three).
 template <int DIR>
 __device__ void scan_phase3(const Item& it, const TensorDir* __restrict__ tds, const float2* __restrict__ gs,
                             const uint32_t* __restrict__ vals_sorted, const float* __restrict__ carry, float* __restrict__ ctx,
@@ -283,39 +265,7 @@ __device__ void scan_phase3(const Item& it, const TensorDir* __restrict__ tds, c
         const int cnt = (it.ue - u0 < TILE_T) ? (it.ue - u0) : TILE_T;
         stage_a<DIR>(tile, gs, it.off, it.n, u0 + j, j < cnt, j);
         __syncwarp(hmask);
-#if SG_SCAN_PIPE
-        // Software pipeline over the timesteps of the tile: the transition coefficients of step l + 1 (which do not depend on the
-        // state: 27 special-function results) are computed while the recurrence of step l runs on the FMA pipe.
-        StepCoef cur, nxt;
-        step_coeffs<DIR>(cc, tile, cur);
-        for (int l = 0; l < cnt; ++l) {                 // lane j = column
-            float* row = tile + l * ROW;
-            step_coeffs<DIR>(cc, tile + ((l + 1 < TILE_T) ? l + 1 : l) * ROW, nxt);       // beyond cnt: computed from stale rows, never used
-            float B[16], C[16];
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                const float4 t = reinterpret_cast<const float4*>(row)[q];
-                B[4 * q] = t.x; B[4 * q + 1] = t.y; B[4 * q + 2] = t.z; B[4 * q + 3] = t.w;
-                const float4 c = reinterpret_cast<const float4*>(row + 16)[q];
-                C[4 * q] = c.x; C[4 * q + 1] = c.y; C[4 * q + 2] = c.z; C[4 * q + 3] = c.w;
-            }
-            float y0 = 0.f, y1 = 0.f;
-#pragma unroll
-            for (int p = 0; p < 8; ++p) {
-                const float he = h[2 * p], ho = h[2 * p + 1];
-                const float ne = fmaf(cur.abe[p], he * cur.cs[p] - ho * cur.sn[p], cur.dtx * B[2 * p]);
-                const float no = fmaf(cur.abo[p], ho * cur.cs[p] + he * cur.sn[p], cur.dtx * B[2 * p + 1]);
-                h[2 * p] = ne; h[2 * p + 1] = no;
-                y0 = fmaf(ne, C[2 * p], y0);
-                y1 = fmaf(no, C[2 * p + 1], y1);
-            }
-            row[36 + j] = fmaf(y0 + y1, cur.gz, cur.dx);  // out_j of this timestep
-            cur = nxt;
-        }
-#else
-        constexpr int UNROLL = SG_SCAN_UNROLL;
-#pragma unroll UNROLL
-        for (int l = 0; l < cnt; ++l) {                 // lane j = column
+        for (int l = 0; l < cnt; ++l) {                 // lane j = column (unrolling two timesteps together was measured 4 % slower)
             float* row = tile + l * ROW;
             const float2 v = *reinterpret_cast<const float2*>(row + 32);
             const float x = fmaf(cc.ux[0], v.x, fmaf(cc.ux[1], v.y, cc.ux[2]));
@@ -343,7 +293,6 @@ __device__ void scan_phase3(const Item& it, const TensorDir* __restrict__ tds, c
             }
             row[36 + j] = fmaf(y, silu(z), cc.Dj * x);    // out_j of this timestep
         }
-#endif
         __syncwarp(hmask);
         if (j < cnt) {                                    // lane = timestep again: ctx = out_proj . out at the ORIGINAL index
             const float* row = tile + j * ROW;

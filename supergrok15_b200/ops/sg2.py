@@ -19,7 +19,7 @@ import torch
 from .. import _build
 from . import oracle
 
-# Scan items that are resident at once: 148 SMs x 4 CTAs (112 registers, 26.6 KB shared memory each) x 8 items per CTA.  All chunks
+# Scan items that are resident at once: 148 SMs x the CTAs per SM the kernel is compiled for (three; 26.6 KB shared memory each) x 8 items per CTA.  All chunks
 # take about the same time, so the items should fill WHOLE waves of that many: one item too many starts a second wave that costs as
 # much as the first.  One wave for small steps (longer chunks: the per-chunk aggregate pass of phase 1 costs a fixed ~300 timesteps
 # per chunk), two for large ones.

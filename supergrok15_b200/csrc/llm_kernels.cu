@@ -101,7 +101,7 @@ __device__ __forceinline__ void gelu8(const float (&a)[8], const float (&d)[8], 
         if constexpr (sizeof(T) == 2) {
             const float z = fabsf(a[k]) * 0.70710678118654752f;
             e = __expf(-z * z);
-            const float t = __frcp_rn(fmaf(0.3275911f, z, 1.f));
+            const float t = __fdividef(1.f, fmaf(0.3275911f, z, 1.f));      // approximate reciprocal: one special-function result
             const float poly = t * fmaf(t, fmaf(t, fmaf(t, fmaf(t, 1.061405429f, -1.453152027f), 1.421413741f), -0.284496736f), 0.254829592f);
             const float half_tail = 0.5f * poly * e;                 // (1 - erf(|z|)) / 2
             cdf = a[k] >= 0.f ? 1.f - half_tail : half_tail;

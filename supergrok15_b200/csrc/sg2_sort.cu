@@ -19,7 +19,13 @@ namespace {
 
 constexpr int SORT_THREADS = 256;
 constexpr int SORT_WARPS = SORT_THREADS / 32;
-constexpr int SORT_IPT = 16;                          // items per thread
+#ifndef SG_SORT_IPT
+#define SG_SORT_IPT 16
+#endif
+#ifndef SG_SORT_MINB
+#define SG_SORT_MINB 3                  // resident CTAs per SM of the scatter (80 registers): 1,014 -> 839 us per step at 18.9 M keys
+#endif
+constexpr int SORT_IPT = SG_SORT_IPT;                  // items per thread
 constexpr int SORT_TILE = SORT_THREADS * SORT_IPT;    // 4096 keys per CTA
 constexpr int MAX_SEG = 4096;
 
@@ -38,8 +44,8 @@ __device__ __forceinline__ uint32_t digit_of(uint32_t key, uint32_t val, int pas
     return ((uint32_t)seg_of(val, seg_off, n_seg) >> (8 * (pass - 4))) & 0xffu;
 }
 
-// warp w of the CTA owns the contiguous range [tile + w*512, tile + (w+1)*512); item r of lane l is
-// tile + w*512 + r*32 + l, so (warp, round, lane) order equals index order: ranking in that order is stable.
+// warp w of the CTA owns the contiguous range [tile + w*32*IPT, tile + (w+1)*32*IPT); item r of lane l is
+// tile + w*32*IPT + r*32 + l, so (warp, round, lane) order equals index order: ranking in that order is stable.
 __global__ void __launch_bounds__(SORT_THREADS) sort_hist_kernel(const uint32_t* __restrict__ keys,
                                                                  const uint32_t* __restrict__ vals, uint32_t* __restrict__ hist,
                                                                  const int64_t* __restrict__ seg_off, int n_seg, int64_t total,
@@ -91,7 +97,7 @@ __global__ void __launch_bounds__(256) sort_scan_rows_kernel(uint32_t* __restric
 // shared memory in their digit order inside the tile; the tile is then written out entry by entry, so that the entries of one
 // digit - which go to consecutive global positions - are stored by consecutive lanes (runs of ~16 keys = 64 bytes instead of
 // isolated 4-byte writes).
-__global__ void __launch_bounds__(SORT_THREADS) sort_scatter_kernel(const uint32_t* __restrict__ keys_in,
+__global__ void __launch_bounds__(SORT_THREADS, SG_SORT_MINB) sort_scatter_kernel(const uint32_t* __restrict__ keys_in,
                                                                     const uint32_t* __restrict__ vals_in,
                                                                     uint32_t* __restrict__ keys_out, uint32_t* __restrict__ vals_out,
                                                                     const uint32_t* __restrict__ hist,
@@ -123,12 +129,18 @@ __global__ void __launch_bounds__(SORT_THREADS) sort_scatter_kernel(const uint32
     const int64_t wbase = tile0 + (int64_t)w * (32 * SORT_IPT);
     const int n_tile = (int)((total - tile0 < SORT_TILE) ? total - tile0 : SORT_TILE);
     uint32_t k[SORT_IPT], v[SORT_IPT], d[SORT_IPT], rk[SORT_IPT];
+    // all 32 loads of the thread are issued before the ranking starts: the warp votes below are scheduling barriers, and with the
+    // loads inside that loop every round waited for its own pair (ncu: 10 cycles of long-scoreboard stall per issued instruction)
 #pragma unroll
     for (int r = 0; r < SORT_IPT; ++r) {
         const int64_t i = wbase + r * 32 + lane;
         const bool ok = i < total;
         k[r] = ok ? keys_in[i] : 0u;
         v[r] = ok ? vals_in[i] : 0u;
+    }
+#pragma unroll
+    for (int r = 0; r < SORT_IPT; ++r) {
+        const bool ok = wbase + r * 32 + lane < total;
         d[r] = ok ? digit_of(k[r], v[r], pass, seg_off, n_seg) : 0xffffffffu;
         const uint32_t peers = __match_any_sync(0xffffffffu, d[r]);
         const int leader = __ffs(peers) - 1;

@@ -163,6 +163,11 @@ def bench_small_ops(small: bool, it: int):
         t_b = timed(lambda: torch.autograd.grad(y, h, g, retain_graph=True), it)
         print(json.dumps({"kernel": name, "rows": rows, "C": F4, "fwd_ms": t_f, "bwd_ms": t_b, "fwd_GBps": rows * F4 * 4 / t_f / 1e6,
                           "bwd_GBps": rows * F4 * 6 / t_b / 1e6}), flush=True)
+    out = torch.empty_like(g)
+    t_c = timed(lambda: out.copy_(g), it)
+    t_a = timed(lambda: torch.add(g, 1.0, out=out), it)
+    print(json.dumps({"kernel": "torch_copy_and_add_same_shape", "rows": rows, "C": F4, "copy_ms": t_c, "copy_GBps": rows * F4 * 4 / t_c / 1e6,
+                      "add_ms": t_a, "add_GBps": rows * F4 * 4 / t_a / 1e6}), flush=True)
     for Cw in (D, 3 * D, F4):
         dy = torch.randn(rows, Cw, device=dev).to(torch.bfloat16)
         t_o, t_r = timed(lambda: C.col_sum(dy), it), timed(lambda: dy.sum(0), it)

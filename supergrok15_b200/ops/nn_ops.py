@@ -359,7 +359,8 @@ class _Embedding(torch.autograd.Function):
 
 
 def embedding(ids: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
-    if not _native_ok(weight) or not weight.is_contiguous() or (weight.shape[1] * weight.element_size()) % 16 or weight.shape[1] % 8:
+    if (not _native_ok(weight) or not weight.is_contiguous() or (weight.shape[1] * weight.element_size()) % 16 or weight.shape[1] % 8
+            or ids.dtype != torch.int64 or ids.device != weight.device):
         return F.embedding(ids, weight)
     return _Embedding.apply(ids, weight)
 

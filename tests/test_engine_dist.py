@@ -47,7 +47,11 @@ def test_ownership_is_deterministic_and_balanced():
     numels = [786432, 1536, 262144, 512, 512, 512, 1048576, 2048, 1048576, 512, 512, 512] * 6 + [50688, 2048, 512, 512, 50688, 99]
     own = assign_tensors(numels, 8)
     assert own == assign_tensors(list(numels), 8)
-    assert imbalance(numels, own, 8) < 1.15
+    assert imbalance(numels, own, 8) < 1.03          # greedy alone leaves 1.10: the local search after it must run
+    for w in (1, 2, 3, 4):
+        o = assign_tensors(numels, w)
+        assert len(o) == len(numels) and set(o) == set(range(w)) and imbalance(numels, o, w) < 1.02
+    assert assign_tensors([5], 4) == [0] and assign_tensors([], 3) == []
     offs, regions, total = grouped_layout(numels, own, 8)
     assert all(o % 8 == 0 for o in offs) and regions[0][0] == 0 and regions[-1][1] == total
     for r, (b, e) in enumerate(regions):

@@ -13,6 +13,9 @@ void embed_fwd(int dtype, const int64_t* ids, const void* W, void* out, int64_t 
 void embed_keys(const int64_t* ids, uint32_t* keys, uint32_t* vals, int64_t T_tok, int V, cudaStream_t st);
 void embed_bwd(int dtype, const uint32_t* keys, const uint32_t* vals, const void* dout, void* dW, int64_t T_tok, int D, cudaStream_t st);
 bool embed_bwd_small_ok(int64_t T_tok, int V);
+int embed_bwd_table_splits(int64_t T_tok, int D, int V);
+void embed_bwd_table(int dtype, const int64_t* ids, const void* dout, float* part, void* dW, int64_t T_tok, int D, int V, int S, bool accumulate,
+                     cudaStream_t st);
 void embed_bwd_small(int dtype, const int64_t* ids, const void* dout, void* dW, int64_t T_tok, int D, int V, bool accumulate, cudaStream_t st);
 void ce_fwd(int dtype, const void* logits, const int64_t* target, float* lse, float* loss, float* mean_out, int64_t rows, int V, int64_t ignore_index,
             cudaStream_t st);
@@ -115,6 +118,13 @@ Tensor embedding_bwd(const Tensor& ids, const Tensor& dout_, int64_t V, const c1
     c10::cuda::CUDAGuard guard(dout.device());
     auto st = at::cuda::getCurrentCUDAStream();
     auto io = dout.options().dtype(at::kInt);
+    if (const int S = sg::embed_bwd_table_splits(T_tok, D, (int)V)) {     // table fits shared memory: per-split tables + ordered sum
+        Tensor out = acc.has_value() ? *acc : at::empty({V, D}, dout.options());
+        Tensor part = at::empty({S, V, D}, dout.options().dtype(at::kFloat));
+        sg::embed_bwd_table(dtype_code(dout), ids.data_ptr<int64_t>(), dout.data_ptr(), part.data_ptr<float>(), out.data_ptr(), T_tok, D, (int)V, S,
+                            acc.has_value(), st);
+        return out;
+    }
     if (sg::embed_bwd_small_ok(T_tok, (int)V)) {                         // small table: one kernel, no sort, no zero fill
         Tensor out = acc.has_value() ? *acc : at::empty({V, D}, dout.options());
         sg::embed_bwd_small(dtype_code(dout), ids.data_ptr<int64_t>(), dout.data_ptr(), out.data_ptr(), T_tok, D, (int)V, acc.has_value(), st);

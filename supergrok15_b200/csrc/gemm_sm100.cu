@@ -405,6 +405,14 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tn_kernel(const __grid_c
                         if (ep.bias && n0 + c + h + lane < N)
                             bias_l = ep.bias_is_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(ep.bias)[n0 + c + h + lane])
                                                      : reinterpret_cast<const float*>(ep.bias)[n0 + c + h + lane];
+                        // alpha and bias only (a Linear forward): one FMA per element, no per-element branches.  The general loop
+                        // below took 360 us for a 32768 x 1536 x 512 product with a bias against 50 us without one.
+                        const bool simple = (ep.D == nullptr) && ep.diag == 0.f && ep.act == 0;
+                        if (simple) {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                r[j] = __float_as_uint(fmaf(ep.alpha, __uint_as_float(r[j]), __shfl_sync(0xffffffffu, bias_l, j)));
+                        } else
 #pragma unroll
                         for (int j = 0; j < 32; ++j) {
                             const int col = n0 + c + h + j;

@@ -223,6 +223,51 @@ __global__ void __launch_bounds__(256) embed_bwd_small_kernel(const int64_t* __r
     }
 }
 
+// Tables of at most EMB_TAB_V rows (the modular-arithmetic vocabularies) whatever the token statistics: the kernel above walks the
+// matches of one id serially, and in those datasets two ids ("op", "=") occur in every sequence.  Here CTA (split s, slab) walks a
+// contiguous range of token positions in order; thread c adds dout[t][slab * 256 + c] into ITS column of a [V][256] fp32 table in
+// shared memory (row = id of token t): no conflicts, no atomics, a fixed order.  The S partial tables are then added in split order.
+constexpr int EMB_TAB_V = 208;                     // 208 x 256 x 4 B = 208 KB of shared memory
+template <typename T>
+__global__ void __launch_bounds__(256) embed_bwd_table_kernel(const int64_t* __restrict__ ids, const T* __restrict__ dout, float* __restrict__ part,
+                                                              int64_t T_tok, int D, int V, int S) {
+    extern __shared__ float tab[];                 // [V][256]; thread c only ever touches column c
+    const int c = blockIdx.y * 256 + threadIdx.x;
+    for (int v = 0; v < V; ++v) tab[v * 256 + threadIdx.x] = 0.f;
+    const int64_t per = (T_tok + S - 1) / S;
+    const int64_t t0 = (int64_t)blockIdx.x * per, t1 = (t0 + per < T_tok) ? t0 + per : T_tok;
+    if (c < D) {
+        int64_t t = t0;
+        for (; t + 8 <= t1; t += 8) {              // eight rows in flight; the table is updated in position order
+            int id[8]; float x[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                int64_t i = ids[t + u];
+                id[u] = (int)(i < 0 ? 0 : (i >= V ? V - 1 : i));
+                x[u] = Cvt<T>::to(dout[(t + u) * D + c]);
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) tab[id[u] * 256 + threadIdx.x] += x[u];
+        }
+        for (; t < t1; ++t) {
+            int64_t i = ids[t];
+            const int id = (int)(i < 0 ? 0 : (i >= V ? V - 1 : i));
+            tab[id * 256 + threadIdx.x] += Cvt<T>::to(dout[t * D + c]);
+        }
+        for (int v = 0; v < V; ++v) part[((int64_t)blockIdx.x * V + v) * D + c] = tab[v * 256 + threadIdx.x];
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) embed_bwd_table_reduce_kernel(const float* __restrict__ part, T* __restrict__ dW, int64_t VD, int S, bool accumulate) {
+    const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
+    if (i >= VD) return;
+    float a = 0.f;
+    for (int s = 0; s < S; ++s) a += part[(int64_t)s * VD + i];
+    if (accumulate) a += Cvt<T>::to(dW[i]);
+    dW[i] = Cvt<T>::from(a);
+}
+
 // ------------------------------------------------------------------------------------------------ cross-entropy
 // One CTA per row of logits [rows, V] (V a multiple of 8).  Forward: log-sum-exp (online max) and the row loss lse - x[target];
 // rows whose target equals ignore_index contribute nothing.
@@ -356,6 +401,28 @@ void embed_bwd(int dtype, const uint32_t* keys, const uint32_t* vals, const void
     if (T_tok <= 0) return;
     count_launch();
     DISPATCH_T(dtype, embed_bwd_kernel<T><<<(unsigned)((T_tok + 7) / 8), 256, 0, st>>>(keys, vals, (const T*)dout, (T*)dW, T_tok, D);)
+}
+
+// splits of the token range for the table kernel: enough CTAs to fill the GPU, at least 64 positions each
+int embed_bwd_table_splits(int64_t T_tok, int D, int V) {
+    if (V <= 0 || V > EMB_TAB_V || T_tok <= 0) return 0;
+    const int slabs = (D + 255) / 256;
+    int64_t S = (2 * 148 + slabs - 1) / slabs;
+    if (S > 64) S = 64;
+    if (S > (T_tok + 63) / 64) S = (T_tok + 63) / 64;
+    return (int)(S < 1 ? 1 : S);
+}
+
+void embed_bwd_table(int dtype, const int64_t* ids, const void* dout, float* part, void* dW, int64_t T_tok, int D, int V, int S, bool accumulate,
+                     cudaStream_t st) {
+    count_launch(2);
+    const dim3 grid((unsigned)S, (unsigned)((D + 255) / 256));
+    const size_t smem = (size_t)V * 256 * sizeof(float);
+    const int64_t VD = (int64_t)V * D;
+    DISPATCH_T(dtype,
+        cudaFuncSetAttribute(embed_bwd_table_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        embed_bwd_table_kernel<T><<<grid, 256, smem, st>>>(ids, (const T*)dout, part, T_tok, D, V, S);
+        embed_bwd_table_reduce_kernel<T><<<(unsigned)((VD + 255) / 256), 256, 0, st>>>(part, (T*)dW, VD, S, accumulate);)
 }
 
 bool embed_bwd_small_ok(int64_t T_tok, int V) { return V > 0 && V <= 65535 && T_tok * (int64_t)V <= ((int64_t)1 << 24); }

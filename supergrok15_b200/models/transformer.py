@@ -25,11 +25,8 @@ from ..ops import nn_ops
 
 
 def _linear(x, weight, bias):
-    """nn.Linear forward.  With SG_LINEAR=tcgen05 (and bf16 CUDA tensors) the three GEMMs of the layer run on the
-    hand-written tcgen05 kernel instead of cuBLAS."""
-    if os.environ.get("SG_LINEAR", "cublas") == "tcgen05" and x.is_cuda and x.dtype == torch.bfloat16:
-        from ..ops import gemm
-        return gemm.linear(x, weight, bias)
+    """nn.Linear forward: ``nn_ops.linear`` (gradient sink inside the engine; SG_LINEAR=tcgen05 puts the three GEMMs of the layer
+    on the hand-written tcgen05 kernel instead of cuBLAS)."""
     return nn_ops.linear(x, weight, bias)
 
 

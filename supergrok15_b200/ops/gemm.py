@@ -24,15 +24,16 @@ def _err_flag(dev) -> torch.Tensor:
     return t
 
 
-_ws: Dict[torch.device, torch.Tensor] = {}
+_ws: Dict[tuple, torch.Tensor] = {}
 
 
-def _splitk_ws(dev) -> torch.Tensor:
-    """64 MB fp32 scratch for split-K partial tiles (used when the output has too few tiles to fill the GPU)."""
-    t = _ws.get(dev)
+def _splitk_ws(dev, slot: int = 0) -> torch.Tensor:
+    """64 MB fp32 scratch for split-K partial tiles (used when the output has too few tiles to fill the GPU).  ``slot``: GEMMs
+    that may run at the same time on different streams take different scratch buffers."""
+    t = _ws.get((dev, slot))
     if t is None:
         t = torch.empty(16 * 1024 * 1024, dtype=torch.float32, device=dev)
-        _ws[dev] = t
+        _ws[(dev, slot)] = t
     return t
 
 
@@ -48,16 +49,17 @@ def check(dev=None) -> None:
 
 def gemm_tn(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None, *, alpha: float = 1.0, beta: float = 0.0,
             d: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None, diag: float = 0.0, act=None,
-            out_dtype=torch.bfloat16, out_t: Optional[torch.Tensor] = None, a_t: bool = False, b_t: bool = False) -> torch.Tensor:
+            out_dtype=torch.bfloat16, out_t: Optional[torch.Tensor] = None, a_t: bool = False, b_t: bool = False,
+            ws_slot: int = 0) -> torch.Tensor:
     """``a_t`` / ``b_t``: the operand is passed transposed (``a`` as [K, M], ``b`` as [K, N]) and read in place through an
-    MN-major descriptor; supported combinations: none, ``b_t``, ``a_t and b_t``."""
+    MN-major descriptor; supported combinations: none, ``b_t``, ``a_t and b_t``.  ``ws_slot``: which split-K scratch to use."""
     C = _build.require()
     if out is None:
         n = b.shape[1 if b_t else 0]
         q = 8 if out_dtype == torch.bfloat16 else 4          # the output is written by TMA: 16-byte row pitch
         npad = -(-n // q) * q
         out = torch.empty(a.shape[1 if a_t else 0], npad, dtype=out_dtype, device=a.device)[:, :n]
-    C.gemm_tn(a, b, out, alpha, beta, d, bias, diag, ACT[act], out_t, _err_flag(a.device), _splitk_ws(a.device), a_t, b_t)
+    C.gemm_tn(a, b, out, alpha, beta, d, bias, diag, ACT[act], out_t, _err_flag(a.device), _splitk_ws(a.device, ws_slot), a_t, b_t)
     return out
 
 

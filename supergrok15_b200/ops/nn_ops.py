@@ -16,6 +16,7 @@ All fall back to the equivalent PyTorch expression on CPU tensors (used by the C
 from __future__ import annotations
 
 import contextlib
+import os
 from typing import Optional
 
 import torch
@@ -119,14 +120,27 @@ class _LayerNorm(torch.autograd.Function):
         return dz, (dz if ctx.has_res else None), dg, (db if ctx.has_bias else None), None, None
 
 
+def _tc_linear_ok(x2: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor]) -> bool:
+    """Shapes the tcgen05 GEMM takes without copies: bf16, 16-byte row pitches, at least one full tile of rows."""
+    return (x2.is_cuda and x2.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x2.shape[0] >= 128 and x2.shape[1] % 8 == 0
+            and weight.shape[0] % 8 == 0 and x2.is_contiguous() and weight.is_contiguous() and (bias is None or bias.dtype == torch.bfloat16))
+
+
 class _LinearSink(torch.autograd.Function):
     """F.linear; the backward adds dW = dy^T x into ``weight.grad`` with the GEMM's beta = 1 and db into ``bias.grad``, on the
-    sink's side stream when it has one, while the dgrad GEMM runs on the main stream."""
+    sink's side stream when it has one, while the dgrad GEMM runs on the main stream.  With SG_LINEAR=tcgen05 the three GEMMs
+    run on the hand-written tcgen05 kernel (bias in the forward epilogue, W / dy / x read where they are through MN-major
+    descriptors, beta = 1 accumulation in the wgrad epilogue) instead of cuBLAS."""
 
     @staticmethod
     def forward(ctx, x, weight, bias):
         ctx.save_for_backward(x, weight)
         ctx.params = (weight, bias)
+        x2 = x.reshape(-1, x.shape[-1])
+        ctx.tc = os.environ.get("SG_LINEAR", "cublas") == "tcgen05" and _tc_linear_ok(x2, weight, bias)
+        if ctx.tc:
+            from . import gemm
+            return gemm.gemm_tn(x2, weight, bias=bias, out_dtype=torch.bfloat16).view(*x.shape[:-1], weight.shape[0])
         return F.linear(x, weight, bias)
 
     @staticmethod
@@ -139,21 +153,33 @@ class _LinearSink(torch.autograd.Function):
         if gw is None or (bp is not None and gb is None):
             dx = (dy2 @ weight).view(x.shape) if ctx.needs_input_grad[0] else None
             return dx, dy2.t() @ x2, (dy2.sum(0) if bp is not None else None)
+        tc = ctx.tc and dy2.is_contiguous()
         _SINK.join()                                   # the previous layer's side work becomes a dependency; its operands are released
         side = _SINK.stream if dy2.is_cuda else None
         if side is not None:
             side.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(side):
-                _LinearSink._param_grads(gw, gb, dy2, x2)
+                _param_grads(gw, gb, dy2, x2, tc)
             _SINK.keep, _SINK.forked = [dy2, x2], True
         else:
-            _LinearSink._param_grads(gw, gb, dy2, x2)
-        dx = (dy2 @ weight).view(x.shape) if ctx.needs_input_grad[0] else None
+            _param_grads(gw, gb, dy2, x2, tc)
+        dx = None
+        if ctx.needs_input_grad[0]:
+            if tc:
+                from . import gemm
+                dx = gemm.gemm_tn(dy2, weight, out_dtype=torch.bfloat16, b_t=True).view(x.shape)      # dy [M,N] @ W [N,K]
+            else:
+                dx = (dy2 @ weight).view(x.shape)
         return dx, None, None
 
 
-def _param_grads(gw, gb, dy2, x2):
-    gw.addmm_(dy2.t(), x2)                                             # the GEMM's beta = 1: no temporary, no separate add
+def _param_grads(gw, gb, dy2, x2, tc=False):
+    if tc:
+        from . import gemm
+        # dy^T [N,M] @ x [M,K] added to the gradient buffer in the epilogue; own split-K scratch: the dgrad GEMM runs concurrently
+        gemm.gemm_tn(dy2, x2, out=gw, beta=1.0, d=gw, a_t=True, b_t=True, ws_slot=1)
+    else:
+        gw.addmm_(dy2.t(), x2)                                         # the GEMM's beta = 1: no temporary, no separate add
     if gb is not None:
         if dy2.is_cuda and dy2.stride(-1) == 1 and dy2.dtype in (torch.bfloat16, torch.float32, torch.float16):
             _build.require().col_sum(dy2, gb)                          # two-stage fp32 column sum added to the bias gradient
@@ -161,13 +187,14 @@ def _param_grads(gw, gb, dy2, x2):
             gb.add_(dy2.sum(0))
 
 
-_LinearSink._param_grads = staticmethod(_param_grads)
-
-
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """``F.linear``; inside a ``grad_sink`` block (CUDA) the parameter gradients go straight into ``.grad``."""
+    """``F.linear``; inside a ``grad_sink`` block the parameter gradients go straight into ``.grad``.  SG_LINEAR=tcgen05 routes the
+    GEMMs of bf16 CUDA layers through ``csrc/gemm_sm100.cu`` (inside and outside the sink)."""
     if _SINK.on and torch.is_grad_enabled() and weight.requires_grad and weight.grad is not None:
         return _LinearSink.apply(x, weight, bias)
+    if x.is_cuda and x.dtype == torch.bfloat16 and os.environ.get("SG_LINEAR", "cublas") == "tcgen05":
+        from . import gemm
+        return gemm.linear(x, weight, bias)
     return F.linear(x, weight, bias)
 
 

@@ -5,6 +5,7 @@
 #include "mt_host.h"
 
 namespace sg {
+void gemm_plain_tile_coords(int tile, int n_tiles_m, int n_tiles_n, int* mt, int* nt);
 int gemm_bf16_tn(const void* A, int lda, const void* B, int ldb, int M, int N, int K, float alpha, float beta, const void* D, int ldd,
                  bool d_bf16, const void* bias, bool bias_bf16, float diag, int act, void* C, int ldc, bool c_bf16, void* C2, int ldc2,
                  float* splitk_ws, int64_t splitk_ws_floats, int* err, cudaStream_t s, bool a_t, bool b_t);
@@ -111,6 +112,15 @@ void gemm_tn_reducescatter(const Tensor& a, const Tensor& b, const std::vector<i
 }  // namespace
 
 void register_gemm(pybind11::module_& m) {
+    m.def("gemm_tile_order", [](int64_t n_tiles_m, int64_t n_tiles_n) {          // the plain GEMM's tile order, for host-side checks
+        std::vector<std::pair<int64_t, int64_t>> order;
+        for (int64_t t = 0; t < n_tiles_m * n_tiles_n; ++t) {
+            int mt = 0, nt = 0;
+            sg::gemm_plain_tile_coords((int)t, (int)n_tiles_m, (int)n_tiles_n, &mt, &nt);
+            order.emplace_back(mt, nt);
+        }
+        return order;
+    });
     m.def("gemm_tn", &gemm_tn, py::arg("a"), py::arg("b"), py::arg("out"), py::arg("alpha") = 1.0, py::arg("beta") = 0.0,
           py::arg("d") = c10::nullopt, py::arg("bias") = c10::nullopt, py::arg("diag") = 0.0, py::arg("act") = 0,
           py::arg("out_t") = c10::nullopt, py::arg("err"), py::arg("splitk_ws") = c10::nullopt, py::arg("a_t") = false, py::arg("b_t") = false);

@@ -219,6 +219,7 @@ void register_llm(pybind11::module_& m) {
     m.def("gelu_fwd", &gelu_fwd);
     m.def("gelu_bwd", &gelu_bwd);
     m.def("embedding_fwd", &embedding_fwd);
+    m.def("embedding_bwd_table_splits", [](int64_t tokens, int64_t D, int64_t V) { return (int64_t)sg::embed_bwd_table_splits(tokens, (int)D, (int)V); });
     m.def("embedding_bwd", &embedding_bwd, py::arg("ids"), py::arg("dout"), py::arg("vocab"), py::arg("acc") = c10::optional<Tensor>());
     m.def("flash_fwd", &flash_fwd, py::arg("q"), py::arg("k"), py::arg("v"), py::arg("causal"), py::arg("err"), py::arg("variant") = 3);
     m.def("flash_bwd", &flash_bwd);

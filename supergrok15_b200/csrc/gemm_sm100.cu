@@ -127,7 +127,7 @@ __device__ __forceinline__ void red_release_sys_add(int* p, int v) {
 // then cover a near-square patch (16 A panels x ~9 B panels instead of ~5 x all n panels), and B is streamed from DRAM once per
 // group of 16 tile rows instead of once per tile row (n fastest re-read the operands ~7x at 8192 x 8192 x 4096).
 constexpr int RASTER_GM = 16;
-__device__ __forceinline__ void plain_tile_coords(int tl, int n_tiles_m, int n_tiles_n, int& mt, int& nt) {
+__host__ __device__ __forceinline__ void plain_tile_coords(int tl, int n_tiles_m, int n_tiles_n, int& mt, int& nt) {
     const int per_group = RASTER_GM * n_tiles_n;
     const int first_m = (tl / per_group) * RASTER_GM;
     const int gsz = (n_tiles_m - first_m < RASTER_GM) ? n_tiles_m - first_m : RASTER_GM;
@@ -619,6 +619,10 @@ int launch(const void* A, int lda, const void* B, int ldb, int M, int N, int K, 
 }
 
 }  // namespace
+
+// (tile row, tile column) of work item `tile` of the plain GEMM, as the kernel computes it: lets the host check that the order
+// visits every tile exactly once.
+void gemm_plain_tile_coords(int tile, int n_tiles_m, int n_tiles_n, int* mt, int* nt) { plain_tile_coords(tile, n_tiles_m, n_tiles_n, *mt, *nt); }
 
 // C = act(alpha * A[M,K] . B[N,K]^T + beta * D + bias + diag*I); A, B bf16 with leading dimensions lda / ldb (elements, multiples of 8).
 // a_t / b_t: the operand is passed transposed, as a [K, M] resp. [K, N] row-major matrix (supported: none, b_t, a_t && b_t).

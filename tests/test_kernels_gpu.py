@@ -407,3 +407,28 @@ def test_zz_bounds_report_is_clean_and_catches_an_understated_extent():
     count, _, role, tensor, lo, hi, _, _ = rep
     assert count > 0 and tensor == 0 and 0 <= role < 7 and hi == 0 and 3072 <= lo < 4096, rep
     assert bool((p.detach()[3072:] == 0).all()) and bool((p.detach()[:3072] != 0).all())
+
+
+def test_sg2_memory_does_not_grow_between_phases():
+    """Peak memory of a second 100-step phase of SuperGrok v2 stays within 10 % of the first (the reference's own growth check,
+    tests/test_supergrok2.py:386-419): the workspaces are allocated once and expert recycling (step 100) adds nothing."""
+    torch.manual_seed(0)
+    model = torch.nn.Sequential(torch.nn.Linear(16, 32), torch.nn.ReLU(), torch.nn.Linear(32, 10)).cuda()
+    opt = O.SuperGrok2(model.parameters(), lr=1e-3)
+    x = torch.randn(64, 16, device="cuda")
+    y = torch.randint(0, 10, (64,), device="cuda")
+
+    def phase(n):
+        torch.cuda.synchronize()
+        torch.cuda.reset_peak_memory_stats()
+        for _ in range(n):
+            opt.zero_grad()
+            F.cross_entropy(model(x), y).backward()
+            opt.step(train_acc=0.5)
+        torch.cuda.synchronize()
+        return torch.cuda.max_memory_allocated()
+
+    phase(5)                                         # lazy state and workspaces
+    first, second = phase(100), phase(100)
+    assert second <= 1.10 * first, (first, second)
+    assert all(torch.isfinite(p).all().item() for p in model.parameters())

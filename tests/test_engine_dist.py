@@ -74,6 +74,20 @@ def test_sharded_equals_unsharded_cpu_gloo(optimizer):
 
 
 @pytest.mark.dist
+@pytest.mark.parametrize("optimizer", ["supergrok2", "adamw"])
+def test_sharded_equals_unsharded_cpu_gloo_world4(optimizer):
+    """Four gloo ranks (16 rows each): tensor ownership after the balancing search, grouped layout and the scalar reductions give
+    the parameters of the plain optimizer on the full batch, identical on every rank."""
+    steps = 2
+    res = _launch(4, optimizer, "cpu", "nccl", steps)
+    ref = dist_worker.reference_run(optimizer, steps)
+    for got in res["params"]:
+        assert torch.allclose(got, ref, rtol=2e-4, atol=2e-6), (got - ref).abs().max()
+    assert all(torch.equal(res["params"][0], p) for p in res["params"])
+    assert len(set(res["owner"])) == (1 if optimizer == "adamw" else 4)
+
+
+@pytest.mark.dist
 @pytest.mark.parametrize("optimizer", ["adamw+overlap", "lion+overlap", "adamw+overlap2"])
 def test_bucketed_overlap_equals_unsharded_cpu_gloo(optimizer):
     """The step issued bucket by bucket from gradient hooks (asynchronous all-reduce per bucket on this path) gives the

@@ -525,3 +525,25 @@ def test_grad_sink_linear_adds_into_existing_grads():
     with nn_ops.grad_sink(True):                                    # no .grad to add to: autograd's own path
         (nn_ops.linear(x, w, b) ** 2).sum().backward()
     assert torch.allclose(w.grad, gw, atol=1e-5) and torch.allclose(b.grad, gb, atol=1e-5)
+
+
+def test_grad_sink_restores_its_state_on_exit_and_on_error():
+    """``grad_sink`` blocks nest and always restore the previous state, also when the body raises: a failed step must not leave later
+    backward passes writing gradients in place."""
+    from supergrok15_b200.ops import nn_ops
+    assert not nn_ops._SINK.on
+    with nn_ops.grad_sink(True):
+        assert nn_ops._SINK.on
+        with nn_ops.grad_sink(False):
+            assert not nn_ops._SINK.on
+        assert nn_ops._SINK.on
+        with pytest.raises(RuntimeError):
+            with nn_ops.grad_sink(True):
+                raise RuntimeError("step failed")
+        assert nn_ops._SINK.on
+    assert not nn_ops._SINK.on and nn_ops._SINK.stream is None and nn_ops._SINK.keep == []
+    w = torch.randn(3, 2, requires_grad=True)
+    w.grad = torch.zeros_like(w)
+    x = torch.randn(4, 2)
+    nn_ops.linear(x, w).sum().backward()                          # outside a block: autograd accumulates as usual
+    assert torch.allclose(w.grad, x.sum(0).expand(3, 2))
